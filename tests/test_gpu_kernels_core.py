@@ -1,0 +1,243 @@
+"""GPU numerics of the core kernels against the fp32 PyTorch reference."""
+import math
+
+import pytest
+import torch
+
+from vllm_gcu_b200.ops import _native, ref
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def C():
+    from vllm_gcu_b200.ops import cuda
+    return cuda
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    yield
+    if torch.cuda.is_available():
+        _native.check_status()
+
+
+def _close(a, b, rtol, atol):
+    a, b = a.float(), b.float()
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    bad = (err > tol).float().mean().item()
+    assert bad == 0.0, f"{bad:.2%} out of tolerance, max err {err.max().item():.4g}"
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 512, 4096), (1, 4096, 4096),
+                                   (77, 6144, 4096), (333, 256, 200), (1024, 28672, 4096),
+                                   (8192, 4096, 4096), (130, 136, 72)])
+def test_gemm_bf16(C, M, N, K):
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    out = C.gemm_bf16(a, b)
+    want = ref.gemm(a, b, out_dtype=torch.float32)
+    _close(out, want, 2e-2, 2e-2 * math.sqrt(K) * 0.05)
+
+
+def test_gemm_bf16_epilogues(C):
+    torch.manual_seed(1)
+    M, N, K = 200, 1024, 512
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    res = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    atol = 2e-2 * math.sqrt(K) * 0.05
+    _close(C.gemm_bf16(a, b, bias=bias), ref.gemm(a, b, bias=bias, out_dtype=torch.float32),
+           2e-2, atol)
+    _close(C.gemm_bf16(a, b, residual=res),
+           ref.gemm(a, b, residual=res, out_dtype=torch.float32), 2e-2, atol)
+    out32 = C.gemm_bf16(a, b, epilogue=C.EPI_FP32)
+    assert out32.dtype == torch.float32
+    _close(out32, ref.gemm(a, b, out_dtype=torch.float32), 1e-3, 1e-3)
+    wg, wu = b[: N // 2].contiguous(), b[N // 2:].contiguous()
+    wi = ref.interleave_gate_up(wg, wu)
+    got = C.gemm_bf16(a, wi, epilogue=C.EPI_SILU_MUL)
+    want = ref.silu_and_mul(torch.cat([ref.gemm(a, wg, out_dtype=torch.float32),
+                                       ref.gemm(a, wu, out_dtype=torch.float32)], -1))
+    _close(got, want, 3e-2, 3e-2)
+
+
+def test_gemm_bf16_strided_views(C):
+    torch.manual_seed(2)
+    big = torch.randn(300, 1024, device="cuda", dtype=torch.bfloat16)
+    a = big[:, 256:768]
+    b = (torch.randn(384, 512, device="cuda") * 0.05).to(torch.bfloat16)
+    outbuf = torch.zeros(300, 1024, device="cuda", dtype=torch.bfloat16)
+    C.gemm_bf16(a, b, out=outbuf[:, 128:512])
+    _close(outbuf[:, 128:512], ref.gemm(a, b, out_dtype=torch.float32), 2e-2, 3e-2)
+    assert outbuf[:, :128].abs().sum().item() == 0 and outbuf[:, 512:].abs().sum().item() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("T,H", [(1, 256), (7, 4096), (33, 7168), (5, 8192 + 128)])
+def test_rms_norm_family(C, dtype, T, H):
+    torch.manual_seed(3)
+    x = torch.randn(T, H, device="cuda", dtype=dtype)
+    w = (1 + 0.1 * torch.randn(H, device="cuda")).to(dtype)
+    r = torch.randn(T, H, device="cuda", dtype=dtype)
+    _close(C.norm(x, w, 1e-6), ref.rms_norm(x, w, 1e-6), 1e-2, 1e-2)
+    r2 = r.clone()
+    got = C.norm(x, w, 1e-6, residual=r2)
+    want, want_r = ref.fused_add_rms_norm(x, r, w, 1e-6)
+    _close(got, want, 1e-2, 1e-2)
+    _close(r2, want_r, 1e-2, 1e-2)
+    # dynamic group quant
+    q, s = C.norm(x, w, 1e-6, quant="fp8_group128")
+    qr, sr, _ = ref.rms_norm_quant(x, w, 1e-6, "fp8_group128")
+    _close(s, sr, 2e-2, 1e-6)
+    deq = q.float().view(T, H // 128, 128) * s[..., None]
+    deqr = qr.float().view(T, H // 128, 128) * sr[..., None]
+    _close(deq, deqr, 0.13, 0.02)
+    q, s = C.norm(x, w, 1e-6, quant="fp8_token")
+    qr, sr, _ = ref.rms_norm_quant(x, w, 1e-6, "fp8_token")
+    _close(s, sr, 2e-2, 1e-6)
+    _close(q.float() * s, qr.float() * sr, 0.13, 0.05)
+    sc = torch.tensor([0.05], device="cuda")
+    q = C.norm(x, w, 1e-6, quant="int8_static", scale=sc)
+    qr, _, _ = ref.rms_norm_quant(x, w, 1e-6, "int8_static", scale=sc)
+    assert ((q.int() - qr.int()).abs() <= 1).all()
+
+
+@pytest.mark.parametrize("act", ["silu", "gelu", "gelu_tanh", "fatrelu"])
+def test_act_and_mul(C, act):
+    torch.manual_seed(4)
+    x = torch.randn(19, 2 * 1408, device="cuda", dtype=torch.bfloat16)
+    _close(C.activation(x, act, threshold=0.1), ref.act_and_mul(x, act, 0.1), 2e-2, 2e-2)
+    if act == "silu":
+        q, s = C.activation(x, act, quant="fp8_group128")
+        qr, sr = ref.per_token_group_fp8_quant(ref.silu_and_mul(x), 128)
+        _close(s, sr, 2e-2, 1e-6)
+        n = torch.tensor([5], device="cuda", dtype=torch.int32)
+        out = torch.zeros(19, 1408, device="cuda", dtype=torch.bfloat16)
+        C.activation(x, act, out=out, valid_rows=n)
+        assert out[5:].abs().sum().item() == 0
+        _close(out[:5], ref.silu_and_mul(x[:5]), 2e-2, 2e-2)
+        _close(C.activation(x, "silu", mode="mul_act"), ref.mul_and_silu(x), 2e-2, 2e-2)
+    for name in ("gelu_new", "gelu_fast", "gelu_quick"):
+        _close(C.activation(x, name, mode="plain"), ref.activation(x, name), 2e-2, 2e-2)
+
+
+@pytest.mark.parametrize("is_neox", [True, False])
+def test_rope_and_cache_flash(C, is_neox):
+    torch.manual_seed(5)
+    T, Hq, Hkv, D, bs, nb = 37, 8, 2, 128, 16, 12
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda", dtype=torch.bfloat16)
+    q, k, v = qkv.split([Hq * D, Hkv * D, Hkv * D], dim=-1)
+    pos = torch.randint(0, 500, (T,), device="cuda")
+    cs = ref.make_cos_sin_cache(D, 512, 10000.0).cuda().to(torch.bfloat16)
+    slots = torch.randperm(nb * bs, device="cuda")[:T]
+    slots[3] = -1
+    kc = torch.zeros(nb, bs, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    q_ref, k_ref = ref.rotary_embedding(pos, q, k, D, cs, is_neox)
+    kc_r, vc_r = kc.clone(), vc.clone()
+    ref.reshape_and_cache_flash(k_ref, v, kc_r, vc_r, slots)
+    C.rope_cache_flash(q, k, v, pos, cs, is_neox, D, slots, kc, vc)
+    _close(q, q_ref, 2e-2, 2e-2)
+    _close(k, k_ref, 2e-2, 2e-2)
+    _close(kc, kc_r, 2e-2, 2e-2)
+    assert torch.equal(vc, vc_r)
+
+
+def _make_paged(B, lens, Hkv, D, bs, dtype=torch.bfloat16):
+    max_blocks = (max(lens) + bs - 1) // bs + 1
+    nb = B * max_blocks + 3
+    kc = torch.randn(nb, bs, Hkv, D, device="cuda", dtype=dtype)
+    vc = torch.randn(nb, bs, Hkv, D, device="cuda", dtype=dtype)
+    perm = torch.randperm(nb, device="cuda")[: B * max_blocks].to(torch.int32)
+    bt = perm.view(B, max_blocks).contiguous()
+    return kc, vc, bt
+
+
+@pytest.mark.parametrize("Hq,Hkv,D", [(32, 8, 128), (4, 2, 64), (8, 1, 128), (16, 16, 128)])
+@pytest.mark.parametrize("splits", [1, 3])
+def test_paged_decode(C, Hq, Hkv, D, splits):
+    torch.manual_seed(6)
+    lens = [1, 17, 64, 65, 300, 1000, 33]
+    B = len(lens)
+    kc, vc, bt = _make_paged(B, lens, Hkv, D, 16)
+    q = torch.randn(B, Hq, D, device="cuda", dtype=torch.bfloat16)
+    sl = torch.tensor(lens, device="cuda", dtype=torch.int32)
+    scale = D ** -0.5
+    got = C.paged_decode(q, kc, vc, bt, sl, scale, num_splits=splits)
+    want = ref.paged_attention_decode(q, kc, vc, bt, sl, scale)
+    _close(got, want, 2e-2, 2e-2)
+
+
+@pytest.mark.parametrize("Hq,Hkv,D", [(8, 2, 128), (4, 2, 64)])
+def test_varlen_prefill(C, Hq, Hkv, D):
+    torch.manual_seed(7)
+    q_lens = [5, 64, 130, 1, 77]
+    ctx = [0, 16, 50, 200, 3]
+    lens = [a + b for a, b in zip(q_lens, ctx)]
+    B = len(lens)
+    kc, vc, bt = _make_paged(B, lens, Hkv, D, 16)
+    T = sum(q_lens)
+    q = torch.randn(T, Hq, D, device="cuda", dtype=torch.bfloat16)
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), device="cuda",
+                      dtype=torch.int32)
+    sl = torch.tensor(lens, device="cuda", dtype=torch.int32)
+    tiles = sum((x + 63) // 64 for x in q_lens)
+    scale = D ** -0.5
+    got, lse = C.varlen_prefill(q, kc, vc, bt, cu, sl, scale, tiles, return_lse=True)
+    want, lse_r = ref.varlen_prefill_attention(q, kc, vc, bt, cu, sl, scale, return_lse=True)
+    _close(got, want, 2e-2, 2e-2)
+    _close(lse, lse_r, 1e-2, 1e-2)
+
+
+def test_sampler(C):
+    torch.manual_seed(8)
+    B, V = 9, 32000
+    logits = torch.randn(B, V, device="cuda", dtype=torch.float32) * 3
+    ids = C.sample(logits)
+    assert torch.equal(ids, logits.argmax(-1))
+    ids16 = C.sample(logits.to(torch.bfloat16))
+    assert torch.equal(ids16, logits.to(torch.bfloat16).float().argmax(-1))
+    temp = torch.full((B,), 0.8, device="cuda")
+    temp[0] = 0.0
+    k = torch.tensor([0, 1, 5, 50, 0, 0, 20, 1000, 3], device="cuda", dtype=torch.int32)
+    p = torch.tensor([1.0, 1.0, 1.0, 1.0, 0.5, 0.9, 0.7, 0.95, 1.0], device="cuda")
+    noise = torch.empty(B, V, device="cuda").exponential_()
+    got = C.sample(logits, temp, k, p, noise=noise)
+    want = ref.sample(logits, temp, k, p, noise=noise)
+    # ties at the nucleus boundary may differ by one token; the pick must be in the kept set
+    masked = ref.apply_top_k_top_p(logits / torch.where(temp > 0, temp, torch.ones_like(temp))[:, None],
+                                   k, p)
+    for b in range(B):
+        assert torch.isfinite(masked[b, got[b]]) or got[b] == want[b]
+    assert (got == want).float().mean().item() >= 0.8
+    # built-in generator: valid ids, different draws for different steps
+    seeds = torch.arange(B, device="cuda", dtype=torch.int64)
+    a = C.sample(logits, temp, k, p, seeds=seeds, step=1)
+    b2 = C.sample(logits, temp, k, p, seeds=seeds, step=1)
+    assert torch.equal(a, b2)
+    assert ((a >= 0) & (a < V)).all()
+    lg = logits.clone()
+    C.top_k_top_p_(lg, k, p)
+    kept = torch.isfinite(lg).sum(-1)
+    kept_ref = torch.isfinite(masked).sum(-1)
+    assert ((kept - kept_ref).abs() <= 2).all(), (kept, kept_ref)
+
+
+def test_advance_step(C):
+    torch.manual_seed(9)
+    n, pad, bs, mb = 50, 64, 16, 40
+    toks = torch.zeros(pad, device="cuda", dtype=torch.int64)
+    sampled = torch.randint(0, 1000, (n,), device="cuda")
+    pos = torch.zeros(pad, device="cuda", dtype=torch.int64)
+    sl = torch.randint(1, bs * mb - 1, (pad,), device="cuda", dtype=torch.int32)
+    slots = torch.zeros(pad, device="cuda", dtype=torch.int64)
+    bt = torch.randint(0, 5000, (pad, mb), device="cuda", dtype=torch.int32)
+    r = [t.clone() for t in (toks, pos, sl, slots)]
+    ref.advance_step(pad, n, bs, r[0], sampled, r[1], r[2], r[3], bt)
+    C.advance_step(pad, n, bs, toks, sampled, pos, sl, slots, bt)
+    for a, b in zip((toks, pos, sl, slots), r):
+        assert torch.equal(a, b)

@@ -1,0 +1,366 @@
+// Dense bf16 GEMM for sm_100a:  C[M,N] = A[M,K] * B[N,K]^T  (+ epilogue).
+//
+// Design
+//   * persistent kernel, one CTA per SM, static round-robin tile schedule with
+//     the M index fastest so CTAs that run at the same time share a weight tile
+//     in L2;
+//   * warp 0 = TMA producer, warp 1 = tcgen05.mma issuer and TMEM owner,
+//     warps 2..5 = epilogue (one TMEM lane quarter each);
+//   * operands are staged by TMA into 128-byte-swizzled K-major tiles
+//     (BM x 64 and BN x 64 bf16) through a STAGES-deep mbarrier ring;
+//   * accumulators live in tensor memory, double buffered (2 x BN fp32 columns)
+//     so the epilogue of tile i overlaps the main loop of tile i+1;
+//   * epilogues: plain, +bias, SiLU(gate)*up for a gate/up weight interleaved in
+//     blocks of 128 rows, +residual, fp32 output.
+//
+// Replaces the vendor matmul behind every unquantised linear layer of the
+// reference (vllm_gcu/kernels/linear.py, upstream UnquantizedLinearMethod) and
+// folds vllm_gcu/kernels/activation.py:20-32 (SiluAndMul) into the gate-up GEMM.
+#include "common.cuh"
+
+namespace b200 {
+namespace gemm {
+
+constexpr unsigned int kKernelId = 10;
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int kThreads = 192;
+
+enum Epilogue : int {
+  kEpiNone = 0,
+  kEpiBias = 1,
+  kEpiSiluMul = 2,
+  kEpiResidual = 3,
+  kEpiFp32 = 4,
+};
+
+struct Args {
+  void* C;
+  long long ldc;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* residual;
+  long long ldr;
+  int M, N, K;
+  int tiles_m, tiles_n;
+  unsigned int* status;
+};
+
+template <int BN, int STAGES>
+struct Smem {
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarOffset = STAGES * kStageBytes;
+  static constexpr int kTotal = kBarOffset + 256 + 1024;  // barriers + alignment slack
+};
+
+// Stores 32 consecutive output columns of one row (values in v[0..31]).
+__device__ __forceinline__ void store_row_bf16(__nv_bfloat16* dst, const float* v, int ncols) {
+  if (ncols >= 32) {
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint4 u;
+      u.x = pack_bf16x2(v[i * 8 + 0], v[i * 8 + 1]);
+      u.y = pack_bf16x2(v[i * 8 + 2], v[i * 8 + 3]);
+      u.z = pack_bf16x2(v[i * 8 + 4], v[i * 8 + 5]);
+      u.w = pack_bf16x2(v[i * 8 + 6], v[i * 8 + 7]);
+      d4[i] = u;
+    }
+  } else {
+    for (int i = 0; i < ncols; ++i) dst[i] = __float2bfloat16(v[i]);
+  }
+}
+
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+    gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA,
+                     const __grid_constant__ CUtensorMap tmB, const Args p) {
+  using L = Smem<BN, STAGES>;
+  constexpr uint32_t kTmemCols = 2 * BN;
+  constexpr uint32_t kIdesc = make_idesc(BM, BN, 1, 1);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 4);
+    }
+    *abort_flag = 0u;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        const int m0 = (tile % p.tiles_m) * BM;
+        const int n0 = (tile / p.tiles_m) * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, p.status, kKernelId, 0x100u + stage,
+                         abort_flag)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * L::kStageBytes;
+          uint8_t* sb = sa + L::kABytes;
+          mbar_expect_tx(&full_bar[stage], L::kStageBytes);
+          tma_load_2d(sa, &tmA, &full_bar[stage], kb * BK, m0);
+          tma_load_2d(sb, &tmB, &full_bar[stage], kb * BK, n0);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, p.status, kKernelId, 0x200u + acc,
+                       abort_flag))
+          break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, p.status, kKernelId, 0x300u + stage,
+                         abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * L::kStageBytes);
+          const uint32_t b_addr = a_addr + L::kABytes;
+          const uint64_t adesc = make_desc_k_sw128(a_addr);
+          const uint64_t bdesc = make_desc_k_sw128(b_addr);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // 16 bf16 along K = 32 bytes = 2 descriptor address units
+            umma_f16(tmem_d, adesc + static_cast<uint64_t>(k * 2),
+                     bdesc + static_cast<uint64_t>(k * 2), kIdesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&tfull_bar[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      const int m0 = (tile % p.tiles_m) * BM;
+      const int n0 = (tile / p.tiles_m) * BN;
+      if (!mbar_wait(&tfull_bar[acc], acc_phase, p.status, kKernelId, 0x400u + acc, abort_flag))
+        break;
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr =
+          tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
+
+      if constexpr (EPI == kEpiSiluMul) {
+        // tile columns [0,128) = gate block, [128,256) = matching up block
+        static_assert(EPI != kEpiSiluMul || BN == 256, "SiLU-mul epilogue needs BN = 256");
+        const int out_n0 = (n0 >> 1);
+        const int out_n = p.N >> 1;
+        __nv_bfloat16* crow =
+            reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t g[32], u[32];
+          tmem_ld_32x32(taddr + c * 32, g);
+          tmem_ld_32x32(taddr + 128 + c * 32, u);
+          tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            v[i] = silu_f(__uint_as_float(g[i])) * __uint_as_float(u[i]);
+          const int col = out_n0 + c * 32;
+          if (row_ok && col < out_n) store_row_bf16(crow + col, v, min(32, out_n - col));
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          const int col = n0 + c * 32;
+          if (!row_ok || col >= p.N) continue;
+          const int ncols = min(32, p.N - col);
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          if constexpr (EPI == kEpiBias) {
+            for (int i = 0; i < ncols; ++i) v[i] += __bfloat162float(p.bias[col + i]);
+          }
+          if constexpr (EPI == kEpiResidual) {
+            const __nv_bfloat16* rr = p.residual + static_cast<long long>(row) * p.ldr + col;
+            for (int i = 0; i < ncols; ++i) v[i] += __bfloat162float(rr[i]);
+          }
+          if constexpr (EPI == kEpiFp32) {
+            float* crow = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col;
+            if (ncols == 32) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                reinterpret_cast<float4*>(crow)[i] =
+                    make_float4(v[i * 4], v[i * 4 + 1], v[i * 4 + 2], v[i * 4 + 3]);
+            } else {
+              for (int i = 0; i < ncols; ++i) crow[i] = v[i];
+            }
+          } else {
+            __nv_bfloat16* crow =
+                reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col;
+            store_row_bf16(crow, v, ncols);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+template <int BN, int STAGES, int EPI>
+int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const Args& a, cudaStream_t stream) {
+  using L = Smem<BN, STAGES>;
+  auto kern = gemm_bf16_kernel<BN, STAGES, EPI>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e =
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured[dev] = true;
+  }
+  const int tiles = a.tiles_m * a.tiles_n;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kern<<<grid, kThreads, L::kTotal, stream>>>(tmA, tmB, a);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace gemm
+}  // namespace b200
+
+// C[M,N] (bf16, or fp32 when epi == 4) = A[M,K] * B[N,K]^T with epilogue `epi`:
+//   0 none, 1 + bias[N], 2 SiLU(gate)*up (B rows interleaved gate/up in blocks
+//   of 128; C is [M, N/2]), 3 + residual[M,N], 4 fp32 output.
+// lda / ldb / ldc / ldr are row pitches in elements.  K, lda, ldb must be
+// multiples of 8; N, ldc multiples of 8; all base pointers 16-byte aligned.
+// Returns 0 on success, a CUDA error code, or a negative argument error.
+B200_API int b200_gemm_bf16(const void* A, long long lda, const void* B, long long ldb, void* C,
+                            long long ldc, int M, int N, int K, const void* bias,
+                            const void* residual, long long ldr, int epi, void* stream) {
+  using namespace b200;
+  using namespace b200::gemm;
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K % 8) != 0 || (lda % 8) != 0 || (ldb % 8) != 0 || (N % 8) != 0 ||
+      (ldc % 8) != 0)
+    return -2;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) |
+       reinterpret_cast<uintptr_t>(C)) & 15)
+    return -3;
+  if (epi == kEpiSiluMul && (N % 256) != 0) return -4;
+  if (epi == kEpiBias && bias == nullptr) return -5;
+  if (epi == kEpiResidual && residual == nullptr) return -5;
+
+  // Wide tiles when there is enough work to fill the machine with them.
+  const int tiles_m = (M + BM - 1) / BM;
+  const bool wide = (epi == kEpiSiluMul) ||
+                    ((N % 256) == 0 && static_cast<long long>(tiles_m) * (N / 256) >= sm_count());
+  const int bn = wide ? 256 : 128;
+
+  CUtensorMap tmA, tmB;
+  int r = encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, static_cast<uint64_t>(M),
+                         static_cast<uint64_t>(K), static_cast<uint64_t>(lda) * 2, BM, BK,
+                         CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r != 0) return r < 0 ? -6 : r;
+  r = encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, static_cast<uint64_t>(N),
+                     static_cast<uint64_t>(K), static_cast<uint64_t>(ldb) * 2, bn, BK,
+                     CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r != 0) return r < 0 ? -6 : r;
+
+  Args a;
+  a.C = C;
+  a.ldc = ldc;
+  a.bias = static_cast<const __nv_bfloat16*>(bias);
+  a.residual = static_cast<const __nv_bfloat16*>(residual);
+  a.ldr = ldr;
+  a.M = M;
+  a.N = N;
+  a.K = K;
+  a.tiles_m = tiles_m;
+  a.tiles_n = (N + bn - 1) / bn;
+  a.status = status_ptr();
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+#define B200_GEMM_CASE(E)                                                       \
+  case E:                                                                       \
+    return wide ? launch<256, 4, E>(tmA, tmB, a, s) : launch<128, 6, E>(tmA, tmB, a, s);
+  switch (epi) {
+    B200_GEMM_CASE(kEpiNone)
+    B200_GEMM_CASE(kEpiBias)
+    B200_GEMM_CASE(kEpiResidual)
+    B200_GEMM_CASE(kEpiFp32)
+    case kEpiSiluMul:
+      return launch<256, 4, kEpiSiluMul>(tmA, tmB, a, s);
+    default:
+      return -7;
+  }
+#undef B200_GEMM_CASE
+}

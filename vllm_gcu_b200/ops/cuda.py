@@ -1,0 +1,357 @@
+"""Thin wrappers that launch the sm_100a kernels of ``_b200.so`` on torch tensors.
+
+All functions take CUDA tensors, launch on the current torch stream and never
+synchronise.  Argument checking that would cost a device sync is left to the
+kernels' own guards (status word, see ``_native.check_status``).
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+
+from . import _native as N
+from ._native import DTYPE_CODE, call, ptr, stream_ptr
+
+EPI_NONE, EPI_BIAS, EPI_SILU_MUL, EPI_RESIDUAL, EPI_FP32 = 0, 1, 2, 3, 4
+
+NORM_QMODES = {None: 0, "fp8_static": 1, "fp8_token": 2, "fp8_group128": 3,
+               "int8_static": 4, "int8_token": 5}
+ACT_CODES = {"silu": 0, "gelu": 1, "gelu_tanh": 2, "fatrelu": 3, "gelu_new": 4,
+             "gelu_fast": 5, "gelu_quick": 6, "identity": 7}
+ACT_QUANT = {None: 0, "fp8_group128": 1, "fp8_static": 2, "int8_static": 3, "int8_asym": 4}
+FP8 = torch.float8_e4m3fn
+
+
+def _rowmajor_2d(t: torch.Tensor) -> torch.Tensor:
+    if t.dim() != 2:
+        t = t.reshape(-1, t.shape[-1])
+    if t.stride(-1) != 1:
+        t = t.contiguous()
+    return t
+
+
+# ---------------------------------------------------------------------------
+# GEMM
+# ---------------------------------------------------------------------------
+def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None,
+              bias: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
+              epilogue: int = EPI_NONE) -> torch.Tensor:
+    """``out[M,N] = a[M,K] @ b[N,K]^T`` on the tcgen05 path (bf16 in, fp32 accumulate).
+
+    epilogue EPI_SILU_MUL expects ``b`` interleaved by ``ref.interleave_gate_up`` and
+    yields ``[M, N/2]``; EPI_FP32 writes fp32."""
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    a = _rowmajor_2d(a)
+    M, K = a.shape
+    Nn = b.shape[0]
+    assert b.shape[1] == K and b.stride(1) == 1
+    if bias is not None:
+        epilogue = EPI_BIAS
+    if residual is not None:
+        epilogue = EPI_RESIDUAL
+    out_cols = Nn // 2 if epilogue == EPI_SILU_MUL else Nn
+    if out is None:
+        out = torch.empty((M, out_cols), device=a.device,
+                          dtype=torch.float32 if epilogue == EPI_FP32 else torch.bfloat16)
+    assert out.stride(-1) == 1 and out.shape[-1] == out_cols
+    call("b200_gemm_bf16", ptr(a), a.stride(0), ptr(b), b.stride(0), ptr(out), out.stride(0),
+         M, Nn, K, ptr(bias), ptr(residual), residual.stride(0) if residual is not None else 0,
+         epilogue, stream_ptr())
+    return out
+
+
+# ---------------------------------------------------------------------------
+# norm / activation
+# ---------------------------------------------------------------------------
+def norm(x: torch.Tensor, weight: torch.Tensor, eps: float,
+         residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+         quant: Optional[str] = None, scale: Optional[torch.Tensor] = None,
+         valid_rows: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+         layer_norm: bool = False):
+    """RMSNorm / LayerNorm family.  With ``residual`` the residual tensor is updated in
+    place.  Returns ``out`` or ``(out, scales)`` for the dynamic quant modes."""
+    x2 = _rowmajor_2d(x)
+    T, H = x2.shape
+    qmode = NORM_QMODES[quant]
+    scale_out = None
+    if out is None:
+        if qmode == 0:
+            out = torch.empty_like(x2)
+        elif qmode in (1, 2, 3):
+            out = torch.empty((T, H), device=x.device, dtype=FP8)
+        else:
+            out = torch.empty((T, H), device=x.device, dtype=torch.int8)
+    if qmode in (2, 5):
+        scale_out = torch.empty((T, 1), device=x.device, dtype=torch.float32)
+    elif qmode == 3:
+        scale_out = torch.empty((T, H // 128), device=x.device, dtype=torch.float32)
+    res2 = None
+    if residual is not None:
+        res2 = residual if residual.dim() == 2 else residual.view(-1, H)
+    call("b200_norm", ptr(x2), x2.stride(0), ptr(res2), res2.stride(0) if res2 is not None else 0,
+         ptr(weight), ptr(bias), ptr(out), out.stride(0) if out.dim() == 2 else H,
+         ptr(scale_out), ptr(scale), ptr(valid_rows), T, H, float(eps), DTYPE_CODE[x.dtype],
+         qmode, int(layer_norm), stream_ptr())
+    out = out.view(x.shape) if out.shape != x.shape and out.numel() == x.numel() else out
+    return (out, scale_out) if scale_out is not None else out
+
+
+def activation(x: torch.Tensor, act: str = "silu", mode: str = "act_mul",
+               out: Optional[torch.Tensor] = None, quant: Optional[str] = None,
+               scale: Optional[torch.Tensor] = None, azp: Optional[torch.Tensor] = None,
+               valid_rows: Optional[torch.Tensor] = None, threshold: float = 0.0):
+    """Gated (``act_mul`` / ``mul_act``) or plain activation, optionally quantising."""
+    x2 = _rowmajor_2d(x)
+    T = x2.shape[0]
+    m = {"act_mul": 0, "mul_act": 1, "plain": 2}[mode]
+    d = x2.shape[1] if m == 2 else x2.shape[1] // 2
+    q = ACT_QUANT[quant]
+    scale_out = None
+    if out is None:
+        if q == 0:
+            out = torch.empty((T, d), device=x.device, dtype=x.dtype)
+        elif q in (1, 2):
+            out = torch.empty((T, d), device=x.device, dtype=FP8)
+        else:
+            out = torch.empty((T, d), device=x.device, dtype=torch.int8)
+    if q == 1:
+        scale_out = torch.empty((T, d // 128), device=x.device, dtype=torch.float32)
+    call("b200_activation", ptr(x2), x2.stride(0), ptr(out), out.stride(0), ptr(scale_out),
+         ptr(scale), ptr(azp), ptr(valid_rows), T, d, ACT_CODES[act], m, q, float(threshold),
+         DTYPE_CODE[x.dtype], stream_ptr())
+    if x.dim() != 2:
+        out = out.view(*x.shape[:-1], d)
+    return (out, scale_out) if scale_out is not None else out
+
+
+# ---------------------------------------------------------------------------
+# rope / cache
+# ---------------------------------------------------------------------------
+def rope_cache_flash(q: Optional[torch.Tensor], k: Optional[torch.Tensor],
+                     v: Optional[torch.Tensor], positions: Optional[torch.Tensor],
+                     cos_sin: Optional[torch.Tensor], is_neox: bool, head_size: int,
+                     slot_mapping: Optional[torch.Tensor] = None,
+                     k_cache: Optional[torch.Tensor] = None,
+                     v_cache: Optional[torch.Tensor] = None,
+                     k_scale: Optional[torch.Tensor] = None,
+                     v_scale: Optional[torch.Tensor] = None) -> None:
+    """In-place RoPE on q ``[T, Hq*D]`` / k ``[T, Hkv*D]`` (views with a row stride are
+    fine) and paged write of k, v into ``[blocks, bs, Hkv, D]`` caches."""
+    ref_t = q if q is not None else k
+    T = ref_t.shape[0]
+    D = head_size
+    Hq = q.shape[-1] // D if q is not None else 0
+    kv_src = k if k is not None else v
+    Hkv = kv_src.shape[-1] // D if kv_src is not None else 0
+    for t in (q, k, v):
+        assert t is None or t.stride(-1) == 1
+    slot_stride = head_stride = num_slots = 0
+    fp8 = 0
+    if slot_mapping is not None:
+        nb, bs = k_cache.shape[0], k_cache.shape[1]
+        assert k_cache.stride(1) * bs == k_cache.stride(0), "slots must be evenly strided"
+        slot_stride, head_stride, num_slots = k_cache.stride(1), k_cache.stride(2), nb * bs
+        fp8 = int(k_cache.dtype == FP8)
+    call("b200_rope_cache_flash", ptr(q), q.stride(0) if q is not None else 0, ptr(k),
+         k.stride(0) if k is not None else 0, ptr(v), v.stride(0) if v is not None else 0,
+         ptr(positions), ptr(cos_sin),
+         int(cos_sin is not None and cos_sin.dtype == torch.float32),
+         cos_sin.shape[-1] if cos_sin is not None else 0, int(is_neox), ptr(slot_mapping),
+         ptr(k_cache), ptr(v_cache), slot_stride, head_stride, num_slots, fp8, ptr(k_scale),
+         ptr(v_scale), T, Hq, Hkv, D, DTYPE_CODE[ref_t.dtype], stream_ptr())
+
+
+def reshape_and_cache(key, value, k_cache, v_cache, slot_mapping, k_scale=1.0, v_scale=1.0,
+                      k_zp=0.0, v_zp=0.0) -> None:
+    nb, H, Dx, bs, x = k_cache.shape
+    D = Dx * x
+    T = key.shape[0]
+    key = key.reshape(T, H * D)
+    value = value.reshape(T, H * D)
+    qmode = 1 if k_cache.dtype == torch.int8 else (2 if k_cache.dtype == FP8 else 0)
+    call("b200_reshape_and_cache", ptr(key), key.stride(0), ptr(value), value.stride(0),
+         ptr(k_cache), ptr(v_cache), ptr(slot_mapping), nb * bs, T, H, D, bs, x, qmode,
+         float(k_scale), float(v_scale), float(k_zp), float(v_zp), DTYPE_CODE[key.dtype],
+         stream_ptr())
+
+
+def mla_rope_cache(q_pe: Optional[torch.Tensor], kv: torch.Tensor, positions: torch.Tensor,
+                   cos_sin: torch.Tensor, weight: torch.Tensor, eps: float,
+                   kv_cache: Optional[torch.Tensor], slot_mapping: Optional[torch.Tensor],
+                   kv_lora_rank: int, is_neox: bool = False,
+                   scale: Optional[torch.Tensor] = None, q_out: Optional[torch.Tensor] = None,
+                   want_k_pe: bool = False, want_kv_c: bool = False):
+    """Fused MLA cache update.  q_pe ``[T, H, R]`` is rotated in place unless ``q_out``
+    (``[T, H, *]`` view whose last R columns receive the result) is given."""
+    T = kv.shape[0]
+    L = kv_lora_rank
+    R = kv.shape[-1] - L
+    assert cos_sin.dtype == torch.float32
+    k_pe_out = torch.empty((T, R), device=kv.device, dtype=kv.dtype) if want_k_pe else None
+    kv_c_out = torch.empty((T, L), device=kv.device, dtype=kv.dtype) if want_kv_c else None
+    H = q_pe.shape[1] if q_pe is not None else 0
+    slot_stride = num_slots = 0
+    fp8 = 0
+    if kv_cache is not None:
+        W = kv_cache.shape[-1]
+        flat = kv_cache.view(-1, W)
+        slot_stride, num_slots = flat.stride(0), flat.shape[0]
+        fp8 = int(kv_cache.dtype == FP8)
+    call("b200_mla_rope_cache", ptr(q_pe), q_pe.stride(0) if q_pe is not None else 0,
+         q_pe.stride(1) if q_pe is not None else 0, ptr(q_out),
+         q_out.stride(0) if q_out is not None else 0,
+         q_out.stride(1) if q_out is not None else 0, ptr(kv), kv.stride(0), None, None,
+         ptr(kv_cache), slot_stride, num_slots, ptr(k_pe_out), ptr(kv_c_out), ptr(positions),
+         ptr(cos_sin), ptr(weight), ptr(slot_mapping if kv_cache is not None else None),
+         ptr(scale), T, H, L, R, float(eps), int(is_neox), fp8, DTYPE_CODE[kv.dtype],
+         stream_ptr())
+    return k_pe_out, kv_c_out
+
+
+def concat_and_cache_mla(kv_c, k_pe, kv_cache, slot_mapping, scale=None) -> None:
+    T, L = kv_c.shape
+    k_pe = k_pe.reshape(T, -1).contiguous()
+    kv_c = kv_c.contiguous()
+    R = k_pe.shape[-1]
+    W = kv_cache.shape[-1]
+    flat = kv_cache.view(-1, W)
+    call("b200_mla_rope_cache", None, 0, 0, None, 0, 0, None, 0, ptr(kv_c), ptr(k_pe),
+         ptr(kv_cache), flat.stride(0), flat.shape[0], None, None, None, None, None,
+         ptr(slot_mapping), ptr(scale), T, 0, L, R, 0.0, 0, int(kv_cache.dtype == FP8),
+         DTYPE_CODE[kv_c.dtype], stream_ptr())
+
+
+def gather_cache(src_cache, block_table, cu_seq_lens, total_tokens: int, seq_starts=None,
+                 out=None) -> torch.Tensor:
+    nb, bs = src_cache.shape[0], src_cache.shape[1]
+    W = src_cache.shape[2:].numel()
+    flat = src_cache.view(nb * bs, W)
+    if out is None:
+        out = torch.empty((total_tokens, W), device=src_cache.device, dtype=src_cache.dtype)
+    es = src_cache.element_size()
+    call("b200_gather_cache", ptr(flat), ptr(out), ptr(block_table), ptr(cu_seq_lens),
+         ptr(seq_starts), block_table.shape[0], block_table.shape[1], bs, W * es,
+         flat.stride(0) * es, nb * bs, total_tokens, stream_ptr())
+    return out
+
+
+def copy_blocks(caches: Sequence[torch.Tensor], mapping: torch.Tensor) -> None:
+    if mapping.numel() == 0 or not caches:
+        return
+    ptrs = torch.tensor([c.data_ptr() for c in caches], dtype=torch.int64,
+                        device=mapping.device)
+    block_bytes = caches[0].stride(0) * caches[0].element_size()
+    mapping = mapping.to(torch.int64).contiguous()
+    call("b200_copy_blocks", ptr(ptrs), len(caches), ptr(mapping), mapping.shape[0],
+         block_bytes, stream_ptr())
+
+
+def swap_blocks(src: torch.Tensor, dst: torch.Tensor, mapping_cpu: torch.Tensor) -> None:
+    """mapping_cpu: int64 ``[n, 2]`` on the host; src / dst: device or pinned host."""
+    m = mapping_cpu.to(torch.int64).contiguous()
+    block_bytes = src.stride(0) * src.element_size()
+    call("b200_swap_blocks", ptr(src), ptr(dst), ptr(m), m.shape[0], block_bytes, stream_ptr())
+
+
+# ---------------------------------------------------------------------------
+# attention
+# ---------------------------------------------------------------------------
+def decode_num_splits(B: int, Hkv: int, max_seq_len: int) -> int:
+    return int(N.lib().b200_decode_num_splits(B, Hkv, max_seq_len))
+
+
+def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                 block_tables: torch.Tensor, seq_lens: torch.Tensor, scale: float,
+                 out: Optional[torch.Tensor] = None, num_splits: int = 0,
+                 workspace: Optional[tuple[torch.Tensor, torch.Tensor]] = None,
+                 max_seq_len: int = 0) -> torch.Tensor:
+    """q ``[B, Hq, D]`` (row stride free), caches ``[blocks, bs, Hkv, D]``."""
+    B, Hq, D = q.shape
+    nb, bs, Hkv, _ = k_cache.shape
+    assert q.stride(2) == 1 and q.stride(1) == D
+    if out is None:
+        out = torch.empty((B, Hq, D), device=q.device, dtype=q.dtype)
+    if num_splits <= 0:
+        num_splits = decode_num_splits(B, Hkv, max_seq_len or block_tables.shape[1] * bs)
+    tmp_out = tmp_lse = None
+    if num_splits > 1:
+        if workspace is None:
+            tmp_out = torch.empty((B, Hq, num_splits, D), device=q.device, dtype=torch.float32)
+            tmp_lse = torch.empty((B, Hq, num_splits), device=q.device, dtype=torch.float32)
+        else:
+            tmp_out, tmp_lse = workspace
+            assert tmp_out.numel() >= B * Hq * num_splits * D
+            assert tmp_lse.numel() >= B * Hq * num_splits
+    call("b200_paged_decode", ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(k_cache),
+         ptr(v_cache), k_cache.stride(1), k_cache.stride(2), nb * bs, ptr(block_tables),
+         block_tables.stride(0), bs, ptr(seq_lens), ptr(tmp_out), ptr(tmp_lse), num_splits,
+         B, Hq, Hkv, D, float(scale), DTYPE_CODE[q.dtype], stream_ptr())
+    return out
+
+
+def varlen_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                   block_tables: torch.Tensor, cu_q: torch.Tensor, seq_lens: torch.Tensor,
+                   scale: float, num_q_tiles: int, out: Optional[torch.Tensor] = None,
+                   causal: bool = True, window: int = 0, return_lse: bool = False):
+    """q ``[T, Hq, D]``; ``num_q_tiles`` >= sum_b ceil(q_len_b / 64) (host-known)."""
+    T, Hq, D = q.shape
+    nb, bs, Hkv, _ = k_cache.shape
+    assert q.stride(2) == 1 and q.stride(1) == D
+    if out is None:
+        out = torch.empty((T, Hq, D), device=q.device, dtype=q.dtype)
+    lse = torch.empty((Hq, T), device=q.device, dtype=torch.float32) if return_lse else None
+    call("b200_varlen_prefill", ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(lse), ptr(cu_q),
+         ptr(seq_lens), ptr(k_cache), ptr(v_cache), k_cache.stride(1), k_cache.stride(2),
+         nb * bs, ptr(block_tables), block_tables.stride(0), bs, block_tables.shape[0], T,
+         num_q_tiles, Hq, Hkv, D, float(scale), int(causal), int(window),
+         DTYPE_CODE[q.dtype], stream_ptr())
+    return (out, lse) if return_lse else out
+
+
+def merge_attn_states(p_out, p_lse, s_out, s_lse, want_lse: bool = True):
+    T, H, Dv = p_out.shape
+    out = torch.empty_like(p_out)
+    lse = torch.empty_like(p_lse) if want_lse else None
+    call("b200_merge_attn_states", ptr(out), ptr(lse), ptr(p_out.contiguous()),
+         ptr(p_lse.contiguous()), ptr(s_out.contiguous()), ptr(s_lse.contiguous()), T, H, Dv,
+         DTYPE_CODE[p_out.dtype], stream_ptr())
+    return out, lse
+
+
+# ---------------------------------------------------------------------------
+# sampling / step
+# ---------------------------------------------------------------------------
+def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None,
+           top_k: Optional[torch.Tensor] = None, top_p: Optional[torch.Tensor] = None,
+           noise: Optional[torch.Tensor] = None, seeds: Optional[torch.Tensor] = None,
+           step: int = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    B, V = logits.shape
+    assert logits.stride(1) == 1
+    if out is None:
+        out = torch.empty((B,), device=logits.device, dtype=torch.int64)
+    call("b200_sample", ptr(logits), logits.stride(0), B, V, DTYPE_CODE[logits.dtype],
+         ptr(temperature), ptr(top_k), ptr(top_p), ptr(noise), ptr(seeds), int(step), ptr(out),
+         stream_ptr())
+    return out
+
+
+def top_k_top_p_(logits: torch.Tensor, top_k: Optional[torch.Tensor],
+                 top_p: Optional[torch.Tensor]) -> torch.Tensor:
+    B, V = logits.shape
+    call("b200_top_k_top_p", ptr(logits), logits.stride(0), B, V, DTYPE_CODE[logits.dtype],
+         ptr(top_k), ptr(top_p), stream_ptr())
+    return logits
+
+
+def advance_step(num_seqs: int, num_queries: int, block_size: int, input_tokens, sampled,
+                 positions, seq_lens, slot_mapping, block_tables, active_only: bool = False
+                 ) -> None:
+    call("b200_advance_step", num_seqs, num_queries, block_size, ptr(input_tokens), ptr(sampled),
+         ptr(positions), ptr(seq_lens), ptr(slot_mapping), ptr(block_tables),
+         block_tables.stride(0), int(active_only), stream_ptr())
+
+
+def feed_tokens(input_ids, prev_sampled, dst_idx, src_idx, n: int) -> None:
+    call("b200_feed_tokens", ptr(input_ids), ptr(prev_sampled), ptr(dst_idx), ptr(src_idx),
+         n, stream_ptr())
