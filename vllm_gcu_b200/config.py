@@ -1,0 +1,279 @@
+"""Typed configuration of the engine.
+
+``ModelConfig`` is built from a HuggingFace-style ``config.json`` dict (or one of
+the named architecture presets used by the benchmarks), the remaining classes
+mirror the knobs the reference exposes through vLLM's ``EngineArgs`` and its
+``additional_config`` dictionary (vllm_gcu/gcu.py:184-354).
+"""
+from __future__ import annotations
+
+import dataclasses
+import json
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Any, Optional
+
+import torch
+
+_DTYPES = {"bfloat16": torch.bfloat16, "float16": torch.float16, "float32": torch.float32,
+           "bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32,
+           "half": torch.float16, "float": torch.float32}
+
+
+def to_dtype(x: Any) -> torch.dtype:
+    if isinstance(x, torch.dtype):
+        return x
+    return _DTYPES[str(x).replace("torch.", "")]
+
+
+@dataclass
+class ModelConfig:
+    architecture: str = "LlamaForCausalLM"
+    vocab_size: int = 32000
+    hidden_size: int = 4096
+    intermediate_size: int = 11008
+    num_hidden_layers: int = 32
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 32
+    head_dim: int = 0                      # 0 -> hidden_size // num_attention_heads
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 10000.0
+    rope_scaling: Optional[dict] = None
+    partial_rotary_factor: float = 1.0
+    rope_is_neox: bool = True
+    max_position_embeddings: int = 8192
+    tie_word_embeddings: bool = False
+    attention_bias: bool = False
+    mlp_bias: bool = False
+    hidden_act: str = "silu"
+    qk_norm: bool = False                  # per-head RMSNorm on q and k (Qwen3)
+    sandwich_norm: bool = False            # GLM-4-0414: extra post-attn / post-mlp norms
+    sliding_window: int = 0
+    dtype: torch.dtype = torch.bfloat16
+    # MoE
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    num_shared_experts: int = 0
+    first_k_dense_replace: int = 0
+    moe_layer_freq: int = 1
+    norm_topk_prob: bool = True
+    scoring_func: str = "softmax"
+    n_group: int = 1
+    topk_group: int = 1
+    routed_scaling_factor: float = 1.0
+    topk_method: str = "greedy"            # "noaux_tc" adds e_score_correction_bias
+    # MLA
+    q_lora_rank: int = 0
+    kv_lora_rank: int = 0
+    qk_nope_head_dim: int = 0
+    qk_rope_head_dim: int = 0
+    v_head_dim: int = 0
+    # MTP
+    num_nextn_predict_layers: int = 0
+    # quantisation (HF quantization_config / quantize_config.json, see layers/quant)
+    quantization: Optional[str] = None
+    quant_config: Optional[dict] = None
+    kv_cache_dtype: str = "auto"
+    extra: dict = field(default_factory=dict)
+
+    def __post_init__(self) -> None:
+        self.dtype = to_dtype(self.dtype)
+        if self.head_dim <= 0:
+            self.head_dim = self.hidden_size // self.num_attention_heads
+
+    # -- derived ---------------------------------------------------------
+    @property
+    def is_mla(self) -> bool:
+        return self.kv_lora_rank > 0
+
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    @property
+    def rotary_dim(self) -> int:
+        d = self.qk_rope_head_dim if self.is_mla else self.head_dim
+        return int(d * self.partial_rotary_factor)
+
+    def is_moe_layer(self, layer_idx: int) -> bool:
+        return (self.is_moe and layer_idx >= self.first_k_dense_replace
+                and layer_idx % self.moe_layer_freq == 0)
+
+    def kv_bytes_per_token(self, tp_size: int = 1) -> int:
+        es = 1 if self.kv_cache_dtype.startswith("fp8") or self.kv_cache_dtype == "int8" else \
+            torch.empty((), dtype=self.dtype).element_size()
+        if self.is_mla:
+            return self.num_hidden_layers * (self.kv_lora_rank + self.qk_rope_head_dim) * es
+        kvh = max(1, self.num_key_value_heads // tp_size)
+        return self.num_hidden_layers * 2 * kvh * self.head_dim * es
+
+    # -- construction ----------------------------------------------------
+    @classmethod
+    def from_hf_dict(cls, d: dict, **overrides) -> "ModelConfig":
+        archs = d.get("architectures") or ["LlamaForCausalLM"]
+        names = {f.name for f in dataclasses.fields(cls)}
+        kw: dict[str, Any] = {"architecture": archs[0]}
+        alias = {"n_routed_experts": "num_experts", "num_local_experts": "num_experts",
+                 "n_shared_experts": "num_shared_experts", "torch_dtype": "dtype"}
+        extra = {}
+        for k, v in d.items():
+            k2 = alias.get(k, k)
+            if k2 in names and v is not None:
+                kw[k2] = v
+            else:
+                extra[k] = v
+        arch = archs[0]
+        if "Qwen3" in arch:
+            kw.setdefault("qk_norm", True)
+        if arch.startswith("Glm4"):
+            kw.setdefault("sandwich_norm", True)
+            kw.setdefault("rope_is_neox", False)
+            kw.setdefault("partial_rotary_factor", d.get("partial_rotary_factor", 0.5))
+        if "Deepseek" in arch:
+            kw.setdefault("rope_is_neox", False)
+        qc = d.get("quantization_config")
+        if qc:
+            kw["quant_config"] = qc
+            kw["quantization"] = qc.get("quant_method")
+        kw["extra"] = extra
+        kw.update(overrides)
+        return cls(**kw)
+
+    @classmethod
+    def from_pretrained(cls, path: str, **overrides) -> "ModelConfig":
+        p = Path(path)
+        d = json.loads((p / "config.json").read_text())
+        cfg = cls.from_hf_dict(d, **overrides)
+        qpath = p / "quantize_config.json"
+        if cfg.quant_config is None and qpath.exists():
+            cfg.quant_config = json.loads(qpath.read_text())
+            cfg.quantization = cfg.quantization or cfg.quant_config.get("quant_method")
+        return cfg
+
+
+def preset(name: str, **overrides) -> ModelConfig:
+    """Architecture presets of the benchmark configurations (random-init weights)."""
+    presets: dict[str, dict] = {
+        "tiny-llama": dict(vocab_size=32000, hidden_size=256, intermediate_size=688,
+                           num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                           head_dim=64, rms_norm_eps=1e-6, rope_theta=10000.0,
+                           max_position_embeddings=2048, dtype="float32"),
+        "llama-3-8b": dict(vocab_size=128256, hidden_size=4096, intermediate_size=14336,
+                           num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8,
+                           head_dim=128, rms_norm_eps=1e-5, rope_theta=500000.0,
+                           max_position_embeddings=8192, dtype="bfloat16"),
+        "llama-3-70b": dict(vocab_size=128256, hidden_size=8192, intermediate_size=28672,
+                            num_hidden_layers=80, num_attention_heads=64, num_key_value_heads=8,
+                            head_dim=128, rms_norm_eps=1e-5, rope_theta=500000.0,
+                            max_position_embeddings=8192, dtype="bfloat16"),
+        "qwen3-30b-a3b": dict(architecture="Qwen3MoeForCausalLM", vocab_size=151936,
+                              hidden_size=2048, intermediate_size=6144, num_hidden_layers=48,
+                              num_attention_heads=32, num_key_value_heads=4, head_dim=128,
+                              qk_norm=True, num_experts=128, num_experts_per_tok=8,
+                              moe_intermediate_size=768, norm_topk_prob=True,
+                              rms_norm_eps=1e-6, rope_theta=1000000.0,
+                              max_position_embeddings=40960, dtype="bfloat16"),
+        "deepseek-v3": dict(architecture="DeepseekV3ForCausalLM", vocab_size=129280,
+                            hidden_size=7168, intermediate_size=18432, num_hidden_layers=61,
+                            num_attention_heads=128, num_key_value_heads=128,
+                            q_lora_rank=1536, kv_lora_rank=512, qk_nope_head_dim=128,
+                            qk_rope_head_dim=64, v_head_dim=128, head_dim=192,
+                            num_experts=256, num_experts_per_tok=8, moe_intermediate_size=2048,
+                            num_shared_experts=1, first_k_dense_replace=3, n_group=8,
+                            topk_group=4, scoring_func="sigmoid", topk_method="noaux_tc",
+                            routed_scaling_factor=2.5, norm_topk_prob=True,
+                            num_nextn_predict_layers=1, rope_is_neox=False,
+                            rms_norm_eps=1e-6, rope_theta=10000.0,
+                            max_position_embeddings=163840, dtype="bfloat16"),
+        "tiny-qwen3-moe": dict(architecture="Qwen3MoeForCausalLM", vocab_size=1024,
+                               hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+                               num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+                               qk_norm=True, num_experts=8, num_experts_per_tok=2,
+                               moe_intermediate_size=64, dtype="float32"),
+        "tiny-deepseek": dict(architecture="DeepseekV3ForCausalLM", vocab_size=1024,
+                              hidden_size=128, intermediate_size=256, num_hidden_layers=3,
+                              num_attention_heads=4, num_key_value_heads=4, q_lora_rank=48,
+                              kv_lora_rank=32, qk_nope_head_dim=16, qk_rope_head_dim=8,
+                              v_head_dim=16, head_dim=24, num_experts=8, num_experts_per_tok=2,
+                              moe_intermediate_size=32, num_shared_experts=1,
+                              first_k_dense_replace=1, n_group=2, topk_group=1,
+                              scoring_func="sigmoid", topk_method="noaux_tc",
+                              routed_scaling_factor=2.5, num_nextn_predict_layers=1,
+                              rope_is_neox=False, dtype="float32"),
+    }
+    kw = dict(presets[name])
+    kw.update(overrides)
+    return ModelConfig(**kw)
+
+
+@dataclass
+class CacheConfig:
+    block_size: int = 16
+    gpu_memory_utilization: float = 0.90
+    num_gpu_blocks: Optional[int] = None   # override of the profiled value
+    num_cpu_blocks: int = 0                # swap space
+    enable_prefix_caching: bool = True
+    cache_dtype: str = "auto"
+
+
+@dataclass
+class SchedulerConfig:
+    max_num_seqs: int = 256
+    max_num_batched_tokens: int = 8192
+    max_model_len: int = 8192
+    enable_chunked_prefill: bool = True
+    policy: str = "fcfs"                   # or "priority"
+    async_scheduling: bool = False
+    num_scheduler_steps: int = 1           # multi-step decode (device-side advance)
+    long_prefill_token_threshold: int = 0
+
+
+@dataclass
+class ParallelConfig:
+    tensor_parallel_size: int = 1
+    pipeline_parallel_size: int = 1
+    data_parallel_size: int = 1
+    enable_expert_parallel: bool = False
+    enable_sequence_parallel: bool = False
+    comm_backend: str = "fused"            # "fused" (symmetric-memory kernels) | "nccl"
+    num_redundant_experts: int = 0
+    enable_eplb: bool = False
+
+    @property
+    def world_size(self) -> int:
+        return self.tensor_parallel_size * self.pipeline_parallel_size * self.data_parallel_size
+
+
+@dataclass
+class SpeculativeConfig:
+    method: Optional[str] = None           # "ngram" | "mtp" | "draft_model"
+    num_speculative_tokens: int = 0
+    prompt_lookup_max: int = 4
+    prompt_lookup_min: int = 1
+    draft_model: Optional[str] = None
+
+
+@dataclass
+class EngineConfig:
+    model: ModelConfig
+    cache: CacheConfig = field(default_factory=CacheConfig)
+    scheduler: SchedulerConfig = field(default_factory=SchedulerConfig)
+    parallel: ParallelConfig = field(default_factory=ParallelConfig)
+    speculative: SpeculativeConfig = field(default_factory=SpeculativeConfig)
+    device: str = "auto"
+    seed: int = 0
+    enforce_eager: bool = False
+    cuda_graph_sizes: Optional[list[int]] = None
+    load_format: str = "dummy"             # "dummy" (random init) | "safetensors"
+    model_path: Optional[str] = None
+    additional_config: dict = field(default_factory=dict)
+
+    def __post_init__(self) -> None:
+        if self.device == "auto":
+            self.device = "cuda" if torch.cuda.is_available() else "cpu"
+        self.scheduler.max_model_len = min(self.scheduler.max_model_len,
+                                           self.model.max_position_embeddings)
+        if not self.scheduler.enable_chunked_prefill:
+            self.scheduler.max_num_batched_tokens = max(self.scheduler.max_num_batched_tokens,
+                                                        self.scheduler.max_model_len)

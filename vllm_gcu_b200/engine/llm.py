@@ -1,0 +1,189 @@
+"""Engine front end: ``LLM.generate`` and the step loop.
+
+One engine runs per process (one process per GPU).  Under tensor / pipeline
+parallelism every rank runs the same deterministic scheduler on the same requests, so
+no control-plane broadcast is needed inside a step; only device collectives cross ranks.
+With ``async_scheduling`` the loop keeps two steps in flight: step N+1 is scheduled,
+prepared and launched while step N still runs, and the ids of step N are read one
+iteration later (the batch queue of vllm_gcu/patch/patch_0_9_2/core.py:102-154 with
+depth 2, vllm_gcu/v1/executor/async_multiproc_executor.py:186-191).
+"""
+from __future__ import annotations
+
+import itertools
+import time
+from collections import deque
+from typing import Iterable, Optional, Sequence, Union
+
+import torch
+
+from ..config import (CacheConfig, EngineConfig, ModelConfig, ParallelConfig, SchedulerConfig,
+                      preset)
+from ..models import build_model
+from ..parallel.state import get_state, init_distributed
+from .model_runner import ModelRunner, StepHandle
+from .request import Request, RequestOutput, SamplingParams
+from .scheduler import Scheduler, SchedulerOutput
+
+
+class LLMEngine:
+    def __init__(self, cfg: EngineConfig):
+        self.cfg = cfg
+        pc = cfg.parallel
+        if pc.world_size > 1 and not get_state().initialized:
+            init_distributed(pc.tensor_parallel_size, pc.pipeline_parallel_size,
+                             pc.data_parallel_size, enable_ep=pc.enable_expert_parallel)
+        st = get_state()
+        if cfg.device == "cuda":
+            self.device = torch.device("cuda", st.local_rank if st.world_size > 1
+                                       else torch.cuda.current_device())
+            torch.cuda.set_device(self.device)
+        else:
+            self.device = torch.device(cfg.device)
+        torch.manual_seed(cfg.seed)
+        self.model = build_model(cfg.model, self.device)
+        if cfg.load_format == "dummy":
+            self.model.init_random(cfg.seed)
+        elif cfg.load_format == "safetensors":
+            from ..utils.weights import iter_safetensors
+            self.model.load_weights(iter_safetensors(cfg.model_path))
+        self.model.eval()
+        if pc.world_size > 1 and pc.comm_backend == "fused" and self.device.type == "cuda":
+            from ..parallel import symm
+            symm.attach(cfg)
+        self.runner = ModelRunner(cfg, self.model, self.device)
+        num_blocks = self.runner.profile_num_blocks()
+        if st.world_size > 1:
+            num_blocks = self._agree_min(num_blocks)
+        self.runner.init_kv_cache(num_blocks)
+        self.runner.capture_graphs(cfg.cuda_graph_sizes)
+        self.scheduler = Scheduler(cfg.scheduler, cfg.cache, num_blocks,
+                                   separate_prefill_decode=bool(
+                                       cfg.additional_config.get("separate_prefill_decode")))
+        self._ids = itertools.count()
+        self._pending: deque[tuple[SchedulerOutput, StepHandle]] = deque()
+        self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0}
+
+    @staticmethod
+    def _agree_min(n: int) -> int:
+        """All ranks use the smallest block count any of them can afford
+        (vllm_gcu/worker/worker.py:182-189)."""
+        import torch.distributed as dist
+        st = get_state()
+        t = torch.tensor([n], dtype=torch.int64)
+        if st.backend == "nccl":
+            t = t.cuda()
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return int(t.item())
+
+    # -- requests -------------------------------------------------------------------
+    def add_request(self, prompt_token_ids: Sequence[int],
+                    sampling_params: Optional[SamplingParams] = None,
+                    request_id: Optional[str] = None, priority: int = 0,
+                    eos_token_id: Optional[int] = None, lora_id: int = -1) -> str:
+        rid = request_id if request_id is not None else f"req-{next(self._ids)}"
+        req = Request(rid, list(prompt_token_ids), sampling_params or SamplingParams(),
+                      eos_token_id=eos_token_id, priority=priority, lora_id=lora_id)
+        self.scheduler.add_request(req)
+        return rid
+
+    def abort_request(self, request_id: str) -> None:
+        self.scheduler.abort_request(request_id)
+
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_unfinished() or bool(self._pending)
+
+    # -- stepping ---------------------------------------------------------------------
+    def _launch(self) -> Optional[tuple[SchedulerOutput, StepHandle]]:
+        so = self.scheduler.schedule()
+        if so.is_empty:
+            self.runner.release(so.finished_req_ids)
+            self.runner.release(so.preempted_req_ids)
+            return None
+        handle = self.runner.execute(so)
+        self.stats["steps"] += 1
+        return so, handle
+
+    def _finish(self, so: SchedulerOutput, handle: StepHandle) -> list[RequestOutput]:
+        return self.scheduler.update_from_output(so, handle.token_ids(), handle.draft)
+
+    def step(self) -> list[RequestOutput]:
+        """Runs (or, with async scheduling, launches and retires) one engine step."""
+        if not self.cfg.scheduler.async_scheduling:
+            item = self._launch()
+            return self._finish(*item) if item is not None else []
+        outs: list[RequestOutput] = []
+        item = self._launch() if self.scheduler.has_unfinished() else None
+        if item is not None:
+            self._pending.append(item)
+        if self._pending and (len(self._pending) >= 2 or item is None):
+            outs = self._finish(*self._pending.popleft())
+        return outs
+
+    def generate(self, prompts: Iterable[Sequence[int]],
+                 sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
+                 ) -> list[RequestOutput]:
+        prompts = list(prompts)
+        if sampling_params is None or isinstance(sampling_params, SamplingParams):
+            sps = [sampling_params or SamplingParams()] * len(prompts)
+        else:
+            sps = list(sampling_params)
+        order = [self.add_request(p, sp) for p, sp in zip(prompts, sps)]
+        final: dict[str, RequestOutput] = {}
+        while self.has_unfinished():
+            for ro in self.step():
+                if ro.finished:
+                    final[ro.request_id] = ro
+        return [final[r] for r in order]
+
+
+class LLM:
+    """Convenience wrapper mirroring the offline-inference entry point users of the
+    reference call (``vllm.LLM``): build from a preset / HF config / checkpoint directory and
+    call :meth:`generate` with token-id prompts."""
+
+    def __init__(self, model: Union[str, ModelConfig], tensor_parallel_size: int = 1,
+                 pipeline_parallel_size: int = 1, max_num_seqs: int = 256,
+                 max_num_batched_tokens: int = 8192, max_model_len: Optional[int] = None,
+                 block_size: int = 16, gpu_memory_utilization: float = 0.9,
+                 enable_prefix_caching: bool = True, async_scheduling: bool = False,
+                 enforce_eager: bool = False, device: str = "auto", seed: int = 0,
+                 num_gpu_blocks: Optional[int] = None, scheduling_policy: str = "fcfs",
+                 load_format: Optional[str] = None, comm_backend: str = "fused",
+                 enable_expert_parallel: bool = False, dtype: Optional[str] = None,
+                 cuda_graph_sizes: Optional[list[int]] = None,
+                 additional_config: Optional[dict] = None, **model_overrides):
+        model_path = None
+        if isinstance(model, ModelConfig):
+            mc = model
+        else:
+            import os
+            if os.path.isdir(model):
+                mc = ModelConfig.from_pretrained(model, **model_overrides)
+                model_path = model
+            else:
+                mc = preset(model, **model_overrides)
+        if dtype is not None:
+            from ..config import to_dtype
+            mc.dtype = to_dtype(dtype)
+        cfg = EngineConfig(
+            model=mc,
+            cache=CacheConfig(block_size=block_size, gpu_memory_utilization=gpu_memory_utilization,
+                              enable_prefix_caching=enable_prefix_caching,
+                              num_gpu_blocks=num_gpu_blocks),
+            scheduler=SchedulerConfig(max_num_seqs=max_num_seqs,
+                                      max_num_batched_tokens=max_num_batched_tokens,
+                                      max_model_len=max_model_len or mc.max_position_embeddings,
+                                      policy=scheduling_policy, async_scheduling=async_scheduling),
+            parallel=ParallelConfig(tensor_parallel_size=tensor_parallel_size,
+                                    pipeline_parallel_size=pipeline_parallel_size,
+                                    comm_backend=comm_backend,
+                                    enable_expert_parallel=enable_expert_parallel),
+            device=device, seed=seed, enforce_eager=enforce_eager,
+            cuda_graph_sizes=cuda_graph_sizes,
+            load_format=load_format or ("safetensors" if model_path else "dummy"),
+            model_path=model_path, additional_config=additional_config or {})
+        self.engine = LLMEngine(cfg)
+
+    def generate(self, prompts, sampling_params=None) -> list[RequestOutput]:
+        return self.engine.generate(prompts, sampling_params)

@@ -1,0 +1,486 @@
+"""Model runner: turns a scheduler decision into device work.
+
+Responsibilities (the reference splits them over ``GCUModelRunner`` and
+``AsyncGCUModelRunner``, vllm_gcu/worker/worker_v1.py:30-230 and
+vllm_gcu/v1/gcu_async_model_runner.py:99-1081):
+
+* persistent input buffers on the device, filled from pinned host staging with two
+  asynchronous copies per step (one int64 block, one int32 block);
+* batch layout "decodes first", attention metadata, KV-cache allocation from a memory
+  profile;
+* device-side next-token feed: a request that continues from a token sampled by the
+  previous step takes it from the previous step's on-device output, so the host never
+  waits for token ids before launching the next step (async_model_runner.py:370-473);
+* CUDA-graph capture of decode-only steps per padded batch size, with batch size 0
+  handled eagerly as the dummy step of idle data-parallel ranks (worker_v1.py:52-180);
+* fused sampling on the device and an asynchronous device-to-host copy of the ids.
+"""
+from __future__ import annotations
+
+import time
+import zlib
+from dataclasses import dataclass, field
+from typing import Optional
+
+import numpy as np
+import torch
+
+from ..config import EngineConfig
+from ..layers.attention import AttentionMetadata
+from ..layers.sampler import Sampler, SamplingTensors
+from ..ops import _native
+from .scheduler import ScheduledRequest, SchedulerOutput
+
+
+@dataclass
+class StepHandle:
+    """Result of a launched step; ``token_ids()`` blocks until the ids are on the host."""
+    req_ids: list[str]                     # sampling requests, in output order
+    num_sampled: int
+    sampled_host: Optional[torch.Tensor]   # pinned int64 [num_sampled * width]
+    event: Optional[torch.cuda.Event]
+    width: int = 1                         # tokens per request (1 + speculative tokens)
+    accepted_host: Optional[torch.Tensor] = None
+    draft: Optional[dict[str, list[int]]] = None
+    device_ms_events: Optional[tuple] = None
+    extra: dict = field(default_factory=dict)
+
+    def ready(self) -> bool:
+        return self.event is None or self.event.query()
+
+    def wait(self) -> None:
+        if self.event is not None:
+            self.event.synchronize()
+
+    def token_ids(self) -> dict[str, list[int]]:
+        self.wait()
+        out: dict[str, list[int]] = {}
+        if self.num_sampled == 0:
+            return out
+        arr = self.sampled_host[: self.num_sampled * self.width].numpy()
+        if self.width == 1:
+            for i, rid in enumerate(self.req_ids):
+                out[rid] = [int(arr[i])]
+        else:
+            arr = arr.reshape(self.num_sampled, self.width)
+            for i, rid in enumerate(self.req_ids):
+                row = arr[i]
+                out[rid] = [int(t) for t in row if t >= 0]
+        return out
+
+
+def _pad_batch(n: int, sizes: list[int]) -> int:
+    for s in sizes:
+        if s >= n:
+            return s
+    return n
+
+
+class ModelRunner:
+    def __init__(self, cfg: EngineConfig, model, device: torch.device):
+        self.cfg = cfg
+        self.model = model
+        self.device = device
+        self.is_cuda = device.type == "cuda"
+        sc = cfg.scheduler
+        self.block_size = cfg.cache.block_size
+        self.max_seqs = sc.max_num_seqs
+        self.max_tokens = max(sc.max_num_batched_tokens, sc.max_num_seqs)
+        self.max_blocks = -(-sc.max_model_len // self.block_size) + 1
+        self.kv_caches: list[torch.Tensor] = []
+        self.num_blocks = 0
+        self.sampler = Sampler(cfg.model.vocab_size)
+        self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        self.graph_sizes: list[int] = []
+        self.graph_pool = None
+        self.step_counter = 0
+        self.prev_index: dict[str, int] = {}       # req id -> row in prev_sampled
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+        self.graph_launches = 0                    # kernels replayed through CUDA graphs
+        self.graph_kernel_counts: dict = {}
+        self.timing_events: Optional[list] = None  # set to a list to time every step
+        self._alloc_buffers()
+
+    # -- buffers -------------------------------------------------------------------
+    def _alloc_buffers(self) -> None:
+        dev, pin = self.device, self.is_cuda
+        T, S, MB = self.max_tokens, self.max_seqs, self.max_blocks
+        # int64 block: input_ids | positions | slot_mapping | sample_indices | seeds
+        self.i64_layout = {"input_ids": (0, T), "positions": (T, T), "slot_mapping": (2 * T, T),
+                           "sample_indices": (3 * T, S), "seeds": (3 * T + S, S)}
+        n64 = 3 * T + 2 * S
+        # int32 block: seq_lens | cu_q | feed_dst | feed_src | top_k | block_tables
+        self.i32_layout = {"seq_lens": (0, S), "cu_q": (S, S + 1), "feed_dst": (2 * S + 1, S),
+                           "feed_src": (3 * S + 1, S), "top_k": (4 * S + 1, S),
+                           "block_tables": (5 * S + 1, S * MB)}
+        n32 = 5 * S + 1 + S * MB
+        self.h_i64 = torch.zeros(n64, dtype=torch.int64, pin_memory=pin)
+        self.h_i32 = torch.zeros(n32, dtype=torch.int32, pin_memory=pin)
+        self.h_f32 = torch.zeros(2 * S, dtype=torch.float32, pin_memory=pin)  # temperature | top_p
+        self.d_i64 = torch.zeros(n64, dtype=torch.int64, device=dev)
+        self.d_i32 = torch.zeros(n32, dtype=torch.int32, device=dev)
+        self.d_f32 = torch.zeros(2 * S, dtype=torch.float32, device=dev)
+        self.np_i64 = self.h_i64.numpy()
+        self.np_i32 = self.h_i32.numpy()
+        self.np_f32 = self.h_f32.numpy()
+
+        def v64(name):
+            o, n = self.i64_layout[name]
+            return self.d_i64[o:o + n]
+
+        def v32(name):
+            o, n = self.i32_layout[name]
+            return self.d_i32[o:o + n]
+
+        self.input_ids, self.positions = v64("input_ids"), v64("positions")
+        self.slot_mapping, self.sample_indices = v64("slot_mapping"), v64("sample_indices")
+        self.seeds = v64("seeds")
+        self.seq_lens, self.cu_q = v32("seq_lens"), v32("cu_q")
+        self.feed_dst, self.feed_src, self.top_k = v32("feed_dst"), v32("feed_src"), v32("top_k")
+        self.block_tables = v32("block_tables").view(S, MB)
+        self.temperature, self.top_p = self.d_f32[:S], self.d_f32[S:]
+        self.sampled = [torch.zeros(S, dtype=torch.int64, device=dev) for _ in range(2)]
+        self.sampled_host = [torch.zeros(S, dtype=torch.int64, pin_memory=pin) for _ in range(2)]
+        self.decode_ws: Optional[tuple[torch.Tensor, torch.Tensor]] = None
+        # host-side block table, one row per live request
+        self.bt_rows: dict[str, int] = {}
+        self.free_rows = list(range(S * 2 - 1, -1, -1))
+        self.bt_host = np.zeros((S * 2, MB), dtype=np.int32)
+        self.bt_len = np.zeros(S * 2, dtype=np.int32)
+
+    # -- KV cache --------------------------------------------------------------------
+    def profile_num_blocks(self) -> int:
+        """Number of KV blocks that fit next to the weights and the peak activations of a
+        full prefill step (vllm_gcu/worker/worker.py:120-191 does the same accounting)."""
+        cc = self.cfg.cache
+        if cc.num_gpu_blocks is not None:
+            return cc.num_gpu_blocks
+        bytes_per_block = self.cfg.model.kv_bytes_per_token(
+            self.cfg.parallel.tensor_parallel_size) * self.block_size
+        bytes_per_block = bytes_per_block * self.model.num_local_layers \
+            // max(1, self.cfg.model.num_hidden_layers)
+        if not self.is_cuda:
+            return max(64, min(4096, (1 << 28) // max(1, bytes_per_block)))
+        torch.cuda.synchronize()
+        torch.cuda.reset_peak_memory_stats()
+        self._dummy_forward(self.cfg.scheduler.max_num_batched_tokens)
+        torch.cuda.synchronize()
+        peak = torch.cuda.max_memory_allocated()
+        free, total = torch.cuda.mem_get_info()
+        torch.cuda.empty_cache()
+        weights_and_act = peak
+        budget = int(total * cc.gpu_memory_utilization) - weights_and_act
+        # the dummy forward is gone but other processes may hold memory too
+        budget = min(budget, int(torch.cuda.mem_get_info()[0] * 0.97))
+        n = budget // bytes_per_block
+        if n < 16:
+            raise RuntimeError(f"not enough GPU memory for the KV cache ({budget} bytes)")
+        cap = self.max_seqs * self.max_blocks * 4
+        return int(min(n, cap))
+
+    def init_kv_cache(self, num_blocks: int) -> None:
+        spec = self.model.kv_cache_spec()
+        mc = self.cfg.model
+        dt = mc.dtype
+        if spec["type"] == "mla":
+            self.kv_caches = [torch.zeros(num_blocks, self.block_size, spec["width"], dtype=dt,
+                                          device=self.device) for _ in range(spec["layers"])]
+        else:
+            self.kv_caches = [torch.zeros(2, num_blocks, self.block_size, spec["kv_heads"],
+                                          spec["head_dim"], dtype=dt, device=self.device)
+                              for _ in range(spec["layers"])]
+        self.num_blocks = num_blocks
+        if self.is_cuda and spec["type"] == "gqa":
+            Hq = mc.num_attention_heads // self.cfg.parallel.tensor_parallel_size
+            ns = 32
+            self.decode_ws = (
+                torch.empty(self.max_seqs * Hq * ns * spec["head_dim"] // 8 + 1024,
+                            dtype=torch.float32, device=self.device),
+                torch.empty(self.max_seqs * Hq * ns // 8 + 1024, dtype=torch.float32,
+                            device=self.device))
+
+    def _decode_splits(self, batch: int, max_seq_len: int) -> int:
+        if not self.is_cuda or self.model.kv_cache_spec()["type"] != "gqa":
+            return 1
+        from ..ops import cuda as C
+        kvh = self.model.kv_cache_spec()["kv_heads"]
+        s = C.decode_num_splits(batch, kvh, max_seq_len)
+        Hq = self.cfg.model.num_attention_heads // self.cfg.parallel.tensor_parallel_size
+        while s > 1 and batch * Hq * s * self.cfg.model.head_dim > self.decode_ws[0].numel():
+            s -= 1
+        return s
+
+    def _dummy_forward(self, num_tokens: int) -> None:
+        """Forward over ``num_tokens`` padding tokens that touch no cache slot (memory
+        profile; also the keep-alive step of an idle data-parallel rank)."""
+        T = max(0, min(num_tokens, self.max_tokens))
+        md = AttentionMetadata(
+            num_tokens=T, num_decodes=0, num_prefills=0, num_decode_tokens=0,
+            positions=self.positions[:T], slot_mapping=torch.full_like(self.slot_mapping[:T], -1),
+            block_tables=self.block_tables[:1], seq_lens=self.seq_lens[:1], is_dummy=True)
+        caches = self.kv_caches or [None] * self.model.num_local_layers
+        with torch.inference_mode():
+            hidden = self.model(self.input_ids[:T], md, caches)
+            if T > 0 and self.model.is_last_stage:
+                self.model.compute_logits(hidden[: min(T, self.max_seqs)])
+
+    def execute_dummy_batch(self) -> None:
+        self._dummy_forward(0 if self.cfg.parallel.enable_expert_parallel else 1)
+
+    # -- request bookkeeping -----------------------------------------------------------
+    def _row_of(self, s: ScheduledRequest) -> int:
+        rid = s.req.request_id
+        row = self.bt_rows.get(rid)
+        if row is None:
+            row = self.free_rows.pop()
+            self.bt_rows[rid] = row
+            self.bt_len[row] = 0
+        if s.is_new:
+            self.bt_len[row] = 0
+        n0 = int(self.bt_len[row])
+        ids = s.req.block_ids
+        if len(ids) > n0:
+            self.bt_host[row, n0:len(ids)] = ids[n0:]
+            self.bt_len[row] = len(ids)
+        return row
+
+    def release(self, req_ids) -> None:
+        for rid in req_ids:
+            row = self.bt_rows.pop(rid, None)
+            if row is not None:
+                self.free_rows.append(row)
+            self.prev_index.pop(rid, None)
+
+    # -- one step ---------------------------------------------------------------------
+    def execute(self, so: SchedulerOutput, want_device_timing: bool = False) -> StepHandle:
+        self.release(so.finished_req_ids)
+        self.release(so.preempted_req_ids)
+        if so.is_empty:
+            return StepHandle([], 0, None, None)
+        sched = so.scheduled
+        decodes = [s for s in sched if s.num_tokens == 1 and s.will_sample]
+        prefills = [s for s in sched if not (s.num_tokens == 1 and s.will_sample)]
+        order = decodes + prefills
+        nd, npf = len(decodes), len(prefills)
+        B = nd + npf
+        bs = self.block_size
+        T_real = nd + sum(s.num_tokens for s in prefills)
+
+        use_graph = (self.is_cuda and npf == 0 and self.graphs and nd <= self.graph_sizes[-1])
+        B_pad = _pad_batch(nd, self.graph_sizes) if use_graph else B
+        T = T_real + (B_pad - B)
+
+        i64, i32, f32 = self.np_i64, self.np_i32, self.np_f32
+        o_ids, o_pos, o_slot = (self.i64_layout[k][0] for k in ("input_ids", "positions",
+                                                                "slot_mapping"))
+        o_samp, o_seed = self.i64_layout["sample_indices"][0], self.i64_layout["seeds"][0]
+        o_sl, o_cu = self.i32_layout["seq_lens"][0], self.i32_layout["cu_q"][0]
+        o_fd, o_fs = self.i32_layout["feed_dst"][0], self.i32_layout["feed_src"][0]
+        o_tk, o_bt = self.i32_layout["top_k"][0], self.i32_layout["block_tables"][0]
+        MB = self.max_blocks
+
+        rows = np.fromiter((self._row_of(s) for s in order), dtype=np.int64, count=B)
+        starts = np.fromiter((s.start for s in order), dtype=np.int64, count=B)
+        ntok = np.fromiter((s.num_tokens for s in order), dtype=np.int64, count=B)
+        seq_after = starts + ntok
+        max_seq_len = int(seq_after.max())
+        used_blocks = -(-max_seq_len // bs)
+
+        # token ids / positions
+        feed_dst: list[int] = []
+        feed_src: list[int] = []
+        tok_off = np.zeros(B + 1, dtype=np.int64)
+        np.cumsum(ntok, out=tok_off[1:])
+        pos = i64[o_pos:o_pos + T_real]
+        ids = i64[o_ids:o_ids + T_real]
+        if nd:
+            pos[:nd] = starts[:nd]
+        for j, s in enumerate(order):
+            a, b = int(tok_off[j]), int(tok_off[j + 1])
+            req = s.req
+            known = req.num_tokens
+            n_spec = len(s.spec_token_ids)
+            if j >= nd:
+                pos[a:b] = np.arange(s.start, s.start + s.num_tokens)
+            end = s.start + s.num_tokens
+            n_known = max(0, min(end, known) - s.start)
+            if n_known:
+                if s.start + n_known <= req.num_prompt_tokens:
+                    ids[a:a + n_known] = req.prompt_token_ids[s.start:s.start + n_known]
+                else:
+                    ids[a:a + n_known] = [req.token_at(p) for p in range(s.start,
+                                                                         s.start + n_known)]
+            p = a + n_known
+            if p < b - n_spec:
+                # exactly one unknown id: the token sampled by the previous step
+                src = self.prev_index.get(req.request_id)
+                assert src is not None and b - n_spec - p == 1, "token id not available"
+                ids[p] = 0
+                feed_dst.append(p)
+                feed_src.append(src)
+                p += 1
+            if n_spec:
+                ids[b - n_spec:b] = s.spec_token_ids
+        # slots
+        blk_idx = pos // bs
+        tok_rows = np.repeat(rows, ntok)
+        i64[o_slot:o_slot + T_real] = (self.bt_host[tok_rows, blk_idx].astype(np.int64) * bs
+                                       + pos % bs)
+        if T > T_real:
+            i64[o_slot + T_real:o_slot + T] = -1
+            i64[o_ids + T_real:o_ids + T] = 0
+            i64[o_pos + T_real:o_pos + T] = 0
+        # sampling rows
+        samplers = [j for j, s in enumerate(order) if s.will_sample]
+        ns = len(samplers)
+        width = 1
+        samp_idx = tok_off[1:][samplers] - 1 if ns else np.zeros(0, dtype=np.int64)
+        i64[o_samp:o_samp + ns] = samp_idx
+        if B_pad > B:
+            i64[o_samp + ns:o_samp + B_pad] = 0
+        sp_list = [order[j].req.sampling_params for j in samplers]
+        all_greedy = all(sp.greedy for sp in sp_list)
+        if not all_greedy:
+            for r, j in enumerate(samplers):
+                sp, req = sp_list[r], order[j].req
+                f32[r] = sp.temperature
+                f32[self.max_seqs + r] = sp.top_p
+                i32[o_tk + r] = sp.top_k
+                base = sp.seed if sp.seed is not None else zlib.crc32(req.request_id.encode())
+                i64[o_seed + r] = (base * 1000003 + len(req.output_token_ids)
+                                   + req.num_output_placeholders) & 0x7FFFFFFFFFFFFFFF
+        # per-sequence metadata
+        i32[o_sl:o_sl + B] = seq_after
+        if B_pad > B:
+            i32[o_sl + B:o_sl + B_pad] = 0
+        cu = np.zeros(npf + 1, dtype=np.int64)
+        if npf:
+            np.cumsum(ntok[nd:], out=cu[1:])
+            i32[o_cu:o_cu + npf + 1] = cu
+        nf = len(feed_dst)
+        if nf:
+            i32[o_fd:o_fd + nf] = feed_dst
+            i32[o_fs:o_fs + nf] = feed_src
+        bt_view = i32[o_bt:o_bt + self.max_seqs * MB].reshape(self.max_seqs, MB)
+        bt_view[:B, :used_blocks] = self.bt_host[rows, :used_blocks]
+        if B_pad > B:
+            bt_view[B:B_pad, :used_blocks] = 0
+
+        # host -> device
+        ev0 = ev1 = None
+        if self.is_cuda and (want_device_timing or self.timing_events is not None):
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+        n64 = o_seed + self.max_seqs if not all_greedy else o_samp + max(ns, B_pad)
+        n32 = o_bt + (max(B_pad, B) - 1) * MB + used_blocks
+        self.d_i64[:n64].copy_(self.h_i64[:n64], non_blocking=True)
+        self.d_i32[:n32].copy_(self.h_i32[:n32], non_blocking=True)
+        self.h2d_bytes += n64 * 8 + n32 * 4
+        if not all_greedy:
+            self.d_f32.copy_(self.h_f32, non_blocking=True)
+            self.h2d_bytes += self.h_f32.numel() * 4
+        cur = self.step_counter & 1
+        prev_sampled = self.sampled[cur ^ 1]
+        if nf:
+            if self.is_cuda:
+                from ..ops import cuda as C
+                C.feed_tokens(self.input_ids, prev_sampled, self.feed_dst, self.feed_src, nf)
+            else:
+                self.input_ids[self.feed_dst[:nf].long()] = prev_sampled[self.feed_src[:nf].long()]
+
+        out_ids = self.sampled[cur]
+        md = AttentionMetadata(
+            num_tokens=T, num_decodes=B_pad - npf if use_graph else nd, num_prefills=npf,
+            num_decode_tokens=(B_pad if use_graph else nd),
+            positions=self.positions[:T], slot_mapping=self.slot_mapping[:T],
+            block_tables=self.block_tables[:max(B_pad, B)], seq_lens=self.seq_lens[:max(B_pad, B)],
+            cu_q_prefill=self.cu_q[:npf + 1] if npf else None,
+            num_q_tiles=int(((ntok[nd:] + 63) // 64).sum()) if npf else 0,
+            max_seq_len=max_seq_len,
+            decode_splits=self._decode_splits(B_pad if use_graph else max(nd, 1), max_seq_len),
+            decode_workspace=self.decode_ws,
+            sample_indices=self.sample_indices[:max(ns, 1)],
+            q_lens_cpu=[int(x) for x in ntok], seq_lens_cpu=[int(x) for x in seq_after])
+
+        if use_graph:
+            key = (B_pad, cur, all_greedy)
+            self.graphs[key].replay()
+            self.graph_launches += self.graph_kernel_counts.get(key, 0)
+        else:
+            with torch.inference_mode():
+                self._forward_and_sample(md, T, ns, out_ids, all_greedy)
+
+        # device -> host (asynchronous; consumed by StepHandle.token_ids)
+        host = self.sampled_host[cur]
+        event = None
+        if ns:
+            host[:ns].copy_(out_ids[:ns], non_blocking=True)
+            self.d2h_bytes += ns * 8
+        if self.is_cuda:
+            if ev1 is not None:
+                ev1.record()
+                if self.timing_events is not None:
+                    self.timing_events.append((ev0, ev1))
+            event = torch.cuda.Event()
+            event.record()
+        self.prev_index = {order[j].req.request_id: r for r, j in enumerate(samplers)}
+        self.step_counter += 1
+        return StepHandle([order[j].req.request_id for j in samplers], ns, host, event,
+                          width, device_ms_events=(ev0, ev1) if ev0 is not None else None)
+
+    def _forward_and_sample(self, md: AttentionMetadata, T: int, ns: int, out_ids: torch.Tensor,
+                            all_greedy: bool) -> None:
+        hidden = self.model(self.input_ids[:T], md, self.kv_caches)
+        if not self.model.is_last_stage or ns == 0:
+            return
+        if md.num_prefills == 0:
+            rows = hidden[:ns]          # decode-only: row i is the i-th sampling request
+        else:
+            rows = hidden.index_select(0, self.sample_indices[:ns])
+        logits = self.model.compute_logits(rows)
+        st = None if all_greedy else SamplingTensors(self.temperature[:ns], self.top_k[:ns],
+                                                     self.top_p[:ns], self.seeds[:ns])
+        self.sampler(logits, st, out=out_ids[:ns])
+
+    # -- CUDA graphs -----------------------------------------------------------------
+    def capture_graphs(self, sizes: Optional[list[int]] = None) -> None:
+        """Captures the decode-only step for every padded batch size, for both output
+        buffers and for the greedy / sampled variants."""
+        if not self.is_cuda or self.cfg.enforce_eager:
+            return
+        if sizes is None:
+            sizes = [1, 2, 4, 8] + list(range(16, self.max_seqs + 1, 16))
+        sizes = sorted({s for s in sizes if s <= self.max_seqs})
+        if self.max_seqs not in sizes:
+            sizes.append(self.max_seqs)
+        self.graph_sizes = sizes
+        self.seq_lens.zero_()
+        self.slot_mapping.fill_(-1)
+        torch.cuda.synchronize()
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream), torch.inference_mode():
+            for Bp in reversed(sizes):
+                for cur in (0, 1):
+                    for greedy in (True, False):
+                        md = AttentionMetadata(
+                            num_tokens=Bp, num_decodes=Bp, num_prefills=0, num_decode_tokens=Bp,
+                            positions=self.positions[:Bp], slot_mapping=self.slot_mapping[:Bp],
+                            block_tables=self.block_tables[:Bp], seq_lens=self.seq_lens[:Bp],
+                            max_seq_len=self.cfg.scheduler.max_model_len,
+                            decode_splits=self._decode_splits(Bp, self.cfg.scheduler.max_model_len),
+                            decode_workspace=self.decode_ws,
+                            sample_indices=self.sample_indices[:Bp])
+                        # warm-up outside the graph (lazy initialisation, autotuning)
+                        self._forward_and_sample(md, Bp, Bp, self.sampled[cur], greedy)
+                        stream.synchronize()
+                        g = torch.cuda.CUDAGraph()
+                        n0 = _native.launch_count
+                        with torch.cuda.graph(g, pool=self.graph_pool, stream=stream):
+                            self._forward_and_sample(md, Bp, Bp, self.sampled[cur], greedy)
+                        self.graph_kernel_counts[(Bp, cur, greedy)] = _native.launch_count - n0
+                        if self.graph_pool is None:
+                            self.graph_pool = g.pool()
+                        self.graphs[(Bp, cur, greedy)] = g
+        torch.cuda.synchronize()
+        _native.check_status()

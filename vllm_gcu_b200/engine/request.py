@@ -1,0 +1,146 @@
+"""Requests, sampling parameters and outputs of the engine."""
+from __future__ import annotations
+
+import enum
+import time
+from dataclasses import dataclass, field
+from typing import Any, Optional
+
+
+@dataclass
+class SamplingParams:
+    """Per-request sampling options (the subset the reference documents as supported,
+    ReadMe-EN.md:283-292: top-p / top-k, presence / frequency / repetition penalty,
+    ignore-eos, stop handling, logprobs)."""
+    max_tokens: int = 16
+    min_tokens: int = 0
+    temperature: float = 0.0
+    top_k: int = 0
+    top_p: float = 1.0
+    presence_penalty: float = 0.0
+    frequency_penalty: float = 0.0
+    repetition_penalty: float = 1.0
+    seed: Optional[int] = None
+    ignore_eos: bool = False
+    stop_token_ids: tuple[int, ...] = ()
+    include_stop_str_in_output: bool = False
+    logprobs: Optional[int] = None
+    prompt_logprobs: Optional[int] = None
+    n: int = 1
+    best_of: Optional[int] = None
+    use_beam_search: bool = False
+    extra_args: dict[str, Any] = field(default_factory=dict)
+
+    @property
+    def greedy(self) -> bool:
+        return self.temperature <= 0.0
+
+    @property
+    def has_penalties(self) -> bool:
+        return (self.presence_penalty != 0.0 or self.frequency_penalty != 0.0
+                or self.repetition_penalty != 1.0)
+
+
+class RequestStatus(enum.IntEnum):
+    WAITING = 0
+    RUNNING = 1
+    PREEMPTED = 2
+    SWAPPED = 3
+    FINISHED_STOPPED = 4
+    FINISHED_LENGTH = 5
+    FINISHED_ABORTED = 6
+
+    @property
+    def finished(self) -> bool:
+        return self >= RequestStatus.FINISHED_STOPPED
+
+
+@dataclass
+class Request:
+    request_id: str
+    prompt_token_ids: list[int]
+    sampling_params: SamplingParams
+    eos_token_id: Optional[int] = None
+    arrival_time: float = field(default_factory=time.monotonic)
+    priority: int = 0
+    lora_id: int = -1
+    is_idle: bool = False                     # keep-alive request of a DP replica
+    kv_transfer_params: Optional[dict] = None
+
+    # mutable state -------------------------------------------------------
+    status: RequestStatus = RequestStatus.WAITING
+    output_token_ids: list[int] = field(default_factory=list)
+    num_computed_tokens: int = 0              # tokens whose KV is in the cache
+    num_output_placeholders: int = 0          # async scheduling: tokens scheduled, id unknown
+    num_cached_tokens: int = 0                # prefix-cache hit length (first schedule)
+    spec_token_ids: list[int] = field(default_factory=list)
+    block_ids: list[int] = field(default_factory=list)
+    num_preemptions: int = 0
+    first_token_time: Optional[float] = None
+    finish_time: Optional[float] = None
+    logprobs: list[Any] = field(default_factory=list)
+
+    @property
+    def num_prompt_tokens(self) -> int:
+        return len(self.prompt_token_ids)
+
+    @property
+    def num_tokens(self) -> int:
+        """Known tokens (prompt + generated)."""
+        return len(self.prompt_token_ids) + len(self.output_token_ids)
+
+    @property
+    def num_tokens_with_placeholders(self) -> int:
+        return self.num_tokens + self.num_output_placeholders
+
+    @property
+    def all_token_ids(self) -> list[int]:
+        return self.prompt_token_ids + self.output_token_ids
+
+    @property
+    def finished(self) -> bool:
+        return self.status.finished
+
+    def token_at(self, i: int) -> int:
+        n = len(self.prompt_token_ids)
+        return self.prompt_token_ids[i] if i < n else self.output_token_ids[i - n]
+
+
+@dataclass
+class CompletionOutput:
+    index: int
+    token_ids: list[int]
+    finish_reason: Optional[str] = None
+    logprobs: Optional[list] = None
+    cumulative_logprob: Optional[float] = None
+
+
+@dataclass
+class RequestOutput:
+    request_id: str
+    prompt_token_ids: list[int]
+    outputs: list[CompletionOutput]
+    finished: bool
+    num_cached_tokens: int = 0
+    metrics: dict[str, float] = field(default_factory=dict)
+
+
+def check_stop(req: Request, max_model_len: int) -> bool:
+    """Applies the stop conditions to the last appended token.  Returns True when the
+    request finished (status updated)."""
+    sp = req.sampling_params
+    n_out = len(req.output_token_ids)
+    if n_out == 0:
+        return False
+    last = req.output_token_ids[-1]
+    if n_out >= sp.min_tokens:
+        if not sp.ignore_eos and req.eos_token_id is not None and last == req.eos_token_id:
+            req.status = RequestStatus.FINISHED_STOPPED
+            return True
+        if last in sp.stop_token_ids:
+            req.status = RequestStatus.FINISHED_STOPPED
+            return True
+    if n_out >= sp.max_tokens or req.num_tokens >= max_model_len:
+        req.status = RequestStatus.FINISHED_LENGTH
+        return True
+    return False

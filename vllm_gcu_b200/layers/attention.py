@@ -1,0 +1,126 @@
+"""Paged attention layer (GQA / MHA / MQA) and its per-step metadata.
+
+Batch layout of one step: the first ``num_decodes`` tokens are single-token decode
+requests, followed by the tokens of ``num_prefills`` requests with more than one
+scheduled token (prefill chunks, speculative verification).  The reference orders
+its MLA batches the same way (vllm_gcu/attention/backends/mla_v1_fusion.py:126-138).
+
+KV cache of a layer: one tensor ``[2, num_blocks, block_size, kv_heads, head_dim]``
+(the "flash" layout of csrc/src/reshape_and_cache_flash.cpp:23).
+
+GPU path per layer: one fused RoPE + cache-write kernel, then the split-KV decode
+kernel on the decode rows and the varlen paged-prefill kernel on the rest.  CPU path:
+the torch reference of the same ops.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+from ..ops import cuda as C
+from ..ops import ref
+from .basic import RMSNorm, RotaryEmbedding
+
+
+@dataclass
+class AttentionMetadata:
+    num_tokens: int                      # tokens in the step (incl. graph padding)
+    num_decodes: int                     # leading single-token requests
+    num_prefills: int                    # following multi-token requests
+    num_decode_tokens: int               # == num_decodes (kept for clarity)
+    positions: torch.Tensor              # [T] int64
+    slot_mapping: torch.Tensor           # [T] int64, -1 = padding
+    block_tables: torch.Tensor           # [B, max_blocks] int32
+    seq_lens: torch.Tensor               # [B] int32, kv length after this step
+    cu_q_prefill: Optional[torch.Tensor] = None   # [num_prefills + 1] int32, relative
+    num_q_tiles: int = 0                 # sum ceil(q_len / 64) over prefills (host value)
+    max_seq_len: int = 0
+    decode_splits: int = 1
+    decode_workspace: Optional[tuple[torch.Tensor, torch.Tensor]] = None
+    sample_indices: Optional[torch.Tensor] = None  # rows of the hidden states to sample from
+    # host copies (CPU reference path, drafters)
+    q_lens_cpu: list[int] = field(default_factory=list)
+    seq_lens_cpu: list[int] = field(default_factory=list)
+    # speculative decoding: every request with q_len > 1 verifies draft tokens
+    is_dummy: bool = False
+
+
+def allocate_kv_cache(num_layers: int, num_blocks: int, block_size: int, kv_heads: int,
+                      head_dim: int, dtype: torch.dtype, device) -> list[torch.Tensor]:
+    return [torch.zeros(2, num_blocks, block_size, kv_heads, head_dim, dtype=dtype, device=device)
+            for _ in range(num_layers)]
+
+
+class PagedAttention(nn.Module):
+    def __init__(self, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+                 rotary: Optional[RotaryEmbedding], q_norm: Optional[RMSNorm] = None,
+                 k_norm: Optional[RMSNorm] = None, sliding_window: int = 0):
+        super().__init__()
+        self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
+        self.scale = scale
+        self.rotary = rotary
+        self.q_norm, self.k_norm = q_norm, k_norm
+        self.window = sliding_window
+
+    def forward(self, qkv: torch.Tensor, kv_cache: torch.Tensor, md: AttentionMetadata
+                ) -> torch.Tensor:
+        """qkv ``[T, (Hq + 2 Hkv) * D]`` -> ``[T, Hq * D]``."""
+        T = qkv.shape[0]
+        D, Hq, Hkv = self.head_dim, self.num_heads, self.num_kv_heads
+        q, k, v = qkv.split([Hq * D, Hkv * D, Hkv * D], dim=-1)
+        if self.q_norm is not None:     # per-head QK RMSNorm (Qwen3)
+            q = self.q_norm(q.reshape(T, Hq, D)).reshape(T, Hq * D)
+            k = self.k_norm(k.reshape(T, Hkv, D)).reshape(T, Hkv * D)
+        k_cache, v_cache = kv_cache[0], kv_cache[1]
+        if ops.use_native(qkv) and qkv.dtype in (torch.bfloat16, torch.float16):
+            return self._forward_cuda(q, k, v, k_cache, v_cache, md)
+        return self._forward_ref(q, k, v, k_cache, v_cache, md)
+
+    # -- GPU -----------------------------------------------------------------
+    def _forward_cuda(self, q, k, v, k_cache, v_cache, md: AttentionMetadata) -> torch.Tensor:
+        T = q.shape[0]
+        D, Hq = self.head_dim, self.num_heads
+        rot = self.rotary
+        C.rope_cache_flash(q, k, v, md.positions if rot is not None else None,
+                           rot.cos_sin_cache if rot is not None else None,
+                           rot.is_neox if rot is not None else True, D, md.slot_mapping,
+                           k_cache, v_cache)
+        out = torch.empty((T, Hq * D), dtype=q.dtype, device=q.device)
+        nd = md.num_decode_tokens
+        if nd > 0:
+            C.paged_decode(q[:nd].view(nd, Hq, D), k_cache, v_cache, md.block_tables[:nd],
+                           md.seq_lens[:nd], self.scale, out=out[:nd].view(nd, Hq, D),
+                           num_splits=md.decode_splits, workspace=md.decode_workspace)
+        if md.num_prefills > 0:
+            npf = T - nd
+            C.varlen_prefill(q[nd:].view(npf, Hq, D), k_cache, v_cache,
+                             md.block_tables[md.num_decodes:md.num_decodes + md.num_prefills],
+                             md.cu_q_prefill,
+                             md.seq_lens[md.num_decodes:md.num_decodes + md.num_prefills],
+                             self.scale, md.num_q_tiles, out=out[nd:].view(npf, Hq, D),
+                             window=self.window)
+        return out
+
+    # -- CPU reference ----------------------------------------------------------
+    def _forward_ref(self, q, k, v, k_cache, v_cache, md: AttentionMetadata) -> torch.Tensor:
+        T = q.shape[0]
+        D, Hq, Hkv = self.head_dim, self.num_heads, self.num_kv_heads
+        if self.rotary is not None:
+            q, k = self.rotary(md.positions, q, k)
+        ref.reshape_and_cache_flash(k.reshape(T, Hkv, D), v.reshape(T, Hkv, D), k_cache, v_cache,
+                                    md.slot_mapping)
+        B = md.num_decodes + md.num_prefills
+        q_lens = [1] * md.num_decodes + list(md.q_lens_cpu[md.num_decodes:B])
+        cu = torch.zeros(B + 1, dtype=torch.int32)
+        cu[1:] = torch.tensor(q_lens, dtype=torch.int32).cumsum(0)
+        n_real = int(cu[-1])
+        out = torch.zeros((T, Hq * D), dtype=q.dtype, device=q.device)
+        o = ref.varlen_prefill_attention(q[:n_real].reshape(n_real, Hq, D), k_cache, v_cache,
+                                         md.block_tables[:B], cu, md.seq_lens[:B], self.scale,
+                                         window=self.window)
+        out[:n_real] = o.reshape(n_real, Hq * D)
+        return out

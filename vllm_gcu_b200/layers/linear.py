@@ -1,0 +1,263 @@
+"""Linear layers with tensor-parallel sharding and pluggable quantisation.
+
+Weights keep the ``[out_features, in_features]`` checkpoint layout, which is the
+K-major "B" operand of the tcgen05 GEMM, so loading is a slice-and-copy.
+
+Parallel flavours (names follow the checkpoint conventions the reference loads,
+vllm_gcu/models/deepseek_v3/deepseek_v3.py:1037-1173):
+
+* ``ColumnParallelLinear``        – output sharded over TP
+* ``MergedColumnParallelLinear``  – several column-parallel matrices stacked
+  (``gate_up_proj``); with ``fuse_silu`` the gate/up rows are interleaved in blocks
+  of 128 at load time and SiLU(gate)*up runs in the GEMM epilogue
+* ``QKVParallelLinear``           – fused q/k/v with GQA-aware sharding
+* ``RowParallelLinear``           – input sharded, output all-reduced (or left partial /
+  reduce-scattered for sequence parallelism)
+* ``ReplicatedLinear`` / ``MergedReplicatedLinear`` – unsharded (router gate, MLA
+  ``q_a_proj`` + ``kv_a_proj_with_mqa`` fused as in vllm_gcu/kernels/linear.py:21-149)
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import ops
+from ..ops import cuda as C
+from ..ops import ref
+from ..parallel.communicator import get_comm
+from ..parallel.state import tp_rank, tp_size
+
+
+class LinearMethod:
+    """Strategy object: creates the parameters of a layer and applies it."""
+
+    def create_weights(self, layer: "LinearBase") -> None:
+        raise NotImplementedError
+
+    def apply(self, layer: "LinearBase", x: torch.Tensor, **kw) -> torch.Tensor:
+        raise NotImplementedError
+
+    def process_weights_after_loading(self, layer: "LinearBase") -> None:
+        pass
+
+
+class UnquantizedLinearMethod(LinearMethod):
+    def create_weights(self, layer: "LinearBase") -> None:
+        layer.weight = nn.Parameter(torch.empty(layer.out_per_rank, layer.in_per_rank,
+                                                dtype=layer.dtype, device=layer.device),
+                                    requires_grad=False)
+
+    def process_weights_after_loading(self, layer: "LinearBase") -> None:
+        if getattr(layer, "fuse_silu", False) and not getattr(layer, "_interleaved", False):
+            w = layer.weight.data
+            half = w.shape[0] // 2
+            if half % 128 == 0 and w.dtype == torch.bfloat16:
+                layer.weight.data = ref.interleave_gate_up(w[:half], w[half:]).contiguous()
+                layer._interleaved = True
+
+    def apply(self, layer: "LinearBase", x: torch.Tensor, residual=None, skip_bias=False,
+              **kw) -> torch.Tensor:
+        w = layer.weight
+        bias = None if skip_bias else layer.bias
+        if ops.use_native(x) and x.dtype == torch.bfloat16:
+            shape = x.shape
+            x2 = x.reshape(-1, shape[-1])
+            if getattr(layer, "_interleaved", False):
+                y = C.gemm_bf16(x2, w, epilogue=C.EPI_SILU_MUL)
+            else:
+                if bias is not None and residual is not None:
+                    y = C.gemm_bf16(x2, w, bias=bias)
+                    y += residual
+                else:
+                    y = C.gemm_bf16(x2, w, bias=bias, residual=residual)
+                if getattr(layer, "fuse_silu", False):
+                    y = C.activation(y, "silu")
+            return y.view(*shape[:-1], y.shape[-1])
+        y = F.linear(x, w, bias)
+        if residual is not None:
+            y = y + residual
+        if getattr(layer, "fuse_silu", False):
+            y = ref.silu_and_mul(y)
+        return y
+
+
+class LinearBase(nn.Module):
+    def __init__(self, in_features: int, out_features: int, in_per_rank: int, out_per_rank: int,
+                 bias: bool, dtype: torch.dtype, device, quant_method: Optional[LinearMethod],
+                 prefix: str = ""):
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        self.in_per_rank, self.out_per_rank = in_per_rank, out_per_rank
+        self.dtype, self.device, self.prefix = dtype, device, prefix
+        self.quant_method = quant_method or UnquantizedLinearMethod()
+        self.quant_method.create_weights(self)
+        if bias:
+            self.bias = nn.Parameter(torch.zeros(out_per_rank, dtype=dtype, device=device),
+                                     requires_grad=False)
+        else:
+            self.bias = None
+
+    def forward(self, x: torch.Tensor, **kw) -> torch.Tensor:
+        return self.quant_method.apply(self, x, **kw)
+
+    # -- loading -----------------------------------------------------------
+    def shard_of(self, name: str, full: torch.Tensor, shard_id=None) -> tuple[torch.Tensor, Optional[slice]]:
+        """Returns (tensor slice for this rank, destination row range or None)."""
+        return full, None
+
+    def load_weight(self, name: str, full: torch.Tensor, shard_id=None) -> None:
+        """Copies the part of checkpoint tensor ``full`` (parameter ``name``: 'weight',
+        'bias', or a quantisation tensor) that belongs to this rank."""
+        loader = getattr(self.quant_method, "load_weight", None)
+        if loader is not None and loader(self, name, full, shard_id):
+            return
+        param = getattr(self, name)
+        src, rows = self.shard_of(name, full, shard_id)
+        dst = param.data if rows is None else param.data[rows]
+        assert dst.shape == src.shape, f"{self.prefix}.{name}: {tuple(dst.shape)} vs {tuple(src.shape)}"
+        dst.copy_(src)
+
+    def finalize(self) -> None:
+        self.quant_method.process_weights_after_loading(self)
+
+
+class ReplicatedLinear(LinearBase):
+    def __init__(self, in_features, out_features, bias=False, dtype=torch.bfloat16,
+                 device=None, quant_method=None, prefix=""):
+        super().__init__(in_features, out_features, in_features, out_features, bias, dtype,
+                         device, quant_method, prefix)
+
+
+class MergedReplicatedLinear(ReplicatedLinear):
+    """Several replicated projections of the same input stacked along the output dim."""
+
+    def __init__(self, in_features, output_sizes: Sequence[int], **kw):
+        self.output_sizes = list(output_sizes)
+        super().__init__(in_features, sum(output_sizes), **kw)
+
+    def shard_of(self, name, full, shard_id=None):
+        if shard_id is None:
+            return full, None
+        off = sum(self.output_sizes[:shard_id])
+        return full, slice(off, off + self.output_sizes[shard_id])
+
+
+class ColumnParallelLinear(LinearBase):
+    def __init__(self, in_features, out_features, bias=False, gather_output=False,
+                 dtype=torch.bfloat16, device=None, quant_method=None, prefix=""):
+        tp = tp_size()
+        assert out_features % tp == 0
+        self.gather_output = gather_output
+        super().__init__(in_features, out_features, in_features, out_features // tp, bias, dtype,
+                         device, quant_method, prefix)
+
+    def shard_of(self, name, full, shard_id=None):
+        n = self.out_per_rank
+        return full.narrow(0, tp_rank() * n, n), None
+
+    def forward(self, x, **kw):
+        y = super().forward(x, **kw)
+        if self.gather_output and tp_size() > 1:
+            y = get_comm("tp").all_gather(y, dim=-1)
+        return y
+
+
+class MergedColumnParallelLinear(LinearBase):
+    def __init__(self, in_features, output_sizes: Sequence[int], bias=False, fuse_silu=False,
+                 dtype=torch.bfloat16, device=None, quant_method=None, prefix=""):
+        tp = tp_size()
+        self.output_sizes = list(output_sizes)
+        assert all(s % tp == 0 for s in output_sizes)
+        self.fuse_silu = fuse_silu
+        self._interleaved = False
+        super().__init__(in_features, sum(output_sizes), in_features, sum(output_sizes) // tp,
+                         bias, dtype, device, quant_method, prefix)
+
+    def shard_of(self, name, full, shard_id=None):
+        tp, r = tp_size(), tp_rank()
+        if shard_id is None:      # already-merged checkpoint tensor: split it first
+            parts = torch.split(full, self.output_sizes, dim=0)
+            src = torch.cat([p.narrow(0, r * (p.shape[0] // tp), p.shape[0] // tp)
+                             for p in parts], dim=0)
+            return src, None
+        n = self.output_sizes[shard_id] // tp
+        off = sum(s // tp for s in self.output_sizes[:shard_id])
+        return full.narrow(0, r * n, n), slice(off, off + n)
+
+
+class QKVParallelLinear(LinearBase):
+    def __init__(self, hidden_size, head_dim, num_heads, num_kv_heads, bias=False,
+                 dtype=torch.bfloat16, device=None, quant_method=None, prefix=""):
+        tp = tp_size()
+        assert num_heads % tp == 0
+        self.head_dim = head_dim
+        self.num_heads = num_heads // tp
+        if num_kv_heads >= tp:
+            assert num_kv_heads % tp == 0
+            self.num_kv_heads, self.kv_replicas = num_kv_heads // tp, 1
+        else:
+            assert tp % num_kv_heads == 0
+            self.num_kv_heads, self.kv_replicas = 1, tp // num_kv_heads
+        self.total_kv_heads = num_kv_heads
+        out_pr = (self.num_heads + 2 * self.num_kv_heads) * head_dim
+        super().__init__(hidden_size, (num_heads + 2 * num_kv_heads) * head_dim, hidden_size,
+                         out_pr, bias, dtype, device, quant_method, prefix)
+
+    @property
+    def q_size(self) -> int:
+        return self.num_heads * self.head_dim
+
+    @property
+    def kv_size(self) -> int:
+        return self.num_kv_heads * self.head_dim
+
+    def shard_of(self, name, full, shard_id=None):
+        r = tp_rank()
+        if shard_id is None:
+            tq = self.num_heads * tp_size() * self.head_dim
+            tkv = self.total_kv_heads * self.head_dim
+            q, k, v = torch.split(full, [tq, tkv, tkv], dim=0)
+            parts = [self.shard_of(name, q, "q")[0], self.shard_of(name, k, "k")[0],
+                     self.shard_of(name, v, "v")[0]]
+            return torch.cat(parts, dim=0), None
+        if shard_id == "q":
+            return full.narrow(0, r * self.q_size, self.q_size), slice(0, self.q_size)
+        kv_rank = r // self.kv_replicas
+        src = full.narrow(0, kv_rank * self.kv_size, self.kv_size)
+        off = self.q_size + (0 if shard_id == "k" else self.kv_size)
+        return src, slice(off, off + self.kv_size)
+
+
+class RowParallelLinear(LinearBase):
+    def __init__(self, in_features, out_features, bias=False, reduce_results=True,
+                 dtype=torch.bfloat16, device=None, quant_method=None, prefix=""):
+        tp = tp_size()
+        assert in_features % tp == 0
+        self.reduce_results = reduce_results
+        super().__init__(in_features, out_features, in_features // tp, out_features, bias, dtype,
+                         device, quant_method, prefix)
+
+    def shard_of(self, name, full, shard_id=None):
+        if name == "bias" or full.dim() == 1:
+            return full, None
+        n = self.in_per_rank
+        return full.narrow(1, tp_rank() * n, n), None
+
+    def forward(self, x, **kw):
+        if tp_size() == 1 or not self.reduce_results:
+            return super().forward(x, **kw)
+        comm = get_comm("tp")
+        fused = getattr(comm, "fused", None)
+        if fused is not None and isinstance(self.quant_method, UnquantizedLinearMethod) \
+                and self.bias is None:
+            y = fused.gemm_all_reduce(x, self.weight)
+            if y is not None:
+                return y
+        y = self.quant_method.apply(self, x, skip_bias=True)
+        y = comm.all_reduce(y)
+        if self.bias is not None:   # added once, after the reduction
+            y = y + self.bias
+        return y

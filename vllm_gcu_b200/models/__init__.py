@@ -1,0 +1,48 @@
+"""Model registry: HuggingFace architecture name -> implementation.
+
+The reference registers its model classes with vLLM's ``ModelRegistry``
+(vllm_gcu/models/__init__.py:20-40); this table is the same idea for the built-in engine
+and is also what the vLLM plugin entry point registers.
+"""
+from __future__ import annotations
+
+import importlib
+from typing import Callable
+
+_REGISTRY: dict[str, str] = {
+    "LlamaForCausalLM": "vllm_gcu_b200.models.llama:LlamaForCausalLM",
+    "MistralForCausalLM": "vllm_gcu_b200.models.llama:LlamaForCausalLM",
+    "Qwen2ForCausalLM": "vllm_gcu_b200.models.llama:Qwen2ForCausalLM",
+    "Qwen3ForCausalLM": "vllm_gcu_b200.models.llama:Qwen3ForCausalLM",
+    "Glm4ForCausalLM": "vllm_gcu_b200.models.llama:Glm4ForCausalLM",
+    "InternLM2ForCausalLM": "vllm_gcu_b200.models.llama:LlamaForCausalLM",
+    "YiForCausalLM": "vllm_gcu_b200.models.llama:LlamaForCausalLM",
+    "Qwen3MoeForCausalLM": "vllm_gcu_b200.models.moe_models:Qwen3MoeForCausalLM",
+    "MixtralForCausalLM": "vllm_gcu_b200.models.moe_models:MixtralForCausalLM",
+    "QuantMixtralForCausalLM": "vllm_gcu_b200.models.moe_models:MixtralForCausalLM",
+    "DeepseekV2ForCausalLM": "vllm_gcu_b200.models.deepseek:DeepseekV3ForCausalLM",
+    "DeepseekV3ForCausalLM": "vllm_gcu_b200.models.deepseek:DeepseekV3ForCausalLM",
+    "DeepSeekMTPModel": "vllm_gcu_b200.models.deepseek_mtp:DeepSeekMTP",
+}
+
+
+def register_model(arch: str, target: str) -> None:
+    """``target`` is ``"module.path:ClassName"``."""
+    _REGISTRY[arch] = target
+
+
+def supported_architectures() -> list[str]:
+    return sorted(_REGISTRY)
+
+
+def get_model_class(arch: str) -> Callable:
+    try:
+        target = _REGISTRY[arch]
+    except KeyError:
+        raise ValueError(f"unsupported architecture {arch!r}; known: {supported_architectures()}")
+    mod, _, cls = target.partition(":")
+    return getattr(importlib.import_module(mod), cls)
+
+
+def build_model(cfg, device):
+    return get_model_class(cfg.architecture)(cfg, device)

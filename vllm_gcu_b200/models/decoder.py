@@ -1,0 +1,275 @@
+"""Generic pre-norm decoder-only transformer.
+
+One implementation, configured by :class:`ModelConfig`, serves the dense families the
+reference supports through its own or upstream model code (Llama 2/3, Qwen 2/2.5/3,
+GLM-4-0414 with sandwich norms and partial GPT-J rotary, Mistral/Yi/InternLM-style
+checkpoints) and hosts the MoE and MLA blocks of the Qwen3-MoE / Mixtral / DeepSeek
+models.  The layer structure follows vllm_gcu/models/qwen3/qwen3.py:437 and
+vllm_gcu/models/glm4/glm4.py:173-231; checkpoint names are the HuggingFace ones.
+"""
+from __future__ import annotations
+
+import zlib
+from typing import Iterable, Optional
+
+import torch
+import torch.nn as nn
+
+from ..config import ModelConfig
+from ..layers.attention import AttentionMetadata, PagedAttention
+from ..layers.basic import ParallelLMHead, RMSNorm, RotaryEmbedding, VocabParallelEmbedding
+from ..layers.linear import (MergedColumnParallelLinear, QKVParallelLinear, RowParallelLinear)
+from ..parallel.state import get_state, tp_size
+
+
+def get_linear_method(cfg: ModelConfig, prefix: str):
+    """Quantised linear method for the layer called ``prefix`` (None = unquantised)."""
+    if not cfg.quantization:
+        return None
+    from ..layers.quant import get_quant_config
+    return get_quant_config(cfg).get_linear_method(prefix)
+
+
+class DenseMLP(nn.Module):
+    def __init__(self, cfg: ModelConfig, hidden: int, inter: int, device, prefix: str,
+                 reduce_results: bool = True):
+        super().__init__()
+        self.gate_up_proj = MergedColumnParallelLinear(
+            hidden, [inter, inter], bias=cfg.mlp_bias, fuse_silu=(cfg.hidden_act == "silu"),
+            dtype=cfg.dtype, device=device,
+            quant_method=get_linear_method(cfg, prefix + ".gate_up_proj"),
+            prefix=prefix + ".gate_up_proj")
+        self.down_proj = RowParallelLinear(
+            inter, hidden, bias=cfg.mlp_bias, reduce_results=reduce_results, dtype=cfg.dtype,
+            device=device, quant_method=get_linear_method(cfg, prefix + ".down_proj"),
+            prefix=prefix + ".down_proj")
+        self.act = cfg.hidden_act
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        h = self.gate_up_proj(x)
+        if not self.gate_up_proj.fuse_silu:
+            from ..layers.activation import act_and_mul
+            h = act_and_mul(h, self.act)
+        return self.down_proj(h)
+
+
+class GQAAttention(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, device, prefix: str):
+        super().__init__()
+        D = cfg.head_dim
+        self.qkv_proj = QKVParallelLinear(
+            cfg.hidden_size, D, cfg.num_attention_heads, cfg.num_key_value_heads,
+            bias=cfg.attention_bias, dtype=cfg.dtype, device=device,
+            quant_method=get_linear_method(cfg, prefix + ".qkv_proj"), prefix=prefix + ".qkv_proj")
+        self.o_proj = RowParallelLinear(
+            cfg.num_attention_heads * D, cfg.hidden_size, bias=False, dtype=cfg.dtype,
+            device=device, quant_method=get_linear_method(cfg, prefix + ".o_proj"),
+            prefix=prefix + ".o_proj")
+        rotary = RotaryEmbedding(D, cfg.rotary_dim, cfg.max_position_embeddings, cfg.rope_theta,
+                                 cfg.rope_is_neox, cfg.rope_scaling, cfg.dtype, device)
+        qn = kn = None
+        if cfg.qk_norm:
+            qn = RMSNorm(D, cfg.rms_norm_eps, cfg.dtype, device)
+            kn = RMSNorm(D, cfg.rms_norm_eps, cfg.dtype, device)
+        self.q_norm, self.k_norm = qn, kn
+        self.attn = PagedAttention(self.qkv_proj.num_heads, self.qkv_proj.num_kv_heads, D,
+                                   D ** -0.5, rotary, qn, kn, cfg.sliding_window)
+
+    def forward(self, x: torch.Tensor, kv_cache: torch.Tensor, md: AttentionMetadata
+                ) -> torch.Tensor:
+        qkv = self.qkv_proj(x)
+        return self.o_proj(self.attn(qkv, kv_cache, md))
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, device, prefix: str):
+        super().__init__()
+        self.layer_idx = layer_idx
+        H = cfg.hidden_size
+        if cfg.is_mla:
+            from .deepseek import MLAAttention
+            self.self_attn = MLAAttention(cfg, layer_idx, device, prefix + ".self_attn")
+        else:
+            self.self_attn = GQAAttention(cfg, layer_idx, device, prefix + ".self_attn")
+        if cfg.is_moe_layer(layer_idx):
+            from ..layers.moe import SparseMoeBlock
+            self.mlp = SparseMoeBlock(cfg, device, prefix + ".mlp")
+        else:
+            self.mlp = DenseMLP(cfg, H, cfg.intermediate_size, device, prefix + ".mlp")
+        self.input_layernorm = RMSNorm(H, cfg.rms_norm_eps, cfg.dtype, device)
+        self.post_attention_layernorm = RMSNorm(H, cfg.rms_norm_eps, cfg.dtype, device)
+        self.sandwich = cfg.sandwich_norm
+        if self.sandwich:
+            self.post_self_attn_layernorm = RMSNorm(H, cfg.rms_norm_eps, cfg.dtype, device)
+            self.post_mlp_layernorm = RMSNorm(H, cfg.rms_norm_eps, cfg.dtype, device)
+
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor], kv_cache: torch.Tensor,
+                md: AttentionMetadata):
+        if residual is None:
+            residual = x
+            h = self.input_layernorm(x)
+        else:
+            h, residual = self.input_layernorm(x, residual)
+        h = self.self_attn(h, kv_cache, md)
+        if self.sandwich:
+            h = self.post_self_attn_layernorm(h)
+        h, residual = self.post_attention_layernorm(h, residual)
+        h = self.mlp(h)
+        if self.sandwich:
+            h = self.post_mlp_layernorm(h)
+        return h, residual
+
+
+class DecoderLM(nn.Module):
+    """Embedding -> N decoder layers -> final norm -> vocab-parallel LM head."""
+
+    # checkpoint-name fragments that are stacked into one parameter: (param, ckpt, shard id)
+    stacked_params = [
+        ("qkv_proj", "q_proj", "q"), ("qkv_proj", "k_proj", "k"), ("qkv_proj", "v_proj", "v"),
+        ("gate_up_proj", "gate_proj", 0), ("gate_up_proj", "up_proj", 1),
+    ]
+
+    def __init__(self, cfg: ModelConfig, device="cpu"):
+        super().__init__()
+        self.cfg = cfg
+        self.device = torch.device(device)
+        st = get_state()
+        pp, pp_rank = st.pp.world_size, st.pp.rank_in_group
+        L = cfg.num_hidden_layers
+        per = -(-L // pp)
+        self.start_layer, self.end_layer = min(L, pp_rank * per), min(L, (pp_rank + 1) * per)
+        self.is_first_stage, self.is_last_stage = pp_rank == 0, pp_rank == pp - 1
+        if self.is_first_stage or (cfg.tie_word_embeddings and self.is_last_stage):
+            self.embed_tokens = VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, cfg.dtype,
+                                                       device)
+        self.layers = nn.ModuleDict({
+            str(i): DecoderLayer(cfg, i, device, f"model.layers.{i}")
+            for i in range(self.start_layer, self.end_layer)})
+        if self.is_last_stage:
+            self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.dtype, device)
+            if cfg.tie_word_embeddings:
+                self.lm_head = None
+            else:
+                self.lm_head = ParallelLMHead(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device)
+
+    # -- execution ---------------------------------------------------------------
+    @property
+    def num_local_layers(self) -> int:
+        return self.end_layer - self.start_layer
+
+    def kv_cache_spec(self) -> dict:
+        """Shape information the runner needs to allocate this model's KV cache."""
+        cfg = self.cfg
+        if cfg.is_mla:
+            return {"type": "mla", "layers": self.num_local_layers,
+                    "width": cfg.kv_lora_rank + cfg.qk_rope_head_dim}
+        kvh = max(1, cfg.num_key_value_heads // tp_size())
+        return {"type": "gqa", "layers": self.num_local_layers, "kv_heads": kvh,
+                "head_dim": cfg.head_dim}
+
+    def forward(self, input_ids: Optional[torch.Tensor], md: AttentionMetadata,
+                kv_caches: list[torch.Tensor],
+                intermediate: Optional[tuple[torch.Tensor, torch.Tensor]] = None,
+                inputs_embeds: Optional[torch.Tensor] = None):
+        """Returns final hidden states ``[T, H]`` on the last pipeline stage, otherwise the
+        ``(hidden, residual)`` pair handed to the next stage."""
+        if self.is_first_stage:
+            x = inputs_embeds if inputs_embeds is not None else self.embed_tokens(input_ids)
+            residual = None
+        else:
+            x, residual = intermediate
+        for j, i in enumerate(range(self.start_layer, self.end_layer)):
+            x, residual = self.layers[str(i)](x, residual, kv_caches[j], md)
+        if not self.is_last_stage:
+            return x, residual
+        if residual is None:
+            return self.norm(x)
+        x, _ = self.norm(x, residual)
+        return x
+
+    def _head(self) -> ParallelLMHead:
+        return self.lm_head if self.lm_head is not None else self.embed_tokens  # type: ignore
+
+    def compute_logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        head = self._head()
+        if isinstance(head, ParallelLMHead):
+            return head.logits(hidden)
+        return ParallelLMHead.logits(head, hidden)  # tied embedding
+
+    def greedy_tokens(self, hidden: torch.Tensor) -> torch.Tensor:
+        head = self._head()
+        return ParallelLMHead.greedy(head, hidden)
+
+    # -- weights --------------------------------------------------------------------
+    def named_loadables(self) -> dict[str, nn.Module]:
+        """Maps parameter-owner module paths (``model.layers.0.self_attn.qkv_proj``) to
+        modules that implement ``load_weight``."""
+        out: dict[str, nn.Module] = {}
+        for name, mod in self.named_modules():
+            if hasattr(mod, "load_weight"):
+                out[self._ckpt_prefix(name)] = mod
+        return out
+
+    @staticmethod
+    def _ckpt_prefix(module_path: str) -> str:
+        # self.layers is a ModuleDict keyed by layer index
+        if module_path.startswith("layers."):
+            return "model." + module_path
+        if module_path in ("embed_tokens", "norm"):
+            return "model." + module_path
+        return module_path
+
+    def map_weight_name(self, name: str) -> Optional[tuple[str, str, object]]:
+        """checkpoint tensor name -> (owner module path, parameter name, shard id)."""
+        if "rotary_emb.inv_freq" in name:
+            return None
+        owner, _, pname = name.rpartition(".")
+        for stacked, ckpt, sid in self.stacked_params:
+            if owner.endswith("." + ckpt):
+                return owner[: -len(ckpt)] + stacked, pname, sid
+        if owner.endswith(".q_norm") or owner.endswith(".k_norm"):
+            return owner, pname, None
+        return owner, pname, None
+
+    def load_weights(self, weights: Iterable[tuple[str, torch.Tensor]]) -> set[str]:
+        owners = self.named_loadables()
+        loaded: set[str] = set()
+        for name, tensor in weights:
+            m = self.map_weight_name(name)
+            if m is None:
+                continue
+            owner, pname, sid = m
+            mod = owners.get(owner)
+            if mod is None:
+                continue        # another pipeline stage / unused tensor
+            mod.load_weight(pname, tensor, sid)
+            loaded.add(name)
+        self.finalize_weights()
+        return loaded
+
+    def finalize_weights(self) -> None:
+        for mod in self.modules():
+            fin = getattr(mod, "finalize", None)
+            if fin is not None and mod is not self:
+                fin()
+
+    @torch.no_grad()
+    def init_random(self, seed: int = 0, std: float = 0.02) -> None:
+        """Random initialisation N(0, std) of this rank's shards ("dummy" load format of
+        the benchmarks); norm weights are one, biases zero."""
+        gen_dev = self.device
+        for name, p in sorted(self.named_parameters()):
+            if p.dtype not in (torch.float32, torch.bfloat16, torch.float16):
+                continue
+            g = torch.Generator(device=gen_dev)
+            g.manual_seed(zlib.crc32(name.encode()) ^ seed)
+            if name.endswith("norm.weight") or ".q_norm." in name or ".k_norm." in name \
+                    or name.endswith("layernorm.weight"):
+                p.data.fill_(1.0)
+            elif name.endswith(".bias") or "e_score_correction_bias" in name:
+                p.data.zero_()
+            else:
+                chunk = torch.empty(p.shape, dtype=torch.float32, device=gen_dev)
+                chunk.normal_(0.0, std, generator=g)
+                p.data.copy_(chunk)
+        self.finalize_weights()

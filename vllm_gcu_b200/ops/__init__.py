@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import torch
 
-from . import _native, ref  # noqa: F401
+from . import _native, cuda, ref  # noqa: F401
 
 
 def use_native(t: torch.Tensor) -> bool:
@@ -20,10 +20,3 @@ def use_native(t: torch.Tensor) -> bool:
     if _native.lib() is None:  # raises on a GPU machine without the build
         return False
     return True
-
-
-def __getattr__(name: str):
-    if name == "cuda":
-        from . import cuda as _cuda
-        return _cuda
-    raise AttributeError(name)
