@@ -163,9 +163,12 @@ def main() -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
+    breakdown: dict = {}
+
     def one_pass(seed: int, timed: bool):
         prompts = make_prompts(seed)       # fresh ids: no prefix-cache reuse across passes
         eng.runner.timing_events = [] if timed else None
+        eng.runner.timing_meta = []
         t0 = time.perf_counter()
         outs = llm.generate(prompts, sp)
         torch.cuda.synchronize()
@@ -173,7 +176,14 @@ def main() -> None:
         n_out = sum(len(o.outputs[0].token_ids) for o in outs)
         dev_ms = 0.0
         if timed:
-            dev_ms = sum(a.elapsed_time(b) for a, b in eng.runner.timing_events)
+            times = [a.elapsed_time(b) for a, b in eng.runner.timing_events]
+            dev_ms = sum(times)
+            for t, (nd, npf, ntok) in zip(times, eng.runner.timing_meta):
+                kind = "decode" if npf == 0 else ("prefill" if nd == 0 else "mixed")
+                acc = breakdown.setdefault(kind, [0, 0.0, 0])
+                acc[0] += 1
+                acc[1] += t
+                acc[2] += ntok
             eng.runner.timing_events = None
         return n_out, wall, dev_ms
 
@@ -230,6 +240,8 @@ def main() -> None:
                     "d2h_bytes_per_step": (eng.runner.d2h_bytes - d2h0) // max(1, args.steps),
                     "wall_ms_per_step": round(wall_ms / args.steps, 3)},
             "gpu_launches": int(launches),
+            "step_breakdown": {k: {"engine_steps": v[0], "device_ms": round(v[1], 1),
+                                   "tokens": v[2]} for k, v in breakdown.items()},
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)

@@ -100,6 +100,9 @@ class ModelRunner:
         self.graph_launches = 0                    # kernels replayed through CUDA graphs
         self.graph_kernel_counts: dict = {}
         self.timing_events: Optional[list] = None  # set to a list to time every step
+        self.timing_meta: list = []                # (decodes, prefills, tokens) per timed step
+        self.keep_logits = False                   # debugging / tests: keep last step's logits
+        self.last_logits: Optional[torch.Tensor] = None
         self._alloc_buffers()
 
     # -- buffers -------------------------------------------------------------------
@@ -422,6 +425,7 @@ class ModelRunner:
                 ev1.record()
                 if self.timing_events is not None:
                     self.timing_events.append((ev0, ev1))
+                    self.timing_meta.append((nd, npf, T_real))
             event = torch.cuda.Event()
             event.record()
         self.prev_index = {order[j].req.request_id: r for r, j in enumerate(samplers)}
@@ -439,6 +443,8 @@ class ModelRunner:
         else:
             rows = hidden.index_select(0, self.sample_indices[:ns])
         logits = self.model.compute_logits(rows)
+        if self.keep_logits:
+            self.last_logits = logits.float().cpu()
         st = None if all_greedy else SamplingTensors(self.temperature[:ns], self.top_k[:ns],
                                                      self.top_p[:ns], self.seeds[:ns])
         self.sampler(logits, st, out=out_ids[:ns])

@@ -72,6 +72,9 @@ class PagedAttention(nn.Module):
         T = qkv.shape[0]
         D, Hq, Hkv = self.head_dim, self.num_heads, self.num_kv_heads
         q, k, v = qkv.split([Hq * D, Hkv * D, Hkv * D], dim=-1)
+        if kv_cache is None or md.is_dummy:
+            # memory profile / keep-alive step of an idle rank: no cache, no attention
+            return torch.zeros((T, Hq * D), dtype=qkv.dtype, device=qkv.device)
         if self.q_norm is not None:     # per-head QK RMSNorm (Qwen3)
             q = self.q_norm(q.reshape(T, Hq, D)).reshape(T, Hq * D)
             k = self.k_norm(k.reshape(T, Hkv, D)).reshape(T, Hkv * D)
