@@ -33,6 +33,21 @@ enum Epilogue : int {
   kEpiSiluMul = 2,
   kEpiResidual = 3,
   kEpiFp32 = 4,
+  kEpiAllReduce = 5,  // row-parallel partial product -> tile-wise two-shot all-reduce over peers
+};
+
+constexpr int kMaxPeers = 8;
+
+// Peer-visible addresses of the symmetric buffers used by the fused all-reduce epilogue.
+// Index r is rank r's copy; [rank] is this GPU's own memory.
+struct ArArgs {
+  __nv_bfloat16* partial[kMaxPeers];  // [tiles][BM*BN] bf16 partial products of rank r
+  __nv_bfloat16* out[kMaxPeers];      // [M, ldc] reduced result on rank r
+  uint32_t* ready[kMaxPeers];         // [tiles][p]: partial of (tile, src) is complete (epoch value)
+  uint32_t* done[kMaxPeers];          // [tiles]: reduced tile has been written to rank r (epoch)
+  uint32_t* epoch_ptr;                // local: epoch of the previous launch
+  uint32_t* done_ctr;                 // local: CTAs of this launch that have finished
+  int rank, p;
 };
 
 struct Args {
@@ -44,7 +59,32 @@ struct Args {
   int M, N, K;
   int tiles_m, tiles_n;
   unsigned int* status;
+  ArArgs ar;
 };
+
+// Bounded acquire-wait until *flag == want.  Returns false on timeout.
+__device__ __forceinline__ bool wait_flag_sys(const uint32_t* flag, uint32_t want) {
+  for (uint32_t it = 0; it < (1u << 22); ++it) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v == want) return true;
+    if (it > 64) __nanosleep(100);
+  }
+  return false;
+}
+__device__ __forceinline__ void signal_flag_sys(uint32_t* flag, uint32_t val) {
+  __threadfence_system();
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(val) : "memory");
+}
+__device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 template <int BN, int STAGES>
 struct Smem {
@@ -119,6 +159,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   const int num_kb = (p.K + BK - 1) / BK;
   const int num_tiles = p.tiles_m * p.tiles_n;
+  uint32_t epoch = 0;
+  if constexpr (EPI == kEpiAllReduce)
+    epoch = *reinterpret_cast<volatile uint32_t*>(p.ar.epoch_ptr) + 1u;
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -226,6 +269,27 @@ __global__ void __launch_bounds__(kThreads, 1)
           const int col = out_n0 + c * 32;
           if (row_ok && col < out_n) store_row_bf16(crow + col, v, min(32, out_n - col));
         }
+      } else if constexpr (EPI == kEpiAllReduce) {
+        // phase 1: park the bf16 partial tile in this GPU's symmetric buffer, then tell
+        // the tile's owner that this rank's contribution is complete
+        __nv_bfloat16* ptile = p.ar.partial[p.ar.rank] + static_cast<long long>(tile) * (BM * BN) +
+                               (q * 32 + lane) * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          store_row_bf16(ptile + c * 32, v, 32);
+        }
+        epi_bar_sync();
+        if (threadIdx.x == 64) {
+          const int owner = tile % p.ar.p;
+          signal_flag_sys(p.ar.ready[owner] + static_cast<long long>(tile) * p.ar.p + p.ar.rank,
+                          epoch);
+        }
       } else {
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
@@ -268,11 +332,80 @@ __global__ void __launch_bounds__(kThreads, 1)
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
+
+    if constexpr (EPI == kEpiAllReduce) {
+      const int te = threadIdx.x - 64;  // 0..127 among the epilogue warps
+      const int np = p.ar.p, rank = p.ar.rank;
+      constexpr int kVecPerRow = BN / 8;
+      // phase 2: reduce the tiles this rank owns (tile % p == rank) and broadcast them
+      for (int t = rank + static_cast<int>(blockIdx.x) * np; t < num_tiles; t += gridDim.x * np) {
+        bool ok = true;
+        if (te < np)
+          ok = wait_flag_sys(p.ar.ready[rank] + static_cast<long long>(t) * np + te, epoch);
+        if (!ok) {
+          report_status(p.status, kStatusFlagTimeout, kKernelId, 0x500u + te);
+          *abort_flag = 1u;
+        }
+        epi_bar_sync();
+        if (*abort_flag != 0u) break;
+        const int m0 = (t % p.tiles_m) * BM;
+        const int n0 = (t / p.tiles_m) * BN;
+        const long long tile_off = static_cast<long long>(t) * (BM * BN);
+        for (int v = te; v < BM * kVecPerRow; v += 128) {
+          const int row = v / kVecPerRow, cv = v % kVecPerRow;
+          const int grow = m0 + row, gcol = n0 + cv * 8;
+          if (grow >= p.M || gcol >= p.N) continue;
+          float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          for (int r = 0; r < np; ++r) {
+            const uint4 u = ld_volatile_v4(p.ar.partial[r] + tile_off + row * BN + cv * 8);
+            const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c2 = unpack_bf16x2(u.z),
+                         d = unpack_bf16x2(u.w);
+            acc8[0] += a.x; acc8[1] += a.y; acc8[2] += b.x; acc8[3] += b.y;
+            acc8[4] += c2.x; acc8[5] += c2.y; acc8[6] += d.x; acc8[7] += d.y;
+          }
+          if (p.residual != nullptr) {
+            const uint4 u = *reinterpret_cast<const uint4*>(
+                p.residual + static_cast<long long>(grow) * p.ldr + gcol);
+            const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c2 = unpack_bf16x2(u.z),
+                         d = unpack_bf16x2(u.w);
+            acc8[0] += a.x; acc8[1] += a.y; acc8[2] += b.x; acc8[3] += b.y;
+            acc8[4] += c2.x; acc8[5] += c2.y; acc8[6] += d.x; acc8[7] += d.y;
+          }
+          uint4 o;
+          o.x = pack_bf16x2(acc8[0], acc8[1]);
+          o.y = pack_bf16x2(acc8[2], acc8[3]);
+          o.z = pack_bf16x2(acc8[4], acc8[5]);
+          o.w = pack_bf16x2(acc8[6], acc8[7]);
+          const long long ooff = static_cast<long long>(grow) * p.ldc + gcol;
+          for (int r = 0; r < np; ++r) *reinterpret_cast<uint4*>(p.ar.out[r] + ooff) = o;
+        }
+        epi_bar_sync();
+        if (te < np) signal_flag_sys(p.ar.done[te] + t, epoch);
+      }
+      // phase 3: the result is complete on this rank once every tile reports done
+      for (int t = te; t < num_tiles && *abort_flag == 0u; t += 128) {
+        if (!wait_flag_sys(p.ar.done[rank] + t, epoch)) {
+          report_status(p.status, kStatusFlagTimeout, kKernelId, 0x600u);
+          *abort_flag = 1u;
+        }
+      }
+    }
   }
 
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  if constexpr (EPI == kEpiAllReduce) {
+    // the last CTA to finish publishes the new epoch for the next launch
+    if (threadIdx.x == 0) {
+      __threadfence();
+      if (atomicAdd(p.ar.done_ctr, 1u) == gridDim.x - 1) {
+        *p.ar.done_ctr = 0u;
+        __threadfence();
+        *reinterpret_cast<volatile uint32_t*>(p.ar.epoch_ptr) = epoch;
+      }
+    }
+  }
 }
 
 template <int BN, int STAGES, int EPI>
@@ -319,11 +452,13 @@ B200_API int b200_gemm_bf16(const void* A, long long lda, const void* B, long lo
   if (epi == kEpiBias && bias == nullptr) return -5;
   if (epi == kEpiResidual && residual == nullptr) return -5;
 
-  // Wide tiles when there is enough work to fill the machine with them.
+  // Tile width: wide tiles when there is enough work to fill the machine with them,
+  // narrow ones when the problem is small (decode) so that more SMs stream weights.
   const int tiles_m = (M + BM - 1) / BM;
   const bool wide = (epi == kEpiSiluMul) ||
                     ((N % 256) == 0 && static_cast<long long>(tiles_m) * (N / 256) >= sm_count());
-  const int bn = wide ? 256 : 128;
+  const bool narrow = !wide && static_cast<long long>(tiles_m) * ((N + 127) / 128) < sm_count();
+  const int bn = wide ? 256 : (narrow ? 64 : 128);
 
   CUtensorMap tmA, tmB;
   int r = encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, static_cast<uint64_t>(M),
@@ -347,11 +482,14 @@ B200_API int b200_gemm_bf16(const void* A, long long lda, const void* B, long lo
   a.tiles_m = tiles_m;
   a.tiles_n = (N + bn - 1) / bn;
   a.status = status_ptr();
+  a.ar = ArArgs{};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 
 #define B200_GEMM_CASE(E)                                                       \
   case E:                                                                       \
-    return wide ? launch<256, 4, E>(tmA, tmB, a, s) : launch<128, 6, E>(tmA, tmB, a, s);
+    if (wide) return launch<256, 4, E>(tmA, tmB, a, s);                         \
+    if (narrow) return launch<64, 8, E>(tmA, tmB, a, s);                        \
+    return launch<128, 6, E>(tmA, tmB, a, s);
   switch (epi) {
     B200_GEMM_CASE(kEpiNone)
     B200_GEMM_CASE(kEpiBias)
@@ -363,4 +501,66 @@ B200_API int b200_gemm_bf16(const void* A, long long lda, const void* B, long lo
       return -7;
   }
 #undef B200_GEMM_CASE
+}
+
+// Row-parallel GEMM fused with the all-reduce over the tensor-parallel peers:
+//   out_r[M,N] = sum over ranks ( A_rank[M,K] * B_rank[N,K]^T ) (+ residual), on every rank r.
+// Every rank launches this with the same M, N, K.  `partial`, `out`, `ready`, `done` are
+// arrays of `p` peer-visible device addresses (symmetric memory, index = rank);
+// `epoch_ptr` / `done_ctr` are local zero-initialised words.  Tile t is reduced by rank
+// t % p, which pulls the p partial tiles with plain peer loads and pushes the sum to all
+// ranks with peer stores; flags use release/acquire at system scope with bounded waits.
+// Capacity needed: partial >= tiles * 128 * BN bf16, ready >= tiles * p, done >= tiles words,
+// where tiles = ceil(M/128) * ceil(N/BN) and BN is what b200_gemm_ar_tile_n(M, N) returns.
+B200_API int b200_gemm_ar_tile_n(int M, int N) {
+  using namespace b200;
+  const int tiles_m = (M + b200::gemm::BM - 1) / b200::gemm::BM;
+  return (static_cast<long long>(tiles_m) * ((N + 127) / 128) < sm_count()) ? 64 : 128;
+}
+
+B200_API int b200_gemm_bf16_allreduce(const void* A, long long lda, const void* B, long long ldb,
+                                      long long ldc, int M, int N, int K, void* const* partial,
+                                      void* const* out, void* const* ready, void* const* done,
+                                      void* epoch_ptr, void* done_ctr, int rank, int p,
+                                      const void* residual, long long ldr, void* stream) {
+  using namespace b200;
+  using namespace b200::gemm;
+  if (M <= 0 || N <= 0) return 0;
+  if (p < 1 || p > kMaxPeers || rank < 0 || rank >= p) return -2;
+  if (K <= 0 || (K % 8) != 0 || (lda % 8) != 0 || (ldb % 8) != 0 || (N % 8) != 0 ||
+      (ldc % 8) != 0)
+    return -2;
+  const int bn = b200_gemm_ar_tile_n(M, N);
+  CUtensorMap tmA, tmB;
+  int r = encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, static_cast<uint64_t>(M),
+                         static_cast<uint64_t>(K), static_cast<uint64_t>(lda) * 2, BM, BK,
+                         CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r != 0) return r < 0 ? -6 : r;
+  r = encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, static_cast<uint64_t>(N),
+                     static_cast<uint64_t>(K), static_cast<uint64_t>(ldb) * 2, bn, BK,
+                     CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r != 0) return r < 0 ? -6 : r;
+  Args a;
+  a.C = nullptr;
+  a.ldc = ldc;
+  a.bias = nullptr;
+  a.residual = static_cast<const __nv_bfloat16*>(residual);
+  a.ldr = ldr;
+  a.M = M; a.N = N; a.K = K;
+  a.tiles_m = (M + BM - 1) / BM;
+  a.tiles_n = (N + bn - 1) / bn;
+  a.status = status_ptr();
+  for (int i = 0; i < kMaxPeers; ++i) {
+    a.ar.partial[i] = i < p ? static_cast<__nv_bfloat16*>(partial[i]) : nullptr;
+    a.ar.out[i] = i < p ? static_cast<__nv_bfloat16*>(out[i]) : nullptr;
+    a.ar.ready[i] = i < p ? static_cast<uint32_t*>(ready[i]) : nullptr;
+    a.ar.done[i] = i < p ? static_cast<uint32_t*>(done[i]) : nullptr;
+  }
+  a.ar.epoch_ptr = static_cast<uint32_t*>(epoch_ptr);
+  a.ar.done_ctr = static_cast<uint32_t*>(done_ctr);
+  a.ar.rank = rank;
+  a.ar.p = p;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (bn == 64) return launch<64, 8, kEpiAllReduce>(tmA, tmB, a, s);
+  return launch<128, 6, kEpiAllReduce>(tmA, tmB, a, s);
 }

@@ -44,6 +44,8 @@ class LLMEngine:
         self.model = build_model(cfg.model, self.device)
         if cfg.load_format == "dummy":
             self.model.init_random(cfg.seed)
+        elif cfg.load_format == "none":
+            pass        # the caller loads weights through model.load_weights()
         elif cfg.load_format == "safetensors":
             from ..utils.weights import iter_safetensors
             self.model.load_weights(iter_safetensors(cfg.model_path))

@@ -50,7 +50,8 @@ class Communicator:
         if self.fused is not None:
             y = self.fused.all_reduce(x)
             if y is not None:
-                return y
+                x.copy_(y)      # keep the in-place contract; the workspace is reused
+                return x
         dist.all_reduce(x, group=self.group.device_group)
         return x
 
