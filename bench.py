@@ -246,8 +246,13 @@ def main() -> None:
         }
         print(json.dumps(line), flush=True)
     if args.gpus > 1:
+        # Leave without tearing down NCCL communicators that captured CUDA graphs still
+        # reference: that teardown can block forever after the result has been printed.
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":

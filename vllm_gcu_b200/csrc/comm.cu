@@ -30,7 +30,7 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t want) {
   for (uint32_t it = 0; it < (1u << 22); ++it) {
     uint32_t v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-    if (v == want) return true;
+    if (static_cast<int32_t>(v - want) >= 0) return true;  // epochs only grow
     if (it > 64) __nanosleep(100);
   }
   return false;

@@ -48,6 +48,8 @@ struct ArArgs {
   uint32_t* epoch_ptr;                // local: epoch of the previous launch
   uint32_t* done_ctr;                 // local: CTAs of this launch that have finished
   int rank, p;
+  int oneshot;                        // 1: push partials to every peer, reduce locally
+  long long slot_elems;               // one-shot: elements per (parity, source rank) slot
 };
 
 struct Args {
@@ -62,12 +64,13 @@ struct Args {
   ArArgs ar;
 };
 
-// Bounded acquire-wait until *flag == want.  Returns false on timeout.
+// Bounded acquire-wait until *flag reaches `want` (a peer that is one launch ahead may
+// already have written want + 1).  Returns false on timeout.
 __device__ __forceinline__ bool wait_flag_sys(const uint32_t* flag, uint32_t want) {
   for (uint32_t it = 0; it < (1u << 22); ++it) {
     uint32_t v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-    if (v == want) return true;
+    if (static_cast<int32_t>(v - want) >= 0) return true;  // epochs only grow
     if (it > 64) __nanosleep(100);
   }
   return false;
@@ -85,6 +88,63 @@ __device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
   return v;
 }
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// Sums `np` bf16 tiles (slot r at base + r * stride) into out rows; 4 vectors in flight per
+// thread and source so the loads overlap.
+template <int BN_>
+__device__ __forceinline__ void reduce_tile(const __nv_bfloat16* const* srcs, int np,
+                                            long long tile_off, int te, int m0, int n0, int M,
+                                            int N, const __nv_bfloat16* residual, long long ldr,
+                                            __nv_bfloat16* const* outs, int nout, long long ldc) {
+  constexpr int kVecPerRow = BN_ / 8;
+  constexpr int kU = 4;
+  for (int v0 = te; v0 < BM * kVecPerRow; v0 += 128 * kU) {
+    float acc[kU][8];
+#pragma unroll
+    for (int k = 0; k < kU; ++k)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[k][i] = 0.0f;
+    for (int r = 0; r < np; ++r) {
+      uint4 u[kU];
+#pragma unroll
+      for (int k = 0; k < kU; ++k) {
+        const int v = v0 + k * 128;
+        u[k] = (v < BM * kVecPerRow) ? ld_volatile_v4(srcs[r] + tile_off + v * 8)
+                                     : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int k = 0; k < kU; ++k) {
+        const float2 a = unpack_bf16x2(u[k].x), b = unpack_bf16x2(u[k].y),
+                     c2 = unpack_bf16x2(u[k].z), d = unpack_bf16x2(u[k].w);
+        acc[k][0] += a.x; acc[k][1] += a.y; acc[k][2] += b.x; acc[k][3] += b.y;
+        acc[k][4] += c2.x; acc[k][5] += c2.y; acc[k][6] += d.x; acc[k][7] += d.y;
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < kU; ++k) {
+      const int v = v0 + k * 128;
+      if (v >= BM * kVecPerRow) continue;
+      const int row = v / kVecPerRow, cv = v % kVecPerRow;
+      const int grow = m0 + row, gcol = n0 + cv * 8;
+      if (grow >= M || gcol >= N) continue;
+      if (residual != nullptr) {
+        const uint4 u = *reinterpret_cast<const uint4*>(residual + static_cast<long long>(grow) * ldr + gcol);
+        const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c2 = unpack_bf16x2(u.z),
+                     d = unpack_bf16x2(u.w);
+        acc[k][0] += a.x; acc[k][1] += a.y; acc[k][2] += b.x; acc[k][3] += b.y;
+        acc[k][4] += c2.x; acc[k][5] += c2.y; acc[k][6] += d.x; acc[k][7] += d.y;
+      }
+      uint4 o;
+      o.x = pack_bf16x2(acc[k][0], acc[k][1]);
+      o.y = pack_bf16x2(acc[k][2], acc[k][3]);
+      o.z = pack_bf16x2(acc[k][4], acc[k][5]);
+      o.w = pack_bf16x2(acc[k][6], acc[k][7]);
+      const long long ooff = static_cast<long long>(grow) * ldc + gcol;
+      for (int r = 0; r < nout; ++r) *reinterpret_cast<uint4*>(outs[r] + ooff) = o;
+    }
+  }
+}
+
 
 template <int BN, int STAGES>
 struct Smem {
@@ -270,10 +330,13 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (row_ok && col < out_n) store_row_bf16(crow + col, v, min(32, out_n - col));
         }
       } else if constexpr (EPI == kEpiAllReduce) {
-        // phase 1: park the bf16 partial tile in this GPU's symmetric buffer, then tell
-        // the tile's owner that this rank's contribution is complete
-        __nv_bfloat16* ptile = p.ar.partial[p.ar.rank] + static_cast<long long>(tile) * (BM * BN) +
-                               (q * 32 + lane) * BN;
+        // phase 1: publish the bf16 partial tile.  Two-shot: park it in this GPU's own
+        // symmetric buffer and tell the tile's owner.  One-shot: push it into the slot
+        // (epoch parity, this rank) of every peer and tell every peer.
+        const long long tile_elems = static_cast<long long>(tile) * (BM * BN) + (q * 32 + lane) * BN;
+        const long long slot_off =
+            p.ar.oneshot ? (static_cast<long long>(epoch & 1u) * p.ar.p + p.ar.rank) * p.ar.slot_elems
+                         : 0;
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t r[32];
@@ -282,10 +345,20 @@ __global__ void __launch_bounds__(kThreads, 1)
           float v[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-          store_row_bf16(ptile + c * 32, v, 32);
+          if (p.ar.oneshot) {
+            for (int pr = 0; pr < p.ar.p; ++pr)
+              store_row_bf16(p.ar.partial[pr] + slot_off + tile_elems + c * 32, v, 32);
+          } else {
+            store_row_bf16(p.ar.partial[p.ar.rank] + tile_elems + c * 32, v, 32);
+          }
         }
         epi_bar_sync();
-        if (threadIdx.x == 64) {
+        const int te1 = threadIdx.x - 64;
+        if (p.ar.oneshot) {
+          if (te1 < p.ar.p)
+            signal_flag_sys(p.ar.ready[te1] + static_cast<long long>(tile) * p.ar.p + p.ar.rank,
+                            epoch);
+        } else if (te1 == 0) {
           const int owner = tile % p.ar.p;
           signal_flag_sys(p.ar.ready[owner] + static_cast<long long>(tile) * p.ar.p + p.ar.rank,
                           epoch);
@@ -336,57 +409,52 @@ __global__ void __launch_bounds__(kThreads, 1)
     if constexpr (EPI == kEpiAllReduce) {
       const int te = threadIdx.x - 64;  // 0..127 among the epilogue warps
       const int np = p.ar.p, rank = p.ar.rank;
-      constexpr int kVecPerRow = BN / 8;
-      // phase 2: reduce the tiles this rank owns (tile % p == rank) and broadcast them
-      for (int t = rank + static_cast<int>(blockIdx.x) * np; t < num_tiles; t += gridDim.x * np) {
-        bool ok = true;
-        if (te < np)
-          ok = wait_flag_sys(p.ar.ready[rank] + static_cast<long long>(t) * np + te, epoch);
-        if (!ok) {
-          report_status(p.status, kStatusFlagTimeout, kKernelId, 0x500u + te);
-          *abort_flag = 1u;
-        }
-        epi_bar_sync();
-        if (*abort_flag != 0u) break;
-        const int m0 = (t % p.tiles_m) * BM;
-        const int n0 = (t / p.tiles_m) * BN;
-        const long long tile_off = static_cast<long long>(t) * (BM * BN);
-        for (int v = te; v < BM * kVecPerRow; v += 128) {
-          const int row = v / kVecPerRow, cv = v % kVecPerRow;
-          const int grow = m0 + row, gcol = n0 + cv * 8;
-          if (grow >= p.M || gcol >= p.N) continue;
-          float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-          for (int r = 0; r < np; ++r) {
-            const uint4 u = ld_volatile_v4(p.ar.partial[r] + tile_off + row * BN + cv * 8);
-            const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c2 = unpack_bf16x2(u.z),
-                         d = unpack_bf16x2(u.w);
-            acc8[0] += a.x; acc8[1] += a.y; acc8[2] += b.x; acc8[3] += b.y;
-            acc8[4] += c2.x; acc8[5] += c2.y; acc8[6] += d.x; acc8[7] += d.y;
+      if (p.ar.oneshot) {
+        // phase 2 (one-shot): every rank reduces every tile from its own slots
+        const __nv_bfloat16* srcs[kMaxPeers];
+        for (int r = 0; r < kMaxPeers; ++r)
+          srcs[r] = p.ar.partial[rank] +
+                    (static_cast<long long>(epoch & 1u) * np + (r < np ? r : 0)) * p.ar.slot_elems;
+        __nv_bfloat16* outs[1] = {p.ar.out[rank]};
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+          bool ok = true;
+          if (te < np)
+            ok = wait_flag_sys(p.ar.ready[rank] + static_cast<long long>(t) * np + te, epoch);
+          if (!ok) {
+            report_status(p.status, kStatusFlagTimeout, kKernelId, 0x500u + te);
+            *abort_flag = 1u;
           }
-          if (p.residual != nullptr) {
-            const uint4 u = *reinterpret_cast<const uint4*>(
-                p.residual + static_cast<long long>(grow) * p.ldr + gcol);
-            const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c2 = unpack_bf16x2(u.z),
-                         d = unpack_bf16x2(u.w);
-            acc8[0] += a.x; acc8[1] += a.y; acc8[2] += b.x; acc8[3] += b.y;
-            acc8[4] += c2.x; acc8[5] += c2.y; acc8[6] += d.x; acc8[7] += d.y;
-          }
-          uint4 o;
-          o.x = pack_bf16x2(acc8[0], acc8[1]);
-          o.y = pack_bf16x2(acc8[2], acc8[3]);
-          o.z = pack_bf16x2(acc8[4], acc8[5]);
-          o.w = pack_bf16x2(acc8[6], acc8[7]);
-          const long long ooff = static_cast<long long>(grow) * p.ldc + gcol;
-          for (int r = 0; r < np; ++r) *reinterpret_cast<uint4*>(p.ar.out[r] + ooff) = o;
+          epi_bar_sync();
+          if (*abort_flag != 0u) break;
+          reduce_tile<BN>(srcs, np, static_cast<long long>(t) * (BM * BN), te,
+                          (t % p.tiles_m) * BM, (t / p.tiles_m) * BN, p.M, p.N, p.residual, p.ldr,
+                          outs, 1, p.ldc);
         }
-        epi_bar_sync();
-        if (te < np) signal_flag_sys(p.ar.done[te] + t, epoch);
-      }
-      // phase 3: the result is complete on this rank once every tile reports done
-      for (int t = te; t < num_tiles && *abort_flag == 0u; t += 128) {
-        if (!wait_flag_sys(p.ar.done[rank] + t, epoch)) {
-          report_status(p.status, kStatusFlagTimeout, kKernelId, 0x600u);
-          *abort_flag = 1u;
+      } else {
+        // phase 2 (two-shot): reduce the tiles this rank owns (tile % p == rank), broadcast
+        for (int t = rank + static_cast<int>(blockIdx.x) * np; t < num_tiles;
+             t += gridDim.x * np) {
+          bool ok = true;
+          if (te < np)
+            ok = wait_flag_sys(p.ar.ready[rank] + static_cast<long long>(t) * np + te, epoch);
+          if (!ok) {
+            report_status(p.status, kStatusFlagTimeout, kKernelId, 0x500u + te);
+            *abort_flag = 1u;
+          }
+          epi_bar_sync();
+          if (*abort_flag != 0u) break;
+          reduce_tile<BN>(p.ar.partial, np, static_cast<long long>(t) * (BM * BN), te,
+                          (t % p.tiles_m) * BM, (t / p.tiles_m) * BN, p.M, p.N, p.residual, p.ldr,
+                          p.ar.out, np, p.ldc);
+          epi_bar_sync();
+          if (te < np) signal_flag_sys(p.ar.done[te] + t, epoch);
+        }
+        // phase 3: the result is complete on this rank once every tile reports done
+        for (int t = te; t < num_tiles && *abort_flag == 0u; t += 128) {
+          if (!wait_flag_sys(p.ar.done[rank] + t, epoch)) {
+            report_status(p.status, kStatusFlagTimeout, kKernelId, 0x600u);
+            *abort_flag = 1u;
+          }
         }
       }
     }
@@ -510,8 +578,12 @@ B200_API int b200_gemm_bf16(const void* A, long long lda, const void* B, long lo
 // `epoch_ptr` / `done_ctr` are local zero-initialised words.  Tile t is reduced by rank
 // t % p, which pulls the p partial tiles with plain peer loads and pushes the sum to all
 // ranks with peer stores; flags use release/acquire at system scope with bounded waits.
-// Capacity needed: partial >= tiles * 128 * BN bf16, ready >= tiles * p, done >= tiles words,
-// where tiles = ceil(M/128) * ceil(N/BN) and BN is what b200_gemm_ar_tile_n(M, N) returns.
+// With oneshot != 0 every rank instead pushes its partial tiles into slot
+// (epoch parity, rank) of every peer's partial buffer and reduces all tiles locally
+// (one flag hop; best for small M or p == 2); slot_elems is the slot pitch in elements.
+// Capacity needed: partial >= tiles * 128 * BN bf16 (two-shot) or 2 * p * slot_elems
+// (one-shot), ready >= tiles * p, done >= tiles words, where
+// tiles = ceil(M/128) * ceil(N/BN) and BN is what b200_gemm_ar_tile_n(M, N) returns.
 B200_API int b200_gemm_ar_tile_n(int M, int N) {
   using namespace b200;
   const int tiles_m = (M + b200::gemm::BM - 1) / b200::gemm::BM;
@@ -522,7 +594,8 @@ B200_API int b200_gemm_bf16_allreduce(const void* A, long long lda, const void* 
                                       long long ldc, int M, int N, int K, void* const* partial,
                                       void* const* out, void* const* ready, void* const* done,
                                       void* epoch_ptr, void* done_ctr, int rank, int p,
-                                      const void* residual, long long ldr, void* stream) {
+                                      const void* residual, long long ldr, int oneshot,
+                                      long long slot_elems, void* stream) {
   using namespace b200;
   using namespace b200::gemm;
   if (M <= 0 || N <= 0) return 0;
@@ -560,6 +633,8 @@ B200_API int b200_gemm_bf16_allreduce(const void* A, long long lda, const void* 
   a.ar.done_ctr = static_cast<uint32_t*>(done_ctr);
   a.ar.rank = rank;
   a.ar.p = p;
+  a.ar.oneshot = oneshot;
+  a.ar.slot_elems = slot_elems;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (bn == 64) return launch<64, 8, kEpiAllReduce>(tmA, tmB, a, s);
   return launch<128, 6, kEpiAllReduce>(tmA, tmB, a, s);

@@ -42,7 +42,8 @@ def _register_sigs() -> None:
     lib.b200_gemm_ar_tile_n.restype = I
     lib.b200_gemm_ar_tile_n.argtypes = [I, I]
     lib.b200_gemm_bf16_allreduce.restype = I
-    lib.b200_gemm_bf16_allreduce.argtypes = [P, L, P, L, L, I, I, I, P, P, P, P, P, P, I, I, P, L, P]
+    lib.b200_gemm_bf16_allreduce.argtypes = [P, L, P, L, L, I, I, I, P, P, P, P, P, P, I, I, P, L,
+                                             I, L, P]
     lib.b200_allreduce.restype = I
     lib.b200_allreduce.argtypes = [P, P, P, P, P, P, L, I, I, I, P]
     _SIG_DONE = True
@@ -79,6 +80,7 @@ class SymmetricBuffer:
 
 class FusedTP:
     BM = 128
+    ONESHOT_MAX_TOKENS = 1024
 
     def __init__(self, max_tokens: int, max_n: int, device: torch.device, group_name: str = "tp"):
         _register_sigs()
@@ -92,7 +94,11 @@ class FusedTP:
         self.max_n = max_n
         pg = grp.device_group
         rows = -(-max_tokens // self.BM) * self.BM
-        self.part_bytes = rows * max_n * 2
+        # one-shot (push to every peer, reduce locally) for every size when p == 2, for
+        # decode-sized batches otherwise; two-shot (owner reduces, broadcasts) above that
+        self.oneshot_rows = rows if self.p == 2 else min(rows, self.ONESHOT_MAX_TOKENS)
+        self.slot_elems = self.oneshot_rows * max_n
+        self.part_bytes = max(rows * max_n * 2, 2 * self.p * self.slot_elems * 2)
         self.out_bytes = rows * max_n * 2
         max_tiles = (rows // self.BM) * (-(-max_n // 64))
         self.ready_bytes = max_tiles * self.p * 4
@@ -142,7 +148,8 @@ class FusedTP:
              _ptr_array(self.buf.peer_ptrs(self.off_ready)),
              _ptr_array(self.buf.peer_ptrs(self.off_done)),
              words, words + 4, self.rank, self.p, ptr(residual),
-             residual.stride(0) if residual is not None else 0, stream_ptr())
+             residual.stride(0) if residual is not None else 0,
+             int(-(-M // self.BM) * self.BM <= self.oneshot_rows), self.slot_elems, stream_ptr())
         return out_local.view(*shape[:-1], N)
 
     def all_reduce(self, x: torch.Tensor) -> Optional[torch.Tensor]:
