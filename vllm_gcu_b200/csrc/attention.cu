@@ -718,3 +718,86 @@ B200_API int b200_merge_attn_states(void* out, float* out_lse, const void* p_out
     return -8;
   return static_cast<int>(cudaGetLastError());
 }
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant of the decode entry point (declared in no_alloc.h)
+// ---------------------------------------------------------------------------
+#include "no_alloc.h"
+
+#include <cstdio>
+
+namespace {
+
+// Split-KV workspace inside the library image.  In host code these names are only
+// stand-ins for the symbols; the device addresses come from cudaGetSymbolAddress.
+static __device__ __align__(256) float g_noalloc_out[B200_NOALLOC_MAX_OUT_FLOATS];
+static __device__ __align__(256) float g_noalloc_lse[B200_NOALLOC_MAX_LSE_FLOATS];
+
+thread_local char t_noalloc_err[256] = "";
+
+struct NoAllocPtrs {
+  float* out = nullptr;
+  float* lse = nullptr;
+};
+
+// Resolved once per device, with that device current.
+int noalloc_ptrs(NoAllocPtrs* res) {
+  static NoAllocPtrs cache[64];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    snprintf(t_noalloc_err, sizeof(t_noalloc_err), "cudaGetDevice failed (%d)", (int)e);
+    return B200_NOALLOC_SETUP_FAILED;
+  }
+  if (cache[dev].out == nullptr) {
+    void* po = nullptr;
+    void* pl = nullptr;
+    e = cudaGetSymbolAddress(&po, g_noalloc_out);
+    if (e == cudaSuccess) e = cudaGetSymbolAddress(&pl, g_noalloc_lse);
+    if (e != cudaSuccess || po == nullptr || pl == nullptr) {
+      snprintf(t_noalloc_err, sizeof(t_noalloc_err),
+               "cudaGetSymbolAddress for the built-in workspace failed: %s",
+               cudaGetErrorString(e));
+      return B200_NOALLOC_SETUP_FAILED;
+    }
+    cache[dev].lse = static_cast<float*>(pl);
+    cache[dev].out = static_cast<float*>(po);
+  }
+  *res = cache[dev];
+  return 0;
+}
+
+}  // namespace
+
+B200_API const char* b200_noalloc_last_error(void) { return t_noalloc_err; }
+
+B200_API int b200_paged_decode_noalloc(const void* q, long long ldq, void* out, long long ldo,
+                                       const void* k_cache, const void* v_cache,
+                                       long long slot_stride, long long head_stride,
+                                       long long num_slots, const int* block_tables,
+                                       int max_blocks, int block_size, const int* seq_lens,
+                                       int num_splits, int B, int Hq, int Hkv, int HD, float scale,
+                                       int dtype, void* stream) {
+  t_noalloc_err[0] = 0;
+  if (B <= 0) return 0;
+  if (num_splits < 1) num_splits = 1;
+  const long long need_out = static_cast<long long>(B) * Hq * num_splits * HD;
+  const long long need_lse = static_cast<long long>(B) * Hq * num_splits;
+  if (num_splits > 1 &&
+      (need_out > B200_NOALLOC_MAX_OUT_FLOATS || need_lse > B200_NOALLOC_MAX_LSE_FLOATS)) {
+    snprintf(t_noalloc_err, sizeof(t_noalloc_err),
+             "problem needs %lld + %lld workspace floats, the built-in workspace holds %d + %d "
+             "(reduce B * Hq * num_splits * HD or use b200_paged_decode with your own workspace)",
+             need_out, need_lse, B200_NOALLOC_MAX_OUT_FLOATS, B200_NOALLOC_MAX_LSE_FLOATS);
+    return B200_NOALLOC_TOO_LARGE;
+  }
+  NoAllocPtrs ws;
+  const int rc = noalloc_ptrs(&ws);
+  if (rc != 0) return rc;
+  const int r = b200_paged_decode(q, ldq, out, ldo, k_cache, v_cache, slot_stride, head_stride,
+                                  num_slots, block_tables, max_blocks, block_size, seq_lens,
+                                  ws.out, ws.lse, num_splits, B, Hq, Hkv, HD, scale, dtype, stream);
+  if (r != 0)
+    snprintf(t_noalloc_err, sizeof(t_noalloc_err), "b200_paged_decode returned %d", r);
+  return r;
+}
