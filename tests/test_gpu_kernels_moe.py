@@ -1,0 +1,133 @@
+"""GPU numerics of the MoE kernels against the torch reference."""
+import pytest
+import torch
+
+from vllm_gcu_b200.ops import _native, ref
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def C():
+    from vllm_gcu_b200.ops import cuda
+    return cuda
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    yield
+    if torch.cuda.is_available():
+        _native.check_status()
+
+
+@pytest.mark.parametrize("E,k,ng,tg,sigmoid,use_bias", [(128, 8, 1, 1, False, False),
+                                                        (256, 8, 8, 4, True, True),
+                                                        (16, 4, 4, 2, False, False),
+                                                        (8, 2, 1, 1, False, False)])
+def test_moe_topk(C, E, k, ng, tg, sigmoid, use_bias):
+    torch.manual_seed(0)
+    T = 37
+    g = torch.randn(T, E, device="cuda", dtype=torch.float32)
+    bias = (torch.randn(E, device="cuda") * 0.1) if use_bias else None
+    w, ids = C.moe_topk(g, k, True, ng, tg, bias, sigmoid, 2.5 if ng > 1 else 1.0)
+    if ng > 1 or sigmoid:
+        wr, ir = ref.grouped_topk(g, k, True, ng, tg, bias, "sigmoid" if sigmoid else "softmax",
+                                  2.5 if ng > 1 else 1.0)
+    else:
+        wr, ir = ref.topk_softmax(g, k, True)
+    # compare as sets per row (order of equal-rank experts is not part of the contract)
+    so, sr = ids.long().sort(-1), ir.long().sort(-1)
+    assert torch.equal(so.values, sr.values)
+    assert torch.allclose(w.gather(1, so.indices), wr.gather(1, sr.indices), atol=1e-5, rtol=1e-4)
+
+
+def test_moe_align_and_ep_indices(C):
+    torch.manual_seed(1)
+    T, k, E = 50, 4, 16
+    ids = torch.stack([torch.randperm(E)[:k] for _ in range(T)]).to(torch.int32).cuda()
+    sorted_ids, expert_ids, npp, pos_of = C.moe_align(ids, E)
+    n = int(npp.item())
+    assert n % 128 == 0
+    flat = ids.reshape(-1).cpu()
+    s = sorted_ids.cpu()
+    for b in range(n // 128):
+        e = int(expert_ids[b])
+        rows = s[b * 128:(b + 1) * 128]
+        real = rows[rows < T * k]
+        assert (flat[real.long()] == e).all()
+    placed = s[:n][s[:n] < T * k]
+    assert sorted(placed.tolist()) == list(range(T * k))
+    assert (s[pos_of.cpu().long()] == torch.arange(T * k)).all()
+    # expert map: only experts 4..7 are local
+    emap = torch.full((E,), -1, dtype=torch.int32)
+    emap[4:8] = torch.arange(4, dtype=torch.int32)
+    s2, e2, n2, p2 = C.moe_align(ids, 4, expert_map=emap.cuda())
+    keep = ((flat >= 4) & (flat < 8)).nonzero().flatten()
+    got = s2.cpu()[: int(n2)]
+    assert sorted(got[got < T * k].tolist()) == keep.tolist()
+    assert ((p2.cpu() >= 0) == ((flat >= 4) & (flat < 8))).all()
+    cnt, idx, tot = C.get_ep_indices(ids, 4, 4)
+    cr, ir, tr = ref.get_ep_indices(ids.cpu(), 4, 4)
+    assert torch.equal(cnt.cpu(), cr) and int(tot) == tr
+    off = 0
+    for r in range(4):
+        c = int(cr[r])
+        assert sorted(idx.cpu()[off:off + c].tolist()) == sorted(ir[off:off + c].tolist())
+        off += c
+
+
+@pytest.mark.parametrize("T,E,k,H,I", [(33, 8, 2, 256, 128), (300, 16, 4, 512, 256),
+                                       (1, 128, 8, 2048, 768)])
+def test_fused_experts(C, T, E, k, H, I):
+    torch.manual_seed(2)
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    w13 = (torch.randn(E, 2 * I, H, device="cuda") * 0.05).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, device="cuda") * 0.05).to(torch.bfloat16)
+    g = torch.randn(T, E, device="cuda")
+    tw, ti = C.moe_topk(g, k, True)
+    want = ref.fused_experts(x, w13, w2, tw, ti)
+    w13i = torch.stack([ref.interleave_gate_up(w13[e, :I], w13[e, I:]) for e in range(E)])
+    add = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    got = C.fused_experts(x, w13i.contiguous(), w2, tw, ti, add=add)
+    err = (got.float() - (want.float() + add.float())).abs()
+    tol = 3e-2 + 3e-2 * want.float().abs()
+    assert bool((err <= tol).all()), err.max().item()
+    # expert-parallel slice: only half of the experts are local
+    emap = torch.full((E,), -1, dtype=torch.int32, device="cuda")
+    emap[E // 2:] = torch.arange(E - E // 2, dtype=torch.int32, device="cuda")
+    got2 = C.fused_experts(x, w13i[E // 2:].contiguous(), w2[E // 2:].contiguous(), tw, ti,
+                           expert_map=emap)
+    want2 = ref.fused_experts(x, w13[E // 2:], w2[E // 2:], tw, ti, expert_map=emap)
+    err2 = (got2.float() - want2.float()).abs()
+    assert bool((err2 <= 3e-2 + 3e-2 * want2.float().abs()).all()), err2.max().item()
+
+
+def test_qwen3_moe_engine_gpu_vs_cpu():
+    from vllm_gcu_b200.engine.llm import LLM
+    from vllm_gcu_b200.engine.request import SamplingParams
+    kw = dict(num_hidden_layers=2, hidden_size=256, num_attention_heads=4, num_key_value_heads=2,
+              head_dim=64, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128,
+              vocab_size=1024, dtype="bfloat16", max_num_seqs=8, max_num_batched_tokens=128,
+              max_model_len=256, num_gpu_blocks=64)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (33, 70, 9)]
+    one = SamplingParams(max_tokens=1, temperature=0.0, ignore_eos=True)
+    gpu = LLM("tiny-qwen3-moe", device="cuda", enforce_eager=True, **kw)
+    cpu = LLM("tiny-qwen3-moe", device="cpu", load_format="none", **kw)
+    sd = {k: v.detach().cpu() for k, v in gpu.engine.model.state_dict().items()}
+    for name, mod in gpu.engine.model.named_modules():
+        if getattr(mod, "_interleaved", False) and hasattr(mod, "w13"):
+            w = sd[name + ".w13"]
+            E, I2, H = w.shape
+            I = I2 // 2
+            w4 = w.view(E, I // 128, 2, 128, H)
+            sd[name + ".w13"] = torch.cat([w4[:, :, 0].reshape(E, I, H),
+                                           w4[:, :, 1].reshape(E, I, H)], 1)
+    cpu.engine.model.load_state_dict(sd, strict=False)
+    gpu.engine.runner.keep_logits = True
+    cpu.engine.runner.keep_logits = True
+    gpu.generate(prompts, one)
+    cpu.generate(prompts, one)
+    lg, lc = gpu.engine.runner.last_logits, cpu.engine.runner.last_logits
+    err = (lg - lc).abs().max().item()
+    assert err < 0.08 * lc.std().item() + 0.03, (err, lc.std().item())

@@ -61,8 +61,29 @@ struct Args {
   int M, N, K;
   int tiles_m, tiles_n;
   unsigned int* status;
+  // grouped (mixture-of-experts) mode: A rows are sorted by expert in tiles of BM rows
+  const int* expert_ids;      // [tiles_m] expert of each M tile (-1: skip), null = dense GEMM
+  const int* num_valid_rows;  // device scalar: rows of A that are in use (multiple of BM)
+  const float* row_scale;     // optional [M] factor applied to each output row
   ArArgs ar;
 };
+
+// Resolves tile -> (m0, n0, first B row).  Returns false for tiles that carry no work.
+template <int BN_>
+__device__ __forceinline__ bool tile_coords(const Args& p, int tile, int& m0, int& n0,
+                                            int& b_row) {
+  const int tm = tile % p.tiles_m;
+  m0 = tm * BM;
+  n0 = (tile / p.tiles_m) * BN_;
+  b_row = n0;
+  if (p.expert_ids != nullptr) {
+    if (m0 >= *p.num_valid_rows) return false;
+    const int e = p.expert_ids[tm];
+    if (e < 0) return false;
+    b_row = e * p.N + n0;
+  }
+  return true;
+}
 
 // Bounded acquire-wait until *flag reaches `want` (a peer that is one launch ahead may
 // already have written want + 1).  Returns false on timeout.
@@ -230,8 +251,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-        const int m0 = (tile % p.tiles_m) * BM;
-        const int n0 = (tile / p.tiles_m) * BN;
+        int m0, n0, b_row;
+        if (!tile_coords<BN>(p, tile, m0, n0, b_row)) continue;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, p.status, kKernelId, 0x100u + stage,
                          abort_flag)) {
@@ -242,7 +263,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           uint8_t* sb = sa + L::kABytes;
           mbar_expect_tx(&full_bar[stage], L::kStageBytes);
           tma_load_2d(sa, &tmA, &full_bar[stage], kb * BK, m0);
-          tma_load_2d(sb, &tmB, &full_bar[stage], kb * BK, n0);
+          tma_load_2d(sb, &tmB, &full_bar[stage], kb * BK, b_row);
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
@@ -259,6 +280,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        {
+          int m0s, n0s, brs;
+          if (!tile_coords<BN>(p, tile, m0s, n0s, brs)) continue;
+        }
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, p.status, kKernelId, 0x200u + acc,
                        abort_flag))
           break;
@@ -299,8 +324,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-      const int m0 = (tile % p.tiles_m) * BM;
-      const int n0 = (tile / p.tiles_m) * BN;
+      int m0, n0, b_row_unused;
+      if (!tile_coords<BN>(p, tile, m0, n0, b_row_unused)) continue;
       if (!mbar_wait(&tfull_bar[acc], acc_phase, p.status, kKernelId, 0x400u + acc, abort_flag))
         break;
       tc_fence_after();
@@ -375,6 +400,11 @@ __global__ void __launch_bounds__(kThreads, 1)
           float v[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          if (p.row_scale != nullptr) {
+            const float rs = p.row_scale[row];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] *= rs;
+          }
           if constexpr (EPI == kEpiBias) {
             for (int i = 0; i < ncols; ++i) v[i] += __bfloat162float(p.bias[col + i]);
           }
@@ -550,6 +580,9 @@ B200_API int b200_gemm_bf16(const void* A, long long lda, const void* B, long lo
   a.tiles_m = tiles_m;
   a.tiles_n = (N + bn - 1) / bn;
   a.status = status_ptr();
+  a.expert_ids = nullptr;
+  a.num_valid_rows = nullptr;
+  a.row_scale = nullptr;
   a.ar = ArArgs{};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 
@@ -623,6 +656,9 @@ B200_API int b200_gemm_bf16_allreduce(const void* A, long long lda, const void* 
   a.tiles_m = (M + BM - 1) / BM;
   a.tiles_n = (N + bn - 1) / bn;
   a.status = status_ptr();
+  a.expert_ids = nullptr;
+  a.num_valid_rows = nullptr;
+  a.row_scale = nullptr;
   for (int i = 0; i < kMaxPeers; ++i) {
     a.ar.partial[i] = i < p ? static_cast<__nv_bfloat16*>(partial[i]) : nullptr;
     a.ar.out[i] = i < p ? static_cast<__nv_bfloat16*>(out[i]) : nullptr;
@@ -638,4 +674,61 @@ B200_API int b200_gemm_bf16_allreduce(const void* A, long long lda, const void* 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (bn == 64) return launch<64, 8, kEpiAllReduce>(tmA, tmB, a, s);
   return launch<128, 6, kEpiAllReduce>(tmA, tmB, a, s);
+}
+
+// Grouped GEMM for mixture-of-experts layers.  A [M_cap, K] holds token rows sorted by
+// expert, every expert segment padded to a multiple of 128 rows (b200_moe_align);
+// B [E * N, K] stacks the expert weights; tile i of A uses expert expert_ids[i] (-1 and
+// tiles at or past *num_valid_rows are skipped, so M_cap may be a static upper bound).
+// epi 0: C[M_cap, N] = A * B_e^T (optionally scaled per row by row_scale);
+// epi 2: SiLU(gate) * up with the gate / up rows of every expert interleaved in blocks of
+// 128 (C is [M_cap, N / 2]).  N must be a multiple of the tile width (256 for epi 2,
+// else 128 or 64).
+B200_API int b200_gemm_bf16_grouped(const void* A, long long lda, const void* B, long long ldb,
+                                    void* C, long long ldc, int M_cap, int N, int K, int E,
+                                    const int* expert_ids, const int* num_valid_rows,
+                                    const float* row_scale, int epi, void* stream) {
+  using namespace b200;
+  using namespace b200::gemm;
+  if (M_cap <= 0 || N <= 0 || E <= 0) return 0;
+  if ((M_cap % BM) != 0 || K <= 0 || (K % 8) != 0 || (lda % 8) != 0 || (ldb % 8) != 0 ||
+      (ldc % 8) != 0 || expert_ids == nullptr || num_valid_rows == nullptr)
+    return -2;
+  int bn;
+  if (epi == kEpiSiluMul) {
+    if ((N % 256) != 0) return -4;
+    bn = 256;
+  } else if (epi == kEpiNone) {
+    bn = (N % 128) == 0 ? 128 : 64;
+    if ((N % bn) != 0) return -4;
+  } else {
+    return -7;
+  }
+  CUtensorMap tmA, tmB;
+  int r = encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A,
+                         static_cast<uint64_t>(M_cap), static_cast<uint64_t>(K),
+                         static_cast<uint64_t>(lda) * 2, BM, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r != 0) return r < 0 ? -6 : r;
+  r = encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B,
+                     static_cast<uint64_t>(E) * N, static_cast<uint64_t>(K),
+                     static_cast<uint64_t>(ldb) * 2, bn, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r != 0) return r < 0 ? -6 : r;
+  Args a;
+  a.C = C;
+  a.ldc = ldc;
+  a.bias = nullptr;
+  a.residual = nullptr;
+  a.ldr = 0;
+  a.M = M_cap; a.N = N; a.K = K;
+  a.tiles_m = M_cap / BM;
+  a.tiles_n = N / bn;
+  a.status = status_ptr();
+  a.expert_ids = expert_ids;
+  a.num_valid_rows = num_valid_rows;
+  a.row_scale = row_scale;
+  a.ar = ArArgs{};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (epi == kEpiSiluMul) return launch<256, 4, kEpiSiluMul>(tmA, tmB, a, s);
+  if (bn == 128) return launch<128, 6, kEpiNone>(tmA, tmB, a, s);
+  return launch<64, 8, kEpiNone>(tmA, tmB, a, s);
 }

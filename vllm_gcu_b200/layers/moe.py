@@ -1,0 +1,251 @@
+"""Mixture-of-experts layers.
+
+``FusedMoE`` holds the stacked expert weights of this rank (``w13 [E_local, 2I, H]``,
+``w2 [E_local, H, I]``) and runs routed tokens through them: on the GPU with the native
+pipeline (align -> permute -> grouped tcgen05 GEMM with SiLU-mul epilogue -> grouped GEMM
+scaled by the routing weight -> un-permute + sum), elsewhere with the torch reference.
+
+Parallel layouts (vllm_gcu/kernels/prepare_finalize.py:19-610, patch_0_9_2/moe_layer.py):
+
+* no EP: the intermediate dimension of every expert is sharded over TP; partial sums are
+  all-reduced by the caller (``MoEPrepareAndFinalizeNoEP``);
+* EP with replicated tokens (attention is tensor parallel, so every rank holds the same
+  hidden states): each rank owns ``E / ep`` contiguous experts, computes their contribution
+  for all tokens and the partial sums are all-reduced – no dispatch is needed;
+* EP with data-parallel attention (every rank holds different tokens): tokens travel to the
+  ranks that own their experts and back, see ``layers/moe_ep.py``.
+
+``SparseMoeBlock`` = router gate + ``FusedMoE`` (+ shared experts whose output seeds the
+result, vllm_gcu/kernels/modular_kernel.py:288-295).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+from ..config import ModelConfig
+from ..ops import cuda as C
+from ..ops import ref
+from ..parallel.communicator import get_comm
+from ..parallel.state import ep_rank, ep_size, get_state, tp_rank, tp_size
+from .linear import ReplicatedLinear
+
+
+def select_experts(router_logits: torch.Tensor, cfg: ModelConfig,
+                   bias: Optional[torch.Tensor] = None, eplb=None
+                   ) -> tuple[torch.Tensor, torch.Tensor]:
+    """Routing weights fp32 ``[T, k]`` and expert ids int32 ``[T, k]``."""
+    k = cfg.num_experts_per_tok
+    grouped = cfg.n_group > 1 or cfg.scoring_func == "sigmoid" or bias is not None
+    scale = cfg.routed_scaling_factor if grouped else 1.0
+    if ops.use_native(router_logits):
+        return C.moe_topk(router_logits, k, cfg.norm_topk_prob, cfg.n_group, cfg.topk_group, bias,
+                          cfg.scoring_func == "sigmoid", scale,
+                          log2phy=eplb.log2phy if eplb is not None else None,
+                          replica_count=eplb.replica_count if eplb is not None else None,
+                          load=eplb.load if eplb is not None else None)
+    if grouped:
+        w, ids = ref.grouped_topk(router_logits, k, cfg.norm_topk_prob, max(cfg.n_group, 1),
+                                  max(cfg.topk_group, 1), bias, cfg.scoring_func, scale)
+    else:
+        w, ids = ref.topk_softmax(router_logits, k, cfg.norm_topk_prob)
+    if eplb is not None:
+        ids = ref.eplb_map_to_physical(ids, eplb.log2phy, eplb.replica_count, eplb.load)
+    return w, ids
+
+
+class FusedMoE(nn.Module):
+    def __init__(self, num_experts: int, hidden: int, inter: int, dtype, device,
+                 use_ep: bool, prefix: str = "", num_redundant: int = 0):
+        super().__init__()
+        self.global_experts = num_experts + num_redundant
+        self.hidden, self.inter_full = hidden, inter
+        self.use_ep = use_ep and ep_size() > 1
+        if self.use_ep:
+            ep, r = ep_size(), ep_rank()
+            assert self.global_experts % ep == 0
+            self.local_experts = self.global_experts // ep
+            self.expert_start = r * self.local_experts
+            self.inter = inter
+            emap = torch.full((self.global_experts,), -1, dtype=torch.int32)
+            emap[self.expert_start:self.expert_start + self.local_experts] = torch.arange(
+                self.local_experts, dtype=torch.int32)
+            self.register_buffer("expert_map", emap.to(device), persistent=False)
+        else:
+            tp = tp_size()
+            assert inter % tp == 0
+            self.local_experts, self.expert_start = self.global_experts, 0
+            self.inter = inter // tp
+            self.expert_map = None
+        E, I, H = self.local_experts, self.inter, hidden
+        self.w13 = nn.Parameter(torch.empty(E, 2 * I, H, dtype=dtype, device=device),
+                                requires_grad=False)
+        self.w2 = nn.Parameter(torch.empty(E, H, I, dtype=dtype, device=device),
+                               requires_grad=False)
+        self.prefix = prefix
+        self._interleaved = False
+
+    # -- weights -------------------------------------------------------------------
+    def load_expert_weight(self, expert_id: int, which: str, full: torch.Tensor) -> bool:
+        """``which`` in {gate, up, down} (HF ``gate_proj`` / ``up_proj`` / ``down_proj`` or
+        Mixtral ``w1`` / ``w3`` / ``w2``).  Returns False when the expert lives elsewhere."""
+        le = expert_id - self.expert_start
+        if le < 0 or le >= self.local_experts:
+            return False
+        I = self.inter
+        if self.use_ep or tp_size() == 1:
+            lo = 0
+        else:
+            lo = tp_rank() * I
+        if which == "gate":
+            self.w13.data[le, :I].copy_(full[lo:lo + I])
+        elif which == "up":
+            self.w13.data[le, I:].copy_(full[lo:lo + I])
+        elif which == "down":
+            self.w2.data[le].copy_(full[:, lo:lo + I])
+        else:
+            raise ValueError(which)
+        return True
+
+    def finalize(self) -> None:
+        """GPU layout: gate / up rows of every expert interleaved in blocks of 128 so the
+        grouped GEMM applies SiLU(gate) * up in its epilogue."""
+        if self._interleaved or not self.w13.is_cuda or self.w13.dtype != torch.bfloat16:
+            return
+        I = self.inter
+        if I % 128 != 0 or self.hidden % 64 != 0:
+            return
+        w = self.w13.data
+        E = w.shape[0]
+        g = w[:, :I].reshape(E, I // 128, 128, -1)
+        u = w[:, I:].reshape(E, I // 128, 128, -1)
+        self.w13.data = torch.stack([g, u], dim=2).reshape(E, 2 * I, -1).contiguous()
+        self._interleaved = True
+
+    # -- compute -------------------------------------------------------------------
+    def forward(self, x: torch.Tensor, topk_w: torch.Tensor, topk_ids: torch.Tensor,
+                add: Optional[torch.Tensor] = None, alpha: float = 1.0) -> torch.Tensor:
+        """Contribution of this rank's experts (partial sum over TP / EP ranks) plus ``add``."""
+        if x.shape[0] == 0:
+            return x if add is None else add
+        if self._interleaved and ops.use_native(x):
+            return C.fused_experts(x, self.w13, self.w2, topk_w, topk_ids, self.expert_map,
+                                   add=add, alpha=alpha)
+        w13 = self.w13
+        if self._interleaved:    # undo the GPU layout for the reference path
+            E, I = w13.shape[0], self.inter
+            w4 = w13.view(E, I // 128, 2, 128, -1)
+            w13 = torch.cat([w4[:, :, 0].reshape(E, I, -1), w4[:, :, 1].reshape(E, I, -1)], dim=1)
+        y = ref.fused_experts(x, w13, self.w2, topk_w, topk_ids, self.expert_map)
+        if alpha != 1.0:
+            y = (y.float() * alpha).to(x.dtype)
+        return y if add is None else y + add
+
+
+class EplbState:
+    """Logical -> physical expert mapping with redundant replicas and a load histogram
+    (``enable_eplb`` / ``num_redundant_experts`` of the reference's ``additional_config``,
+    vllm_gcu/gcu.py:302-308; static placement from ``expert_map_path``,
+    vllm_gcu/models/deepseek_v3/deepseek_v3.py:880-913)."""
+
+    def __init__(self, num_logical: int, num_redundant: int, device,
+                 phy2log: Optional[torch.Tensor] = None):
+        num_phys = num_logical + num_redundant
+        if phy2log is None:
+            phy2log = torch.cat([torch.arange(num_logical),
+                                 torch.arange(num_redundant) % max(num_logical, 1)])
+        self.phy2log = phy2log.to(torch.int32)
+        reps: list[list[int]] = [[] for _ in range(num_logical)]
+        for p, l in enumerate(self.phy2log.tolist()):
+            reps[l].append(p)
+        R = max(len(r) for r in reps)
+        l2p = torch.zeros(num_logical, R, dtype=torch.int32)
+        cnt = torch.zeros(num_logical, dtype=torch.int32)
+        for l, r in enumerate(reps):
+            cnt[l] = len(r)
+            for j in range(R):
+                l2p[l, j] = r[j % len(r)]
+        self.log2phy = l2p.to(device)
+        self.replica_count = cnt.to(device)
+        self.load = torch.zeros(num_phys, dtype=torch.int32, device=device)
+        self.num_physical = num_phys
+
+    def rebalance(self) -> torch.Tensor:
+        """Greedy re-placement of the redundant slots onto the most loaded logical experts.
+        Returns the new ``phy2log`` (weights must be re-homed by the caller)."""
+        num_logical = self.log2phy.shape[0]
+        load_l = torch.zeros(num_logical, dtype=torch.float64)
+        load_l.index_add_(0, self.phy2log.long(), self.load.double().cpu())
+        num_red = self.num_physical - num_logical
+        cnt = torch.ones(num_logical, dtype=torch.float64)
+        extra = []
+        for _ in range(num_red):
+            j = int(torch.argmax(load_l / cnt))
+            extra.append(j)
+            cnt[j] += 1
+        return torch.cat([torch.arange(num_logical), torch.tensor(extra, dtype=torch.long)]).to(
+            torch.int32)
+
+
+class SparseMoeBlock(nn.Module):
+    def __init__(self, cfg: ModelConfig, device, prefix: str):
+        super().__init__()
+        self.cfg = cfg
+        st = get_state()
+        self.use_ep = st.ep.world_size > 1
+        self.gate = ReplicatedLinear(cfg.hidden_size, cfg.num_experts, bias=False,
+                                     dtype=cfg.dtype, device=device, prefix=prefix + ".gate")
+        if cfg.topk_method == "noaux_tc":
+            self.e_score_correction_bias = nn.Parameter(
+                torch.zeros(cfg.num_experts, dtype=torch.float32, device=device),
+                requires_grad=False)
+        else:
+            self.e_score_correction_bias = None
+        num_red = int(cfg.extra.get("num_redundant_experts", 0))
+        self.experts = FusedMoE(cfg.num_experts, cfg.hidden_size, cfg.moe_intermediate_size,
+                                cfg.dtype, device, self.use_ep, prefix + ".experts", num_red)
+        self.eplb = EplbState(cfg.num_experts, num_red, device) if num_red > 0 else None
+        if cfg.num_shared_experts > 0:
+            from ..models.decoder import DenseMLP
+            self.shared_experts = DenseMLP(cfg, cfg.hidden_size,
+                                           cfg.moe_intermediate_size * cfg.num_shared_experts,
+                                           device, prefix + ".shared_experts",
+                                           reduce_results=False)
+        else:
+            self.shared_experts = None
+        self.dp_attention = bool(cfg.extra.get("dp_attention", False))
+        self.dispatcher = None
+        if self.use_ep and self.dp_attention:
+            from .moe_ep import AllToAllDispatcher
+            self.dispatcher = AllToAllDispatcher(self.experts, cfg)
+
+    def load_weight(self, name: str, full: torch.Tensor, shard_id=None) -> None:
+        if name == "e_score_correction_bias":
+            self.e_score_correction_bias.data.copy_(full)
+        else:
+            raise KeyError(name)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        shape = x.shape
+        x = x.reshape(-1, shape[-1])
+        logits = self.gate(x)
+        topk_w, topk_ids = select_experts(logits, self.cfg, self.e_score_correction_bias,
+                                          self.eplb)
+        shared = self.shared_experts(x) if self.shared_experts is not None else None
+        if self.dispatcher is not None:
+            # tokens differ per rank: all-to-all dispatch / combine; the shared experts are
+            # replicated so their (TP-partial) output only needs the TP reduction below
+            out = self.dispatcher(x, topk_w, topk_ids, shared)
+            tp_partial = shared is not None and tp_size() > 1
+            return (get_comm("tp").all_reduce(out) if tp_partial else out).view(shape)
+        # For plain top-k routing the scaling factor is applied on the combined output;
+        # the grouped router already folded it into the weights.
+        out = self.experts(x, topk_w, topk_ids, add=shared)
+        if self.use_ep:
+            out = get_comm("ep").all_reduce(out)
+        elif tp_size() > 1:
+            out = get_comm("tp").all_reduce(out)
+        return out.view(shape)

@@ -231,10 +231,18 @@ class DecoderLM(nn.Module):
             return owner, pname, None
         return owner, pname, None
 
+    def load_special(self, name: str, tensor: torch.Tensor, owners: dict) -> bool:
+        """Hook for tensors that do not map 1:1 onto a ``load_weight`` owner (stacked
+        experts, renamed modules).  Returns True when the tensor was consumed."""
+        return False
+
     def load_weights(self, weights: Iterable[tuple[str, torch.Tensor]]) -> set[str]:
         owners = self.named_loadables()
         loaded: set[str] = set()
         for name, tensor in weights:
+            if self.load_special(name, tensor, owners):
+                loaded.add(name)
+                continue
             m = self.map_weight_name(name)
             if m is None:
                 continue

@@ -1,0 +1,68 @@
+"""Mixture-of-experts decoder families on :class:`DecoderLM`.
+
+``Qwen3MoeForCausalLM``: QK-RMSNorm attention, softmax top-k router, routed experts only
+(vllm_gcu/models/qwen3_moe/qwen3_moe.py:132-238).  ``MixtralForCausalLM``: Mixtral naming
+(``block_sparse_moe.gate``, experts ``w1`` / ``w3`` / ``w2``); the reference's
+``QuantMixtralForCausalLM`` loads the same layout with per-expert quantised linears
+(vllm_gcu/models/... deepseek_moe_quant.py:487 ``load_kv_cache_scales``).
+"""
+from __future__ import annotations
+
+import dataclasses
+import re
+
+import torch
+
+from ..config import ModelConfig
+from .decoder import DecoderLM
+
+_EXPERT_RE = re.compile(r"^(model\.layers\.\d+\.)(mlp|block_sparse_moe)\.experts\.(\d+)\."
+                        r"(gate_proj|up_proj|down_proj|w1|w2|w3)\.weight$")
+_WHICH = {"gate_proj": "gate", "up_proj": "up", "down_proj": "down",
+          "w1": "gate", "w3": "up", "w2": "down"}
+
+
+class MoeDecoderLM(DecoderLM):
+    def load_special(self, name, tensor, owners) -> bool:
+        m = _EXPERT_RE.match(name)
+        if m is not None:
+            layer = int(m.group(1).split(".")[2])
+            if not (self.start_layer <= layer < self.end_layer):
+                return True
+            moe = self.layers[str(layer)].mlp.experts
+            moe.load_expert_weight(int(m.group(3)), _WHICH[m.group(4)], tensor)
+            return True
+        if ".block_sparse_moe.gate." in name:
+            return self._load_renamed(name.replace(".block_sparse_moe.gate.", ".mlp.gate."),
+                                      tensor, owners)
+        if name.endswith(".mlp.gate.e_score_correction_bias"):
+            owner = name[: -len(".gate.e_score_correction_bias")]
+            mod = owners.get(owner)
+            if mod is not None:
+                mod.load_weight("e_score_correction_bias", tensor)
+            return True
+        return False
+
+    def _load_renamed(self, name, tensor, owners) -> bool:
+        m = self.map_weight_name(name)
+        if m is None:
+            return True
+        owner, pname, sid = m
+        mod = owners.get(owner)
+        if mod is not None:
+            mod.load_weight(pname, tensor, sid)
+        return True
+
+
+class Qwen3MoeForCausalLM(MoeDecoderLM):
+    def __init__(self, cfg: ModelConfig, device="cpu"):
+        if not cfg.qk_norm:
+            cfg = dataclasses.replace(cfg, qk_norm=True)
+        super().__init__(cfg, device)
+
+
+class MixtralForCausalLM(MoeDecoderLM):
+    def __init__(self, cfg: ModelConfig, device="cpu"):
+        if cfg.moe_intermediate_size == 0:
+            cfg = dataclasses.replace(cfg, moe_intermediate_size=cfg.intermediate_size)
+        super().__init__(cfg, device)

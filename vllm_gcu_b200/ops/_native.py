@@ -100,6 +100,13 @@ class _Sigs:
     b200_top_k_top_p = [P, L, I, I, I, P, P, P]
     b200_advance_step = [I, I, I, P, P, P, P, P, P, I, I, P]
     b200_feed_tokens = [P, P, P, P, I, P]
+    b200_moe_topk = [P, L, P, P, P, I, I, I, I, I, I, I, F, P, I, P, P, I, P]
+    b200_moe_align = [P, P, P, P, P, P, P, I, I, I, I, P]
+    b200_moe_permute = [P, L, P, L, P, P, I, I, I, I, I, P]
+    b200_moe_row_weights = [P, P, P, P, I, I, P]
+    b200_moe_unpermute_sum = [P, L, P, P, L, P, L, P, I, I, I, F, I, P]
+    b200_get_ep_indices = [P, I, I, I, I, P, P, P, P]
+    b200_gemm_bf16_grouped = [P, L, P, L, P, L, I, I, I, I, P, P, P, I, P]
 
 
 def ptr(t: Optional[torch.Tensor]) -> Optional[int]:

@@ -355,3 +355,100 @@ def advance_step(num_seqs: int, num_queries: int, block_size: int, input_tokens,
 def feed_tokens(input_ids, prev_sampled, dst_idx, src_idx, n: int) -> None:
     call("b200_feed_tokens", ptr(input_ids), ptr(prev_sampled), ptr(dst_idx), ptr(src_idx),
          n, stream_ptr())
+
+
+# ---------------------------------------------------------------------------
+# mixture of experts
+# ---------------------------------------------------------------------------
+def moe_topk(gating: torch.Tensor, k: int, renormalize: bool, n_group: int = 1,
+             topk_group: int = 1, bias: Optional[torch.Tensor] = None, sigmoid: bool = False,
+             scale: float = 1.0, log2phy: Optional[torch.Tensor] = None,
+             replica_count: Optional[torch.Tensor] = None, load: Optional[torch.Tensor] = None
+             ) -> tuple[torch.Tensor, torch.Tensor]:
+    T, E = gating.shape
+    w = torch.empty((T, k), device=gating.device, dtype=torch.float32)
+    ids = torch.empty((T, k), device=gating.device, dtype=torch.int32)
+    call("b200_moe_topk", ptr(gating), gating.stride(0), ptr(bias), ptr(w), ptr(ids), T, E, k,
+         n_group, topk_group, int(sigmoid), int(renormalize), float(scale), ptr(log2phy),
+         log2phy.shape[1] if log2phy is not None else 1, ptr(replica_count), ptr(load),
+         DTYPE_CODE[gating.dtype], stream_ptr())
+    return w, ids
+
+
+def moe_align_cap(num_pairs: int, num_local_experts: int) -> int:
+    return -(-(num_pairs + num_local_experts * 127) // 128) * 128
+
+
+def moe_align(topk_ids: torch.Tensor, num_local_experts: int, cap: Optional[int] = None,
+              expert_map: Optional[torch.Tensor] = None,
+              valid_tokens: Optional[torch.Tensor] = None):
+    """Returns (sorted_ids [cap], expert_ids [cap/128], num_post_pad [1], pos_of [T*k])."""
+    T, k = topk_ids.shape
+    numel = T * k
+    cap = cap or moe_align_cap(numel, num_local_experts)
+    dev = topk_ids.device
+    sorted_ids = torch.empty(cap, device=dev, dtype=torch.int32)
+    expert_ids = torch.empty(cap // 128, device=dev, dtype=torch.int32)
+    npp = torch.empty(1, device=dev, dtype=torch.int32)
+    pos_of = torch.empty(max(numel, 1), device=dev, dtype=torch.int32)
+    call("b200_moe_align", ptr(topk_ids), ptr(expert_map), ptr(valid_tokens), ptr(sorted_ids),
+         ptr(expert_ids), ptr(npp), ptr(pos_of), numel, k, num_local_experts, cap, stream_ptr())
+    return sorted_ids, expert_ids, npp, pos_of
+
+
+def gemm_bf16_grouped(a: torch.Tensor, w: torch.Tensor, expert_ids: torch.Tensor,
+                      num_valid_rows: torch.Tensor, silu_mul: bool = False,
+                      row_scale: Optional[torch.Tensor] = None,
+                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """a ``[M_cap, K]`` expert-sorted rows, w ``[E, N, K]``."""
+    M_cap, K = a.shape
+    E, Nn, _ = w.shape
+    assert w.is_contiguous() and a.stride(1) == 1
+    out_cols = Nn // 2 if silu_mul else Nn
+    if out is None:
+        out = torch.empty((M_cap, out_cols), device=a.device, dtype=torch.bfloat16)
+    call("b200_gemm_bf16_grouped", ptr(a), a.stride(0), ptr(w), K, ptr(out), out.stride(0), M_cap,
+         Nn, K, E, ptr(expert_ids), ptr(num_valid_rows), ptr(row_scale),
+         EPI_SILU_MUL if silu_mul else EPI_NONE, stream_ptr())
+    return out
+
+
+def fused_experts(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_w: torch.Tensor,
+                  topk_ids: torch.Tensor, expert_map: Optional[torch.Tensor] = None,
+                  add: Optional[torch.Tensor] = None, alpha: float = 1.0,
+                  valid_tokens: Optional[torch.Tensor] = None,
+                  w13_interleaved: bool = True) -> torch.Tensor:
+    """Routed-expert MLP on the native path: align -> permute -> grouped GEMM1 with the
+    SiLU-mul epilogue -> grouped GEMM2 scaled by the routing weight -> un-permute + sum
+    (+ ``add``, e.g. the shared-expert output).  ``w13`` must hold gate/up interleaved in
+    blocks of 128 per expert (``ref.interleave_gate_up``)."""
+    T, H = x.shape
+    k = topk_ids.shape[1]
+    E = w13.shape[0]
+    numel = T * k
+    cap = moe_align_cap(numel, E)
+    sorted_ids, expert_ids, npp, pos_of = moe_align(topk_ids, E, cap, expert_map, valid_tokens)
+    a_sorted = torch.empty((cap, H), device=x.device, dtype=x.dtype)
+    call("b200_moe_permute", ptr(x), x.stride(0), ptr(a_sorted), H, ptr(sorted_ids), ptr(npp),
+         numel, k, H, cap, DTYPE_CODE[x.dtype], stream_ptr())
+    row_w = torch.empty(cap, device=x.device, dtype=torch.float32)
+    call("b200_moe_row_weights", ptr(sorted_ids), ptr(topk_w), ptr(npp), ptr(row_w), numel, cap,
+         stream_ptr())
+    h = gemm_bf16_grouped(a_sorted, w13, expert_ids, npp, silu_mul=True)
+    y = gemm_bf16_grouped(h, w2, expert_ids, npp, row_scale=row_w)
+    out = torch.empty((T, H), device=x.device, dtype=x.dtype)
+    call("b200_moe_unpermute_sum", ptr(y), y.stride(0), ptr(pos_of), ptr(add),
+         add.stride(0) if add is not None else 0, ptr(out), H, ptr(valid_tokens), T, k, H,
+         float(alpha), DTYPE_CODE[x.dtype], stream_ptr())
+    return out
+
+
+def get_ep_indices(topk_ids: torch.Tensor, experts_per_rank: int, ep: int):
+    T, k = topk_ids.shape
+    dev = topk_ids.device
+    cnt = torch.empty(ep, device=dev, dtype=torch.int32)
+    idx = torch.zeros(T * min(k, ep), device=dev, dtype=torch.int32)
+    total = torch.empty(1, device=dev, dtype=torch.int32)
+    call("b200_get_ep_indices", ptr(topk_ids), T, k, experts_per_rank, ep, ptr(cnt), ptr(idx),
+         ptr(total), stream_ptr())
+    return cnt, idx, total

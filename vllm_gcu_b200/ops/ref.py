@@ -551,3 +551,244 @@ def advance_step(num_seqs: int, num_queries: int, block_size: int, input_tokens:
     seq_lens[:n] = (sl + 1).to(seq_lens.dtype)
     if num_seqs > n:
         slot_mapping[n:num_seqs] = -1
+
+
+# ---------------------------------------------------------------------------
+# mixture of experts
+# ---------------------------------------------------------------------------
+def topk_softmax(gating: torch.Tensor, k: int, renormalize: bool
+                 ) -> tuple[torch.Tensor, torch.Tensor]:
+    """softmax over experts then top-k (csrc/src/topk_softmax.cpp:32).  Returns
+    (weights fp32 ``[T, k]``, ids int32 ``[T, k]``)."""
+    probs = torch.softmax(gating.float(), dim=-1)
+    w, ids = probs.topk(k, dim=-1)
+    if renormalize:
+        w = w / w.sum(-1, keepdim=True)
+    return w, ids.to(torch.int32)
+
+
+def grouped_topk(gating: torch.Tensor, k: int, renormalize: bool, n_group: int, topk_group: int,
+                 bias: Optional[torch.Tensor] = None, scoring: str = "softmax",
+                 routed_scaling_factor: float = 1.0) -> tuple[torch.Tensor, torch.Tensor]:
+    """DeepSeek grouped routing (csrc/src/fused_grouped_topk.cpp:35,
+    vllm_gcu/kernels/fused_moe.py:234-267): score = sigmoid | softmax; selection uses
+    ``score + bias``; group score = sum of the top-2 biased scores of the group (max without
+    bias); keep ``topk_group`` groups, then top-k experts; the returned weights are the
+    unbiased scores (optionally renormalised)."""
+    g = gating.float()
+    scores = torch.sigmoid(g) if scoring == "sigmoid" else torch.softmax(g, dim=-1)
+    T, E = scores.shape
+    sel = scores + bias.float()[None] if bias is not None else scores
+    grp = sel.view(T, n_group, E // n_group)
+    if bias is not None:
+        gscore = grp.topk(2, dim=-1).values.sum(-1)
+    else:
+        gscore = grp.max(-1).values
+    gidx = gscore.topk(topk_group, dim=-1).indices
+    gmask = torch.zeros_like(gscore).scatter_(1, gidx, 1.0)
+    mask = gmask[:, :, None].expand(T, n_group, E // n_group).reshape(T, E)
+    masked = sel.masked_fill(mask == 0, float("-inf"))
+    ids = masked.topk(k, dim=-1).indices
+    w = scores.gather(1, ids)
+    if renormalize:
+        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    return w * routed_scaling_factor, ids.to(torch.int32)
+
+
+def moe_align_block_size(topk_ids: torch.Tensor, num_experts: int, block: int,
+                         valid_tokens: Optional[int] = None,
+                         expert_map: Optional[torch.Tensor] = None):
+    """Stable counting sort of the flattened (token, slot) pairs by expert; every expert
+    segment is padded to a multiple of ``block`` with the sentinel ``numel``.  Returns
+    (sorted_ids, expert_ids per block, num_tokens_post_pad) like
+    csrc/src/moe_align_block_size.cpp:37; ``valid_tokens`` limits the input to its first
+    rows (``_pad`` variant) and ``expert_map`` maps global to local expert ids with -1 for
+    experts that live elsewhere (``exts_`` variant), whose pairs are dropped."""
+    flat = topk_ids.reshape(-1).long()
+    numel = flat.numel()
+    k = topk_ids.shape[1]
+    if valid_tokens is not None:
+        flat = flat[: valid_tokens * k]
+    idx = torch.arange(flat.numel(), device=flat.device)
+    if expert_map is not None:
+        flat = expert_map.long()[flat]
+        keep = flat >= 0
+        flat, idx = flat[keep], idx[keep]
+    sorted_ids, expert_ids = [], []
+    for e in range(num_experts):
+        sel = idx[flat == e]
+        n = sel.numel()
+        if n == 0:
+            continue
+        pad = (-n) % block
+        sorted_ids.append(sel)
+        if pad:
+            sorted_ids.append(torch.full((pad,), numel, device=flat.device, dtype=idx.dtype))
+        expert_ids += [e] * ((n + pad) // block)
+    if sorted_ids:
+        sid = torch.cat(sorted_ids)
+    else:
+        sid = idx[:0]
+    return (sid.to(torch.int32),
+            torch.tensor(expert_ids, dtype=torch.int32, device=flat.device),
+            torch.tensor([sid.numel()], dtype=torch.int32, device=flat.device))
+
+
+def fused_experts(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_w: torch.Tensor,
+                  topk_ids: torch.Tensor, expert_map: Optional[torch.Tensor] = None,
+                  act: str = "silu") -> torch.Tensor:
+    """``sum_k w_k * down_e(act(gate_e(x)) * up_e(x))`` with ``w13 [E, 2I, H]`` (gate rows
+    first) and ``w2 [E, H, I]`` (csrc/src/fused_moe_kernel.cpp:43-63 +
+    vllm_gcu/kernels/modular_experts.py:81-288).  With ``expert_map`` only local experts
+    contribute (others add zero), which is what one EP rank computes."""
+    T, H = x.shape
+    out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
+    ids = topk_ids.long()
+    if expert_map is not None:
+        ids = expert_map.long()[ids]
+    E = w13.shape[0]
+    xf = x.float()
+    for e in range(E):
+        tok, slot = (ids == e).nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        h = xf[tok] @ w13[e].float().t()
+        h = act_and_mul(h.to(x.dtype), act).float()
+        y = h @ w2[e].float().t()
+        out.index_add_(0, tok, y * topk_w[tok, slot].float()[:, None])
+    return out.to(x.dtype)
+
+
+def moe_sum(x: torch.Tensor, valid_rows: Optional[int] = None) -> torch.Tensor:
+    """``[M, topk, K] -> [M, K]`` (csrc/src/moe_sum.cpp:75)."""
+    out = x.float().sum(1).to(x.dtype)
+    if valid_rows is not None:
+        out[valid_rows:] = 0
+    return out
+
+
+def get_ep_indices(topk_ids: torch.Tensor, experts_per_rank: int, ep: int):
+    """Per destination rank: the tokens that have at least one selected expert there
+    (a token is listed once per rank).  Returns (count ``[ep]``, token indices rank-major,
+    total) as in tests/kernels/test_get_ep_indices.py:5-53."""
+    T = topk_ids.shape[0]
+    rank_of = (topk_ids.long() // experts_per_rank)
+    counts, idxs = [], []
+    for r in range(ep):
+        hit = (rank_of == r).any(dim=1).nonzero(as_tuple=True)[0]
+        counts.append(hit.numel())
+        idxs.append(hit)
+    idx = torch.cat(idxs) if idxs else torch.zeros(0, dtype=torch.long)
+    return (torch.tensor(counts, dtype=torch.int32, device=topk_ids.device), idx.to(torch.int32),
+            int(sum(counts)))
+
+
+def eplb_map_to_physical(topk_ids: torch.Tensor, log2phy: torch.Tensor,
+                         replica_count: torch.Tensor, load: Optional[torch.Tensor] = None
+                         ) -> torch.Tensor:
+    """Logical -> physical expert ids; the replica is chosen from the (token, slot)
+    position modulo the replica count, and the per-physical-expert load histogram is
+    updated (csrc/src/eplb_map_to_physical_and_record.cpp:36,
+    vllm_gcu/kernels/quantization/utils.py:23-54)."""
+    ids = topk_ids.long()
+    T, k = ids.shape
+    pos = torch.arange(T * k, device=ids.device).view(T, k)
+    rep = pos % replica_count.long()[ids]
+    phys = log2phy.long()[ids, rep]
+    if load is not None:
+        load.index_add_(0, phys.reshape(-1), torch.ones(T * k, dtype=load.dtype,
+                                                        device=load.device))
+    return phys.to(topk_ids.dtype)
+
+
+# ---------------------------------------------------------------------------
+# speculative decoding (vllm_gcu/patch/patch_0_9_2/rejection_sampler.py:11-120)
+# ---------------------------------------------------------------------------
+def rejection_greedy_sample(draft_ids: torch.Tensor, target_argmax: torch.Tensor,
+                            bonus_ids: torch.Tensor, num_draft: torch.Tensor) -> torch.Tensor:
+    """Greedy verification.  draft_ids ``[B, S]`` (padded), target_argmax ``[B, S]`` (argmax of
+    the target at each draft position), bonus ``[B]``.  Output ``[B, S + 1]`` int32 filled
+    with -1: accepted prefix, then the target's token at the first mismatch, or the bonus
+    token when every draft token was accepted."""
+    B, S = draft_ids.shape
+    out = torch.full((B, S + 1), -1, dtype=torch.int32, device=draft_ids.device)
+    for b in range(B):
+        n = int(num_draft[b])
+        rejected = False
+        for i in range(n):
+            out[b, i] = target_argmax[b, i]
+            if int(draft_ids[b, i]) != int(target_argmax[b, i]):
+                rejected = True
+                break
+        if not rejected:
+            out[b, n] = bonus_ids[b]
+    return out
+
+
+def rejection_random_sample(draft_ids: torch.Tensor, draft_probs: Optional[torch.Tensor],
+                            target_probs: torch.Tensor, bonus_ids: torch.Tensor,
+                            recovered_ids: torch.Tensor, uniform: torch.Tensor,
+                            num_draft: torch.Tensor) -> torch.Tensor:
+    """Standard speculative rejection sampling: accept draft token x with probability
+    ``min(1, p_target(x) / p_draft(x))`` (``p_draft = 1`` for draft-free proposers such as
+    n-gram), otherwise emit the recovered token.  Shapes: probs ``[B, S, V]``,
+    uniform ``[B, S]``."""
+    B, S = draft_ids.shape
+    out = torch.full((B, S + 1), -1, dtype=torch.int32, device=draft_ids.device)
+    for b in range(B):
+        n = int(num_draft[b])
+        rejected = False
+        for i in range(n):
+            x = int(draft_ids[b, i])
+            pt = float(target_probs[b, i, x])
+            pd = 1.0 if draft_probs is None else float(draft_probs[b, i, x])
+            if pd > 0 and pt / pd >= float(uniform[b, i]):
+                out[b, i] = x
+            else:
+                out[b, i] = recovered_ids[b, i]
+                rejected = True
+                break
+        if not rejected:
+            out[b, n] = bonus_ids[b]
+    return out
+
+
+def sample_recovered_tokens(draft_ids: torch.Tensor, draft_probs: Optional[torch.Tensor],
+                            target_probs: torch.Tensor, noise: torch.Tensor) -> torch.Tensor:
+    """Recovered token at every draft position: argmax of ``max(0, p_t - p_d) / q`` with
+    ``q ~ Exp(1)`` (for draft-free proposers the draft token itself is excluded)."""
+    if draft_probs is None:
+        adj = target_probs.clone()
+        adj.scatter_(-1, draft_ids.long()[..., None], 0.0)
+    else:
+        adj = (target_probs - draft_probs).clamp_min(0.0)
+    return (adj / noise.clamp_min(1e-30)).argmax(-1).to(torch.int32)
+
+
+def expand_batch_to_tokens(x: torch.Tensor, cu_num_tokens: torch.Tensor,
+                           replace_from: int = 0, replace_to: int = 0) -> torch.Tensor:
+    """Repeats ``x[b]`` for each token of request b (``cu_num_tokens`` inclusive prefix
+    sums), optionally replacing one value."""
+    counts = torch.diff(cu_num_tokens, prepend=cu_num_tokens.new_zeros(1))
+    y = torch.repeat_interleave(x, counts.long())
+    if replace_from != replace_to:
+        y = torch.where(y == replace_from, torch.full_like(y, replace_to), y)
+    return y
+
+
+# ---------------------------------------------------------------------------
+# multi-LoRA (vllm_gcu/lora/lora_ops.py:10-139, csrc/src/dispatch_bgmv.cpp:19)
+# ---------------------------------------------------------------------------
+def bgmv(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, indices: torch.Tensor,
+         scale: float = 1.0, y_offset: int = 0, y_slice: Optional[int] = None) -> torch.Tensor:
+    """``y[t, off:off+n] += scale * w[idx[t]] @ x[t]`` for ``idx[t] >= 0``;
+    ``w [L, h_out, h_in]`` (a leading singleton layer dim is accepted)."""
+    if w.dim() == 4:
+        w = w[:, 0]
+    n = w.shape[1] if y_slice is None else y_slice
+    valid = indices >= 0
+    if valid.any():
+        wi = w[indices[valid].long()].float()
+        upd = torch.einsum("tnk,tk->tn", wi, x[valid].float()) * scale
+        y[valid, y_offset:y_offset + n] += upd.to(y.dtype)
+    return y
