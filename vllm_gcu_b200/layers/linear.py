@@ -104,9 +104,30 @@ class LinearBase(nn.Module):
         return self.quant_method.apply(self, x, **kw)
 
     # -- loading -----------------------------------------------------------
-    def shard_of(self, name: str, full: torch.Tensor, shard_id=None) -> tuple[torch.Tensor, Optional[slice]]:
-        """Returns (tensor slice for this rank, destination row range or None)."""
-        return full, None
+    def shard_spec(self, shard_id=None):
+        """Which part of a full (unsharded) checkpoint tensor belongs to this rank:
+        ``(out_segments, in_range)`` in feature units.  ``out_segments`` is a list of
+        ``(src_offset, size, dst_offset)`` along the output dimension (None = everything),
+        ``in_range`` is ``(src_offset, size)`` along the input dimension (None = everything)."""
+        return None, None
+
+    def copy_sharded(self, dst: torch.Tensor, full: torch.Tensor, shard_id, out_dim: int,
+                     in_dim: int, out_pack: int = 1, in_pack: int = 1) -> None:
+        """Copies this rank's part of ``full`` into ``dst``.  ``out_dim`` / ``in_dim`` name the
+        tensor dimensions that run along output / input features (-1: absent) and
+        ``*_pack`` how many features one element of that dimension holds."""
+        segs, rng = self.shard_spec(shard_id)
+        src = full
+        if rng is not None and in_dim >= 0:
+            src = src.narrow(in_dim, rng[0] // in_pack, rng[1] // in_pack)
+        if segs is None or out_dim < 0:
+            assert dst.shape == src.shape, \
+                f"{self.prefix}: {tuple(dst.shape)} vs {tuple(src.shape)}"
+            dst.copy_(src)
+            return
+        for so, n, do in segs:
+            dst.narrow(out_dim, do // out_pack, n // out_pack).copy_(
+                src.narrow(out_dim, so // out_pack, n // out_pack))
 
     def load_weight(self, name: str, full: torch.Tensor, shard_id=None) -> None:
         """Copies the part of checkpoint tensor ``full`` (parameter ``name``: 'weight',
@@ -115,10 +136,10 @@ class LinearBase(nn.Module):
         if loader is not None and loader(self, name, full, shard_id):
             return
         param = getattr(self, name)
-        src, rows = self.shard_of(name, full, shard_id)
-        dst = param.data if rows is None else param.data[rows]
-        assert dst.shape == src.shape, f"{self.prefix}.{name}: {tuple(dst.shape)} vs {tuple(src.shape)}"
-        dst.copy_(src)
+        if full.dim() == 1:
+            self.copy_sharded(param.data, full, shard_id, 0, -1)
+        else:
+            self.copy_sharded(param.data, full, shard_id, 0, 1)
 
     def finalize(self) -> None:
         self.quant_method.process_weights_after_loading(self)
@@ -138,11 +159,11 @@ class MergedReplicatedLinear(ReplicatedLinear):
         self.output_sizes = list(output_sizes)
         super().__init__(in_features, sum(output_sizes), **kw)
 
-    def shard_of(self, name, full, shard_id=None):
+    def shard_spec(self, shard_id=None):
         if shard_id is None:
-            return full, None
+            return None, None
         off = sum(self.output_sizes[:shard_id])
-        return full, slice(off, off + self.output_sizes[shard_id])
+        return [(0, self.output_sizes[shard_id], off)], None
 
 
 class ColumnParallelLinear(LinearBase):
@@ -154,9 +175,9 @@ class ColumnParallelLinear(LinearBase):
         super().__init__(in_features, out_features, in_features, out_features // tp, bias, dtype,
                          device, quant_method, prefix)
 
-    def shard_of(self, name, full, shard_id=None):
+    def shard_spec(self, shard_id=None):
         n = self.out_per_rank
-        return full.narrow(0, tp_rank() * n, n), None
+        return [(tp_rank() * n, n, 0)], None
 
     def forward(self, x, **kw):
         y = super().forward(x, **kw)
@@ -176,16 +197,16 @@ class MergedColumnParallelLinear(LinearBase):
         super().__init__(in_features, sum(output_sizes), in_features, sum(output_sizes) // tp,
                          bias, dtype, device, quant_method, prefix)
 
-    def shard_of(self, name, full, shard_id=None):
+    def shard_spec(self, shard_id=None):
         tp, r = tp_size(), tp_rank()
-        if shard_id is None:      # already-merged checkpoint tensor: split it first
-            parts = torch.split(full, self.output_sizes, dim=0)
-            src = torch.cat([p.narrow(0, r * (p.shape[0] // tp), p.shape[0] // tp)
-                             for p in parts], dim=0)
-            return src, None
-        n = self.output_sizes[shard_id] // tp
-        off = sum(s // tp for s in self.output_sizes[:shard_id])
-        return full.narrow(0, r * n, n), slice(off, off + n)
+        ids = range(len(self.output_sizes)) if shard_id is None else [shard_id]
+        segs = []
+        for i in ids:
+            n = self.output_sizes[i] // tp
+            dst = sum(s // tp for s in self.output_sizes[:i])
+            base = sum(self.output_sizes[:i]) if shard_id is None else 0
+            segs.append((base + r * n, n, dst))
+        return segs, None
 
 
 class QKVParallelLinear(LinearBase):
@@ -214,21 +235,20 @@ class QKVParallelLinear(LinearBase):
     def kv_size(self) -> int:
         return self.num_kv_heads * self.head_dim
 
-    def shard_of(self, name, full, shard_id=None):
+    def shard_spec(self, shard_id=None):
         r = tp_rank()
-        if shard_id is None:
-            tq = self.num_heads * tp_size() * self.head_dim
-            tkv = self.total_kv_heads * self.head_dim
-            q, k, v = torch.split(full, [tq, tkv, tkv], dim=0)
-            parts = [self.shard_of(name, q, "q")[0], self.shard_of(name, k, "k")[0],
-                     self.shard_of(name, v, "v")[0]]
-            return torch.cat(parts, dim=0), None
-        if shard_id == "q":
-            return full.narrow(0, r * self.q_size, self.q_size), slice(0, self.q_size)
+        tq = self.num_heads * tp_size() * self.head_dim
+        tkv = self.total_kv_heads * self.head_dim
         kv_rank = r // self.kv_replicas
-        src = full.narrow(0, kv_rank * self.kv_size, self.kv_size)
-        off = self.q_size + (0 if shard_id == "k" else self.kv_size)
-        return src, slice(off, off + self.kv_size)
+        spec = {"q": (r * self.q_size, self.q_size, 0, 0),
+                "k": (kv_rank * self.kv_size, self.kv_size, self.q_size, tq),
+                "v": (kv_rank * self.kv_size, self.kv_size, self.q_size + self.kv_size, tq + tkv)}
+        ids = ["q", "k", "v"] if shard_id is None else [shard_id]
+        segs = []
+        for i in ids:
+            so, n, do, base = spec[i]
+            segs.append(((base if shard_id is None else 0) + so, n, do))
+        return segs, None
 
 
 class RowParallelLinear(LinearBase):
@@ -240,11 +260,9 @@ class RowParallelLinear(LinearBase):
         super().__init__(in_features, out_features, in_features // tp, out_features, bias, dtype,
                          device, quant_method, prefix)
 
-    def shard_of(self, name, full, shard_id=None):
-        if name == "bias" or full.dim() == 1:
-            return full, None
+    def shard_spec(self, shard_id=None):
         n = self.in_per_rank
-        return full.narrow(1, tp_rank() * n, n), None
+        return None, (tp_rank() * n, n)
 
     def forward(self, x, **kw):
         if tp_size() == 1 or not self.reduce_results:

@@ -44,6 +44,9 @@ class DenseMLP(nn.Module):
             device=device, quant_method=get_linear_method(cfg, prefix + ".down_proj"),
             prefix=prefix + ".down_proj")
         self.act = cfg.hidden_act
+        from ..layers.linear import UnquantizedLinearMethod
+        if not isinstance(self.gate_up_proj.quant_method, UnquantizedLinearMethod):
+            self.gate_up_proj.fuse_silu = False   # quantised GEMMs have no SiLU epilogue yet
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         h = self.gate_up_proj(x)

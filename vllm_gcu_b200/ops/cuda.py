@@ -452,3 +452,65 @@ def get_ep_indices(topk_ids: torch.Tensor, experts_per_rank: int, ep: int):
     call("b200_get_ep_indices", ptr(topk_ids), T, k, experts_per_rank, ep, ptr(cnt), ptr(idx),
          ptr(total), stream_ptr())
     return cnt, idx, total
+
+
+# ---------------------------------------------------------------------------
+# quantisation
+# ---------------------------------------------------------------------------
+def per_token_quant(x: torch.Tensor, kind: str = "fp8",
+                    valid_rows: Optional[torch.Tensor] = None):
+    """Dynamic per-token quantisation to fp8 e4m3 or int8; returns (q, scales [T, 1])."""
+    x2 = _rowmajor_2d(x)
+    T, H = x2.shape
+    q = torch.empty((T, H), device=x.device, dtype=FP8 if kind == "fp8" else torch.int8)
+    s = torch.empty((T, 1), device=x.device, dtype=torch.float32)
+    call("b200_per_token_quant", ptr(x2), x2.stride(0), ptr(q), H, ptr(s), ptr(valid_rows), T, H,
+         0 if kind == "fp8" else 1, DTYPE_CODE[x.dtype], stream_ptr())
+    return q, s
+
+
+def per_tensor_fp8_quant(x: torch.Tensor):
+    xc = x.contiguous()
+    q = torch.empty(xc.shape, device=x.device, dtype=FP8)
+    ws = torch.empty(1, device=x.device, dtype=torch.float32)
+    s = torch.empty(1, device=x.device, dtype=torch.float32)
+    call("b200_per_tensor_fp8_quant", ptr(xc), ptr(q), xc.numel(), ptr(ws), ptr(s),
+         DTYPE_CODE[x.dtype], stream_ptr())
+    return q, s
+
+
+def int8_dequant(q: torch.Tensor, scale: torch.Tensor, azp: Optional[torch.Tensor] = None,
+                 dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    qc = q.contiguous()
+    out = torch.empty(qc.shape, device=q.device, dtype=dtype)
+    call("b200_int8_dequant", ptr(qc), ptr(out), qc.numel(), ptr(scale), ptr(azp),
+         DTYPE_CODE[dtype], stream_ptr())
+    return out
+
+
+def gemm_q8(a: torch.Tensor, b: torch.Tensor, a_scale: torch.Tensor, b_scale: torch.Tensor,
+            bias: Optional[torch.Tensor] = None, kind: int = 0,
+            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """8-bit GEMM ``a [M,K] @ b [N,K]^T`` -> bf16.  kind 0: fp8 with per-token ``a_scale [M]``
+    and per-channel ``b_scale [N]``; 1: fp8 block scales ``a_scale [M, K/128]``,
+    ``b_scale [N/128, K/128]``; 2: int8 with per-token / per-channel scales."""
+    M, K = a.shape
+    Nn = b.shape[0]
+    assert a.element_size() == 1 and b.element_size() == 1 and a.stride(1) == 1
+    if out is None:
+        out = torch.empty((M, Nn), device=a.device, dtype=torch.bfloat16)
+    a_scale = a_scale.contiguous()
+    b_scale = b_scale.contiguous()
+    lds_a = a_scale.stride(0) if (kind == 1 and a_scale.dim() == 2) else 1
+    lds_b = b_scale.stride(0) if (kind == 1 and b_scale.dim() == 2) else 1
+    call("b200_gemm_q8", ptr(a), a.stride(0), ptr(b), b.stride(0), ptr(out), out.stride(0), M, Nn,
+         K, ptr(a_scale), lds_a, ptr(b_scale), lds_b, ptr(bias), kind, stream_ptr())
+    return out
+
+
+def weight_dequant(qw: torch.Tensor, scales: torch.Tensor, zs: torch.Tensor, out: torch.Tensor,
+                   group: int, bits: int) -> torch.Tensor:
+    N, K = out.shape
+    call("b200_weight_dequant", ptr(qw), ptr(scales), ptr(zs), ptr(out), N, K, group, bits,
+         DTYPE_CODE[out.dtype], stream_ptr())
+    return out
