@@ -214,6 +214,7 @@ int launch_t(const Args& a, int act, int mode, int quant, cudaStream_t s) {
     B200_ACT_CASE(kGeluQuick)
     case kIdentity:
       if (mode == kActMul) return launch_q<T, kIdentity, kActMul>(a, quant, s);
+      if (mode == kPlain) return launch_q<T, kIdentity, kPlain>(a, quant, s);  // pure quantisation
       break;
     default:
       break;

@@ -18,7 +18,7 @@ from typing import Iterable, Optional, Sequence, Union
 import torch
 
 from ..config import (CacheConfig, EngineConfig, ModelConfig, ParallelConfig, SchedulerConfig,
-                      preset)
+                      SpeculativeConfig, preset)
 from ..models import build_model
 from ..parallel.state import get_state, init_distributed
 from .model_runner import ModelRunner, StepHandle
@@ -54,6 +54,32 @@ class LLMEngine:
             from ..parallel import symm
             symm.attach(cfg)
         self.runner = ModelRunner(cfg, self.model, self.device)
+        self.proposer = None
+        self.spec_metrics = None
+        sp = cfg.speculative
+        if sp.method:
+            from ..spec import NgramProposer, SpecMetrics
+            self.spec_metrics = SpecMetrics()
+            if cfg.scheduler.async_scheduling:
+                # draft tokens come from the previous step's verified output
+                cfg.scheduler.async_scheduling = False
+            if sp.method == "ngram":
+                self.proposer = NgramProposer(sp.num_speculative_tokens, sp.prompt_lookup_max,
+                                              sp.prompt_lookup_min)
+            elif sp.method in ("mtp", "deepseek_mtp"):
+                from ..models.deepseek_mtp import DeepSeekMTP
+                if sp.num_speculative_tokens != 1:
+                    raise ValueError("the MTP drafter proposes one token per step")
+                drafter = DeepSeekMTP(cfg.model, self.device, target=self.model)
+                if cfg.load_format == "dummy":
+                    drafter.init_random(cfg.seed)
+                elif cfg.load_format == "safetensors":
+                    from ..utils.weights import iter_safetensors
+                    drafter.load_weights(iter_safetensors(cfg.model_path))
+                drafter.eval()
+                self.runner.drafter = drafter
+            else:
+                raise ValueError(f"unknown speculative method {sp.method!r}")
         num_blocks = self.runner.profile_num_blocks()
         if st.world_size > 1:
             num_blocks = self._agree_min(num_blocks)
@@ -61,7 +87,9 @@ class LLMEngine:
         self.runner.capture_graphs(cfg.cuda_graph_sizes)
         self.scheduler = Scheduler(cfg.scheduler, cfg.cache, num_blocks,
                                    separate_prefill_decode=bool(
-                                       cfg.additional_config.get("separate_prefill_decode")))
+                                       cfg.additional_config.get("separate_prefill_decode")),
+                                   num_lookahead_tokens=sp.num_speculative_tokens
+                                   if sp.method else 0)
         self._ids = itertools.count()
         self._pending: deque[tuple[SchedulerOutput, StepHandle]] = deque()
         self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0}
@@ -107,7 +135,20 @@ class LLMEngine:
         return so, handle
 
     def _finish(self, so: SchedulerOutput, handle: StepHandle) -> list[RequestOutput]:
-        return self.scheduler.update_from_output(so, handle.token_ids(), handle.draft)
+        toks = handle.token_ids()
+        draft = handle.draft_tokens()
+        if self.spec_metrics is not None:
+            for rid, nd in zip(handle.req_ids, handle.extra.get("num_draft", [])):
+                if nd:
+                    self.spec_metrics.update(nd, len(toks.get(rid, ())))
+        outs = self.scheduler.update_from_output(so, toks, draft)
+        if self.proposer is not None:
+            for s in so.scheduled:
+                r = s.req
+                if s.will_sample and not r.finished and r.request_id in self.scheduler.requests:
+                    room = r.sampling_params.max_tokens - len(r.output_token_ids) - 1
+                    r.spec_token_ids = self.proposer.propose(r.all_token_ids)[:max(0, room)]
+        return outs
 
     def step(self) -> list[RequestOutput]:
         """Runs (or, with async scheduling, launches and retires) one engine step."""
@@ -154,6 +195,8 @@ class LLM:
                  load_format: Optional[str] = None, comm_backend: str = "fused",
                  enable_expert_parallel: bool = False, dtype: Optional[str] = None,
                  cuda_graph_sizes: Optional[list[int]] = None,
+                 speculative_method: Optional[str] = None, num_speculative_tokens: int = 0,
+                 prompt_lookup_max: int = 4, prompt_lookup_min: int = 1,
                  additional_config: Optional[dict] = None, **model_overrides):
         model_path = None
         if isinstance(model, ModelConfig):
@@ -181,6 +224,8 @@ class LLM:
                                     pipeline_parallel_size=pipeline_parallel_size,
                                     comm_backend=comm_backend,
                                     enable_expert_parallel=enable_expert_parallel),
+            speculative=SpeculativeConfig(speculative_method, num_speculative_tokens,
+                                          prompt_lookup_max, prompt_lookup_min),
             device=device, seed=seed, enforce_eager=enforce_eager,
             cuda_graph_sizes=cuda_graph_sizes,
             load_format=load_format or ("safetensors" if model_path else "dummy"),

@@ -43,7 +43,16 @@ class StepHandle:
     accepted_host: Optional[torch.Tensor] = None
     draft: Optional[dict[str, list[int]]] = None
     device_ms_events: Optional[tuple] = None
+    draft_host: Optional[torch.Tensor] = None
     extra: dict = field(default_factory=dict)
+
+    def draft_tokens(self) -> Optional[dict[str, list[int]]]:
+        """Draft token proposed by the on-device drafter for every sampling request."""
+        if self.draft_host is None or self.num_sampled == 0:
+            return None
+        self.wait()
+        arr = self.draft_host[: self.num_sampled].numpy()
+        return {rid: [int(arr[i])] for i, rid in enumerate(self.req_ids)}
 
     def ready(self) -> bool:
         return self.event is None or self.event.query()
@@ -90,6 +99,13 @@ class ModelRunner:
         self.kv_caches: list[torch.Tensor] = []
         self.num_blocks = 0
         self.sampler = Sampler(cfg.model.vocab_size)
+        self.max_spec = cfg.speculative.num_speculative_tokens if cfg.speculative.method else 0
+        self.rejection = None
+        self.drafter = None                        # on-device drafter (DeepSeek MTP)
+        self.drafter_caches: list[torch.Tensor] = []
+        if self.max_spec:
+            from ..spec import RejectionSampler
+            self.rejection = RejectionSampler()
         self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
         self.graph_sizes: list[int] = []
         self.graph_pool = None
@@ -109,15 +125,22 @@ class ModelRunner:
     def _alloc_buffers(self) -> None:
         dev, pin = self.device, self.is_cuda
         T, S, MB = self.max_tokens, self.max_seqs, self.max_blocks
-        # int64 block: input_ids | positions | slot_mapping | sample_indices | seeds
+        W = 1 + self.max_spec          # sampled positions per request
+        # int64 block: input_ids | positions | slot_mapping | sample_indices | seeds | mtp_ids
         self.i64_layout = {"input_ids": (0, T), "positions": (T, T), "slot_mapping": (2 * T, T),
-                           "sample_indices": (3 * T, S), "seeds": (3 * T + S, S)}
-        n64 = 3 * T + 2 * S
-        # int32 block: seq_lens | cu_q | feed_dst | feed_src | top_k | block_tables
-        self.i32_layout = {"seq_lens": (0, S), "cu_q": (S, S + 1), "feed_dst": (2 * S + 1, S),
-                           "feed_src": (3 * S + 1, S), "top_k": (4 * S + 1, S),
-                           "block_tables": (5 * S + 1, S * MB)}
-        n32 = 5 * S + 1 + S * MB
+                           "sample_indices": (3 * T, S * W), "seeds": (3 * T + S * W, S),
+                           "mtp_ids": (3 * T + S * W + S, T if self.max_spec else 0)}
+        n64 = 3 * T + S * W + S + (T if self.max_spec else 0)
+        # int32 block: seq_lens | cu_q | feed_dst | feed_src | top_k | num_draft | draft_ids |
+        #              block_tables
+        o = 0
+        self.i32_layout = {}
+        for name, n in (("seq_lens", S), ("cu_q", S + 1), ("feed_dst", S), ("feed_src", S),
+                        ("top_k", S), ("num_draft", S), ("draft_ids", S * max(self.max_spec, 1)),
+                        ("block_tables", S * MB)):
+            self.i32_layout[name] = (o, n)
+            o += n
+        n32 = o
         self.h_i64 = torch.zeros(n64, dtype=torch.int64, pin_memory=pin)
         self.h_i32 = torch.zeros(n32, dtype=torch.int32, pin_memory=pin)
         self.h_f32 = torch.zeros(2 * S, dtype=torch.float32, pin_memory=pin)  # temperature | top_p
@@ -143,8 +166,13 @@ class ModelRunner:
         self.feed_dst, self.feed_src, self.top_k = v32("feed_dst"), v32("feed_src"), v32("top_k")
         self.block_tables = v32("block_tables").view(S, MB)
         self.temperature, self.top_p = self.d_f32[:S], self.d_f32[S:]
-        self.sampled = [torch.zeros(S, dtype=torch.int64, device=dev) for _ in range(2)]
-        self.sampled_host = [torch.zeros(S, dtype=torch.int64, pin_memory=pin) for _ in range(2)]
+        self.num_draft, self.draft_ids = v32("num_draft"), v32("draft_ids")
+        self.mtp_ids = v64("mtp_ids") if self.max_spec else None
+        self.sampled = [torch.zeros(S * W, dtype=torch.int64, device=dev) for _ in range(2)]
+        self.sampled_host = [torch.zeros(S * W, dtype=torch.int64, pin_memory=pin)
+                             for _ in range(2)]
+        self.draft_out = torch.zeros(S, dtype=torch.int64, device=dev)
+        self.draft_host = torch.zeros(S, dtype=torch.int64, pin_memory=pin)
         self.decode_ws: Optional[tuple[torch.Tensor, torch.Tensor]] = None
         # host-side block table, one row per live request
         self.bt_rows: dict[str, int] = {}
@@ -194,6 +222,16 @@ class ModelRunner:
                                           spec["head_dim"], dtype=dt, device=self.device)
                               for _ in range(spec["layers"])]
         self.num_blocks = num_blocks
+        if self.drafter is not None:
+            ds = self.drafter.kv_cache_spec()
+            if ds["type"] == "mla":
+                self.drafter_caches = [torch.zeros(num_blocks, self.block_size, ds["width"],
+                                                   dtype=dt, device=self.device)
+                                       for _ in range(ds["layers"])]
+            else:
+                self.drafter_caches = [torch.zeros(2, num_blocks, self.block_size, ds["kv_heads"],
+                                                   ds["head_dim"], dtype=dt, device=self.device)
+                                       for _ in range(ds["layers"])]
         if self.is_cuda and spec["type"] == "gqa":
             Hq = mc.num_attention_heads // self.cfg.parallel.tensor_parallel_size
             ns = 32
@@ -270,7 +308,8 @@ class ModelRunner:
         bs = self.block_size
         T_real = nd + sum(s.num_tokens for s in prefills)
 
-        use_graph = (self.is_cuda and npf == 0 and self.graphs and nd <= self.graph_sizes[-1])
+        use_graph = (self.is_cuda and npf == 0 and self.graphs and nd <= self.graph_sizes[-1]
+                     and self.drafter is None)
         B_pad = _pad_batch(nd, self.graph_sizes) if use_graph else B
         T = T_real + (B_pad - B)
 
@@ -337,11 +376,28 @@ class ModelRunner:
         # sampling rows
         samplers = [j for j, s in enumerate(order) if s.will_sample]
         ns = len(samplers)
-        width = 1
-        samp_idx = tok_off[1:][samplers] - 1 if ns else np.zeros(0, dtype=np.int64)
-        i64[o_samp:o_samp + ns] = samp_idx
-        if B_pad > B:
-            i64[o_samp + ns:o_samp + B_pad] = 0
+        nspec = [len(order[j].spec_token_ids) for j in samplers]
+        S_max = max(nspec) if nspec else 0
+        width = 1 + S_max
+        last = tok_off[1:][samplers] - 1 if ns else np.zeros(0, dtype=np.int64)
+        if S_max == 0:
+            i64[o_samp:o_samp + ns] = last
+            if B_pad > B:
+                i64[o_samp + ns:o_samp + B_pad] = 0
+        else:
+            # row (r, i) = i-th verified position of request r; rows past its own draft length
+            # repeat its last position and are ignored by the verification kernel
+            ns_arr = np.asarray(nspec, dtype=np.int64)
+            first = last - ns_arr
+            grid = first[:, None] + np.minimum(np.arange(width)[None, :], ns_arr[:, None])
+            i64[o_samp:o_samp + ns * width] = grid.reshape(-1)
+            o_nd, o_dr = self.i32_layout["num_draft"][0], self.i32_layout["draft_ids"][0]
+            i32[o_nd:o_nd + ns] = ns_arr
+            dr = np.zeros((ns, S_max), dtype=np.int32)
+            for r, j in enumerate(samplers):
+                if nspec[r]:
+                    dr[r, :nspec[r]] = order[j].spec_token_ids
+            i32[o_dr:o_dr + ns * S_max] = dr.reshape(-1)
         sp_list = [order[j].req.sampling_params for j in samplers]
         all_greedy = all(sp.greedy for sp in sp_list)
         if not all_greedy:
@@ -375,7 +431,19 @@ class ModelRunner:
         if self.is_cuda and (want_device_timing or self.timing_events is not None):
             ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             ev0.record()
-        n64 = o_seed + self.max_seqs if not all_greedy else o_samp + max(ns, B_pad)
+        if self.drafter is not None:
+            # drafter inputs: the step's token ids shifted left by one inside each request; the
+            # id that is being sampled right now is patched in on the device
+            o_mt = self.i64_layout["mtp_ids"][0]
+            mt = i64[o_mt:o_mt + T_real]
+            mt[:T_real - 1] = ids[1:T_real]
+            for j, s_ in enumerate(order):
+                b_ = int(tok_off[j + 1])
+                nxt = s_.start + s_.num_tokens
+                mt[b_ - 1] = s_.req.token_at(nxt) if nxt < s_.req.num_tokens else 0
+            n64 = o_mt + T_real
+        else:
+            n64 = o_seed + self.max_seqs if not all_greedy else o_samp + max(ns * width, B_pad)
         n32 = o_bt + (max(B_pad, B) - 1) * MB + used_blocks
         self.d_i64[:n64].copy_(self.h_i64[:n64], non_blocking=True)
         self.d_i32[:n32].copy_(self.h_i32[:n32], non_blocking=True)
@@ -403,7 +471,7 @@ class ModelRunner:
             max_seq_len=max_seq_len,
             decode_splits=self._decode_splits(B_pad if use_graph else max(nd, 1), max_seq_len),
             decode_workspace=self.decode_ws,
-            sample_indices=self.sample_indices[:max(ns, 1)],
+            sample_indices=self.sample_indices[:max(ns * width, 1)],
             q_lens_cpu=[int(x) for x in ntok], seq_lens_cpu=[int(x) for x in seq_after])
 
         if use_graph:
@@ -412,14 +480,17 @@ class ModelRunner:
             self.graph_launches += self.graph_kernel_counts.get(key, 0)
         else:
             with torch.inference_mode():
-                self._forward_and_sample(md, T, ns, out_ids, all_greedy)
+                self._forward_and_sample(md, T, ns, out_ids, all_greedy, width)
 
         # device -> host (asynchronous; consumed by StepHandle.token_ids)
         host = self.sampled_host[cur]
         event = None
         if ns:
-            host[:ns].copy_(out_ids[:ns], non_blocking=True)
-            self.d2h_bytes += ns * 8
+            host[:ns * width].copy_(out_ids[:ns * width], non_blocking=True)
+            self.d2h_bytes += ns * width * 8
+            if self.drafter is not None:
+                self.draft_host[:ns].copy_(self.draft_out[:ns], non_blocking=True)
+                self.d2h_bytes += ns * 8
         if self.is_cuda:
             if ev1 is not None:
                 ev1.record()
@@ -431,23 +502,76 @@ class ModelRunner:
         self.prev_index = {order[j].req.request_id: r for r, j in enumerate(samplers)}
         self.step_counter += 1
         return StepHandle([order[j].req.request_id for j in samplers], ns, host, event,
-                          width, device_ms_events=(ev0, ev1) if ev0 is not None else None)
+                          width, device_ms_events=(ev0, ev1) if ev0 is not None else None,
+                          draft_host=self.draft_host if self.drafter is not None else None,
+                          extra={"num_draft": nspec})
 
     def _forward_and_sample(self, md: AttentionMetadata, T: int, ns: int, out_ids: torch.Tensor,
-                            all_greedy: bool) -> None:
+                            all_greedy: bool, width: int = 1) -> None:
         hidden = self.model(self.input_ids[:T], md, self.kv_caches)
         if not self.model.is_last_stage or ns == 0:
             return
-        if md.num_prefills == 0:
+        if md.num_prefills == 0 and width == 1:
             rows = hidden[:ns]          # decode-only: row i is the i-th sampling request
         else:
-            rows = hidden.index_select(0, self.sample_indices[:ns])
+            rows = hidden.index_select(0, self.sample_indices[:ns * width])
         logits = self.model.compute_logits(rows)
         if self.keep_logits:
             self.last_logits = logits.float().cpu()
         st = None if all_greedy else SamplingTensors(self.temperature[:ns], self.top_k[:ns],
                                                      self.top_p[:ns], self.seeds[:ns])
-        self.sampler(logits, st, out=out_ids[:ns])
+        if width == 1:
+            self.sampler(logits, st, out=out_ids[:ns])
+        else:
+            self._verify(logits, st, ns, width, out_ids)
+        if self.drafter is not None:
+            self._draft_mtp(hidden, md, T, ns, width, out_ids)
+
+    def _verify(self, logits: torch.Tensor, st: Optional[SamplingTensors], ns: int, width: int,
+                out_ids: torch.Tensor) -> None:
+        """Rejection sampling of the draft tokens; writes ``[ns, width]`` ids (-1 padded)."""
+        S = width - 1
+        draft = self.draft_ids[:ns * S].view(ns, S)
+        nd = self.num_draft[:ns]
+        if st is None:
+            tgt = self.sampler(logits, None).view(ns, width)
+            out = self.rejection.greedy(draft, tgt, nd)
+        else:
+            V = logits.shape[-1]
+            t = st.temperature.repeat_interleave(width)
+            safe_t = torch.where(t > 0, t, torch.ones_like(t))
+            from ..ops import ref as _ref
+            masked = _ref.apply_top_k_top_p(
+                logits.float() / safe_t[:, None],
+                None if st.top_k is None else st.top_k.repeat_interleave(width),
+                None if st.top_p is None else st.top_p.repeat_interleave(width)).float()
+            probs = masked.softmax(-1).view(ns, width, V)
+            greedy_rows = (st.temperature <= 0)
+            if bool(greedy_rows.any()):
+                onehot = torch.zeros_like(probs)
+                onehot.scatter_(-1, logits.view(ns, width, V).argmax(-1, keepdim=True), 1.0)
+                probs = torch.where(greedy_rows[:, None, None], onehot, probs)
+            idx = nd.long().clamp(max=S)
+            bonus_p = probs.gather(1, idx[:, None, None].expand(ns, 1, V)).squeeze(1)
+            bonus = torch.multinomial(bonus_p.clamp_min(0) + 1e-20, 1).squeeze(1)
+            out = self.rejection.random(draft, None, probs[:, :S].contiguous(), bonus, nd)
+        out_ids[:ns * width].copy_(out.reshape(-1))
+
+    def _draft_mtp(self, hidden: torch.Tensor, md: AttentionMetadata, T: int, ns: int,
+                   width: int, out_ids: torch.Tensor) -> None:
+        """Runs the MTP module on this step's tokens (ids shifted by one, the freshly emitted
+        token patched in at the last accepted position) and takes the draft for the next
+        step from the row of the last accepted position."""
+        toks = out_ids[:ns * width].view(ns, width)
+        n_emit = (toks >= 0).sum(dim=1)                       # accepted drafts + 1
+        last_tok = toks.gather(1, (n_emit - 1).clamp(min=0)[:, None]).squeeze(1)
+        rows0 = self.sample_indices[:ns * width].view(ns, width)[:, 0]
+        row = rows0 + (n_emit - 1).clamp(min=0)               # position of the last accepted token
+        ids = self.mtp_ids[:T]
+        ids.index_copy_(0, row, last_tok)
+        h = self.drafter(ids, hidden, md, self.drafter_caches)
+        lg = self.drafter.compute_logits(h.index_select(0, row))
+        self.draft_out[:ns].copy_(lg.float().argmax(-1))
 
     # -- CUDA graphs -----------------------------------------------------------------
     def capture_graphs(self, sizes: Optional[list[int]] = None) -> None:

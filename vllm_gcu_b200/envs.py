@@ -1,0 +1,66 @@
+"""Environment flags, evaluated lazily on attribute access.
+
+Every flag is read as ``VLLM_B200_<NAME>``; the reference's ``VLLM_GCU_<NAME>`` spelling is
+accepted as an alias so existing launch scripts keep working (vllm_gcu/envs.py:4-41).
+"""
+from __future__ import annotations
+
+import os
+from typing import Any, Callable
+
+
+def _get(name: str, default: str | None = None) -> str | None:
+    for prefix in ("VLLM_B200_", "VLLM_GCU_"):
+        v = os.environ.get(prefix + name)
+        if v is not None:
+            return v
+    return default
+
+
+def _flag(name: str, default: str = "0") -> Callable[[], bool]:
+    return lambda: bool(int(_get(name, default)))
+
+
+def _path(name: str) -> Callable[[], str | None]:
+    return lambda: (None if _get(name) is None else os.path.expanduser(_get(name)))
+
+
+environment_variables: dict[str, Callable[[], Any]] = {
+    # Megatron-style sequence parallelism over the TP group (DeepSeek family)
+    "ENABLE_SEQUENCE_PARALLEL": _flag("ENABLE_SEQUENCE_PARALLEL"),
+    # run the sampler with the torch reference on the host (debugging)
+    "SAMPLER_ON_CPU": lambda: int(_get("SAMPLER_ON_CPU", "0")),
+    # dump the allocator history every n engine steps and on exceptions (0 = off)
+    "DUMP_SNAPSHOT_EVERY_N_STEP": lambda: int(
+        os.environ.get("VLLM_DUMP_SNAPSHOT_EVERY_N_STEP", _get("DUMP_SNAPSHOT_EVERY_N_STEP", "0"))),
+    # directory for per-rank stdout/stderr logs (worker_<rank>.log)
+    "RANK_LOG_PATH": _path("RANK_LOG_PATH"),
+    # overlap the shared-expert MLP with the expert dispatch on a side stream
+    "ENABLE_PARALLEL_COMPUTE": _flag("ENABLE_PARALLEL_COMPUTE"),
+    # fused MLA path (RMSNorm + RoPE + cache write in one kernel); on by default here
+    "DEEPSEEK_FUSION": _flag("DEEPSEEK_FUSION", "1"),
+    # cross-check the rejection-sampler kernels against the torch oracle at run time
+    "REJECT_SAMPLER_CHECK": _flag("REJECT_SAMPLER_CHECK"),
+    # synthetic round-robin routing (benchmarking expert-parallel balance)
+    "FORCE_EP_BALANCE": _flag("FORCE_EP_BALANCE"),
+    # comma-separated list of enabled forward hooks (entry-point group vllm_gcu_b200.hooks)
+    "HOOKS": lambda: None if _get("HOOKS") is None else _get("HOOKS").split(","),
+    # JSON file mapping GPUs to NICs for multi-node KV transfer
+    "NET_CONFIG": _path("NET_CONFIG"),
+    # run selected ops through the torch reference and compare ("all" or op1,op2,...)
+    "ORACLE": lambda: None if _get("ORACLE") is None else _get("ORACLE").split(","),
+    # communication backend of the tensor-parallel collectives: fused | nccl
+    "COMM": lambda: _get("COMM", "fused"),
+    "NIXL_ENABLE_FULL_KV_TRANSFER": _flag("NIXL_ENABLE_FULL_KV_TRANSFER"),
+    "NIXL_ENABLE_FIRST_TOKEN_REUSE": _flag("NIXL_ENABLE_FIRST_TOKEN_REUSE"),
+}
+
+
+def __getattr__(name: str):
+    if name in environment_variables:
+        return environment_variables[name]()
+    raise AttributeError(name)
+
+
+def __dir__():
+    return list(environment_variables.keys())
