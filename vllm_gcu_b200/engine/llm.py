@@ -54,6 +54,13 @@ class LLMEngine:
             from ..parallel import symm
             symm.attach(cfg)
         self.runner = ModelRunner(cfg, self.model, self.device)
+        lora_cfg = cfg.additional_config.get("lora")
+        if lora_cfg:
+            from ..lora import LoRAManager
+            self.runner.lora = LoRAManager(self.model, int(lora_cfg.get("max_loras", 4)),
+                                           int(lora_cfg.get("max_lora_rank", 16)),
+                                           self.runner.max_tokens, self.runner.max_seqs,
+                                           self.device)
         self.proposer = None
         self.spec_metrics = None
         sp = cfg.speculative
@@ -119,6 +126,12 @@ class LLMEngine:
 
     def abort_request(self, request_id: str) -> None:
         self.scheduler.abort_request(request_id)
+
+    def add_lora(self, lora_request, tensors=None, config=None) -> int:
+        """Loads a LoRA adapter; requests select it with ``lora_id=lora_request.lora_int_id``."""
+        if self.runner.lora is None:
+            raise RuntimeError("start the engine with enable_lora=True")
+        return self.runner.lora.add_adapter(lora_request, tensors, config)
 
     def has_unfinished(self) -> bool:
         return self.scheduler.has_unfinished() or bool(self._pending)
@@ -197,6 +210,7 @@ class LLM:
                  cuda_graph_sizes: Optional[list[int]] = None,
                  speculative_method: Optional[str] = None, num_speculative_tokens: int = 0,
                  prompt_lookup_max: int = 4, prompt_lookup_min: int = 1,
+                 enable_lora: bool = False, max_loras: int = 4, max_lora_rank: int = 16,
                  additional_config: Optional[dict] = None, **model_overrides):
         model_path = None
         if isinstance(model, ModelConfig):
@@ -211,6 +225,9 @@ class LLM:
         if dtype is not None:
             from ..config import to_dtype
             mc.dtype = to_dtype(dtype)
+        additional_config = dict(additional_config or {})
+        if enable_lora:
+            additional_config["lora"] = {"max_loras": max_loras, "max_lora_rank": max_lora_rank}
         cfg = EngineConfig(
             model=mc,
             cache=CacheConfig(block_size=block_size, gpu_memory_utilization=gpu_memory_utilization,

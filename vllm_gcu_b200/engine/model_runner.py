@@ -102,6 +102,7 @@ class ModelRunner:
         self.max_spec = cfg.speculative.num_speculative_tokens if cfg.speculative.method else 0
         self.rejection = None
         self.drafter = None                        # on-device drafter (DeepSeek MTP)
+        self.lora = None                           # LoRAManager when multi-LoRA is enabled
         self.drafter_caches: list[torch.Tensor] = []
         if self.max_spec:
             from ..spec import RejectionSampler
@@ -308,8 +309,9 @@ class ModelRunner:
         bs = self.block_size
         T_real = nd + sum(s.num_tokens for s in prefills)
 
+        batch_has_lora = self.lora is not None and any(s.req.lora_id >= 0 for s in sched)
         use_graph = (self.is_cuda and npf == 0 and self.graphs and nd <= self.graph_sizes[-1]
-                     and self.drafter is None)
+                     and self.drafter is None and not batch_has_lora)
         B_pad = _pad_batch(nd, self.graph_sizes) if use_graph else B
         T = T_real + (B_pad - B)
 
@@ -373,6 +375,14 @@ class ModelRunner:
             i64[o_slot + T_real:o_slot + T] = -1
             i64[o_ids + T_real:o_ids + T] = 0
             i64[o_pos + T_real:o_pos + T] = 0
+        if self.lora is not None:
+            if batch_has_lora:
+                tok_lora = np.repeat(np.fromiter((s.req.lora_id for s in order), dtype=np.int64,
+                                                 count=B), ntok).tolist()
+                smp_lora = [s.req.lora_id for s in order if s.will_sample]
+                self.lora.set_batch(tok_lora, smp_lora)
+            else:
+                self.lora.punica.no_lora = True
         # sampling rows
         samplers = [j for j, s in enumerate(order) if s.will_sample]
         ns = len(samplers)

@@ -112,6 +112,10 @@ class _Sigs:
     b200_per_tensor_fp8_quant = [P, P, L, P, P, I, P]
     b200_int8_dequant = [P, P, L, P, P, I, P]
     b200_weight_dequant = [P, P, P, P, I, I, I, I, I, P]
+    b200_bgmv = [P, L, P, L, P, P, I, I, I, I, F, I, I, I, P]
+    b200_rejection_greedy = [P, P, P, P, P, I, I, P]
+    b200_rejection_random = [P, P, P, P, P, P, P, P, I, I, I, P]
+    b200_expand_batch_to_tokens = [P, P, P, I, L, L, P]
 
 
 def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
