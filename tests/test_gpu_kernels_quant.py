@@ -118,7 +118,9 @@ def test_weight_dequant_and_quant_linear(C):
                                      quant_method=Q.Fp8LinearMethod(None, False))
         layer.load_weight("weight", w.to(dev))
         res[dev] = layer(x.to(dev)).float().cpu()
-    _close(res["cuda"], res["cpu"], 3e-2, 3e-2)
+    # both sides quantise activations to fp8 independently: one e4m3 step (6 %) apart at most
+    _close(res["cuda"], res["cpu"], 0.1, 0.1)
+    _close(res["cuda"], (x.float() @ w.float().t()), 0.15, 0.15)
     qd, sd = C.per_tensor_fp8_quant(x.cuda())
     qr, sr = ref.dynamic_per_tensor_fp8_quant(x)
     _close(sd.cpu(), sr, 1e-3, 0)

@@ -1,0 +1,359 @@
+"""Multi-process executor: one worker process per GPU, one front-end process.
+
+Every worker hosts a complete engine replica (scheduler + runner) and the replicas advance
+in lock-step: rank 0 decides how many queued commands (new requests, aborts) are applied
+before the next step and broadcasts that count over the gloo group, so all schedulers see
+the same inputs and stay bit-identical while only device collectives cross ranks inside a
+step.  Outputs come from rank 0.
+
+Failure handling (the reference's executor reports worker exceptions as a ``FAILURE``
+message and shuts the system down, vllm_gcu/v1/executor/async_multiproc_executor.py:92-171):
+
+* an exception in any worker is sent to the front end as ``("FAILURE", rank, traceback)``;
+* the front end watches the process sentinels and a per-worker heartbeat; a worker that
+  exits or stops beating marks the executor dead;
+* ``SIGTERM`` / ``SIGINT`` in a worker raise ``SystemExit`` once so ``finally`` blocks run;
+* after a failure every call raises :class:`EngineDeadError` and ``shutdown`` terminates the
+  remaining workers.
+
+``AsyncMultiprocExecutor`` keeps the same process layout and adds an asyncio front end that
+streams per-request outputs (used by the API server).
+"""
+from __future__ import annotations
+
+import asyncio
+import multiprocessing as mp
+import os
+import queue
+import signal
+import socket
+import threading
+import time
+import traceback
+from dataclasses import dataclass, field
+from typing import Any, AsyncIterator, Optional, Sequence
+
+from ..config import EngineConfig
+from .request import RequestOutput, SamplingParams
+
+
+class EngineDeadError(RuntimeError):
+    """A worker failed; the executor cannot make progress any more."""
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@dataclass
+class _Cmd:
+    kind: str                       # add | abort | stop | inject
+    payload: Any = None
+
+
+def _worker_main(rank: int, world: int, port: int, cfg: EngineConfig, cmd_q, out_q, hb,
+                 backend: Optional[str]) -> None:
+    """Entry point of a worker process."""
+    fired = {"v": False}
+
+    def _on_signal(signum, frame):
+        if not fired["v"]:
+            fired["v"] = True
+            raise SystemExit(128 + signum)
+
+    signal.signal(signal.SIGTERM, _on_signal)
+    signal.signal(signal.SIGINT, _on_signal)
+    os.environ.update({"RANK": str(rank), "WORLD_SIZE": str(world), "LOCAL_RANK": str(rank),
+                       "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port)})
+    try:
+        import torch
+        import torch.distributed as dist
+        from ..parallel.state import get_state, init_distributed
+        from ..utils import redirect_rank_output
+        redirect_rank_output(rank)
+        pc = cfg.parallel
+        if world > 1:
+            init_distributed(pc.tensor_parallel_size, pc.pipeline_parallel_size,
+                             pc.data_parallel_size, backend=backend,
+                             enable_ep=pc.enable_expert_parallel)
+        from .llm import LLMEngine
+        engine = LLMEngine(cfg)
+        st = get_state()
+        ctrl = None
+        if world > 1:
+            ctrl = dist.new_group(list(range(world)), backend="gloo")
+        out_q.put(("READY", rank, engine.runner.num_blocks))
+        pending: list[_Cmd] = []
+        stop = False
+        while not stop:
+            hb.value = time.monotonic()
+            # 1) agree on the commands applied before this step
+            if rank == 0:
+                while True:
+                    try:
+                        pending.append(cmd_q.get_nowait())
+                    except queue.Empty:
+                        break
+                if not pending and not engine.has_unfinished():
+                    try:
+                        pending.append(cmd_q.get(timeout=0.05))
+                    except queue.Empty:
+                        pass
+                n = len(pending)
+            else:
+                n = 0
+            if ctrl is not None:
+                t = torch.tensor([n], dtype=torch.int64)
+                dist.broadcast(t, 0, group=ctrl)
+                n = int(t.item())
+                while len(pending) < n:
+                    pending.append(cmd_q.get())
+            batch, pending = pending[:n], pending[n:]
+            for c in batch:
+                if c.kind == "add":
+                    rid, prompt, sp, prio, lora = c.payload
+                    engine.add_request(prompt, sp, request_id=rid, priority=prio, lora_id=lora)
+                elif c.kind == "abort":
+                    engine.abort_request(c.payload)
+                elif c.kind == "stop":
+                    stop = True
+                elif c.kind == "inject":
+                    # host-side fault injection for tests: ("raise" | "exit", rank)
+                    what, target = c.payload
+                    if target == rank:
+                        if what == "raise":
+                            raise RuntimeError("injected worker failure")
+                        if what == "exit":
+                            os._exit(17)
+            if stop:
+                break
+            # 2) one engine step
+            if engine.has_unfinished():
+                outs = engine.step()
+                if rank == 0 and outs:
+                    out_q.put(("OUT", outs))
+        out_q.put(("STOPPED", rank, None))
+    except SystemExit:
+        raise
+    except BaseException:  # noqa: BLE001 - everything is reported to the front end
+        try:
+            out_q.put(("FAILURE", rank, traceback.format_exc()))
+            out_q.close()
+            out_q.join_thread()          # flush the message before the process goes away
+        finally:
+            os._exit(1)
+
+
+class MultiprocExecutor:
+    HEARTBEAT_TIMEOUT_S = 120.0
+
+    def __init__(self, cfg: EngineConfig, backend: Optional[str] = None,
+                 start_timeout_s: float = 600.0):
+        self.cfg = cfg
+        self.world = cfg.parallel.world_size
+        ctx = mp.get_context("spawn")
+        self.out_q = ctx.Queue()
+        self.cmd_qs = [ctx.Queue() for _ in range(self.world)]
+        self.hbs = [ctx.Value("d", time.monotonic()) for _ in range(self.world)]
+        port = _free_port()
+        self.procs = [ctx.Process(target=_worker_main, daemon=True,
+                                  args=(r, self.world, port, cfg, self.cmd_qs[r], self.out_q,
+                                        self.hbs[r], backend))
+                      for r in range(self.world)]
+        for p in self.procs:
+            p.start()
+        self.dead: Optional[str] = None
+        self._lock = threading.Lock()
+        self._ids = 0
+        ready = 0
+        deadline = time.monotonic() + start_timeout_s
+        while ready < self.world:
+            msg = self._get(max(0.1, deadline - time.monotonic()))
+            if msg is None:
+                self._fail("worker start-up timed out")
+            if msg[0] == "READY":
+                ready += 1
+            elif msg[0] == "FAILURE":
+                self._fail(f"worker {msg[1]} failed during start-up:\n{msg[2]}")
+
+    # -- plumbing ------------------------------------------------------------------
+    def _get(self, timeout: float):
+        """Next message from the workers, or None; checks worker liveness while waiting."""
+        end = time.monotonic() + timeout
+        while True:
+            try:
+                return self.out_q.get(timeout=0.05)
+            except queue.Empty:
+                pass
+            self.check_health()
+            if time.monotonic() >= end:
+                return None
+
+    def _fail(self, why: str) -> None:
+        self.dead = why
+        self.shutdown()
+        raise EngineDeadError(why)
+
+    def check_health(self) -> None:
+        if self.dead:
+            raise EngineDeadError(self.dead)
+        now = time.monotonic()
+        for r, p in enumerate(self.procs):
+            if not p.is_alive() and p.exitcode not in (0, None):
+                # drain a FAILURE message if the worker managed to send one
+                detail = ""
+                try:
+                    while True:
+                        m = self.out_q.get_nowait()
+                        if m[0] == "FAILURE":
+                            detail = "\n" + m[2]
+                            break
+                except queue.Empty:
+                    pass
+                self._fail(f"worker {r} exited with code {p.exitcode}{detail}")
+            if p.is_alive() and now - self.hbs[r].value > self.HEARTBEAT_TIMEOUT_S:
+                self._fail(f"worker {r} stopped responding")
+
+    def _broadcast(self, cmd: _Cmd) -> None:
+        if self.dead:
+            raise EngineDeadError(self.dead)
+        with self._lock:
+            for q in self.cmd_qs:
+                q.put(cmd)
+
+    # -- API -----------------------------------------------------------------------
+    def add_request(self, prompt_token_ids: Sequence[int],
+                    sampling_params: Optional[SamplingParams] = None,
+                    request_id: Optional[str] = None, priority: int = 0, lora_id: int = -1) -> str:
+        if request_id is None:
+            request_id = f"req-{self._ids}"
+            self._ids += 1
+        self._broadcast(_Cmd("add", (request_id, list(prompt_token_ids),
+                                     sampling_params or SamplingParams(), priority, lora_id)))
+        return request_id
+
+    def abort_request(self, request_id: str) -> None:
+        self._broadcast(_Cmd("abort", request_id))
+
+    def inject_fault(self, what: str, rank: int) -> None:
+        """Test hook: make worker ``rank`` raise an exception or exit at its next step."""
+        self._broadcast(_Cmd("inject", (what, rank)))
+
+    def poll(self, timeout: float = 0.1) -> list[RequestOutput]:
+        """Outputs produced since the last call (blocks up to ``timeout`` for the first)."""
+        outs: list[RequestOutput] = []
+        msg = self._get(timeout)
+        while msg is not None:
+            if msg[0] == "OUT":
+                outs.extend(msg[1])
+            elif msg[0] == "FAILURE":
+                self._fail(f"worker {msg[1]} failed:\n{msg[2]}")
+            try:
+                msg = self.out_q.get_nowait()
+            except queue.Empty:
+                msg = None
+        return outs
+
+    def generate(self, prompts, sampling_params=None, timeout_s: float = 600.0
+                 ) -> list[RequestOutput]:
+        prompts = list(prompts)
+        if sampling_params is None or isinstance(sampling_params, SamplingParams):
+            sps = [sampling_params or SamplingParams()] * len(prompts)
+        else:
+            sps = list(sampling_params)
+        ids = [self.add_request(p, sp) for p, sp in zip(prompts, sps)]
+        final: dict[str, RequestOutput] = {}
+        deadline = time.monotonic() + timeout_s
+        while len(final) < len(ids):
+            for o in self.poll(0.2):
+                if o.finished:
+                    final[o.request_id] = o
+            if time.monotonic() > deadline:
+                self._fail("generate() timed out")
+        return [final[i] for i in ids]
+
+    def shutdown(self) -> None:
+        for q in self.cmd_qs:
+            try:
+                q.put(_Cmd("stop"))
+            except Exception:
+                pass
+        t_end = time.monotonic() + 5.0
+        for p in self.procs:
+            p.join(max(0.0, t_end - time.monotonic()))
+        for p in self.procs:
+            if p.is_alive():
+                p.terminate()
+        for p in self.procs:
+            p.join(2.0)
+            if p.is_alive():
+                p.kill()
+
+    def __del__(self):
+        try:
+            self.shutdown()
+        except Exception:
+            pass
+
+
+class AsyncMultiprocExecutor(MultiprocExecutor):
+    """asyncio front end: ``generate_stream`` yields the outputs of one request as they are
+    produced while other requests run concurrently; a background thread pumps ``poll``."""
+
+    def __init__(self, *a, **kw):
+        super().__init__(*a, **kw)
+        self._streams: dict[str, asyncio.Queue] = {}
+        self._loop: Optional[asyncio.AbstractEventLoop] = None
+        self._pump: Optional[threading.Thread] = None
+        self._stop_pump = threading.Event()
+
+    def _ensure_pump(self) -> None:
+        if self._pump is not None:
+            return
+        self._loop = asyncio.get_running_loop()
+
+        def run():
+            while not self._stop_pump.is_set():
+                try:
+                    outs = self.poll(0.05)
+                except EngineDeadError as e:
+                    for q in list(self._streams.values()):
+                        self._loop.call_soon_threadsafe(q.put_nowait, e)
+                    return
+                for o in outs:
+                    q = self._streams.get(o.request_id)
+                    if q is not None:
+                        self._loop.call_soon_threadsafe(q.put_nowait, o)
+
+        self._pump = threading.Thread(target=run, daemon=True)
+        self._pump.start()
+
+    async def generate_stream(self, prompt_token_ids: Sequence[int],
+                              sampling_params: Optional[SamplingParams] = None,
+                              request_id: Optional[str] = None, priority: int = 0
+                              ) -> AsyncIterator[RequestOutput]:
+        self._ensure_pump()
+        q: asyncio.Queue = asyncio.Queue()
+        rid = request_id or f"areq-{self._ids}"
+        self._ids += 1
+        self._streams[rid] = q
+        self.add_request(prompt_token_ids, sampling_params, rid, priority)
+        try:
+            while True:
+                item = await q.get()
+                if isinstance(item, Exception):
+                    raise item
+                yield item
+                if item.finished:
+                    break
+        except asyncio.CancelledError:
+            self.abort_request(rid)
+            raise
+        finally:
+            self._streams.pop(rid, None)
+
+    def shutdown(self) -> None:
+        self._stop_pump.set()
+        super().shutdown()

@@ -1,0 +1,240 @@
+"""Minimal OpenAI-compatible completion server on the built-in engine.
+
+Endpoints: ``POST /v1/completions`` (``prompt`` as a list of token ids, a list of such lists,
+or a string tokenised byte-wise when no tokenizer directory is given; ``stream`` for server
+sent events; per-request ``extra_args`` are forwarded into the sampling parameters, which is
+how the router marks keep-alive requests, vllm_gcu/patch/patch_0_9_2/entrypoints.py:7-68),
+``GET /v1/models``, ``GET /health``, ``GET /metrics`` (Prometheus text),
+``POST /start_profile`` / ``POST /stop_profile`` (torch profiler, as used by the reference's
+benchmark tools, benchmarks/benchmark_test.py:352-353).
+
+Run: ``python -m vllm_gcu_b200.entrypoints.api_server --model llama-3-8b --port 8000``
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import time
+import uuid
+from typing import Any, Optional
+
+from ..config import (CacheConfig, EngineConfig, ModelConfig, ParallelConfig, SchedulerConfig,
+                      preset)
+from ..engine.request import SamplingParams
+
+try:        # module level so that FastAPI can resolve the handler annotations
+    from fastapi import FastAPI, Request
+    from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
+except Exception:   # pragma: no cover - the server needs fastapi, the helpers do not
+    FastAPI = Request = JSONResponse = PlainTextResponse = StreamingResponse = None
+
+
+class ByteTokenizer:
+    """Fallback when no tokenizer files are available: UTF-8 bytes offset into the vocabulary."""
+
+    def __init__(self, vocab_size: int):
+        self.vocab_size = vocab_size
+
+    def encode(self, text: str) -> list[int]:
+        return [3 + b for b in text.encode("utf-8")] or [3]
+
+    def decode(self, ids: list[int]) -> str:
+        return bytes((i - 3) % 256 for i in ids).decode("utf-8", errors="replace")
+
+
+def load_tokenizer(path: Optional[str], vocab_size: int):
+    if path:
+        try:
+            from transformers import AutoTokenizer
+            return AutoTokenizer.from_pretrained(path)
+        except Exception:
+            pass
+    return ByteTokenizer(vocab_size)
+
+
+def sampling_from_body(body: dict, default_max: int = 16) -> SamplingParams:
+    extra = dict(body.get("extra_args") or {})
+    stop_ids = tuple(body.get("stop_token_ids") or ())
+    return SamplingParams(
+        max_tokens=int(body.get("max_tokens", default_max)),
+        min_tokens=int(body.get("min_tokens", 0)),
+        temperature=float(body.get("temperature", 1.0)),
+        top_k=int(body.get("top_k", 0) or 0), top_p=float(body.get("top_p", 1.0)),
+        presence_penalty=float(body.get("presence_penalty", 0.0)),
+        frequency_penalty=float(body.get("frequency_penalty", 0.0)),
+        repetition_penalty=float(body.get("repetition_penalty", 1.0)),
+        seed=body.get("seed"), ignore_eos=bool(body.get("ignore_eos", False)),
+        stop_token_ids=stop_ids, logprobs=body.get("logprobs"), extra_args=extra)
+
+
+def build_app(engine: Any, tokenizer: Any, model_name: str):
+    if FastAPI is None:
+        raise RuntimeError("the API server needs the fastapi package")
+    app = FastAPI()
+    state = {"profiler": None, "requests": 0, "tokens_out": 0, "t0": time.time()}
+
+    def to_ids(p) -> list[int]:
+        if isinstance(p, str):
+            return list(tokenizer.encode(p))
+        return [int(t) for t in p]
+
+    @app.get("/health")
+    async def health():
+        err = getattr(engine, "error", None) or getattr(engine, "dead", None)
+        if err:
+            return JSONResponse({"status": "dead", "detail": str(err)}, status_code=503)
+        return {"status": "ok"}
+
+    @app.get("/v1/models")
+    async def models():
+        return {"object": "list", "data": [{"id": model_name, "object": "model"}]}
+
+    @app.get("/metrics")
+    async def metrics():
+        lines = [f"vllm_b200_requests_total {state['requests']}",
+                 f"vllm_b200_generation_tokens_total {state['tokens_out']}"]
+        st = engine.stats() if hasattr(engine, "stats") else {}
+        for k, v in st.items():
+            try:
+                lines.append(f"vllm_b200_{k} {float(v)}")
+            except (TypeError, ValueError):
+                pass
+        return PlainTextResponse("\n".join(lines) + "\n")
+
+    @app.post("/start_profile")
+    async def start_profile():
+        import torch
+        if state["profiler"] is None:
+            acts = [torch.profiler.ProfilerActivity.CPU]
+            if torch.cuda.is_available():
+                acts.append(torch.profiler.ProfilerActivity.CUDA)
+            state["profiler"] = torch.profiler.profile(activities=acts)
+            state["profiler"].__enter__()
+        return {"status": "started"}
+
+    @app.post("/stop_profile")
+    async def stop_profile():
+        prof = state["profiler"]
+        if prof is not None:
+            prof.__exit__(None, None, None)
+            path = f"/tmp/vllm_b200_trace_{int(time.time())}.json"
+            prof.export_chrome_trace(path)
+            state["profiler"] = None
+            return {"status": "stopped", "trace": path}
+        return {"status": "idle"}
+
+    @app.post("/v1/completions")
+    async def completions(request: Request):
+        body = await request.json()
+        prompt = body.get("prompt")
+        if prompt is None:
+            return JSONResponse({"error": "prompt is required"}, status_code=400)
+        batch = prompt if (isinstance(prompt, list) and prompt and
+                           isinstance(prompt[0], (list, str))) else [prompt]
+        sp = sampling_from_body(body)
+        rid = "cmpl-" + uuid.uuid4().hex[:16]
+        created = int(time.time())
+        state["requests"] += len(batch)
+        priority = int(body.get("priority", 0))
+
+        def chunk(idx: int, toks: list[int], finish: Optional[str]) -> dict:
+            return {"id": rid, "object": "text_completion", "created": created,
+                    "model": model_name,
+                    "choices": [{"index": idx, "text": tokenizer.decode(toks),
+                                 "token_ids": toks, "finish_reason": finish}]}
+
+        if body.get("stream", False):
+            async def sse():
+                ids = to_ids(batch[0])
+                sent = 0
+                async for out in engine.generate_stream(ids, sp, priority=priority):
+                    toks = out.outputs[0].token_ids
+                    new = toks[sent:]
+                    sent = len(toks)
+                    state["tokens_out"] += len(new)
+                    yield "data: " + json.dumps(chunk(0, new, out.outputs[0].finish_reason)) + "\n\n"
+                yield "data: [DONE]\n\n"
+            return StreamingResponse(sse(), media_type="text/event-stream")
+
+        import asyncio
+
+        async def one(idx: int, p) -> dict:
+            ids = to_ids(p)
+            last = None
+            async for out in engine.generate_stream(ids, sp, priority=priority):
+                last = out
+            toks = last.outputs[0].token_ids
+            state["tokens_out"] += len(toks)
+            c = chunk(idx, toks, last.outputs[0].finish_reason)["choices"][0]
+            c["prompt_tokens"] = len(ids)
+            return c
+
+        choices = await asyncio.gather(*[one(i, p) for i, p in enumerate(batch)])
+        usage = {"prompt_tokens": sum(c.pop("prompt_tokens") for c in choices),
+                 "completion_tokens": sum(len(c["token_ids"]) for c in choices)}
+        usage["total_tokens"] = usage["prompt_tokens"] + usage["completion_tokens"]
+        return {"id": rid, "object": "text_completion", "created": created, "model": model_name,
+                "choices": list(choices), "usage": usage}
+
+    return app
+
+
+def make_engine(args) -> tuple[Any, ModelConfig]:
+    import os
+    overrides = {}
+    if args.num_hidden_layers:
+        overrides["num_hidden_layers"] = args.num_hidden_layers
+    if os.path.isdir(args.model):
+        mc = ModelConfig.from_pretrained(args.model, **overrides)
+        path, fmt = args.model, "safetensors"
+    else:
+        mc = preset(args.model, **overrides)
+        path, fmt = None, "dummy"
+    cfg = EngineConfig(
+        model=mc,
+        cache=CacheConfig(block_size=args.block_size,
+                          gpu_memory_utilization=args.gpu_memory_utilization,
+                          num_gpu_blocks=args.num_gpu_blocks),
+        scheduler=SchedulerConfig(max_num_seqs=args.max_num_seqs,
+                                  max_num_batched_tokens=args.max_num_batched_tokens,
+                                  max_model_len=args.max_model_len or mc.max_position_embeddings,
+                                  policy=args.scheduling_policy,
+                                  async_scheduling=not args.no_async_scheduling),
+        parallel=ParallelConfig(tensor_parallel_size=args.tensor_parallel_size),
+        device=args.device, enforce_eager=args.enforce_eager, load_format=fmt, model_path=path)
+    if args.tensor_parallel_size > 1:
+        from ..engine.executor import AsyncMultiprocExecutor
+        return AsyncMultiprocExecutor(cfg), mc
+    from ..engine.async_llm import AsyncLLM
+    return AsyncLLM(cfg), mc
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__)
+    ap.add_argument("--model", default="llama-3-8b")
+    ap.add_argument("--tokenizer", default=None)
+    ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--port", type=int, default=8000)
+    ap.add_argument("--tensor-parallel-size", type=int, default=1)
+    ap.add_argument("--max-num-seqs", type=int, default=256)
+    ap.add_argument("--max-num-batched-tokens", type=int, default=8192)
+    ap.add_argument("--max-model-len", type=int, default=0)
+    ap.add_argument("--block-size", type=int, default=16)
+    ap.add_argument("--gpu-memory-utilization", type=float, default=0.9)
+    ap.add_argument("--num-gpu-blocks", type=int, default=None)
+    ap.add_argument("--scheduling-policy", default="fcfs", choices=["fcfs", "priority"])
+    ap.add_argument("--no-async-scheduling", action="store_true")
+    ap.add_argument("--enforce-eager", action="store_true")
+    ap.add_argument("--device", default="auto")
+    ap.add_argument("--num-hidden-layers", type=int, default=0)
+    args = ap.parse_args()
+    engine, mc = make_engine(args)
+    tok = load_tokenizer(args.tokenizer or (args.model if "/" in args.model else None),
+                         mc.vocab_size)
+    import uvicorn
+    uvicorn.run(build_app(engine, tok, args.model), host=args.host, port=args.port,
+                log_level="warning")
+
+
+if __name__ == "__main__":
+    main()

@@ -59,8 +59,11 @@ class Communicator:
         if self.world_size == 1:
             return x
         ws = self.world_size
-        out = torch.empty((ws,) + tuple(x.shape), dtype=x.dtype, device=x.device)
-        dist.all_gather_into_tensor(out, x.contiguous(), group=self.group.device_group)
+        xc = x.contiguous()
+        flat = torch.empty((ws * xc.shape[0],) + tuple(xc.shape[1:]), dtype=x.dtype,
+                           device=x.device)
+        dist.all_gather_into_tensor(flat, xc, group=self.group.device_group)
+        out = flat.view((ws,) + tuple(xc.shape))
         dim = dim % x.dim()
         out = out.movedim(0, dim)
         return out.reshape(x.shape[:dim] + (ws * x.shape[dim],) + x.shape[dim + 1:])
