@@ -1,0 +1,102 @@
+"""Collective semantics on CPU ranks (gloo, world size 2 and 3): uneven scatter,
+reduce-scatter-v / all-gather-v, sequence-parallel round trip, all-to-all-v and the
+expert-parallel dispatch / combine against the single-process reference."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, fn_name):
+    sys.path.insert(0, ROOT)
+    os.environ.update({"RANK": str(rank), "WORLD_SIZE": str(world), "LOCAL_RANK": str(rank),
+                       "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port)})
+    from vllm_gcu_b200.parallel.state import init_distributed
+    init_distributed(tp=world, backend="gloo", enable_ep=True)
+    globals()[fn_name](rank, world)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _spawn(fn_name, world):
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_worker, args=(world, port, fn_name), nprocs=world, join=True)
+
+
+def _check_sp(rank, world):
+    from vllm_gcu_b200.parallel import sp
+    from vllm_gcu_b200.parallel.communicator import get_comm, scatter_sizes
+    for T in (7, 8, 1, 0):
+        sizes = scatter_sizes(T, world)
+        assert sum(sizes) == T and sizes == sorted(sizes)
+        g = torch.Generator().manual_seed(T)
+        full = [torch.randn(T, 5, generator=g) for _ in range(world)]
+        mine = full[rank]
+        red = sp.tp_to_sp(mine.clone())
+        want = sum(full)
+        start = sum(sizes[:rank])
+        assert torch.allclose(red, want[start:start + sizes[rank]], atol=1e-6)
+        back = sp.sp_to_tp(red, T)
+        assert torch.allclose(back, want, atol=1e-6)
+        assert torch.equal(sp.slice_tensor_sp(want), want[start:start + sizes[rank]])
+    comm = get_comm("tp")
+    x = torch.full((rank + 1, 2), float(rank))
+    send = [1] * min(world, rank + 1) + [0] * max(0, world - rank - 1)
+    send[0] += rank + 1 - sum(send)
+    recv = []
+    for r in range(world):
+        s_r = [1] * min(world, r + 1) + [0] * max(0, world - r - 1)
+        s_r[0] += r + 1 - sum(s_r)
+        recv.append(s_r[rank])
+    out = comm.all_to_all_v(x, send, recv)
+    assert out.shape[0] == sum(recv)
+
+
+def _check_ep(rank, world):
+    from vllm_gcu_b200.config import preset
+    from vllm_gcu_b200.layers.moe import SparseMoeBlock
+    from vllm_gcu_b200.ops import ref
+    cfg = preset("tiny-qwen3-moe", num_experts=6 if world == 3 else 8, num_experts_per_tok=2)
+    cfg.extra["dp_attention"] = True
+    torch.manual_seed(0)
+    blk = SparseMoeBlock(cfg, "cpu", "m")
+    E, I, H = cfg.num_experts, cfg.moe_intermediate_size, cfg.hidden_size
+    g = torch.Generator().manual_seed(1)
+    w13 = torch.randn(E, 2 * I, H, generator=g) * 0.05
+    w2 = torch.randn(E, H, I, generator=g) * 0.05
+    gate = torch.randn(E, H, generator=g) * 0.5
+    blk.gate.weight.data.copy_(gate)
+    for e in range(E):
+        blk.experts.load_expert_weight(e, "gate", w13[e, :I])
+        blk.experts.load_expert_weight(e, "up", w13[e, I:])
+        blk.experts.load_expert_weight(e, "down", w2[e])
+    # every rank owns different tokens (data-parallel attention); rank 1 is idle (T = 0)
+    T = 0 if rank == 1 else 5 + rank
+    xg = torch.Generator().manual_seed(10 + rank)
+    x = torch.randn(T, H, generator=xg)
+    got = blk(x)
+    logits = x @ gate.t()
+    w, ids = ref.topk_softmax(logits, 2, True) if T else (torch.zeros(0, 2), torch.zeros(0, 2, dtype=torch.int32))
+    want = ref.fused_experts(x, w13, w2, w, ids) if T else x
+    assert got.shape == x.shape
+    assert torch.allclose(got, want, atol=1e-5, rtol=1e-4), (got - want).abs().max()
+
+
+@pytest.mark.timeout(300)
+@pytest.mark.parametrize("world", [2, 3])
+def test_sequence_parallel_and_collectives(world):
+    _spawn("_check_sp", world)
+
+
+@pytest.mark.timeout(300)
+@pytest.mark.parametrize("world", [2, 3])
+def test_expert_parallel_dispatch_combine(world):
+    _spawn("_check_ep", world)

@@ -90,10 +90,18 @@ class Communicator:
             lst = [torch.zeros_like(t) for _ in range(self.world_size)]
             dist.all_gather(lst, t, group=self.group.cpu_group or self.group.device_group)
             sizes = [int(v) for v in lst]
-        outs = [torch.empty((s,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
-                for s in sizes]
-        dist.all_gather(outs, x.contiguous(), group=self.group.device_group)
-        return torch.cat(outs, dim=0)
+        sizes = [int(v) for v in sizes]
+        m = max(sizes)
+        if m == 0:
+            return x.new_zeros((0,) + tuple(x.shape[1:]))
+        # pad every contribution to the largest one, gather, then drop the padding
+        pad = torch.zeros((m,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        pad[: x.shape[0]] = x
+        flat = torch.empty((self.world_size * m,) + tuple(x.shape[1:]), dtype=x.dtype,
+                           device=x.device)
+        dist.all_gather_into_tensor(flat, pad, group=self.group.device_group)
+        parts = flat.view((self.world_size, m) + tuple(x.shape[1:]))
+        return torch.cat([parts[r, : sizes[r]] for r in range(self.world_size)], dim=0)
 
     def reduce_scatter_v(self, x: torch.Tensor, sizes: Optional[Sequence[int]] = None
                          ) -> torch.Tensor:
@@ -103,10 +111,25 @@ class Communicator:
         if self.world_size == 1:
             return x
         sizes = list(sizes) if sizes is not None else scatter_sizes(x.shape[0], self.world_size)
-        chunks = list(torch.split(x.contiguous(), sizes, dim=0))
-        out = torch.empty_like(chunks[self.rank])
-        dist.reduce_scatter(out, chunks, group=self.group.device_group)
-        return out
+        start = sum(sizes[: self.rank])
+        if dist.get_backend(self.group.device_group) == "gloo":
+            # gloo has no reduce-scatter: reduce everything, keep the own rows
+            y = x.contiguous().clone()
+            dist.all_reduce(y, group=self.group.device_group)
+            return y[start:start + sizes[self.rank]].contiguous()
+        m = max(sizes)
+        if m == 0:
+            return x.new_zeros((0,) + tuple(x.shape[1:]))
+        padded = torch.zeros((self.world_size, m) + tuple(x.shape[1:]), dtype=x.dtype,
+                             device=x.device)
+        off = 0
+        for r, n in enumerate(sizes):
+            padded[r, :n] = x[off:off + n]
+            off += n
+        out = torch.empty((m,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.reduce_scatter_tensor(out, padded.view((self.world_size * m,) + tuple(x.shape[1:])),
+                                   group=self.group.device_group)
+        return out[: sizes[self.rank]]
 
     def all_to_all_v(self, x: torch.Tensor, send_sizes: Sequence[int],
                      recv_sizes: Sequence[int]) -> torch.Tensor:
