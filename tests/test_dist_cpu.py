@@ -100,3 +100,48 @@ def test_sequence_parallel_and_collectives(world):
 @pytest.mark.parametrize("world", [2, 3])
 def test_expert_parallel_dispatch_combine(world):
     _spawn("_check_ep", world)
+
+
+def _check_pp(rank, world):
+    """Pipeline parallel engine (2 stages) must reproduce the single-stage tokens."""
+    from vllm_gcu_b200.engine.llm import LLM
+    from vllm_gcu_b200.engine.request import SamplingParams
+    g = torch.Generator().manual_seed(9)
+    prompts = [torch.randint(0, 32000, (n,), generator=g).tolist() for n in (21, 40, 6)]
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    llm = LLM("tiny-llama", device="cpu", pipeline_parallel_size=world, max_num_seqs=4,
+              max_num_batched_tokens=32, max_model_len=128, num_gpu_blocks=32)
+    got = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    want = torch.load(os.environ["PP_EXPECT"])
+    assert got == want, (got, want)
+
+
+def _worker_pp(rank, world, port, fn_name):
+    sys.path.insert(0, ROOT)
+    os.environ.update({"RANK": str(rank), "WORLD_SIZE": str(world), "LOCAL_RANK": str(rank),
+                       "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port)})
+    from vllm_gcu_b200.parallel.state import init_distributed
+    init_distributed(tp=1, pp=world, backend="gloo")
+    globals()[fn_name](rank, world)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_pipeline_parallel_matches_single_stage(tmp_path):
+    from vllm_gcu_b200.engine.llm import LLM
+    from vllm_gcu_b200.engine.request import SamplingParams
+    g = torch.Generator().manual_seed(9)
+    prompts = [torch.randint(0, 32000, (n,), generator=g).tolist() for n in (21, 40, 6)]
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    llm = LLM("tiny-llama", device="cpu", max_num_seqs=4, max_num_batched_tokens=32,
+              max_model_len=128, num_gpu_blocks=32)
+    want = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    path = str(tmp_path / "expect.pt")
+    torch.save(want, path)
+    os.environ["PP_EXPECT"] = path
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_worker_pp, args=(2, port, "_check_pp"), nprocs=2, join=True)

@@ -518,8 +518,32 @@ class ModelRunner:
 
     def _forward_and_sample(self, md: AttentionMetadata, T: int, ns: int, out_ids: torch.Tensor,
                             all_greedy: bool, width: int = 1) -> None:
-        hidden = self.model(self.input_ids[:T], md, self.kv_caches)
-        if not self.model.is_last_stage or ns == 0:
+        from ..parallel.state import get_state
+        pp = get_state().pp
+        inter = None
+        if pp.world_size > 1 and not self.model.is_first_stage:
+            # pipeline hand-off: (hidden, residual) of the previous stage over NCCL p2p
+            # (vllm_gcu/worker/worker_v1.py:341-360)
+            import torch.distributed as dist
+            H = self.cfg.model.hidden_size
+            x = torch.empty((T, H), dtype=self.cfg.model.dtype, device=self.device)
+            r = torch.empty_like(x)
+            src = pp.ranks[pp.rank_in_group - 1]
+            dist.recv(x, src, group=pp.device_group)
+            dist.recv(r, src, group=pp.device_group)
+            inter = (x, r)
+        hidden = self.model(self.input_ids[:T], md, self.kv_caches, intermediate=inter)
+        if pp.world_size > 1:
+            import torch.distributed as dist
+            last = pp.ranks[-1]
+            if not self.model.is_last_stage:
+                dst = pp.ranks[pp.rank_in_group + 1]
+                dist.send(hidden[0].contiguous(), dst, group=pp.device_group)
+                dist.send(hidden[1].contiguous(), dst, group=pp.device_group)
+                if ns:      # every stage needs the sampled ids (stop checks, next inputs)
+                    dist.broadcast(out_ids[:ns * width], last, group=pp.device_group)
+                return
+        if ns == 0:
             return
         if md.num_prefills == 0 and width == 1:
             rows = hidden[:ns]          # decode-only: row i is the i-th sampling request
@@ -536,6 +560,9 @@ class ModelRunner:
             self._verify(logits, st, ns, width, out_ids)
         if self.drafter is not None:
             self._draft_mtp(hidden, md, T, ns, width, out_ids)
+        if pp.world_size > 1:
+            import torch.distributed as dist
+            dist.broadcast(out_ids[:ns * width], pp.ranks[-1], group=pp.device_group)
 
     def _verify(self, logits: torch.Tensor, st: Optional[SamplingTensors], ns: int, width: int,
                 out_ids: torch.Tensor) -> None:
