@@ -1,0 +1,106 @@
+"""KV-transfer components on CPU: LMCache ops against index arithmetic, the pinned pool and
+the point-to-point connector (PUT / PUT_ASYNC / GET, spill, NACK, missing tensor)."""
+import torch
+
+from vllm_gcu_b200.ops import ref
+from vllm_gcu_b200.parallel.kv_transfer import P2PKVConnector, TensorMemoryPool, lmcache_ops
+
+
+def test_multi_and_single_layer_transfer_roundtrip():
+    torch.manual_seed(0)
+    L, slots, W, T = 3, 40, 16, 9
+    layers = [torch.randn(2, slots, W) for _ in range(L)]
+    sm = torch.randperm(slots)[:T]
+    sm[2] = -1
+    buf = torch.zeros(2, L, T, W)
+    lmcache_ops.multi_layer_kv_transfer(buf, torch.zeros(L, dtype=torch.int64), sm, "cpu", slots,
+                                        True, False, layers=layers)
+    for l in range(L):
+        for t in range(T):
+            if sm[t] >= 0:
+                assert torch.equal(buf[0, l, t], layers[l][0, sm[t]])
+                assert torch.equal(buf[1, l, t], layers[l][1, sm[t]])
+    fresh = [torch.zeros(2, slots, W) for _ in range(L)]
+    lmcache_ops.multi_layer_kv_transfer(buf, torch.zeros(L, dtype=torch.int64), sm, "cpu", slots,
+                                        False, False, layers=fresh)
+    for l in range(L):
+        v = sm[sm >= 0]
+        assert torch.equal(fresh[l][:, v], layers[l][:, v])
+    one = torch.zeros(T, 2, W)
+    lmcache_ops.single_layer_kv_transfer(one, layers[1][0], layers[1][1], sm, True, True)
+    assert torch.equal(one[0, 1], layers[1][1, sm[0]])
+
+
+def test_rerotation_equals_fresh_rotation():
+    torch.manual_seed(1)
+    T, H, D = 6, 2, 32
+    cs = ref.make_cos_sin_cache(D, 128)
+    k = torch.randn(T, H * D)
+    old = torch.randint(0, 60, (T,))
+    new = old + torch.randint(0, 60, (T,))
+    for neox in (True, False):
+        _, k_old = ref.rotary_embedding(old, k.clone(), k.clone(), D, cs, neox)
+        _, k_new = ref.rotary_embedding(new, k.clone(), k.clone(), D, cs, neox)
+        moved = k_old.clone()
+        lmcache_ops.rotary_embedding_k_fused(old, new, moved, D, cs, neox)
+        assert torch.allclose(moved, k_new, atol=1e-4)
+
+
+def test_cachegen_cdf():
+    x = torch.randint(0, 8, (2, 50, 5), dtype=torch.int8)
+    cdf = lmcache_ops.calculate_cdf(x, 8)
+    assert cdf.shape == (2, 5, 9)
+    c = cdf.to(torch.int32) & 0xFFFF
+    assert (c[..., 0] == 0).all() and (c[..., -1] == 65535).all()
+    assert (c[..., 1:] >= c[..., :-1]).all()
+
+
+def test_memory_pool_reuse():
+    pool = TensorMemoryPool(4096, pin=False)
+    a = pool.store(torch.arange(256, dtype=torch.float32))
+    b = pool.store(torch.ones(256, dtype=torch.float32))
+    assert a is not None and b is not None and a != b
+    assert pool.store(torch.zeros(1024, dtype=torch.float32)) is None
+    assert torch.equal(pool.load(a, (256,), torch.float32, "cpu"),
+                       torch.arange(256, dtype=torch.float32))
+    pool.release(a)
+    pool.release(b)
+    assert pool.store(torch.zeros(1000, dtype=torch.float32)) is not None
+
+
+def test_p2p_connector_put_spill_nack_get():
+    prod = P2PKVConnector(send_type="PUT", mem_pool_size=0)
+    cons = P2PKVConnector(send_type="PUT", kv_buffer_size=1024, mem_pool_size=2048)
+    try:
+        t1 = torch.randn(4, 32)                       # 512 B: fits the device budget
+        t2 = torch.randn(8, 32)                       # 1 KiB: spills to the pinned pool
+        t3 = torch.randn(64, 32)                      # 8 KiB: nowhere to go -> NACK
+        assert prod.send_tensor("r1#l0", t1, cons.addr)
+        assert prod.send_tensor("r1#l1", t2, cons.addr)
+        assert not prod.send_tensor("r1#l2", t3, cons.addr)
+        assert torch.equal(cons.recv_tensor("r1#l0"), t1)
+        assert torch.equal(cons.recv_tensor("r1#l1"), t2)
+        assert cons.recv_tensor("r1#l2", timeout_s=0.2) is None   # consumer recomputes
+        assert cons.stats["spilled"] == 1 and prod.stats["nack"] == 1
+    finally:
+        prod.close()
+        cons.close()
+    p2 = P2PKVConnector(send_type="GET")
+    c2 = P2PKVConnector(send_type="GET")
+    try:
+        t = torch.randn(3, 7)
+        p2.send_tensor("r9#l0", t, c2.addr)
+        assert torch.equal(c2.recv_tensor("r9#l0", remote=p2.addr), t)
+        assert c2.recv_tensor("missing#l0", remote=p2.addr) is None
+    finally:
+        p2.close()
+        c2.close()
+    pa = P2PKVConnector(send_type="PUT_ASYNC")
+    ca = P2PKVConnector(send_type="PUT")
+    try:
+        t = torch.randn(5, 5)
+        assert pa.send_tensor("ra#l0", t, ca.addr)
+        assert torch.equal(ca.recv_tensor("ra#l0", timeout_s=10), t)
+    finally:
+        pa.close()
+        ca.close()
