@@ -156,6 +156,19 @@ class Scheduler:
             if (head.priority, head.arrival_time) > best_running:
                 allow_waiting = False       # the low-priority prefill stays in `waiting`
 
+        # Priority policy: a waiting request that outranks running ones takes their blocks
+        # when the cache cannot hold its first chunk.
+        if self.priority and self.waiting and allow_waiting:
+            head = self.waiting[0]
+            first = min(head.num_tokens - head.num_computed_tokens, budget)
+            need = self.kv.pool.blocks_needed(first + self.num_lookahead_tokens, 0)
+            while self.running and self.kv.pool.num_free_blocks < need:
+                victim = max(self.running, key=lambda r: (r.priority, r.arrival_time))
+                if (victim.priority, victim.arrival_time) <= (head.priority, head.arrival_time):
+                    break
+                self._preempt(victim, out)
+        priority_preempted = len(out.preempted_req_ids)
+
         # 1) requests that are already running
         scheduled_ids: set[str] = set()
         i = 0
@@ -207,7 +220,7 @@ class Scheduler:
             i += 1
 
         # 2) admit waiting requests (only if nothing was preempted in this step)
-        if allow_waiting and not out.preempted_req_ids:
+        if allow_waiting and len(out.preempted_req_ids) == priority_preempted:
             while self.waiting and budget > 0 and len(self.running) < self.cfg.max_num_seqs:
                 req = self.waiting[0]
                 computed_blocks: list[int] = []
