@@ -46,10 +46,15 @@ def main():
     out = torch.empty_like(q)
     scale = D ** -0.5
     kv_bytes = 2 * B * ctx * Hkv * D * 2
-    for splits in (1, 2, 4):
-        ms = timeit(lambda: C.paged_decode(q, kc, vc, bt, sl, scale, out=out, num_splits=splits))
-        print(f"decode B={B} ctx={ctx} splits={splits}: {ms*1e3:8.1f} us  "
-              f"{kv_bytes/ms/1e6:7.0f} GB/s (KV bytes {kv_bytes/1e6:.0f} MB)", flush=True)
+    for tma in (True, False):
+        C.USE_TMA_DECODE = tma
+        for splits in (1, 2, 4):
+            ms = timeit(lambda: C.paged_decode(q, kc, vc, bt, sl, scale, out=out,
+                                               num_splits=splits))
+            print(f"decode {'tma     ' if tma else 'cp.async'} B={B} ctx={ctx} splits={splits}: "
+                  f"{ms*1e3:8.1f} us  {kv_bytes/ms/1e6:7.0f} GB/s "
+                  f"(KV bytes {kv_bytes/1e6:.0f} MB)", flush=True)
+    C.USE_TMA_DECODE = True
     # prefill: 8 sequences of 1024 new tokens
     nseq, ql = 8, 1024
     T = nseq * ql

@@ -669,6 +669,28 @@ B200_API int b200_paged_decode(const void* q, long long ldq, void* out, long lon
   return -8;
 }
 
+// Second pass of split-KV decode: LSE-weighted sum of the per-split partial outputs
+// (tmp_out fp32 [B, Hq, num_splits, HD], tmp_lse fp32 [B, Hq, num_splits], log2 domain).
+B200_API int b200_decode_reduce(void* out, long long ldo, float* tmp_out, float* tmp_lse,
+                                int num_splits, int B, int Hq, int HD, int dtype, void* stream) {
+  if (B <= 0 || num_splits <= 1) return 0;
+  DecodeArgs a{};
+  a.out = out; a.tmp_out = tmp_out; a.tmp_lse = tmp_lse; a.ldo = ldo; a.B = B; a.Hq = Hq;
+  a.num_splits = num_splits;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  dim3 grid(B, Hq);
+#define B200_RED(TT, H) decode_reduce_kernel<TT, H><<<grid, 128, 0, s>>>(a)
+  if (dtype == 0 && HD == 128) B200_RED(__nv_bfloat16, 128);
+  else if (dtype == 0 && HD == 64) B200_RED(__nv_bfloat16, 64);
+  else if (dtype == 0 && HD == 256) B200_RED(__nv_bfloat16, 256);
+  else if (dtype == 1 && HD == 128) B200_RED(__half, 128);
+  else if (dtype == 1 && HD == 64) B200_RED(__half, 64);
+  else if (dtype == 1 && HD == 256) B200_RED(__half, 256);
+  else return -8;
+#undef B200_RED
+  return static_cast<int>(cudaGetLastError());
+}
+
 // Prefill / chunked-prefill / prefix attention.  num_q_tiles must be
 // sum_b ceil(q_len_b / 64) (an upper bound is fine: extra CTAs exit).
 B200_API int b200_varlen_prefill(const void* q, long long ldq, void* out, long long ldo,

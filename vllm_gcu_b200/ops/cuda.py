@@ -21,6 +21,8 @@ ACT_CODES = {"silu": 0, "gelu": 1, "gelu_tanh": 2, "fatrelu": 3, "gelu_new": 4,
              "gelu_fast": 5, "gelu_quick": 6, "identity": 7}
 ACT_QUANT = {None: 0, "fp8_group128": 1, "fp8_static": 2, "int8_static": 3, "int8_asym": 4}
 FP8 = torch.float8_e4m3fn
+#: route head-dim-128 decode attention through the TMA-fed kernel (False: cp.async kernel)
+USE_TMA_DECODE = True
 
 
 def _rowmajor_2d(t: torch.Tensor) -> torch.Tensor:
@@ -283,10 +285,19 @@ def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
             tmp_out, tmp_lse = workspace
             assert tmp_out.numel() >= B * Hq * num_splits * D
             assert tmp_lse.numel() >= B * Hq * num_splits
-    call("b200_paged_decode", ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(k_cache),
-         ptr(v_cache), k_cache.stride(1), k_cache.stride(2), nb * bs, ptr(block_tables),
-         block_tables.stride(0), bs, ptr(seq_lens), ptr(tmp_out), ptr(tmp_lse), num_splits,
-         B, Hq, Hkv, D, float(scale), DTYPE_CODE[q.dtype], stream_ptr())
+    args = (ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(k_cache),
+            ptr(v_cache), k_cache.stride(1), k_cache.stride(2), nb * bs, ptr(block_tables),
+            block_tables.stride(0), bs, ptr(seq_lens), ptr(tmp_out), ptr(tmp_lse), num_splits,
+            B, Hq, Hkv, D, float(scale), DTYPE_CODE[q.dtype], stream_ptr())
+    if USE_TMA_DECODE and D == 128 and bs % 16 == 0 and k_cache.stride(2) == 128 \
+            and k_cache.stride(1) == Hkv * 128:
+        rc = N.lib().b200_paged_decode_tma(*args)      # TMA-fed variant (attention_tma.cu)
+        N.launch_count += 1
+        if rc == 0:
+            return out
+        if rc != -20:
+            raise N.NativeError(f"b200_paged_decode_tma failed with code {rc}")
+    call("b200_paged_decode", *args)
     return out
 
 
