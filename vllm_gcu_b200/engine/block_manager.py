@@ -168,6 +168,9 @@ class KVCacheManager:
         """Makes sure ``req`` owns blocks for ``num_computed + num_new (+ lookahead)``
         tokens.  Returns the newly appended block ids, or None when the pool cannot
         supply them (nothing is changed in that case)."""
+        if not new_computed_blocks and (req.num_computed_tokens + num_new_tokens
+                                        + num_lookahead_tokens) <= len(req.block_ids) * self.block_size:
+            return []                       # the blocks already owned cover this step
         num_computed = req.num_computed_tokens + len(new_computed_blocks) * self.block_size \
             if new_computed_blocks else req.num_computed_tokens
         total = num_computed + num_new_tokens + num_lookahead_tokens
@@ -186,12 +189,46 @@ class KVCacheManager:
         return list(new_computed_blocks) + new_ids
 
     def cache_blocks(self, req, num_tokens: int) -> None:
+        """Registers the full blocks among the first ``num_tokens`` tokens of ``req``.
+        Incremental: only blocks completed since the previous call are hashed."""
+        pool = self.pool
+        if not pool.enable_prefix_caching:
+            return
+        bs = self.block_size
+        nfull = min(num_tokens, req.num_tokens) // bs
+        done = getattr(req, "_hashed_blocks", 0)
+        if nfull <= done:
+            return
         extra = (req.lora_id,) if req.lora_id >= 0 else ()
-        self.pool.cache_full_blocks(req.block_ids, req.all_token_ids, num_tokens, extra)
+        parent = getattr(req, "_last_hash", None)
+        if done == 0:
+            parent = None
+        npt = req.num_prompt_tokens
+        for i in range(done, nfull):
+            a, b = i * bs, (i + 1) * bs
+            if b <= npt:
+                toks = req.prompt_token_ids[a:b]
+            elif a >= npt:
+                toks = req.output_token_ids[a - npt:b - npt]
+            else:
+                toks = req.prompt_token_ids[a:] + req.output_token_ids[:b - npt]
+            blk = pool.blocks[req.block_ids[i]]
+            if blk.block_hash is not None:
+                parent = blk.block_hash
+                continue
+            h = hash_block(parent, toks, extra)
+            parent = h
+            if h not in pool.cached:
+                pool.cached[h] = blk.block_id
+                blk.block_hash = h
+        req._hashed_blocks = nfull
+        req._last_hash = parent
 
     def free(self, req) -> None:
         self.pool.release(req.block_ids)
         req.block_ids = []
+        req._hashed_blocks = 0
+        req._last_hash = None
 
     @property
     def usage(self) -> float:

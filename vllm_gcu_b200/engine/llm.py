@@ -186,10 +186,14 @@ class LLMEngine:
             sps = list(sampling_params)
         order = [self.add_request(p, sp) for p, sp in zip(prompts, sps)]
         final: dict[str, RequestOutput] = {}
-        while self.has_unfinished():
-            for ro in self.step():
-                if ro.finished:
-                    final[ro.request_id] = ro
+        prev, self.scheduler.emit_partial = self.scheduler.emit_partial, False
+        try:
+            while self.has_unfinished():
+                for ro in self.step():
+                    if ro.finished:
+                        final[ro.request_id] = ro
+        finally:
+            self.scheduler.emit_partial = prev
         return [final[r] for r in order]
 
 

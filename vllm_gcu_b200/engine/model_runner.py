@@ -339,14 +339,30 @@ class ModelRunner:
         pos = i64[o_pos:o_pos + T_real]
         ids = i64[o_ids:o_ids + T_real]
         if nd:
+            # decode fast path: one token per request, either known or fed on the device
             pos[:nd] = starts[:nd]
-        for j, s in enumerate(order):
+            dec_ids = [0] * nd
+            prev_index = self.prev_index
+            for j in range(nd):
+                s = order[j]
+                req = s.req
+                npt = len(req.prompt_token_ids)
+                st = s.start
+                if st < npt:
+                    dec_ids[j] = req.prompt_token_ids[st]
+                elif st - npt < len(req.output_token_ids):
+                    dec_ids[j] = req.output_token_ids[st - npt]
+                else:
+                    feed_dst.append(j)
+                    feed_src.append(prev_index[req.request_id])
+            ids[:nd] = dec_ids
+        for j in range(nd, B):
+            s = order[j]
             a, b = int(tok_off[j]), int(tok_off[j + 1])
             req = s.req
             known = req.num_tokens
             n_spec = len(s.spec_token_ids)
-            if j >= nd:
-                pos[a:b] = np.arange(s.start, s.start + s.num_tokens)
+            pos[a:b] = np.arange(s.start, s.start + s.num_tokens)
             end = s.start + s.num_tokens
             n_known = max(0, min(end, known) - s.start)
             if n_known:

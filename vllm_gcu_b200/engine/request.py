@@ -55,7 +55,7 @@ class RequestStatus(enum.IntEnum):
         return self >= RequestStatus.FINISHED_STOPPED
 
 
-@dataclass
+@dataclass(eq=False)      # identity semantics: requests live in lists and sets
 class Request:
     request_id: str
     prompt_token_ids: list[int]

@@ -25,7 +25,7 @@ from .block_manager import KVCacheManager
 from .request import (CompletionOutput, Request, RequestOutput, RequestStatus, check_stop)
 
 
-@dataclass
+@dataclass(eq=False)
 class ScheduledRequest:
     req: Request
     start: int                 # first position computed in this step
@@ -66,6 +66,8 @@ class Scheduler:
         self.num_lookahead_tokens = num_lookahead_tokens
         self.step_id = 0
         self.num_preemptions = 0
+        #: emit a RequestOutput for every sampled token (streaming); False: finished only
+        self.emit_partial = True
 
     # -- request lifecycle ---------------------------------------------------
     def add_request(self, req: Request) -> None:
@@ -294,7 +296,7 @@ class Scheduler:
             req = s.req
             if req.finished or req.request_id not in self.requests:
                 continue                    # aborted / finished while the step was in flight
-            if req.status == RequestStatus.PREEMPTED or req not in self.running:
+            if req.status != RequestStatus.RUNNING:
                 continue
             toks = list(sampled.get(req.request_id, ()))
             if not s.will_sample:
@@ -327,7 +329,8 @@ class Scheduler:
                 import time as _t
                 req.finish_time = _t.monotonic()
                 self._free(req)
-            results.append(self._make_output(req, emitted))
+            if stopped or self.emit_partial:
+                results.append(self._make_output(req, emitted))
         return results
 
     @staticmethod
@@ -339,8 +342,9 @@ class Scheduler:
             reason = "length"
         elif req.status == RequestStatus.FINISHED_ABORTED:
             reason = "abort"
-        comp = CompletionOutput(0, list(req.output_token_ids), reason,
-                                list(req.logprobs) if req.logprobs else None)
+        # token_ids is the request's live list (no per-step copy); treat it as read-only
+        comp = CompletionOutput(0, req.output_token_ids, reason,
+                                req.logprobs if req.logprobs else None)
         return RequestOutput(req.request_id, req.prompt_token_ids, [comp], req.finished,
                              req.num_cached_tokens)
 
