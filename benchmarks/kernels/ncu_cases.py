@@ -1,0 +1,110 @@
+"""Small, self-terminating workloads for Nsight Compute captures of single kernels.
+
+Each case allocates well under 2 GB, uses inputs larger than L2 where DRAM figures matter and
+launches the kernel of interest a handful of times:
+
+  python benchmarks/kernels/ncu_cases.py --case gemm_prefill   # 8192 x 4096 x 4096 bf16
+  python benchmarks/kernels/ncu_cases.py --case gemm_decode    # 256 x 4096 x 14336 bf16
+  python benchmarks/kernels/ncu_cases.py --case decode_attn    # B=256, ctx=1152, GQA 32/8
+  python benchmarks/kernels/ncu_cases.py --case prefill_attn   # 8 x 1024 tokens, causal
+  python benchmarks/kernels/ncu_cases.py --case gemm_fp8       # 4096 x 4096 x 4096 fp8
+  python benchmarks/kernels/ncu_cases.py --case gemm_ar_single # fused all-reduce epilogue, p = 1
+
+Capture (one GPU):
+  ncu --set full --clock-control none -k regex:<kernel> -s 2 -c 2 -o gpurun_out/<name> \
+      python benchmarks/kernels/ncu_cases.py --case <case>
+"""
+import argparse
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+from vllm_gcu_b200.ops import _native  # noqa: E402
+from vllm_gcu_b200.ops import cuda as C  # noqa: E402
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", required=True)
+    ap.add_argument("--iters", type=int, default=5)
+    a = ap.parse_args()
+    dev = "cuda"
+    torch.manual_seed(0)
+    if a.case in ("gemm_prefill", "gemm_decode"):
+        M, N, K = (8192, 4096, 4096) if a.case == "gemm_prefill" else (256, 4096, 14336)
+        x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02
+        out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        fn = lambda: C.gemm_bf16(x, w, out=out)  # noqa: E731
+    elif a.case == "gemm_fp8":
+        M = N = K = 4096
+        x = torch.randn(M, K, device=dev).to(torch.float8_e4m3fn)
+        w = torch.randn(N, K, device=dev).to(torch.float8_e4m3fn)
+        sa = torch.ones(M, device=dev)
+        sb = torch.ones(N, device=dev)
+        out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        fn = lambda: C.gemm_q8(x, w, sa, sb, None, kind=0, out=out)  # noqa: E731
+    elif a.case == "decode_attn":
+        B, ctx, Hq, Hkv, D, bs = 256, 1152, 32, 8, 128, 16
+        mb = ctx // bs
+        nb = B * mb
+        kc = torch.randn(nb, bs, Hkv, D, device=dev, dtype=torch.bfloat16)
+        vc = torch.randn(nb, bs, Hkv, D, device=dev, dtype=torch.bfloat16)
+        bt = torch.randperm(nb, device=dev).to(torch.int32).view(B, mb)
+        sl = torch.full((B,), ctx, device=dev, dtype=torch.int32)
+        q = torch.randn(B, Hq, D, device=dev, dtype=torch.bfloat16)
+        out = torch.empty_like(q)
+        fn = lambda: C.paged_decode(q, kc, vc, bt, sl, D ** -0.5, out=out, num_splits=1)  # noqa
+    elif a.case == "prefill_attn":
+        nseq, ql, Hq, Hkv, D, bs = 8, 1024, 32, 8, 128, 16
+        nb = nseq * ql // bs
+        kc = torch.randn(nb, bs, Hkv, D, device=dev, dtype=torch.bfloat16)
+        vc = torch.randn(nb, bs, Hkv, D, device=dev, dtype=torch.bfloat16)
+        bt = torch.randperm(nb, device=dev).to(torch.int32).view(nseq, ql // bs)
+        q = torch.randn(nseq * ql, Hq, D, device=dev, dtype=torch.bfloat16)
+        cu = torch.arange(0, nseq * ql + 1, ql, device=dev, dtype=torch.int32)
+        sl = torch.full((nseq,), ql, device=dev, dtype=torch.int32)
+        out = torch.empty_like(q)
+        fn = lambda: C.varlen_prefill(q, kc, vc, bt, cu, sl, D ** -0.5, nseq * ql // 64,  # noqa
+                                      out=out)
+    elif a.case == "gemm_ar_single":
+        # the fused row-parallel GEMM + all-reduce kernel with a one-rank "group": same code
+        # path (partial tile -> flags -> reduce -> output) without a second process
+        import ctypes
+        M, N, K = 8192, 4096, 2048
+        x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02
+        part = torch.zeros(2 * M * N, device=dev, dtype=torch.bfloat16)
+        out = torch.zeros(M, N, device=dev, dtype=torch.bfloat16)
+        flags = torch.zeros(1 << 16, device=dev, dtype=torch.int32)
+        words = torch.zeros(16, device=dev, dtype=torch.int32)
+        lib = _native.lib()
+        P, I, L = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+        lib.b200_gemm_bf16_allreduce.argtypes = [P, L, P, L, L, I, I, I, P, P, P, P, P, P, I, I,
+                                                 P, L, I, L, P]
+
+        def arr(p):
+            v = (ctypes.c_void_p * 8)()
+            v[0] = p
+            return v
+
+        def fn():
+            rc = lib.b200_gemm_bf16_allreduce(
+                x.data_ptr(), K, w.data_ptr(), K, N, M, N, K, arr(part.data_ptr()),
+                arr(out.data_ptr()), arr(flags.data_ptr()), arr(flags.data_ptr() + (1 << 17)),
+                words.data_ptr(), words.data_ptr() + 16, 0, 1, None, 0, 1, M * N,
+                torch.cuda.current_stream().cuda_stream)
+            assert rc == 0, rc
+    else:
+        raise SystemExit(f"unknown case {a.case}")
+    for _ in range(a.iters):
+        fn()
+    torch.cuda.synchronize()
+    _native.check_status()
+    print("ok", a.case)
+
+
+if __name__ == "__main__":
+    main()
