@@ -1,0 +1,74 @@
+"""Worker of the expert-parallel multi-GPU test (torch.distributed.run, one rank per GPU).
+
+Every rank holds different tokens; the fused peer-memory dispatch / combine must give the
+same result as running all experts on one device (fp32 reference), for several launches in a
+row, for uneven token counts and for a rank that has no tokens at all.
+"""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from vllm_gcu_b200.layers.moe_ep import EPWorkspace  # noqa: E402
+from vllm_gcu_b200.ops import _native  # noqa: E402
+from vllm_gcu_b200.ops import cuda as C  # noqa: E402
+from vllm_gcu_b200.ops import ref  # noqa: E402
+from vllm_gcu_b200.parallel.state import init_distributed  # noqa: E402
+
+
+def main():
+    world = int(os.environ["WORLD_SIZE"])
+    rank = int(os.environ["RANK"])
+    st = init_distributed(tp=1, dp=world, enable_ep=True)
+    dev = torch.device("cuda", st.local_rank)
+    E, k, H, I = 8 * world, 4, 512, 256
+    epr = E // world
+    g = torch.Generator().manual_seed(1)
+    w13_full = (torch.randn(E, 2 * I, H, generator=g) * 0.05).to(torch.bfloat16)
+    w2_full = (torch.randn(E, H, I, generator=g) * 0.05).to(torch.bfloat16)
+    lo = rank * epr
+    w13 = torch.stack([ref.interleave_gate_up(w13_full[e, :I], w13_full[e, I:])
+                       for e in range(lo, lo + epr)]).to(dev).contiguous()
+    w2 = w2_full[lo:lo + epr].to(dev).contiguous()
+    emap = torch.full((E,), -1, dtype=torch.int32)
+    emap[lo:lo + epr] = torch.arange(epr, dtype=torch.int32)
+    emap = emap.to(dev)
+    ws = EPWorkspace.get(H, k, epr, 300, dev)
+
+    for it, counts in enumerate([[37 + 11 * r for r in range(world)],
+                                 [0 if r == 0 else 64 for r in range(world)],
+                                 [300] * world,
+                                 [1] * world]):
+        T = counts[rank]
+        gt = torch.Generator().manual_seed(100 * it + rank)
+        x = torch.randn(T, H, generator=gt).to(torch.bfloat16).to(dev)
+        logits = torch.randn(T, E, generator=gt)
+        topk_w, topk_ids = torch.topk(torch.softmax(logits, -1), k, dim=-1)
+        topk_w = topk_w.float().to(dev)
+        topk_ids = topk_ids.to(torch.int32).to(dev)
+        shared = torch.randn(T, H, generator=gt).to(torch.bfloat16).to(dev)
+        want = ref.fused_experts(x.float().cpu(), w13_full.float(), w2_full.float(), topk_w.cpu(),
+                                 topk_ids.cpu().long()).float() * 2.5 + shared.float().cpu()
+        for rep in range(2):
+            xr, w_r, ids_r, total = ws.dispatch(x, topk_w, topk_ids, max(counts))
+            yr = C.fused_experts(xr, w13, w2, w_r, ids_r, emap, valid_tokens=total)
+            out = ws.combine(yr, T, shared, alpha=2.5)
+            torch.cuda.synchronize()
+            _native.check_status()
+            if T:
+                err = (out.float().cpu() - want).abs().max().item()
+                tol = 0.03 * want.abs().max().item() + 0.03
+                assert err < tol, f"case {it} rep {rep} rank {rank}: err {err} tol {tol}"
+        dist.barrier()
+    if rank == 0:
+        print(f"ep{world} fused dispatch/combine ok", flush=True)
+    dist.barrier()
+    sys.stdout.flush()
+    os._exit(0)
+
+
+if __name__ == "__main__":
+    main()

@@ -78,12 +78,50 @@ def main():
         torch.cuda.synchronize()
         _native.check_status()
         assert (got.float() - want).abs().max().item() < 0.05 * want.abs().max().item() + 0.05
+    # ---- GEMM + all-gather of the output (vocabulary-parallel LM head) ------------------
+    fg = symm.FusedGather(dev, out_rows=300, out_cols=4096 * world, sp_tokens=1200, sp_k=1024)
+    for (M, N, K) in [(256, 4096, 512), (5, 1024, 256), (300, 520, 72)]:
+        g = torch.Generator(device="cuda").manual_seed(7)          # same x on every rank
+        x = torch.randn(M, K, device=dev, dtype=torch.bfloat16, generator=g)
+        g2 = torch.Generator(device="cuda").manual_seed(200 + rank)
+        w = (torch.randn(N, K, device=dev, generator=g2) * 0.05).to(torch.bfloat16)
+        mine = (x.float() @ w.float().t())
+        parts = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(parts, mine)
+        want = torch.cat(parts, dim=1)
+        for rep in range(3):
+            got = fg.gemm_all_gather(x, w)
+            assert got is not None
+            torch.cuda.synchronize()
+            _native.check_status()
+            err = (got.float() - want).abs().max().item()
+            assert err < 0.02 * want.abs().max().item() + 0.02, \
+                f"gemm_all_gather {M}x{N}x{K} rep {rep}: err {err}"
+    # ---- all-gather of the input fused into the GEMM (sequence-parallel activations) ----
+    from vllm_gcu_b200.parallel.sp import scatter
+    for (M, N, K) in [(1024, 2048, 1024), (1200, 512, 1024), (77, 256, 1024), (3, 128, 1024)]:
+        sizes = scatter(M, world)
+        g = torch.Generator(device="cuda").manual_seed(300 + rank)
+        xs = torch.randn(sizes[rank], K, device=dev, dtype=torch.bfloat16, generator=g)
+        g2 = torch.Generator(device="cuda").manual_seed(9)
+        w = (torch.randn(N, K, device=dev, generator=g2) * 0.05).to(torch.bfloat16)
+        full = get_comm("tp").all_gather_v(xs, sizes)
+        want = full.float() @ w.float().t()
+        for rep in range(3):
+            got = fg.all_gather_gemm(xs, w, sizes)
+            assert got is not None
+            torch.cuda.synchronize()
+            _native.check_status()
+            err = (got.float() - want).abs().max().item()
+            assert err < 0.02 * want.abs().max().item() + 0.02, \
+                f"all_gather_gemm {M}x{N}x{K} rep {rep}: err {err}"
     if rank == 0:
         print("fused collectives ok", flush=True)
 
     # ---- tensor-parallel engine vs single GPU --------------------------------------------
     kw = dict(num_hidden_layers=2, hidden_size=1024, intermediate_size=2048,
-              num_attention_heads=8, num_key_value_heads=2, head_dim=128, vocab_size=4096,
+              num_attention_heads=max(8, world), num_key_value_heads=max(2, world), head_dim=128,
+              vocab_size=4096,
               max_num_seqs=8, max_num_batched_tokens=256, max_model_len=256, num_gpu_blocks=128)
     cfg = preset("llama-3-8b", **{k: v for k, v in kw.items() if k in (
         "num_hidden_layers", "hidden_size", "intermediate_size", "num_attention_heads",
@@ -95,6 +133,7 @@ def main():
     results = {}
     for comm in ("nccl", "fused"):
         get_comm("tp").fused = None
+        get_comm("tp").fused_gather = None
         llm = LLM("llama-3-8b", tensor_parallel_size=world, comm_backend=comm, enforce_eager=True,
                   load_format="none", **kw)
         llm.engine.model.load_weights(sd.items())
@@ -104,6 +143,7 @@ def main():
         _native.check_status()
         results[comm] = llm.engine.runner.last_logits
     get_comm("tp").fused = None
+    get_comm("tp").fused_gather = None
     if rank == 0:
         # single-GPU reference on the same weights (TP groups of size 1 via a fresh state)
         pass

@@ -15,9 +15,23 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
                     reason="needs >= 2 GPUs")
 def test_tensor_parallel_two_gpus():
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+    n = os.environ.get("B200_TEST_TP", "2")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", n,
            "--master-addr", "127.0.0.1", "--master-port", "29611",
            os.path.join(ROOT, "tests", "_tp_worker.py")]
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert "engine ok" in res.stdout
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2,
+                    reason="needs >= 2 GPUs")
+def test_expert_parallel_fused_dispatch_two_gpus():
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    n = min(torch.cuda.device_count(), 8)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(n),
+           "--master-addr", "127.0.0.1", "--master-port", "29613",
+           os.path.join(ROOT, "tests", "_ep_worker.py")]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert "fused dispatch/combine ok" in res.stdout

@@ -34,7 +34,14 @@ enum Epilogue : int {
   kEpiResidual = 3,
   kEpiFp32 = 4,
   kEpiAllReduce = 5,  // row-parallel partial product -> tile-wise two-shot all-reduce over peers
+  kEpiAllGather = 6,  // column-parallel shard -> every peer's full-width output (peer stores)
+  kEpiGatherA = 7,    // A rows are gathered from the peers' shards by extra warps of this kernel
 };
+
+template <int EPI>
+constexpr int kThreadsFor = (EPI == kEpiGatherA) ? 320 : 192;
+template <int EPI>
+constexpr bool kPeerEpi = (EPI == kEpiAllReduce || EPI == kEpiAllGather || EPI == kEpiGatherA);
 
 constexpr int kMaxPeers = 8;
 
@@ -50,7 +57,31 @@ struct ArArgs {
   int rank, p;
   int oneshot;                        // 1: push partials to every peer, reduce locally
   long long slot_elems;               // one-shot: elements per (parity, source rank) slot
+  long long col_off;                  // all-gather epilogue: first output column of this rank
 };
+
+// All-gather of the A operand inside the GEMM (sequence-parallel input of a column-parallel
+// layer).  Rank r owns rows [row_off[r], row_off[r + 1]) of A; its shard lives in symmetric
+// memory.  Four extra warps copy the shards with plain peer loads into the local buffer
+// `a_full` (the only memory the TMA descriptor covers) one 128-row chunk at a time and publish
+// chunk_ready[chunk]; the TMA warp waits for the chunk before loading it.
+struct AgArgs {
+  const __nv_bfloat16* shard[kMaxPeers];  // rows of rank r, pitch lds
+  __nv_bfloat16* a_full;                  // local [M, lda]
+  long long lds, lda;
+  uint32_t* in_ready[kMaxPeers];          // [p] on rank r: in_ready[r][src] = src's shard is valid
+  uint32_t* rd_done[kMaxPeers];           // [p] on rank r: rd_done[r][reader] = reader is done with r's shard
+  uint32_t* chunk_ready;                  // local [tiles_m]
+  uint32_t* gather_ctr;                   // local
+  int row_off[kMaxPeers + 1];             // first row of every rank's shard; [p] = M
+  int enabled;
+};
+
+__device__ __forceinline__ int ag_owner(const AgArgs& g, int np, int row) {
+  int o = 0;
+  while (o + 1 < np && row >= g.row_off[o + 1]) ++o;
+  return o;
+}
 
 struct Args {
   void* C;
@@ -65,14 +96,17 @@ struct Args {
   const int* expert_ids;      // [tiles_m] expert of each M tile (-1: skip), null = dense GEMM
   const int* num_valid_rows;  // device scalar: rows of A that are in use (multiple of BM)
   const float* row_scale;     // optional [M] factor applied to each output row
+  int m_rot;                  // M tiles are visited starting at this tile (gathered-A mode)
   ArArgs ar;
+  AgArgs ag;
 };
 
 // Resolves tile -> (m0, n0, first B row).  Returns false for tiles that carry no work.
 template <int BN_>
 __device__ __forceinline__ bool tile_coords(const Args& p, int tile, int& m0, int& n0,
                                             int& b_row) {
-  const int tm = tile % p.tiles_m;
+  int tm = tile % p.tiles_m + p.m_rot;
+  if (tm >= p.tiles_m) tm -= p.tiles_m;
   m0 = tm * BM;
   n0 = (tile / p.tiles_m) * BN_;
   b_row = n0;
@@ -109,6 +143,17 @@ __device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
   return v;
 }
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void gather_bar_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
+// Bounded acquire-wait at GPU scope on a flag written by another CTA of this kernel.
+__device__ __forceinline__ bool wait_flag_gpu(const uint32_t* flag, uint32_t want) {
+  for (uint32_t it = 0; it < (1u << 22); ++it) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (static_cast<int32_t>(v - want) >= 0) return true;
+    if (it > 64) __nanosleep(100);
+  }
+  return false;
+}
 
 // Sums `np` bf16 tiles (slot r at base + r * stride) into out rows; 4 vectors in flight per
 // thread and source so the loads overlap.
@@ -195,7 +240,7 @@ __device__ __forceinline__ void store_row_bf16(__nv_bfloat16* dst, const float* 
 }
 
 template <int BN, int STAGES, int EPI>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreadsFor<EPI>, 1)
     gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA,
                      const __grid_constant__ CUtensorMap tmB, const Args p) {
   using L = Smem<BN, STAGES>;
@@ -241,7 +286,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int num_kb = (p.K + BK - 1) / BK;
   const int num_tiles = p.tiles_m * p.tiles_n;
   uint32_t epoch = 0;
-  if constexpr (EPI == kEpiAllReduce)
+  if constexpr (kPeerEpi<EPI>)
     epoch = *reinterpret_cast<volatile uint32_t*>(p.ar.epoch_ptr) + 1u;
 
   if (warp == 0) {
@@ -253,6 +298,16 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         int m0, n0, b_row;
         if (!tile_coords<BN>(p, tile, m0, n0, b_row)) continue;
+        if constexpr (EPI == kEpiGatherA) {
+          // rows of this M tile must have been copied into the local buffer (generic-proxy
+          // stores by the gather warps of some CTA) before the async proxy reads them
+          if (!wait_flag_gpu(p.ag.chunk_ready + m0 / BM, epoch)) {
+            report_status(p.status, kStatusFlagTimeout, kKernelId, 0x700u);
+            *abort_flag = 1u;
+            break;
+          }
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, p.status, kKernelId, 0x100u + stage,
                          abort_flag)) {
@@ -318,11 +373,92 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (acc == 0) acc_phase ^= 1u;
       }
     }
+  } else if (warp >= 6) {
+    // ---------------- A gather (warps 6..9, gathered-A variant only) ----------------
+    if constexpr (EPI == kEpiGatherA) {
+      const int tg = threadIdx.x - 192;  // 0..127
+      const int np = p.ar.p, rank = p.ar.rank;
+      if (blockIdx.x == 0 && tg < np)    // this rank's shard was written before the launch
+        signal_flag_sys(p.ag.in_ready[tg] + rank, epoch);
+      const int kvec = p.K / 8;
+      bool ok = true;
+      for (int c = blockIdx.x; ok && c < p.tiles_m; c += gridDim.x) {
+        int tm = c + p.m_rot;
+        if (tm >= p.tiles_m) tm -= p.tiles_m;
+        const int r0 = tm * BM, r1 = min(p.M, r0 + BM);
+        const int o0 = ag_owner(p.ag, np, r0), o1 = ag_owner(p.ag, np, r1 - 1);
+        if (tg >= o0 && tg <= o1 && tg != rank) {
+          if (!wait_flag_sys(p.ag.in_ready[rank] + tg, epoch)) {
+            report_status(p.status, kStatusFlagTimeout, kKernelId, 0x710u + tg);
+            *abort_flag = 1u;
+          }
+        }
+        gather_bar_sync();
+        if (*abort_flag != 0u) break;
+        const int nvec = (r1 - r0) * kvec;
+        constexpr int kU = 8;
+        for (int v0 = tg; v0 < nvec; v0 += 128 * kU) {
+          uint4 u[kU];
+#pragma unroll
+          for (int k = 0; k < kU; ++k) {
+            const int v = v0 + k * 128;
+            if (v < nvec) {
+              const int row = r0 + v / kvec, cv = v % kvec;
+              const int owner = ag_owner(p.ag, np, row);
+              u[k] = ld_volatile_v4(p.ag.shard[owner] +
+                                    static_cast<long long>(row - p.ag.row_off[owner]) * p.ag.lds +
+                                    cv * 8);
+            }
+          }
+#pragma unroll
+          for (int k = 0; k < kU; ++k) {
+            const int v = v0 + k * 128;
+            if (v < nvec) {
+              const int row = r0 + v / kvec, cv = v % kvec;
+              *reinterpret_cast<uint4*>(p.ag.a_full + static_cast<long long>(row) * p.ag.lda +
+                                        cv * 8) = u[k];
+            }
+          }
+        }
+        asm volatile("fence.proxy.async;" ::: "memory");
+        __threadfence();
+        gather_bar_sync();
+        if (tg == 0)
+          asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.ag.chunk_ready + tm),
+                       "r"(epoch)
+                       : "memory");
+      }
+      gather_bar_sync();
+      if (tg == 0) {
+        // the last CTA to finish its chunks tells every owner that this rank is done reading
+        __threadfence();
+        if (atomicAdd(p.ag.gather_ctr, 1u) == gridDim.x - 1) {
+          *p.ag.gather_ctr = 0u;
+          for (int r = 0; r < np; ++r) signal_flag_sys(p.ag.rd_done[r] + rank, epoch);
+        }
+      }
+      // the shard may be overwritten after this kernel: wait until every reader is done
+      if (blockIdx.x == 0 && tg < np && *abort_flag == 0u) {
+        if (!wait_flag_sys(p.ag.rd_done[rank] + tg, epoch))
+          report_status(p.status, kStatusFlagTimeout, kKernelId, 0x720u + tg);
+      }
+    }
   } else {
     // ---------------- epilogue (warps 2..5) ----------------
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     int acc = 0;
     uint32_t acc_phase = 0;
+    if constexpr (EPI == kEpiAllGather) {
+      // A peer's output buffer may be overwritten once that peer has started this launch
+      // (its stream is then past the consumers of the previous result).
+      const int te0 = threadIdx.x - 64;
+      if (blockIdx.x == 0 && te0 < p.ar.p) signal_flag_sys(p.ar.done[te0] + p.ar.rank, epoch);
+      if (te0 < p.ar.p && !wait_flag_sys(p.ar.done[p.ar.rank] + te0, epoch)) {
+        report_status(p.status, kStatusFlagTimeout, kKernelId, 0x810u + te0);
+        *abort_flag = 1u;
+      }
+      epi_bar_sync();
+    }
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
       int m0, n0, b_row_unused;
       if (!tile_coords<BN>(p, tile, m0, n0, b_row_unused)) continue;
@@ -388,6 +524,27 @@ __global__ void __launch_bounds__(kThreads, 1)
           signal_flag_sys(p.ar.ready[owner] + static_cast<long long>(tile) * p.ar.p + p.ar.rank,
                           epoch);
         }
+      } else if constexpr (EPI == kEpiAllGather) {
+        // store this rank's column block of the tile into every peer's full-width output
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          const int col = n0 + c * 32;
+          if (!row_ok || col >= p.N) continue;
+          const int ncols = min(32, p.N - col);
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          const long long off = static_cast<long long>(row) * p.ldc + p.ar.col_off + col;
+          for (int pr = 0; pr < p.ar.p; ++pr) store_row_bf16(p.ar.out[pr] + off, v, ncols);
+        }
+        epi_bar_sync();
+        const int te1 = threadIdx.x - 64;
+        if (te1 < p.ar.p)
+          signal_flag_sys(p.ar.ready[te1] + static_cast<long long>(tile) * p.ar.p + p.ar.rank,
+                          epoch);
       } else {
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
@@ -436,6 +593,19 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (acc == 0) acc_phase ^= 1u;
     }
 
+    if constexpr (EPI == kEpiAllGather) {
+      // the output is complete on this rank once every peer's column block of every tile
+      // has landed; each CTA checks the tiles it produced itself
+      const int te = threadIdx.x - 64;
+      const int np = p.ar.p, rank = p.ar.rank;
+      for (int t = blockIdx.x; t < num_tiles && *abort_flag == 0u; t += gridDim.x) {
+        if (te < np &&
+            !wait_flag_sys(p.ar.ready[rank] + static_cast<long long>(t) * np + te, epoch)) {
+          report_status(p.status, kStatusFlagTimeout, kKernelId, 0x800u + te);
+          *abort_flag = 1u;
+        }
+      }
+    }
     if constexpr (EPI == kEpiAllReduce) {
       const int te = threadIdx.x - 64;  // 0..127 among the epilogue warps
       const int np = p.ar.p, rank = p.ar.rank;
@@ -493,7 +663,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
-  if constexpr (EPI == kEpiAllReduce) {
+  if constexpr (kPeerEpi<EPI>) {
     // the last CTA to finish publishes the new epoch for the next launch
     if (threadIdx.x == 0) {
       __threadfence();
@@ -521,7 +691,7 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const Args& a, cudaSt
   }
   const int tiles = a.tiles_m * a.tiles_n;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  kern<<<grid, kThreads, L::kTotal, stream>>>(tmA, tmB, a);
+  kern<<<grid, kThreadsFor<EPI>, L::kTotal, stream>>>(tmA, tmB, a);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -583,6 +753,8 @@ B200_API int b200_gemm_bf16(const void* A, long long lda, const void* B, long lo
   a.expert_ids = nullptr;
   a.num_valid_rows = nullptr;
   a.row_scale = nullptr;
+  a.m_rot = 0;
+  a.ag = AgArgs{};
   a.ar = ArArgs{};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 
@@ -659,6 +831,8 @@ B200_API int b200_gemm_bf16_allreduce(const void* A, long long lda, const void* 
   a.expert_ids = nullptr;
   a.num_valid_rows = nullptr;
   a.row_scale = nullptr;
+  a.m_rot = 0;
+  a.ag = AgArgs{};
   for (int i = 0; i < kMaxPeers; ++i) {
     a.ar.partial[i] = i < p ? static_cast<__nv_bfloat16*>(partial[i]) : nullptr;
     a.ar.out[i] = i < p ? static_cast<__nv_bfloat16*>(out[i]) : nullptr;
@@ -674,6 +848,139 @@ B200_API int b200_gemm_bf16_allreduce(const void* A, long long lda, const void* 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (bn == 64) return launch<64, 8, kEpiAllReduce>(tmA, tmB, a, s);
   return launch<128, 6, kEpiAllReduce>(tmA, tmB, a, s);
+}
+
+namespace {
+int fill_peer_args(b200::gemm::Args& a, void* const* out, void* const* ready,
+                   void* const* started, void* epoch_ptr,
+                   void* done_ctr, int rank, int p) {
+  using namespace b200::gemm;
+  if (p < 1 || p > kMaxPeers || rank < 0 || rank >= p) return -2;
+  a.ar = ArArgs{};
+  for (int i = 0; i < p; ++i) {
+    a.ar.out[i] = out ? static_cast<__nv_bfloat16*>(out[i]) : nullptr;
+    a.ar.ready[i] = ready ? static_cast<uint32_t*>(ready[i]) : nullptr;
+    a.ar.done[i] = started ? static_cast<uint32_t*>(started[i]) : nullptr;
+  }
+  a.ar.epoch_ptr = static_cast<uint32_t*>(epoch_ptr);
+  a.ar.done_ctr = static_cast<uint32_t*>(done_ctr);
+  a.ar.rank = rank;
+  a.ar.p = p;
+  return 0;
+}
+}  // namespace
+
+// Column-parallel GEMM fused with the all-gather of its output over the peers (the
+// vocabulary-parallel LM head): rank r computes C_r[M, N] = A[M,K] * B_r[N,K]^T and its
+// epilogue stores the tile into columns [col_off, col_off + N) of the [M, ldc] output of
+// EVERY rank with peer stores, then raises ready[peer][tile * p + rank]; a launch returns
+// once all peers' blocks of the tiles it produced have landed locally.  A rank stores into a
+// peer only after that peer has entered the same launch (started[peer][rank] flag), so one
+// output buffer per rank is enough even when the launches are replayed from a CUDA graph.
+// `out` / `ready` / `started` are arrays of p peer-visible addresses; ready needs tiles * p
+// words with tiles = ceil(M/128) * ceil(N/BN), BN = b200_gemm_ar_tile_n(M, N); started needs
+// p words.  All ranks pass the same M, N, K.
+B200_API int b200_gemm_bf16_allgather(const void* A, long long lda, const void* B, long long ldb,
+                                      long long ldc, long long col_off, int M, int N, int K,
+                                      void* const* out, void* const* ready,
+                                      void* const* started, void* epoch_ptr, void* done_ctr,
+                                      int rank, int p, void* stream) {
+  using namespace b200;
+  using namespace b200::gemm;
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K % 8) != 0 || (lda % 8) != 0 || (ldb % 8) != 0 || (N % 8) != 0 ||
+      (ldc % 8) != 0 || (col_off % 8) != 0)
+    return -2;
+  const int bn = b200_gemm_ar_tile_n(M, N);
+  CUtensorMap tmA, tmB;
+  int r = encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, static_cast<uint64_t>(M),
+                         static_cast<uint64_t>(K), static_cast<uint64_t>(lda) * 2, BM, BK,
+                         CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r != 0) return r < 0 ? -6 : r;
+  r = encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, static_cast<uint64_t>(N),
+                     static_cast<uint64_t>(K), static_cast<uint64_t>(ldb) * 2, bn, BK,
+                     CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r != 0) return r < 0 ? -6 : r;
+  Args a{};
+  a.ldc = ldc;
+  a.M = M; a.N = N; a.K = K;
+  a.tiles_m = (M + BM - 1) / BM;
+  a.tiles_n = (N + bn - 1) / bn;
+  a.status = status_ptr();
+  a.ag = AgArgs{};
+  r = fill_peer_args(a, out, ready, started, epoch_ptr, done_ctr, rank, p);
+  if (r != 0) return r;
+  a.ar.col_off = col_off;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (bn == 64) return launch<64, 8, kEpiAllGather>(tmA, tmB, a, s);
+  return launch<128, 6, kEpiAllGather>(tmA, tmB, a, s);
+}
+
+// All-gather of the input fused into a column-parallel GEMM (sequence-parallel activations):
+//   C[M, N] = gather_r(A_r)[M, K] * B[N, K]^T,   rank r owning rows
+//   [row_off[r], row_off[r+1]) with row_off[0] = 0 and row_off[p] = M (host array, p + 1 ints).
+// `shard` holds p peer-visible addresses of the row shards (pitch lds); a_full is a
+// LOCAL [M, lda] staging buffer that the gather warps of the kernel fill chunk by chunk with
+// peer loads while the tensor cores already work on the chunks that have arrived (own rows
+// first, then the peers in ring order).  in_ready / rd_done: p words per rank in symmetric
+// memory; chunk_ready: ceil(M/128) local words; gather_ctr, epoch_ptr, done_ctr: local words,
+// all zero-initialised once.  The caller may overwrite its shard as soon as the launch has
+// finished (the kernel waits until every peer is done reading it).
+B200_API int b200_gemm_bf16_gather_a(void* const* shard, long long lds, const int* row_off,
+                                     void* a_full,
+                                     long long lda, const void* B, long long ldb, void* C,
+                                     long long ldc, int M, int N, int K, void* const* in_ready,
+                                     void* const* rd_done, void* chunk_ready, void* gather_ctr,
+                                     void* epoch_ptr, void* done_ctr, int rank, int p,
+                                     void* stream) {
+  using namespace b200;
+  using namespace b200::gemm;
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K % 8) != 0 || (lda % 8) != 0 || (ldb % 8) != 0 || (N % 8) != 0 ||
+      (ldc % 8) != 0 || (lds % 8) != 0 || row_off == nullptr || p < 1 || p > kMaxPeers ||
+      row_off[0] != 0 || row_off[p] != M)
+    return -2;
+  for (int i = 0; i < p; ++i)
+    if (row_off[i + 1] < row_off[i]) return -2;
+  const int tiles_m = (M + BM - 1) / BM;
+  const bool narrow = static_cast<long long>(tiles_m) * ((N + 127) / 128) < sm_count();
+  const int bn = narrow ? 64 : 128;
+  CUtensorMap tmA, tmB;
+  int r = encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a_full,
+                         static_cast<uint64_t>(M), static_cast<uint64_t>(K),
+                         static_cast<uint64_t>(lda) * 2, BM, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r != 0) return r < 0 ? -6 : r;
+  r = encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, static_cast<uint64_t>(N),
+                     static_cast<uint64_t>(K), static_cast<uint64_t>(ldb) * 2, bn, BK,
+                     CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r != 0) return r < 0 ? -6 : r;
+  Args a{};
+  a.C = C;
+  a.ldc = ldc;
+  a.M = M; a.N = N; a.K = K;
+  a.tiles_m = tiles_m;
+  a.tiles_n = (N + bn - 1) / bn;
+  a.status = status_ptr();
+  r = fill_peer_args(a, nullptr, nullptr, nullptr, epoch_ptr, done_ctr, rank, p);
+  if (r != 0) return r;
+  a.ag = AgArgs{};
+  for (int i = 0; i < p; ++i) {
+    a.ag.shard[i] = static_cast<const __nv_bfloat16*>(shard[i]);
+    a.ag.in_ready[i] = static_cast<uint32_t*>(in_ready[i]);
+    a.ag.rd_done[i] = static_cast<uint32_t*>(rd_done[i]);
+  }
+  a.ag.a_full = static_cast<__nv_bfloat16*>(a_full);
+  a.ag.lds = lds;
+  a.ag.lda = lda;
+  a.ag.chunk_ready = static_cast<uint32_t*>(chunk_ready);
+  a.ag.gather_ctr = static_cast<uint32_t*>(gather_ctr);
+  for (int i = 0; i <= p; ++i) a.ag.row_off[i] = row_off[i];
+  for (int i = p + 1; i <= kMaxPeers; ++i) a.ag.row_off[i] = M;
+  a.ag.enabled = 1;
+  a.m_rot = (row_off[rank] / BM) % tiles_m;   // start with the tiles of this rank's own rows
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (bn == 64) return launch<64, 8, kEpiGatherA>(tmA, tmB, a, s);
+  return launch<128, 6, kEpiGatherA>(tmA, tmB, a, s);
 }
 
 // Grouped GEMM for mixture-of-experts layers.  A [M_cap, K] holds token rows sorted by
@@ -726,6 +1033,8 @@ B200_API int b200_gemm_bf16_grouped(const void* A, long long lda, const void* B,
   a.expert_ids = expert_ids;
   a.num_valid_rows = num_valid_rows;
   a.row_scale = row_scale;
+  a.m_rot = 0;
+  a.ag = AgArgs{};
   a.ar = ArArgs{};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (epi == kEpiSiluMul) return launch<256, 4, kEpiSiluMul>(tmA, tmB, a, s);

@@ -173,6 +173,12 @@ class ParallelLMHead(VocabParallelEmbedding):
         return F.linear(hidden, self.weight)
 
     def logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        if tp_size() > 1 and ops.use_native(hidden) and hidden.dim() == 2:
+            # GEMM whose epilogue writes this rank's vocabulary block into every peer
+            fg = getattr(get_comm("tp"), "fused_gather", None)
+            lg = fg.gemm_all_gather(hidden, self.weight) if fg is not None else None
+            if lg is not None:
+                return lg[..., : self.vocab_size]
         lg = self._local_logits(hidden)
         if tp_size() > 1:
             lg = get_comm("tp").all_gather(lg, dim=-1)

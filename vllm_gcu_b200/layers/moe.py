@@ -127,13 +127,16 @@ class FusedMoE(nn.Module):
 
     # -- compute -------------------------------------------------------------------
     def forward(self, x: torch.Tensor, topk_w: torch.Tensor, topk_ids: torch.Tensor,
-                add: Optional[torch.Tensor] = None, alpha: float = 1.0) -> torch.Tensor:
-        """Contribution of this rank's experts (partial sum over TP / EP ranks) plus ``add``."""
+                add: Optional[torch.Tensor] = None, alpha: float = 1.0,
+                valid_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Contribution of this rank's experts (partial sum over TP / EP ranks) plus ``add``.
+        ``valid_tokens`` (device int32 scalar) bounds the rows of ``x`` that are in use; rows
+        past it produce unspecified output."""
         if x.shape[0] == 0:
             return x if add is None else add
         if self._interleaved and ops.use_native(x):
             return C.fused_experts(x, self.w13, self.w2, topk_w, topk_ids, self.expert_map,
-                                   add=add, alpha=alpha)
+                                   add=add, alpha=alpha, valid_tokens=valid_tokens)
         w13 = self.w13
         if self._interleaved:    # undo the GPU layout for the reference path
             E, I = w13.shape[0], self.inter
@@ -219,8 +222,16 @@ class SparseMoeBlock(nn.Module):
         self.dp_attention = bool(cfg.extra.get("dp_attention", False))
         self.dispatcher = None
         if self.use_ep and self.dp_attention:
-            from .moe_ep import AllToAllDispatcher
-            self.dispatcher = AllToAllDispatcher(self.experts, cfg)
+            from .moe_ep import AllToAllDispatcher, FusedEPDispatcher
+            fused_ok = (torch.device(device).type == "cuda" and st.ep.world_size <= 8
+                        and cfg.dtype == torch.bfloat16
+                        and cfg.extra.get("ep_backend", "fused") == "fused")
+            if fused_ok:
+                self.dispatcher = FusedEPDispatcher(
+                    self.experts, cfg, int(cfg.extra.get("ep_max_tokens", 8192)),
+                    torch.device(device))
+            else:
+                self.dispatcher = AllToAllDispatcher(self.experts, cfg)
 
     def load_weight(self, name: str, full: torch.Tensor, shard_id=None) -> None:
         if name == "e_score_correction_bias":

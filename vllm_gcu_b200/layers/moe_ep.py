@@ -86,3 +86,138 @@ class AllToAllDispatcher:
         if tok_idx.numel():
             out.index_add_(0, tok_idx, ys.to(out.dtype))
         return out
+
+
+class EPWorkspace:
+    """Dispatch / combine with the peer-memory kernels of ``csrc/ep.cu`` (same contract as
+    :class:`AllToAllDispatcher`).  Rows travel with plain peer stores into symmetric receive
+    buffers; the only hop before data moves is the ep x ep count matrix; every row count stays
+    on the device (``recv_total`` is handed to the expert kernels as their valid-row bound), so
+    a layer is three launches around the expert GEMMs and can be captured in a CUDA graph.
+
+    ``max_tokens`` bounds the tokens of one rank per call; the receive buffer holds
+    ``ep * max_tokens`` rows (every token of every rank can land on one rank).  One
+    workspace serves all MoE layers of a model (``EPWorkspace.get``)."""
+
+    _cache: dict = {}
+
+    @classmethod
+    def get(cls, hidden: int, top_k: int, experts_per_rank: int, max_tokens: int,
+            device: torch.device, group_name: str = "ep") -> "EPWorkspace":
+        key = (hidden, top_k, experts_per_rank, max_tokens, str(device), group_name)
+        if key not in cls._cache:
+            cls._cache[key] = cls(hidden, top_k, experts_per_rank, max_tokens, device, group_name)
+        return cls._cache[key]
+
+    def __init__(self, hidden: int, top_k: int, experts_per_rank: int, max_tokens: int,
+                 device: torch.device, group_name: str = "ep"):
+        import ctypes
+
+        from ..ops import _native
+        from ..parallel.symm import SymmetricBuffer
+        st = get_state()
+        grp = getattr(st, group_name)
+        self.ep = grp.world_size
+        self.rank = grp.rank_in_group
+        assert self.ep <= 8, "the fused dispatch supports up to 8 expert-parallel ranks"
+        self.epr = experts_per_rank
+        self.k = top_k
+        self.H = hidden
+        self.max_tokens = max_tokens
+        self.device = device
+        lib = _native.lib()
+        P, I, L, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+        lib.b200_ep_meta_ints.restype = I
+        lib.b200_ep_route.restype = I
+        lib.b200_ep_route.argtypes = [P, I, I, I, I, I, P, P, P, P, P]
+        lib.b200_ep_dispatch.restype = I
+        lib.b200_ep_dispatch.argtypes = [P, L, P, P, P, I, I, I, I, I, I, P, P, P, P, P, P, P, P, P]
+        lib.b200_ep_combine.restype = I
+        lib.b200_ep_combine.argtypes = [P, L, I, P, P, L, P, L, F, I, I, I, I, P, P, P, P, P, P]
+        ep, k, H = self.ep, self.k, self.H
+        self.recv_cap = ep * max_tokens
+        self.send_cap = max_tokens * min(k, ep)
+
+        def al(n):
+            return -(-n // 256) * 256
+        self.off_cmat = 0
+        self.off_flags = al(2 * ep * ep * 8)                # data_flag | ret_flag, 256 B each
+        self.off_recv_x = self.off_flags + 512
+        self.off_recv_ids = self.off_recv_x + al(self.recv_cap * H * 2)
+        self.off_recv_w = self.off_recv_ids + al(self.recv_cap * k * 4)
+        self.off_ret = self.off_recv_w + al(self.recv_cap * k * 4)
+        total = self.off_ret + al(self.send_cap * H * 2)
+        self.buf = SymmetricBuffer(total, grp.device_group, device)
+        self.meta = torch.zeros(lib.b200_ep_meta_ints(), dtype=torch.int32, device=device)
+        self.words = torch.zeros(8, dtype=torch.int32, device=device)   # epochs and counters
+        self.tok_idx = torch.zeros(max(self.send_cap, 1), dtype=torch.int32, device=device)
+        self.tok_pos = torch.zeros(max(max_tokens, 1) * ep, dtype=torch.int32, device=device)
+        loc = self.buf.local
+        self.recv_x = loc[self.off_recv_x:self.off_recv_x + self.recv_cap * H * 2] \
+            .view(torch.bfloat16).view(self.recv_cap, H)
+        self.recv_ids = loc[self.off_recv_ids:self.off_recv_ids + self.recv_cap * k * 4] \
+            .view(torch.int32).view(self.recv_cap, k)
+        self.recv_w = loc[self.off_recv_w:self.off_recv_w + self.recv_cap * k * 4] \
+            .view(torch.float32).view(self.recv_cap, k)
+        self.recv_total = self.meta[0:1]
+        dist.barrier(group=grp.device_group)
+        torch.cuda.synchronize()
+
+    def _parr(self, off: int):
+        from ..parallel.symm import _ptr_array
+        return _ptr_array(self.buf.peer_ptrs(off))
+
+    def dispatch(self, x: torch.Tensor, topk_w: torch.Tensor, topk_ids: torch.Tensor,
+                 max_tokens_per_rank: Optional[int] = None):
+        """Returns (recv_x, recv_w, recv_ids, recv_total): static-size views of the receive
+        buffers (``ep * max_tokens_per_rank`` rows) and the device scalar of valid rows."""
+        from ..ops._native import call, ptr, stream_ptr
+        T, H = x.shape
+        assert T <= self.max_tokens and H == self.H and x.dtype == torch.bfloat16
+        assert topk_ids.dtype == torch.int32 and topk_w.dtype == torch.float32
+        if T and x.stride(1) != 1:
+            x = x.contiguous()
+        topk_ids = topk_ids.contiguous()
+        topk_w = topk_w.contiguous()
+        w = self.words.data_ptr()
+        call("b200_ep_route", ptr(topk_ids), T, self.k, self.epr, self.ep, self.rank,
+             ptr(self.tok_idx), ptr(self.tok_pos), self._parr(self.off_cmat), w, stream_ptr())
+        call("b200_ep_dispatch", ptr(x) if T else None, x.stride(0) if T else H, ptr(topk_ids),
+             ptr(topk_w), ptr(self.tok_idx), T, H, self.k, self.ep, self.rank, self.recv_cap,
+             self.buf.ptrs[self.rank] + self.off_cmat, self._parr(self.off_recv_x),
+             self._parr(self.off_recv_ids), self._parr(self.off_recv_w),
+             self._parr(self.off_flags), w, w + 4, ptr(self.meta), stream_ptr())
+        rows = self.ep * min(self.max_tokens, max_tokens_per_rank or self.max_tokens)
+        return self.recv_x[:rows], self.recv_w[:rows], self.recv_ids[:rows], self.recv_total
+
+    def combine(self, y: torch.Tensor, T: int, add: Optional[torch.Tensor], alpha: float = 1.0
+                ) -> torch.Tensor:
+        from ..ops._native import call, ptr, stream_ptr
+        out = torch.empty((T, self.H), dtype=torch.bfloat16, device=self.device)
+        w = self.words.data_ptr()
+        call("b200_ep_combine", ptr(y), y.stride(0), y.shape[0], ptr(self.tok_pos), ptr(add),
+             add.stride(0) if add is not None else 0, ptr(out) if T else None, self.H,
+             float(alpha), T, self.H, self.ep, self.rank, ptr(self.meta),
+             self._parr(self.off_ret), self._parr(self.off_flags + 256), w + 8, w + 12,
+             stream_ptr())
+        return out
+
+
+
+class FusedEPDispatcher:
+    """Per-layer front end of :class:`EPWorkspace` (call contract of
+    :class:`AllToAllDispatcher`)."""
+
+    def __init__(self, experts, cfg, max_tokens: int, device: torch.device):
+        self.experts = experts
+        self.ws = EPWorkspace.get(cfg.hidden_size, cfg.num_experts_per_tok,
+                                  experts.local_experts, max_tokens, device)
+
+    def __call__(self, x: torch.Tensor, topk_w: torch.Tensor, topk_ids: torch.Tensor,
+                 shared: Optional[torch.Tensor],
+                 max_tokens_per_rank: Optional[int] = None) -> torch.Tensor:
+        T = x.shape[0]
+        xr, w_r, ids_r, total = self.ws.dispatch(x, topk_w.float(), topk_ids.to(torch.int32),
+                                                 max_tokens_per_rank)
+        yr = self.experts(xr, w_r, ids_r, valid_tokens=total)
+        return self.ws.combine(yr, T, shared)

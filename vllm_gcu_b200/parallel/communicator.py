@@ -34,6 +34,7 @@ class Communicator:
         self.group = group
         self.mode = mode
         self.fused = None          # set by parallel.symm.attach() when available
+        self.fused_gather = None   # gather-fused GEMMs (LM head, sequence-parallel input)
 
     @property
     def world_size(self) -> int:

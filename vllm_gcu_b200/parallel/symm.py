@@ -12,7 +12,14 @@ release / acquire flags at system scope; no TMA load ever targets peer memory.
   two-shot all-reduce (``b200_gemm_bf16_allreduce``), replacing
   ``RowParallelLinear`` + ``GCUCommunicator.all_reduce`` of the reference
   (vllm_gcu/distributed/gcu_communicator.py:88-111);
-* ``all_reduce(x)`` – stand-alone all-reduce for tensors produced elsewhere (embedding).
+* ``all_reduce(x)`` – stand-alone all-reduce for tensors produced elsewhere (embedding);
+* ``gemm_all_gather(x, w_shard)`` – column-parallel GEMM whose epilogue stores its column
+  block into every peer's full-width output (``b200_gemm_bf16_allgather``): the
+  vocabulary-parallel LM head + logits gather of the reference
+  (vllm_gcu/distributed/gcu_communicator.py:112-160 ``gather`` / ``all_gather``);
+* ``all_gather_gemm(x_shard, w)`` – all-gather of sequence-parallel activations fused into
+  the following column-parallel GEMM (``b200_gemm_bf16_gather_a``; the reference runs
+  ``all_gather`` then the matmul, vllm_gcu/patch/sp_model.py).
 
 Every wait inside the kernels is bounded; a timeout is reported through the status word
 (``ops._native.check_status``) and raises ``KernelTimeoutError`` on the host.
@@ -44,6 +51,11 @@ def _register_sigs() -> None:
     lib.b200_gemm_bf16_allreduce.restype = I
     lib.b200_gemm_bf16_allreduce.argtypes = [P, L, P, L, L, I, I, I, P, P, P, P, P, P, I, I, P, L,
                                              I, L, P]
+    lib.b200_gemm_bf16_allgather.restype = I
+    lib.b200_gemm_bf16_allgather.argtypes = [P, L, P, L, L, L, I, I, I, P, P, P, P, P, I, I, P]
+    lib.b200_gemm_bf16_gather_a.restype = I
+    lib.b200_gemm_bf16_gather_a.argtypes = [P, L, P, P, L, P, L, P, L, I, I, I, P, P, P, P, P, P,
+                                            I, I, P]
     lib.b200_allreduce.restype = I
     lib.b200_allreduce.argtypes = [P, P, P, P, P, P, L, I, I, I, P]
     _SIG_DONE = True
@@ -176,6 +188,97 @@ class FusedTP:
         return out
 
 
+class FusedGather:
+    """Workspaces of the two gather-fused GEMMs of one tensor-parallel group."""
+    BM = 128
+
+    def __init__(self, device: torch.device, out_rows: int = 0, out_cols: int = 0,
+                 sp_tokens: int = 0, sp_k: int = 0, group_name: str = "tp"):
+        _register_sigs()
+        st = get_state()
+        grp = getattr(st, group_name)
+        self.p = grp.world_size
+        self.rank = grp.rank_in_group
+        self.device = device
+        pg = grp.device_group
+        self.out_rows, self.out_cols = out_rows, out_cols
+        self.sp_tokens, self.sp_k = sp_tokens, sp_k
+        rows = -(-max(out_rows, 1) // self.BM) * self.BM
+        self.out_bytes = rows * out_cols * 2
+        self.max_tiles = (rows // self.BM) * (-(-max(out_cols, 64) // self.p // 64) + 1)
+        self.ready_bytes = self.max_tiles * self.p * 4
+        self.m_loc_max = -(-max(sp_tokens, 1) // self.p) + 1
+        self.shard_bytes = self.m_loc_max * sp_k * 2
+        self.off_out = 0
+        self.off_ready = -(-self.out_bytes // 256) * 256
+        self.off_shard = self.off_ready + -(-self.ready_bytes // 256) * 256
+        # flag words: in_ready | rd_done | started, 256 bytes each
+        self.off_flags = self.off_shard + -(-self.shard_bytes // 256) * 256
+        self.buf = SymmetricBuffer(self.off_flags + 768, pg, device)
+        self.a_full = torch.empty((max(sp_tokens, 1), max(sp_k, 8)), dtype=torch.bfloat16,
+                                  device=device)
+        self.chunk_ready = torch.zeros(-(-max(sp_tokens, 1) // self.BM) + 1, dtype=torch.int32,
+                                       device=device)
+        self.local_words = torch.zeros(16, dtype=torch.int32, device=device)
+        dist.barrier(group=pg)
+        torch.cuda.synchronize()
+
+    def gemm_all_gather(self, x: torch.Tensor, w: torch.Tensor) -> Optional[torch.Tensor]:
+        """``concat_r(x @ w_r^T)`` on every rank ([M, p * N_local] view of the symmetric
+        output buffer), or None when the problem does not fit."""
+        if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.dim() != 2:
+            return None
+        if x.stride(-1) != 1:
+            x = x.contiguous()
+        M, K = x.shape
+        N = w.shape[0]
+        ldc = N * self.p
+        if M == 0:
+            return x.new_empty(0, ldc)
+        if M > self.out_rows or ldc > self.out_cols or K % 8 or N % 8:
+            return None
+        lib = _native.lib()
+        bn = lib.b200_gemm_ar_tile_n(M, N)
+        if (-(-M // self.BM)) * (-(-N // bn)) > self.max_tiles:
+            return None
+        off_out = self.off_out
+        words = self.local_words.data_ptr()
+        call("b200_gemm_bf16_allgather", ptr(x), x.stride(0), ptr(w), w.stride(0), ldc,
+             self.rank * N, M, N, K, _ptr_array(self.buf.peer_ptrs(off_out)),
+             _ptr_array(self.buf.peer_ptrs(self.off_ready)),
+             _ptr_array(self.buf.peer_ptrs(self.off_flags + 512)), words, words + 4, self.rank,
+             self.p, stream_ptr())
+        return self.buf.local[off_out:off_out + M * ldc * 2].view(torch.bfloat16).view(M, ldc)
+
+    def all_gather_gemm(self, x_shard: torch.Tensor, w: torch.Tensor, sizes: list[int]
+                        ) -> Optional[torch.Tensor]:
+        """``gather_r(x_r) @ w^T`` where rank r passes its ``[sizes[r], K]`` rows (the uneven
+        sequence-parallel split of ``parallel.sp.scatter`` is allowed)."""
+        if x_shard.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x_shard.dim() != 2:
+            return None
+        m_loc, K = x_shard.shape
+        N = w.shape[0]
+        M = sum(sizes)
+        assert len(sizes) == self.p and sizes[self.rank] == m_loc
+        if (M <= 0 or M > self.sp_tokens or K != self.sp_k or max(sizes) > self.m_loc_max
+                or K % 8 or N % 8):
+            return None
+        row_off = (ctypes.c_int * (self.p + 1))()
+        for i, n in enumerate(sizes):
+            row_off[i + 1] = row_off[i] + n
+        shard = self.buf.local[self.off_shard:self.off_shard + m_loc * K * 2] \
+            .view(torch.bfloat16).view(m_loc, K)
+        shard.copy_(x_shard)
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x_shard.device)
+        words = self.local_words.data_ptr()
+        call("b200_gemm_bf16_gather_a", _ptr_array(self.buf.peer_ptrs(self.off_shard)), K, row_off,
+             ptr(self.a_full), self.a_full.stride(0), ptr(w), w.stride(0), ptr(out), N, M, N, K,
+             _ptr_array(self.buf.peer_ptrs(self.off_flags)),
+             _ptr_array(self.buf.peer_ptrs(self.off_flags + 256)), ptr(self.chunk_ready),
+             words + 12, words + 8, words + 16, self.rank, self.p, stream_ptr())
+        return out
+
+
 def attach(cfg) -> Optional[FusedTP]:
     """Creates the fused-TP workspace for the engine configuration and hooks it into the
     tensor-parallel communicator."""
@@ -185,5 +288,12 @@ def attach(cfg) -> Optional[FusedTP]:
     mc = cfg.model
     max_tokens = max(cfg.scheduler.max_num_batched_tokens, cfg.scheduler.max_num_seqs)
     fused = FusedTP(max_tokens, mc.hidden_size, torch.device("cuda", torch.cuda.current_device()))
-    get_comm("tp").fused = fused
+    comm = get_comm("tp")
+    comm.fused = fused
+    # LM head: logits are needed for the sampled rows only (one per sequence, plus the
+    # speculative positions)
+    tp = st.tp.world_size
+    rows = cfg.scheduler.max_num_seqs * (1 + getattr(cfg.speculative, "num_speculative_tokens", 0))
+    padded_vocab = -(-mc.vocab_size // (tp * 64)) * (tp * 64)
+    comm.fused_gather = FusedGather(fused.device, out_rows=max(rows, 128), out_cols=padded_vocab)
     return fused
