@@ -63,3 +63,36 @@ def test_worker_failure_is_detected(what):
             ex.add_request([1, 2, 3], sp)
     finally:
         ex.shutdown()
+
+
+def _dp_cfg():
+    mc = preset("tiny-qwen3-moe")
+    mc.extra["dp_attention"] = True
+    return EngineConfig(model=mc, cache=CacheConfig(block_size=16, num_gpu_blocks=64),
+                        scheduler=SchedulerConfig(max_num_seqs=8, max_num_batched_tokens=64,
+                                                  max_model_len=128),
+                        parallel=ParallelConfig(data_parallel_size=2, enable_expert_parallel=True,
+                                                comm_backend="nccl"),
+                        device="cpu", seed=0)
+
+
+@pytest.mark.timeout(300)
+def test_dp2_ep_executor_keeps_idle_replica_in_step():
+    """Data-parallel attention with expert parallelism: requests are spread over two
+    replicas; with a single request one replica is idle and must still join every
+    expert-parallel exchange (zero-token forward), otherwise the busy one would stall."""
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (9, 30, 4, 21, 13)]
+    ex = MultiprocExecutor(_dp_cfg())
+    try:
+        one = ex.generate(prompts[:1], sp, timeout_s=120)
+        many = ex.generate(prompts, sp, timeout_s=120)
+        ex.check_health()
+    finally:
+        ex.shutdown()
+    assert len(one[0].outputs[0].token_ids) == 6
+    assert [len(o.outputs[0].token_ids) for o in many] == [6] * 5
+    # the first prompt gives the same tokens whether or not the other replica has work:
+    # a request only sees its own tokens and the (replicated or expert-sharded) weights
+    assert many[0].outputs[0].token_ids == one[0].outputs[0].token_ids

@@ -6,6 +6,14 @@ before the next step and broadcasts that count over the gloo group, so all sched
 the same inputs and stay bit-identical while only device collectives cross ranks inside a
 step.  Outputs come from rank 0.
 
+With data parallelism (``data_parallel_size > 1``) the ranks form ``dp`` replicas of
+``tp * pp`` ranks.  The front end routes each request to the replica with the fewest
+requests in flight (the reference patches vLLM's DP load balancer the same way,
+vllm_gcu/patch/patch_0_9_2/engine.py:8-44); the command-count agreement runs inside a
+replica, rank 0 of every replica returns outputs, and all replicas step together as long
+as any of them has work (idle replicas run a zero-token forward so that expert-parallel
+collectives line up).
+
 Failure handling (the reference's executor reports worker exceptions as a ``FAILURE``
 message and shuts the system down, vllm_gcu/v1/executor/async_multiproc_executor.py:92-171):
 
@@ -82,21 +90,29 @@ def _worker_main(rank: int, world: int, port: int, cfg: EngineConfig, cmd_q, out
         engine = LLMEngine(cfg)
         st = get_state()
         ctrl = None
+        dp = pc.data_parallel_size
+        per_replica = world // dp
+        lead = (rank // per_replica) * per_replica           # first rank of this replica
         if world > 1:
-            ctrl = dist.new_group(list(range(world)), backend="gloo")
+            for d in range(dp):                               # every rank joins every new_group
+                ranks = list(range(d * per_replica, (d + 1) * per_replica))
+                g = dist.new_group(ranks, backend="gloo") if len(ranks) > 1 else None
+                if rank in ranks:
+                    ctrl = g
         out_q.put(("READY", rank, engine.runner.num_blocks))
         pending: list[_Cmd] = []
         stop = False
         while not stop:
             hb.value = time.monotonic()
             # 1) agree on the commands applied before this step
-            if rank == 0:
+            if rank == lead:
                 while True:
                     try:
                         pending.append(cmd_q.get_nowait())
                     except queue.Empty:
                         break
-                if not pending and not engine.has_unfinished():
+                if not pending and not engine.has_unfinished() and not (
+                        dp > 1 and engine.dp_global_busy):
                     try:
                         pending.append(cmd_q.get(timeout=0.05))
                     except queue.Empty:
@@ -106,7 +122,7 @@ def _worker_main(rank: int, world: int, port: int, cfg: EngineConfig, cmd_q, out
                 n = 0
             if ctrl is not None:
                 t = torch.tensor([n], dtype=torch.int64)
-                dist.broadcast(t, 0, group=ctrl)
+                dist.broadcast(t, lead, group=ctrl)
                 n = int(t.item())
                 while len(pending) < n:
                     pending.append(cmd_q.get())
@@ -130,9 +146,9 @@ def _worker_main(rank: int, world: int, port: int, cfg: EngineConfig, cmd_q, out
             if stop:
                 break
             # 2) one engine step
-            if engine.has_unfinished():
-                outs = engine.step()
-                if rank == 0 and outs:
+            if engine.has_unfinished() or dp > 1:
+                outs = engine.step()          # dp > 1: every replica joins the exchange
+                if rank == lead and outs:
                     out_q.put(("OUT", outs))
         out_q.put(("STOPPED", rank, None))
     except SystemExit:
@@ -167,6 +183,10 @@ class MultiprocExecutor:
         self.dead: Optional[str] = None
         self._lock = threading.Lock()
         self._ids = 0
+        self.dp = cfg.parallel.data_parallel_size
+        self.per_replica = self.world // self.dp
+        self._replica_of: dict[str, int] = {}
+        self._in_flight = [0] * self.dp
         ready = 0
         deadline = time.monotonic() + start_timeout_s
         while ready < self.world:
@@ -230,8 +250,19 @@ class MultiprocExecutor:
         if request_id is None:
             request_id = f"req-{self._ids}"
             self._ids += 1
-        self._broadcast(_Cmd("add", (request_id, list(prompt_token_ids),
-                                     sampling_params or SamplingParams(), priority, lora_id)))
+        cmd = _Cmd("add", (request_id, list(prompt_token_ids),
+                           sampling_params or SamplingParams(), priority, lora_id))
+        if self.dp == 1:
+            self._broadcast(cmd)
+            return request_id
+        if self.dead:
+            raise EngineDeadError(self.dead)
+        with self._lock:
+            d = min(range(self.dp), key=lambda i: self._in_flight[i])
+            self._in_flight[d] += 1
+            self._replica_of[request_id] = d
+            for r in range(d * self.per_replica, (d + 1) * self.per_replica):
+                self.cmd_qs[r].put(cmd)
         return request_id
 
     def abort_request(self, request_id: str) -> None:
@@ -248,6 +279,12 @@ class MultiprocExecutor:
         while msg is not None:
             if msg[0] == "OUT":
                 outs.extend(msg[1])
+                if self.dp > 1:
+                    for o in msg[1]:
+                        if o.finished:
+                            d = self._replica_of.pop(o.request_id, None)
+                            if d is not None:
+                                self._in_flight[d] -= 1
             elif msg[0] == "FAILURE":
                 self._fail(f"worker {msg[1]} failed:\n{msg[2]}")
             try:

@@ -98,6 +98,11 @@ class LLMEngine:
                                    num_lookahead_tokens=sp.num_speculative_tokens
                                    if sp.method else 0)
         self._ids = itertools.count()
+        self.dp_size = st.dp.world_size
+        self.dp_global_busy = self.dp_size > 1     # learnt from the exchange of every step
+        if self.dp_size > 1:
+            # replicas hold different requests: no replica may run ahead of the exchange
+            cfg.scheduler.async_scheduling = False
         self._pending: deque[tuple[SchedulerOutput, StepHandle]] = deque()
         self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0}
 
@@ -137,8 +142,31 @@ class LLMEngine:
         return self.scheduler.has_unfinished() or bool(self._pending)
 
     # -- stepping ---------------------------------------------------------------------
+    def _dp_exchange(self, num_tokens: int, busy: bool) -> int:
+        """Data-parallel attention: every replica publishes its token count and whether it
+        still has requests (CPU all-gather over gloo, as the reference does for its DP
+        metadata, vllm_gcu/patch/patch_0_9_2/forward_context.py:10-43).  Returns the largest
+        token count; ``dp_global_busy`` tells the caller whether any replica has work."""
+        import torch.distributed as dist
+        st = get_state()
+        mine = torch.tensor([num_tokens, int(busy)], dtype=torch.int64)
+        parts = [torch.zeros_like(mine) for _ in range(self.dp_size)]
+        dist.all_gather(parts, mine, group=st.dp.cpu_group or st.dp.device_group)
+        self.dp_global_busy = any(int(p[1]) for p in parts)
+        mx = max(int(p[0]) for p in parts)
+        st.dp_max_tokens = mx
+        return mx
+
     def _launch(self) -> Optional[tuple[SchedulerOutput, StepHandle]]:
+        busy = self.has_unfinished()
         so = self.scheduler.schedule()
+        if self.dp_size > 1:
+            n_tok = sum(s.num_tokens for s in so.scheduled)
+            mx = self._dp_exchange(n_tok, busy)
+            if so.is_empty and mx > 0:
+                # keep-alive forward: this replica takes part in every expert-parallel
+                # collective of the step with zero tokens
+                self.runner.execute_dummy_batch()
         if so.is_empty:
             self.runner.release(so.finished_req_ids)
             self.runner.release(so.preempted_req_ids)
@@ -188,7 +216,7 @@ class LLMEngine:
         final: dict[str, RequestOutput] = {}
         prev, self.scheduler.emit_partial = self.scheduler.emit_partial, False
         try:
-            while self.has_unfinished():
+            while self.has_unfinished() or self.dp_global_busy:
                 for ro in self.step():
                     if ro.finished:
                         final[ro.request_id] = ro

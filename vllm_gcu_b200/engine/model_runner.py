@@ -311,7 +311,8 @@ class ModelRunner:
 
         batch_has_lora = self.lora is not None and any(s.req.lora_id >= 0 for s in sched)
         use_graph = (self.is_cuda and npf == 0 and self.graphs and nd <= self.graph_sizes[-1]
-                     and self.drafter is None and not batch_has_lora)
+                     and self.drafter is None and not batch_has_lora
+                     and self.cfg.parallel.data_parallel_size == 1)
         B_pad = _pad_batch(nd, self.graph_sizes) if use_graph else B
         T = T_real + (B_pad - B)
 

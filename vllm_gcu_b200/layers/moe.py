@@ -249,7 +249,7 @@ class SparseMoeBlock(nn.Module):
         if self.dispatcher is not None:
             # tokens differ per rank: all-to-all dispatch / combine; the shared experts are
             # replicated so their (TP-partial) output only needs the TP reduction below
-            out = self.dispatcher(x, topk_w, topk_ids, shared)
+            out = self.dispatcher(x, topk_w, topk_ids, shared, get_state().dp_max_tokens)
             tp_partial = shared is not None and tp_size() > 1
             return (get_comm("tp").all_reduce(out) if tp_partial else out).view(shape)
         # For plain top-k routing the scaling factor is applied on the combined output;

@@ -55,7 +55,8 @@ class AllToAllDispatcher:
         self.epr = experts.local_experts
 
     def __call__(self, x: torch.Tensor, topk_w: torch.Tensor, topk_ids: torch.Tensor,
-                 shared: Optional[torch.Tensor]) -> torch.Tensor:
+                 shared: Optional[torch.Tensor],
+                 max_tokens_per_rank: Optional[int] = None) -> torch.Tensor:
         comm = get_comm("ep")
         T, H = x.shape
         k = topk_ids.shape[1]
@@ -219,5 +220,9 @@ class FusedEPDispatcher:
         T = x.shape[0]
         xr, w_r, ids_r, total = self.ws.dispatch(x, topk_w.float(), topk_ids.to(torch.int32),
                                                  max_tokens_per_rank)
-        yr = self.experts(xr, w_r, ids_r, valid_tokens=total)
+        if getattr(self.experts, "_interleaved", False):
+            yr = self.experts(xr, w_r, ids_r, valid_tokens=total)
+        else:           # layout without the grouped-GEMM path: run on the valid rows only
+            n = int(total.item())
+            yr = self.experts(xr[:n], w_r[:n], ids_r[:n]) if n else xr[:0]
         return self.ws.combine(yr, T, shared)

@@ -23,7 +23,14 @@ _REGISTRY: dict[str, str] = {
     "DeepseekV2ForCausalLM": "vllm_gcu_b200.models.deepseek:DeepseekV3ForCausalLM",
     "DeepseekV3ForCausalLM": "vllm_gcu_b200.models.deepseek:DeepseekV3ForCausalLM",
     "DeepSeekMTPModel": "vllm_gcu_b200.models.deepseek_mtp:DeepSeekMTP",
+    # pooling models (no KV cache; built by build_pooling_model)
+    "XLMRobertaForSequenceClassification":
+        "vllm_gcu_b200.models.roberta:XLMRobertaForSequenceClassification",
+    "XLMRobertaModel": "vllm_gcu_b200.models.roberta:RobertaEmbeddingModel",
+    "RobertaModel": "vllm_gcu_b200.models.roberta:RobertaEmbeddingModel",
 }
+
+POOLING_ARCHITECTURES = {"XLMRobertaForSequenceClassification", "XLMRobertaModel", "RobertaModel"}
 
 
 def register_model(arch: str, target: str) -> None:
@@ -46,3 +53,15 @@ def get_model_class(arch: str) -> Callable:
 
 def build_model(cfg, device):
     return get_model_class(cfg.architecture)(cfg, device)
+
+
+def build_pooling_model(hf_config: dict, device="cpu", dtype=None):
+    """Cross-encoder / embedding model from a HuggingFace ``config.json`` dict, wrapped in a
+    ``PoolingRunner`` (``run`` for embeddings or logits, ``score`` for query-document pairs)."""
+    from .roberta import PoolingRunner, RobertaConfig
+    arch = (hf_config.get("architectures") or ["XLMRobertaModel"])[0]
+    if arch not in POOLING_ARCHITECTURES:
+        raise ValueError(f"{arch!r} is not a pooling architecture")
+    over = {"dtype": dtype} if dtype is not None else {}
+    cfg = RobertaConfig.from_hf_dict(hf_config, **over)
+    return PoolingRunner(get_model_class(arch)(cfg, device), device)

@@ -58,6 +58,9 @@ class ParallelState:
         self.ep = _SINGLE("ep")
         self.world = _SINGLE("world")
         self.backend = "none"
+        # data-parallel attention: largest token count of any DP rank in the current step
+        # (None outside a DP step); bounds the rows an expert-parallel rank can receive
+        self.dp_max_tokens = None
 
     def reset(self) -> None:
         self.__init__()
