@@ -23,6 +23,11 @@ SHAPES = [  # (M, N, K, label)
     (256, 28672, 4096, "8B gate_up decode"),
     (256, 4096, 14336, "8B down decode"),
     (256, 128256, 4096, "8B lm_head decode"),
+    (64, 6144, 4096, "8B qkv decode b64"),
+    (64, 28672, 4096, "8B gate_up decode b64"),
+    (64, 4096, 14336, "8B down decode b64"),
+    (256, 2048, 2048, "o_proj tp2 decode"),
+    (256, 4096, 7168, "down tp2 decode"),
     (8192, 8192, 8192, "square 8k"),
 ]
 
@@ -55,6 +60,13 @@ def main():
         t_ours = timeit(lambda: C.gemm_bf16(x, w, out=out), a.iters, flush)
         t_ref = timeit(lambda: torch.matmul(x, w.t(), out=out), a.iters, flush)
         fl = 2.0 * M * N * K
+        if M <= C.SKINNY_MAX_M:          # decode-sized: also time the persistent-tile kernel
+            C.USE_SKINNY_GEMM = False
+            t_tile = timeit(lambda: C.gemm_bf16(x, w, out=out), a.iters, flush)
+            C.USE_SKINNY_GEMM = True
+            ref = x.float() @ w.float().t()
+            err = (C.gemm_bf16(x, w).float() - ref).abs().max().item() / ref.abs().max().item()
+            label = f"{label} [tile kernel {t_tile*1e3:.1f} us, rel err {err:.1e}]"
         print(f"{label:22s} M={M:5d} N={N:6d} K={K:5d}  ours {t_ours*1e3:8.1f} us "
               f"{fl/t_ours/1e9:7.1f} TFLOP/s  w-bw {N*K*2/t_ours/1e6:6.0f} GB/s | cublas "
               f"{t_ref*1e3:8.1f} us {fl/t_ref/1e9:7.1f} TFLOP/s | ratio {t_ref/t_ours:.2f}",

@@ -42,6 +42,34 @@ def test_gemm_bf16(C, M, N, K):
     _close(out, want, 2e-2, 2e-2 * math.sqrt(K) * 0.05)
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 6144, 4096), (256, 4096, 14336), (200, 4096, 4096),
+                                   (129, 28672, 4096), (64, 2048, 2048), (7, 136, 72),
+                                   (256, 128256, 1024), (128, 64, 8192), (256, 1024, 256)])
+def test_gemm_skinny_decode_shapes(C, M, N, K, monkeypatch):
+    """Weight-streaming kernel for M <= 256 (column tile x K slice per CTA, split-K reduce):
+    same result as the fp32 reference, also on repeated launches (the counters must come back
+    to zero) and identical to the persistent-tile kernel within bf16 rounding."""
+    assert C.USE_SKINNY_GEMM and M <= C.SKINNY_MAX_M
+    monkeypatch.setattr(C, "SKINNY_ALLOW_SPLIT", True)      # exercise the split-K path too
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = (torch.randn(N, K, device="cuda") / math.sqrt(K)).to(torch.bfloat16)
+    want = ref.gemm(a, b, out_dtype=torch.float32)
+    first = None
+    for _ in range(3):
+        out = C.gemm_bf16(a, b)
+        _close(out, want, 2e-2, 2e-2)
+        if first is None:
+            first = out.clone()
+        assert torch.equal(out, first), "split-K reduction must be reproducible"
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    _close(C.gemm_bf16(a, b, bias=bias), want + bias.float(), 2e-2, 3e-2)
+    if N % 256 == 0:
+        got = C.gemm_bf16(a, b, epilogue=C.EPI_SILU_MUL)
+        w4 = want.view(M, N // 256, 2, 128)
+        _close(got, (torch.nn.functional.silu(w4[:, :, 0]) * w4[:, :, 1]).reshape(M, N // 2),
+               3e-2, 3e-2)
+
+
 def test_gemm_bf16_epilogues(C):
     torch.manual_seed(1)
     M, N, K = 200, 1024, 512

@@ -39,7 +39,7 @@ enum Epilogue : int {
 };
 
 template <int EPI>
-constexpr int kThreadsFor = (EPI == kEpiGatherA) ? 320 : 192;
+constexpr int kThreadsFor = (EPI == kEpiGatherA || EPI == kEpiAllReduce) ? 320 : 192;
 template <int EPI>
 constexpr bool kPeerEpi = (EPI == kEpiAllReduce || EPI == kEpiAllGather || EPI == kEpiGatherA);
 
@@ -155,7 +155,7 @@ __device__ __forceinline__ bool wait_flag_gpu(const uint32_t* flag, uint32_t wan
   return false;
 }
 
-// Sums `np` bf16 tiles (slot r at base + r * stride) into out rows; 4 vectors in flight per
+// Sums `np` bf16 tiles (slot r at base + r * stride) into out rows; 8 vectors in flight per
 // thread and source so the loads overlap.
 template <int BN_>
 __device__ __forceinline__ void reduce_tile(const __nv_bfloat16* const* srcs, int np,
@@ -163,7 +163,7 @@ __device__ __forceinline__ void reduce_tile(const __nv_bfloat16* const* srcs, in
                                             int N, const __nv_bfloat16* residual, long long ldr,
                                             __nv_bfloat16* const* outs, int nout, long long ldc) {
   constexpr int kVecPerRow = BN_ / 8;
-  constexpr int kU = 4;
+  constexpr int kU = 8;
   for (int v0 = te; v0 < BM * kVecPerRow; v0 += 128 * kU) {
     float acc[kU][8];
 #pragma unroll
@@ -212,14 +212,48 @@ __device__ __forceinline__ void reduce_tile(const __nv_bfloat16* const* srcs, in
 }
 
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int EPI = kEpiNone>
 struct Smem {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kBarOffset = STAGES * kStageBytes;
+  // epilogues that store into peer memory stage the bf16 tile here so that the peer stores
+  // are full, contiguous 128-byte lines instead of one 16-byte piece per row
+  static constexpr int kOutOffset = STAGES * kStageBytes;
+  static constexpr int kOutCols = BN < 128 ? BN : 128;   // columns staged per pass
+  static constexpr int kOutBytes =
+      (EPI == kEpiAllReduce || EPI == kEpiAllGather) ? BM * kOutCols * 2 : 0;
+  static constexpr int kBarOffset = kOutOffset + kOutBytes;
   static constexpr int kTotal = kBarOffset + 256 + 1024;  // barriers + alignment slack
+  static_assert(kTotal <= 232448, "exceeds the shared memory of one CTA");
 };
+
+// Shared staging tile [BM][BN] bf16; the 16-byte chunk index of a row is XORed with the low
+// three bits of the row, so row-per-lane writes and flat reads are both conflict free.
+template <int BN_>
+__device__ __forceinline__ uint32_t stage_off(int row, int chunk) {
+  return static_cast<uint32_t>(row * (BN_ * 2) + ((chunk ^ (row & 7)) << 4));
+}
+// Moves BN_ columns of this thread's accumulator row (32 TMEM columns per step, starting at
+// taddr) into the staging tile.
+template <int BN_>
+__device__ __forceinline__ void stage_tile(uint8_t* stage, uint32_t taddr, int row) {
+#pragma unroll 1
+  for (int c = 0; c < BN_ / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld_32x32(taddr + c * 32, r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint4 u;
+      u.x = pack_bf16x2(__uint_as_float(r[i * 8 + 0]), __uint_as_float(r[i * 8 + 1]));
+      u.y = pack_bf16x2(__uint_as_float(r[i * 8 + 2]), __uint_as_float(r[i * 8 + 3]));
+      u.z = pack_bf16x2(__uint_as_float(r[i * 8 + 4]), __uint_as_float(r[i * 8 + 5]));
+      u.w = pack_bf16x2(__uint_as_float(r[i * 8 + 6]), __uint_as_float(r[i * 8 + 7]));
+      *reinterpret_cast<uint4*>(stage + stage_off<BN_>(row, c * 4 + i)) = u;
+    }
+  }
+}
 
 // Stores 32 consecutive output columns of one row (values in v[0..31]).
 __device__ __forceinline__ void store_row_bf16(__nv_bfloat16* dst, const float* v, int ncols) {
@@ -243,8 +277,8 @@ template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(kThreadsFor<EPI>, 1)
     gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA,
                      const __grid_constant__ CUtensorMap tmB, const Args p) {
-  using L = Smem<BN, STAGES>;
-  constexpr uint32_t kTmemCols = 2 * BN;
+  using L = Smem<BN, STAGES, EPI>;
+  constexpr uint32_t kTmemCols = 2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512);
   constexpr uint32_t kIdesc = make_idesc(BM, BN, 1, 1);
 
   extern __shared__ uint8_t smem_raw[];
@@ -256,6 +290,9 @@ __global__ void __launch_bounds__(kThreadsFor<EPI>, 1)
   uint64_t* tempty_bar = tfull_bar + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  // written by warps 6..9 only (before their named barrier) and read after it, so that all of
+  // them leave their loops in the same iteration
+  volatile uint32_t* aux_abort = tmem_slot + 2;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -270,6 +307,7 @@ __global__ void __launch_bounds__(kThreadsFor<EPI>, 1)
       mbar_init(&tempty_bar[a], 4);
     }
     *abort_flag = 0u;
+    *aux_abort = 0u;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
@@ -374,6 +412,60 @@ __global__ void __launch_bounds__(kThreadsFor<EPI>, 1)
       }
     }
   } else if (warp >= 6) {
+    if constexpr (EPI == kEpiAllReduce) {
+      // ---------------- reducers (warps 6..9): run while the tensor cores work on later tiles
+
+      const int te = threadIdx.x - 192;  // 0..127 among the reducer warps
+      const int np = p.ar.p, rank = p.ar.rank;
+      if (p.ar.oneshot) {
+        // phase 2 (one-shot): every rank reduces every tile from its own slots
+        const __nv_bfloat16* srcs[kMaxPeers];
+        for (int r = 0; r < kMaxPeers; ++r)
+          srcs[r] = p.ar.partial[rank] +
+                    (static_cast<long long>(epoch & 1u) * np + (r < np ? r : 0)) * p.ar.slot_elems;
+        __nv_bfloat16* outs[1] = {p.ar.out[rank]};
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+          bool ok = true;
+          if (te < np)
+            ok = wait_flag_sys(p.ar.ready[rank] + static_cast<long long>(t) * np + te, epoch);
+          if (!ok) {
+            report_status(p.status, kStatusFlagTimeout, kKernelId, 0x500u + te);
+            *aux_abort = 1u;
+          }
+          gather_bar_sync();
+          if (*aux_abort != 0u) break;
+          reduce_tile<BN>(srcs, np, static_cast<long long>(t) * (BM * BN), te,
+                          (t % p.tiles_m) * BM, (t / p.tiles_m) * BN, p.M, p.N, p.residual, p.ldr,
+                          outs, 1, p.ldc);
+        }
+      } else {
+        // phase 2 (two-shot): reduce the tiles this rank owns (tile % p == rank), broadcast
+        for (int t = rank + static_cast<int>(blockIdx.x) * np; t < num_tiles;
+             t += gridDim.x * np) {
+          bool ok = true;
+          if (te < np)
+            ok = wait_flag_sys(p.ar.ready[rank] + static_cast<long long>(t) * np + te, epoch);
+          if (!ok) {
+            report_status(p.status, kStatusFlagTimeout, kKernelId, 0x500u + te);
+            *aux_abort = 1u;
+          }
+          gather_bar_sync();
+          if (*aux_abort != 0u) break;
+          reduce_tile<BN>(p.ar.partial, np, static_cast<long long>(t) * (BM * BN), te,
+                          (t % p.tiles_m) * BM, (t / p.tiles_m) * BN, p.M, p.N, p.residual, p.ldr,
+                          p.ar.out, np, p.ldc);
+          gather_bar_sync();
+          if (te < np) signal_flag_sys(p.ar.done[te] + t, epoch);
+        }
+        // phase 3: the result is complete on this rank once every tile reports done
+        for (int t = te; t < num_tiles && *aux_abort == 0u; t += 128) {
+          if (!wait_flag_sys(p.ar.done[rank] + t, epoch)) {
+            report_status(p.status, kStatusFlagTimeout, kKernelId, 0x600u);
+            *aux_abort = 1u;
+          }
+        }
+      }
+    }
     // ---------------- A gather (warps 6..9, gathered-A variant only) ----------------
     if constexpr (EPI == kEpiGatherA) {
       const int tg = threadIdx.x - 192;  // 0..127
@@ -390,11 +482,11 @@ __global__ void __launch_bounds__(kThreadsFor<EPI>, 1)
         if (tg >= o0 && tg <= o1 && tg != rank) {
           if (!wait_flag_sys(p.ag.in_ready[rank] + tg, epoch)) {
             report_status(p.status, kStatusFlagTimeout, kKernelId, 0x710u + tg);
-            *abort_flag = 1u;
+            *aux_abort = 1u;
           }
         }
         gather_bar_sync();
-        if (*abort_flag != 0u) break;
+        if (*aux_abort != 0u) break;
         const int nvec = (r1 - r0) * kvec;
         constexpr int kU = 8;
         for (int v0 = tg; v0 < nvec; v0 += 128 * kU) {
@@ -438,7 +530,7 @@ __global__ void __launch_bounds__(kThreadsFor<EPI>, 1)
         }
       }
       // the shard may be overwritten after this kernel: wait until every reader is done
-      if (blockIdx.x == 0 && tg < np && *abort_flag == 0u) {
+      if (blockIdx.x == 0 && tg < np && *aux_abort == 0u) {
         if (!wait_flag_sys(p.ag.rd_done[rank] + tg, epoch))
           report_status(p.status, kStatusFlagTimeout, kKernelId, 0x720u + tg);
       }
@@ -493,28 +585,40 @@ __global__ void __launch_bounds__(kThreadsFor<EPI>, 1)
       } else if constexpr (EPI == kEpiAllReduce) {
         // phase 1: publish the bf16 partial tile.  Two-shot: park it in this GPU's own
         // symmetric buffer and tell the tile's owner.  One-shot: push it into the slot
-        // (epoch parity, this rank) of every peer and tell every peer.
-        const long long tile_elems = static_cast<long long>(tile) * (BM * BN) + (q * 32 + lane) * BN;
+        // (epoch parity, this rank) of every peer and tell every peer.  The tile goes
+        // through the staging buffer so that every store instruction of a warp covers 512
+        // contiguous bytes of the (contiguous) tile in the destination.
+        uint8_t* stage = smem + L::kOutOffset;
+        constexpr int SC = L::kOutCols;            // staged columns per pass
+        constexpr int kChunksPerRow = SC / 8;
+        const int te1 = threadIdx.x - 64;
+        const long long tile_elems = static_cast<long long>(tile) * (BM * BN);
         const long long slot_off =
             p.ar.oneshot ? (static_cast<long long>(epoch & 1u) * p.ar.p + p.ar.rank) * p.ar.slot_elems
                          : 0;
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + c * 32, r);
-          tmem_ld_wait();
-          float v[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-          if (p.ar.oneshot) {
-            for (int pr = 0; pr < p.ar.p; ++pr)
-              store_row_bf16(p.ar.partial[pr] + slot_off + tile_elems + c * 32, v, 32);
-          } else {
-            store_row_bf16(p.ar.partial[p.ar.rank] + tile_elems + c * 32, v, 32);
+        for (int h = 0; h < BN / SC; ++h) {
+          stage_tile<SC>(stage, taddr + h * SC, q * 32 + lane);
+          if (h == BN / SC - 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty_bar[acc]);   // the accumulator is free again
           }
+          epi_bar_sync();
+#pragma unroll 2
+          for (int v = te1; v < BM * kChunksPerRow; v += 128) {
+            const int rr = v / kChunksPerRow, cc = v % kChunksPerRow;
+            const uint4 u = *reinterpret_cast<const uint4*>(stage + stage_off<SC>(rr, cc));
+            const long long off = tile_elems + rr * BN + h * SC + cc * 8;
+            if (p.ar.oneshot) {
+              for (int pr = 0; pr < p.ar.p; ++pr)
+                *reinterpret_cast<uint4*>(p.ar.partial[pr] + slot_off + off) = u;
+            } else {
+              *reinterpret_cast<uint4*>(p.ar.partial[p.ar.rank] + off) = u;
+            }
+          }
+          epi_bar_sync();
         }
-        epi_bar_sync();
-        const int te1 = threadIdx.x - 64;
         if (p.ar.oneshot) {
           if (te1 < p.ar.p)
             signal_flag_sys(p.ar.ready[te1] + static_cast<long long>(tile) * p.ar.p + p.ar.rank,
@@ -525,23 +629,31 @@ __global__ void __launch_bounds__(kThreadsFor<EPI>, 1)
                           epoch);
         }
       } else if constexpr (EPI == kEpiAllGather) {
-        // store this rank's column block of the tile into every peer's full-width output
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + c * 32, r);
-          tmem_ld_wait();
-          const int col = n0 + c * 32;
-          if (!row_ok || col >= p.N) continue;
-          const int ncols = min(32, p.N - col);
-          float v[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-          const long long off = static_cast<long long>(row) * p.ldc + p.ar.col_off + col;
-          for (int pr = 0; pr < p.ar.p; ++pr) store_row_bf16(p.ar.out[pr] + off, v, ncols);
-        }
-        epi_bar_sync();
+        // store this rank's column block of the tile into every peer's full-width output;
+        // staged so that a warp writes whole row segments (BN * 2 contiguous bytes per row)
+        uint8_t* stage = smem + L::kOutOffset;
+        constexpr int SC = L::kOutCols;
+        constexpr int kChunksPerRow = SC / 8;
         const int te1 = threadIdx.x - 64;
+#pragma unroll 1
+        for (int h = 0; h < BN / SC; ++h) {
+          stage_tile<SC>(stage, taddr + h * SC, q * 32 + lane);
+          if (h == BN / SC - 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+          }
+          epi_bar_sync();
+          for (int v = te1; v < BM * kChunksPerRow; v += 128) {
+            const int rr = v / kChunksPerRow, cc = v % kChunksPerRow;
+            const int grow = m0 + rr, gcol = n0 + h * SC + cc * 8;
+            if (grow >= p.M || gcol >= p.N) continue;
+            const uint4 u = *reinterpret_cast<const uint4*>(stage + stage_off<SC>(rr, cc));
+            const long long off = static_cast<long long>(grow) * p.ldc + p.ar.col_off + gcol;
+            for (int pr = 0; pr < p.ar.p; ++pr) *reinterpret_cast<uint4*>(p.ar.out[pr] + off) = u;
+          }
+          epi_bar_sync();
+        }
         if (te1 < p.ar.p)
           signal_flag_sys(p.ar.ready[te1] + static_cast<long long>(tile) * p.ar.p + p.ar.rank,
                           epoch);
@@ -586,9 +698,11 @@ __global__ void __launch_bounds__(kThreadsFor<EPI>, 1)
           }
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if constexpr (EPI != kEpiAllReduce && EPI != kEpiAllGather) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
@@ -603,58 +717,6 @@ __global__ void __launch_bounds__(kThreadsFor<EPI>, 1)
             !wait_flag_sys(p.ar.ready[rank] + static_cast<long long>(t) * np + te, epoch)) {
           report_status(p.status, kStatusFlagTimeout, kKernelId, 0x800u + te);
           *abort_flag = 1u;
-        }
-      }
-    }
-    if constexpr (EPI == kEpiAllReduce) {
-      const int te = threadIdx.x - 64;  // 0..127 among the epilogue warps
-      const int np = p.ar.p, rank = p.ar.rank;
-      if (p.ar.oneshot) {
-        // phase 2 (one-shot): every rank reduces every tile from its own slots
-        const __nv_bfloat16* srcs[kMaxPeers];
-        for (int r = 0; r < kMaxPeers; ++r)
-          srcs[r] = p.ar.partial[rank] +
-                    (static_cast<long long>(epoch & 1u) * np + (r < np ? r : 0)) * p.ar.slot_elems;
-        __nv_bfloat16* outs[1] = {p.ar.out[rank]};
-        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-          bool ok = true;
-          if (te < np)
-            ok = wait_flag_sys(p.ar.ready[rank] + static_cast<long long>(t) * np + te, epoch);
-          if (!ok) {
-            report_status(p.status, kStatusFlagTimeout, kKernelId, 0x500u + te);
-            *abort_flag = 1u;
-          }
-          epi_bar_sync();
-          if (*abort_flag != 0u) break;
-          reduce_tile<BN>(srcs, np, static_cast<long long>(t) * (BM * BN), te,
-                          (t % p.tiles_m) * BM, (t / p.tiles_m) * BN, p.M, p.N, p.residual, p.ldr,
-                          outs, 1, p.ldc);
-        }
-      } else {
-        // phase 2 (two-shot): reduce the tiles this rank owns (tile % p == rank), broadcast
-        for (int t = rank + static_cast<int>(blockIdx.x) * np; t < num_tiles;
-             t += gridDim.x * np) {
-          bool ok = true;
-          if (te < np)
-            ok = wait_flag_sys(p.ar.ready[rank] + static_cast<long long>(t) * np + te, epoch);
-          if (!ok) {
-            report_status(p.status, kStatusFlagTimeout, kKernelId, 0x500u + te);
-            *abort_flag = 1u;
-          }
-          epi_bar_sync();
-          if (*abort_flag != 0u) break;
-          reduce_tile<BN>(p.ar.partial, np, static_cast<long long>(t) * (BM * BN), te,
-                          (t % p.tiles_m) * BM, (t / p.tiles_m) * BN, p.M, p.N, p.residual, p.ldr,
-                          p.ar.out, np, p.ldc);
-          epi_bar_sync();
-          if (te < np) signal_flag_sys(p.ar.done[te] + t, epoch);
-        }
-        // phase 3: the result is complete on this rank once every tile reports done
-        for (int t = te; t < num_tiles && *abort_flag == 0u; t += 128) {
-          if (!wait_flag_sys(p.ar.done[rank] + t, epoch)) {
-            report_status(p.status, kStatusFlagTimeout, kKernelId, 0x600u);
-            *abort_flag = 1u;
-          }
         }
       }
     }
@@ -678,7 +740,7 @@ __global__ void __launch_bounds__(kThreadsFor<EPI>, 1)
 
 template <int BN, int STAGES, int EPI>
 int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const Args& a, cudaStream_t stream) {
-  using L = Smem<BN, STAGES>;
+  using L = Smem<BN, STAGES, EPI>;
   auto kern = gemm_bf16_kernel<BN, STAGES, EPI>;
   static bool configured[64] = {false};
   int dev = 0;
@@ -720,13 +782,27 @@ B200_API int b200_gemm_bf16(const void* A, long long lda, const void* B, long lo
   if (epi == kEpiBias && bias == nullptr) return -5;
   if (epi == kEpiResidual && residual == nullptr) return -5;
 
-  // Tile width: wide tiles when there is enough work to fill the machine with them,
-  // narrow ones when the problem is small (decode) so that more SMs stream weights.
+  // Tile width: the candidate with the smallest (waves over the SMs) x (tile width + the
+  // activation tile's share of the shared-memory fill).  Wide tiles win when there is enough
+  // work; for decode-sized M a width that yields one full wave wins (6144 columns: 96).
   const int tiles_m = (M + BM - 1) / BM;
-  const bool wide = (epi == kEpiSiluMul) ||
-                    ((N % 256) == 0 && static_cast<long long>(tiles_m) * (N / 256) >= sm_count());
-  const bool narrow = !wide && static_cast<long long>(tiles_m) * ((N + 127) / 128) < sm_count();
-  const int bn = wide ? 256 : (narrow ? 64 : 128);
+  int bn = 256;
+  if (epi != kEpiSiluMul) {
+    const int cands[4] = {256, 128, 96, 64};
+    long long best = -1;
+    for (int i = 0; i < 4; ++i) {
+      const int c = cands[i];
+      if (c == 256 && (N % 256) != 0) continue;
+      const long long tiles = static_cast<long long>(tiles_m) * ((N + c - 1) / c);
+      const long long waves = (tiles + sm_count() - 1) / sm_count();
+      const long long cost = waves * (c + 32);
+      if (best < 0 || cost < best) {
+        best = cost;
+        bn = c;
+      }
+    }
+  }
+  const bool wide = bn == 256;
 
   CUtensorMap tmA, tmB;
   int r = encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, static_cast<uint64_t>(M),
@@ -761,7 +837,8 @@ B200_API int b200_gemm_bf16(const void* A, long long lda, const void* B, long lo
 #define B200_GEMM_CASE(E)                                                       \
   case E:                                                                       \
     if (wide) return launch<256, 4, E>(tmA, tmB, a, s);                         \
-    if (narrow) return launch<64, 8, E>(tmA, tmB, a, s);                        \
+    if (bn == 64) return launch<64, 8, E>(tmA, tmB, a, s);                      \
+    if (bn == 96) return launch<96, 6, E>(tmA, tmB, a, s);                      \
     return launch<128, 6, E>(tmA, tmB, a, s);
   switch (epi) {
     B200_GEMM_CASE(kEpiNone)
@@ -792,6 +869,7 @@ B200_API int b200_gemm_bf16(const void* A, long long lda, const void* B, long lo
 B200_API int b200_gemm_ar_tile_n(int M, int N) {
   using namespace b200;
   const int tiles_m = (M + b200::gemm::BM - 1) / b200::gemm::BM;
+  if ((N % 256) == 0 && static_cast<long long>(tiles_m) * (N / 256) >= sm_count()) return 256;
   return (static_cast<long long>(tiles_m) * ((N + 127) / 128) < sm_count()) ? 64 : 128;
 }
 
@@ -847,6 +925,7 @@ B200_API int b200_gemm_bf16_allreduce(const void* A, long long lda, const void* 
   a.ar.slot_elems = slot_elems;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (bn == 64) return launch<64, 8, kEpiAllReduce>(tmA, tmB, a, s);
+  if (bn == 256) return launch<256, 4, kEpiAllReduce>(tmA, tmB, a, s);
   return launch<128, 6, kEpiAllReduce>(tmA, tmB, a, s);
 }
 
@@ -913,6 +992,7 @@ B200_API int b200_gemm_bf16_allgather(const void* A, long long lda, const void* 
   a.ar.col_off = col_off;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (bn == 64) return launch<64, 8, kEpiAllGather>(tmA, tmB, a, s);
+  if (bn == 256) return launch<256, 4, kEpiAllGather>(tmA, tmB, a, s);
   return launch<128, 6, kEpiAllGather>(tmA, tmB, a, s);
 }
 

@@ -119,6 +119,8 @@ class ModelRunner:
         self.timing_events: Optional[list] = None  # set to a list to time every step
         self.timing_meta: list = []                # (decodes, prefills, tokens) per timed step
         self.keep_logits = False                   # debugging / tests: keep last step's logits
+        from .. import envs
+        self.nvtx = bool(envs.NVTX) and self.is_cuda
         self.last_logits: Optional[torch.Tensor] = None
         self._alloc_buffers()
 
@@ -501,6 +503,9 @@ class ModelRunner:
             sample_indices=self.sample_indices[:max(ns * width, 1)],
             q_lens_cpu=[int(x) for x in ntok], seq_lens_cpu=[int(x) for x in seq_after])
 
+        if self.nvtx:
+            torch.cuda.nvtx.range_push("decode_step" if npf == 0 else
+                                       ("prefill_step" if nd == 0 else "mixed_step"))
         if use_graph:
             key = (B_pad, cur, all_greedy)
             self.graphs[key].replay()
@@ -508,6 +513,8 @@ class ModelRunner:
         else:
             with torch.inference_mode():
                 self._forward_and_sample(md, T, ns, out_ids, all_greedy, width)
+        if self.nvtx:
+            torch.cuda.nvtx.range_pop()
 
         # device -> host (asynchronous; consumed by StepHandle.token_ids)
         host = self.sampled_host[cur]

@@ -51,6 +51,9 @@ environment_variables: dict[str, Callable[[], Any]] = {
     "ORACLE": lambda: None if _get("ORACLE") is None else _get("ORACLE").split(","),
     # communication backend of the tensor-parallel collectives: fused | nccl
     "COMM": lambda: _get("COMM", "fused"),
+    # NVTX range around every engine step, named by its kind (the reference opens a vendor
+    # profiler range per step, vllm_gcu/worker/worker_v1.py:322-335)
+    "NVTX": _flag("NVTX"),
     "NIXL_ENABLE_FULL_KV_TRANSFER": _flag("NIXL_ENABLE_FULL_KV_TRANSFER"),
     "NIXL_ENABLE_FIRST_TOKEN_REUSE": _flag("NIXL_ENABLE_FIRST_TOKEN_REUSE"),
 }

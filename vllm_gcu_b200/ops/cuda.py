@@ -6,6 +6,7 @@ kernels' own guards (status word, see ``_native.check_status``).
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Optional, Sequence
 
 import torch
@@ -36,6 +37,27 @@ def _rowmajor_2d(t: torch.Tensor) -> torch.Tensor:
 # ---------------------------------------------------------------------------
 # GEMM
 # ---------------------------------------------------------------------------
+# Decode-sized activations (M <= 256) take the weight-streaming kernel of gemm_skinny.cu.
+USE_SKINNY_GEMM = True
+SKINNY_ALLOW_SPLIT = False      # K-split plans lose to the persistent-tile kernel (measured)
+SKINNY_MAX_M = 256
+_SKINNY_WS: dict = {}
+
+
+def _skinny_workspace(device: torch.device):
+    """Per (device, stream) split-K workspace: fp32 partial sums + zeroed counters."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    w = _SKINNY_WS.get(key)
+    if w is None:
+        nbytes = ctypes.c_longlong()
+        nctr = ctypes.c_int()
+        N.lib().b200_gemm_skinny_workspace(1 << 20, ctypes.byref(nbytes), ctypes.byref(nctr))
+        w = (torch.empty(nbytes.value // 4, dtype=torch.float32, device=device),
+             torch.zeros(nctr.value, dtype=torch.int32, device=device))
+        _SKINNY_WS[key] = w
+    return w
+
+
 def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None,
               bias: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
               epilogue: int = EPI_NONE) -> torch.Tensor:
@@ -57,6 +79,16 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = No
         out = torch.empty((M, out_cols), device=a.device,
                           dtype=torch.float32 if epilogue == EPI_FP32 else torch.bfloat16)
     assert out.stride(-1) == 1 and out.shape[-1] == out_cols
+    if M <= SKINNY_MAX_M and USE_SKINNY_GEMM and epilogue in (EPI_NONE, EPI_BIAS, EPI_SILU_MUL):
+        ws, ctr = _skinny_workspace(a.device)
+        rc = N.lib().b200_gemm_skinny(
+            ptr(a), a.stride(0), ptr(b), b.stride(0), ptr(out), out.stride(0), M, Nn, K,
+            ptr(bias), epilogue, ptr(ws), ptr(ctr), int(SKINNY_ALLOW_SPLIT), stream_ptr())
+        N.launch_count += 1
+        if rc == 0:
+            return out
+        if rc != -20:
+            raise N.NativeError(f"b200_gemm_skinny failed with code {rc}")
     call("b200_gemm_bf16", ptr(a), a.stride(0), ptr(b), b.stride(0), ptr(out), out.stride(0),
          M, Nn, K, ptr(bias), ptr(residual), residual.stride(0) if residual is not None else 0,
          epilogue, stream_ptr())

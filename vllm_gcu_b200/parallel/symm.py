@@ -125,6 +125,7 @@ class FusedTP:
         self.buf = SymmetricBuffer(total, pg, device)
         self.local_words = torch.zeros(16, dtype=torch.int32, device=device)  # epoch, ctr, ...
         self.out_sel = 0
+        self.force_mode: Optional[str] = None     # benchmarks: "oneshot" | "twoshot"
         dist.barrier(group=pg)
         torch.cuda.synchronize()
 
@@ -161,8 +162,14 @@ class FusedTP:
              _ptr_array(self.buf.peer_ptrs(self.off_done)),
              words, words + 4, self.rank, self.p, ptr(residual),
              residual.stride(0) if residual is not None else 0,
-             int(-(-M // self.BM) * self.BM <= self.oneshot_rows), self.slot_elems, stream_ptr())
+             int(self._oneshot(M)), self.slot_elems, stream_ptr())
         return out_local.view(*shape[:-1], N)
+
+    def _oneshot(self, M: int) -> bool:
+        fits = -(-M // self.BM) * self.BM <= self.oneshot_rows
+        if self.force_mode == "twoshot":
+            return False
+        return fits
 
     def all_reduce(self, x: torch.Tensor) -> Optional[torch.Tensor]:
         """Two-shot all-reduce of a bf16 tensor through the symmetric workspace (pull the
