@@ -64,9 +64,14 @@ def main():
     btp = bt[:nseq, : (ql + bs - 1) // bs].contiguous()
     outp = torch.empty_like(qp)
     tiles = nseq * (ql // 64)
-    ms = timeit(lambda: C.varlen_prefill(qp, kc, vc, btp, cu, slp, scale, tiles, out=outp))
     fl = 4.0 * nseq * Hq * D * ql * ql / 2
-    print(f"prefill {nseq}x{ql}: {ms*1e3:8.1f} us  {fl/ms/1e9:7.1f} TFLOP/s (causal)", flush=True)
+    for name, flag in (("tcgen05", True), ("mma.sync", False)):
+        C.USE_FMHA_PREFILL = flag
+        ms = timeit(lambda: C.varlen_prefill(qp, kc, vc, btp, cu, slp, scale, tiles, out=outp,
+                                             num_q_tiles_128=nseq * (ql // 128)))
+        print(f"prefill {name:8s} {nseq}x{ql}: {ms*1e3:8.1f} us  {fl/ms/1e9:7.1f} TFLOP/s (causal)",
+              flush=True)
+    C.USE_FMHA_PREFILL = True
 
 
 if __name__ == "__main__":

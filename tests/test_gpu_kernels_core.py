@@ -221,6 +221,43 @@ def test_varlen_prefill(C, Hq, Hkv, D):
     _close(lse, lse_r, 1e-2, 1e-2)
 
 
+@pytest.mark.parametrize("Hq,Hkv", [(8, 2), (4, 4), (8, 1)])
+@pytest.mark.parametrize("window", [0, 100])
+def test_fmha_prefill_tcgen05(C, Hq, Hkv, window):
+    """tcgen05 prefill attention (128-row query tiles, scores and output in tensor memory):
+    long and short sequences, cached prefixes, tiles that end inside a page, sliding window;
+    also equal to the mma.sync kernel within bf16 rounding."""
+    torch.manual_seed(17)
+    D = 128
+    q_lens = [5, 64, 130, 1, 77, 300, 1024, 128]
+    ctx = [0, 16, 50, 200, 3, 500, 0, 128]
+    lens = [a + b for a, b in zip(q_lens, ctx)]
+    B = len(lens)
+    kc, vc, bt = _make_paged(B, lens, Hkv, D, 16)
+    T = sum(q_lens)
+    q = torch.randn(T, Hq, D, device="cuda", dtype=torch.bfloat16)
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), device="cuda",
+                      dtype=torch.int32)
+    sl = torch.tensor(lens, device="cuda", dtype=torch.int32)
+    tiles = sum((x + 63) // 64 for x in q_lens)
+    scale = D ** -0.5
+    assert C.USE_FMHA_PREFILL
+    got, lse = C.varlen_prefill(q, kc, vc, bt, cu, sl, scale, tiles, window=window,
+                                return_lse=True)
+    C.USE_FMHA_PREFILL = False
+    try:
+        old, lse_old = C.varlen_prefill(q, kc, vc, bt, cu, sl, scale, tiles, window=window,
+                                        return_lse=True)
+    finally:
+        C.USE_FMHA_PREFILL = True
+    _close(got, old, 2e-2, 2e-2)
+    _close(lse, lse_old, 1e-2, 1e-2)
+    if window == 0:
+        want, lse_r = ref.varlen_prefill_attention(q, kc, vc, bt, cu, sl, scale, return_lse=True)
+        _close(got, want, 2e-2, 2e-2)
+        _close(lse, lse_r, 1e-2, 1e-2)
+
+
 def test_sampler(C):
     torch.manual_seed(8)
     B, V = 9, 32000

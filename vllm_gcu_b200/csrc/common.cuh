@@ -255,6 +255,28 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// Stores 32 consecutive fp32 columns of this thread's TMEM lane (counterpart of
+// tmem_ld_32x32); complete after tmem_st_wait().
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      :
+      : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]),
+        "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+        "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+        "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+// Makes generic-proxy writes to shared memory visible to the async proxy (TMA, tcgen05.mma).
+__device__ __forceinline__ void fence_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
 
 // Shared-memory matrix descriptor for a K-major operand tile stored as rows of
 // 128 bytes with the 128-byte swizzle that TMA SWIZZLE_128B produces.  Eight
@@ -270,6 +292,23 @@ __device__ __forceinline__ uint64_t make_desc_k_sw128(uint32_t smem_addr) {
   d |= static_cast<uint64_t>(2) << 61;                       // SWIZZLE_128B
   return d;
 }
+
+// Descriptor of an MN-major operand tile (the contraction index runs over rows of 128 bytes,
+// 64 elements of the M/N extent are contiguous in a row; this is how a [keys, head_dim] value
+// tile lands in shared memory under TMA SWIZZLE_128B).  Eight rows form a 1024-byte atom and
+// atoms follow each other along K (stride byte offset 1024); the next 64 elements of the M/N
+// extent start `mn_chunk_bytes` further (leading byte offset).  A step of 16 along K advances
+// the start address by 2048 bytes.  Needs the MN-major bit of the instruction descriptor.
+__device__ __forceinline__ uint64_t make_desc_mn_sw128(uint32_t smem_addr, uint32_t mn_chunk_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((mn_chunk_bytes >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+constexpr uint32_t kIdescBMajorMN = 1u << 16;   // instruction descriptor: B operand is MN-major
 
 // Instruction descriptor, dense, fp32 accumulate, both operands K-major.
 // fmt: 0 = f16, 1 = bf16 for kind::f16; 0 = e4m3, 1 = e5m2 for kind::f8f6f4.

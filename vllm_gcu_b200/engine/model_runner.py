@@ -497,6 +497,7 @@ class ModelRunner:
             block_tables=self.block_tables[:max(B_pad, B)], seq_lens=self.seq_lens[:max(B_pad, B)],
             cu_q_prefill=self.cu_q[:npf + 1] if npf else None,
             num_q_tiles=int(((ntok[nd:] + 63) // 64).sum()) if npf else 0,
+            num_q_tiles_128=int(((ntok[nd:] + 127) // 128).sum()) if npf else 0,
             max_seq_len=max_seq_len,
             decode_splits=self._decode_splits(B_pad if use_graph else max(nd, 1), max_seq_len),
             decode_workspace=self.decode_ws,

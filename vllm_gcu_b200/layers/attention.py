@@ -38,6 +38,7 @@ class AttentionMetadata:
     seq_lens: torch.Tensor               # [B] int32, kv length after this step
     cu_q_prefill: Optional[torch.Tensor] = None   # [num_prefills + 1] int32, relative
     num_q_tiles: int = 0                 # sum ceil(q_len / 64) over prefills (host value)
+    num_q_tiles_128: Optional[int] = None  # the same for 128-row tiles (tcgen05 kernel)
     max_seq_len: int = 0
     decode_splits: int = 1
     decode_workspace: Optional[tuple[torch.Tensor, torch.Tensor]] = None
@@ -105,7 +106,7 @@ class PagedAttention(nn.Module):
                              md.cu_q_prefill,
                              md.seq_lens[md.num_decodes:md.num_decodes + md.num_prefills],
                              self.scale, md.num_q_tiles, out=out[nd:].view(npf, Hq, D),
-                             window=self.window)
+                             window=self.window, num_q_tiles_128=md.num_q_tiles_128)
         return out
 
     # -- CPU reference ----------------------------------------------------------

@@ -96,6 +96,8 @@ class _Sigs:
     b200_paged_decode_tma = [P, L, P, L, P, P, L, L, L, P, I, I, P, P, P, I, I, I, I, I, F, I, P]
     b200_varlen_prefill = [P, L, P, L, P, P, P, P, P, L, L, L, P, I, I, I, I, I, I, I, I, F,
                            I, I, I, P]
+    b200_fmha_prefill = [P, L, P, L, P, P, P, P, P, L, L, L, P, I, I, I, I, I, I, I, I, F,
+                         I, I, I, P]
     b200_merge_attn_states = [P, P, P, P, P, P, I, I, I, I, P]
     b200_sample = [P, L, I, I, I, P, P, P, P, P, L, P, P]
     b200_top_k_top_p = [P, L, I, I, I, P, P, P]

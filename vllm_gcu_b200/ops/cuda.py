@@ -333,17 +333,35 @@ def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     return out
 
 
+USE_FMHA_PREFILL = True      # tcgen05 prefill attention for bf16 / head_dim 128
+
+
 def varlen_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                    block_tables: torch.Tensor, cu_q: torch.Tensor, seq_lens: torch.Tensor,
                    scale: float, num_q_tiles: int, out: Optional[torch.Tensor] = None,
-                   causal: bool = True, window: int = 0, return_lse: bool = False):
-    """q ``[T, Hq, D]``; ``num_q_tiles`` >= sum_b ceil(q_len_b / 64) (host-known)."""
+                   causal: bool = True, window: int = 0, return_lse: bool = False,
+                   num_q_tiles_128: Optional[int] = None):
+    """q ``[T, Hq, D]``; ``num_q_tiles`` >= sum_b ceil(q_len_b / 64) (host-known);
+    ``num_q_tiles_128`` the same for 128-row tiles (defaults to the 64-row bound)."""
     T, Hq, D = q.shape
     nb, bs, Hkv, _ = k_cache.shape
     assert q.stride(2) == 1 and q.stride(1) == D
     if out is None:
         out = torch.empty((T, Hq, D), device=q.device, dtype=q.dtype)
     lse = torch.empty((Hq, T), device=q.device, dtype=torch.float32) if return_lse else None
+    if USE_FMHA_PREFILL and q.dtype == torch.bfloat16 and D == 128:
+        # tcgen05 kernel (attention_fmha.cu); -20 = layout outside what it covers
+        rc = N.lib().b200_fmha_prefill(
+            ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(lse), ptr(cu_q), ptr(seq_lens),
+            ptr(k_cache), ptr(v_cache), k_cache.stride(1), k_cache.stride(2), nb * bs,
+            ptr(block_tables), block_tables.stride(0), bs, block_tables.shape[0], T,
+            num_q_tiles_128 if num_q_tiles_128 is not None else num_q_tiles,
+            Hq, Hkv, D, float(scale), int(causal), int(window), DTYPE_CODE[q.dtype], stream_ptr())
+        N.launch_count += 1
+        if rc == 0:
+            return (out, lse) if return_lse else out
+        if rc != -20:
+            raise N.NativeError(f"b200_fmha_prefill failed with code {rc}")
     call("b200_varlen_prefill", ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(lse), ptr(cu_q),
          ptr(seq_lens), ptr(k_cache), ptr(v_cache), k_cache.stride(1), k_cache.stride(2),
          nb * bs, ptr(block_tables), block_tables.stride(0), bs, block_tables.shape[0], T,
