@@ -51,6 +51,12 @@ constexpr uint32_t kColS = 0;      // two score buffers of 128 columns
 constexpr uint32_t kColO = 256;    // output accumulator, 128 columns
 constexpr uint32_t kTmemCols = 512;
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 struct Args {
   __nv_bfloat16* out;      // [T, Hq * 128], row pitch ldo
   float* lse;              // optional [Hq, T]
@@ -270,6 +276,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       tc_fence_after();
       const uint32_t s_addr = lane_addr + kColS + b * BKV;
       const int key0 = (t0 + j) * BKV;
+      // Only tiles that touch the causal diagonal, the window start or the end of the
+      // sequence need per-element masks; the test is uniform over the CTA.
+      const bool need_mask = (key0 + BKV - 1 > (a.causal ? min(pos0, seq_len - 1) : seq_len - 1)) ||
+                             (a.window > 0 && key0 < pos0 + BQ - a.window);
       // pass 1: row maximum over the visible keys
       float mt = -INFINITY;
 #pragma unroll 1
@@ -277,38 +287,63 @@ __global__ void __launch_bounds__(kThreads, 1)
         uint32_t v[32];
         tmem_ld_32x32(s_addr + c * 32, v);
         tmem_ld_wait();
+        if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int key = key0 + c * 32 + i;
-          if (key <= hi && key >= lo) mt = fmaxf(mt, __uint_as_float(v[i]));
+          for (int i = 0; i < 32; ++i) {
+            const int key = key0 + c * 32 + i;
+            if (key <= hi && key >= lo) mt = fmaxf(mt, __uint_as_float(v[i]));
+          }
+        } else {
+          float m0 = mt, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            m0 = fmaxf(m0, __uint_as_float(v[i]));
+            m1 = fmaxf(m1, __uint_as_float(v[i + 1]));
+            m2 = fmaxf(m2, __uint_as_float(v[i + 2]));
+            m3 = fmaxf(m3, __uint_as_float(v[i + 3]));
+          }
+          mt = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
         }
       }
       float alpha = 1.0f;
       float m_new = m_used;
       if (mt > m_used && (m_used == -INFINITY || (mt - m_used) * sl2 > 8.0f)) {
         m_new = mt;
-        alpha = m_used == -INFINITY ? 0.0f : exp2f((m_used - m_new) * sl2);
+        alpha = m_used == -INFINITY ? 0.0f : ex2_approx((m_used - m_new) * sl2);
       }
       const float mb = (m_new == -INFINITY ? 0.0f : m_new) * sl2;
       // pass 2: probabilities (bf16, kept in registers until the P buffer is free) and row sum
       uint32_t pk[64];
-      float rowsum = 0.0f;
+      float rs0 = 0.0f, rs1 = 0.0f;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t v[32];
         tmem_ld_32x32(s_addr + c * 32, v);
         tmem_ld_wait();
+        if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const int key = key0 + c * 32 + i;
-          float p0 = exp2f(__uint_as_float(v[i]) * sl2 - mb);
-          float p1 = exp2f(__uint_as_float(v[i + 1]) * sl2 - mb);
-          if (key > hi || key < lo) p0 = 0.0f;
-          if (key + 1 > hi || key + 1 < lo) p1 = 0.0f;
-          rowsum += p0 + p1;
-          pk[c * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
+          for (int i = 0; i < 32; i += 2) {
+            const int key = key0 + c * 32 + i;
+            float p0 = ex2_approx(fmaf(__uint_as_float(v[i]), sl2, -mb));
+            float p1 = ex2_approx(fmaf(__uint_as_float(v[i + 1]), sl2, -mb));
+            if (key > hi || key < lo) p0 = 0.0f;
+            if (key + 1 > hi || key + 1 < lo) p1 = 0.0f;
+            rs0 += p0;
+            rs1 += p1;
+            pk[c * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = ex2_approx(fmaf(__uint_as_float(v[i]), sl2, -mb));
+            const float p1 = ex2_approx(fmaf(__uint_as_float(v[i + 1]), sl2, -mb));
+            rs0 += p0;
+            rs1 += p1;
+            pk[c * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
+          }
         }
       }
+      const float rowsum = rs0 + rs1;
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[b]);
