@@ -1,0 +1,71 @@
+"""Sampling extras of the engine on the CPU path: log-probabilities, prompt log-probabilities,
+penalties, n / best_of and beam search (ReadMe-EN.md:283-292 and
+docs/source/user_guide/support_matrix/supported_features.md:11-64 list them as supported)."""
+import math
+
+import torch
+
+from vllm_gcu_b200.engine.llm import LLM
+from vllm_gcu_b200.engine.request import SamplingParams
+
+
+def _llm(**kw):
+    return LLM("tiny-llama", device="cpu", max_num_seqs=8, max_num_batched_tokens=64,
+               max_model_len=128, num_gpu_blocks=128, dtype="float32", **kw)
+
+
+def _prompt(n, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, 32000, (n,), generator=g).tolist()
+
+
+def test_logprobs_and_prompt_logprobs_are_consistent():
+    llm = _llm()
+    p = _prompt(21, 1)
+    sp = SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True, logprobs=3,
+                        prompt_logprobs=2)
+    out = llm.generate([p], sp)[0]
+    comp = out.outputs[0]
+    assert len(comp.logprobs) == 5
+    for tok, d in zip(comp.token_ids, comp.logprobs):
+        assert tok in d and len(d) >= 3
+        assert d[tok] == max(d.values())            # greedy: the sampled token is the arg-max
+        assert all(v <= 1e-6 for v in d.values())
+    assert math.isclose(comp.cumulative_logprob,
+                        sum(d[t] for t, d in zip(comp.token_ids, comp.logprobs)), rel_tol=1e-6)
+    assert out.prompt_logprobs[0] is None and len(out.prompt_logprobs) == len(p)
+    for tok, d in zip(p[1:], out.prompt_logprobs[1:]):
+        assert tok in d and d[tok] <= 1e-6
+    # chunked prefill (budget 64 > 21 here; force chunks of 8) gives the same prompt logprobs
+    llm2 = LLM("tiny-llama", device="cpu", max_num_seqs=8, max_num_batched_tokens=8,
+               max_model_len=128, num_gpu_blocks=128, dtype="float32")
+    out2 = llm2.generate([p], sp)[0]
+    for a, b, tok in zip(out.prompt_logprobs[1:], out2.prompt_logprobs[1:], p[1:]):
+        assert abs(a[tok] - b[tok]) < 1e-4
+    assert out2.outputs[0].token_ids == comp.token_ids
+
+
+def test_repetition_penalty_changes_greedy_choice_and_presence_blocks_repeats():
+    llm = _llm()
+    p = _prompt(12, 2)
+    base = llm.generate([p], SamplingParams(max_tokens=12, temperature=0.0, ignore_eos=True))[0]
+    pen = llm.generate([p], SamplingParams(max_tokens=12, temperature=0.0, ignore_eos=True,
+                                           presence_penalty=1e4))[0]
+    toks = pen.outputs[0].token_ids
+    assert len(set(toks)) == len(toks), "a huge presence penalty forbids repeating a token"
+    assert len(base.outputs[0].token_ids) == 12
+
+
+def test_n_best_of_and_beam_search():
+    llm = _llm()
+    p = _prompt(9, 3)
+    outs = llm.generate([p], SamplingParams(max_tokens=4, temperature=1.0, n=2, best_of=4,
+                                            ignore_eos=True, seed=5))[0]
+    assert len(outs.outputs) == 2
+    assert outs.outputs[0].cumulative_logprob >= outs.outputs[1].cumulative_logprob
+    beam = llm.beam_search(p, beam_width=3, max_tokens=4, num_return=2)
+    greedy = llm.generate([p], SamplingParams(max_tokens=4, temperature=0.0, ignore_eos=True,
+                                              logprobs=0))[0]
+    assert len(beam.outputs) == 2 and len(beam.outputs[0].token_ids) == 4
+    # the best beam is at least as likely as the greedy continuation
+    assert beam.outputs[0].cumulative_logprob >= greedy.outputs[0].cumulative_logprob - 1e-5

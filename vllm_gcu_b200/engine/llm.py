@@ -98,6 +98,7 @@ class LLMEngine:
                                    num_lookahead_tokens=sp.num_speculative_tokens
                                    if sp.method else 0)
         self._ids = itertools.count()
+        self._want_sync = False
         self.dp_size = st.dp.world_size
         self.dp_global_busy = self.dp_size > 1     # learnt from the exchange of every step
         if self.dp_size > 1:
@@ -126,6 +127,10 @@ class LLMEngine:
         rid = request_id if request_id is not None else f"req-{next(self._ids)}"
         req = Request(rid, list(prompt_token_ids), sampling_params or SamplingParams(),
                       eos_token_id=eos_token_id, priority=priority, lora_id=lora_id)
+        sp_ = req.sampling_params
+        if sp_.has_penalties or sp_.logprobs is not None or sp_.prompt_logprobs is not None:
+            # these need the ids of every earlier token on the host before the next step
+            self._want_sync = True
         self.scheduler.add_request(req)
         return rid
 
@@ -182,7 +187,31 @@ class LLMEngine:
             for rid, nd in zip(handle.req_ids, handle.extra.get("num_draft", [])):
                 if nd:
                     self.spec_metrics.update(nd, len(toks.get(rid, ())))
-        outs = self.scheduler.update_from_output(so, toks, draft)
+        lp = None
+        raw = handle.extra.get("logprobs")
+        if raw is not None:
+            chosen, tv, ti, ks = raw
+            lp = {}
+            for i, rid in enumerate(handle.req_ids):
+                if ks[i] < 0:
+                    continue
+                top = {int(ti[i, c]): float(tv[i, c]) for c in range(ks[i])}
+                tok = toks[rid][0] if toks.get(rid) else -1
+                top.setdefault(int(tok), float(chosen[i]))
+                lp[rid] = top
+        pl = handle.extra.get("prompt_logprobs")
+        if pl:
+            for rid, (chosen, tv, ti, targets) in pl.items():
+                req = self.scheduler.requests.get(rid)
+                if req is None:
+                    continue
+                if not hasattr(req, "prompt_logprobs") or req.prompt_logprobs is None:
+                    req.prompt_logprobs = [None]          # the first token has no prediction
+                for r_, t_ in enumerate(targets):
+                    d = {int(ti[r_, c]): float(tv[r_, c]) for c in range(tv.shape[1])}
+                    d.setdefault(int(t_), float(chosen[r_]))
+                    req.prompt_logprobs.append(d)
+        outs = self.scheduler.update_from_output(so, toks, draft, lp)
         if self.proposer is not None:
             for s in so.scheduled:
                 r = s.req
@@ -193,6 +222,9 @@ class LLMEngine:
 
     def step(self) -> list[RequestOutput]:
         """Runs (or, with async scheduling, launches and retires) one engine step."""
+        if self._want_sync and self.cfg.scheduler.async_scheduling and not self._pending:
+            self.cfg.scheduler.async_scheduling = False
+            self.scheduler.async_mode = False
         if not self.cfg.scheduler.async_scheduling:
             item = self._launch()
             return self._finish(*item) if item is not None else []
@@ -282,4 +314,85 @@ class LLM:
         self.engine = LLMEngine(cfg)
 
     def generate(self, prompts, sampling_params=None) -> list[RequestOutput]:
-        return self.engine.generate(prompts, sampling_params)
+        """One ``RequestOutput`` per prompt.  ``n`` / ``best_of`` > 1 run that many sampled
+        continuations per prompt (sharing the prompt's KV blocks through the prefix cache)
+        and return the ``n`` with the highest cumulative log-probability; ``use_beam_search``
+        routes to :meth:`beam_search` (best-of and beam search are listed as functional in
+        docs/source/user_guide/support_matrix/supported_features.md:11-64)."""
+        prompts = list(prompts)
+        if sampling_params is None or isinstance(sampling_params, SamplingParams):
+            sps = [sampling_params or SamplingParams()] * len(prompts)
+        else:
+            sps = list(sampling_params)
+        if all(sp.n == 1 and not sp.best_of and not sp.use_beam_search for sp in sps):
+            return self.engine.generate(prompts, sps)
+        import dataclasses
+        flat_p, flat_sp, owner = [], [], []
+        results: list[Optional[RequestOutput]] = [None] * len(prompts)
+        for i, (p, sp) in enumerate(zip(prompts, sps)):
+            if sp.use_beam_search:
+                results[i] = self.beam_search(p, max(sp.best_of or sp.n, 1), sp.max_tokens,
+                                              num_return=sp.n, eos_token_id=None)
+                continue
+            k = max(sp.best_of or sp.n, sp.n)
+            for c in range(k):
+                seed = (sp.seed if sp.seed is not None else 0) * 7919 + c + 1
+                flat_sp.append(dataclasses.replace(
+                    sp, n=1, best_of=None, seed=seed,
+                    logprobs=sp.logprobs if sp.logprobs is not None else (0 if k > sp.n else None)))
+                flat_p.append(p)
+                owner.append(i)
+        outs = self.engine.generate(flat_p, flat_sp) if flat_p else []
+        grouped: dict[int, list] = {}
+        for o, i in zip(outs, owner):
+            grouped.setdefault(i, []).append(o)
+        for i, group in grouped.items():
+            comps = [g.outputs[0] for g in group]
+            if len(comps) > sps[i].n:
+                comps.sort(key=lambda c: -(c.cumulative_logprob or 0.0))
+                comps = comps[:sps[i].n]
+            for idx, c in enumerate(comps):
+                c.index = idx
+            results[i] = RequestOutput(group[0].request_id, group[0].prompt_token_ids, comps, True,
+                                       group[0].num_cached_tokens, group[0].prompt_logprobs)
+        return results          # type: ignore[return-value]
+
+    def beam_search(self, prompt: Sequence[int], beam_width: int, max_tokens: int,
+                    num_return: int = 1, eos_token_id: Optional[int] = None,
+                    length_penalty: float = 1.0) -> RequestOutput:
+        """Beam search on top of the engine: every step scores the live beams with one
+        single-token request each (``logprobs = 2 * beam_width``); the shared prefixes are
+        served by the prefix cache, so a step costs one decode token per beam."""
+        from .request import CompletionOutput
+        beams = [(list(prompt), 0.0)]
+        done: list[tuple[list[int], float]] = []
+        n_prompt = len(prompt)
+        sp = SamplingParams(max_tokens=1, temperature=0.0, logprobs=2 * beam_width,
+                            ignore_eos=True)
+        for _ in range(max_tokens):
+            outs = self.engine.generate([b[0] for b in beams], sp)
+            cand = []
+            for (toks, score), o in zip(beams, outs):
+                lp = o.outputs[0].logprobs[0]
+                for tid, l in lp.items():
+                    cand.append((toks + [tid], score + l))
+            cand.sort(key=lambda c: -c[1])
+            beams = []
+            for toks, score in cand:
+                if eos_token_id is not None and toks[-1] == eos_token_id:
+                    done.append((toks, score))
+                else:
+                    beams.append((toks, score))
+                if len(beams) >= beam_width:
+                    break
+            if not beams:
+                break
+        done += beams
+
+        def norm(item):
+            toks, score = item
+            return score / (max(len(toks) - n_prompt, 1) ** length_penalty)
+        done.sort(key=lambda c: -norm(c))
+        comps = [CompletionOutput(i, toks[n_prompt:], "length", None, score)
+                 for i, (toks, score) in enumerate(done[:num_return])]
+        return RequestOutput("beam", list(prompt), comps, True)

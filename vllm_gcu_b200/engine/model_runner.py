@@ -119,6 +119,7 @@ class ModelRunner:
         self.timing_events: Optional[list] = None  # set to a list to time every step
         self.timing_meta: list = []                # (decodes, prefills, tokens) per timed step
         self.keep_logits = False                   # debugging / tests: keep last step's logits
+        self._features = None                      # per-step sampling extras (penalties, logprobs)
         from .. import envs
         self.nvtx = bool(envs.NVTX) and self.is_cuda
         self.last_logits: Optional[torch.Tensor] = None
@@ -312,8 +313,12 @@ class ModelRunner:
         T_real = nd + sum(s.num_tokens for s in prefills)
 
         batch_has_lora = self.lora is not None and any(s.req.lora_id >= 0 for s in sched)
+        # penalties / log-probabilities need the logits on a side path: no graph for that step
+        feat = any(s.req.sampling_params.has_penalties
+                   or s.req.sampling_params.logprobs is not None
+                   or s.req.sampling_params.prompt_logprobs is not None for s in sched)
         use_graph = (self.is_cuda and npf == 0 and self.graphs and nd <= self.graph_sizes[-1]
-                     and self.drafter is None and not batch_has_lora
+                     and self.drafter is None and not batch_has_lora and not feat
                      and self.cfg.parallel.data_parallel_size == 1)
         B_pad = _pad_batch(nd, self.graph_sizes) if use_graph else B
         T = T_real + (B_pad - B)
@@ -504,6 +509,7 @@ class ModelRunner:
             sample_indices=self.sample_indices[:max(ns * width, 1)],
             q_lens_cpu=[int(x) for x in ntok], seq_lens_cpu=[int(x) for x in seq_after])
 
+        self._features = self._build_features(order, samplers, tok_off) if feat else None
         if self.nvtx:
             torch.cuda.nvtx.range_push("decode_step" if npf == 0 else
                                        ("prefill_step" if nd == 0 else "mixed_step"))
@@ -536,10 +542,98 @@ class ModelRunner:
             event.record()
         self.prev_index = {order[j].req.request_id: r for r, j in enumerate(samplers)}
         self.step_counter += 1
+        extra = {"num_draft": nspec}
+        if self._features is not None:
+            extra["logprobs"] = self._features.pop("logprobs_out", None)
+            extra["prompt_logprobs"] = self._features.pop("prompt_logprobs_out", None)
+            self._features = None
         return StepHandle([order[j].req.request_id for j in samplers], ns, host, event,
                           width, device_ms_events=(ev0, ev1) if ev0 is not None else None,
                           draft_host=self.draft_host if self.drafter is not None else None,
-                          extra={"num_draft": nspec})
+                          extra=extra)
+
+    def _build_features(self, order, samplers, tok_off) -> dict:
+        """Host-side description of the per-request sampling extras of this step: penalty
+        rows (token histories as index lists), log-probability widths, prompt positions whose
+        log-probabilities are wanted (ReadMe-EN.md:283-292 lists the supported options)."""
+        f: dict = {}
+        V = self.cfg.model.vocab_size
+        pen_rows, p_r, p_t, o_r, o_t, pres, freq, rep_ = [], [], [], [], [], [], [], []
+        lp_k = []
+        for r, j in enumerate(samplers):
+            req = order[j].req
+            sp = req.sampling_params
+            lp_k.append(-1 if sp.logprobs is None else int(sp.logprobs))
+            if sp.has_penalties:
+                i = len(pen_rows)
+                pen_rows.append(r)
+                p_r += [i] * len(req.prompt_token_ids)
+                p_t += [t for t in req.prompt_token_ids]
+                o_r += [i] * len(req.output_token_ids)
+                o_t += [t for t in req.output_token_ids]
+                pres.append(sp.presence_penalty)
+                freq.append(sp.frequency_penalty)
+                rep_.append(sp.repetition_penalty)
+        dev = self.device
+        if pen_rows:
+            n = len(pen_rows)
+            pm = torch.zeros((n, V), dtype=torch.bool, device=dev)
+            oc = torch.zeros((n, V), dtype=torch.int32, device=dev)
+            if p_r:
+                pm[torch.tensor(p_r, device=dev), torch.tensor(p_t, device=dev).clamp_(0, V - 1)] = True
+            if o_r:
+                oc.index_put_((torch.tensor(o_r, device=dev),
+                               torch.tensor(o_t, device=dev).clamp_(0, V - 1)),
+                              torch.ones(len(o_r), dtype=torch.int32, device=dev), accumulate=True)
+            f["penalties"] = (torch.tensor(pen_rows, device=dev), pm, oc,
+                              torch.tensor(pres, device=dev), torch.tensor(freq, device=dev),
+                              torch.tensor(rep_, device=dev))
+        if any(k >= 0 for k in lp_k):
+            f["logprob_k"] = lp_k
+        # prompt log-probabilities: hidden row of prompt position p predicts token p + 1
+        pl = []
+        for j, s_ in enumerate(order):
+            req = s_.req
+            k = req.sampling_params.prompt_logprobs
+            if k is None or s_.start >= req.num_prompt_tokens - 1:
+                continue
+            a = int(tok_off[j])
+            n = min(s_.start + s_.num_tokens, req.num_prompt_tokens - 1) - s_.start
+            if n > 0:
+                pl.append((req.request_id, a, n,
+                           req.prompt_token_ids[s_.start + 1:s_.start + 1 + n], int(k)))
+        if pl:
+            f["prompt_logprobs"] = pl
+        return f
+
+    def _apply_features(self, hidden: torch.Tensor, logits: torch.Tensor, ns: int,
+                        out_ids: torch.Tensor, before_sampling: bool) -> torch.Tensor:
+        f = self._features
+        if before_sampling:
+            if "penalties" in f:
+                from ..layers.sampler import apply_penalties
+                rows, pm, oc, pres, freq, rep_ = f["penalties"]
+                sub = logits.index_select(0, rows).float()
+                apply_penalties(sub, pm, oc, pres, freq, rep_)
+                logits = logits.clone() if not logits.is_contiguous() else logits
+                logits.index_copy_(0, rows, sub.to(logits.dtype))
+            return logits
+        if "logprob_k" in f:
+            ks = f["logprob_k"]
+            kmax = max(ks)
+            chosen, tv, ti = self.sampler.logprobs(logits[:ns], out_ids[:ns].long(), max(kmax, 0))
+            f["logprobs_out"] = (chosen.cpu(), tv.cpu(), ti.cpu(), ks)
+        if "prompt_logprobs" in f:
+            out = {}
+            for rid, a, n, targets, k in f["prompt_logprobs"]:
+                lg = self.model.compute_logits(hidden[a:a + n]).float()
+                lp = torch.log_softmax(lg, dim=-1)
+                tgt = torch.tensor(targets, device=lp.device)
+                chosen = lp.gather(-1, tgt[:, None]).squeeze(-1).cpu()
+                tv, ti = lp.topk(k, dim=-1) if k > 0 else (lp[:, :0], tgt[:, None][:, :0])
+                out[rid] = (chosen, tv.cpu(), ti.cpu(), targets)
+            f["prompt_logprobs_out"] = out
+        return logits
 
     def _forward_and_sample(self, md: AttentionMetadata, T: int, ns: int, out_ids: torch.Tensor,
                             all_greedy: bool, width: int = 1) -> None:
@@ -568,7 +662,10 @@ class ModelRunner:
                 if ns:      # every stage needs the sampled ids (stop checks, next inputs)
                     dist.broadcast(out_ids[:ns * width], last, group=pp.device_group)
                 return
+        feats = getattr(self, "_features", None)
         if ns == 0:
+            if feats is not None and "prompt_logprobs" in feats and self.model.is_last_stage:
+                self._apply_features(hidden, hidden, 0, out_ids, before_sampling=False)
             return
         if md.num_prefills == 0 and width == 1:
             rows = hidden[:ns]          # decode-only: row i is the i-th sampling request
@@ -577,10 +674,14 @@ class ModelRunner:
         logits = self.model.compute_logits(rows)
         if self.keep_logits:
             self.last_logits = logits.float().cpu()
+        if feats is not None and width == 1:
+            logits = self._apply_features(hidden, logits, ns, out_ids, before_sampling=True)
         st = None if all_greedy else SamplingTensors(self.temperature[:ns], self.top_k[:ns],
                                                      self.top_p[:ns], self.seeds[:ns])
         if width == 1:
             self.sampler(logits, st, out=out_ids[:ns])
+            if feats is not None:
+                self._apply_features(hidden, logits, ns, out_ids, before_sampling=False)
         else:
             self._verify(logits, st, ns, width, out_ids)
         if self.drafter is not None:

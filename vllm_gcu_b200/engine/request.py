@@ -78,7 +78,8 @@ class Request:
     num_preemptions: int = 0
     first_token_time: Optional[float] = None
     finish_time: Optional[float] = None
-    logprobs: list[Any] = field(default_factory=list)
+    logprobs: list[Any] = field(default_factory=list)          # per output token: {id: logprob}
+    prompt_logprobs: Optional[list] = None                     # per prompt token (first: None)
 
     @property
     def num_prompt_tokens(self) -> int:
@@ -122,6 +123,7 @@ class RequestOutput:
     outputs: list[CompletionOutput]
     finished: bool
     num_cached_tokens: int = 0
+    prompt_logprobs: Optional[list] = None
     metrics: dict[str, float] = field(default_factory=dict)
 
 

@@ -227,7 +227,8 @@ class Scheduler:
                 req = self.waiting[0]
                 computed_blocks: list[int] = []
                 num_cached = 0
-                if req.num_computed_tokens == 0:
+                if req.num_computed_tokens == 0 and req.sampling_params.prompt_logprobs is None:
+                    # (prompt log-probabilities need every prompt position computed)
                     computed_blocks, num_cached = self.kv.get_computed_blocks(req)
                 want = req.num_tokens - num_cached - req.num_computed_tokens
                 n = min(want, budget)
@@ -287,6 +288,7 @@ class Scheduler:
     def update_from_output(self, out: SchedulerOutput,
                            sampled: dict[str, Sequence[int]],
                            draft: Optional[dict[str, Sequence[int]]] = None,
+                           logprobs: Optional[dict[str, dict]] = None,
                            ) -> list[RequestOutput]:
         """``sampled[req_id]`` holds the token ids emitted by the step (one, or up to
         ``1 + len(spec)`` accepted tokens under speculative decoding; empty for a
@@ -316,6 +318,8 @@ class Scheduler:
             for t in toks:
                 req.output_token_ids.append(int(t))
                 emitted += 1
+                if logprobs is not None and req.request_id in logprobs:
+                    req.logprobs.append(logprobs[req.request_id])
                 if req.first_token_time is None:
                     import time as _t
                     req.first_token_time = _t.monotonic()
@@ -343,10 +347,13 @@ class Scheduler:
         elif req.status == RequestStatus.FINISHED_ABORTED:
             reason = "abort"
         # token_ids is the request's live list (no per-step copy); treat it as read-only
+        cum = None
+        if req.logprobs:
+            cum = sum(d.get(t, 0.0) for d, t in zip(req.logprobs, req.output_token_ids))
         comp = CompletionOutput(0, req.output_token_ids, reason,
-                                req.logprobs if req.logprobs else None)
+                                req.logprobs if req.logprobs else None, cum)
         return RequestOutput(req.request_id, req.prompt_token_ids, [comp], req.finished,
-                             req.num_cached_tokens)
+                             req.num_cached_tokens, req.prompt_logprobs)
 
     # -- stats -------------------------------------------------------------------
     def stats(self) -> dict[str, float]:
