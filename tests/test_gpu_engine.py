@@ -73,3 +73,29 @@ def test_graphs_async_and_eager_agree(async_sched):
 def test_smoke_entry():
     import __graft_entry__ as g
     g.smoke()
+
+
+@pytest.mark.parametrize("kvd", ["fp8", "int8"])
+def test_engine_with_8bit_kv_cache_tracks_bf16(kvd):
+    """The engine with an fp8 / int8 KV cache: logits of a step that reads a long cached
+    prefix stay close to the bf16-cache engine; sampling extras work on the GPU path."""
+    kw = dict(num_hidden_layers=2, max_num_seqs=8, max_num_batched_tokens=256,
+              max_model_len=512, num_gpu_blocks=256, enforce_eager=True)
+    prompts = _prompts(3, [200, 33, 120], 128256, seed=9)
+    sp = SamplingParams(max_tokens=3, temperature=0.0, ignore_eos=True, logprobs=2)
+    base = LLM("llama-3-8b", device="cuda", **kw)
+    base.engine.runner.keep_logits = True
+    ob = base.generate(prompts, sp)
+    lb = base.engine.runner.last_logits
+    q8 = LLM("llama-3-8b", device="cuda", kv_cache_dtype=kvd, **kw)
+    assert q8.engine.runner.kv_caches[0].element_size() == 1
+    q8.engine.runner.keep_logits = True
+    oq = q8.generate(prompts, sp)
+    lq = q8.engine.runner.last_logits
+    assert lb.shape == lq.shape
+    cos = torch.nn.functional.cosine_similarity(lb.flatten(), lq.flatten(), dim=0).item()
+    rms = ((lb - lq).pow(2).mean().sqrt() / lb.std()).item()
+    assert cos > 0.97 and rms < 0.25, (cos, rms)
+    for o in ob + oq:
+        assert len(o.outputs[0].logprobs) == 3 and o.outputs[0].cumulative_logprob <= 0
+    _native.check_status()

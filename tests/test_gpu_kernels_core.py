@@ -258,6 +258,59 @@ def test_fmha_prefill_tcgen05(C, Hq, Hkv, window):
         _close(lse, lse_r, 1e-2, 1e-2)
 
 
+@pytest.mark.parametrize("kind", ["fp8", "int8"])
+def test_attention_over_8bit_kv_cache(C, kind):
+    """Decode and prefill attention reading an fp8 / int8 KV cache (dequantised inside the
+    kernel) against the reference on the dequantised cache; the cache is filled by the fused
+    RoPE + cache-write kernel so the write path is covered too."""
+    torch.manual_seed(23)
+    Hq, Hkv, D, bs = 8, 2, 128, 16
+    lens = [40, 300, 17, 129]
+    B = len(lens)
+    max_blocks = max(lens) // bs + 2
+    nb = B * max_blocks + 1
+    qdt = torch.float8_e4m3fn if kind == "fp8" else torch.int8
+    scale_k, scale_v = (0.5, 0.25) if kind == "fp8" else (1 / 24.0, 1 / 20.0)
+    kc = torch.zeros(nb, bs, Hkv, D, device="cuda", dtype=qdt)
+    vc = torch.zeros_like(kc)
+    bt = torch.randperm(nb - 1, device="cuda")[: B * max_blocks].add_(1).to(torch.int32).view(
+        B, max_blocks)
+    kc_ref = torch.zeros(nb, bs, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    vc_ref = torch.zeros_like(kc_ref)
+    sc = torch.tensor([scale_k, scale_v], device="cuda")
+    for b, n in enumerate(lens):
+        k = torch.randn(n, Hkv * D, device="cuda", dtype=torch.bfloat16)
+        v = torch.randn(n, Hkv * D, device="cuda", dtype=torch.bfloat16)
+        pos = torch.arange(n, device="cuda")
+        slots = (bt[b, pos // bs].long() * bs + pos % bs)
+        C.rope_cache_flash(None, k, v, None, None, True, D, slots, kc, vc, sc[0:1], sc[1:2])
+        if kind == "fp8":
+            kd = (k.float() / scale_k).to(qdt).float() * scale_k
+            vd = (v.float() / scale_v).to(qdt).float() * scale_v
+        else:
+            kd = (k.float() / scale_k).round().clamp(-128, 127) * scale_k
+            vd = (v.float() / scale_v).round().clamp(-128, 127) * scale_v
+        kc_ref.view(-1, Hkv * D)[slots] = kd.to(torch.bfloat16)
+        vc_ref.view(-1, Hkv * D)[slots] = vd.to(torch.bfloat16)
+    sl = torch.tensor(lens, device="cuda", dtype=torch.int32)
+    att = D ** -0.5
+    q = torch.randn(B, Hq, D, device="cuda", dtype=torch.bfloat16)
+    got = C.paged_decode(q, kc, vc, bt, sl, att, num_splits=2,
+                         kv_quant=(scale_k, scale_v, 0.0, 0.0))
+    want = ref.paged_attention_decode(q, kc_ref, vc_ref, bt, sl, att)
+    _close(got, want, 3e-2, 3e-2)
+    q_lens = [8, 100, 17, 64]
+    T = sum(q_lens)
+    qp = torch.randn(T, Hq, D, device="cuda", dtype=torch.bfloat16)
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), device="cuda",
+                      dtype=torch.int32)
+    tiles = sum((x + 63) // 64 for x in q_lens)
+    gotp = C.varlen_prefill(qp, kc, vc, bt, cu, sl, att, tiles,
+                            kv_quant=(scale_k, scale_v, 0.0, 0.0))
+    wantp = ref.varlen_prefill_attention(qp, kc_ref, vc_ref, bt, cu, sl, att)
+    _close(gotp, wantp, 3e-2, 3e-2)
+
+
 def test_sampler(C):
     torch.manual_seed(8)
     B, V = 9, 32000

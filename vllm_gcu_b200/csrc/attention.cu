@@ -81,7 +81,25 @@ struct KvView {
   long long num_slots;
   int max_blocks;
   int block_size;
+  // 8-bit caches: 0 = cache holds T, 1 = fp8 e4m3 (value = q * scale),
+  // 2 = int8 (value = (q - zero_point) * scale).  Strides are then in bytes.
+  int qmode = 0;
+  float k_scale = 1.0f, v_scale = 1.0f, k_zp = 0.0f, v_zp = 0.0f;
 };
+
+// Eight cached 8-bit values -> eight T in shared memory.
+template <typename T>
+__device__ __forceinline__ void dequant8(T* dst, const uint8_t* src, int qmode, float scale,
+                                         float zp) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(src);
+  const uint8_t* b = reinterpret_cast<const uint8_t*>(&raw);
+  float f[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    f[i] = qmode == 1 ? e4m3_to_f32(b[i]) * scale
+                      : (static_cast<float>(static_cast<int8_t>(b[i])) - zp) * scale;
+  vec8_store<T>(dst, f);
+}
 
 // Stages KV tokens [t0, t0 + kTile) of sequence `b`, kv head `kvh` into shared
 // memory rows of HD + kPad elements.  Rows at or past kv_end are zero filled.
@@ -105,7 +123,12 @@ __device__ __forceinline__ void load_kv_tile(T* sK, T* sV, const KvView& kv, int
       slot = static_cast<long long>(blk) * kv.block_size + tok % kv.block_size;
       ok = slot >= 0 && slot < kv.num_slots;  // a bad table entry reads zeros, never memory
     }
-    if (ok) {
+    if (ok && kv.qmode != 0) {
+      // 8-bit cache: plain loads, dequantised on the way into shared memory
+      const long long off = slot * kv.slot_stride + kvh * kv.head_stride + ch * 8;
+      dequant8<T>(dk, static_cast<const uint8_t*>(kv.k_cache) + off, kv.qmode, kv.k_scale, kv.k_zp);
+      dequant8<T>(dv, static_cast<const uint8_t*>(kv.v_cache) + off, kv.qmode, kv.v_scale, kv.v_zp);
+    } else if (ok) {
       const long long off = slot * kv.slot_stride + kvh * kv.head_stride + ch * 8;
       cp_async16(dk, kc + off);
       cp_async16(dv, vc + off);
@@ -636,13 +659,14 @@ B200_API int b200_decode_num_splits(int B, int Hkv, int max_seq_len) {
 // Decode attention.  Workspace (only read when num_splits > 1):
 //   tmp_out fp32 [B, Hq, num_splits, HD], tmp_lse fp32 [B, Hq, num_splits].
 // dtype 0 bf16 / 1 fp16; HD in {64, 128, 256}; Hq / Hkv <= 16.
-B200_API int b200_paged_decode(const void* q, long long ldq, void* out, long long ldo,
-                               const void* k_cache, const void* v_cache, long long slot_stride,
-                               long long head_stride, long long num_slots,
-                               const int* block_tables, int max_blocks, int block_size,
-                               const int* seq_lens, float* tmp_out, float* tmp_lse,
-                               int num_splits, int B, int Hq, int Hkv, int HD, float scale,
-                               int dtype, void* stream) {
+static int paged_decode_impl(const void* q, long long ldq, void* out, long long ldo,
+                             const void* k_cache, const void* v_cache, long long slot_stride,
+                             long long head_stride, long long num_slots,
+                             const int* block_tables, int max_blocks, int block_size,
+                             const int* seq_lens, float* tmp_out, float* tmp_lse,
+                             int num_splits, int B, int Hq, int Hkv, int HD, float scale,
+                             int dtype, int qmode, float k_scale, float v_scale, float k_zp,
+                             float v_zp, void* stream) {
   if (B <= 0) return 0;
   if (Hkv <= 0 || Hq % Hkv != 0 || Hq / Hkv > 16) return -2;
   if (num_splits < 1) return -2;
@@ -652,6 +676,8 @@ B200_API int b200_paged_decode(const void* q, long long ldq, void* out, long lon
   a.kv.k_cache = k_cache; a.kv.v_cache = v_cache; a.kv.block_tables = block_tables;
   a.kv.slot_stride = slot_stride; a.kv.head_stride = head_stride; a.kv.num_slots = num_slots;
   a.kv.max_blocks = max_blocks; a.kv.block_size = block_size;
+  a.kv.qmode = qmode; a.kv.k_scale = k_scale; a.kv.v_scale = v_scale;
+  a.kv.k_zp = k_zp; a.kv.v_zp = v_zp;
   a.ldq = ldq; a.ldo = ldo; a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.num_splits = num_splits;
   a.scale = scale;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -667,6 +693,38 @@ B200_API int b200_paged_decode(const void* q, long long ldq, void* out, long lon
   }
 #undef B200_DEC
   return -8;
+}
+
+B200_API int b200_paged_decode(const void* q, long long ldq, void* out, long long ldo,
+                               const void* k_cache, const void* v_cache, long long slot_stride,
+                               long long head_stride, long long num_slots,
+                               const int* block_tables, int max_blocks, int block_size,
+                               const int* seq_lens, float* tmp_out, float* tmp_lse,
+                               int num_splits, int B, int Hq, int Hkv, int HD, float scale,
+                               int dtype, void* stream) {
+  return paged_decode_impl(q, ldq, out, ldo, k_cache, v_cache, slot_stride, head_stride, num_slots,
+                           block_tables, max_blocks, block_size, seq_lens, tmp_out, tmp_lse,
+                           num_splits, B, Hq, Hkv, HD, scale, dtype, 0, 1.0f, 1.0f, 0.0f, 0.0f,
+                           stream);
+}
+
+// Decode attention over an 8-bit KV cache (same layout, one byte per element; slot_stride and
+// head_stride in bytes).  qmode 1: fp8 e4m3 with per-tensor scales; qmode 2: int8 with scales
+// and zero points (the reference's int8 KV cache, vllm_gcu/kernels/quantization/kv_cache.py:12-61).
+// Queries and output stay bf16 / fp16 (dtype).
+B200_API int b200_paged_decode_q8kv(const void* q, long long ldq, void* out, long long ldo,
+                                    const void* k_cache, const void* v_cache,
+                                    long long slot_stride, long long head_stride,
+                                    long long num_slots, const int* block_tables, int max_blocks,
+                                    int block_size, const int* seq_lens, float* tmp_out,
+                                    float* tmp_lse, int num_splits, int B, int Hq, int Hkv, int HD,
+                                    float scale, int dtype, int qmode, float k_scale,
+                                    float v_scale, float k_zp, float v_zp, void* stream) {
+  if (qmode != 1 && qmode != 2) return -2;
+  return paged_decode_impl(q, ldq, out, ldo, k_cache, v_cache, slot_stride, head_stride, num_slots,
+                           block_tables, max_blocks, block_size, seq_lens, tmp_out, tmp_lse,
+                           num_splits, B, Hq, Hkv, HD, scale, dtype, qmode, k_scale, v_scale,
+                           k_zp, v_zp, stream);
 }
 
 // Second pass of split-KV decode: LSE-weighted sum of the per-split partial outputs
@@ -693,13 +751,14 @@ B200_API int b200_decode_reduce(void* out, long long ldo, float* tmp_out, float*
 
 // Prefill / chunked-prefill / prefix attention.  num_q_tiles must be
 // sum_b ceil(q_len_b / 64) (an upper bound is fine: extra CTAs exit).
-B200_API int b200_varlen_prefill(const void* q, long long ldq, void* out, long long ldo,
-                                 float* lse, const int* cu_q, const int* seq_lens,
-                                 const void* k_cache, const void* v_cache, long long slot_stride,
-                                 long long head_stride, long long num_slots,
-                                 const int* block_tables, int max_blocks, int block_size, int B,
-                                 int T, int num_q_tiles, int Hq, int Hkv, int HD, float scale,
-                                 int causal, int window, int dtype, void* stream) {
+static int varlen_prefill_impl(const void* q, long long ldq, void* out, long long ldo,
+                               float* lse, const int* cu_q, const int* seq_lens,
+                               const void* k_cache, const void* v_cache, long long slot_stride,
+                               long long head_stride, long long num_slots,
+                               const int* block_tables, int max_blocks, int block_size, int B,
+                               int T, int num_q_tiles, int Hq, int Hkv, int HD, float scale,
+                               int causal, int window, int dtype, int qmode, float k_scale,
+                               float v_scale, float k_zp, float v_zp, void* stream) {
   if (B <= 0 || T <= 0 || num_q_tiles <= 0) return 0;
   if (Hkv <= 0 || Hq % Hkv != 0) return -2;
   PrefillArgs a;
@@ -707,6 +766,8 @@ B200_API int b200_varlen_prefill(const void* q, long long ldq, void* out, long l
   a.kv.k_cache = k_cache; a.kv.v_cache = v_cache; a.kv.block_tables = block_tables;
   a.kv.slot_stride = slot_stride; a.kv.head_stride = head_stride; a.kv.num_slots = num_slots;
   a.kv.max_blocks = max_blocks; a.kv.block_size = block_size;
+  a.kv.qmode = qmode; a.kv.k_scale = k_scale; a.kv.v_scale = v_scale;
+  a.kv.k_zp = k_zp; a.kv.v_zp = v_zp;
   a.ldq = ldq; a.ldo = ldo; a.B = B; a.T = T; a.Hq = Hq; a.Hkv = Hkv; a.causal = causal;
   a.window = window; a.scale = scale;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -720,6 +781,36 @@ B200_API int b200_varlen_prefill(const void* q, long long ldq, void* out, long l
   }
 #undef B200_PRE
   return -8;
+}
+
+B200_API int b200_varlen_prefill(const void* q, long long ldq, void* out, long long ldo,
+                                 float* lse, const int* cu_q, const int* seq_lens,
+                                 const void* k_cache, const void* v_cache, long long slot_stride,
+                                 long long head_stride, long long num_slots,
+                                 const int* block_tables, int max_blocks, int block_size, int B,
+                                 int T, int num_q_tiles, int Hq, int Hkv, int HD, float scale,
+                                 int causal, int window, int dtype, void* stream) {
+  return varlen_prefill_impl(q, ldq, out, ldo, lse, cu_q, seq_lens, k_cache, v_cache, slot_stride,
+                             head_stride, num_slots, block_tables, max_blocks, block_size, B, T,
+                             num_q_tiles, Hq, Hkv, HD, scale, causal, window, dtype, 0, 1.0f, 1.0f,
+                             0.0f, 0.0f, stream);
+}
+
+// Prefill attention over an 8-bit KV cache; see b200_paged_decode_q8kv for qmode and scales.
+B200_API int b200_varlen_prefill_q8kv(const void* q, long long ldq, void* out, long long ldo,
+                                      float* lse, const int* cu_q, const int* seq_lens,
+                                      const void* k_cache, const void* v_cache,
+                                      long long slot_stride, long long head_stride,
+                                      long long num_slots, const int* block_tables,
+                                      int max_blocks, int block_size, int B, int T,
+                                      int num_q_tiles, int Hq, int Hkv, int HD, float scale,
+                                      int causal, int window, int dtype, int qmode, float k_scale,
+                                      float v_scale, float k_zp, float v_zp, void* stream) {
+  if (qmode != 1 && qmode != 2) return -2;
+  return varlen_prefill_impl(q, ldq, out, ldo, lse, cu_q, seq_lens, k_cache, v_cache, slot_stride,
+                             head_stride, num_slots, block_tables, max_blocks, block_size, B, T,
+                             num_q_tiles, Hq, Hkv, HD, scale, causal, window, dtype, qmode, k_scale,
+                             v_scale, k_zp, v_zp, stream);
 }
 
 B200_API int b200_merge_attn_states(void* out, float* out_lse, const void* p_out,

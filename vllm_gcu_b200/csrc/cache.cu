@@ -42,7 +42,7 @@ struct RopeCacheArgs {
   int T, Hq, Hkv, D, rot_dim;
   int is_neox;
   int cos_sin_fp32;
-  int cache_fp8;
+  int cache_fp8;   // 0: cache holds T, 1: fp8 e4m3, 2: int8 (symmetric)
   unsigned int* status;
 };
 
@@ -108,8 +108,15 @@ __global__ void __launch_bounds__(256) rope_cache_flash_kernel(const RopeCacheAr
       const float inv = 1.0f / (is_v ? *a.v_scale : *a.k_scale);
       uint2 pk;
       uint8_t* b = reinterpret_cast<uint8_t*>(&pk);
+      if (a.cache_fp8 == 2) {          // int8, symmetric (zero point 0)
 #pragma unroll
-      for (int u = 0; u < 8; ++u) b[u] = f32_to_e4m3(f[u] * inv);
+        for (int u = 0; u < 8; ++u)
+          b[u] = static_cast<uint8_t>(static_cast<int8_t>(
+              fminf(fmaxf(rintf(f[u] * inv), -128.0f), 127.0f)));
+      } else {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) b[u] = f32_to_e4m3(f[u] * inv);
+      }
       uint8_t* dst = static_cast<uint8_t*>(is_v ? a.v_cache : a.k_cache);
       *reinterpret_cast<uint2*>(dst + dst_off) = pk;
     } else {

@@ -218,6 +218,14 @@ class ModelRunner:
         spec = self.model.kv_cache_spec()
         mc = self.cfg.model
         dt = mc.dtype
+        kvd = (mc.kv_cache_dtype or "auto").lower()
+        if self.is_cuda and spec["type"] == "gqa":
+            # 8-bit KV cache (fp8 e4m3 or symmetric int8); the attention kernels dequantise on
+            # the way into shared memory.  The CPU path keeps the model dtype.
+            if kvd.startswith("fp8"):
+                dt = torch.float8_e4m3fn
+            elif kvd == "int8":
+                dt = torch.int8
         if spec["type"] == "mla":
             self.kv_caches = [torch.zeros(num_blocks, self.block_size, spec["width"], dtype=dt,
                                           device=self.device) for _ in range(spec["layers"])]

@@ -66,6 +66,12 @@ class PagedAttention(nn.Module):
         self.rotary = rotary
         self.q_norm, self.k_norm = q_norm, k_norm
         self.window = sliding_window
+        # per-tensor scales of an fp8 / int8 KV cache (value = stored * scale); checkpoints may
+        # provide them (``load_kv_cache_scales`` of the reference's quantised models,
+        # vllm_gcu/models/deepseek_moe_quant.py:487), the default 1.0 suits fp8
+        self.k_scale = 1.0
+        self.v_scale = 1.0
+        self._scale_t = None
 
     def forward(self, qkv: torch.Tensor, kv_cache: torch.Tensor, md: AttentionMetadata
                 ) -> torch.Tensor:
@@ -89,16 +95,27 @@ class PagedAttention(nn.Module):
         T = q.shape[0]
         D, Hq = self.head_dim, self.num_heads
         rot = self.rotary
+        kvq = None
+        ks_t = vs_t = None
+        if k_cache.element_size() == 1:
+            if k_cache.dtype == torch.int8 and self.k_scale == 1.0 and self.v_scale == 1.0:
+                self.k_scale = self.v_scale = 1.0 / 16.0     # no calibrated scales were loaded
+            if self._scale_t is None or self._scale_t.device != q.device:
+                self._scale_t = torch.tensor([self.k_scale, self.v_scale], dtype=torch.float32,
+                                             device=q.device)
+            ks_t, vs_t = self._scale_t[0:1], self._scale_t[1:2]
+            kvq = (self.k_scale, self.v_scale, 0.0, 0.0)
         C.rope_cache_flash(q, k, v, md.positions if rot is not None else None,
                            rot.cos_sin_cache if rot is not None else None,
                            rot.is_neox if rot is not None else True, D, md.slot_mapping,
-                           k_cache, v_cache)
+                           k_cache, v_cache, ks_t, vs_t)
         out = torch.empty((T, Hq * D), dtype=q.dtype, device=q.device)
         nd = md.num_decode_tokens
         if nd > 0:
             C.paged_decode(q[:nd].view(nd, Hq, D), k_cache, v_cache, md.block_tables[:nd],
                            md.seq_lens[:nd], self.scale, out=out[:nd].view(nd, Hq, D),
-                           num_splits=md.decode_splits, workspace=md.decode_workspace)
+                           num_splits=md.decode_splits, workspace=md.decode_workspace,
+                           kv_quant=kvq)
         if md.num_prefills > 0:
             npf = T - nd
             C.varlen_prefill(q[nd:].view(npf, Hq, D), k_cache, v_cache,
@@ -106,7 +123,8 @@ class PagedAttention(nn.Module):
                              md.cu_q_prefill,
                              md.seq_lens[md.num_decodes:md.num_decodes + md.num_prefills],
                              self.scale, md.num_q_tiles, out=out[nd:].view(npf, Hq, D),
-                             window=self.window, num_q_tiles_128=md.num_q_tiles_128)
+                             window=self.window, num_q_tiles_128=md.num_q_tiles_128,
+                             kv_quant=kvq)
         return out
 
     # -- CPU reference ----------------------------------------------------------

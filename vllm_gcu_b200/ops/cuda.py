@@ -186,7 +186,7 @@ def rope_cache_flash(q: Optional[torch.Tensor], k: Optional[torch.Tensor],
         nb, bs = k_cache.shape[0], k_cache.shape[1]
         assert k_cache.stride(1) * bs == k_cache.stride(0), "slots must be evenly strided"
         slot_stride, head_stride, num_slots = k_cache.stride(1), k_cache.stride(2), nb * bs
-        fp8 = int(k_cache.dtype == FP8)
+        fp8 = 1 if k_cache.dtype == FP8 else (2 if k_cache.dtype == torch.int8 else 0)
     call("b200_rope_cache_flash", ptr(q), q.stride(0) if q is not None else 0, ptr(k),
          k.stride(0) if k is not None else 0, ptr(v), v.stride(0) if v is not None else 0,
          ptr(positions), ptr(cos_sin),
@@ -299,8 +299,9 @@ def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                  block_tables: torch.Tensor, seq_lens: torch.Tensor, scale: float,
                  out: Optional[torch.Tensor] = None, num_splits: int = 0,
                  workspace: Optional[tuple[torch.Tensor, torch.Tensor]] = None,
-                 max_seq_len: int = 0) -> torch.Tensor:
-    """q ``[B, Hq, D]`` (row stride free), caches ``[blocks, bs, Hkv, D]``."""
+                 max_seq_len: int = 0, kv_quant: Optional[tuple] = None) -> torch.Tensor:
+    """q ``[B, Hq, D]`` (row stride free), caches ``[blocks, bs, Hkv, D]``.  For fp8 / int8
+    caches ``kv_quant = (k_scale, v_scale, k_zero_point, v_zero_point)`` (floats)."""
     B, Hq, D = q.shape
     nb, bs, Hkv, _ = k_cache.shape
     assert q.stride(2) == 1 and q.stride(1) == D
@@ -321,6 +322,11 @@ def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
             ptr(v_cache), k_cache.stride(1), k_cache.stride(2), nb * bs, ptr(block_tables),
             block_tables.stride(0), bs, ptr(seq_lens), ptr(tmp_out), ptr(tmp_lse), num_splits,
             B, Hq, Hkv, D, float(scale), DTYPE_CODE[q.dtype], stream_ptr())
+    if k_cache.element_size() == 1:
+        ks, vs, kz, vz = kv_quant or (1.0, 1.0, 0.0, 0.0)
+        call("b200_paged_decode_q8kv", *args[:-1], 1 if k_cache.dtype == FP8 else 2, float(ks),
+             float(vs), float(kz), float(vz), stream_ptr())
+        return out
     if USE_TMA_DECODE and D == 128 and bs % 16 == 0 and k_cache.stride(2) == 128 \
             and k_cache.stride(1) == Hkv * 128:
         rc = N.lib().b200_paged_decode_tma(*args)      # TMA-fed variant (attention_tma.cu)
@@ -340,7 +346,7 @@ def varlen_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor
                    block_tables: torch.Tensor, cu_q: torch.Tensor, seq_lens: torch.Tensor,
                    scale: float, num_q_tiles: int, out: Optional[torch.Tensor] = None,
                    causal: bool = True, window: int = 0, return_lse: bool = False,
-                   num_q_tiles_128: Optional[int] = None):
+                   num_q_tiles_128: Optional[int] = None, kv_quant: Optional[tuple] = None):
     """q ``[T, Hq, D]``; ``num_q_tiles`` >= sum_b ceil(q_len_b / 64) (host-known);
     ``num_q_tiles_128`` the same for 128-row tiles (defaults to the 64-row bound)."""
     T, Hq, D = q.shape
@@ -349,6 +355,15 @@ def varlen_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor
     if out is None:
         out = torch.empty((T, Hq, D), device=q.device, dtype=q.dtype)
     lse = torch.empty((Hq, T), device=q.device, dtype=torch.float32) if return_lse else None
+    if k_cache.element_size() == 1:
+        ks, vs, kz, vz = kv_quant or (1.0, 1.0, 0.0, 0.0)
+        call("b200_varlen_prefill_q8kv", ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(lse),
+             ptr(cu_q), ptr(seq_lens), ptr(k_cache), ptr(v_cache), k_cache.stride(1),
+             k_cache.stride(2), nb * bs, ptr(block_tables), block_tables.stride(0), bs,
+             block_tables.shape[0], T, num_q_tiles, Hq, Hkv, D, float(scale), int(causal),
+             int(window), DTYPE_CODE[q.dtype], 1 if k_cache.dtype == FP8 else 2, float(ks),
+             float(vs), float(kz), float(vz), stream_ptr())
+        return (out, lse) if return_lse else out
     if USE_FMHA_PREFILL and q.dtype == torch.bfloat16 and D == 128:
         # tcgen05 kernel (attention_fmha.cu); -20 = layout outside what it covers
         rc = N.lib().b200_fmha_prefill(
