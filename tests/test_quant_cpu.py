@@ -106,3 +106,83 @@ def test_int8_w8a8():
     layer.load_weight("out_scales", ws)
     layer.load_weight("bias", torch.ones(N))
     assert (layer(x) - (x @ w.t() + 1)).abs().max() < 0.05
+
+
+def _awq_pack(t):
+    R, C = t.shape
+    v = t.view(R, C // 8, 8).to(torch.int64)
+    out = torch.zeros(R, C // 8, dtype=torch.int64)
+    for c in range(8):
+        out |= v[:, :, c] << (4 * Q.AWQ_REVERSE_ORDER[c])
+    return _to_i32(out)
+
+
+def test_moe_checkpoints_awq_fp8_block_and_int8_load_into_the_expert_tensors():
+    """Quantised expert tensors (AWQ ``moe_wna16``, fp8 128x128 block, int8 per-channel) are
+    de-quantised at load into the grouped-GEMM expert weights; the model then matches one
+    loaded from the de-quantised bf16 checkpoint."""
+    import dataclasses
+
+    from vllm_gcu_b200.config import preset
+    from vllm_gcu_b200.models import build_model
+    torch.manual_seed(3)
+    base_cfg = dataclasses.replace(preset("tiny-qwen3-moe"), dtype=torch.float32)
+    ref_model = build_model(base_cfg, "cpu")
+    ref_model.init_random(0)
+    E, I, H = base_cfg.num_experts, base_cfg.moe_intermediate_size, base_cfg.hidden_size
+    L = base_cfg.num_hidden_layers
+    g = 32
+    for kind in ("awq", "fp8", "w8a8"):
+        qcfg = {"awq": {"quant_method": "awq", "bits": 4, "group_size": g,
+                        "modules_to_not_convert": ["self_attn", "gate", "lm_head"]},
+                "fp8": {"quant_method": "fp8", "weight_block_size": [128, 128],
+                        "ignored_layers": ["self_attn", "mlp.gate", "lm_head"]},
+                "w8a8": {"ignored_layers": ["self_attn", "mlp.gate", "lm_head"]}}[kind]
+        name = {"awq": "moe_wna16_gcu", "fp8": "fp8", "w8a8": "w8a8"}[kind]
+        cfg = dataclasses.replace(base_cfg, quantization=name, quant_config=qcfg)
+        sd_q, sd_ref = {}, {}
+        for k, v in ref_model.state_dict().items():
+            if ".mlp.experts." not in k:
+                sd_q["model." + k if not k.startswith(("model.", "lm_head")) else k] = v
+        # rebuild per-expert HF tensors from the stacked parameters of the reference model
+        for li in range(L):
+            moe = ref_model.layers[str(li)].mlp.experts
+            for e in range(E):
+                mats = {"gate_proj": moe.w13.data[e, :I], "up_proj": moe.w13.data[e, I:],
+                        "down_proj": moe.w2.data[e]}
+                for proj, w in mats.items():
+                    pre = f"model.layers.{li}.mlp.experts.{e}.{proj}."
+                    N_, K_ = w.shape
+                    if kind == "awq":
+                        q = torch.randint(0, 16, (K_, N_), dtype=torch.uint8)
+                        z = torch.randint(0, 16, (K_ // g, N_), dtype=torch.uint8)
+                        s = torch.rand(K_ // g, N_) * 0.02 + 0.01
+                        deq = ((q.float() - z.float().repeat_interleave(g, 0))
+                               * s.repeat_interleave(g, 0)).t().contiguous()
+                        sd_q[pre + "qweight"] = _awq_pack(q)
+                        sd_q[pre + "qzeros"] = _awq_pack(z)
+                        sd_q[pre + "scales"] = s
+                    elif kind == "fp8":
+                        q = (w * 8).to(torch.float8_e4m3fn)
+                        s = torch.rand(-(-N_ // 128), -(-K_ // 128)) * 0.1 + 0.05
+                        deq = q.float() * s.repeat_interleave(128, 0)[:N_].repeat_interleave(
+                            128, 1)[:, :K_]
+                        sd_q[pre + "weight"] = q
+                        sd_q[pre + "weight_scale_inv"] = s
+                    else:
+                        q = torch.randint(-127, 128, (N_, K_), dtype=torch.int8)
+                        s = torch.rand(N_) * 0.002 + 0.001
+                        deq = q.float() * s[:, None]
+                        sd_q[pre + "weight"] = q
+                        sd_q[pre + "weight_scale"] = s
+                    sd_ref[pre + "weight"] = deq
+        # the un-quantised parts are shared; names follow the HF layout of the checkpoint
+        hf_common = {k: v for k, v in sd_q.items() if ".experts." not in k}
+        m_ref = build_model(base_cfg, "cpu")
+        m_ref.load_weights(list(hf_common.items()) + list(sd_ref.items()))
+        m_q = build_model(cfg, "cpu")
+        m_q.load_weights(list(sd_q.items()))
+        for li in range(L):
+            a, b = m_ref.layers[str(li)].mlp.experts, m_q.layers[str(li)].mlp.experts
+            assert torch.allclose(a.w13.data, b.w13.data, atol=1e-5), kind
+            assert torch.allclose(a.w2.data, b.w2.data, atol=1e-5), kind

@@ -408,11 +408,33 @@ class GPTQConfig(QuantConfig):
                                  bool(self.cfg.get("sym", False)))
 
 
+class MoeWNA16Config(QuantConfig):
+    """``moe_wna16``: AWQ or GPTQ tensors for the experts (de-quantised at load, see
+    ``layers.quant.moe``) and the matching weight-only method for the linear layers
+    (vllm_gcu/kernels/quantization/moe_wna16.py:26-643)."""
+    name = "moe_wna16"
+
+    def __init__(self, cfg: dict):
+        super().__init__(cfg)
+        inner = (self.cfg.get("quant_method") or "awq").replace("_gcu", "")
+        self.inner = (GPTQConfig if inner == "gptq" else AWQConfig)(cfg)
+
+    def _method(self, prefix):
+        return self.inner._method(prefix)
+
+
+class W4A8Config(Fp8Config):
+    """``w4a8``: int4 expert tensors (group scales), fp8 128x128 block-scaled dense layers
+    (vllm_gcu/kernels/quantization/w4a8.py:134-235)."""
+    name = "w4a8"
+
+
 _CONFIGS = {"fp8": Fp8Config, "fp8_gcu": Fp8Config, "w8a8": W8A8Config, "w8a8_gcu": W8A8Config,
             "compressed-tensors": W8A8Config, "awq": AWQConfig, "awq_gcu": AWQConfig,
-            "gptq": GPTQConfig, "gptq_gcu": GPTQConfig}
+            "gptq": GPTQConfig, "gptq_gcu": GPTQConfig, "moe_wna16": MoeWNA16Config,
+            "moe_wna16_gcu": MoeWNA16Config, "w4a8": W4A8Config, "w4a8_gcu": W4A8Config}
 
-SUPPORTED_QUANTIZATION = sorted(_CONFIGS) + ["moe_wna16", "moe_wna16_gcu", "w4a8_gcu"]
+SUPPORTED_QUANTIZATION = sorted(_CONFIGS)
 
 
 def register_quantization_config(name: str, cls) -> None:

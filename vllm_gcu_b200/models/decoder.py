@@ -255,6 +255,9 @@ class DecoderLM(nn.Module):
                 continue        # another pipeline stage / unused tensor
             mod.load_weight(pname, tensor, sid)
             loaded.add(name)
+        fin = getattr(self, "finish_loading", None)
+        if fin is not None:
+            fin()
         self.finalize_weights()
         return loaded
 

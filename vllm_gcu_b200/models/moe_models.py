@@ -18,12 +18,43 @@ from .decoder import DecoderLM
 
 _EXPERT_RE = re.compile(r"^(model\.layers\.\d+\.)(mlp|block_sparse_moe)\.experts\.(\d+)\."
                         r"(gate_proj|up_proj|down_proj|w1|w2|w3)\.weight$")
+# quantised checkpoints: the same expert projections with format-specific tensor suffixes
+_QEXPERT_RE = re.compile(r"^(model\.layers\.\d+\.)(mlp|block_sparse_moe)\.experts\.(\d+)\."
+                         r"(gate_proj|up_proj|down_proj|w1|w2|w3)\."
+                         r"(weight|qweight|qzeros|scales|g_idx|weight_scale|weight_scale_inv|"
+                         r"out_scales|input_scale|in_scales)$")
 _WHICH = {"gate_proj": "gate", "up_proj": "up", "down_proj": "down",
           "w1": "gate", "w3": "up", "w2": "down"}
 
 
 class MoeDecoderLM(DecoderLM):
+    def _expert_loader(self):
+        ld = getattr(self, "_qexpert_loader", None)
+        if ld is None:
+            from ..layers.quant.moe import QuantExpertLoader
+            ld = QuantExpertLoader(self.cfg.quantization, self.cfg.quant_config, self.cfg.dtype)
+            self._qexpert_loader = ld
+        return ld
+
+    def finish_loading(self) -> None:
+        """Called after the last checkpoint tensor: flushes buffered quantised experts."""
+        ld = getattr(self, "_qexpert_loader", None)
+        if ld is not None:
+            ld.flush(lambda key: self.layers[key.split(".")[2]].mlp.experts)
+
     def load_special(self, name, tensor, owners) -> bool:
+        if self.cfg.quantization:
+            mq = _QEXPERT_RE.match(name)
+            if mq is not None:
+                layer = int(mq.group(1).split(".")[2])
+                if not (self.start_layer <= layer < self.end_layer):
+                    return True
+                if mq.group(5) in ("input_scale", "in_scales"):
+                    return True                 # activations stay bf16 on this path
+                moe = self.layers[str(layer)].mlp.experts
+                self._expert_loader().add(moe, mq.group(1), int(mq.group(3)), _WHICH[mq.group(4)],
+                                          mq.group(5), tensor.to(moe.w13.device))
+                return True
         m = _EXPERT_RE.match(name)
         if m is not None:
             layer = int(m.group(1).split(".")[2])
@@ -66,3 +97,11 @@ class MixtralForCausalLM(MoeDecoderLM):
         if cfg.moe_intermediate_size == 0:
             cfg = dataclasses.replace(cfg, moe_intermediate_size=cfg.intermediate_size)
         super().__init__(cfg, device)
+
+
+class DeepseekMoeForCausalLM(MoeDecoderLM):
+    """DeepSeek-MoE (v1, e.g. deepseek-moe-16b): multi-head attention without MLA, softmax
+    top-k routing without groups, shared experts, the first ``first_k_dense_replace`` layers
+    dense.  The reference's ``QuantDeepseekForCausalLM`` serves it from per-expert quantised
+    linears (vllm_gcu/models/deepseek_moe_quant.py:487); here the quantised expert tensors go
+    through ``layers.quant.moe``."""
