@@ -112,6 +112,12 @@ class ModelConfig:
     @classmethod
     def from_hf_dict(cls, d: dict, **overrides) -> "ModelConfig":
         archs = d.get("architectures") or ["LlamaForCausalLM"]
+        if isinstance(d.get("text_config"), dict):
+            # multimodal configs nest the language model's fields; vision_config, token ids
+            # and everything else stay reachable through ``extra``
+            d = {**{k: v for k, v in d.items() if k != "text_config"},
+                 **{k: v for k, v in d["text_config"].items()
+                    if k not in ("architectures", "model_type")}}
         names = {f.name for f in dataclasses.fields(cls)}
         kw: dict[str, Any] = {"architecture": archs[0]}
         alias = {"n_routed_experts": "num_experts", "num_local_experts": "num_experts",
@@ -132,6 +138,12 @@ class ModelConfig:
             kw.setdefault("partial_rotary_factor", d.get("partial_rotary_factor", 0.5))
         if "Deepseek" in arch:
             kw.setdefault("rope_is_neox", False)
+        if "rope_parameters" in d and isinstance(d["rope_parameters"], dict):
+            rp = d["rope_parameters"]
+            kw.setdefault("rope_theta", rp.get("rope_theta", kw.get("rope_theta", 10000.0)))
+            if kw.get("rope_scaling") is None and (rp.get("mrope_section") or
+                                                   rp.get("rope_type", "default") != "default"):
+                kw["rope_scaling"] = rp
         qc = d.get("quantization_config")
         if qc:
             kw["quant_config"] = qc

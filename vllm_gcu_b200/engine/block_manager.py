@@ -157,8 +157,17 @@ class KVCacheManager:
         self.block_size = block_size
         self.watermark = watermark_blocks
 
+    @staticmethod
+    def _extra(req) -> tuple:
+        """What besides the token ids identifies a block's content: the LoRA adapter and the
+        salt of multimodal requests (same placeholder ids, different image)."""
+        salt = getattr(req, "cache_salt", None)
+        if salt is not None:
+            return (req.lora_id, salt)
+        return (req.lora_id,) if req.lora_id >= 0 else ()
+
     def get_computed_blocks(self, req) -> tuple[list[int], int]:
-        extra = (req.lora_id,) if req.lora_id >= 0 else ()
+        extra = self._extra(req)
         ids = self.pool.find_cached_prefix(req.all_token_ids, extra)
         return ids, len(ids) * self.block_size
 
@@ -199,7 +208,7 @@ class KVCacheManager:
         done = getattr(req, "_hashed_blocks", 0)
         if nfull <= done:
             return
-        extra = (req.lora_id,) if req.lora_id >= 0 else ()
+        extra = self._extra(req)
         parent = getattr(req, "_last_hash", None)
         if done == 0:
             parent = None

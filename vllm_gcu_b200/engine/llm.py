@@ -123,10 +123,21 @@ class LLMEngine:
     def add_request(self, prompt_token_ids: Sequence[int],
                     sampling_params: Optional[SamplingParams] = None,
                     request_id: Optional[str] = None, priority: int = 0,
-                    eos_token_id: Optional[int] = None, lora_id: int = -1) -> str:
+                    eos_token_id: Optional[int] = None, lora_id: int = -1,
+                    multi_modal_data: Optional[dict] = None) -> str:
+        """``multi_modal_data``: processor outputs of a multimodal model
+        (``{"pixel_values": [n_patches, C*Tp*P*P], "image_grid_thw": [n_images, 3]}``); the
+        prompt must already contain one placeholder token per merged patch."""
         rid = request_id if request_id is not None else f"req-{next(self._ids)}"
         req = Request(rid, list(prompt_token_ids), sampling_params or SamplingParams(),
                       eos_token_id=eos_token_id, priority=priority, lora_id=lora_id)
+        if multi_modal_data:
+            prep = getattr(self.model, "prepare_request", None)
+            if prep is None:
+                raise ValueError(f"{self.cfg.model.architecture} takes no multimodal input")
+            for k, v in prep(req.prompt_token_ids, multi_modal_data["pixel_values"],
+                             multi_modal_data["image_grid_thw"]).items():
+                setattr(req, k, v)
         sp_ = req.sampling_params
         if sp_.has_penalties or sp_.logprobs is not None or sp_.prompt_logprobs is not None:
             # these need the ids of every earlier token on the host before the next step
@@ -244,7 +255,13 @@ class LLMEngine:
             sps = [sampling_params or SamplingParams()] * len(prompts)
         else:
             sps = list(sampling_params)
-        order = [self.add_request(p, sp) for p, sp in zip(prompts, sps)]
+        order = []
+        for p, sp in zip(prompts, sps):
+            if isinstance(p, dict):      # {"prompt_token_ids": [...], "multi_modal_data": {...}}
+                order.append(self.add_request(p["prompt_token_ids"], sp,
+                                              multi_modal_data=p.get("multi_modal_data")))
+            else:
+                order.append(self.add_request(p, sp))
         final: dict[str, RequestOutput] = {}
         prev, self.scheduler.emit_partial = self.scheduler.emit_partial, False
         try:

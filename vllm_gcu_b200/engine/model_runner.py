@@ -120,6 +120,7 @@ class ModelRunner:
         self.timing_meta: list = []                # (decodes, prefills, tokens) per timed step
         self.keep_logits = False                   # debugging / tests: keep last step's logits
         self._features = None                      # per-step sampling extras (penalties, logprobs)
+        self._mm_inputs = None                     # (inputs_embeds, mrope positions) of a step
         from .. import envs
         self.nvtx = bool(envs.NVTX) and self.is_cuda
         self.last_logits: Optional[torch.Tensor] = None
@@ -403,6 +404,22 @@ class ModelRunner:
         tok_rows = np.repeat(rows, ntok)
         i64[o_slot:o_slot + T_real] = (self.bt_host[tok_rows, blk_idx].astype(np.int64) * bs
                                        + pos % bs)
+        # multimodal requests: rotary positions differ from sequence positions (M-RoPE)
+        mm_step = any(s_.req.mm_embeds is not None or s_.req.mrope_delta for s_ in order)
+        mm_chunks = []
+        if mm_step:
+            deltas = np.fromiter((s_.req.mrope_delta for s_ in order), dtype=np.int64, count=B)
+            nprompt = np.fromiter((len(s_.req.prompt_token_ids) for s_ in order), dtype=np.int64,
+                                  count=B)
+            tok_delta = np.repeat(deltas, ntok)
+            pos += np.where(pos >= np.repeat(nprompt, ntok), tok_delta, 0)
+            for j, s_ in enumerate(order):
+                r_ = s_.req
+                if r_.mm_embeds is None and r_.mrope_positions is None:
+                    continue
+                if s_.start < len(r_.prompt_token_ids):
+                    mm_chunks.append((int(tok_off[j]), s_.start,
+                                      min(s_.start + s_.num_tokens, len(r_.prompt_token_ids)), r_))
         if T > T_real:
             i64[o_slot + T_real:o_slot + T] = -1
             i64[o_ids + T_real:o_ids + T] = 0
@@ -518,6 +535,9 @@ class ModelRunner:
             q_lens_cpu=[int(x) for x in ntok], seq_lens_cpu=[int(x) for x in seq_after])
 
         self._features = self._build_features(order, samplers, tok_off) if feat else None
+        self._mm_inputs = self._build_mm_inputs(mm_chunks, T) if mm_chunks else None
+        if self._mm_inputs is not None:
+            md.mrope_positions = self._mm_inputs[1]
         if self.nvtx:
             torch.cuda.nvtx.range_push("decode_step" if npf == 0 else
                                        ("prefill_step" if nd == 0 else "mixed_step"))
@@ -559,6 +579,28 @@ class ModelRunner:
                           width, device_ms_events=(ev0, ev1) if ev0 is not None else None,
                           draft_host=self.draft_host if self.drafter is not None else None,
                           extra=extra)
+
+    def _build_mm_inputs(self, mm_chunks, T: int):
+        """(inputs_embeds [T, H], mrope_positions [3, T]) of a step that contains multimodal
+        prompt tokens: placeholder rows of the token embedding are replaced by the vision
+        embeddings of the request, and the prompt part of every such request gets its
+        (t, h, w) rotary positions; all other tokens use their 1-D position on all axes."""
+        with torch.inference_mode():
+            emb = self.model.embed_tokens(self.input_ids[:T]).clone() \
+                if self.model.is_first_stage else None
+            mpos = self.positions[:T].unsqueeze(0).repeat(3, 1)
+            for a, lo, hi, req in mm_chunks:
+                if req.mrope_positions is not None:
+                    mpos[:, a:a + hi - lo] = req.mrope_positions[:, lo:hi].to(mpos.device)
+                if req.mm_embeds is not None and emb is not None:
+                    import bisect
+                    p0 = bisect.bisect_left(req.mm_positions, lo)
+                    p1 = bisect.bisect_left(req.mm_positions, hi)
+                    if p1 > p0:
+                        rows = torch.tensor([a + p - lo for p in req.mm_positions[p0:p1]],
+                                            device=emb.device)
+                        emb[rows] = req.mm_embeds[p0:p1].to(device=emb.device, dtype=emb.dtype)
+        return emb, mpos
 
     def _build_features(self, order, samplers, tok_off) -> dict:
         """Host-side description of the per-request sampling extras of this step: penalty
@@ -659,7 +701,9 @@ class ModelRunner:
             dist.recv(x, src, group=pp.device_group)
             dist.recv(r, src, group=pp.device_group)
             inter = (x, r)
-        hidden = self.model(self.input_ids[:T], md, self.kv_caches, intermediate=inter)
+        mm = getattr(self, "_mm_inputs", None)
+        hidden = self.model(self.input_ids[:T], md, self.kv_caches, intermediate=inter,
+                            inputs_embeds=mm[0] if mm is not None else None)
         if pp.world_size > 1:
             import torch.distributed as dist
             last = pp.ranks[-1]

@@ -66,6 +66,14 @@ class Request:
     lora_id: int = -1
     is_idle: bool = False                     # keep-alive request of a DP replica
     kv_transfer_params: Optional[dict] = None
+    # multimodal inputs: embeddings of the placeholder tokens (row i belongs to prompt position
+    # mm_positions[i]), M-RoPE (t, h, w) positions of the prompt ``[3, n_prompt]`` and the
+    # offset added to the position of every later token
+    mm_embeds: Optional[Any] = None
+    mm_positions: Optional[list] = None
+    mrope_positions: Optional[Any] = None
+    mrope_delta: int = 0
+    cache_salt: Optional[int] = None          # separates prefix-cache entries (image content)
 
     # mutable state -------------------------------------------------------
     status: RequestStatus = RequestStatus.WAITING

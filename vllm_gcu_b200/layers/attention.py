@@ -48,6 +48,10 @@ class AttentionMetadata:
     seq_lens_cpu: list[int] = field(default_factory=list)
     # speculative decoding: every request with q_len > 1 verifies draft tokens
     is_dummy: bool = False
+    # multimodal rotary embedding: (t, h, w) position of every token, ``[3, T]``; the cos / sin
+    # rows gathered per section are cached here by the first layer of a step
+    mrope_positions: Optional[torch.Tensor] = None
+    mrope_cos_sin: Optional[torch.Tensor] = None
 
 
 def allocate_kv_cache(num_layers: int, num_blocks: int, block_size: int, kv_heads: int,
@@ -66,6 +70,7 @@ class PagedAttention(nn.Module):
         self.rotary = rotary
         self.q_norm, self.k_norm = q_norm, k_norm
         self.window = sliding_window
+        self.mrope_section: Optional[list[int]] = None     # set by M-RoPE models (Qwen2.5-VL)
         # per-tensor scales of an fp8 / int8 KV cache (value = stored * scale); checkpoints may
         # provide them (``load_kv_cache_scales`` of the reference's quantised models,
         # vllm_gcu/models/deepseek_moe_quant.py:487), the default 1.0 suits fp8
@@ -90,11 +95,28 @@ class PagedAttention(nn.Module):
             return self._forward_cuda(q, k, v, k_cache, v_cache, md)
         return self._forward_ref(q, k, v, k_cache, v_cache, md)
 
+    def _rope_inputs(self, md: AttentionMetadata, T: int):
+        """(positions, cos/sin table) of this step; with M-RoPE the table rows are gathered
+        per section once per step and the ordinary rotary kernel runs with positions 0..T-1
+        (vllm_gcu/kernels/rotary_embedding.py:108-169)."""
+        rot = self.rotary
+        if rot is None:
+            return None, None
+        if md.mrope_positions is None or not self.mrope_section:
+            return md.positions, rot.cos_sin_cache
+        if md.mrope_cos_sin is None:
+            from .basic import mrope_gather_cos_sin
+            md.mrope_cos_sin = mrope_gather_cos_sin(
+                rot.cos_sin_cache.float(), md.mrope_positions[:, :T], self.mrope_section)
+            md.mrope_arange = torch.arange(T, device=md.mrope_cos_sin.device)
+        return md.mrope_arange, md.mrope_cos_sin
+
     # -- GPU -----------------------------------------------------------------
     def _forward_cuda(self, q, k, v, k_cache, v_cache, md: AttentionMetadata) -> torch.Tensor:
         T = q.shape[0]
         D, Hq = self.head_dim, self.num_heads
         rot = self.rotary
+        rope_pos, rope_table = self._rope_inputs(md, T)
         kvq = None
         ks_t = vs_t = None
         if k_cache.element_size() == 1:
@@ -105,8 +127,7 @@ class PagedAttention(nn.Module):
                                              device=q.device)
             ks_t, vs_t = self._scale_t[0:1], self._scale_t[1:2]
             kvq = (self.k_scale, self.v_scale, 0.0, 0.0)
-        C.rope_cache_flash(q, k, v, md.positions if rot is not None else None,
-                           rot.cos_sin_cache if rot is not None else None,
+        C.rope_cache_flash(q, k, v, rope_pos, rope_table,
                            rot.is_neox if rot is not None else True, D, md.slot_mapping,
                            k_cache, v_cache, ks_t, vs_t)
         out = torch.empty((T, Hq * D), dtype=q.dtype, device=q.device)
@@ -132,7 +153,11 @@ class PagedAttention(nn.Module):
         T = q.shape[0]
         D, Hq, Hkv = self.head_dim, self.num_heads, self.num_kv_heads
         if self.rotary is not None:
-            q, k = self.rotary(md.positions, q, k)
+            rope_pos, rope_table = self._rope_inputs(md, T)
+            if rope_table is self.rotary.cos_sin_cache:
+                q, k = self.rotary(md.positions, q, k)
+            else:
+                q, k = ref.rotary_embedding(rope_pos, q, k, D, rope_table, self.rotary.is_neox)
         ref.reshape_and_cache_flash(k.reshape(T, Hkv, D), v.reshape(T, Hkv, D), k_cache, v_cache,
                                     md.slot_mapping)
         B = md.num_decodes + md.num_prefills

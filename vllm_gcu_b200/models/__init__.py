@@ -20,6 +20,8 @@ _REGISTRY: dict[str, str] = {
     "Qwen3MoeForCausalLM": "vllm_gcu_b200.models.moe_models:Qwen3MoeForCausalLM",
     "MixtralForCausalLM": "vllm_gcu_b200.models.moe_models:MixtralForCausalLM",
     "QuantMixtralForCausalLM": "vllm_gcu_b200.models.moe_models:MixtralForCausalLM",
+    "Qwen2_5_VLForConditionalGeneration":
+        "vllm_gcu_b200.models.qwen2_5_vl:Qwen2_5_VLForConditionalGeneration",
     "DeepseekForCausalLM": "vllm_gcu_b200.models.moe_models:DeepseekMoeForCausalLM",
     "QuantDeepseekForCausalLM": "vllm_gcu_b200.models.moe_models:DeepseekMoeForCausalLM",
     "DeepseekV2ForCausalLM": "vllm_gcu_b200.models.deepseek:DeepseekV3ForCausalLM",
