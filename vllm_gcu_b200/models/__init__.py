@@ -22,6 +22,9 @@ _REGISTRY: dict[str, str] = {
     "QuantMixtralForCausalLM": "vllm_gcu_b200.models.moe_models:MixtralForCausalLM",
     "Qwen2_5_VLForConditionalGeneration":
         "vllm_gcu_b200.models.qwen2_5_vl:Qwen2_5_VLForConditionalGeneration",
+    "GotOcr2ForConditionalGeneration":
+        "vllm_gcu_b200.models.got_ocr2:GotOcr2ForConditionalGeneration",
+    "GOTQwenForCausalLM": "vllm_gcu_b200.models.got_ocr2:GotOcr2ForConditionalGeneration",
     "DeepseekForCausalLM": "vllm_gcu_b200.models.moe_models:DeepseekMoeForCausalLM",
     "QuantDeepseekForCausalLM": "vllm_gcu_b200.models.moe_models:DeepseekMoeForCausalLM",
     "DeepseekV2ForCausalLM": "vllm_gcu_b200.models.deepseek:DeepseekV3ForCausalLM",
