@@ -200,3 +200,182 @@ B200_API int b200_free_pinned(void* p, int numa_node) {
 B200_API int b200_gpu_pci_bus_id(int device, char* out, int len) {
   return static_cast<int>(cudaDeviceGetPCIBusId(out, len, device));
 }
+
+// ---------------------------------------------------------------------------
+// CacheGen arithmetic codec (lmcache/csrc/encode_cuda_new.cpp:29, decode_cuda_new.cpp:28,
+// decode_cuda_prefsum.cpp:27): one stream per (layer, token); the C channel symbols of a
+// token are coded in order with the per-(layer, channel) cumulative table of
+// b200_lmc_calculate_cdf.  Binary arithmetic coder with 32-bit low / high registers and
+// carry-less renormalisation (pending underflow bits).  Table entry i is used as
+// cdf[i] + i so that every symbol keeps a non-empty interval even when the histogram never
+// saw it; encoder and decoder apply the same rule, so any table decodes what it encoded.
+// ---------------------------------------------------------------------------
+namespace b200 {
+namespace lmc {
+
+struct BitWriter {
+  uint8_t* dst;
+  int cap;
+  int nbytes;
+  uint32_t acc;
+  int nbits;
+  bool overflow;
+  __device__ void put(uint32_t bit) {
+    acc = (acc << 1) | (bit & 1u);
+    if (++nbits == 8) {
+      if (nbytes < cap) dst[nbytes] = static_cast<uint8_t>(acc);
+      else overflow = true;
+      ++nbytes;
+      acc = 0;
+      nbits = 0;
+    }
+  }
+  __device__ void put_with_pending(uint32_t bit, int& pending) {
+    put(bit);
+    for (; pending > 0; --pending) put(bit ^ 1u);
+  }
+  __device__ void flush() {
+    while (nbits != 0) put(0u);
+  }
+};
+
+__device__ __forceinline__ uint32_t cdf_at(const unsigned short* row, int i, int bins) {
+  return (i >= bins ? 65536u : static_cast<uint32_t>(row[i])) + static_cast<uint32_t>(i);
+}
+
+__global__ void cachegen_encode_kernel(const unsigned short* cdf, const int8_t* sym,
+                                       uint8_t* out, int* out_len, int L, int T, int C,
+                                       int bins, int max_bytes) {
+  const int s = blockIdx.x * blockDim.x + threadIdx.x;
+  if (s >= L * T) return;
+  const int l = s / T;
+  const uint32_t total = 65536u + static_cast<uint32_t>(bins);
+  BitWriter w{out + static_cast<long long>(s) * max_bytes, max_bytes, 0, 0u, 0, false};
+  uint32_t low = 0u, high = 0xFFFFFFFFu;
+  int pending = 0;
+  const int8_t* src = sym + static_cast<long long>(s) * C;
+  for (int c = 0; c < C; ++c) {
+    int v = src[c];
+    v = v < 0 ? 0 : (v >= bins ? bins - 1 : v);
+    const unsigned short* row = cdf + (static_cast<long long>(l) * C + c) * (bins + 1);
+    const unsigned long long span = static_cast<unsigned long long>(high) - low + 1ull;
+    const uint32_t c_lo = cdf_at(row, v, bins), c_hi = cdf_at(row, v + 1, bins);
+    high = low + static_cast<uint32_t>(span * c_hi / total) - 1u;
+    low = low + static_cast<uint32_t>(span * c_lo / total);
+    for (;;) {
+      if (high < 0x80000000u) {
+        w.put_with_pending(0u, pending);
+      } else if (low >= 0x80000000u) {
+        w.put_with_pending(1u, pending);
+      } else if (low >= 0x40000000u && high < 0xC0000000u) {
+        ++pending;
+        low -= 0x40000000u;
+        high -= 0x40000000u;
+      } else {
+        break;
+      }
+      low <<= 1;
+      high = (high << 1) | 1u;
+    }
+  }
+  ++pending;
+  w.put_with_pending(low < 0x40000000u ? 0u : 1u, pending);
+  w.flush();
+  out_len[s] = w.overflow ? -1 : w.nbytes;
+}
+
+struct BitReader {
+  const uint8_t* src;
+  int nbytes;
+  int pos;
+  __device__ uint32_t get() {
+    const int byte = pos >> 3;
+    const uint32_t b = byte < nbytes ? (src[byte] >> (7 - (pos & 7))) & 1u : 0u;
+    ++pos;
+    return b;
+  }
+};
+
+// offsets != null: packed streams (stream s occupies bytes [offsets[s], offsets[s + 1]));
+// otherwise stream s starts at s * max_bytes and lens[s] gives its length.
+__global__ void cachegen_decode_kernel(const unsigned short* cdf, const uint8_t* bytes,
+                                       const int* lens, const long long* offsets, int8_t* out,
+                                       int L, int T, int C, int bins, int max_bytes) {
+  const int s = blockIdx.x * blockDim.x + threadIdx.x;
+  if (s >= L * T) return;
+  const int l = s / T;
+  const uint32_t total = 65536u + static_cast<uint32_t>(bins);
+  BitReader r;
+  if (offsets != nullptr) {
+    r.src = bytes + offsets[s];
+    r.nbytes = static_cast<int>(offsets[s + 1] - offsets[s]);
+  } else {
+    r.src = bytes + static_cast<long long>(s) * max_bytes;
+    r.nbytes = lens[s] < 0 ? 0 : lens[s];
+  }
+  r.pos = 0;
+  uint32_t low = 0u, high = 0xFFFFFFFFu, code = 0u;
+  for (int i = 0; i < 32; ++i) code = (code << 1) | r.get();
+  int8_t* dst = out + static_cast<long long>(s) * C;
+  for (int c = 0; c < C; ++c) {
+    const unsigned short* row = cdf + (static_cast<long long>(l) * C + c) * (bins + 1);
+    const unsigned long long span = static_cast<unsigned long long>(high) - low + 1ull;
+    const uint32_t target = static_cast<uint32_t>(
+        ((static_cast<unsigned long long>(code - low) + 1ull) * total - 1ull) / span);
+    int v = 0;
+    {   // largest v with cdf'(v) <= target (tables are short: linear scan)
+      while (v + 1 < bins && cdf_at(row, v + 1, bins) <= target) ++v;
+    }
+    dst[c] = static_cast<int8_t>(v);
+    const uint32_t c_lo = cdf_at(row, v, bins), c_hi = cdf_at(row, v + 1, bins);
+    high = low + static_cast<uint32_t>(span * c_hi / total) - 1u;
+    low = low + static_cast<uint32_t>(span * c_lo / total);
+    for (;;) {
+      if (high < 0x80000000u) {
+      } else if (low >= 0x80000000u) {
+        low -= 0x80000000u;
+        high -= 0x80000000u;
+        code -= 0x80000000u;
+      } else if (low >= 0x40000000u && high < 0xC0000000u) {
+        low -= 0x40000000u;
+        high -= 0x40000000u;
+        code -= 0x40000000u;
+      } else {
+        break;
+      }
+      low <<= 1;
+      high = (high << 1) | 1u;
+      code = (code << 1) | r.get();
+    }
+  }
+}
+
+}  // namespace lmc
+}  // namespace b200
+
+// cdf int16 [L, C, bins + 1] (as produced by b200_lmc_calculate_cdf), sym int8 [L, T, C];
+// out uint8 [L * T, max_bytes], out_len int32 [L * T] (bytes used; -1: max_bytes too small).
+B200_API int b200_lmc_encode(const void* cdf, const void* sym, void* out, int* out_len, int L,
+                             int T, int C, int bins, int max_bytes, void* stream) {
+  if (L <= 0 || T <= 0) return 0;
+  if (bins <= 0 || bins >= 64 || C <= 0 || max_bytes < 8) return -2;
+  const int n = L * T;
+  b200::lmc::cachegen_encode_kernel<<<(n + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const unsigned short*>(cdf), static_cast<const int8_t*>(sym),
+      static_cast<uint8_t*>(out), out_len, L, T, C, bins, max_bytes);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Inverse of b200_lmc_encode.  Either lens (fixed max_bytes slots) or offsets (int64
+// [L * T + 1] prefix sums over packed streams) describes where each stream lies.
+B200_API int b200_lmc_decode(const void* cdf, const void* bytes, const int* lens,
+                             const long long* offsets, void* out, int L, int T, int C, int bins,
+                             int max_bytes, void* stream) {
+  if (L <= 0 || T <= 0) return 0;
+  if (bins <= 0 || bins >= 64 || C <= 0 || (lens == nullptr && offsets == nullptr)) return -2;
+  const int n = L * T;
+  b200::lmc::cachegen_decode_kernel<<<(n + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const unsigned short*>(cdf), static_cast<const uint8_t*>(bytes), lens, offsets,
+      static_cast<int8_t*>(out), L, T, C, bins, max_bytes);
+  return static_cast<int>(cudaGetLastError());
+}

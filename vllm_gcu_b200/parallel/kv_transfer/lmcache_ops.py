@@ -24,6 +24,8 @@ def _lib():
         lib.b200_lmc_single_layer_kv_transfer.argtypes = [P, P, P, P, I, L, L, I, I, P]
         lib.b200_lmc_rerotate_k.argtypes = [P, L, P, P, P, I, I, I, I, I, I, P]
         lib.b200_lmc_calculate_cdf.argtypes = [P, P, I, I, I, I, P]
+        lib.b200_lmc_encode.argtypes = [P, P, P, P, I, I, I, I, I, P]
+        lib.b200_lmc_decode.argtypes = [P, P, P, P, P, I, I, I, I, I, P]
         lib.b200_alloc_pinned.restype = P
         lib.b200_alloc_pinned.argtypes = [ctypes.c_ulonglong, I]
         lib.b200_free_pinned.argtypes = [P, I]
@@ -206,3 +208,165 @@ def get_gpu_pci_bus_id(device: int) -> str:
     buf = ctypes.create_string_buffer(32)
     _check(_lib().b200_gpu_pci_bus_id(device, buf, 32), "get_gpu_pci_bus_id")
     return buf.value.decode()
+
+
+# ---------------------------------------------------------------------------
+# CacheGen arithmetic codec
+# ---------------------------------------------------------------------------
+def _cdf_at(row, i: int, bins: int) -> int:
+    return (65536 if i >= bins else int(row[i]) & 0xFFFF) + i
+
+
+def _encode_stream_py(rows, syms, bins: int) -> bytes:
+    """Reference of the device coder (same arithmetic, one stream)."""
+    total = 65536 + bins
+    low, high, pending = 0, 0xFFFFFFFF, 0
+    bits: list[int] = []
+
+    def put(b):
+        nonlocal pending
+        bits.append(b)
+        bits.extend([b ^ 1] * pending)
+        pending = 0
+
+    for c, v in enumerate(syms):
+        v = min(max(int(v), 0), bins - 1)
+        span = high - low + 1
+        c_lo, c_hi = _cdf_at(rows[c], v, bins), _cdf_at(rows[c], v + 1, bins)
+        high = low + span * c_hi // total - 1
+        low = low + span * c_lo // total
+        while True:
+            if high < 0x80000000:
+                put(0)
+            elif low >= 0x80000000:
+                put(1)
+                low -= 0x80000000
+                high -= 0x80000000
+            elif low >= 0x40000000 and high < 0xC0000000:
+                pending += 1
+                low -= 0x40000000
+                high -= 0x40000000
+            else:
+                break
+            low = (low << 1) & 0xFFFFFFFF
+            high = ((high << 1) | 1) & 0xFFFFFFFF
+    pending += 1
+    put(0 if low < 0x40000000 else 1)
+    while len(bits) % 8:
+        bits.append(0)
+    return bytes(int("".join(map(str, bits[i:i + 8])), 2) for i in range(0, len(bits), 8))
+
+
+def _decode_stream_py(rows, data: bytes, n: int, bins: int) -> list[int]:
+    total = 65536 + bins
+    pos = 0
+
+    def get():
+        nonlocal pos
+        byte = pos >> 3
+        b = (data[byte] >> (7 - (pos & 7))) & 1 if byte < len(data) else 0
+        pos += 1
+        return b
+
+    low, high, code = 0, 0xFFFFFFFF, 0
+    for _ in range(32):
+        code = (code << 1) | get()
+    out = []
+    for c in range(n):
+        span = high - low + 1
+        target = ((code - low + 1) * total - 1) // span
+        v = 0
+        while v + 1 < bins and _cdf_at(rows[c], v + 1, bins) <= target:
+            v += 1
+        out.append(v)
+        c_lo, c_hi = _cdf_at(rows[c], v, bins), _cdf_at(rows[c], v + 1, bins)
+        high = low + span * c_hi // total - 1
+        low = low + span * c_lo // total
+        while True:
+            if high < 0x80000000:
+                pass
+            elif low >= 0x80000000:
+                low -= 0x80000000
+                high -= 0x80000000
+                code -= 0x80000000
+            elif low >= 0x40000000 and high < 0xC0000000:
+                low -= 0x40000000
+                high -= 0x40000000
+                code -= 0x40000000
+            else:
+                break
+            low = (low << 1) & 0xFFFFFFFF
+            high = ((high << 1) | 1) & 0xFFFFFFFF
+            code = ((code << 1) | get()) & 0xFFFFFFFF
+    return out
+
+
+def encode_fast_new(cdf: torch.Tensor, input_sym: torch.Tensor, output_buffer: torch.Tensor,
+                    output_lengths: torch.Tensor) -> None:
+    """CacheGen encoder (lmcache/csrc/encode_cuda_new.cpp:29): ``cdf`` int16
+    ``[L, C, bins + 1]``, ``input_sym`` int8 ``[L, T, C]``; stream (l, t) is written to
+    ``output_buffer[l, t, :]`` (uint8 ``[L, T, max_bytes]``) and its byte count to
+    ``output_lengths[l, t]`` (int32; -1 when ``max_bytes`` is too small)."""
+    L, T, C = input_sym.shape
+    bins = cdf.shape[-1] - 1
+    max_bytes = output_buffer.shape[-1]
+    if input_sym.is_cuda:
+        rc = _lib().b200_lmc_encode(ptr(cdf.contiguous()), ptr(input_sym.contiguous()),
+                                    ptr(output_buffer), ptr(output_lengths), L, T, C, bins,
+                                    max_bytes, stream_ptr())
+        _check(rc, "encode")
+        return
+    cu = cdf.to(torch.int32) & 0xFFFF
+    for l in range(L):
+        rows = cu[l].tolist()
+        for t in range(T):
+            b = _encode_stream_py(rows, input_sym[l, t].tolist(), bins)
+            if len(b) > max_bytes:
+                output_lengths[l, t] = -1
+                continue
+            output_buffer[l, t, :len(b)] = torch.tensor(list(b), dtype=torch.uint8)
+            output_lengths[l, t] = len(b)
+
+
+def decode_fast_new(cdf: torch.Tensor, bytestreams: torch.Tensor, lengths: torch.Tensor,
+                    output: torch.Tensor) -> None:
+    """Inverse of :func:`encode_fast_new` over fixed-size slots
+    (lmcache/csrc/decode_cuda_new.cpp:28); ``output`` int8 ``[L, T, C]``."""
+    L, T, C = output.shape
+    bins = cdf.shape[-1] - 1
+    if output.is_cuda:
+        rc = _lib().b200_lmc_decode(ptr(cdf.contiguous()), ptr(bytestreams), ptr(lengths), None,
+                                    ptr(output), L, T, C, bins, bytestreams.shape[-1],
+                                    stream_ptr())
+        _check(rc, "decode")
+        return
+    cu = cdf.to(torch.int32) & 0xFFFF
+    for l in range(L):
+        rows = cu[l].tolist()
+        for t in range(T):
+            n = int(lengths[l, t])
+            data = bytes(bytestreams[l, t, :max(n, 0)].tolist())
+            output[l, t] = torch.tensor(_decode_stream_py(rows, data, C, bins), dtype=torch.int8)
+
+
+def decode_fast_prefsum(cdf: torch.Tensor, bytestreams: torch.Tensor,
+                        lengths_prefsum: torch.Tensor, output: torch.Tensor) -> None:
+    """Decoder over packed streams (lmcache/csrc/decode_cuda_prefsum.cpp:27):
+    ``bytestreams`` is one uint8 vector, stream s = (l, t) occupies
+    ``[lengths_prefsum[s], lengths_prefsum[s + 1])`` (int64 ``[L * T + 1]``)."""
+    L, T, C = output.shape
+    bins = cdf.shape[-1] - 1
+    if output.is_cuda:
+        rc = _lib().b200_lmc_decode(ptr(cdf.contiguous()), ptr(bytestreams), None,
+                                    ptr(lengths_prefsum.contiguous()), ptr(output), L, T, C, bins,
+                                    0, stream_ptr())
+        _check(rc, "decode_prefsum")
+        return
+    cu = cdf.to(torch.int32) & 0xFFFF
+    off = lengths_prefsum.tolist()
+    for l in range(L):
+        rows = cu[l].tolist()
+        for t in range(T):
+            s = l * T + t
+            data = bytes(bytestreams[off[s]:off[s + 1]].tolist())
+            output[l, t] = torch.tensor(_decode_stream_py(rows, data, C, bins), dtype=torch.int8)
