@@ -115,6 +115,22 @@ def main():
             err = (got.float() - want).abs().max().item()
             assert err < 0.02 * want.abs().max().item() + 0.02, \
                 f"all_gather_gemm {M}x{N}x{K} rep {rep}: err {err}"
+    # ---- raw NCCL binding (unique id over the gloo group) ---------------------------------
+    from vllm_gcu_b200.parallel.pynccl import PyNcclCommunicator
+    pn = PyNcclCommunicator(rank, world, dev, group=st.tp.cpu_group)
+    x = torch.full((1000,), float(rank + 1), device=dev, dtype=torch.bfloat16)
+    pn.all_reduce(x)
+    torch.cuda.synchronize()
+    assert torch.all(x == world * (world + 1) / 2)
+    y = torch.full((8,), float(rank), device=dev)
+    if rank == 0:
+        pn.send(y, 1)
+    elif rank == 1:
+        pn.recv(y, 0)
+    torch.cuda.synchronize()
+    if rank == 1:
+        assert torch.all(y == 0)
+    pn.destroy()
     if rank == 0:
         print("fused collectives ok", flush=True)
 
