@@ -99,3 +99,22 @@ def test_engine_with_8bit_kv_cache_tracks_bf16(kvd):
     for o in ob + oq:
         assert len(o.outputs[0].logprobs) == 3 and o.outputs[0].cumulative_logprob <= 0
     _native.check_status()
+
+
+def test_oracle_mode_checks_every_step(monkeypatch):
+    """With VLLM_B200_ORACLE=all the GEMM and attention wrappers recompute their result with
+    the torch reference and raise on a mismatch; a short eager run must pass all checks."""
+    from vllm_gcu_b200.ops import cuda as C
+    monkeypatch.setenv("VLLM_B200_ORACLE", "all")
+    assert C.oracle_enabled("gemm_bf16") and C.oracle_enabled("paged_decode")
+    kw = dict(num_hidden_layers=2, hidden_size=512, intermediate_size=1024,
+              num_attention_heads=8, num_key_value_heads=2, head_dim=128, vocab_size=2048,
+              max_num_seqs=8, max_num_batched_tokens=256, max_model_len=256, num_gpu_blocks=128,
+              enforce_eager=True)
+    llm = LLM("llama-3-8b", device="cuda", **kw)
+    out = llm.generate(_prompts(4, [40, 7, 150, 64], 2048, seed=11),
+                       SamplingParams(max_tokens=4, temperature=0.0, ignore_eos=True))
+    assert all(len(o.outputs[0].token_ids) == 4 for o in out)
+    with pytest.raises(C.OracleMismatch):
+        C.oracle_compare("probe", torch.ones(4, device="cuda"), torch.zeros(4))
+    _native.check_status()

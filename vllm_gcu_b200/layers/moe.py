@@ -39,6 +39,17 @@ def select_experts(router_logits: torch.Tensor, cfg: ModelConfig,
                    ) -> tuple[torch.Tensor, torch.Tensor]:
     """Routing weights fp32 ``[T, k]`` and expert ids int32 ``[T, k]``."""
     k = cfg.num_experts_per_tok
+    from .. import envs
+    if envs.FORCE_EP_BALANCE:
+        # synthetic round-robin routing with uniform weights: every expert (hence every
+        # expert-parallel rank) gets the same load, for benchmarking the dispatch path
+        # (VLLM_GCU_FORCE_EP_BALANCE, vllm_gcu/kernels/modular_kernel.py:99-128)
+        T = router_logits.shape[0]
+        E = router_logits.shape[1] if eplb is None else eplb.num_physical
+        base = torch.arange(T, device=router_logits.device)[:, None] * k
+        ids = ((base + torch.arange(k, device=router_logits.device)[None, :]) % E).to(torch.int32)
+        w = torch.full((T, k), 1.0 / k, dtype=torch.float32, device=router_logits.device)
+        return w, ids
     grouped = cfg.n_group > 1 or cfg.scoring_func == "sigmoid" or bias is not None
     scale = cfg.routed_scaling_factor if grouped else 1.0
     if ops.use_native(router_logits):
@@ -245,7 +256,32 @@ class SparseMoeBlock(nn.Module):
         logits = self.gate(x)
         topk_w, topk_ids = select_experts(logits, self.cfg, self.e_score_correction_bias,
                                           self.eplb)
-        shared = self.shared_experts(x) if self.shared_experts is not None else None
+        from .. import envs
+        side = None
+        if (self.shared_experts is not None and self.dispatcher is not None and x.is_cuda
+                and envs.ENABLE_PARALLEL_COMPUTE and not torch.cuda.is_current_stream_capturing()):
+            # shared experts on a side stream, overlapped with the dispatch kernels
+            # (VLLM_GCU_ENABLE_PARALLEL_COMPUTE, vllm_gcu/kernels/prepare_finalize.py:326-336)
+            if not hasattr(self, "_side_stream"):
+                self._side_stream = torch.cuda.Stream()
+            side = self._side_stream
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                shared = self.shared_experts(x)
+        else:
+            shared = self.shared_experts(x) if self.shared_experts is not None else None
+        if side is not None:
+            # the dispatcher adds `shared` in its combine step: join before that
+            xr = self.dispatcher.ws.dispatch(x, topk_w.float(), topk_ids.to(torch.int32),
+                                             get_state().dp_max_tokens) \
+                if hasattr(self.dispatcher, "ws") else None
+            torch.cuda.current_stream().wait_stream(side)
+            if xr is not None:
+                rx, rw, rids, total = xr
+                yr = self.experts(rx, rw, rids, valid_tokens=total)
+                out = self.dispatcher.ws.combine(yr, x.shape[0], shared)
+                tp_partial = tp_size() > 1
+                return (get_comm("tp").all_reduce(out) if tp_partial else out).view(shape)
         if self.dispatcher is not None:
             # tokens differ per rank: all-to-all dispatch / combine; the shared experts are
             # replicated so their (TP-partial) output only needs the TP reduction below

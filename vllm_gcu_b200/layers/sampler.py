@@ -52,6 +52,20 @@ class Sampler(nn.Module):
     def forward(self, logits: torch.Tensor, st: Optional[SamplingTensors],
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Returns int64 token ids ``[B]`` (written into ``out`` when given)."""
+        from .. import envs
+        if envs.SAMPLER_ON_CPU and logits.is_cuda:
+            # debugging aid: the torch reference on the host (VLLM_GCU_SAMPLER_ON_CPU)
+            cpu_st = None
+            if st is not None:
+                cpu_st = SamplingTensors(st.temperature.cpu(),
+                                         None if st.top_k is None else st.top_k.cpu(),
+                                         None if st.top_p is None else st.top_p.cpu(),
+                                         None if st.seeds is None else st.seeds.cpu())
+            ids = self.forward(logits.float().cpu(), cpu_st).to(logits.device)
+            if out is not None:
+                out.copy_(ids)
+                return out
+            return ids
         if ops.use_native(logits):
             if not logits.is_contiguous():
                 logits = logits.contiguous()

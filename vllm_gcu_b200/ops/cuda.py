@@ -37,6 +37,35 @@ def _rowmajor_2d(t: torch.Tensor) -> torch.Tensor:
 # ---------------------------------------------------------------------------
 # GEMM
 # ---------------------------------------------------------------------------
+# ---------------------------------------------------------------------------
+# run-time oracle: selected ops are recomputed with the torch reference and compared
+# ---------------------------------------------------------------------------
+class OracleMismatch(AssertionError):
+    """A native op disagreed with its torch reference (``VLLM_B200_ORACLE``)."""
+
+
+def oracle_enabled(name: str) -> bool:
+    """``VLLM_B200_ORACLE=all`` or a comma-separated list of op names switches the check on.
+    The reference compiles the same idea into its extension as a debug layer: CPU
+    re-implementations and ``*Check`` comparators wrapped around 22 ops
+    (csrc/src/native_vllm.h:37-446)."""
+    from .. import envs
+    sel = envs.ORACLE
+    return sel is not None and ("all" in sel or name in sel)
+
+
+def oracle_compare(name: str, got: torch.Tensor, want: torch.Tensor, rtol: float = 3e-2,
+                   atol: float = 3e-2) -> None:
+    g, w = got.float(), want.float().to(got.device)
+    bad = (g - w).abs() > atol + rtol * w.abs()
+    if bool(bad.any()):
+        idx = int(bad.flatten().nonzero()[0])
+        raise OracleMismatch(
+            f"{name}: {int(bad.sum())} of {bad.numel()} elements differ from the reference "
+            f"(first at flat index {idx}: got {g.flatten()[idx].item():.6g}, "
+            f"want {w.flatten()[idx].item():.6g})")
+
+
 # Decode-sized activations (M <= 256) take the weight-streaming kernel of gemm_skinny.cu.
 USE_SKINNY_GEMM = True
 SKINNY_ALLOW_SPLIT = False      # K-split plans lose to the persistent-tile kernel (measured)
@@ -61,6 +90,21 @@ def _skinny_workspace(device: torch.device):
 def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None,
               bias: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
               epilogue: int = EPI_NONE) -> torch.Tensor:
+    res = _gemm_bf16(a, b, out, bias, residual, epilogue)
+    if oracle_enabled("gemm_bf16") and not torch.cuda.is_current_stream_capturing():
+        from . import ref
+        a2 = a.reshape(-1, a.shape[-1])
+        want = ref.gemm(a2, b, bias=bias, residual=residual, out_dtype=torch.float32)
+        if bias is None and residual is None and epilogue == EPI_SILU_MUL:
+            w4 = want.view(want.shape[0], -1, 2, 128)
+            want = (torch.nn.functional.silu(w4[:, :, 0]) * w4[:, :, 1]).reshape(want.shape[0], -1)
+        oracle_compare("gemm_bf16", res, want, 3e-2, 3e-2 * max(1.0, float(want.abs().mean())))
+    return res
+
+
+def _gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None,
+               bias: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
+               epilogue: int = EPI_NONE) -> torch.Tensor:
     """``out[M,N] = a[M,K] @ b[N,K]^T`` on the tcgen05 path (bf16 in, fp32 accumulate).
 
     epilogue EPI_SILU_MUL expects ``b`` interleaved by ``ref.interleave_gate_up`` and
@@ -300,6 +344,23 @@ def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                  out: Optional[torch.Tensor] = None, num_splits: int = 0,
                  workspace: Optional[tuple[torch.Tensor, torch.Tensor]] = None,
                  max_seq_len: int = 0, kv_quant: Optional[tuple] = None) -> torch.Tensor:
+    res = _paged_decode(q, k_cache, v_cache, block_tables, seq_lens, scale, out, num_splits,
+                        workspace, max_seq_len, kv_quant)
+    if (oracle_enabled("paged_decode") and k_cache.element_size() > 1
+            and not torch.cuda.is_current_stream_capturing()):
+        from . import ref
+        live = seq_lens > 0
+        want = ref.paged_attention_decode(q, k_cache, v_cache, block_tables,
+                                          seq_lens.clamp(min=1), scale)
+        oracle_compare("paged_decode", res[live], want[live])
+    return res
+
+
+def _paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                  block_tables: torch.Tensor, seq_lens: torch.Tensor, scale: float,
+                  out: Optional[torch.Tensor] = None, num_splits: int = 0,
+                  workspace: Optional[tuple[torch.Tensor, torch.Tensor]] = None,
+                  max_seq_len: int = 0, kv_quant: Optional[tuple] = None) -> torch.Tensor:
     """q ``[B, Hq, D]`` (row stride free), caches ``[blocks, bs, Hkv, D]``.  For fp8 / int8
     caches ``kv_quant = (k_scale, v_scale, k_zero_point, v_zero_point)`` (floats)."""
     B, Hq, D = q.shape
@@ -347,6 +408,21 @@ def varlen_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor
                    scale: float, num_q_tiles: int, out: Optional[torch.Tensor] = None,
                    causal: bool = True, window: int = 0, return_lse: bool = False,
                    num_q_tiles_128: Optional[int] = None, kv_quant: Optional[tuple] = None):
+    res = _varlen_prefill(q, k_cache, v_cache, block_tables, cu_q, seq_lens, scale, num_q_tiles,
+                          out, causal, window, return_lse, num_q_tiles_128, kv_quant)
+    if oracle_enabled("varlen_prefill") and k_cache.element_size() > 1 and causal:
+        from . import ref
+        want = ref.varlen_prefill_attention(q, k_cache, v_cache, block_tables, cu_q, seq_lens,
+                                            scale, window=window)
+        oracle_compare("varlen_prefill", res[0] if return_lse else res, want)
+    return res
+
+
+def _varlen_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                    block_tables: torch.Tensor, cu_q: torch.Tensor, seq_lens: torch.Tensor,
+                    scale: float, num_q_tiles: int, out: Optional[torch.Tensor] = None,
+                    causal: bool = True, window: int = 0, return_lse: bool = False,
+                    num_q_tiles_128: Optional[int] = None, kv_quant: Optional[tuple] = None):
     """q ``[T, Hq, D]``; ``num_q_tiles`` >= sum_b ceil(q_len_b / 64) (host-known);
     ``num_q_tiles_128`` the same for 128-row tiles (defaults to the 64-row bound)."""
     T, Hq, D = q.shape
