@@ -140,3 +140,63 @@ def test_cachegen_codec_roundtrip_reference():
     dec3 = torch.zeros_like(sym)
     O.decode_fast_new(other, out, lens, dec3)
     assert torch.equal(dec3, sym)
+
+
+def test_disaggregated_prefill_one_prefill_one_decode_instance():
+    """1P1D: the prefill engine ships the prompt's KV through the point-to-point connector,
+    the decode engine injects it, computes only the last prompt token and continues; the
+    tokens equal those of a single engine.  A missing transfer falls back to local prefill."""
+    import torch
+    from vllm_gcu_b200.engine.llm import LLM
+    from vllm_gcu_b200.engine.request import SamplingParams
+    kw = dict(device="cpu", max_num_seqs=4, max_num_batched_tokens=64, max_model_len=128,
+              num_gpu_blocks=64, dtype="float32", seed=0)
+    g = torch.Generator().manual_seed(8)
+    prompt = torch.randint(0, 32000, (37,), generator=g).tolist()
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    want = LLM("tiny-llama", **kw).generate([prompt], sp)[0].outputs[0].token_ids
+
+    pre, dec = LLM("tiny-llama", **kw), LLM("tiny-llama", **kw)
+    cp, cd = P2PKVConnector(send_type="PUT"), P2PKVConnector(send_type="PUT")
+    try:
+        dp = pre.engine.attach_kv_connector(cp)
+        dd = dec.engine.attach_kv_connector(cd, recv_timeout_s=5.0)
+        rid = pre.engine.add_request(prompt, SamplingParams(max_tokens=1, temperature=0.0,
+                                                            ignore_eos=True),
+                                     request_id="r-77",
+                                     kv_transfer_params={"do_remote_decode": True,
+                                                         "remote": cd.addr})
+        first = None
+        while pre.engine.has_unfinished():
+            for o in pre.engine.step():
+                if o.finished:
+                    first = o.outputs[0].token_ids
+        assert first == want[:1] and dp.stats["sent"] == 1
+        dec.engine.add_request(prompt, sp, request_id="d-1",
+                               kv_transfer_params={"do_remote_prefill": True, "remote": cp.addr,
+                                                   "remote_request_id": rid})
+        assert dd.stats["injected"] == 1
+        got = None
+        steps = 0
+        while dec.engine.has_unfinished():
+            steps += 1
+            for o in dec.engine.step():
+                if o.finished:
+                    got = o.outputs[0].token_ids
+        assert got == want
+        assert dec.engine.stats["prefill_tokens"] <= 1 or steps <= 7   # no full local prefill
+        # nothing was sent for this id: falls back to computing the prompt locally
+        dd.recv_timeout_s = 0.2
+        dec.engine.add_request(prompt, sp, request_id="d-2",
+                               kv_transfer_params={"do_remote_prefill": True, "remote": cp.addr,
+                                                   "remote_request_id": "missing"})
+        assert dd.stats["fallback"] == 1
+        got2 = None
+        while dec.engine.has_unfinished():
+            for o in dec.engine.step():
+                if o.finished:
+                    got2 = o.outputs[0].token_ids
+        assert got2 == want
+    finally:
+        cp.close()
+        cd.close()

@@ -99,6 +99,7 @@ class LLMEngine:
                                    if sp.method else 0)
         self._ids = itertools.count()
         self._want_sync = False
+        self.disagg = None               # set by attach_kv_connector()
         self.dp_size = st.dp.world_size
         self.dp_global_busy = self.dp_size > 1     # learnt from the exchange of every step
         if self.dp_size > 1:
@@ -124,7 +125,8 @@ class LLMEngine:
                     sampling_params: Optional[SamplingParams] = None,
                     request_id: Optional[str] = None, priority: int = 0,
                     eos_token_id: Optional[int] = None, lora_id: int = -1,
-                    multi_modal_data: Optional[dict] = None) -> str:
+                    multi_modal_data: Optional[dict] = None,
+                    kv_transfer_params: Optional[dict] = None) -> str:
         """``multi_modal_data``: processor outputs of a multimodal model
         (``{"pixel_values": [n_patches, C*Tp*P*P], "image_grid_thw": [n_images, 3]}``); the
         prompt must already contain one placeholder token per merged patch."""
@@ -138,6 +140,10 @@ class LLMEngine:
             for k, v in prep(req.prompt_token_ids, multi_modal_data["pixel_values"],
                              multi_modal_data["image_grid_thw"]).items():
                 setattr(req, k, v)
+        if kv_transfer_params:
+            req.kv_transfer_params = dict(kv_transfer_params)
+            if self.disagg is not None:
+                self.disagg.on_add(req)
         sp_ = req.sampling_params
         if sp_.has_penalties or sp_.logprobs is not None or sp_.prompt_logprobs is not None:
             # these need the ids of every earlier token on the host before the next step
@@ -147,6 +153,14 @@ class LLMEngine:
 
     def abort_request(self, request_id: str) -> None:
         self.scheduler.abort_request(request_id)
+
+    def attach_kv_connector(self, connector, recv_timeout_s: float = 30.0):
+        """Disaggregated prefill: requests with ``kv_transfer_params`` send their KV to /
+        take their KV from the peer instance through ``connector`` (engine/kv_disagg.py)."""
+        from .kv_disagg import DisaggCoordinator
+        self.disagg = DisaggCoordinator(self, connector, recv_timeout_s)
+        self.scheduler.on_free = self.disagg.before_free
+        return self.disagg
 
     def add_lora(self, lora_request, tensors=None, config=None) -> int:
         """Loads a LoRA adapter; requests select it with ``lora_id=lora_request.lora_int_id``."""
@@ -232,6 +246,23 @@ class LLMEngine:
         return outs
 
     def step(self) -> list[RequestOutput]:
+        """One scheduling round.  With ``num_scheduler_steps = n > 1`` (the reference's
+        multi-step scheduler, vllm_gcu/worker/multi_step_worker.py:33-336) the round runs up to
+        n engine steps back to back and hands their outputs over together; the steps
+        themselves use the device-side next-token feed, so the GPU does not wait for the host
+        in between."""
+        n = max(1, int(self.cfg.scheduler.num_scheduler_steps))
+        if n == 1:
+            return self._step_once()
+        merged: dict[str, RequestOutput] = {}
+        for _ in range(n):
+            for o in self._step_once():
+                merged[o.request_id] = o
+            if not self.has_unfinished():
+                break
+        return list(merged.values())
+
+    def _step_once(self) -> list[RequestOutput]:
         """Runs (or, with async scheduling, launches and retires) one engine step."""
         if self._want_sync and self.cfg.scheduler.async_scheduling and not self._pending:
             self.cfg.scheduler.async_scheduling = False
@@ -284,6 +315,7 @@ class LLM:
                  max_num_batched_tokens: int = 8192, max_model_len: Optional[int] = None,
                  block_size: int = 16, gpu_memory_utilization: float = 0.9,
                  enable_prefix_caching: bool = True, async_scheduling: bool = False,
+                 num_scheduler_steps: int = 1,
                  enforce_eager: bool = False, device: str = "auto", seed: int = 0,
                  num_gpu_blocks: Optional[int] = None, scheduling_policy: str = "fcfs",
                  load_format: Optional[str] = None, comm_backend: str = "fused",
@@ -317,7 +349,8 @@ class LLM:
             scheduler=SchedulerConfig(max_num_seqs=max_num_seqs,
                                       max_num_batched_tokens=max_num_batched_tokens,
                                       max_model_len=max_model_len or mc.max_position_embeddings,
-                                      policy=scheduling_policy, async_scheduling=async_scheduling),
+                                      policy=scheduling_policy, async_scheduling=async_scheduling,
+                                      num_scheduler_steps=num_scheduler_steps),
             parallel=ParallelConfig(tensor_parallel_size=tensor_parallel_size,
                                     pipeline_parallel_size=pipeline_parallel_size,
                                     comm_backend=comm_backend,

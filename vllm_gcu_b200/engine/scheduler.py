@@ -61,6 +61,7 @@ class Scheduler:
         self.requests: dict[str, Request] = {}
         self.finished_since_last: set[str] = set()
         self.async_mode = sched_cfg.async_scheduling
+        self.on_free = None              # optional callback(req), blocks still allocated
         self.priority = sched_cfg.policy == "priority"
         self.separate_prefill_decode = separate_prefill_decode
         self.num_lookahead_tokens = num_lookahead_tokens
@@ -107,6 +108,8 @@ class Scheduler:
                 self.waiting.remove(req)
             except ValueError:
                 pass
+        if self.on_free is not None:
+            self.on_free(req)           # e.g. ship the KV to a decode instance
         self.kv.free(req)
         self.finished_since_last.add(req.request_id)
         self.requests.pop(req.request_id, None)
