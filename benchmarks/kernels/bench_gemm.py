@@ -60,6 +60,11 @@ def main():
         t_ours = timeit(lambda: C.gemm_bf16(x, w, out=out), a.iters, flush)
         t_ref = timeit(lambda: torch.matmul(x, w.t(), out=out), a.iters, flush)
         fl = 2.0 * M * N * K
+        if M >= C.WIDE2_MIN_M and N % 256 == 0:     # large M: also time the 128 x 256 tile kernel
+            C.USE_WIDE2_GEMM = False
+            t_tile = timeit(lambda: C.gemm_bf16(x, w, out=out), a.iters, flush)
+            C.USE_WIDE2_GEMM = True
+            label = f"{label} [128x256 tiles {t_tile*1e3:.1f} us]"
         if M <= C.SKINNY_MAX_M:          # decode-sized: also time the persistent-tile kernel
             C.USE_SKINNY_GEMM = False
             t_tile = timeit(lambda: C.gemm_bf16(x, w, out=out), a.iters, flush)

@@ -70,6 +70,23 @@ def test_gemm_skinny_decode_shapes(C, M, N, K, monkeypatch):
                3e-2, 3e-2)
 
 
+@pytest.mark.parametrize("M,N,K", [(1100, 512, 320), (2048, 1024, 4096), (1024, 256, 64)])
+def test_gemm_wide2_large_m(C, M, N, K):
+    """Persistent 256 x 256 tile kernel (large M, N a multiple of 256): plain, bias and
+    SiLU-mul epilogues, ragged last row tile."""
+    assert C.USE_WIDE2_GEMM and M >= C.WIDE2_MIN_M
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = (torch.randn(N, K, device="cuda") / math.sqrt(K)).to(torch.bfloat16)
+    want = ref.gemm(a, b, out_dtype=torch.float32)
+    _close(C.gemm_bf16(a, b), want, 2e-2, 2e-2)
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    _close(C.gemm_bf16(a, b, bias=bias), want + bias.float(), 2e-2, 3e-2)
+    got = C.gemm_bf16(a, b, epilogue=C.EPI_SILU_MUL)
+    w4 = want.view(M, N // 256, 2, 128)
+    _close(got, (torch.nn.functional.silu(w4[:, :, 0]) * w4[:, :, 1]).reshape(M, N // 2),
+           3e-2, 3e-2)
+
+
 def test_gemm_bf16_epilogues(C):
     torch.manual_seed(1)
     M, N, K = 200, 1024, 512

@@ -354,6 +354,212 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const Args& a, int un
   return static_cast<int>(cudaGetLastError());
 }
 
+// ---------------------------------------------------------------------------
+// Persistent 256 x 256 tiles for large M: same shared-memory stage as above (two 128-row
+// activation tiles + one 256-row weight tile per 64 of K), so a CTA moves 64 KB from L2 per
+// 2 x 512 tensor-core cycles - two thirds of what the 128 x 256 tiles of gemm_bf16.cu move -
+// at the price of a single accumulator set (all 512 TMEM columns): the MMA of the next tile
+// starts when the epilogue warps have read the accumulators of this one.
+// ---------------------------------------------------------------------------
+struct WideArgs {
+  __nv_bfloat16* C;
+  long long ldc;
+  const __nv_bfloat16* bias;
+  int M, N, K;
+  int tiles_m, tiles_n, num_kb;
+  unsigned int* status;
+};
+
+template <int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+    gemm_wide2_kernel(const __grid_constant__ CUtensorMap tmA,
+                      const __grid_constant__ CUtensorMap tmB, const WideArgs p) {
+  constexpr int BN = 256, MT = 2, STAGES = 3;
+  using L = Smem<BN, MT, STAGES>;
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kIdesc = make_idesc(BM, BN, 1, 1);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 1);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(tfull_bar, 1);
+    mbar_init(tempty_bar, 4);
+    *abort_flag = 0u;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        const int m0 = (tile % p.tiles_m) * (MT * BM), n0 = (tile / p.tiles_m) * BN;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, p.status, kKernelId, 0x900u + stage,
+                         abort_flag)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * L::kStageBytes;
+          uint8_t* sb = sa + MT * L::kABytes;
+          mbar_expect_tx(&full_bar[stage], L::kStageBytes);
+          tma_load_2d(sb, &tmB, &full_bar[stage], kb * BK, n0);
+          tma_load_2d(sa, &tmA, &full_bar[stage], kb * BK, m0);
+          tma_load_2d(sa + L::kABytes, &tmA, &full_bar[stage], kb * BK, m0 + BM);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0, tphase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        if (!mbar_wait(tempty_bar, tphase ^ 1u, p.status, kKernelId, 0x910u, abort_flag)) break;
+        tc_fence_after();
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, p.status, kKernelId, 0x920u + stage,
+                         abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * L::kStageBytes);
+          const uint32_t b_addr = a_addr + MT * L::kABytes;
+          const uint64_t bdesc = make_desc_k_sw128(b_addr);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            const uint64_t adesc = make_desc_k_sw128(a_addr + mt * L::kABytes);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              umma_f16(tmem_base + static_cast<uint32_t>(mt * BN),
+                       adesc + static_cast<uint64_t>(k * 2), bdesc + static_cast<uint64_t>(k * 2),
+                       kIdesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit(tfull_bar);
+        tphase ^= 1u;
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    uint32_t tphase = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      const int m0 = (tile % p.tiles_m) * (MT * BM), n0 = (tile / p.tiles_m) * BN;
+      if (!mbar_wait(tfull_bar, tphase, p.status, kKernelId, 0x930u, abort_flag)) break;
+      tc_fence_after();
+#pragma unroll 1
+      for (int mt = 0; mt < MT; ++mt) {
+        const int row = m0 + mt * BM + q * 32 + lane;
+        const bool row_ok = row < p.M;
+        const uint32_t taddr =
+            tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(mt * BN);
+        if constexpr (EPI == kSiluMul) {
+          __nv_bfloat16* crow = p.C + static_cast<long long>(row) * p.ldc + (n0 >> 1);
+          const int out_n = p.N >> 1;
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t g[32], u[32];
+            tmem_ld_32x32(taddr + c * 32, g);
+            tmem_ld_32x32(taddr + 128 + c * 32, u);
+            tmem_ld_wait();
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              v[i] = silu_f(__uint_as_float(g[i])) * __uint_as_float(u[i]);
+            if (row_ok && (n0 >> 1) + c * 32 < out_n) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) store8_bf16(crow + c * 32 + i * 8, v + i * 8);
+            }
+          }
+        } else {
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(taddr + c * 32, r);
+            tmem_ld_wait();
+            const int col = n0 + c * 32;
+            if (!row_ok || col >= p.N) continue;
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+            if constexpr (EPI == kBias) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] += __bfloat162float(p.bias[col + i]);
+            }
+            __nv_bfloat16* crow = p.C + static_cast<long long>(row) * p.ldc + col;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) store8_bf16(crow + i * 8, v + i * 8);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar);
+      tphase ^= 1u;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+template <int EPI>
+int launch_wide2(const CUtensorMap& tmA, const CUtensorMap& tmB, const WideArgs& a,
+                 cudaStream_t stream) {
+  using L = Smem<256, 2, 3>;
+  auto kern = gemm_wide2_kernel<EPI>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e =
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured[dev] = true;
+  }
+  const int tiles = a.tiles_m * a.tiles_n;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kern<<<grid, kThreads, L::kTotal, stream>>>(tmA, tmB, a);
+  return static_cast<int>(cudaGetLastError());
+}
+
 struct Plan {
   int bn, splits;
 };
@@ -489,4 +695,43 @@ B200_API int b200_gemm_skinny_plan(int M, int N, int K, int epi, int* bn, int* s
   *bn = pl.bn;
   *splits = pl.splits;
   return 0;
+}
+
+// C[M,N] = A[M,K] * B[N,K]^T with persistent 256 x 256 tiles (large M).  N must be a multiple
+// of 256 (epi 2: gate / up interleaved in blocks of 128, C is [M, N/2]); other constraints as
+// b200_gemm_bf16.  Returns -20 when the shape does not qualify.
+B200_API int b200_gemm_wide2(const void* A, long long lda, const void* B, long long ldb, void* C,
+                             long long ldc, int M, int N, int K, const void* bias, int epi,
+                             void* stream) {
+  using namespace b200;
+  using namespace b200::skinny;
+  if (M <= 0 || N <= 0) return 0;
+  if ((N % 256) != 0 || M < 512 || epi < 0 || epi > 2) return -20;
+  if (K <= 0 || (K % 8) != 0 || (lda % 8) != 0 || (ldb % 8) != 0 || (ldc % 8) != 0) return -2;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) |
+       reinterpret_cast<uintptr_t>(C)) & 15)
+    return -3;
+  if (epi == kBias && bias == nullptr) return -5;
+  CUtensorMap tmA, tmB;
+  int r = encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, static_cast<uint64_t>(M),
+                         static_cast<uint64_t>(K), static_cast<uint64_t>(lda) * 2, BM, BK,
+                         CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r != 0) return r < 0 ? -6 : r;
+  r = encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, static_cast<uint64_t>(N),
+                     static_cast<uint64_t>(K), static_cast<uint64_t>(ldb) * 2, 256, BK,
+                     CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r != 0) return r < 0 ? -6 : r;
+  WideArgs a;
+  a.C = static_cast<__nv_bfloat16*>(C);
+  a.ldc = ldc;
+  a.bias = static_cast<const __nv_bfloat16*>(bias);
+  a.M = M; a.N = N; a.K = K;
+  a.tiles_m = (M + 255) / 256;
+  a.tiles_n = N / 256;
+  a.num_kb = (K + BK - 1) / BK;
+  a.status = status_ptr();
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (epi == kSiluMul) return launch_wide2<kSiluMul>(tmA, tmB, a, s);
+  if (epi == kBias) return launch_wide2<kBias>(tmA, tmB, a, s);
+  return launch_wide2<kNone>(tmA, tmB, a, s);
 }
