@@ -26,3 +26,14 @@ def register_custom_models() -> None:
         vllm_quant.register_all()
     except Exception:   # vLLM absent or too old: the built-in engine is unaffected
         pass
+
+
+def __getattr__(name: str):
+    # lazy: importing the package must stay cheap for the vLLM plugin loader
+    if name in ("LLM", "LLMEngine"):
+        from .engine import llm as _llm
+        return getattr(_llm, name)
+    if name in ("SamplingParams", "RequestOutput", "CompletionOutput"):
+        from .engine import request as _req
+        return getattr(_req, name)
+    raise AttributeError(name)
