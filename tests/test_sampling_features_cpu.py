@@ -69,3 +69,16 @@ def test_n_best_of_and_beam_search():
     assert len(beam.outputs) == 2 and len(beam.outputs[0].token_ids) == 4
     # the best beam is at least as likely as the greedy continuation
     assert beam.outputs[0].cumulative_logprob >= greedy.outputs[0].cumulative_logprob - 1e-5
+
+
+def test_allowed_tokens_and_guided_choice():
+    llm = _llm()
+    p = _prompt(10, 4)
+    out = llm.generate([p], SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True,
+                                           allowed_token_ids=(11, 22, 33)))[0]
+    assert set(out.outputs[0].token_ids) <= {11, 22, 33}
+    choices = ((5, 6, 7), (5, 9), (100, 101, 102, 103))
+    out = llm.generate([p], SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True,
+                                           guided_choice=choices))[0]
+    toks = tuple(out.outputs[0].token_ids)
+    assert toks in choices and out.outputs[0].finish_reason == "stop"

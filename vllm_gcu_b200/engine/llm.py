@@ -145,7 +145,8 @@ class LLMEngine:
             if self.disagg is not None:
                 self.disagg.on_add(req)
         sp_ = req.sampling_params
-        if sp_.has_penalties or sp_.logprobs is not None or sp_.prompt_logprobs is not None:
+        if (sp_.has_penalties or sp_.logprobs is not None or sp_.prompt_logprobs is not None
+                or sp_.constrained):
             # these need the ids of every earlier token on the host before the next step
             self._want_sync = True
         self.scheduler.add_request(req)

@@ -325,7 +325,8 @@ class ModelRunner:
         # penalties / log-probabilities need the logits on a side path: no graph for that step
         feat = any(s.req.sampling_params.has_penalties
                    or s.req.sampling_params.logprobs is not None
-                   or s.req.sampling_params.prompt_logprobs is not None for s in sched)
+                   or s.req.sampling_params.prompt_logprobs is not None
+                   or s.req.sampling_params.constrained for s in sched)
         use_graph = (self.is_cuda and npf == 0 and self.graphs and nd <= self.graph_sizes[-1]
                      and self.drafter is None and not batch_has_lora and not feat
                      and self.cfg.parallel.data_parallel_size == 1)
@@ -640,6 +641,15 @@ class ModelRunner:
                               torch.tensor(rep_, device=dev))
         if any(k >= 0 for k in lp_k):
             f["logprob_k"] = lp_k
+        allow_r, allow_t = [], []
+        for r, j in enumerate(samplers):
+            req = order[j].req
+            nxt = req.sampling_params.allowed_next(req.output_token_ids) \
+                if req.sampling_params.constrained else None
+            if nxt is not None:
+                allow_r.append((r, nxt))
+        if allow_r:
+            f["allowed"] = allow_r
         # prompt log-probabilities: hidden row of prompt position p predicts token p + 1
         pl = []
         for j, s_ in enumerate(order):
@@ -667,6 +677,15 @@ class ModelRunner:
                 apply_penalties(sub, pm, oc, pres, freq, rep_)
                 logits = logits.clone() if not logits.is_contiguous() else logits
                 logits.index_copy_(0, rows, sub.to(logits.dtype))
+            if "allowed" in f:
+                logits = logits.clone()
+                for r, ids in f["allowed"]:
+                    if not ids:
+                        continue
+                    keep = torch.tensor(ids, device=logits.device).clamp_(0, logits.shape[1] - 1)
+                    row = torch.full_like(logits[r], float("-inf"))
+                    row[keep] = logits[r, keep]
+                    logits[r] = row
             return logits
         if "logprob_k" in f:
             ks = f["logprob_k"]

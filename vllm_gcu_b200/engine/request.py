@@ -29,11 +29,30 @@ class SamplingParams:
     n: int = 1
     best_of: Optional[int] = None
     use_beam_search: bool = False
+    # constrained decoding: only these token ids may be sampled / the output must be one of
+    # these token sequences (the token-level form of guided "choice" decoding)
+    allowed_token_ids: Optional[tuple[int, ...]] = None
+    guided_choice: Optional[tuple[tuple[int, ...], ...]] = None
     extra_args: dict[str, Any] = field(default_factory=dict)
 
     @property
     def greedy(self) -> bool:
         return self.temperature <= 0.0
+
+    @property
+    def constrained(self) -> bool:
+        return self.allowed_token_ids is not None or self.guided_choice is not None
+
+    def allowed_next(self, output_token_ids: list) -> Optional[list]:
+        """Token ids that may follow ``output_token_ids`` (None = unconstrained)."""
+        if self.guided_choice is not None:
+            n = len(output_token_ids)
+            nxt = sorted({c[n] for c in self.guided_choice
+                          if len(c) > n and list(c[:n]) == list(output_token_ids)})
+            return nxt
+        if self.allowed_token_ids is not None:
+            return list(self.allowed_token_ids)
+        return None
 
     @property
     def has_penalties(self) -> bool:
@@ -150,6 +169,11 @@ def check_stop(req: Request, max_model_len: int) -> bool:
         if last in sp.stop_token_ids:
             req.status = RequestStatus.FINISHED_STOPPED
             return True
+    if sp.guided_choice is not None and any(
+            list(c) == req.output_token_ids for c in sp.guided_choice) and not any(
+            len(c) > n_out and list(c[:n_out]) == req.output_token_ids for c in sp.guided_choice):
+        req.status = RequestStatus.FINISHED_STOPPED      # a complete choice, no longer one
+        return True
     if n_out >= sp.max_tokens or req.num_tokens >= max_model_len:
         req.status = RequestStatus.FINISHED_LENGTH
         return True
