@@ -90,6 +90,40 @@ def _check_ep(rank, world):
     assert torch.allclose(got, want, atol=1e-5, rtol=1e-4), (got - want).abs().max()
 
 
+def _check_sp_model(rank, world):
+    """Tensor-parallel Llama and Qwen3-MoE with the residual stream sharded by rows
+    (sequence parallelism): same logits as the plain tensor-parallel forward."""
+    import dataclasses
+
+    from vllm_gcu_b200.config import preset
+    from vllm_gcu_b200.engine.llm import LLM
+    from vllm_gcu_b200.engine.request import SamplingParams
+    kw = dict(device="cpu", tensor_parallel_size=world, max_num_seqs=4, max_num_batched_tokens=32,
+              max_model_len=128, num_gpu_blocks=64, comm_backend="nccl", seed=0)
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (19, 7, 40)]
+    sp_ = SamplingParams(max_tokens=3, temperature=0.0, ignore_eos=True)
+    for name in ("tiny-llama", "tiny-qwen3-moe"):
+        logits = {}
+        for flag in (False, True):
+            mc = dataclasses.replace(preset(name), dtype=torch.float32)
+            mc.extra = dict(mc.extra, sequence_parallel=flag)
+            llm = LLM(mc, **kw)
+            assert llm.engine.model.sequence_parallel == flag
+            llm.engine.runner.keep_logits = True
+            out = llm.generate(prompts, sp_)
+            logits[flag] = (llm.engine.runner.last_logits, [o.outputs[0].token_ids for o in out])
+        a, b = logits[False], logits[True]
+        assert a[1] == b[1], (name, a[1], b[1])
+        assert torch.allclose(a[0], b[0], atol=1e-4, rtol=1e-4), (name, (a[0] - b[0]).abs().max())
+
+
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("world", [2])
+def test_sequence_parallel_model_matches_tensor_parallel(world):
+    _spawn("_check_sp_model", world)
+
+
 @pytest.mark.timeout(300)
 @pytest.mark.parametrize("world", [2, 3])
 def test_sequence_parallel_and_collectives(world):

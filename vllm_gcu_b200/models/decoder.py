@@ -48,11 +48,26 @@ class DenseMLP(nn.Module):
         if not isinstance(self.gate_up_proj.quant_method, UnquantizedLinearMethod):
             self.gate_up_proj.fuse_silu = False   # quantised GEMMs have no SiLU epilogue yet
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        h = self.gate_up_proj(x)
+    def forward(self, x: torch.Tensor, sp_sizes: Optional[list] = None) -> torch.Tensor:
+        """``sp_sizes`` (sequence parallelism): ``x`` holds this rank's rows; the rows are
+        gathered for the column-parallel projection and the row-parallel output is
+        reduce-scattered back to rows."""
+        if sp_sizes is not None:
+            from ..parallel import sp
+            h = sp.sp_gather_linear(self.gate_up_proj, x, sp_sizes)
+        else:
+            h = self.gate_up_proj(x)
         if not self.gate_up_proj.fuse_silu:
             from ..layers.activation import act_and_mul
             h = act_and_mul(h, self.act)
+        if sp_sizes is not None:
+            from ..parallel import sp
+            keep, self.down_proj.reduce_results = self.down_proj.reduce_results, False
+            try:
+                y = self.down_proj(h)
+            finally:
+                self.down_proj.reduce_results = keep
+            return sp.reduce_scatter_rows(y, sp_sizes)
         return self.down_proj(h)
 
 
@@ -78,10 +93,21 @@ class GQAAttention(nn.Module):
         self.attn = PagedAttention(self.qkv_proj.num_heads, self.qkv_proj.num_kv_heads, D,
                                    D ** -0.5, rotary, qn, kn, cfg.sliding_window)
 
-    def forward(self, x: torch.Tensor, kv_cache: torch.Tensor, md: AttentionMetadata
-                ) -> torch.Tensor:
-        qkv = self.qkv_proj(x)
-        return self.o_proj(self.attn(qkv, kv_cache, md))
+    def forward(self, x: torch.Tensor, kv_cache: torch.Tensor, md: AttentionMetadata,
+                sp_sizes: Optional[list] = None) -> torch.Tensor:
+        if sp_sizes is None:
+            qkv = self.qkv_proj(x)
+            return self.o_proj(self.attn(qkv, kv_cache, md))
+        # sequence parallelism: rows in, rows out (vllm_gcu/models/deepseek_v3/
+        # deepseek_v3.py:611-612,747-748: sp_to_tp before the projections, tp_to_sp after o_proj)
+        from ..parallel import sp
+        qkv = sp.sp_gather_linear(self.qkv_proj, x, sp_sizes)
+        keep, self.o_proj.reduce_results = self.o_proj.reduce_results, False
+        try:
+            y = self.o_proj(self.attn(qkv, kv_cache, md))
+        finally:
+            self.o_proj.reduce_results = keep
+        return sp.reduce_scatter_rows(y, sp_sizes)
 
 
 class DecoderLayer(nn.Module):
@@ -107,17 +133,31 @@ class DecoderLayer(nn.Module):
             self.post_mlp_layernorm = RMSNorm(H, cfg.rms_norm_eps, cfg.dtype, device)
 
     def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor], kv_cache: torch.Tensor,
-                md: AttentionMetadata):
+                md: AttentionMetadata, sp_sizes: Optional[list] = None):
         if residual is None:
             residual = x
             h = self.input_layernorm(x)
         else:
             h, residual = self.input_layernorm(x, residual)
-        h = self.self_attn(h, kv_cache, md)
+        if sp_sizes is not None and isinstance(self.self_attn, GQAAttention):
+            h = self.self_attn(h, kv_cache, md, sp_sizes)
+        elif sp_sizes is not None:
+            from ..parallel import sp
+            full = self.self_attn(sp.sp_to_tp(h, sum(sp_sizes)), kv_cache, md)
+            h = sp.slice_tensor_sp(full)
+        else:
+            h = self.self_attn(h, kv_cache, md)
         if self.sandwich:
             h = self.post_self_attn_layernorm(h)
         h, residual = self.post_attention_layernorm(h, residual)
-        h = self.mlp(h)
+        if sp_sizes is not None and isinstance(self.mlp, DenseMLP):
+            h = self.mlp(h, sp_sizes)
+        elif sp_sizes is not None:
+            # MoE blocks reduce over their own group: run them on all rows, keep ours
+            from ..parallel import sp
+            h = sp.slice_tensor_sp(self.mlp(sp.sp_to_tp(h, sum(sp_sizes))))
+        else:
+            h = self.mlp(h)
         if self.sandwich:
             h = self.post_mlp_layernorm(h)
         return h, residual
@@ -142,6 +182,9 @@ class DecoderLM(nn.Module):
         per = -(-L // pp)
         self.start_layer, self.end_layer = min(L, pp_rank * per), min(L, (pp_rank + 1) * per)
         self.is_first_stage, self.is_last_stage = pp_rank == 0, pp_rank == pp - 1
+        from .. import envs
+        self.sequence_parallel = bool(cfg.extra.get("sequence_parallel")
+                                      or envs.ENABLE_SEQUENCE_PARALLEL)
         if self.is_first_stage or (cfg.tie_word_embeddings and self.is_last_stage):
             self.embed_tokens = VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, cfg.dtype,
                                                        device)
@@ -181,13 +224,25 @@ class DecoderLM(nn.Module):
             residual = None
         else:
             x, residual = intermediate
+        sp_sizes = None
+        if self.sequence_parallel and tp_size() > 1 and x.shape[0] > 0 \
+                and get_state().pp.world_size == 1:
+            # the residual stream is sharded by rows between the attention / MLP blocks
+            from ..parallel import sp
+            total = x.shape[0]
+            sp_sizes = sp.scatter(total, tp_size())
+            x = sp.slice_tensor_sp(x)
         for j, i in enumerate(range(self.start_layer, self.end_layer)):
-            x, residual = self.layers[str(i)](x, residual, kv_caches[j], md)
+            x, residual = self.layers[str(i)](x, residual, kv_caches[j], md, sp_sizes)
         if not self.is_last_stage:
             return x, residual
         if residual is None:
-            return self.norm(x)
-        x, _ = self.norm(x, residual)
+            x = self.norm(x)
+        else:
+            x, _ = self.norm(x, residual)
+        if sp_sizes is not None:
+            from ..parallel import sp
+            x = sp.sp_to_tp(x, sum(sp_sizes))
         return x
 
     def _head(self) -> ParallelLMHead:

@@ -45,3 +45,26 @@ def slice_tensor_sp(x: torch.Tensor) -> torch.Tensor:
     r = tp_rank()
     start = sum(sizes[:r])
     return x[start:start + sizes[r]]
+
+
+def sp_gather_linear(layer, x_local: torch.Tensor, sizes: list[int]) -> torch.Tensor:
+    """``layer(all_gather(x_local))`` for a column-parallel layer whose input is sharded by
+    rows.  On the GPU with bf16 unquantised weights the gather runs inside the GEMM
+    (``FusedGather.all_gather_gemm``: gather warps pull the peers' rows while the tensor
+    cores work on the rows that have arrived); otherwise all-gather-v then the layer."""
+    comm = get_comm("tp")
+    fg = getattr(comm, "fused_gather", None)
+    w = getattr(layer, "weight", None)
+    if (fg is not None and x_local.is_cuda and x_local.dtype == torch.bfloat16 and w is not None
+            and w.dtype == torch.bfloat16 and getattr(layer, "bias", None) is None
+            and not getattr(layer, "fuse_silu", False) and fg.sp_k == x_local.shape[-1]
+            and type(layer.quant_method).__name__ == "UnquantizedLinearMethod"):
+        y = fg.all_gather_gemm(x_local.contiguous(), w, list(sizes))
+        if y is not None:
+            return y
+    return layer(sp_to_tp(x_local, sum(sizes)))
+
+
+def reduce_scatter_rows(partial: torch.Tensor, sizes: list[int]) -> torch.Tensor:
+    """Partial sums ``[T, H]`` -> this rank's reduced rows."""
+    return get_comm("tp").reduce_scatter_v(partial, list(sizes))

@@ -302,5 +302,8 @@ def attach(cfg) -> Optional[FusedTP]:
     tp = st.tp.world_size
     rows = cfg.scheduler.max_num_seqs * (1 + getattr(cfg.speculative, "num_speculative_tokens", 0))
     padded_vocab = -(-mc.vocab_size // (tp * 64)) * (tp * 64)
-    comm.fused_gather = FusedGather(fused.device, out_rows=max(rows, 128), out_cols=padded_vocab)
+    sp_on = bool(mc.extra.get("sequence_parallel"))
+    comm.fused_gather = FusedGather(fused.device, out_rows=max(rows, 128), out_cols=padded_vocab,
+                                    sp_tokens=max_tokens if sp_on else 0,
+                                    sp_k=mc.hidden_size if sp_on else 0)
     return fused
