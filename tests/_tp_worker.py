@@ -147,11 +147,12 @@ def main():
     prompts = [torch.randint(0, 4096, (n,), generator=g).tolist() for n in (33, 64, 5, 120)]
     sp = SamplingParams(max_tokens=1, temperature=0.0, ignore_eos=True)
     results = {}
-    for comm in ("nccl", "fused"):
+    for comm in ("nccl", "fused", "fused+sp"):
         get_comm("tp").fused = None
         get_comm("tp").fused_gather = None
-        llm = LLM("llama-3-8b", tensor_parallel_size=world, comm_backend=comm, enforce_eager=True,
-                  load_format="none", **kw)
+        extra = {"sequence_parallel": True} if comm.endswith("+sp") else {}
+        llm = LLM("llama-3-8b", tensor_parallel_size=world, comm_backend=comm.split("+")[0],
+                  enforce_eager=True, load_format="none", extra=extra, **kw)
         llm.engine.model.load_weights(sd.items())
         llm.engine.runner.keep_logits = True
         llm.generate(prompts, sp)
@@ -166,6 +167,9 @@ def main():
     a, b = results["nccl"], results["fused"]
     err = (a - b).abs().max().item()
     assert err < 0.05 * a.std().item() + 0.02, f"fused vs nccl logits differ: {err}"
+    # sequence parallelism: gather fused into the qkv / gate-up GEMMs, reduce-scatter after
+    err_sp = (a - results["fused+sp"]).abs().max().item()
+    assert err_sp < 0.05 * a.std().item() + 0.02, f"sequence-parallel logits differ: {err_sp}"
     if rank == 0:
         print(f"tp{world} engine ok (nccl vs fused max logit diff {err:.4f})", flush=True)
     dist.barrier()

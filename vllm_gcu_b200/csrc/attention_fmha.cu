@@ -3,9 +3,9 @@
 // One CTA = 128 query rows of one head.  Per tile of 128 keys:
 //   S = Q K^T      tcgen05.mma, Q and K tiles K-major in shared memory (TMA, 128-byte swizzle),
 //                  fp32 scores in tensor memory (two buffers);
-//   softmax        four warps, one query row per thread: two passes over the scores in TMEM
-//                  (row maximum, then exp2 and row sum), probabilities written to shared memory
-//                  as bf16 in the K-major swizzled layout the next MMA reads;
+//   softmax        eight warps, two threads per query row (64 keys each): two passes over the
+//                  scores in TMEM (row maximum, then exp2 and row sum), probabilities written
+//                  to shared memory as bf16 in the K-major swizzled layout the next MMA reads;
 //   O += P V       tcgen05.mma with V as an MN-major operand (keys x head_dim rows exactly as
 //                  they lie in the paged cache), output accumulated in tensor memory.
 // The running maximum is only raised when the new maximum exceeds it by more than 8 (log2
@@ -13,7 +13,7 @@
 // the accumulator in TMEM needs no rescale.  When it is raised, the softmax warps rescale
 // the accumulator in place (tcgen05.ld / tcgen05.st) between two P V products.
 // Warp roles: warp 0 TMA producer (K and V pages through the block table, 16 tokens per
-// copy), warp 1 MMA issuer and TMEM owner, warps 2..5 softmax and epilogue.  S of tile j + 1
+// copy), warp 1 MMA issuer and TMEM owner, warps 2..9 softmax and epilogue.  S of tile j + 1
 // is issued before P V of tile j, so the tensor cores compute the next scores while the
 // softmax warps work on the current ones.
 //
@@ -33,7 +33,7 @@ constexpr int BQ = 128;      // query rows per CTA
 constexpr int BKV = 128;     // keys per tile
 constexpr int HD = 128;      // head dimension
 constexpr int kPage = 16;    // tokens per TMA copy (divides the cache block size)
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;   // TMA warp, MMA warp, 2 x 4 softmax warps
 constexpr int kSub = BQ * 64 * 2;          // one [128 x 64] bf16 sub-tile: 16 KB
 constexpr int kTile = 2 * kSub;            // a [128 x 128] bf16 tile: 32 KB
 constexpr int kStages = 2;
@@ -44,7 +44,8 @@ constexpr int kOffK = kOffQ + kTile;
 constexpr int kOffV = kOffK + kStages * kTile;
 constexpr int kOffP = kOffV + kStages * kTile;
 constexpr int kOffBar = kOffP + kTile;
-constexpr int kSmemBytes = kOffBar + 256 + 1024;
+constexpr int kOffX = kOffBar + 256;       // row maxima / sums exchanged between the warp groups
+constexpr int kSmemBytes = kOffX + 2 * BQ * 4 + 1024;
 
 // tensor memory columns
 constexpr uint32_t kColS = 0;      // two score buffers of 128 columns
@@ -102,9 +103,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 4);
+      mbar_init(&s_empty[i], 8);
     }
-    mbar_init(p_full, 4);
+    mbar_init(p_full, 8);
     mbar_init(o_done, 1);
     *abort_flag = 0u;
     mbar_fence_init();
@@ -256,7 +257,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
   } else {
-    // ---------------- softmax + epilogue (warps 2..5) ----------------
+    // ---------------- softmax + epilogue (warps 2..9) ----------------
+    // Two groups of four warps: group g handles keys / output columns [64 g, 64 g + 64) of
+    // every row, so each scheduler holds two softmax warps and one covers the other's TMEM
+    // and arithmetic latency.  The two threads of a row exchange their partial row maximum
+    // through shared memory once per tile; row sums stay per thread until the end.
+    const int g = (warp - 2) >> 2;
     const int qd = warp & 3;                    // TMEM lane quarter
     const int r = qd * 32 + lane;               // query row in the tile
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(qd * 32) << 16);
@@ -265,46 +271,53 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;       // first visible key
     const float sl2 = a.scale * 1.4426950408889634f;
     float m_used = -INFINITY, l = 0.0f;
-    uint8_t* sp = smem + kOffP;
+    uint8_t* sp = smem + kOffP + g * kSub;      // this group's 64-key sub-tile of P
+    float* xch = reinterpret_cast<float*>(smem + kOffX);   // [2][128]
     bool ok = true;
     for (int j = 0; j < nt; ++j) {
       const int b = j & 1;
-      if (!mbar_wait(&s_full[b], (j >> 1) & 1, a.status, kKernelId, 0x300u + b, abort_flag)) {
+      if (ok && !mbar_wait(&s_full[b], (j >> 1) & 1, a.status, kKernelId, 0x300u + b, abort_flag))
         ok = false;
-        break;
-      }
       tc_fence_after();
-      const uint32_t s_addr = lane_addr + kColS + b * BKV;
-      const int key0 = (t0 + j) * BKV;
+      const uint32_t s_addr = lane_addr + kColS + b * BKV + g * 64;
+      const int key0 = (t0 + j) * BKV + g * 64;
       // Only tiles that touch the causal diagonal, the window start or the end of the
       // sequence need per-element masks; the test is uniform over the CTA.
-      const bool need_mask = (key0 + BKV - 1 > (a.causal ? min(pos0, seq_len - 1) : seq_len - 1)) ||
-                             (a.window > 0 && key0 < pos0 + BQ - a.window);
-      // pass 1: row maximum over the visible keys
+      const int tile_key0 = (t0 + j) * BKV;
+      const bool need_mask =
+          (tile_key0 + BKV - 1 > (a.causal ? min(pos0, seq_len - 1) : seq_len - 1)) ||
+          (a.window > 0 && tile_key0 < pos0 + BQ - a.window);
+      // pass 1: maximum over this thread's 64 keys
       float mt = -INFINITY;
+      if (ok) {
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(s_addr + c * 32, v);
-        tmem_ld_wait();
-        if (need_mask) {
+        for (int c = 0; c < 2; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(s_addr + c * 32, v);
+          tmem_ld_wait();
+          if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int key = key0 + c * 32 + i;
-            if (key <= hi && key >= lo) mt = fmaxf(mt, __uint_as_float(v[i]));
-          }
-        } else {
-          float m0 = mt, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+            for (int i = 0; i < 32; ++i) {
+              const int key = key0 + c * 32 + i;
+              if (key <= hi && key >= lo) mt = fmaxf(mt, __uint_as_float(v[i]));
+            }
+          } else {
+            float m0 = mt, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            m0 = fmaxf(m0, __uint_as_float(v[i]));
-            m1 = fmaxf(m1, __uint_as_float(v[i + 1]));
-            m2 = fmaxf(m2, __uint_as_float(v[i + 2]));
-            m3 = fmaxf(m3, __uint_as_float(v[i + 3]));
+            for (int i = 0; i < 32; i += 4) {
+              m0 = fmaxf(m0, __uint_as_float(v[i]));
+              m1 = fmaxf(m1, __uint_as_float(v[i + 1]));
+              m2 = fmaxf(m2, __uint_as_float(v[i + 2]));
+              m3 = fmaxf(m3, __uint_as_float(v[i + 3]));
+            }
+            mt = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
           }
-          mt = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
         }
       }
+      xch[g * BQ + r] = mt;
+      asm volatile("bar.sync 2, 256;" ::: "memory");       // every softmax thread, every tile
+      mt = fmaxf(mt, xch[(g ^ 1) * BQ + r]);
+      asm volatile("bar.sync 3, 256;" ::: "memory");       // the slot may be rewritten next tile
       float alpha = 1.0f;
       float m_new = m_used;
       if (mt > m_used && (m_used == -INFINITY || (mt - m_used) * sl2 > 8.0f)) {
@@ -313,85 +326,87 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       const float mb = (m_new == -INFINITY ? 0.0f : m_new) * sl2;
       // pass 2: probabilities (bf16, kept in registers until the P buffer is free) and row sum
-      uint32_t pk[64];
+      uint32_t pk[32];
       float rs0 = 0.0f, rs1 = 0.0f;
+      if (ok) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(s_addr + c * 32, v);
-        tmem_ld_wait();
-        if (need_mask) {
+        for (int c = 0; c < 2; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(s_addr + c * 32, v);
+          tmem_ld_wait();
+          if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const int key = key0 + c * 32 + i;
-            float p0 = ex2_approx(fmaf(__uint_as_float(v[i]), sl2, -mb));
-            float p1 = ex2_approx(fmaf(__uint_as_float(v[i + 1]), sl2, -mb));
-            if (key > hi || key < lo) p0 = 0.0f;
-            if (key + 1 > hi || key + 1 < lo) p1 = 0.0f;
-            rs0 += p0;
-            rs1 += p1;
-            pk[c * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
-          }
-        } else {
+            for (int i = 0; i < 32; i += 2) {
+              const int key = key0 + c * 32 + i;
+              float p0 = ex2_approx(fmaf(__uint_as_float(v[i]), sl2, -mb));
+              float p1 = ex2_approx(fmaf(__uint_as_float(v[i + 1]), sl2, -mb));
+              if (key > hi || key < lo) p0 = 0.0f;
+              if (key + 1 > hi || key + 1 < lo) p1 = 0.0f;
+              rs0 += p0;
+              rs1 += p1;
+              pk[c * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
+            }
+          } else {
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float p0 = ex2_approx(fmaf(__uint_as_float(v[i]), sl2, -mb));
-            const float p1 = ex2_approx(fmaf(__uint_as_float(v[i + 1]), sl2, -mb));
-            rs0 += p0;
-            rs1 += p1;
-            pk[c * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
+            for (int i = 0; i < 32; i += 2) {
+              const float p0 = ex2_approx(fmaf(__uint_as_float(v[i]), sl2, -mb));
+              const float p1 = ex2_approx(fmaf(__uint_as_float(v[i + 1]), sl2, -mb));
+              rs0 += p0;
+              rs1 += p1;
+              pk[c * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
+            }
           }
         }
       }
-      const float rowsum = rs0 + rs1;
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[b]);
-      l = l * alpha + rowsum;
+      if (ok && lane == 0) mbar_arrive(&s_empty[b]);
+      l = l * alpha + rs0 + rs1;
       m_used = m_new;
       // the previous P V product must be complete before P is overwritten / O is rescaled
-      if (j > 0) {
-        if (!mbar_wait(o_done, (j - 1) & 1, a.status, kKernelId, 0x310u, abort_flag)) {
-          ok = false;
-          break;
-        }
+      if (ok && j > 0) {
+        if (!mbar_wait(o_done, (j - 1) & 1, a.status, kKernelId, 0x310u, abort_flag)) ok = false;
         tc_fence_after();
-        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+        if (ok && __any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 2; ++c) {
             uint32_t v[32];
-            tmem_ld_32x32(lane_addr + kColO + c * 32, v);
+            tmem_ld_32x32(lane_addr + kColO + g * 64 + c * 32, v);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-            tmem_st_32x32(lane_addr + kColO + c * 32, v);
+            tmem_st_32x32(lane_addr + kColO + g * 64 + c * 32, v);
           }
           tmem_st_wait();
         }
       }
-      // P -> shared memory, K-major rows of 128 bytes, 16-byte chunks XOR-swizzled by row % 8
+      if (ok) {
+        // P -> shared memory, K-major rows of 128 bytes, 16-byte chunks XOR-swizzled by row % 8
 #pragma unroll
-      for (int ch = 0; ch < 16; ++ch) {
-        const int sub = ch >> 3, cc = ch & 7;
-        uint4 u = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
-        *reinterpret_cast<uint4*>(sp + sub * kSub + r * 128 + ((cc ^ (r & 7)) << 4)) = u;
+        for (int cc = 0; cc < 8; ++cc) {
+          uint4 u = make_uint4(pk[cc * 4], pk[cc * 4 + 1], pk[cc * 4 + 2], pk[cc * 4 + 3]);
+          *reinterpret_cast<uint4*>(sp + r * 128 + ((cc ^ (r & 7)) << 4)) = u;
+        }
+        fence_async_smem();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_full);
       }
-      fence_async_smem();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
     }
-    // epilogue
+    // epilogue: total row sum = both halves
+    xch[g * BQ + r] = l;
+    asm volatile("bar.sync 2, 256;" ::: "memory");
+    l += xch[(g ^ 1) * BQ + r];
     if (ok && mbar_wait(o_done, (nt - 1) & 1, a.status, kKernelId, 0x320u, abort_flag)) {
       tc_fence_after();
       const float inv = l > 0.0f ? 1.0f / l : 0.0f;
       const bool row_ok = r < rows;
       __nv_bfloat16* orow =
-          a.out + static_cast<long long>(q_start + q0 + r) * a.ldo + head * HD;
+          a.out + static_cast<long long>(q_start + q0 + r) * a.ldo + head * HD + g * 64;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t v[32];
-        tmem_ld_32x32(lane_addr + kColO + c * 32, v);
+        tmem_ld_32x32(lane_addr + kColO + g * 64 + c * 32, v);
         tmem_ld_wait();
         if (row_ok) {
 #pragma unroll
@@ -405,7 +420,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
       }
-      if (row_ok && a.lse != nullptr)
+      if (g == 0 && row_ok && a.lse != nullptr)
         a.lse[static_cast<long long>(head) * a.T + q_start + q0 + r] =
             l > 0.0f ? m_used * a.scale + logf(l) : -INFINITY;
     }

@@ -64,7 +64,13 @@ def sampling_from_body(body: dict, default_max: int = 16) -> SamplingParams:
         frequency_penalty=float(body.get("frequency_penalty", 0.0)),
         repetition_penalty=float(body.get("repetition_penalty", 1.0)),
         seed=body.get("seed"), ignore_eos=bool(body.get("ignore_eos", False)),
-        stop_token_ids=stop_ids, logprobs=body.get("logprobs"), extra_args=extra)
+        stop_token_ids=stop_ids, logprobs=body.get("logprobs"),
+        prompt_logprobs=body.get("prompt_logprobs"),
+        allowed_token_ids=(tuple(int(t) for t in body["allowed_token_ids"])
+                           if body.get("allowed_token_ids") else None),
+        guided_choice=(tuple(tuple(int(t) for t in c) for c in body["guided_choice_token_ids"])
+                       if body.get("guided_choice_token_ids") else None),
+        extra_args=extra)
 
 
 def build_app(engine: Any, tokenizer: Any, model_name: str):
