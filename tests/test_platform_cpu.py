@@ -1,0 +1,69 @@
+"""Platform policy, environment flags, utilities and the plugin entry points."""
+import os
+
+import torch
+
+import vllm_gcu_b200
+from vllm_gcu_b200 import envs
+from vllm_gcu_b200.platform import PolicyInput, apply_platform_policy
+
+
+def test_entry_points_and_lazy_exports():
+    assert vllm_gcu_b200.register_platform_plugins() == "vllm_gcu_b200.platform.B200Platform"
+    vllm_gcu_b200.register_custom_models()          # must not raise with or without vLLM
+    assert vllm_gcu_b200.LLM.__name__ == "LLM"
+    assert vllm_gcu_b200.SamplingParams(max_tokens=3).max_tokens == 3
+
+
+def test_policy_async_exclusions_and_dp_ep_rules():
+    d = apply_platform_policy(PolicyInput(additional_config={"async_scheduling": True}))
+    assert d.async_scheduling and d.executor_cls is None
+    d = apply_platform_policy(PolicyInput(additional_config={"async_scheduling": True,
+                                                             "async_executing": True}))
+    assert d.async_executing and d.executor_cls.endswith("AsyncMultiprocExecutor")
+    d = apply_platform_policy(PolicyInput(pipeline_parallel_size=2,
+                                          additional_config={"async_scheduling": True}))
+    assert not d.async_scheduling and any("pipeline" in n for n in d.notes)
+    d = apply_platform_policy(PolicyInput(num_scheduler_steps=4,
+                                          additional_config={"async_scheduling": True}))
+    assert not d.async_scheduling
+    d = apply_platform_policy(PolicyInput(data_parallel_size=2, enable_expert_parallel=True,
+                                          cuda_graph_sizes=[1, 2, 4],
+                                          scheduling_policy="priority",
+                                          additional_config={"num_redundant_experts": 8,
+                                                             "enable_eplb": True}))
+    assert d.cuda_graph_sizes[0] == 0 and d.dp_padding is False
+    assert d.scheduler_cls.endswith(":priority")
+    assert d.enable_eplb and d.num_redundant_experts == 8
+    d = apply_platform_policy(PolicyInput(additional_config={"num_redundant_experts": 8}))
+    assert d.num_redundant_experts == 0 and d.notes
+
+
+def test_env_flags_accept_both_prefixes(monkeypatch):
+    monkeypatch.delenv("VLLM_B200_ORACLE", raising=False)
+    assert envs.ORACLE is None and envs.NVTX is False
+    monkeypatch.setenv("VLLM_GCU_ENABLE_SEQUENCE_PARALLEL", "1")      # the reference's spelling
+    assert envs.ENABLE_SEQUENCE_PARALLEL is True
+    monkeypatch.setenv("VLLM_B200_ORACLE", "gemm_bf16,paged_decode")
+    assert envs.ORACLE == ["gemm_bf16", "paged_decode"]
+    monkeypatch.setenv("VLLM_B200_HOOKS", "a,b")
+    assert envs.HOOKS == ["a", "b"]
+
+
+def test_utilities():
+    from vllm_gcu_b200.utils import bind_cpu_affinity, ep_alltoall_threshold
+    from vllm_gcu_b200.utils.sleep_mode import CuMemAllocator
+    import pytest
+    before = os.sched_getaffinity(0)
+    try:
+        mine = bind_cpu_affinity(0, 2)
+        assert mine and set(mine) <= set(before)
+    finally:
+        os.sched_setaffinity(0, before)
+    assert ep_alltoall_threshold(256, 256, 8) >= 256
+    with pytest.raises(NotImplementedError):
+        CuMemAllocator.get_instance().sleep()
+    from vllm_gcu_b200.layers.quant import SUPPORTED_QUANTIZATION
+    for name in ("fp8_gcu", "awq_gcu", "gptq_gcu", "w8a8_gcu", "moe_wna16_gcu", "w4a8_gcu"):
+        assert name in SUPPORTED_QUANTIZATION
+    assert torch.float8_e4m3fn is not None

@@ -81,6 +81,10 @@ def _worker_main(rank: int, world: int, port: int, cfg: EngineConfig, cmd_q, out
         from ..parallel.state import get_state, init_distributed
         from ..utils import redirect_rank_output
         redirect_rank_output(rank)
+        from .. import envs
+        if envs.CPU_AFFINITY:
+            from ..utils import bind_cpu_affinity
+            bind_cpu_affinity(rank, world)
         pc = cfg.parallel
         if world > 1:
             init_distributed(pc.tensor_parallel_size, pc.pipeline_parallel_size,

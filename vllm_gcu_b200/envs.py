@@ -54,6 +54,9 @@ environment_variables: dict[str, Callable[[], Any]] = {
     # NVTX range around every engine step, named by its kind (the reference opens a vendor
     # profiler range per step, vllm_gcu/worker/worker_v1.py:322-335)
     "NVTX": _flag("NVTX"),
+    # pin every worker process to its own slice of the CPU cores (the reference's optional
+    # worker affinity, vllm_gcu/worker/worker_v1.py:259-260)
+    "CPU_AFFINITY": _flag("CPU_AFFINITY"),
     "NIXL_ENABLE_FULL_KV_TRANSFER": _flag("NIXL_ENABLE_FULL_KV_TRANSFER"),
     "NIXL_ENABLE_FIRST_TOKEN_REUSE": _flag("NIXL_ENABLE_FIRST_TOKEN_REUSE"),
 }

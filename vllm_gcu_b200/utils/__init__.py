@@ -115,3 +115,15 @@ def redirect_rank_output(rank: int) -> Optional[str]:
     os.dup2(fd, sys.stdout.fileno())
     os.dup2(fd, sys.stderr.fileno())
     return path
+
+
+def bind_cpu_affinity(rank: int, world: int) -> Optional[list[int]]:
+    """Pins the calling process to the ``rank``-th of ``world`` equal slices of the cores it
+    may run on.  Returns the cores, or None when the platform has no affinity call."""
+    if not hasattr(os, "sched_getaffinity"):
+        return None
+    cores = sorted(os.sched_getaffinity(0))
+    per = max(1, len(cores) // max(world, 1))
+    mine = cores[rank * per:(rank + 1) * per] or cores[-per:]
+    os.sched_setaffinity(0, mine)
+    return mine
