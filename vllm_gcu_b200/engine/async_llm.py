@@ -48,7 +48,8 @@ class AsyncLLM:
     async def generate_stream(self, prompt_token_ids: Sequence[int],
                               sampling_params: Optional[SamplingParams] = None,
                               request_id: Optional[str] = None, priority: int = 0,
-                              lora_id: int = -1) -> AsyncIterator[RequestOutput]:
+                              lora_id: int = -1, kv_transfer_params: Optional[dict] = None
+                              ) -> AsyncIterator[RequestOutput]:
         if self.error is not None:
             raise RuntimeError(f"engine failed: {self.error!r}")
         rid = request_id or f"areq-{next(self._ids)}"
@@ -56,7 +57,7 @@ class AsyncLLM:
         self._streams[rid] = (asyncio.get_running_loop(), q)
         with self._lock:
             self.engine.add_request(prompt_token_ids, sampling_params, rid, priority,
-                                    lora_id=lora_id)
+                                    lora_id=lora_id, kv_transfer_params=kv_transfer_params)
         self._wake.set()
         try:
             while True:

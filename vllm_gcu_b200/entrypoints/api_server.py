@@ -142,6 +142,13 @@ def build_app(engine: Any, tokenizer: Any, model_name: str):
         created = int(time.time())
         state["requests"] += len(batch)
         priority = int(body.get("priority", 0))
+        # disaggregated prefill: the proxy names the request and the peer instance
+        kvp = body.get("kv_transfer_params")
+        gen_kw = {}
+        if kvp:
+            gen_kw = {"kv_transfer_params": kvp}
+            if body.get("request_id") and len(batch) == 1:
+                gen_kw["request_id"] = str(body["request_id"])
 
         def chunk(idx: int, toks: list[int], finish: Optional[str]) -> dict:
             return {"id": rid, "object": "text_completion", "created": created,
@@ -153,7 +160,7 @@ def build_app(engine: Any, tokenizer: Any, model_name: str):
             async def sse():
                 ids = to_ids(batch[0])
                 sent = 0
-                async for out in engine.generate_stream(ids, sp, priority=priority):
+                async for out in engine.generate_stream(ids, sp, priority=priority, **gen_kw):
                     toks = out.outputs[0].token_ids
                     new = toks[sent:]
                     sent = len(toks)
@@ -167,7 +174,7 @@ def build_app(engine: Any, tokenizer: Any, model_name: str):
         async def one(idx: int, p) -> dict:
             ids = to_ids(p)
             last = None
-            async for out in engine.generate_stream(ids, sp, priority=priority):
+            async for out in engine.generate_stream(ids, sp, priority=priority, **gen_kw):
                 last = out
             toks = last.outputs[0].token_ids
             state["tokens_out"] += len(toks)
@@ -212,7 +219,15 @@ def make_engine(args) -> tuple[Any, ModelConfig]:
         from ..engine.executor import AsyncMultiprocExecutor
         return AsyncMultiprocExecutor(cfg), mc
     from ..engine.async_llm import AsyncLLM
-    return AsyncLLM(cfg), mc
+    eng = AsyncLLM(cfg)
+    if getattr(args, "kv_port", 0):
+        # disaggregated prefill / decode: requests that carry kv_transfer_params exchange
+        # their KV with the peer instance through this connector
+        from ..parallel.kv_transfer import P2PKVConnector
+        conn = P2PKVConnector(host=args.host, port=args.kv_port, send_type=args.kv_send_type,
+                              device=str(eng.engine.device))
+        eng.engine.attach_kv_connector(conn)
+    return eng, mc
 
 
 def main() -> None:
@@ -233,6 +248,9 @@ def main() -> None:
     ap.add_argument("--enforce-eager", action="store_true")
     ap.add_argument("--device", default="auto")
     ap.add_argument("--num-hidden-layers", type=int, default=0)
+    ap.add_argument("--kv-port", type=int, default=0,
+                    help="port of the point-to-point KV connector (disaggregated prefill)")
+    ap.add_argument("--kv-send-type", default="PUT_ASYNC", choices=["PUT", "PUT_ASYNC", "GET"])
     args = ap.parse_args()
     engine, mc = make_engine(args)
     tok = load_tokenizer(args.tokenizer or (args.model if "/" in args.model else None),
