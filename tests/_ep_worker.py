@@ -63,6 +63,43 @@ def main():
                 tol = 0.03 * want.abs().max().item() + 0.03
                 assert err < tol, f"case {it} rep {rep} rank {rank}: err {err} tol {tol}"
         dist.barrier()
+    # ---- engine level: data-parallel attention + expert parallelism --------------------------
+    # every rank is its own replica with its own requests (rank 1 gets a single short one, so it
+    # idles and must keep joining the expert exchange); the peer-memory dispatcher must give
+    # the same tokens as the all-to-all baseline
+    from vllm_gcu_b200.config import (CacheConfig, EngineConfig, ParallelConfig, SchedulerConfig,
+                                      preset)
+    from vllm_gcu_b200.engine.llm import LLMEngine
+    from vllm_gcu_b200.engine.request import SamplingParams
+    gp = torch.Generator().manual_seed(50 + rank)
+    n_req = 1 if rank == 1 else 3
+    prompts = [torch.randint(0, 1024, (9 + 7 * i,), generator=gp).tolist() for i in range(n_req)]
+    sp = SamplingParams(max_tokens=2 if rank == 1 else 6, temperature=0.0, ignore_eos=True)
+    toks = {}
+    for backend in ("nccl", "fused"):
+        mc = preset("tiny-qwen3-moe", hidden_size=512, intermediate_size=1024,
+                    num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+                    num_experts=4 * world, num_experts_per_tok=2, moe_intermediate_size=256,
+                    dtype=torch.bfloat16)
+        mc.extra.update(dp_attention=True, ep_backend=backend, ep_max_tokens=256)
+        cfg = EngineConfig(model=mc, cache=CacheConfig(block_size=16, num_gpu_blocks=128),
+                           scheduler=SchedulerConfig(max_num_seqs=8, max_num_batched_tokens=256,
+                                                     max_model_len=256),
+                           parallel=ParallelConfig(data_parallel_size=world,
+                                                   enable_expert_parallel=True,
+                                                   comm_backend="nccl"),
+                           device="cuda", seed=0, enforce_eager=True)
+        eng = LLMEngine(cfg)
+        kind = type(eng.model.layers["0"].mlp.dispatcher).__name__
+        assert kind == ("FusedEPDispatcher" if backend == "fused" else "AllToAllDispatcher"), kind
+        outs = eng.generate(prompts, sp)
+        torch.cuda.synchronize()
+        _native.check_status()
+        toks[backend] = [o.outputs[0].token_ids for o in outs]
+        assert all(len(t) == sp.max_tokens for t in toks[backend])
+        dist.barrier()
+    same = sum(a[0] == b[0] for a, b in zip(toks["nccl"], toks["fused"]))
+    assert same == len(prompts), (toks["nccl"], toks["fused"])
     if rank == 0:
         print(f"ep{world} fused dispatch/combine ok", flush=True)
     dist.barrier()
