@@ -79,6 +79,47 @@ __global__ void __launch_bounds__(256) rope_cache_flash_kernel(const RopeCacheAr
   if (a.positions != nullptr) {
     const long long cs_row = a.positions[t] * a.rot_dim;
     const int heads = (q ? a.Hq : 0) + (k ? a.Hkv : 0);
+    const int half = a.rot_dim >> 1;
+    const bool vec_ok = a.is_neox && (half & 7) == 0 && (a.D & 7) == 0 && (a.ldq & 7) == 0 &&
+                        (a.ldk & 7) == 0 &&
+                        ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k)) & 15) == 0;
+    if (vec_ok) {
+      // NeoX pairs (i, i + half): one thread rotates 8 pairs with 16-byte loads and stores.
+      const int vph = half >> 3;
+      for (int it = threadIdx.x; it < heads * vph; it += blockDim.x) {
+        const int h = it / vph, i = (it % vph) * 8;
+        T* x = (q && h < a.Hq) ? q + static_cast<long long>(h) * a.D
+                               : k + static_cast<long long>(h - (q ? a.Hq : 0)) * a.D;
+        float lo[8], hi[8], c[8], sn[8];
+        vec8_load<T>(x + i, lo);
+        vec8_load<T>(x + half + i, hi);
+        if (a.cos_sin_fp32 && (reinterpret_cast<uintptr_t>(a.cos_sin) & 15) == 0) {
+          const float4* cp = reinterpret_cast<const float4*>(
+              static_cast<const float*>(a.cos_sin) + cs_row + i);
+          const float4* sp = reinterpret_cast<const float4*>(
+              static_cast<const float*>(a.cos_sin) + cs_row + half + i);
+          const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
+          c[0] = c0.x; c[1] = c0.y; c[2] = c0.z; c[3] = c0.w;
+          c[4] = c1.x; c[5] = c1.y; c[6] = c1.z; c[7] = c1.w;
+          sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w;
+          sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+        } else {
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            c[u] = cs_at<T>(a.cos_sin, cs_row + i + u, a.cos_sin_fp32);
+            sn[u] = cs_at<T>(a.cos_sin, cs_row + half + i + u, a.cos_sin_fp32);
+          }
+        }
+        float r0[8], r1[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          r0[u] = lo[u] * c[u] - hi[u] * sn[u];
+          r1[u] = hi[u] * c[u] + lo[u] * sn[u];
+        }
+        vec8_store<T>(x + i, r0);
+        vec8_store<T>(x + half + i, r1);
+      }
+    } else
     for (int h = warp; h < heads; h += nwarps) {
       T* x = (q && h < a.Hq) ? q + static_cast<long long>(h) * a.D
                              : k + static_cast<long long>(h - (q ? a.Hq : 0)) * a.D;
