@@ -145,12 +145,36 @@ class LLMEngine:
             if self.disagg is not None:
                 self.disagg.on_add(req)
         sp_ = req.sampling_params
+        if sp_.guided_regex is not None or sp_.guided_json is not None:
+            if req.eos_token_id is None:     # a guided request ends with EOS once it matches
+                req.eos_token_id = getattr(self.cfg.model, "eos_token_id", None)
+            req.guide = self._make_guide(sp_, req.eos_token_id)
         if (sp_.has_penalties or sp_.logprobs is not None or sp_.prompt_logprobs is not None
                 or sp_.constrained):
             # these need the ids of every earlier token on the host before the next step
             self._want_sync = True
         self.scheduler.add_request(req)
         return rid
+
+    def set_vocabulary(self, vocab: Sequence[Optional[str]]) -> None:
+        """Text of every token id (None for ids that must never be produced by a guided
+        request).  Needed by ``guided_regex`` / ``guided_json``."""
+        self._vocab = list(vocab)
+        self._guides = {}
+
+    def _make_guide(self, sp_: SamplingParams, eos_token_id: Optional[int]):
+        from .guided import GuideCursor, RegexGuide, json_schema_to_regex
+        vocab = getattr(self, "_vocab", None)
+        if vocab is None:
+            raise ValueError("guided_regex / guided_json need the vocabulary: call "
+                             "set_vocabulary(token_texts) first")
+        pattern = sp_.guided_regex if sp_.guided_regex is not None \
+            else json_schema_to_regex(sp_.guided_json)
+        key = (pattern, eos_token_id)
+        guide = self._guides.get(key)
+        if guide is None:
+            guide = self._guides[key] = RegexGuide(pattern, vocab, eos_token_id)
+        return GuideCursor(guide)
 
     def abort_request(self, request_id: str) -> None:
         self.scheduler.abort_request(request_id)
@@ -363,6 +387,14 @@ class LLM:
             load_format=load_format or ("safetensors" if model_path else "dummy"),
             model_path=model_path, additional_config=additional_config or {})
         self.engine = LLMEngine(cfg)
+
+    def set_vocabulary(self, vocab) -> None:
+        """Token texts (index = token id) or a tokenizer; enables ``guided_regex`` /
+        ``guided_json`` requests."""
+        if hasattr(vocab, "decode"):
+            from .guided import vocabulary_of
+            vocab = vocabulary_of(vocab, self.engine.cfg.model.vocab_size)
+        self.engine.set_vocabulary(vocab)
 
     def generate(self, prompts, sampling_params=None) -> list[RequestOutput]:
         """One ``RequestOutput`` per prompt.  ``n`` / ``best_of`` > 1 run that many sampled

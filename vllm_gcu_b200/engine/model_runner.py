@@ -644,8 +644,7 @@ class ModelRunner:
         allow_r, allow_t = [], []
         for r, j in enumerate(samplers):
             req = order[j].req
-            nxt = req.sampling_params.allowed_next(req.output_token_ids) \
-                if req.sampling_params.constrained else None
+            nxt = req.allowed_next() if req.sampling_params.constrained else None
             if nxt is not None:
                 allow_r.append((r, nxt))
         if allow_r:

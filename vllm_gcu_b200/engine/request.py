@@ -33,6 +33,10 @@ class SamplingParams:
     # these token sequences (the token-level form of guided "choice" decoding)
     allowed_token_ids: Optional[tuple[int, ...]] = None
     guided_choice: Optional[tuple[tuple[int, ...], ...]] = None
+    # grammar-guided decoding (engine/guided.py): the output text must match the pattern /
+    # be a JSON document of the schema; needs an engine that knows its vocabulary
+    guided_regex: Optional[str] = None
+    guided_json: Optional[Any] = None
     extra_args: dict[str, Any] = field(default_factory=dict)
 
     @property
@@ -41,7 +45,8 @@ class SamplingParams:
 
     @property
     def constrained(self) -> bool:
-        return self.allowed_token_ids is not None or self.guided_choice is not None
+        return (self.allowed_token_ids is not None or self.guided_choice is not None
+                or self.guided_regex is not None or self.guided_json is not None)
 
     def allowed_next(self, output_token_ids: list) -> Optional[list]:
         """Token ids that may follow ``output_token_ids`` (None = unconstrained)."""
@@ -93,6 +98,7 @@ class Request:
     mrope_positions: Optional[Any] = None
     mrope_delta: int = 0
     cache_salt: Optional[int] = None          # separates prefix-cache entries (image content)
+    guide: Optional[Any] = None               # GuideCursor of a grammar-guided request
 
     # mutable state -------------------------------------------------------
     status: RequestStatus = RequestStatus.WAITING
@@ -128,6 +134,12 @@ class Request:
     @property
     def finished(self) -> bool:
         return self.status.finished
+
+    def allowed_next(self) -> Optional[list]:
+        """Token ids the next sampled token must come from (None = unconstrained)."""
+        if self.guide is not None:
+            return self.guide.allowed_next(self.output_token_ids)
+        return self.sampling_params.allowed_next(self.output_token_ids)
 
     def token_at(self, i: int) -> int:
         n = len(self.prompt_token_ids)
@@ -173,6 +185,10 @@ def check_stop(req: Request, max_model_len: int) -> bool:
             list(c) == req.output_token_ids for c in sp.guided_choice) and not any(
             len(c) > n_out and list(c[:n_out]) == req.output_token_ids for c in sp.guided_choice):
         req.status = RequestStatus.FINISHED_STOPPED      # a complete choice, no longer one
+        return True
+    if req.guide is not None and (last == req.eos_token_id
+                                  or req.guide.finished(req.output_token_ids)):
+        req.status = RequestStatus.FINISHED_STOPPED      # pattern matched, nothing can follow
         return True
     if n_out >= sp.max_tokens or req.num_tokens >= max_model_len:
         req.status = RequestStatus.FINISHED_LENGTH

@@ -70,7 +70,30 @@ def sampling_from_body(body: dict, default_max: int = 16) -> SamplingParams:
                            if body.get("allowed_token_ids") else None),
         guided_choice=(tuple(tuple(int(t) for t in c) for c in body["guided_choice_token_ids"])
                        if body.get("guided_choice_token_ids") else None),
+        guided_regex=_guided_pattern(body), guided_json=_guided_schema(body),
         extra_args=extra)
+
+
+def _guided_pattern(body: dict) -> Optional[str]:
+    """``guided_regex`` as given; ``guided_choice`` (strings) as an alternation."""
+    if body.get("guided_regex"):
+        return str(body["guided_regex"])
+    choice = body.get("guided_choice")
+    if choice:
+        import re
+        return "(" + "|".join(re.escape(str(c)) for c in choice) + ")"
+    return None
+
+
+def _guided_schema(body: dict):
+    """``guided_json`` or the OpenAI form ``response_format = {"type": "json_schema", ...}``."""
+    if body.get("guided_json"):
+        return body["guided_json"]
+    rf = body.get("response_format") or {}
+    if rf.get("type") == "json_schema":
+        js = rf.get("json_schema") or {}
+        return js.get("schema", js) or None
+    return None
 
 
 def build_app(engine: Any, tokenizer: Any, model_name: str):
@@ -94,6 +117,17 @@ def build_app(engine: Any, tokenizer: Any, model_name: str):
     @app.get("/v1/models")
     async def models():
         return {"object": "list", "data": [{"id": model_name, "object": "model"}]}
+
+    def _ensure_vocabulary() -> None:
+        """Guided requests need the text of every token; built on first use."""
+        if state.get("vocab_set"):
+            return
+        inner = getattr(engine, "engine", engine)
+        if not hasattr(inner, "set_vocabulary"):
+            raise ValueError("guided decoding is not available on this engine")
+        from ..engine.guided import vocabulary_of
+        inner.set_vocabulary(vocabulary_of(tokenizer, inner.cfg.model.vocab_size))
+        state["vocab_set"] = True
 
     @app.get("/metrics")
     async def metrics():
@@ -137,7 +171,12 @@ def build_app(engine: Any, tokenizer: Any, model_name: str):
             return JSONResponse({"error": "prompt is required"}, status_code=400)
         batch = prompt if (isinstance(prompt, list) and prompt and
                            isinstance(prompt[0], (list, str))) else [prompt]
-        sp = sampling_from_body(body)
+        try:
+            sp = sampling_from_body(body)
+            if sp.guided_regex is not None or sp.guided_json is not None:
+                _ensure_vocabulary()
+        except ValueError as e:
+            return JSONResponse({"error": str(e)}, status_code=400)
         rid = "cmpl-" + uuid.uuid4().hex[:16]
         created = int(time.time())
         state["requests"] += len(batch)
