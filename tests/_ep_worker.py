@@ -76,7 +76,7 @@ def main():
     prompts = [torch.randint(0, 1024, (9 + 7 * i,), generator=gp).tolist() for i in range(n_req)]
     sp = SamplingParams(max_tokens=2 if rank == 1 else 6, temperature=0.0, ignore_eos=True)
     toks = {}
-    for backend in ("nccl", "fused"):
+    for backend, eager in (("nccl", True), ("fused", True), ("fused", False)):
         mc = preset("tiny-qwen3-moe", hidden_size=512, intermediate_size=1024,
                     num_attention_heads=4, num_key_value_heads=2, head_dim=128,
                     num_experts=4 * world, num_experts_per_tok=2, moe_intermediate_size=256,
@@ -88,18 +88,30 @@ def main():
                            parallel=ParallelConfig(data_parallel_size=world,
                                                    enable_expert_parallel=True,
                                                    comm_backend="nccl"),
-                           device="cuda", seed=0, enforce_eager=True)
+                           device="cuda", seed=0, enforce_eager=eager,
+                           cuda_graph_sizes=None if eager else [2, 4, 8])
         eng = LLMEngine(cfg)
         kind = type(eng.model.layers["0"].mlp.dispatcher).__name__
         assert kind == ("FusedEPDispatcher" if backend == "fused" else "AllToAllDispatcher"), kind
         outs = eng.generate(prompts, sp)
         torch.cuda.synchronize()
         _native.check_status()
-        toks[backend] = [o.outputs[0].token_ids for o in outs]
-        assert all(len(t) == sp.max_tokens for t in toks[backend])
+        name = backend if eager else backend + "+graphs"
+        toks[name] = [o.outputs[0].token_ids for o in outs]
+        assert all(len(t) == sp.max_tokens for t in toks[name])
+        if not eager:
+            # decode-only steps of a data-parallel replica replay CUDA graphs chosen by the
+            # largest batch of any replica
+            assert eng.runner.graphs, "no graphs captured"
+            if rank == 0:
+                assert eng.runner.graph_launches > 0
         dist.barrier()
     same = sum(a[0] == b[0] for a, b in zip(toks["nccl"], toks["fused"]))
     assert same == len(prompts), (toks["nccl"], toks["fused"])
+    # (the graph pads the batch and may split the attention reduction differently, so only
+    # the leading tokens are required to agree)
+    assert all(a[:2] == b[:2] for a, b in zip(toks["fused"], toks["fused+graphs"])), \
+        (toks["fused"], toks["fused+graphs"])
     if rank == 0:
         print(f"ep{world} fused dispatch/combine ok", flush=True)
     dist.barrier()

@@ -327,10 +327,18 @@ class ModelRunner:
                    or s.req.sampling_params.logprobs is not None
                    or s.req.sampling_params.prompt_logprobs is not None
                    or s.req.sampling_params.constrained for s in sched)
-        use_graph = (self.is_cuda and npf == 0 and self.graphs and nd <= self.graph_sizes[-1]
-                     and self.drafter is None and not batch_has_lora and not feat
-                     and self.cfg.parallel.data_parallel_size == 1)
-        B_pad = _pad_batch(nd, self.graph_sizes) if use_graph else B
+        # Data-parallel replicas pick the graph by the largest token count of any replica in
+        # this step (known from the exchange that precedes every step): the expert-parallel
+        # receive area inside the graph is sized by the padded batch, so it must cover what
+        # the busiest peer can send.
+        nd_graph = nd
+        if self.cfg.parallel.data_parallel_size > 1 and self.graphs:
+            from ..parallel.state import get_state
+            nd_graph = max(nd, int(get_state().dp_max_tokens or 0))
+        use_graph = (self.is_cuda and npf == 0 and bool(self.graphs)
+                     and nd_graph <= self.graph_sizes[-1]
+                     and self.drafter is None and not batch_has_lora and not feat)
+        B_pad = _pad_batch(nd_graph, self.graph_sizes) if use_graph else B
         T = T_real + (B_pad - B)
 
         i64, i32, f32 = self.np_i64, self.np_i32, self.np_f32
@@ -812,6 +820,10 @@ class ModelRunner:
         buffers and for the greedy / sampled variants."""
         if not self.is_cuda or self.cfg.enforce_eager:
             return
+        dp = self.cfg.parallel.data_parallel_size > 1
+        if dp and any(type(getattr(m, "dispatcher", None)).__name__ == "AllToAllDispatcher"
+                      for m in self.model.modules()):
+            return      # the library all-to-all sizes its exchange on the host: eager only
         if sizes is None:
             sizes = [1, 2, 4, 8] + list(range(16, self.max_seqs + 1, 16))
         sizes = sorted({s for s in sizes if s <= self.max_seqs})
@@ -824,6 +836,9 @@ class ModelRunner:
         stream = torch.cuda.Stream()
         with torch.cuda.stream(stream), torch.inference_mode():
             for Bp in reversed(sizes):
+                if dp:      # every replica captures the same sizes in the same order, so the
+                    from ..parallel.state import get_state     # warm-up exchanges pair up
+                    get_state().dp_max_tokens = Bp
                 for cur in (0, 1):
                     for greedy in (True, False):
                         md = AttentionMetadata(
