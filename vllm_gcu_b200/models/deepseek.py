@@ -36,6 +36,9 @@ from .decoder import get_linear_method
 from .moe_models import MoeDecoderLM
 
 
+USE_MLA_KERNEL = True     # tcgen05 latent attention (csrc/attention_mla.cu) where the layout allows
+
+
 def mla_attention_ref(q_full: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor,
                       q_lens: list[int], seq_lens: list[int], scale: float, L: int
                       ) -> torch.Tensor:
@@ -172,6 +175,28 @@ class MLAAttention(nn.Module):
         nd = md.num_decode_tokens
         o_lat = torch.empty((T, N, L), dtype=x.dtype, device=x.device)
         B = md.num_decodes + md.num_prefills
+        if (USE_MLA_KERNEL and ops.use_native(x)
+                and C.mla_attention_supported(q_full, kv_cache, L)):
+            # tcgen05 kernel: decode rows (one token per request), then the multi-token
+            # requests (prefill chunks, draft verification) with their own offsets
+            max_len = max(md.max_seq_len, 1)
+            if nd > 0:
+                C.mla_attention(q_full[:nd], kv_cache, md.block_tables[:nd], md.seq_lens[:nd],
+                                None, nd, max_len, self.scale, out=o_lat[:nd])
+            if md.num_prefills > 0:
+                tq = 128 // N
+                n_pf = sum(md.q_lens_cpu[md.num_decodes:B])
+                tiles = sum(-(-q // tq) for q in md.q_lens_cpu[md.num_decodes:B])
+                C.mla_attention(q_full[nd:nd + n_pf], kv_cache, md.block_tables[md.num_decodes:B],
+                                md.seq_lens[md.num_decodes:B], md.cu_q_prefill, tiles, max_len,
+                                self.scale, out=o_lat[nd:nd + n_pf])
+                if nd + n_pf < T:
+                    o_lat[nd + n_pf:] = 0
+            elif nd < T:
+                o_lat[nd:] = 0
+            o = torch.bmm(o_lat.transpose(0, 1), self.w_uv).transpose(0, 1).reshape(
+                T, N * self.vdim)
+            return self.o_proj(o)
         if nd > 0 and x.is_cuda:
             o_lat[:nd] = mla_decode_batched(q_full[:nd], kv_cache, md.block_tables[:nd],
                                             md.seq_lens[:nd], max(md.max_seq_len, 1), self.scale,

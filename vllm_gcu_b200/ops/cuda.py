@@ -489,6 +489,48 @@ def _varlen_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     return (out, lse) if return_lse else out
 
 
+def mla_attention_supported(q: torch.Tensor, cache: torch.Tensor, L: int) -> bool:
+    """Layouts the tcgen05 MLA kernel covers: bf16, 512 + 64 wide latent rows, a power-of-two
+    number of heads up to 128, cache blocks that are a multiple of 16 tokens."""
+    Nh = q.shape[1]
+    return (q.is_cuda and q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16
+            and L == 512 and q.shape[2] == 576 and cache.shape[-1] == 576
+            and 0 < Nh <= 128 and (Nh & (Nh - 1)) == 0 and cache.shape[-2] % 16 == 0)
+
+
+def mla_attention(q: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor,
+                  seq_lens: torch.Tensor, cu_q: Optional[torch.Tensor], num_tiles: int,
+                  max_seq_len: int, scale: float, out: Optional[torch.Tensor] = None,
+                  splits: Optional[int] = None) -> torch.Tensor:
+    """Latent-absorbed multi-head latent attention (attention_mla.cu).  q ``[T, N, 576]``,
+    cache ``[blocks, block_size, 576]``, returns ``[T, N, 512]``.  ``cu_q`` None: one query
+    token per request (decode).  ``num_tiles`` >= sum over requests of
+    ceil(q_len / (128 // N)).  Causal inside each request over absolute positions."""
+    T, Nh, W = q.shape
+    assert q.is_contiguous() and cache.is_contiguous()
+    nb, bs, _ = cache.shape
+    if out is None:
+        out = torch.empty((T, Nh, 512), dtype=q.dtype, device=q.device)
+    B = block_tables.shape[0]
+    if splits is None:
+        ctas = max(num_tiles, 1) * 2
+        global _SM_COUNT
+        if _SM_COUNT == 0:
+            _SM_COUNT = max(1, int(N.lib().b200_sm_count()))
+        splits = max(1, min(_SM_COUNT // ctas, (max_seq_len + 255) // 256, 16))
+    ws = None
+    if splits > 1:
+        ws = torch.empty(splits * T * Nh * 513, dtype=torch.float32, device=q.device)
+    rc = N.lib().b200_mla_attention(
+        ptr(q), ptr(out), ptr(cache), nb * bs, ptr(cu_q), ptr(seq_lens), ptr(block_tables),
+        block_tables.stride(0), bs, B, T, Nh, int(num_tiles), int(splits), ptr(ws), float(scale),
+        stream_ptr())
+    N.launch_count += 1
+    if rc != 0:
+        raise N.NativeError(f"b200_mla_attention failed with code {rc}")
+    return out
+
+
 def merge_attn_states(p_out, p_lse, s_out, s_lse, want_lse: bool = True):
     T, H, Dv = p_out.shape
     out = torch.empty_like(p_out)
