@@ -17,10 +17,17 @@
 //
 // The 128 x 512 fp32 output does not fit tensor memory next to the scores, so a tile is worked
 // on by two CTAs (blockIdx.y): both compute the scores, each accumulates 256 of the 512 output
-// columns.  Shared memory holds Q (144 KB) and one key tile (72 KB); the probabilities reuse
-// the chunks of the key tile that this CTA's half of V does not need, which are free once the
-// score MMAs have completed.  Long contexts are split over blockIdx.z; the partial results
-// (normalised output + log-sum-exp per row) are merged by mla_combine_kernel.
+// columns.  Two shapes of the kernel:
+//   QROWS = 128  Q takes 144 KB, so there is room for one key tile (72 KB) only; the
+//                probabilities reuse the chunks of the key tile that this CTA's half of V does
+//                not need, which are free once the score MMAs have completed;
+//   QROWS = 32   tiles with at most 32 valid rows (decode with up to 32 heads per rank): only
+//                those rows of Q are loaded (the MMA still spans 128 rows and reads whatever
+//                follows in shared memory for the others; rows are independent and the
+//                surplus ones are never stored), which leaves room for two key tiles and a
+//                separate P buffer: loads, score MMAs of tile j + 1 and softmax of tile j overlap.
+// Long contexts are split over blockIdx.z; the partial results (normalised output +
+// log-sum-exp per row) are merged by mla_combine_kernel.
 //
 // Warp roles: warp 0 TMA producer, warp 1 MMA issuer and TMEM owner, warps 2..9 softmax and
 // epilogue.  Every wait is bounded and reports through the status word.
@@ -40,16 +47,26 @@ constexpr int kW = 576;        // latent + rotary
 constexpr int kChunks = kW / 64;          // 9
 constexpr int kPage = 16;      // tokens per TMA copy
 constexpr int kThreads = 320;
-constexpr int kQChunk = BQ * 128;         // [128 x 64] bf16: 16 KB
 constexpr int kKChunk = BKV * 128;        // [64 x 64] bf16: 8 KB
-constexpr int kOffQ = 0;
-constexpr int kOffK = kOffQ + kChunks * kQChunk;            // 147456
-constexpr int kOffBar = kOffK + kChunks * kKChunk;          // 221184
-constexpr int kOffX = kOffBar + 128;
-constexpr int kSmemBytes = kOffX + 2 * BQ * 4 + 1024;       // 223360 (+ alignment slack)
-constexpr uint32_t kColS = 0;      // 64 columns of scores
+constexpr int kKTile = kChunks * kKChunk; // 72 KB
+constexpr uint32_t kColS = 0;      // one or two score buffers of 64 columns
 constexpr uint32_t kColO = 256;    // 256 columns of output
 constexpr uint32_t kTmemCols = 512;
+
+template <int QROWS>
+struct Lay {
+  static constexpr int kStages = QROWS == BQ ? 1 : 2;
+  static constexpr int kQChunk = QROWS * 128;               // bytes of one 64-column chunk of Q
+  static constexpr int kOffBar = 0;                          // barriers first: Q may be read past its end
+  static constexpr int kOffX = 128;
+  static constexpr int kOffQ = 2048;
+  static constexpr int kOffK = kOffQ + kChunks * kQChunk;
+  static constexpr int kOffP = kOffK + kStages * kKTile;     // separate P buffer (two stages only)
+  static constexpr int kEnd = kOffP + (kStages == 2 ? BQ * 128 : 0);
+  // the 128-row MMA reads 16 KB from the start of every Q chunk: keep that inside the allocation
+  static constexpr int kReadEnd = kOffQ + (kChunks - 1) * kQChunk + BQ * 128;
+  static constexpr int kSmemBytes = (kEnd > kReadEnd ? kEnd : kReadEnd) + 1024;
+};
 
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
@@ -69,20 +86,25 @@ struct Args {
   unsigned int* status;
 };
 
+template <int QROWS>
 __global__ void __launch_bounds__(kThreads, 1)
     mla_attn_kernel(const __grid_constant__ CUtensorMap tmQ,
                     const __grid_constant__ CUtensorMap tmK, const Args a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBar);
+  using L = Lay<QROWS>;
+  constexpr int kStages = L::kStages;
+  constexpr int kOffQ = L::kOffQ, kOffK = L::kOffK, kQChunk = L::kQChunk;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
   uint64_t* q_full = bars;
-  uint64_t* k_full = bars + 1;
-  uint64_t* k_empty = bars + 2;
-  uint64_t* s_full = bars + 3;
-  uint64_t* p_full = bars + 4;
-  uint64_t* o_done = bars + 5;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+  uint64_t* k_full = bars + 1;      // [2]
+  uint64_t* k_empty = bars + 3;     // [2]
+  uint64_t* s_full = bars + 5;      // [2]
+  uint64_t* s_empty = bars + 7;     // [2]
+  uint64_t* p_full = bars + 9;
+  uint64_t* o_done = bars + 10;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   int* s_info = reinterpret_cast<int*>(tmem_slot + 2);
 
@@ -94,9 +116,12 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    mbar_init(k_full, 1);
-    mbar_init(k_empty, 1);
-    mbar_init(s_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_empty[i], 8);
+    }
     mbar_init(p_full, 8);
     mbar_init(o_done, 1);
     *abort_flag = 0u;
@@ -185,12 +210,15 @@ __global__ void __launch_bounds__(kThreads, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // the probabilities live in two chunks of the key tile that this CTA's V half does not use
+  // one stage: the probabilities live in two chunks of the key tile that this CTA's V half
+  // does not use; two stages: in their own buffer
   const int p_chunk = half == 0 ? 4 : 0;
-  uint8_t* p_smem = smem + kOffK + p_chunk * kKChunk;
+  uint8_t* p_smem = kStages == 1 ? smem + kOffK + p_chunk * kKChunk : smem + L::kOffP;
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
+    // (One thread issues the 36 copies of a key tile; issuing them from all lanes of the warp
+    // measured 25 % slower.)
     if (elect_one()) {
       mbar_expect_tx(q_full, kChunks * kQChunk);
       for (int c = 0; c < kChunks; ++c)
@@ -198,15 +226,19 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int* bt = a.block_tables + static_cast<long long>(seq) * a.max_blocks;
       const int last_tok = seq_len - 1;
       for (int j = 0; j < nt; ++j) {
-        if (!mbar_wait(k_empty, (j & 1) ^ 1u, a.status, kKernelId, 0x100u, abort_flag)) break;
-        mbar_expect_tx(k_full, kChunks * kKChunk);
+        const int st = j % kStages;
+        const uint32_t use = static_cast<uint32_t>(j / kStages);
+        if (!mbar_wait(&k_empty[st], (use & 1u) ^ 1u, a.status, kKernelId, 0x100u + st, abort_flag))
+          break;
+        mbar_expect_tx(&k_full[st], kKTile);
         const int key0 = (t0 + j) * BKV;
         for (int pg = 0; pg < BKV / kPage; ++pg) {
           const int tok = min(key0 + pg * kPage, last_tok);     // pages past the end: any valid page
           const int blk = bt[tok / a.block_size];
           const int y = blk * a.block_size + ((key0 + pg * kPage) % a.block_size);
           for (int c = 0; c < kChunks; ++c)
-            tma_load_2d(smem + kOffK + c * kKChunk + pg * (kPage * 128), &tmK, k_full, c * 64, y);
+            tma_load_2d(smem + kOffK + st * kKTile + c * kKChunk + pg * (kPage * 128), &tmK,
+                        &k_full[st], c * 64, y);
         }
       }
     }
@@ -216,32 +248,64 @@ __global__ void __launch_bounds__(kThreads, 1)
       constexpr uint32_t kIdescS = make_idesc(BQ, BKV, 1, 1);
       constexpr uint32_t kIdescO = make_idesc(BQ, 256, 1, 1) | kIdescBMajorMN;
       const uint32_t q_addr = smem_u32(smem + kOffQ);
-      const uint32_t k_addr = smem_u32(smem + kOffK);
       const uint32_t p_addr = smem_u32(p_smem);
-      const uint64_t vdesc = make_desc_mn_sw128(k_addr + half * 4 * kKChunk, kKChunk);
-      bool ok = mbar_wait(q_full, 0, a.status, kKernelId, 0x200u, abort_flag);
-      for (int j = 0; ok && j < nt; ++j) {
-        if (!mbar_wait(k_full, j & 1, a.status, kKernelId, 0x210u, abort_flag)) break;
+      auto issue_s = [&](int j) -> bool {
+        const int st = j % kStages;
+        const uint32_t use = static_cast<uint32_t>(j / kStages);
+        if (!mbar_wait(&k_full[st], use & 1u, a.status, kKernelId, 0x210u + st, abort_flag))
+          return false;
+        if (kStages == 2 && j >= 2 &&
+            !mbar_wait(&s_empty[st], (use - 1u) & 1u, a.status, kKernelId, 0x230u + st, abort_flag))
+          return false;
         tc_fence_after();
+        const uint32_t k_addr = smem_u32(smem + kOffK + st * kKTile);
 #pragma unroll 1
         for (int c = 0; c < kChunks; ++c) {
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)
-            umma_f16(tmem_base + kColS,
+            umma_f16(tmem_base + kColS + st * BKV,
                      make_desc_k_sw128(q_addr + c * kQChunk) + static_cast<uint64_t>(ks * 2),
                      make_desc_k_sw128(k_addr + c * kKChunk) + static_cast<uint64_t>(ks * 2),
                      kIdescS, (c > 0 || ks > 0) ? 1u : 0u);
         }
-        umma_commit(s_full);
+        umma_commit(&s_full[st]);
+        return true;
+      };
+      bool ok = mbar_wait(q_full, 0, a.status, kKernelId, 0x200u, abort_flag);
+      ok = ok && issue_s(0);
+      for (int j = 0; ok && j < nt; ++j) {
+        // Two stages: the scores of tile j + 1 and P V of tile j are issued in whichever order
+        // their inputs arrive.  (The key tile j + 1 could only be requested after P V of tile
+        // j - 1 had finished; waiting for it first would hold back P V of tile j.)
+        bool s_pending = kStages == 2 && j + 1 < nt;
+        const int st = j % kStages;
+        if (s_pending) {
+          const int st1 = (j + 1) % kStages;
+          const uint32_t use1 = static_cast<uint32_t>((j + 1) / kStages);
+          for (uint32_t it = 0; it < kMbarSpinLimit; ++it) {
+            if (mbar_test(&k_full[st1], use1 & 1u) &&
+                (j + 1 < 2 || mbar_test(&s_empty[st1], (use1 - 1u) & 1u))) {
+              ok = issue_s(j + 1);            // its waits return at once
+              s_pending = false;
+              break;
+            }
+            if (mbar_test(p_full, j & 1)) break;
+            if ((it & 1023u) == 1023u && *abort_flag != 0u) { ok = false; break; }
+          }
+        }
+        if (!ok) break;
         if (!mbar_wait(p_full, j & 1, a.status, kKernelId, 0x220u, abort_flag)) break;
         tc_fence_after();
+        const uint32_t k_addr = smem_u32(smem + kOffK + st * kKTile);
+        const uint64_t vdesc = make_desc_mn_sw128(k_addr + half * 4 * kKChunk, kKChunk);
 #pragma unroll
         for (int ks = 0; ks < BKV / 16; ++ks)
           umma_f16(tmem_base + kColO, make_desc_k_sw128(p_addr) + static_cast<uint64_t>(ks * 2),
                    vdesc + static_cast<uint64_t>(ks) * (2048 >> 4), kIdescO,
                    (j > 0 || ks > 0) ? 1u : 0u);
-        umma_commit(k_empty);
+        umma_commit(&k_empty[st]);
         umma_commit(o_done);
+        if ((kStages == 1 || s_pending) && j + 1 < nt) ok = issue_s(j + 1);
       }
     }
   } else {
@@ -257,10 +321,13 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int hi_first = min(pos0, seq_len - 1);
     const float sl2 = a.scale * 1.4426950408889634f;
     float m_used = -INFINITY, l = 0.0f;
-    float* xch = reinterpret_cast<float*>(smem + kOffX);    // [2][128]
+    float* xch = reinterpret_cast<float*>(smem + L::kOffX);    // [2][128]
     bool ok = true;
     for (int j = 0; j < nt; ++j) {
-      if (ok && !mbar_wait(s_full, j & 1, a.status, kKernelId, 0x300u, abort_flag)) ok = false;
+      const int st = j % kStages;
+      if (ok && !mbar_wait(&s_full[st], static_cast<uint32_t>(j / kStages) & 1u, a.status,
+                           kKernelId, 0x300u + st, abort_flag))
+        ok = false;
       tc_fence_after();
       const int tile_key0 = (t0 + j) * BKV;
       const int key0 = tile_key0 + g * 32;
@@ -268,7 +335,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       uint32_t v[32];
       float mt = -INFINITY;
       if (ok) {
-        tmem_ld_32x32(lane_addr + kColS + g * 32, v);
+        tmem_ld_32x32(lane_addr + kColS + st * BKV + g * 32, v);
         tmem_ld_wait();
         if (need_mask) {
 #pragma unroll
@@ -307,8 +374,18 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       l = l * alpha + rs;
       m_used = m_new;
-      // The previous P V product is complete: the key tile of this iteration was loaded only
-      // after it.  Rescale the accumulator when the maximum was raised.
+      if (kStages == 2) {
+        tc_fence_before();
+        __syncwarp();
+        if (ok && lane == 0) mbar_arrive(&s_empty[st]);
+        // the previous P V product must be complete before P is overwritten / O is rescaled
+        if (ok && j > 0 &&
+            !mbar_wait(o_done, (j - 1) & 1, a.status, kKernelId, 0x310u, abort_flag))
+          ok = false;
+        tc_fence_after();
+      }
+      // (One stage: the previous P V product is complete already, the key tile of this
+      // iteration was loaded only after it.)  Rescale the accumulator when the maximum rose.
       if (ok && j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
@@ -479,8 +556,11 @@ B200_API int b200_mla_attention(const void* q, void* out, const void* cache, lon
   if (splits > 1 && workspace == nullptr) return -12;
   int log2N = 0;
   while ((1 << log2N) < N) ++log2N;
+  // tiles with at most 32 valid rows (decode, up to 32 heads): the variant that loads only
+  // those rows of Q and double-buffers the key tiles
+  const bool small = cu_q == nullptr && N <= 32;
   CUtensorMap tmQ, tmK;
-  int r = get_map(q, static_cast<unsigned long long>(T) * N, BQ, false, &tmQ);
+  int r = get_map(q, static_cast<unsigned long long>(T) * N, small ? 32 : BQ, false, &tmQ);
   if (r != 0) return r < 0 ? -6 : r;
   r = get_map(cache, static_cast<unsigned long long>(num_slots), kPage, true, &tmK);
   if (r != 0) return r < 0 ? -6 : r;
@@ -497,14 +577,21 @@ B200_API int b200_mla_attention(const void* q, void* out, const void* cache, lon
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(mla_attn_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(mla_attn_kernel<BQ>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Lay<BQ>::kSmemBytes);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(mla_attn_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               Lay<32>::kSmemBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured[dev] = true;
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   dim3 grid(num_tiles, 2, splits);
-  mla_attn_kernel<<<grid, kThreads, kSmemBytes, s>>>(tmQ, tmK, a);
+  if (small)
+    mla_attn_kernel<32><<<grid, kThreads, Lay<32>::kSmemBytes, s>>>(tmQ, tmK, a);
+  else
+    mla_attn_kernel<BQ><<<grid, kThreads, Lay<BQ>::kSmemBytes, s>>>(tmQ, tmK, a);
   int e = static_cast<int>(cudaGetLastError());
   if (e != 0 || splits == 1) return e;
   mla_combine_kernel<<<static_cast<unsigned>(rows_total), 128, 0, s>>>(a.ws_o, a.ws_lse, a.out,
