@@ -9,6 +9,8 @@ launches the kernel of interest a handful of times:
   python benchmarks/kernels/ncu_cases.py --case prefill_attn   # 8 x 1024 tokens, causal
   python benchmarks/kernels/ncu_cases.py --case gemm_fp8       # 4096 x 4096 x 4096 fp8
   python benchmarks/kernels/ncu_cases.py --case gemm_ar_single # fused all-reduce epilogue, p = 1
+  python benchmarks/kernels/ncu_cases.py --case mla_decode     # latent attention, 128 heads
+  python benchmarks/kernels/ncu_cases.py --case mla_decode_small  # latent attention, 16 heads
 
 Capture (one GPU):
   ncu --set full --clock-control none -k regex:<kernel> -s 2 -c 2 -o gpurun_out/<name> \
@@ -97,6 +99,19 @@ def main():
                 words.data_ptr(), words.data_ptr() + 16, 0, 1, None, 0, 1, M * N,
                 torch.cuda.current_stream().cuda_stream)
             assert rc == 0, rc
+    elif a.case in ("mla_decode", "mla_decode_small"):
+        # latent attention, B = 256, ctx = 1152: 340 MB of latent cache (larger than L2);
+        # 128 heads (data-parallel attention) or 16 heads (tensor parallel 8)
+        B, ctx, bs = 256, 1152, 16
+        Nh = 128 if a.case == "mla_decode" else 16
+        mb = ctx // bs
+        cache = (torch.randn(B * mb, bs, 576, device=dev) * 0.3).to(torch.bfloat16)
+        bt = torch.randperm(B * mb, device=dev).to(torch.int32).view(B, mb)
+        sl = torch.full((B,), ctx, device=dev, dtype=torch.int32)
+        q = (torch.randn(B, Nh, 576, device=dev) * 0.3).to(torch.bfloat16)
+        out = torch.empty(B, Nh, 512, device=dev, dtype=torch.bfloat16)
+        fn = lambda: C.mla_attention(q, cache, bt, sl, None, B, ctx, 576 ** -0.5, out=out,  # noqa
+                                     splits=1)
     else:
         raise SystemExit(f"unknown case {a.case}")
     for _ in range(a.iters):

@@ -16,7 +16,7 @@
 //   O += P V     V is the key tile itself read as an MN-major operand (keys x latent columns).
 //
 // The 128 x 512 fp32 output does not fit tensor memory next to the scores, so a tile is worked
-// on by two CTAs (blockIdx.y): both compute the scores, each accumulates 256 of the 512 output
+// on by two CTAs (neighbours in blockIdx.x): both compute the scores, each accumulates 256 of the 512 output
 // columns.  Two shapes of the kernel:
 //   QROWS = 128  Q takes 144 KB, so there is room for one key tile (72 KB) only; the
 //                probabilities reuse the chunks of the key tile that this CTA's half of V does
@@ -26,7 +26,7 @@
 //                follows in shared memory for the others; rows are independent and the
 //                surplus ones are never stored), which leaves room for two key tiles and a
 //                separate P buffer: loads, score MMAs of tile j + 1 and softmax of tile j overlap.
-// Long contexts are split over blockIdx.z; the partial results (normalised output +
+// Long contexts are split over blockIdx.y; the partial results (normalised output +
 // log-sum-exp per row) are merged by mla_combine_kernel.
 //
 // Warp roles: warp 0 TMA producer, warp 1 MMA issuer and TMEM owner, warps 2..9 softmax and
@@ -110,8 +110,12 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int half = blockIdx.y;                 // output columns [256 half, 256 half + 256)
-  const int split = blockIdx.z;
+  // The two CTAs of a tile are neighbours in the grid, so they run at the same time and the
+  // second one finds the key tiles in L2 (as separate grid rows they ran waves apart and
+  // every tile was read from DRAM twice).
+  const int half = blockIdx.x & 1;             // output columns [256 half, 256 half + 256)
+  const int tile_id = blockIdx.x >> 1;
+  const int split = blockIdx.y;
   const int tq = BQ >> a.log2N;                // tokens per tile
 
   if (threadIdx.x == 0) {
@@ -147,13 +151,12 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (lane >= d) inc += n;
       }
       const int start = base + inc - nt_b;
-      const bool mine = nt_b > 0 && static_cast<int>(blockIdx.x) >= start &&
-                        static_cast<int>(blockIdx.x) < start + nt_b;
+      const bool mine = nt_b > 0 && tile_id >= start && tile_id < start + nt_b;
       const unsigned int vote = __ballot_sync(0xffffffffu, mine);
       if (vote != 0u) {
         const int src = __ffs(vote) - 1;
         found = b0 + src;
-        qt = static_cast<int>(blockIdx.x) - __shfl_sync(0xffffffffu, start, src);
+        qt = tile_id - __shfl_sync(0xffffffffu, start, src);
       }
       base += __shfl_sync(0xffffffffu, inc, 31);
     }
@@ -587,7 +590,7 @@ B200_API int b200_mla_attention(const void* q, void* out, const void* cache, lon
     configured[dev] = true;
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  dim3 grid(num_tiles, 2, splits);
+  dim3 grid(num_tiles * 2, splits);
   if (small)
     mla_attn_kernel<32><<<grid, kThreads, Lay<32>::kSmemBytes, s>>>(tmQ, tmK, a);
   else
