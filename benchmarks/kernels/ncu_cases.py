@@ -11,6 +11,7 @@ launches the kernel of interest a handful of times:
   python benchmarks/kernels/ncu_cases.py --case gemm_ar_single # fused all-reduce epilogue, p = 1
   python benchmarks/kernels/ncu_cases.py --case mla_decode     # latent attention, 128 heads
   python benchmarks/kernels/ncu_cases.py --case mla_decode_small  # latent attention, 16 heads
+  python benchmarks/kernels/ncu_cases.py --case wna16_decode   # fused 4-bit de-quantising GEMM
 
 Capture (one GPU):
   ncu --set full --clock-control none -k regex:<kernel> -s 2 -c 2 -o gpurun_out/<name> \
@@ -112,6 +113,20 @@ def main():
         out = torch.empty(B, Nh, 512, device=dev, dtype=torch.bfloat16)
         fn = lambda: C.mla_attention(q, cache, bt, sl, None, B, ctx, 576 ** -0.5, out=out,  # noqa
                                      splits=1)
+    elif a.case == "wna16_decode":
+        # fused de-quantising GEMM, 4-bit weights, M = 64, N = 28672, K = 4096 (59 MB packed;
+        # three weight copies so that consecutive launches miss L2)
+        M, Nn, K, g = 64, 28672, 4096, 128
+        qws = [torch.randint(0, 256, (Nn, K // 2), dtype=torch.uint8, device=dev)
+               for _ in range(3)]
+        sc = (torch.rand(Nn, K // g, device=dev) * 0.02).to(torch.bfloat16)
+        zs = (torch.rand(Nn, K // g, device=dev) * 0.1).to(torch.bfloat16)
+        x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        state = {"i": 0}
+
+        def fn():
+            state["i"] += 1
+            C.gemm_wna16(x, qws[state["i"] % 3], sc, zs, g, 4)
     else:
         raise SystemExit(f"unknown case {a.case}")
     for _ in range(a.iters):

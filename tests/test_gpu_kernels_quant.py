@@ -129,3 +129,39 @@ def test_weight_dequant_and_quant_linear(C):
     zp = torch.tensor([5], dtype=torch.int32, device="cuda")
     _close(C.int8_dequant(i8, sc, zp, torch.float32),
            ref.static_scaled_int8_dequant(i8, sc, zp), 1e-5, 1e-6)
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("M,N,K,g", [(1, 256, 512, 128), (37, 200, 1024, 64), (128, 4096, 4096, 128),
+                                     (256, 1024, 2048, 32), (200, 96, 256, 256)])
+def test_fused_wna16_gemm_matches_dequant_reference(C, bits, M, N, K, g):
+    """De-quantising GEMM (gemm_wna16.cu) against fp32 matmul on the de-quantised weights;
+    the weights the kernel builds in shared memory are the ones the stand-alone kernel writes."""
+    torch.manual_seed(bits * 100 + M)
+    dev = "cuda"
+    qmax = 16 if bits == 4 else 256
+    q = torch.randint(0, qmax, (N, K), dtype=torch.uint8, device=dev)
+    qw = (q[:, 0::2] | (q[:, 1::2] << 4)).contiguous() if bits == 4 else q.contiguous()
+    sc = (torch.rand(N, K // g, device=dev) * 0.02 + 0.005).to(torch.bfloat16)
+    zero = torch.randint(0, qmax, (N, K // g), device=dev).float()
+    zs = (zero * sc.float()).to(torch.bfloat16)
+    x = (torch.randn(M, K, device=dev) * 0.5).to(torch.bfloat16)
+    bias = torch.randn(N, device=dev).to(torch.bfloat16) if M % 2 else None
+    got = C.gemm_wna16(x, qw, sc, zs, g, bits, bias)
+    assert got is not None
+    torch.cuda.synchronize()
+    from vllm_gcu_b200.ops import _native
+    _native.check_status()
+    w = torch.empty(N, K, dtype=torch.bfloat16, device=dev)
+    C.weight_dequant(qw, sc, zs, w, g, bits)
+    w_ref = (q.float() * sc.float().repeat_interleave(g, 1)
+             - zs.float().repeat_interleave(g, 1)).to(torch.bfloat16)
+    assert torch.equal(w, w_ref)
+    want = x.float() @ w.float().t()
+    if bias is not None:
+        want = want + bias.float()
+    err = (got.float() - want).abs().max().item()
+    assert err < 1e-2 * want.abs().max().item() + 1e-2, err
+    # shapes outside the kernel's range are declined, not mis-computed
+    assert C.gemm_wna16(torch.zeros(300, K, dtype=torch.bfloat16, device=dev), qw, sc, zs, g,
+                        bits) is None

@@ -236,8 +236,9 @@ def unpack_gptq(qweight: torch.Tensor, qzeros: torch.Tensor, bits: int
 class WNA16LinearMethod(LinearMethod):
     """AWQ / GPTQ weight-only quantisation.  Device layout after loading: ``qw`` uint8
     ``[N, K/2]`` (two nibbles per byte, low = even k) or ``[N, K]`` for 8 bit, ``scales``
-    and ``zs = zero * scale`` as ``[N, K/g]``.  The GPU path de-quantises the layer into a
-    shared bf16 scratch and runs the tcgen05 GEMM on it."""
+    and ``zs = zero * scale`` as ``[N, K/g]``.  On the GPU, inputs of up to 256 rows go
+    through the fused de-quantising GEMM (csrc/gemm_wna16.cu); larger ones de-quantise the
+    layer into a shared bf16 scratch and run the bf16 tcgen05 GEMM on it."""
 
     _scratch: dict = {}
 
@@ -333,9 +334,16 @@ class WNA16LinearMethod(LinearMethod):
         if not hasattr(layer, "qw"):
             self.process_weights_after_loading(layer)
         bias = None if skip_bias else layer.bias
-        w = self.dequantize(layer)
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
+        if (ops.use_native(x2) and x2.dtype == torch.bfloat16
+                and x2.shape[0] <= C.WNA16_FUSED_MAX_M):
+            # decode-sized input: de-quantise inside the GEMM (reads the packed weights only)
+            g = self.g if self.g > 0 else layer.in_per_rank
+            y = C.gemm_wna16(x2, layer.qw, layer.sc, layer.zs, g, self.bits, bias)
+            if y is not None:
+                return y.view(*shape[:-1], y.shape[1])
+        w = self.dequantize(layer)
         if ops.use_native(x2) and x2.dtype == torch.bfloat16:
             y = C.gemm_bf16(x2, w, bias=bias)
         else:

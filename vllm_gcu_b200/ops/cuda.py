@@ -489,6 +489,32 @@ def _varlen_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     return (out, lse) if return_lse else out
 
 
+WNA16_FUSED_MAX_M = 256
+
+
+def gemm_wna16(x: torch.Tensor, qw: torch.Tensor, scales: torch.Tensor, zs: torch.Tensor,
+               group: int, bits: int, bias: Optional[torch.Tensor] = None
+               ) -> Optional[torch.Tensor]:
+    """Fused de-quantise + GEMM for decode-sized inputs (gemm_wna16.cu): ``x [M, K]`` bf16,
+    ``qw [N, K/2]`` (4 bit) or ``[N, K]`` (8 bit) uint8, ``scales`` / ``zs`` ``[N, K/g]`` bf16.
+    Returns None when the shape is outside what the kernel covers."""
+    M, K = x.shape
+    Nn = qw.shape[0]
+    if (M > WNA16_FUSED_MAX_M or x.dtype != torch.bfloat16 or scales.dtype != torch.bfloat16
+            or x.stride(1) != 1):
+        return None
+    out = torch.empty((M, Nn), dtype=x.dtype, device=x.device)
+    rc = N.lib().b200_gemm_wna16(ptr(x), x.stride(0), ptr(qw), ptr(scales), ptr(zs), ptr(bias),
+                                 ptr(out), out.stride(0), M, Nn, K, int(group), int(bits),
+                                 stream_ptr())
+    N.launch_count += 1
+    if rc == -20:
+        return None
+    if rc != 0:
+        raise N.NativeError(f"b200_gemm_wna16 failed with code {rc}")
+    return out
+
+
 def mla_attention_supported(q: torch.Tensor, cache: torch.Tensor, L: int) -> bool:
     """Layouts the tcgen05 MLA kernel covers: bf16, 512 + 64 wide latent rows, a power-of-two
     number of heads up to 128, cache blocks that are a multiple of 16 tokens."""
