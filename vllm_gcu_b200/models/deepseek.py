@@ -12,9 +12,10 @@ vllm_gcu/models/deepseek_v3/deepseek_v3_fusion.py:105-258):
    and writes the latent row into the paged cache (``ops.cuda.mla_rope_cache``);
 3. ``q_nope x W_UK`` -> latent query; attention over the cached latents; ``x W_UV``; ``o_proj``.
 
-The attention core itself currently runs as batched matrix products over gathered latent
-rows (decode: one padded batch; prefill: per sequence); the dedicated tcgen05 latent
-attention kernel is listed as open work in DESIGN.md.
+The attention core runs in the tcgen05 latent attention kernel (csrc/attention_mla.cu:
+decode, multi-token verification and prefill chunks in one kernel) for bf16 caches and a
+power-of-two head count up to 128; other layouts fall back to batched matrix products over
+gathered latent rows (decode: one padded batch; prefill: per sequence).
 """
 from __future__ import annotations
 
