@@ -118,3 +118,22 @@ def test_oracle_mode_checks_every_step(monkeypatch):
     with pytest.raises(C.OracleMismatch):
         C.oracle_compare("probe", torch.ones(4, device="cuda"), torch.zeros(4))
     _native.check_status()
+
+
+def test_swap_preemption_on_gpu_reproduces_unpreempted_tokens():
+    """Too few KV blocks for the batch: victims are swapped to pinned host blocks
+    (b200_swap_blocks on the step's stream) and resume without recomputing."""
+    kw = dict(num_hidden_layers=2, hidden_size=512, intermediate_size=1024,
+              num_attention_heads=8, num_key_value_heads=2, head_dim=64, vocab_size=2048,
+              max_num_seqs=4, max_num_batched_tokens=64, max_model_len=256,
+              enable_prefix_caching=False, enforce_eager=True)
+    sp = SamplingParams(max_tokens=30, temperature=0.0, ignore_eos=True)
+    prompts = _prompts(3, [50, 44, 37], 2048, seed=9)
+    ample = LLM("llama-3-8b", device="cuda", num_gpu_blocks=64, **kw)
+    want = [o.outputs[0].token_ids for o in ample.generate(prompts, sp)]
+    tight = LLM("llama-3-8b", device="cuda", num_gpu_blocks=12, num_cpu_blocks=16, **kw)
+    got = [o.outputs[0].token_ids for o in tight.generate(prompts, sp)]
+    torch.cuda.synchronize()
+    _native.check_status()
+    assert tight.engine.scheduler.num_swaps > 0
+    assert got == want

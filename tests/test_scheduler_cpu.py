@@ -183,3 +183,50 @@ def test_spec_tokens_rollback_on_rejection():
     assert r.output_token_ids == [5, 6, 9]
     assert r.num_computed_tokens == before - 2
     assert r.num_computed_tokens == r.num_tokens - 1
+
+
+def test_preemption_by_swap_keeps_computed_tokens_and_returns_host_blocks():
+    """With swap space a victim keeps its computed tokens: its blocks are copied out
+    (swap_out pairs), it waits as SWAPPED, and comes back with swap_in pairs onto fresh blocks
+    instead of recomputing the prompt."""
+    sc = SchedulerConfig(max_num_seqs=8, max_num_batched_tokens=128, max_model_len=512)
+    cc = CacheConfig(block_size=16, enable_prefix_caching=False, num_cpu_blocks=16)
+    s = Scheduler(sc, cc, 8)
+    a, b = req(60, max_tokens=40), req(60, max_tokens=40)
+    s.add_request(a)
+    s.add_request(b)
+    outs, ins, computed_after_prefill = [], [], 0
+    done = {}
+    for _ in range(500):
+        if not s.has_unfinished():
+            break
+        so = s.schedule()
+        outs += so.swap_out
+        ins += so.swap_in
+        for x in so.scheduled:
+            # a request that was swapped out never re-runs its prompt
+            if x.req.num_preemptions > 0 and x.req.status == RequestStatus.RUNNING:
+                assert x.num_tokens == 1
+        toks = {x.req.request_id: [7] for x in so.scheduled if x.will_sample}
+        for o in s.update_from_output(so, toks):
+            if o.finished:
+                done[o.request_id] = o
+    assert len(done) == 2 and all(len(o.outputs[0].token_ids) == 40 for o in done.values())
+    assert s.num_swaps > 0 and s.stats()["num_swaps"] == s.num_swaps
+    assert len(outs) == len(ins) > 0
+    assert sorted(c for _, c in outs) == sorted(c for c, _ in ins)     # every host block returns
+    assert sorted(s.cpu_free) == list(range(16))
+    # an aborted swapped request gives its host blocks back
+    s2 = Scheduler(sc, cc, 8)
+    a, b = req(60, max_tokens=40), req(60, max_tokens=40)
+    s2.add_request(a)
+    s2.add_request(b)
+    for _ in range(200):
+        so = s2.schedule()
+        s2.update_from_output(so, {x.req.request_id: [7] for x in so.scheduled if x.will_sample})
+        victim = next((r for r in (a, b) if r.status == RequestStatus.SWAPPED), None)
+        if victim is not None:
+            break
+    assert victim is not None and len(s2.cpu_free) < 16
+    s2.abort_request(victim.request_id)
+    assert sorted(s2.cpu_free) == list(range(16))

@@ -225,6 +225,7 @@ class LLMEngine:
         if so.is_empty:
             self.runner.release(so.finished_req_ids)
             self.runner.release(so.preempted_req_ids)
+            self.runner.apply_swaps(so)
             return None
         handle = self.runner.execute(so)
         self.stats["steps"] += 1
@@ -342,7 +343,8 @@ class LLM:
                  enable_prefix_caching: bool = True, async_scheduling: bool = False,
                  num_scheduler_steps: int = 1,
                  enforce_eager: bool = False, device: str = "auto", seed: int = 0,
-                 num_gpu_blocks: Optional[int] = None, scheduling_policy: str = "fcfs",
+                 num_gpu_blocks: Optional[int] = None, num_cpu_blocks: int = 0,
+                 scheduling_policy: str = "fcfs",
                  load_format: Optional[str] = None, comm_backend: str = "fused",
                  enable_expert_parallel: bool = False, dtype: Optional[str] = None,
                  cuda_graph_sizes: Optional[list[int]] = None,
@@ -370,7 +372,7 @@ class LLM:
             model=mc,
             cache=CacheConfig(block_size=block_size, gpu_memory_utilization=gpu_memory_utilization,
                               enable_prefix_caching=enable_prefix_caching,
-                              num_gpu_blocks=num_gpu_blocks),
+                              num_gpu_blocks=num_gpu_blocks, num_cpu_blocks=num_cpu_blocks),
             scheduler=SchedulerConfig(max_num_seqs=max_num_seqs,
                                       max_num_batched_tokens=max_num_batched_tokens,
                                       max_model_len=max_model_len or mc.max_position_embeddings,

@@ -307,9 +307,40 @@ class ModelRunner:
             self.prev_index.pop(rid, None)
 
     # -- one step ---------------------------------------------------------------------
+    def apply_swaps(self, so: SchedulerOutput) -> None:
+        """Swap preemption: copies whole KV blocks between the device caches and a host copy
+        (pinned, allocated on first use) on the current stream, before this step's kernels can
+        overwrite the released blocks.  Copy-in first: a host block freed by it may be the
+        target of a copy-out of the same step."""
+        if not so.swap_in and not so.swap_out:
+            return
+        n_cpu = int(self.cfg.cache.num_cpu_blocks)
+        if getattr(self, "cpu_caches", None) is None:
+            pin = self.is_cuda
+            self.cpu_caches = []
+            for c in self.kv_caches:
+                shape = list(c.shape)
+                shape[0 if c.dim() == 3 else 1] = n_cpu
+                self.cpu_caches.append(torch.zeros(shape, dtype=c.dtype, device="cpu",
+                                                   pin_memory=pin))
+        from ..ops import cuda as C, ref
+        swap = C.swap_blocks if self.is_cuda else ref.swap_blocks
+        m_in = torch.tensor(so.swap_in, dtype=torch.int64).view(-1, 2)
+        m_out = torch.tensor(so.swap_out, dtype=torch.int64).view(-1, 2)
+        for dev_c, cpu_c in zip(self.kv_caches, self.cpu_caches):
+            planes = [(dev_c, cpu_c)] if dev_c.dim() == 3 else [(dev_c[0], cpu_c[0]),
+                                                                (dev_c[1], cpu_c[1])]
+            for d, h in planes:
+                if len(so.swap_in):
+                    swap(h, d, m_in)
+                if len(so.swap_out):
+                    swap(d, h, m_out)
+        so.swap_in, so.swap_out = [], []
+
     def execute(self, so: SchedulerOutput, want_device_timing: bool = False) -> StepHandle:
         self.release(so.finished_req_ids)
         self.release(so.preempted_req_ids)
+        self.apply_swaps(so)
         if so.is_empty:
             return StepHandle([], 0, None, None)
         sched = so.scheduled

@@ -99,6 +99,7 @@ class Request:
     mrope_delta: int = 0
     cache_salt: Optional[int] = None          # separates prefix-cache entries (image content)
     guide: Optional[Any] = None               # GuideCursor of a grammar-guided request
+    cpu_block_ids: list = field(default_factory=list)   # host blocks while swapped out
 
     # mutable state -------------------------------------------------------
     status: RequestStatus = RequestStatus.WAITING

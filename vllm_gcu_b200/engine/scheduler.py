@@ -42,6 +42,10 @@ class SchedulerOutput:
     total_tokens: int = 0
     finished_req_ids: set[str] = field(default_factory=set)
     preempted_req_ids: list[str] = field(default_factory=list)
+    # swap preemption: (device block, host block) pairs to copy out / (host, device) to copy in,
+    # executed by the runner before the forward pass of this step (copy-in first)
+    swap_out: list[tuple[int, int]] = field(default_factory=list)
+    swap_in: list[tuple[int, int]] = field(default_factory=list)
     step_id: int = 0
 
     @property
@@ -67,6 +71,10 @@ class Scheduler:
         self.num_lookahead_tokens = num_lookahead_tokens
         self.step_id = 0
         self.num_preemptions = 0
+        # host blocks of the swap space (CacheConfig.num_cpu_blocks > 0 turns preemption by
+        # recomputation into preemption by swapping where the victim's state allows it)
+        self.cpu_free: list[int] = list(range(int(getattr(cache_cfg, "num_cpu_blocks", 0) or 0)))
+        self.num_swaps = 0
         #: emit a RequestOutput for every sampled token (streaming); False: finished only
         self.emit_partial = True
 
@@ -110,6 +118,9 @@ class Scheduler:
                 pass
         if self.on_free is not None:
             self.on_free(req)           # e.g. ship the KV to a decode instance
+        if getattr(req, "cpu_block_ids", None):
+            self.cpu_free.extend(req.cpu_block_ids)
+            req.cpu_block_ids = []
         self.kv.free(req)
         self.finished_since_last.add(req.request_id)
         self.requests.pop(req.request_id, None)
@@ -124,6 +135,28 @@ class Scheduler:
     # -- scheduling ------------------------------------------------------------
     def _preempt(self, victim: Request, out: SchedulerOutput) -> None:
         self.running.remove(victim)
+        bs = self.kv.block_size
+        nb = -(-victim.num_computed_tokens // bs)
+        if (0 < nb <= len(self.cpu_free) and victim.num_output_placeholders == 0
+                and not victim.spec_token_ids and victim.mm_embeds is None
+                and nb <= len(victim.block_ids)):
+            # swap: the blocks that hold computed tokens go to host memory and the request
+            # resumes where it stopped (the reference's legacy engine swaps the same way,
+            # vllm_gcu/attention/ops/paged_attn.py:214-234 `swap_blocks`)
+            cpu = [self.cpu_free.pop() for _ in range(nb)]
+            out.swap_out.extend(zip(victim.block_ids[:nb], cpu))
+            victim.cpu_block_ids = cpu
+            self.kv.free(victim)
+            victim.status = RequestStatus.SWAPPED
+            victim.num_preemptions += 1
+            self.num_preemptions += 1
+            self.num_swaps += 1
+            out.preempted_req_ids.append(victim.request_id)
+            if self.priority:
+                self._insert_by_priority(victim)
+            else:
+                self.waiting.appendleft(victim)
+            return
         self.kv.free(victim)
         victim.status = RequestStatus.PREEMPTED
         victim.num_computed_tokens = 0
@@ -246,6 +279,11 @@ class Scheduler:
                         continue
                     break
                 self.waiting.popleft()
+                if req.status == RequestStatus.SWAPPED:
+                    cpu = req.cpu_block_ids
+                    out.swap_in.extend(zip(cpu, req.block_ids[:len(cpu)]))
+                    self.cpu_free.extend(cpu)
+                    req.cpu_block_ids = []
                 if num_cached:
                     req.num_computed_tokens = num_cached
                     if req.num_preemptions == 0:
@@ -364,4 +402,4 @@ class Scheduler:
                 "kv_cache_usage": self.kv.usage,
                 "prefix_cache_queries": self.kv.pool.queries,
                 "prefix_cache_hits": self.kv.pool.hits,
-                "num_preemptions": self.num_preemptions}
+                "num_preemptions": self.num_preemptions, "num_swaps": self.num_swaps}
