@@ -11,10 +11,13 @@
 // multiply-add rounded to bf16, as the stand-alone de-quantisation kernel does) and write the
 // bf16 tile into shared memory in the K-major 128-byte
 // swizzled layout that tcgen05.mma reads; the activation tiles arrive by TMA; accumulators
-// live in tensor memory.  Packed weights are prefetched eight K blocks ahead into registers.
+// live in tensor memory.  Packed weights are prefetched eight K blocks ahead into registers;
+// each producer warp builds every fourth K block on its own.
 //
-// Warp roles: warp 0 TMA (activations), warp 1 MMA issuer + TMEM owner, warps 2..5 weight
-// producers during the main loop and epilogue afterwards.  Bounded waits, status word.
+// Warp roles: warp 0 TMA (activations), warp 1 MMA issuer + TMEM owner, warps 2..9 weight
+// producers (two per scheduler, so one covers the other's stalls); warps 2..5 run the epilogue.
+// When N / 64 column tiles would leave most SMs idle, K is split over blockIdx.y: fp32 partial
+// sums go to a workspace and a second kernel adds them (fixed order) and applies the bias.  Bounded waits, status word.
 #include "common.cuh"
 
 namespace b200 {
@@ -25,9 +28,8 @@ constexpr int BM = 128;
 constexpr int BN = 64;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int kThreads = 192;
-constexpr int kStages = 4;
-constexpr int kPrefetch = 8;
+constexpr int kMaxProdWarps = 8;
+constexpr int kThreads = 64 + 32 * kMaxProdWarps;
 
 struct Args {
   const uint8_t* qw;              // [N, K / 2] (low nibble = even k) or [N, K] for 8 bit
@@ -37,11 +39,22 @@ struct Args {
   __nv_bfloat16* C;
   long long ldc;
   int M, N, K, g;
+  int splits;                     // K split over blockIdx.y; > 1: fp32 partial sums to ws
+  float* ws;                      // [splits, M, N]
   unsigned int* status;
 };
 
+// The loop empty -> TMA load -> full -> MMA -> empty takes about 2 us; with S stages a K block
+// completes every 2 / S us, so the stages fill the shared memory (4 stages: 0.5 us per block).
+// Every stage belongs to exactly one producer warp (stages == producer warps, warp w builds
+// the K blocks w, w + stages, ...): a warp meets its stage's barrier phases in order, so the
+// parity waits cannot be overtaken.  (With stages shared between warps a fast warp could pass
+// a wait meant for a later phase and arrive twice on one barrier phase.)  Two activation
+// tiles per stage leave room for four stages, so only four warps produce then.
 template <int MT>
 struct Smem {
+  static constexpr int kStages = MT == 1 ? 8 : 4;
+  static constexpr int kProdWarps = kStages;
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = MT * kABytes + kBBytes;
@@ -53,6 +66,7 @@ template <int BITS, int MT>
 __global__ void __launch_bounds__(kThreads)
     gemm_wna16_kernel(const __grid_constant__ CUtensorMap tmA, const Args p) {
   using L = Smem<MT>;
+  constexpr int kStages = L::kStages;
   constexpr uint32_t kTmemCols = MT * BN <= 64 ? 64 : 128;
   constexpr uint32_t kIdesc = make_idesc(BM, BN, 1, 1);
   constexpr int kBytesPer = BITS == 4 ? 16 : 32;      // packed bytes of 32 weights
@@ -71,7 +85,7 @@ __global__ void __launch_bounds__(kThreads)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(&full_bar[s], 1 + 4);       // TMA thread (with the byte count) + 4 producer warps
+      mbar_init(&full_bar[s], 1 + 1);       // TMA thread (with the byte count) + one producer warp
       mbar_init(&empty_bar[s], 1);
     }
     mbar_init(tfull_bar, 1);
@@ -89,7 +103,11 @@ __global__ void __launch_bounds__(kThreads)
   const uint32_t tmem_base = *tmem_slot;
 
   const int n0 = blockIdx.x * BN;
-  const int num_kb = p.K / BK;
+  // this CTA's K blocks: [kb_lo, kb_lo + num_kb)
+  const int total_kb = p.K / BK;
+  const int kb_lo = static_cast<int>(static_cast<long long>(blockIdx.y) * total_kb / p.splits);
+  const int num_kb =
+      static_cast<int>(static_cast<long long>(blockIdx.y + 1) * total_kb / p.splits) - kb_lo;
 
   if (warp == 0) {
     if (elect_one()) {
@@ -103,7 +121,7 @@ __global__ void __launch_bounds__(kThreads)
         mbar_expect_tx(&full_bar[stage], MT * L::kABytes);
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
-          tma_load_2d(sa + mt * L::kABytes, &tmA, &full_bar[stage], kb * BK, mt * BM);
+          tma_load_2d(sa + mt * L::kABytes, &tmA, &full_bar[stage], (kb_lo + kb) * BK, mt * BM);
         if (++stage == kStages) {
           stage = 0;
           phase ^= 1u;
@@ -141,120 +159,145 @@ __global__ void __launch_bounds__(kThreads)
       if (ok) umma_commit(tfull_bar);
     }
   } else {
-    // ---------------- weight producers (warps 2..5), then epilogue ----------------
-    const int t = threadIdx.x - 64;          // 0..127
-    const int row = t >> 1;                  // weight row inside the tile
-    const int kh = t & 1;                    // which 32 of the 64 k of a block
-    const int n = n0 + row;
-    const bool n_ok = n < p.N;
+    // ---------------- weight producers (warps 2..9), then epilogue (warps 2..5) -----------
+    // Producer warp w owns the K blocks kb = w (mod 8) and builds the whole 64 x 64 tile of
+    // each: the proxy fence that has to follow the shared-memory stores costs a few hundred
+    // nanoseconds per thread, and with one warp per block the fences of consecutive
+    // blocks overlap instead of adding up.  Lane l holds rows l and l + 32.
+    constexpr int kProdWarps = L::kProdWarps;
+    const int pw = warp - 2;
     const int groups = p.K / p.g;
-    const uint8_t* qrow =
-        p.qw + static_cast<long long>(n_ok ? n : 0) * (BITS == 4 ? p.K / 2 : p.K) + kh * kBytesPer;
-    const __nv_bfloat16* srow = p.scales + static_cast<long long>(n_ok ? n : 0) * groups;
-    const __nv_bfloat16* zrow = p.zs + static_cast<long long>(n_ok ? n : 0) * groups;
-    // register ring of packed weights, kPrefetch K blocks ahead
-    // (scale and zero point travel with them: a dependent load per K block would put a
-    // memory latency on every step)
-    uint4 ring[kPrefetch][BITS == 4 ? 1 : 2];
-    __nv_bfloat16 ring_s[kPrefetch], ring_z[kPrefetch];
+    const int g_shift = 31 - __clz(p.g);             // the group size is a power of two
+    constexpr int kVec = BITS == 4 ? 2 : 4;          // uint4 per row and K block
+    constexpr int kDepth = 2;                        // own blocks prefetched ahead (= 16 K blocks)
+    const uint8_t* qrow[2];
+    const __nv_bfloat16* srow[2];
+    const __nv_bfloat16* zrow[2];
+    bool n_ok[2];
 #pragma unroll
-    for (int i = 0; i < kPrefetch; ++i) {
-      if (i < num_kb) {
-        const uint4* src = reinterpret_cast<const uint4*>(qrow + static_cast<long long>(i) * (2 * kBytesPer));
-        ring[i][0] = src[0];
-        if constexpr (BITS == 8) ring[i][1] = src[1];
-        const int grp = (i * BK + kh * 32) / p.g;
-        ring_s[i] = srow[grp];
-        ring_z[i] = zrow[grp];
-      }
+    for (int r = 0; r < 2; ++r) {
+      const int n = n0 + lane + 32 * r;
+      n_ok[r] = n < p.N;
+      const long long nn = n_ok[r] ? n : 0;
+      qrow[r] = p.qw + nn * (BITS == 4 ? p.K / 2 : p.K);
+      srow[r] = p.scales + nn * groups;
+      zrow[r] = p.zs + nn * groups;
     }
-    int stage = 0;
-    uint32_t phase = 0;
+    uint4 ring[kDepth][2][kVec];
+    __nv_bfloat16 ring_s[kDepth][2][2], ring_z[kDepth][2][2];
+    auto fetch = [&](int slot, int kb) {
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const uint4* src =
+            reinterpret_cast<const uint4*>(qrow[r]) + static_cast<long long>(kb_lo + kb) * kVec;
+#pragma unroll
+        for (int v = 0; v < kVec; ++v)
+          ring[slot][r][v] = src[v];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int grp = ((kb_lo + kb) * BK + h * 32) >> g_shift;
+          ring_s[slot][r][h] = srow[r][grp];
+          ring_z[slot][r][h] = zrow[r][grp];
+        }
+      }
+    };
+#pragma unroll
+    for (int d = 0; d < kDepth; ++d)
+      if (pw < kProdWarps && pw + kProdWarps * d < num_kb) fetch(d, pw + kProdWarps * d);
     bool ok = true;
-    for (int kb0 = 0; kb0 < num_kb && ok; kb0 += kPrefetch) {
+    for (int kb0 = pw; pw < kProdWarps && kb0 < num_kb && ok; kb0 += kProdWarps * kDepth) {
 #pragma unroll
-      for (int i = 0; i < kPrefetch; ++i) {
-        const int kb = kb0 + i;
+      for (int d = 0; d < kDepth; ++d) {
+        const int kb = kb0 + kProdWarps * d;
         if (kb >= num_kb || !ok) break;
-        uint4 cur[BITS == 4 ? 1 : 2];
-        cur[0] = ring[i][0];
-        if constexpr (BITS == 8) cur[1] = ring[i][1];
-        const float s = __bfloat162float(ring_s[i]);
-        const float z = __bfloat162float(ring_z[i]);
-        if (kb + kPrefetch < num_kb) {
-          const uint4* src = reinterpret_cast<const uint4*>(
-              qrow + static_cast<long long>(kb + kPrefetch) * (2 * kBytesPer));
-          ring[i][0] = src[0];
-          if constexpr (BITS == 8) ring[i][1] = src[1];
-          const int grp = ((kb + kPrefetch) * BK + kh * 32) / p.g;
-          ring_s[i] = srow[grp];
-          ring_z[i] = zrow[grp];
-        }
-        uint32_t w[16];
-        if constexpr (BITS == 4) {
-          // Two nibbles at a time as a bf16 pair: 0x4300 | q is the bf16 number 128 + q, the
-          // subtraction of 128 is exact, and one bf16 fused multiply-add gives q * s - zs with
-          // a single rounding (the stand-alone kernel rounds an fp32 result: equal except
-          // for double-rounding ties).  Nibble i of a word is element i, so the pairs come
-          // out as (0, 4), (1, 5), (2, 6), (3, 7) and two byte permutes per four restore
-          // the order.
-          const uint32_t pw[4] = {cur[0].x, cur[0].y, cur[0].z, cur[0].w};
-          const __nv_bfloat162 s2 = __float2bfloat162_rn(s);
-          const __nv_bfloat162 nz2 = __float2bfloat162_rn(-z);
-          const __nv_bfloat162 k128 = __float2bfloat162_rn(128.0f);
+        const int stage = kb % kStages;
+        const uint32_t phase = static_cast<uint32_t>(kb / kStages) & 1u;
+        uint32_t w[2][2][16];                      // [row][half of the block][16 bf16 pairs]
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint32_t tt[4];
+        for (int r = 0; r < 2; ++r) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const uint32_t bits = ((pw[j] >> (4 * e)) & 0x000F000Fu) | 0x43004300u;
-              __nv_bfloat162 q2 = *reinterpret_cast<const __nv_bfloat162*>(&bits);
-              q2 = __hfma2(__hsub2(q2, k128), s2, nz2);
-              tt[e] = *reinterpret_cast<const uint32_t*>(&q2);
+          for (int h = 0; h < 2; ++h) {
+            const float sc = __bfloat162float(ring_s[d][r][h]);
+            const float zz = __bfloat162float(ring_z[d][r][h]);
+            if constexpr (BITS == 4) {
+              // Two nibbles at a time as a bf16 pair: 0x4300 | q is the bf16 number 128 + q,
+              // the subtraction of 128 is exact, and one bf16 fused multiply-add gives
+              // q * s - zs with a single rounding (the stand-alone kernel rounds an fp32
+              // result: equal except for double-rounding ties).  Nibble i of a word is
+              // element i, so the pairs come out as (0, 4), (1, 5), (2, 6), (3, 7) and two
+              // byte permutes per four restore the order.
+              const uint4 c = ring[d][r][h];
+              const uint32_t pq[4] = {c.x, c.y, c.z, c.w};
+              const __nv_bfloat162 s2 = __float2bfloat162_rn(sc);
+              const __nv_bfloat162 nz2 = __float2bfloat162_rn(-zz);
+              const __nv_bfloat162 k128 = __float2bfloat162_rn(128.0f);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint32_t tt[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const uint32_t bits = ((pq[j] >> (4 * e)) & 0x000F000Fu) | 0x43004300u;
+                  __nv_bfloat162 q2 = *reinterpret_cast<const __nv_bfloat162*>(&bits);
+                  q2 = __hfma2(__hsub2(q2, k128), s2, nz2);
+                  tt[e] = *reinterpret_cast<const uint32_t*>(&q2);
+                }
+                w[r][h][j * 4 + 0] = __byte_perm(tt[0], tt[1], 0x5410);
+                w[r][h][j * 4 + 1] = __byte_perm(tt[2], tt[3], 0x5410);
+                w[r][h][j * 4 + 2] = __byte_perm(tt[0], tt[1], 0x7632);
+                w[r][h][j * 4 + 3] = __byte_perm(tt[2], tt[3], 0x7632);
+              }
+            } else {
+#pragma unroll
+              for (int v = 0; v < 2; ++v) {
+                const uint4 c = ring[d][r][h * 2 + v];
+                const uint32_t pq[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float f0 = static_cast<float>(pq[j] & 0xFFu) * sc - zz;
+                  const float f1 = static_cast<float>((pq[j] >> 8) & 0xFFu) * sc - zz;
+                  const float f2 = static_cast<float>((pq[j] >> 16) & 0xFFu) * sc - zz;
+                  const float f3 = static_cast<float>(pq[j] >> 24) * sc - zz;
+                  w[r][h][v * 8 + j * 2] = pack_bf16x2(f0, f1);
+                  w[r][h][v * 8 + j * 2 + 1] = pack_bf16x2(f2, f3);
+                }
+              }
             }
-            w[j * 4 + 0] = __byte_perm(tt[0], tt[1], 0x5410);
-            w[j * 4 + 1] = __byte_perm(tt[2], tt[3], 0x5410);
-            w[j * 4 + 2] = __byte_perm(tt[0], tt[1], 0x7632);
-            w[j * 4 + 3] = __byte_perm(tt[2], tt[3], 0x7632);
-          }
-        } else {
-          const uint8_t* pb = reinterpret_cast<const uint8_t*>(&cur[0]);
+            if (!n_ok[r]) {
 #pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            const float f0 = static_cast<float>(pb[2 * e]) * s - z;
-            const float f1 = static_cast<float>(pb[2 * e + 1]) * s - z;
-            w[e] = pack_bf16x2(f0, f1);
+              for (int e = 0; e < 16; ++e) w[r][h][e] = 0u;
+            }
           }
         }
-        if (!n_ok) {
-#pragma unroll
-          for (int e = 0; e < 16; ++e) w[e] = 0u;
-        }
+        if (kb + kProdWarps * kDepth < num_kb) fetch(d, kb + kProdWarps * kDepth);
         if (!mbar_wait(&empty_bar[stage], phase ^ 1u, p.status, kKernelId, 0x200u + stage,
                        abort_flag)) {
           ok = false;
           break;
         }
-        uint8_t* sb = smem + stage * L::kStageBytes + MT * L::kABytes + row * 128;
+        uint8_t* sb = smem + stage * L::kStageBytes + MT * L::kABytes;
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
-          *reinterpret_cast<uint4*>(sb + (((kh * 4 + c) ^ (row & 7)) << 4)) =
-              make_uint4(w[c * 4], w[c * 4 + 1], w[c * 4 + 2], w[c * 4 + 3]);
+        for (int r = 0; r < 2; ++r) {
+          const int row = lane + 32 * r;
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            *reinterpret_cast<uint4*>(sb + row * 128 + ((c ^ (row & 7)) << 4)) =
+                make_uint4(w[r][c >> 2][(c & 3) * 4], w[r][c >> 2][(c & 3) * 4 + 1],
+                           w[r][c >> 2][(c & 3) * 4 + 2], w[r][c >> 2][(c & 3) * 4 + 3]);
+        }
         fence_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(&full_bar[stage]);
-        if (++stage == kStages) {
-          stage = 0;
-          phase ^= 1u;
-        }
       }
     }
     // ---------------- epilogue ----------------
     const int q = warp & 3;
-    mbar_wait(tfull_bar, 0u, p.status, kKernelId, 0x400u, abort_flag);   // sets abort on timeout
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    const bool have = *abort_flag == 0u;
-    tc_fence_after();
+    bool have = false;
+    if (warp < 6) {
+      mbar_wait(tfull_bar, 0u, p.status, kKernelId, 0x400u, abort_flag);   // sets abort on timeout
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      have = *abort_flag == 0u;
+      tc_fence_after();
+    }
     if (have) {
 #pragma unroll 1
       for (int mt = 0; mt < MT; ++mt) {
@@ -268,6 +311,13 @@ __global__ void __launch_bounds__(kThreads)
           tmem_ld_wait();
           const int col = n0 + c * 32;
           if (r >= p.M || col >= p.N) continue;
+          if (p.splits > 1) {
+            float* wrow = p.ws + (static_cast<long long>(blockIdx.y) * p.M + r) * p.N + col;
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if (col + e < p.N) wrow[e] = __uint_as_float(acc[e]);
+            continue;
+          }
           __nv_bfloat16* crow = p.C + static_cast<long long>(r) * p.ldc + col;
           if (col + 32 <= p.N && (p.ldc & 7) == 0) {
 #pragma unroll
@@ -305,6 +355,30 @@ __global__ void __launch_bounds__(kThreads)
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
 }
 
+// C[r, c] = sum over splits of ws[s, r, c] (+ bias[c]), summed in split order.
+__global__ void __launch_bounds__(256)
+    wna16_reduce_kernel(const float* ws, const __nv_bfloat16* bias, __nv_bfloat16* C, long long ldc,
+                        int M, int N, int splits) {
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<long long>(M) * N) return;
+  const int r = static_cast<int>(idx / N), c = static_cast<int>(idx % N);
+  float acc = 0.0f;
+  for (int s = 0; s < splits; ++s) acc += ws[(static_cast<long long>(s) * M + r) * N + c];
+  if (bias != nullptr) acc += __bfloat162float(bias[c]);
+  C[static_cast<long long>(r) * ldc + c] = __float2bfloat16(acc);
+}
+
+// K splits that bring the grid to about one CTA per SM (every split keeps >= 16 K blocks).
+static int plan_splits(int N, int K) {
+  const int tiles = (N + BN - 1) / BN;
+  const int sms = sm_count() > 0 ? sm_count() : 148;
+  int splits = sms / tiles;
+  const int cap = (K / BK) / 16;
+  if (splits > cap) splits = cap;
+  if (splits > 8) splits = 8;
+  return splits < 1 ? 1 : splits;
+}
+
 template <int BITS, int MT>
 static int launch(const CUtensorMap& tmA, const Args& a, cudaStream_t s) {
   using L = Smem<MT>;
@@ -317,7 +391,13 @@ static int launch(const CUtensorMap& tmA, const Args& a, cudaStream_t s) {
     if (e != cudaSuccess) return static_cast<int>(e);
     configured[dev] = true;
   }
-  kern<<<(a.N + BN - 1) / BN, kThreads, L::kTotal, s>>>(tmA, a);
+  dim3 grid((a.N + BN - 1) / BN, a.splits);
+  kern<<<grid, kThreads, L::kTotal, s>>>(tmA, a);
+  int e = static_cast<int>(cudaGetLastError());
+  if (e != 0 || a.splits == 1) return e;
+  const long long total = static_cast<long long>(a.M) * a.N;
+  wna16_reduce_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, s>>>(
+      a.ws, a.bias, a.C, a.ldc, a.M, a.N, a.splits);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -326,14 +406,22 @@ static int launch(const CUtensorMap& tmA, const Args& a, cudaStream_t s) {
 
 // A [M, K] bf16 (row pitch lda), qw / scales / zs as described above, C [M, N] bf16.
 // Returns -20 when the shape is outside what the kernel covers (M > 256, K % 64, group size
-// not a multiple of 32, misaligned pointers): callers de-quantise and use the bf16 GEMM.
+// not a power of two >= 32, misaligned pointers): callers de-quantise and use the bf16 GEMM.
+// Floats of workspace b200_gemm_wna16 wants for this shape (0: no K split).
+B200_API long long b200_gemm_wna16_workspace(int M, int N, int K) {
+  if (M <= 0 || N <= 0 || K <= 0 || (K % b200::wna16::BK) != 0) return 0;
+  const int splits = b200::wna16::plan_splits(N, K);
+  return splits > 1 ? static_cast<long long>(splits) * M * N : 0;
+}
+
+// `ws` may be null: then K is not split.
 B200_API int b200_gemm_wna16(const void* A, long long lda, const void* qw, const void* scales,
                              const void* zs, const void* bias, void* C, long long ldc, int M,
-                             int N, int K, int g, int bits, void* stream) {
+                             int N, int K, int g, int bits, float* ws, void* stream) {
   using namespace b200;
   using namespace b200::wna16;
   if (M <= 0 || N <= 0) return 0;
-  if (M > 2 * BM || K <= 0 || (K % BK) != 0 || g <= 0 || (g % 32) != 0 || (K % g) != 0 ||
+  if (M > 2 * BM || K <= 0 || (K % BK) != 0 || g < 32 || (g & (g - 1)) != 0 || (K % g) != 0 ||
       (bits != 4 && bits != 8) || (lda % 8) != 0 ||
       ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(qw)) & 15))
     return -20;
@@ -349,6 +437,9 @@ B200_API int b200_gemm_wna16(const void* A, long long lda, const void* qw, const
   a.bias = static_cast<const __nv_bfloat16*>(bias);
   a.C = static_cast<__nv_bfloat16*>(C);
   a.ldc = ldc; a.M = M; a.N = N; a.K = K; a.g = g;
+  a.splits = ws != nullptr ? plan_splits(N, K) : 1;
+  a.ws = ws;
+
   a.status = status_ptr();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool two = M > BM;

@@ -504,9 +504,11 @@ def gemm_wna16(x: torch.Tensor, qw: torch.Tensor, scales: torch.Tensor, zs: torc
             or x.stride(1) != 1):
         return None
     out = torch.empty((M, Nn), dtype=x.dtype, device=x.device)
+    nws = int(N.lib().b200_gemm_wna16_workspace(M, Nn, K))
+    ws = torch.empty(nws, dtype=torch.float32, device=x.device) if nws > 0 else None
     rc = N.lib().b200_gemm_wna16(ptr(x), x.stride(0), ptr(qw), ptr(scales), ptr(zs), ptr(bias),
                                  ptr(out), out.stride(0), M, Nn, K, int(group), int(bits),
-                                 stream_ptr())
+                                 ptr(ws), stream_ptr())
     N.launch_count += 1
     if rc == -20:
         return None
