@@ -131,3 +131,90 @@ def test_qwen3_moe_engine_gpu_vs_cpu():
     lg, lc = gpu.engine.runner.last_logits, cpu.engine.runner.last_logits
     err = (lg - lc).abs().max().item()
     assert err < 0.08 * lc.std().item() + 0.03, (err, lc.std().item())
+
+
+def _block_quant_fp8(w):
+    """[..., N, K] float -> (fp8 codes, scales [..., N/128, K/128]) with one scale per block."""
+    *lead, N, K = w.shape
+    b = w.float().reshape(*lead, N // 128, 128, K // 128, 128)
+    amax = b.abs().amax(dim=(-3, -1), keepdim=True).clamp_min(1e-8)
+    s = amax / 448.0
+    q = (b / s).to(torch.float8_e4m3fn)
+    return q.reshape(*lead, N, K), s.reshape(*lead, N // 128, K // 128)
+
+
+@pytest.mark.parametrize("T,E,k", [(7, 4, 2), (300, 8, 2), (64, 16, 4)])
+def test_fused_experts_fp8_block_matches_dequantised_reference(T, E, k):
+    """Grouped fp8 GEMMs with 128 x 128 weight scales and 1 x 128 activation scales against
+    the fp32 reference on the de-quantised weights (activation quantisation is the only
+    difference: a few percent of the output scale)."""
+    from vllm_gcu_b200.ops import _native, ref
+    from vllm_gcu_b200.ops import cuda as C
+    torch.manual_seed(T)
+    dev = "cuda"
+    H, I = 256, 384
+    w13 = torch.randn(E, 2 * I, H, device=dev) * 0.05
+    w2 = torch.randn(E, H, I, device=dev) * 0.05
+    q13, s13 = _block_quant_fp8(w13)
+    q2, s2 = _block_quant_fp8(w2)
+    x = (torch.randn(T, H, device=dev) * 0.5).to(torch.bfloat16)
+    logits = torch.randn(T, E, device=dev)
+    tw, ti = torch.topk(torch.softmax(logits, -1), k, dim=-1)
+    ti = ti.to(torch.int32)
+    add = (torch.randn(T, H, device=dev) * 0.1).to(torch.bfloat16)
+    got = C.fused_experts_fp8(x, q13.contiguous(), s13.contiguous(), q2.contiguous(),
+                              s2.contiguous(), tw.float(), ti, add=add)
+    torch.cuda.synchronize()
+    _native.check_status()
+    d13 = (q13.float().reshape(E, 2 * I // 128, 128, H // 128, 128)
+           * s13[:, :, None, :, None]).reshape(E, 2 * I, H)
+    d2 = (q2.float().reshape(E, H // 128, 128, I // 128, 128)
+          * s2[:, :, None, :, None]).reshape(E, H, I)
+    want = ref.fused_experts(x.float(), d13, d2, tw.float(), ti).float() + add.float()
+    err = (got.float() - want).abs().max().item()
+    scale = (want - add.float()).abs().max().item()
+    assert err < 0.06 * scale + 0.02, (err, scale)
+    # expert map (expert parallel rank owning the upper half): other experts contribute nothing
+    emap = torch.full((E,), -1, dtype=torch.int32, device=dev)
+    emap[E // 2:] = torch.arange(E - E // 2, dtype=torch.int32, device=dev)
+    got_h = C.fused_experts_fp8(x, q13[E // 2:].contiguous(), s13[E // 2:].contiguous(),
+                                q2[E // 2:].contiguous(), s2[E // 2:].contiguous(), tw.float(),
+                                ti, expert_map=emap)
+    want_h = ref.fused_experts(x.float(), d13[E // 2:], d2[E // 2:], tw.float(), ti, emap).float()
+    torch.cuda.synchronize()
+    _native.check_status()
+    err = (got_h.float() - want_h).abs().max().item()
+    assert err < 0.06 * want_h.abs().max().item() + 0.02, err
+
+
+def test_fp8_block_experts_stay_quantised_through_loader_and_engine():
+    """A Qwen3-MoE-shaped model declared as fp8 with 128 x 128 blocks keeps its experts in
+    fp8 (loader path of quantised checkpoints) and generates through the grouped fp8 GEMMs."""
+    from vllm_gcu_b200.engine.llm import LLM
+    from vllm_gcu_b200.engine.request import SamplingParams
+    from vllm_gcu_b200.layers.quant.moe import QuantExpertLoader
+    llm = LLM("tiny-qwen3-moe", device="cuda", hidden_size=256, intermediate_size=512,
+              num_attention_heads=4, num_key_value_heads=2, head_dim=64, num_experts=8,
+              num_experts_per_tok=2, moe_intermediate_size=128, dtype="bfloat16",
+              quantization="fp8", quant_config={"quant_method": "fp8",
+                                                "weight_block_size": [128, 128]},
+              max_num_seqs=4, max_num_batched_tokens=64, max_model_len=128, num_gpu_blocks=64,
+              cuda_graph_sizes=[4])
+    moe = llm.engine.model.layers["0"].mlp.experts
+    assert moe.fp8_block and moe.w13.dtype == torch.float8_e4m3fn
+    # loader: an fp8 projection with its block scale lands in the fp8 tables untouched
+    w = (torch.randn(128, 256, device="cuda")).to(torch.float8_e4m3fn)
+    sc = torch.rand(1, 2, device="cuda") + 0.5
+    ld = QuantExpertLoader("fp8", {"quant_method": "fp8", "weight_block_size": [128, 128]},
+                           torch.bfloat16)
+    ld.add(moe, "model.layers.0.", 3, "gate", "weight", w)
+    ld.add(moe, "model.layers.0.", 3, "gate", "weight_scale_inv", sc)
+    assert torch.equal(moe.w13.data[3, :128].view(torch.uint8), w.view(torch.uint8))
+    assert torch.equal(moe.w13_scale.data[3, :1], sc)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (20, 9, 33)]
+    n0 = _native.launch_count
+    outs = llm.generate(prompts, SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True))
+    torch.cuda.synchronize()
+    _native.check_status()
+    assert _native.launch_count > n0 and all(len(o.outputs[0].token_ids) == 5 for o in outs)

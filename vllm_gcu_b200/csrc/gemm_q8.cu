@@ -44,8 +44,23 @@ struct Args {
   long long lds_a, lds_b;
   int M, N, K;
   int tiles_m, tiles_n;
+  // grouped (mixture-of-experts) mode: A rows are sorted by expert in tiles of BM rows,
+  // expert_ids[tile_m] names the weight matrix of a row tile (-1 or a tile at / past
+  // *num_post_pad: nothing to do), B holds the experts' [N, K] matrices one after the other,
+  // b_scale their scale tables, row_scale an optional per-row factor (routing weight)
+  const int* expert_ids;
+  const int* num_post_pad;
+  const float* row_scale;
   unsigned int* status;
 };
+
+// Expert of a row tile, or -1 when the tile has no work.  Every role of the CTA evaluates it
+// on the same data, so they skip the same tiles.
+__device__ __forceinline__ int tile_expert(const Args& p, int m0) {
+  if (p.expert_ids == nullptr) return 0;
+  if (m0 >= *p.num_post_pad) return -1;
+  return p.expert_ids[m0 / BM];
+}
 
 template <bool INT8>
 __device__ __forceinline__ void mma8(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc,
@@ -105,6 +120,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         const int m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN;
+        const int expert = tile_expert(p, m0);
+        if (expert < 0) continue;
+        const int b_row = expert * p.N + n0;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, p.status, kKernelId, 0x100u + stage,
                          abort_flag)) {
@@ -114,7 +132,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           uint8_t* sa = smem + stage * kStageBytes;
           mbar_expect_tx(&full_bar[stage], kStageBytes);
           tma_load_2d(sa, &tmA, &full_bar[stage], kb * BK, m0);
-          tma_load_2d(sa + kABytes, &tmB, &full_bar[stage], kb * BK, n0);
+          tma_load_2d(sa + kABytes, &tmB, &full_bar[stage], kb * BK, b_row);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -128,6 +146,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        if (tile_expert(p, (tile % p.tiles_m) * BM) < 0) continue;
         if constexpr (MODE == kRowCol) {
           if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, p.status, kKernelId, 0x200u + acc,
                          abort_flag))
@@ -183,8 +202,11 @@ __global__ void __launch_bounds__(kThreads, 1)
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
       const int m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN;
+      const int expert = tile_expert(p, m0);
+      if (expert < 0) continue;
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
+      const float rs = (p.row_scale != nullptr && row_ok) ? p.row_scale[row] : 1.0f;
       const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
       __nv_bfloat16* crow = p.C + static_cast<long long>(row) * p.ldc;
 
@@ -192,7 +214,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (!mbar_wait(&tfull_bar[acc], acc_phase, p.status, kKernelId, 0x400u + acc, abort_flag))
           break;
         tc_fence_after();
-        const float sa = row_ok ? p.a_scale[row] : 0.0f;
+        const float sa = row_ok ? p.a_scale[row] * rs : 0.0f;
+        const float* b_scale = p.b_scale + static_cast<long long>(expert) * p.N;
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t r[32];
@@ -209,7 +232,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             v[i] = a * sa;
           }
           for (int i = 0; i < ncols; ++i) {
-            v[i] *= p.b_scale[col + i];
+            v[i] *= b_scale[col + i];
             if (p.bias != nullptr) v[i] += __bfloat162float(p.bias[col + i]);
           }
           if (ncols == 32) {
@@ -237,7 +260,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
         for (int i = 0; i < BN; ++i) accum[i] = 0.0f;
         const float* sa_row = p.a_scale + static_cast<long long>(row_ok ? row : 0) * p.lds_a;
-        const float* sb_row = p.b_scale + static_cast<long long>(n0 / 128) * p.lds_b;
+        const float* sb_row =
+            p.b_scale + (static_cast<long long>(expert) * ((p.N + 127) / 128) + n0 / 128) * p.lds_b;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&tfull_bar[acc], acc_phase, p.status, kKernelId, 0x400u + acc,
                          abort_flag)) {
@@ -269,7 +293,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             float v[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-              v[i] = accum[c * 8 + i];
+              v[i] = accum[c * 8 + i] * rs;
               if (p.bias != nullptr && col + i < p.N) v[i] += __bfloat162float(p.bias[col + i]);
             }
             if (col + 8 <= p.N) {
@@ -348,6 +372,56 @@ B200_API int b200_gemm_q8(const void* A, long long lda, const void* B, long long
   a.M = M; a.N = N; a.K = K;
   a.tiles_m = (M + BM - 1) / BM;
   a.tiles_n = (N + BN - 1) / BN;
+  a.expert_ids = nullptr; a.num_post_pad = nullptr; a.row_scale = nullptr;
+  a.status = status_ptr();
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (kind == 0) return launch<false, kRowCol>(tmA, tmB, a, s);
+  if (kind == 1) return launch<false, kBlock128>(tmA, tmB, a, s);
+  if (kind == 2) return launch<true, kRowCol>(tmA, tmB, a, s);
+  return -7;
+}
+
+// Grouped (mixture-of-experts) form of b200_gemm_q8: A [M_cap, K] holds the token rows sorted
+// by expert in tiles of 128 rows (b200_moe_align), B [E * N, K] the experts' weights, b_scale
+// [E, N] (kind 0 / 2) or [E, ceil(N / 128), K / 128] (kind 1), row_scale an optional
+// per-row factor applied to the output.  Tiles whose expert id is negative or that start at
+// or past *num_post_pad are skipped.  Replaces the quantised branches of the reference's
+// fused_moe_kernel / fused_moe_quant_kernel (csrc/torch_bindings.cpp:118-178).
+B200_API int b200_gemm_q8_grouped(const void* A, long long lda, const void* B, long long ldb,
+                                  void* C, long long ldc, int M_cap, int N, int K, int E,
+                                  const float* a_scale, long long lds_a, const float* b_scale,
+                                  long long lds_b, const int* expert_ids,
+                                  const int* num_post_pad, const float* row_scale, int kind,
+                                  void* stream) {
+  using namespace b200;
+  using namespace b200::gemm8;
+  if (M_cap <= 0 || N <= 0 || E <= 0) return 0;
+  if (K <= 0 || (K % 16) != 0 || (lda % 16) != 0 || (ldb % 16) != 0 || (N % 8) != 0 ||
+      (ldc % 8) != 0 || (M_cap % BM) != 0 || a_scale == nullptr || b_scale == nullptr ||
+      expert_ids == nullptr || num_post_pad == nullptr)
+    return -2;
+  if (kind == 1 && (K % 128) != 0) return -2;
+  CUtensorMap tmA, tmB;
+  int r = encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, static_cast<uint64_t>(M_cap),
+                         static_cast<uint64_t>(K), static_cast<uint64_t>(lda), BM, BK,
+                         CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r != 0) return r < 0 ? -6 : r;
+  r = encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B,
+                     static_cast<uint64_t>(E) * static_cast<uint64_t>(N), static_cast<uint64_t>(K),
+                     static_cast<uint64_t>(ldb), BN, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r != 0) return r < 0 ? -6 : r;
+  Args a;
+  a.C = static_cast<__nv_bfloat16*>(C);
+  a.ldc = ldc;
+  a.a_scale = a_scale;
+  a.b_scale = b_scale;
+  a.bias = nullptr;
+  a.lds_a = lds_a;
+  a.lds_b = lds_b;
+  a.M = M_cap; a.N = N; a.K = K;
+  a.tiles_m = M_cap / BM;
+  a.tiles_n = (N + BN - 1) / BN;
+  a.expert_ids = expert_ids; a.num_post_pad = num_post_pad; a.row_scale = row_scale;
   a.status = status_ptr();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (kind == 0) return launch<false, kRowCol>(tmA, tmB, a, s);

@@ -98,6 +98,48 @@ class FusedMoE(nn.Module):
                                requires_grad=False)
         self.prefix = prefix
         self._interleaved = False
+        self.fp8_block = False
+
+    def enable_fp8_block(self) -> bool:
+        """Keeps the experts as fp8 e4m3 with 128 x 128 block scales (the layout of DeepSeek-V3
+        checkpoints, vllm_gcu/kernels/quantization/fp8.py:248-420 serves them through
+        ``fused_moe_quant_kernel``) instead of de-quantising them at load: half the memory of
+        bf16 and fp8 tensor-core GEMMs.  Returns False when the shapes do not allow it."""
+        E, I, H = self.local_experts, self.inter, self.hidden
+        if I % 128 != 0 or H % 128 != 0 or not self.w13.is_cuda:
+            return False
+        dev = self.w13.device
+        f8 = torch.float8_e4m3fn
+        self.w13 = nn.Parameter(torch.zeros(E, 2 * I, H, dtype=f8, device=dev), requires_grad=False)
+        self.w2 = nn.Parameter(torch.zeros(E, H, I, dtype=f8, device=dev), requires_grad=False)
+        self.w13_scale = nn.Parameter(torch.ones(E, 2 * I // 128, H // 128, dtype=torch.float32,
+                                                 device=dev), requires_grad=False)
+        self.w2_scale = nn.Parameter(torch.ones(E, H // 128, I // 128, dtype=torch.float32,
+                                                device=dev), requires_grad=False)
+        self.fp8_block = True
+        return True
+
+    def load_expert_weight_fp8(self, expert_id: int, which: str, weight: torch.Tensor,
+                               scale: torch.Tensor) -> bool:
+        """fp8 ``weight [N, K]`` with its ``scale [N/128, K/128]`` (``weight_scale_inv``)."""
+        le = expert_id - self.expert_start
+        if le < 0 or le >= self.local_experts:
+            return False
+        I = self.inter
+        lo = 0 if (self.use_ep or tp_size() == 1) else tp_rank() * I
+        b0, nb = lo // 128, I // 128
+        if which == "gate":
+            self.w13.data[le, :I].copy_(weight[lo:lo + I])
+            self.w13_scale.data[le, :nb].copy_(scale[b0:b0 + nb])
+        elif which == "up":
+            self.w13.data[le, I:].copy_(weight[lo:lo + I])
+            self.w13_scale.data[le, nb:].copy_(scale[b0:b0 + nb])
+        elif which == "down":
+            self.w2.data[le].copy_(weight[:, lo:lo + I])
+            self.w2_scale.data[le].copy_(scale[:, b0:b0 + nb])
+        else:
+            raise ValueError(which)
+        return True
 
     # -- weights -------------------------------------------------------------------
     def load_expert_weight(self, expert_id: int, which: str, full: torch.Tensor) -> bool:
@@ -145,6 +187,10 @@ class FusedMoE(nn.Module):
         past it produce unspecified output."""
         if x.shape[0] == 0:
             return x if add is None else add
+        if self.fp8_block:
+            return C.fused_experts_fp8(x, self.w13, self.w13_scale, self.w2, self.w2_scale,
+                                       topk_w, topk_ids, self.expert_map, add=add, alpha=alpha,
+                                       valid_tokens=valid_tokens)
         if self._interleaved and ops.use_native(x):
             return C.fused_experts(x, self.w13, self.w2, topk_w, topk_ids, self.expert_map,
                                    add=add, alpha=alpha, valid_tokens=valid_tokens)
@@ -221,6 +267,10 @@ class SparseMoeBlock(nn.Module):
         num_red = int(cfg.extra.get("num_redundant_experts", 0))
         self.experts = FusedMoE(cfg.num_experts, cfg.hidden_size, cfg.moe_intermediate_size,
                                 cfg.dtype, device, self.use_ep, prefix + ".experts", num_red)
+        qc = cfg.quant_config or {}
+        if (cfg.quantization == "fp8" and list(qc.get("weight_block_size") or []) == [128, 128]
+                and cfg.dtype == torch.bfloat16 and cfg.extra.get("fp8_experts", True)):
+            self.experts.enable_fp8_block()
         self.eplb = EplbState(cfg.num_experts, num_red, device) if num_red > 0 else None
         if cfg.num_shared_experts > 0:
             from ..models.decoder import DenseMLP

@@ -117,6 +117,12 @@ class QuantExpertLoader:
             sc = d.get("weight_scale_inv", d.get("weight_scale", d.get("out_scales")))
             if sc is None and not d.get("_flushed"):
                 return
+            if (self.kind == "fp8" and getattr(moe, "fp8_block", False) and sc is not None
+                    and sc.dim() == 2 and d["weight"].dtype == torch.float8_e4m3fn):
+                # the experts stay fp8 with their block scales (grouped fp8 GEMM path)
+                moe.load_expert_weight_fp8(expert, which, d["weight"], sc.to(torch.float32))
+                del self.pending[key]
+                return
             w = (dequant_fp8(d["weight"], sc, self.block, self.dtype) if self.kind == "fp8"
                  else dequant_int8(d["weight"], sc, self.dtype))
             del self.pending[key]

@@ -328,10 +328,18 @@ class DecoderLM(nn.Module):
         the benchmarks); norm weights are one, biases zero."""
         gen_dev = self.device
         for name, p in sorted(self.named_parameters()):
-            if p.dtype not in (torch.float32, torch.bfloat16, torch.float16):
-                continue
             g = torch.Generator(device=gen_dev)
             g.manual_seed(zlib.crc32(name.encode()) ^ seed)
+            if p.dtype == torch.float8_e4m3fn:       # fp8 experts: unit-variance codes ...
+                chunk = torch.empty(p.shape, dtype=torch.float32, device=gen_dev)
+                chunk.normal_(0.0, 1.0, generator=g)
+                p.data.copy_(chunk.to(p.dtype))
+                continue
+            if name.endswith("_scale") and p.dtype == torch.float32:
+                p.data.fill_(std)                    # ... times a block scale of std
+                continue
+            if p.dtype not in (torch.float32, torch.bfloat16, torch.float16):
+                continue
             if name.endswith("norm.weight") or ".q_norm." in name or ".k_norm." in name \
                     or name.endswith("layernorm.weight"):
                 p.data.fill_(1.0)

@@ -79,6 +79,8 @@ def mla_decode_batched(q_full: torch.Tensor, cache: torch.Tensor, block_tables: 
     mask = pos[None, :] < seq_lens[:, None]
     slots = torch.where(mask, slots, torch.zeros_like(slots))
     kv = cache.view(nb * bs, W)[slots]                         # [B, max_len, W]
+    if kv.dtype != q_full.dtype:                               # fp8 latent cache (scale 1)
+        kv = kv.to(q_full.dtype)
     s = torch.bmm(q_full, kv.transpose(1, 2)).float() * scale  # [B, N, max_len]
     s = s.masked_fill(~mask[:, None, :], float("-inf"))
     p = torch.softmax(s, dim=-1).to(q_full.dtype)

@@ -122,6 +122,7 @@ class _Sigs:
     b200_gemm_wide2 = [P, L, P, L, P, L, I, I, I, P, I, P]
     b200_gemm_skinny_plan = [I, I, I, I, P, P]
     b200_gemm_q8 = [P, L, P, L, P, L, I, I, I, P, L, P, L, P, I, P]
+    b200_gemm_q8_grouped = [P, L, P, L, P, L, I, I, I, I, P, L, P, L, P, P, P, I, P]
     b200_per_token_quant = [P, L, P, L, P, P, I, I, I, I, P]
     b200_per_tensor_fp8_quant = [P, P, L, P, P, I, P]
     b200_int8_dequant = [P, P, L, P, P, I, P]

@@ -693,6 +693,59 @@ def fused_experts(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_w: 
     return out
 
 
+def gemm_q8_grouped(a: torch.Tensor, a_scale: torch.Tensor, w: torch.Tensor,
+                    w_scale: torch.Tensor, expert_ids: torch.Tensor, npp: torch.Tensor,
+                    kind: int = 1, row_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Grouped 8-bit GEMM: ``a [cap, K]`` rows sorted by expert in tiles of 128,
+    ``w [E, N, K]``; scales as in :func:`gemm_q8` with a leading expert dimension on
+    ``w_scale``.  Returns bf16 ``[cap, N]`` (rows of skipped tiles are not written)."""
+    cap, K = a.shape
+    E, Nn, _ = w.shape
+    assert w.is_contiguous() and a.stride(1) == 1 and a.element_size() == 1
+    out = torch.empty((cap, Nn), device=a.device, dtype=torch.bfloat16)
+    a_scale = a_scale.contiguous()
+    w_scale = w_scale.contiguous()
+    lds_a = a_scale.stride(0) if kind == 1 else 1
+    lds_b = w_scale.stride(-2) if kind == 1 else 1
+    call("b200_gemm_q8_grouped", ptr(a), a.stride(0), ptr(w), K, ptr(out), out.stride(0), cap, Nn,
+         K, E, ptr(a_scale), lds_a, ptr(w_scale), lds_b, ptr(expert_ids), ptr(npp),
+         ptr(row_scale), kind, stream_ptr())
+    return out
+
+
+def fused_experts_fp8(x: torch.Tensor, w13: torch.Tensor, w13_scale: torch.Tensor,
+                      w2: torch.Tensor, w2_scale: torch.Tensor, topk_w: torch.Tensor,
+                      topk_ids: torch.Tensor, expert_map: Optional[torch.Tensor] = None,
+                      add: Optional[torch.Tensor] = None, alpha: float = 1.0,
+                      valid_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Routed-expert MLP with fp8 e4m3 expert weights and 128 x 128 block scales
+    (DeepSeek-V3 checkpoints): align -> permute -> 1 x 128 activation quantisation ->
+    grouped fp8 GEMM1 -> SiLU-mul + quantisation -> grouped fp8 GEMM2 scaled by the routing
+    weight -> un-permute + sum.  ``w13 [E, 2I, H]`` gate rows first, ``w13_scale
+    [E, 2I/128, H/128]``, ``w2 [E, H, I]``, ``w2_scale [E, H/128, I/128]``."""
+    T, H = x.shape
+    k = topk_ids.shape[1]
+    E = w13.shape[0]
+    numel = T * k
+    cap = moe_align_cap(numel, E)
+    sorted_ids, expert_ids, npp, pos_of = moe_align(topk_ids, E, cap, expert_map, valid_tokens)
+    a_sorted = torch.empty((cap, H), device=x.device, dtype=x.dtype)
+    call("b200_moe_permute", ptr(x), x.stride(0), ptr(a_sorted), H, ptr(sorted_ids), ptr(npp),
+         numel, k, H, cap, DTYPE_CODE[x.dtype], stream_ptr())
+    row_w = torch.empty(cap, device=x.device, dtype=torch.float32)
+    call("b200_moe_row_weights", ptr(sorted_ids), ptr(topk_w), ptr(npp), ptr(row_w), numel, cap,
+         stream_ptr())
+    aq, a_s = activation(a_sorted, "identity", "plain", quant="fp8_group128", valid_rows=npp)
+    h = gemm_q8_grouped(aq, a_s, w13, w13_scale, expert_ids, npp, kind=1)
+    hq, h_s = activation(h, "silu", "act_mul", quant="fp8_group128", valid_rows=npp)
+    y = gemm_q8_grouped(hq, h_s, w2, w2_scale, expert_ids, npp, kind=1, row_scale=row_w)
+    out = torch.empty((T, H), device=x.device, dtype=x.dtype)
+    call("b200_moe_unpermute_sum", ptr(y), y.stride(0), ptr(pos_of), ptr(add),
+         add.stride(0) if add is not None else 0, ptr(out), H, ptr(valid_tokens), T, k, H,
+         float(alpha), DTYPE_CODE[x.dtype], stream_ptr())
+    return out
+
+
 def get_ep_indices(topk_ids: torch.Tensor, experts_per_rank: int, ep: int):
     T, k = topk_ids.shape
     dev = topk_ids.device
