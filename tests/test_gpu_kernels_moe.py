@@ -218,3 +218,36 @@ def test_fp8_block_experts_stay_quantised_through_loader_and_engine():
     torch.cuda.synchronize()
     _native.check_status()
     assert _native.launch_count > n0 and all(len(o.outputs[0].token_ids) == 5 for o in outs)
+
+
+@pytest.mark.parametrize("dtype", [torch.int8, torch.float8_e4m3fn])
+def test_fused_experts_q8_channel_matches_dequantised_reference(dtype):
+    """int8 / fp8 experts with per-channel scales and per-token activation quantisation
+    (w8a8 checkpoints) against the fp32 reference on the de-quantised weights."""
+    from vllm_gcu_b200.ops import cuda as C
+    torch.manual_seed(11)
+    dev = "cuda"
+    T, E, k, H, I = 150, 8, 2, 256, 192
+    w13 = torch.randn(E, 2 * I, H, device=dev) * 0.05
+    w2 = torch.randn(E, H, I, device=dev) * 0.05
+    qmax = 127.0 if dtype == torch.int8 else 448.0
+
+    def quant(w):
+        s = w.abs().amax(-1).clamp_min(1e-8) / qmax
+        q = w / s[..., None]
+        q = torch.round(q).clamp(-128, 127).to(torch.int8) if dtype == torch.int8 else q.to(dtype)
+        return q.contiguous(), s.float().contiguous()
+
+    q13, s13 = quant(w13)
+    q2, s2 = quant(w2)
+    x = (torch.randn(T, H, device=dev) * 0.5).to(torch.bfloat16)
+    tw, ti = torch.topk(torch.softmax(torch.randn(T, E, device=dev), -1), k, dim=-1)
+    ti = ti.to(torch.int32)
+    got = C.fused_experts_q8(x, q13, s13, q2, s2, tw.float(), ti)
+    torch.cuda.synchronize()
+    _native.check_status()
+    want = ref.fused_experts(x.float(), q13.float() * s13[..., None], q2.float() * s2[..., None],
+                             tw.float(), ti).float()
+    err = (got.float() - want).abs().max().item()
+    tol = (0.03 if dtype == torch.int8 else 0.08) * want.abs().max().item() + 0.02
+    assert err < tol, (err, want.abs().max().item())

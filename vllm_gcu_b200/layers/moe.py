@@ -99,6 +99,7 @@ class FusedMoE(nn.Module):
         self.prefix = prefix
         self._interleaved = False
         self.fp8_block = False
+        self.q8_channel = False
 
     def enable_fp8_block(self) -> bool:
         """Keeps the experts as fp8 e4m3 with 128 x 128 block scales (the layout of DeepSeek-V3
@@ -117,6 +118,50 @@ class FusedMoE(nn.Module):
         self.w2_scale = nn.Parameter(torch.ones(E, H // 128, I // 128, dtype=torch.float32,
                                                 device=dev), requires_grad=False)
         self.fp8_block = True
+        return True
+
+    def enable_q8_channel(self, dtype: torch.dtype) -> bool:
+        """Keeps the experts as int8 or fp8 with one scale per output channel (w8a8
+        checkpoints, vllm_gcu/kernels/quantization/w8a8.py:174-342); activations are
+        quantised per token in front of each grouped GEMM."""
+        E, I, H = self.local_experts, self.inter, self.hidden
+        if I % 16 != 0 or H % 16 != 0 or not self.w13.is_cuda:
+            return False
+        dev = self.w13.device
+        self.w13 = nn.Parameter(torch.zeros(E, 2 * I, H, dtype=dtype, device=dev),
+                                requires_grad=False)
+        self.w2 = nn.Parameter(torch.zeros(E, H, I, dtype=dtype, device=dev), requires_grad=False)
+        self.w13_scale = nn.Parameter(torch.ones(E, 2 * I, dtype=torch.float32, device=dev),
+                                      requires_grad=False)
+        self.w2_scale = nn.Parameter(torch.ones(E, H, dtype=torch.float32, device=dev),
+                                     requires_grad=False)
+        self.q8_channel = True
+        return True
+
+    def load_expert_weight_q8(self, expert_id: int, which: str, weight: torch.Tensor,
+                              scale: Optional[torch.Tensor]) -> bool:
+        """8-bit ``weight [N, K]`` with a per-tensor or per-channel ``scale`` (None: 1)."""
+        le = expert_id - self.expert_start
+        if le < 0 or le >= self.local_experts:
+            return False
+        I = self.inter
+        lo = 0 if (self.use_ep or tp_size() == 1) else tp_rank() * I
+        N = weight.shape[0]
+        sc = torch.ones(N, dtype=torch.float32, device=weight.device) if scale is None else \
+            scale.to(torch.float32).reshape(-1)
+        if sc.numel() == 1:
+            sc = sc.expand(N)
+        if which == "gate":
+            self.w13.data[le, :I].copy_(weight[lo:lo + I])
+            self.w13_scale.data[le, :I].copy_(sc[lo:lo + I])
+        elif which == "up":
+            self.w13.data[le, I:].copy_(weight[lo:lo + I])
+            self.w13_scale.data[le, I:].copy_(sc[lo:lo + I])
+        elif which == "down":
+            self.w2.data[le].copy_(weight[:, lo:lo + I])
+            self.w2_scale.data[le].copy_(sc)
+        else:
+            raise ValueError(which)
         return True
 
     def load_expert_weight_fp8(self, expert_id: int, which: str, weight: torch.Tensor,
@@ -191,6 +236,10 @@ class FusedMoE(nn.Module):
             return C.fused_experts_fp8(x, self.w13, self.w13_scale, self.w2, self.w2_scale,
                                        topk_w, topk_ids, self.expert_map, add=add, alpha=alpha,
                                        valid_tokens=valid_tokens)
+        if self.q8_channel:
+            return C.fused_experts_q8(x, self.w13, self.w13_scale, self.w2, self.w2_scale,
+                                      topk_w, topk_ids, self.expert_map, add=add, alpha=alpha,
+                                      valid_tokens=valid_tokens)
         if self._interleaved and ops.use_native(x):
             return C.fused_experts(x, self.w13, self.w2, topk_w, topk_ids, self.expert_map,
                                    add=add, alpha=alpha, valid_tokens=valid_tokens)
@@ -267,10 +316,15 @@ class SparseMoeBlock(nn.Module):
         num_red = int(cfg.extra.get("num_redundant_experts", 0))
         self.experts = FusedMoE(cfg.num_experts, cfg.hidden_size, cfg.moe_intermediate_size,
                                 cfg.dtype, device, self.use_ep, prefix + ".experts", num_red)
-        qc = cfg.quant_config or {}
-        if (cfg.quantization == "fp8" and list(qc.get("weight_block_size") or []) == [128, 128]
-                and cfg.dtype == torch.bfloat16 and cfg.extra.get("fp8_experts", True)):
-            self.experts.enable_fp8_block()
+        if cfg.quantization and cfg.dtype == torch.bfloat16 and cfg.extra.get("q8_experts", True):
+            from .quant.moe import expert_storage
+            kind = expert_storage(cfg.quantization, cfg.quant_config)
+            if kind == "fp8_block":
+                self.experts.enable_fp8_block()
+            elif kind == "int8":
+                self.experts.enable_q8_channel(torch.int8)
+            elif kind == "fp8":
+                self.experts.enable_q8_channel(torch.float8_e4m3fn)
         self.eplb = EplbState(cfg.num_experts, num_red, device) if num_red > 0 else None
         if cfg.num_shared_experts > 0:
             from ..models.decoder import DenseMLP

@@ -220,7 +220,7 @@ class FusedEPDispatcher:
         T = x.shape[0]
         xr, w_r, ids_r, total = self.ws.dispatch(x, topk_w.float(), topk_ids.to(torch.int32),
                                                  max_tokens_per_rank)
-        if getattr(self.experts, "_interleaved", False) or getattr(self.experts, "fp8_block", False):
+        if any(getattr(self.experts, f, False) for f in ("_interleaved", "fp8_block", "q8_channel")):
             yr = self.experts(xr, w_r, ids_r, valid_tokens=total)
         else:           # layout without the grouped-GEMM path: run on the valid rows only
             n = int(total.item())

@@ -4,9 +4,11 @@ The reference serves MoE models from AWQ / GPTQ (``moe_wna16_gcu``,
 vllm_gcu/kernels/quantization/moe_wna16.py:26-643), fp8 block-scaled (fp8.py:215-380), int8
 w8a8 (w8a8.py:174-342) and w4a8 (w4a8.py) expert tensors by re-arranging them at load time
 and running a quantised grouped GEMM.  Here the expert tensors of those checkpoint formats
-are read unchanged and de-quantised **once at load time** into the bf16 expert tensors that
-the tcgen05 grouped GEMM consumes: the file formats and the routing / expert-parallel
-behaviour are the same, the memory footprint of the experts is that of bf16.
+are read unchanged.  On a GPU, fp8 experts with 128 x 128 block scales and int8 / fp8 experts
+with per-channel scales stay quantised and run through the grouped 8-bit tcgen05 GEMM
+(``expert_storage``); AWQ / GPTQ experts, and every format on the CPU path, are de-quantised
+**once at load time** into the bf16 expert tensors of the bf16 grouped GEMM (bf16 footprint).
+File formats and the routing / expert-parallel behaviour are the same either way.
 
 ``QuantExpertLoader`` collects the pieces of one expert projection (``qweight`` / ``qzeros``
 / ``scales`` / ``g_idx``, or ``weight`` / ``weight_scale`` / ``weight_scale_inv``) as the
@@ -73,6 +75,23 @@ def dequant_wna16(kind: str, bits: int, group: int, qweight: torch.Tensor, qzero
     return ((w.to(torch.float32) - zf) * sf).t().contiguous().to(dtype)
 
 
+def expert_storage(quant_name: Optional[str], quant_cfg: Optional[dict]) -> Optional[str]:
+    """How a GPU keeps the experts of a checkpoint format: ``"fp8_block"`` (fp8, 128 x 128
+    scales), ``"fp8"`` / ``"int8"`` (one scale per output channel) or None (de-quantised to
+    bf16 at load: AWQ / GPTQ / unknown block shapes)."""
+    n = (quant_name or "").replace("_gcu", "")
+    q = quant_cfg or {}
+    method = {"compressed-tensors": "w8a8"}.get(q.get("quant_method", n), q.get("quant_method", n))
+    if method == "fp8":
+        block = q.get("weight_block_size")
+        if block:
+            return "fp8_block" if list(block) == [128, 128] else None
+        return "fp8"
+    if method == "w8a8":
+        return "int8"
+    return None
+
+
 class QuantExpertLoader:
     """Buffers quantised expert tensors until a projection is complete."""
 
@@ -123,6 +142,11 @@ class QuantExpertLoader:
                 moe.load_expert_weight_fp8(expert, which, d["weight"], sc.to(torch.float32))
                 del self.pending[key]
                 return
+            if getattr(moe, "q8_channel", False) and d["weight"].dtype == moe.w13.dtype and (
+                    sc is None or sc.dim() <= 1 or sc.shape[-1] == 1):
+                moe.load_expert_weight_q8(expert, which, d["weight"], sc)
+                del self.pending[key]
+                return
             w = (dequant_fp8(d["weight"], sc, self.block, self.dtype) if self.kind == "fp8"
                  else dequant_int8(d["weight"], sc, self.dtype))
             del self.pending[key]
@@ -134,6 +158,10 @@ class QuantExpertLoader:
         for (layer_key, expert, which), d in list(self.pending.items()):
             if "weight" in d and self.kind in ("fp8", "w8a8"):
                 moe = resolve(layer_key)
+                if getattr(moe, "q8_channel", False) and d["weight"].dtype == moe.w13.dtype:
+                    moe.load_expert_weight_q8(expert, which, d["weight"], None)
+                    del self.pending[(layer_key, expert, which)]
+                    continue
                 w = (dequant_fp8(d["weight"], None, self.block, self.dtype) if self.kind == "fp8"
                      else dequant_int8(d["weight"], None, self.dtype))
                 moe.load_expert_weight(expert, which, w)

@@ -746,6 +746,42 @@ def fused_experts_fp8(x: torch.Tensor, w13: torch.Tensor, w13_scale: torch.Tenso
     return out
 
 
+def fused_experts_q8(x: torch.Tensor, w13: torch.Tensor, w13_scale: torch.Tensor,
+                     w2: torch.Tensor, w2_scale: torch.Tensor, topk_w: torch.Tensor,
+                     topk_ids: torch.Tensor, expert_map: Optional[torch.Tensor] = None,
+                     add: Optional[torch.Tensor] = None, alpha: float = 1.0,
+                     valid_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Routed-expert MLP with int8 or fp8 expert weights and per-output-channel scales
+    (w8a8 checkpoints): activations are quantised per token before each grouped GEMM.
+    ``w13 [E, 2I, H]`` gate rows first, ``w13_scale [E, 2I]``, ``w2 [E, H, I]``,
+    ``w2_scale [E, H]``; the weight dtype selects int8 (kind 2) or fp8 (kind 0)."""
+    T, H = x.shape
+    k = topk_ids.shape[1]
+    E = w13.shape[0]
+    numel = T * k
+    kind = 2 if w13.dtype == torch.int8 else 0
+    qname = "int8" if kind == 2 else "fp8"
+    cap = moe_align_cap(numel, E)
+    sorted_ids, expert_ids, npp, pos_of = moe_align(topk_ids, E, cap, expert_map, valid_tokens)
+    a_sorted = torch.empty((cap, H), device=x.device, dtype=x.dtype)
+    call("b200_moe_permute", ptr(x), x.stride(0), ptr(a_sorted), H, ptr(sorted_ids), ptr(npp),
+         numel, k, H, cap, DTYPE_CODE[x.dtype], stream_ptr())
+    row_w = torch.empty(cap, device=x.device, dtype=torch.float32)
+    call("b200_moe_row_weights", ptr(sorted_ids), ptr(topk_w), ptr(npp), ptr(row_w), numel, cap,
+         stream_ptr())
+    aq, a_s = per_token_quant(a_sorted, qname, valid_rows=npp)
+    h = gemm_q8_grouped(aq, a_s.view(-1), w13, w13_scale, expert_ids, npp, kind=kind)
+    hm = activation(h, "silu", "act_mul", valid_rows=npp)
+    hq, h_s = per_token_quant(hm, qname, valid_rows=npp)
+    y = gemm_q8_grouped(hq, h_s.view(-1), w2, w2_scale, expert_ids, npp, kind=kind,
+                        row_scale=row_w)
+    out = torch.empty((T, H), device=x.device, dtype=x.dtype)
+    call("b200_moe_unpermute_sum", ptr(y), y.stride(0), ptr(pos_of), ptr(add),
+         add.stride(0) if add is not None else 0, ptr(out), H, ptr(valid_tokens), T, k, H,
+         float(alpha), DTYPE_CODE[x.dtype], stream_ptr())
+    return out
+
+
 def get_ep_indices(topk_ids: torch.Tensor, experts_per_rank: int, ep: int):
     T, k = topk_ids.shape
     dev = topk_ids.device
