@@ -31,8 +31,16 @@ def main():
     ap.add_argument("--device", default="auto")
     ap.add_argument("--num-hidden-layers", type=int, default=0)
     ap.add_argument("--output-json", default=None)
+    ap.add_argument("--quantization", default=None, choices=[None, "fp8", "fp8_block", "w8a8"],
+                    help="random-init quantised weights: fp8 per-channel, fp8 with 128 x 128 "
+                         "blocks (DeepSeek-V3 layout), or int8 w8a8")
     a = ap.parse_args()
     kw = {"num_hidden_layers": a.num_hidden_layers} if a.num_hidden_layers else {}
+    if a.quantization == "fp8_block":
+        kw.update(quantization="fp8", quant_config={"quant_method": "fp8",
+                                                    "weight_block_size": [128, 128]})
+    elif a.quantization:
+        kw.update(quantization=a.quantization, quant_config={"quant_method": a.quantization})
     llm = LLM(a.model, tensor_parallel_size=a.tensor_parallel_size, max_num_seqs=a.max_num_seqs,
               max_num_batched_tokens=a.max_num_batched_tokens,
               max_model_len=a.input_len + a.output_len + 16, async_scheduling=True,
