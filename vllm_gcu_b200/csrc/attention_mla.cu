@@ -243,6 +243,17 @@ __global__ void __launch_bounds__(kThreads, 1)
             tma_load_2d(smem + kOffK + st * kKTile + c * kKChunk + pg * (kPage * 128), &tmK,
                         &k_full[st], c * 64, y);
         }
+        // While this tile is worked on, pull the next one into L2: its load then pays an L2
+        // latency instead of an HBM latency (with one stage that load is on the critical path).
+        if (j + 1 < nt) {
+          const int nkey0 = (t0 + j + 1) * BKV;
+          for (int pg = 0; pg < BKV / kPage; ++pg) {
+            if (nkey0 + pg * kPage > last_tok) break;
+            const int blk = bt[(nkey0 + pg * kPage) / a.block_size];
+            const int y = blk * a.block_size + ((nkey0 + pg * kPage) % a.block_size);
+            for (int c = 0; c < kChunks; ++c) tma_prefetch_2d(&tmK, c * 64, y);
+          }
+        }
       }
     }
   } else if (warp == 1) {
