@@ -82,3 +82,29 @@ def test_allowed_tokens_and_guided_choice():
                                            guided_choice=choices))[0]
     toks = tuple(out.outputs[0].token_ids)
     assert toks in choices and out.outputs[0].finish_reason == "stop"
+
+
+def test_text_prompts_and_chat_with_a_tokenizer():
+    """``LLM(tokenizer=...)``: text prompts are encoded, completions carry ``text``, ``chat``
+    renders conversations with the tokenizer's template."""
+    class Tok:
+        def encode(self, text):
+            return [3 + b for b in text.encode()]
+
+        def decode(self, ids):
+            return bytes((i - 3) % 256 for i in ids).decode("latin-1")
+
+        def apply_chat_template(self, conv, tokenize=True, add_generation_prompt=True):
+            return self.encode("".join(f"<{m['role']}>{m['content']}" for m in conv) + "<assistant>")
+
+    llm = _llm(tokenizer=Tok())
+    sp = SamplingParams(max_tokens=4, temperature=0.0, ignore_eos=True)
+    a = llm.generate("hello world", sp)[0]
+    b = llm.generate([Tok().encode("hello world")], sp)[0]
+    assert a.outputs[0].token_ids == b.outputs[0].token_ids
+    assert a.outputs[0].text == Tok().decode(a.outputs[0].token_ids)
+    c = llm.chat([{"role": "user", "content": "hi"}], sp)[0]
+    assert c.prompt_token_ids == Tok().encode("<user>hi<assistant>") and len(c.outputs[0].text) == 4
+    import pytest
+    with pytest.raises(ValueError):
+        _llm().generate("text without a tokenizer", sp)

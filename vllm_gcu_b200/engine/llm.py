@@ -351,7 +351,7 @@ class LLM:
                  speculative_method: Optional[str] = None, num_speculative_tokens: int = 0,
                  prompt_lookup_max: int = 4, prompt_lookup_min: int = 1,
                  enable_lora: bool = False, max_loras: int = 4, max_lora_rank: int = 16,
-                 additional_config: Optional[dict] = None, **model_overrides):
+                 additional_config: Optional[dict] = None, tokenizer=None, **model_overrides):
         model_path = None
         if isinstance(model, ModelConfig):
             mc = model
@@ -389,6 +389,49 @@ class LLM:
             load_format=load_format or ("safetensors" if model_path else "dummy"),
             model_path=model_path, additional_config=additional_config or {})
         self.engine = LLMEngine(cfg)
+        # text in / text out: a tokenizer object (``encode`` / ``decode``) or a directory
+        # with tokenizer files; by default the tokenizer next to the checkpoint
+        self.tokenizer = None
+        if tokenizer is None and model_path:
+            tokenizer = model_path
+        if isinstance(tokenizer, str):
+            try:
+                from transformers import AutoTokenizer
+                self.tokenizer = AutoTokenizer.from_pretrained(tokenizer)
+            except Exception:
+                self.tokenizer = None
+        elif tokenizer is not None:
+            self.tokenizer = tokenizer
+
+    def _encode(self, prompt):
+        """Prompts may be token-id lists, dicts with ``prompt_token_ids`` or text."""
+        if isinstance(prompt, str):
+            if self.tokenizer is None:
+                raise ValueError("text prompts need a tokenizer (LLM(..., tokenizer=...))")
+            return list(self.tokenizer.encode(prompt))
+        if isinstance(prompt, dict) and "prompt" in prompt and "prompt_token_ids" not in prompt:
+            d = dict(prompt)
+            d["prompt_token_ids"] = self._encode(d.pop("prompt"))
+            return d
+        return prompt
+
+    def _decode_outputs(self, outs):
+        if self.tokenizer is not None:
+            for o in outs:
+                for c in o.outputs:
+                    c.text = self.tokenizer.decode(c.token_ids)
+        return outs
+
+    def chat(self, messages, sampling_params=None) -> list[RequestOutput]:
+        """One conversation (list of ``{"role", "content"}``) or a list of conversations,
+        rendered with the tokenizer's chat template."""
+        if self.tokenizer is None or not hasattr(self.tokenizer, "apply_chat_template"):
+            raise ValueError("chat() needs a tokenizer with a chat template")
+        convs = messages if messages and isinstance(messages[0], list) else [messages]
+        prompts = [list(self.tokenizer.apply_chat_template(c, tokenize=True,
+                                                           add_generation_prompt=True))
+                   for c in convs]
+        return self.generate(prompts, sampling_params)
 
     def set_vocabulary(self, vocab) -> None:
         """Token texts (index = token id) or a tokenizer; enables ``guided_regex`` /
@@ -404,13 +447,18 @@ class LLM:
         and return the ``n`` with the highest cumulative log-probability; ``use_beam_search``
         routes to :meth:`beam_search` (best-of and beam search are listed as functional in
         docs/source/user_guide/support_matrix/supported_features.md:11-64)."""
-        prompts = list(prompts)
+        if isinstance(prompts, str):
+            prompts = [prompts]
+        prompts = [self._encode(p) for p in prompts]
         if sampling_params is None or isinstance(sampling_params, SamplingParams):
             sps = [sampling_params or SamplingParams()] * len(prompts)
         else:
             sps = list(sampling_params)
+        if any(sp.guided_regex is not None or sp.guided_json is not None for sp in sps) \
+                and getattr(self.engine, "_vocab", None) is None and self.tokenizer is not None:
+            self.set_vocabulary(self.tokenizer)
         if all(sp.n == 1 and not sp.best_of and not sp.use_beam_search for sp in sps):
-            return self.engine.generate(prompts, sps)
+            return self._decode_outputs(self.engine.generate(prompts, sps))
         import dataclasses
         flat_p, flat_sp, owner = [], [], []
         results: list[Optional[RequestOutput]] = [None] * len(prompts)
@@ -440,7 +488,7 @@ class LLM:
                 c.index = idx
             results[i] = RequestOutput(group[0].request_id, group[0].prompt_token_ids, comps, True,
                                        group[0].num_cached_tokens, group[0].prompt_logprobs)
-        return results          # type: ignore[return-value]
+        return self._decode_outputs(results)          # type: ignore[arg-type]
 
     def beam_search(self, prompt: Sequence[int], beam_width: int, max_tokens: int,
                     num_return: int = 1, eos_token_id: Optional[int] = None,

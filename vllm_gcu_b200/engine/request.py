@@ -154,6 +154,7 @@ class CompletionOutput:
     finish_reason: Optional[str] = None
     logprobs: Optional[list] = None
     cumulative_logprob: Optional[float] = None
+    text: Optional[str] = None                # filled when the LLM has a tokenizer
 
 
 @dataclass
