@@ -6,18 +6,19 @@
 // (vllm_gcu/kernels/quantization/awq.py:70-118, gptq.py:95-164) on the decode path.  With
 // M <= 256 the layer is bound by the weight bytes it reads; de-quantising into a bf16 scratch
 // first and running the bf16 GEMM moves 4.5 bytes per weight (read 0.5, write 2, read 2), this
-// kernel moves 0.5: four producer warps read the packed integers straight from global memory,
+// kernel moves 0.5: producer warps read the packed integers straight from global memory,
 // de-quantise in registers (4 bit: bf16 pair arithmetic with a single rounding; 8 bit: fp32
 // multiply-add rounded to bf16, as the stand-alone de-quantisation kernel does) and write the
-// bf16 tile into shared memory in the K-major 128-byte
-// swizzled layout that tcgen05.mma reads; the activation tiles arrive by TMA; accumulators
-// live in tensor memory.  Packed weights are prefetched eight K blocks ahead into registers;
-// each producer warp builds every fourth K block on its own.
+// bf16 tile into shared memory in the K-major 128-byte swizzled layout that tcgen05.mma
+// reads; the activation tiles arrive by TMA; accumulators live in tensor memory.  Packed
+// weights and their scales are prefetched sixteen K blocks ahead into registers; each producer
+// warp builds whole K blocks on its own (every eighth one).
 //
 // Warp roles: warp 0 TMA (activations), warp 1 MMA issuer + TMEM owner, warps 2..9 weight
 // producers (two per scheduler, so one covers the other's stalls); warps 2..5 run the epilogue.
 // When N / 64 column tiles would leave most SMs idle, K is split over blockIdx.y: fp32 partial
-// sums go to a workspace and a second kernel adds them (fixed order) and applies the bias.  Bounded waits, status word.
+// sums go to a workspace and a second kernel adds them (fixed order) and applies the bias.
+// Bounded waits, status word.
 #include "common.cuh"
 
 namespace b200 {
