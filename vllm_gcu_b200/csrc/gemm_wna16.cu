@@ -51,10 +51,13 @@ struct Args {
 // the K blocks w, w + stages, ...): a warp meets its stage's barrier phases in order, so the
 // parity waits cannot be overtaken.  (With stages shared between warps a fast warp could pass
 // a wait meant for a later phase and arrive twice on one barrier phase.)  Two activation
-// tiles per stage leave room for four stages, so only four warps produce then.
-template <int MT>
+// tiles per stage leave room for four stages, so only four warps produce then.  With one
+// activation tile there are two shapes: eight stages / eight producer warps (one CTA per SM),
+// and four / four (96 KB, 192 threads: two CTAs per SM) for grids of more than 1.5 CTAs per
+// SM, where a second resident CTA is worth more than a deeper pipeline.
+template <int MT, int STAGES>
 struct Smem {
-  static constexpr int kStages = MT == 1 ? 8 : 4;
+  static constexpr int kStages = STAGES;
   static constexpr int kProdWarps = kStages;
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
@@ -63,10 +66,10 @@ struct Smem {
   static constexpr int kTotal = kBarOffset + 256 + 1024;
 };
 
-template <int BITS, int MT>
+template <int BITS, int MT, int STAGES>
 __global__ void __launch_bounds__(kThreads)
     gemm_wna16_kernel(const __grid_constant__ CUtensorMap tmA, const Args p) {
-  using L = Smem<MT>;
+  using L = Smem<MT, STAGES>;
   constexpr int kStages = L::kStages;
   constexpr uint32_t kTmemCols = MT * BN <= 64 ? 64 : 128;
   constexpr uint32_t kIdesc = make_idesc(BM, BN, 1, 1);
@@ -380,10 +383,10 @@ static int plan_splits(int N, int K) {
   return splits < 1 ? 1 : splits;
 }
 
-template <int BITS, int MT>
+template <int BITS, int MT, int STAGES>
 static int launch(const CUtensorMap& tmA, const Args& a, cudaStream_t s) {
-  using L = Smem<MT>;
-  auto kern = gemm_wna16_kernel<BITS, MT>;
+  using L = Smem<MT, STAGES>;
+  auto kern = gemm_wna16_kernel<BITS, MT, STAGES>;
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -393,7 +396,7 @@ static int launch(const CUtensorMap& tmA, const Args& a, cudaStream_t s) {
     configured[dev] = true;
   }
   dim3 grid((a.N + BN - 1) / BN, a.splits);
-  kern<<<grid, kThreads, L::kTotal, s>>>(tmA, a);
+  kern<<<grid, 64 + 32 * STAGES, L::kTotal, s>>>(tmA, a);
   int e = static_cast<int>(cudaGetLastError());
   if (e != 0 || a.splits == 1) return e;
   const long long total = static_cast<long long>(a.M) * a.N;
@@ -444,6 +447,12 @@ B200_API int b200_gemm_wna16(const void* A, long long lda, const void* qw, const
   a.status = status_ptr();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool two = M > BM;
-  if (bits == 4) return two ? launch<4, 2>(tmA, a, s) : launch<4, 1>(tmA, a, s);
-  return two ? launch<8, 2>(tmA, a, s) : launch<8, 1>(tmA, a, s);
+  const int ctas = ((N + BN - 1) / BN) * a.splits;
+  const int sms = sm_count() > 0 ? sm_count() : 148;
+  const bool wide = !two && 2 * ctas > 3 * sms;
+  if (bits == 4)
+    return two ? launch<4, 2, 4>(tmA, a, s)
+               : (wide ? launch<4, 1, 4>(tmA, a, s) : launch<4, 1, 8>(tmA, a, s));
+  return two ? launch<8, 2, 4>(tmA, a, s)
+             : (wide ? launch<8, 1, 4>(tmA, a, s) : launch<8, 1, 8>(tmA, a, s));
 }
