@@ -1,0 +1,95 @@
+"""Dense decoder families that differ from Llama only in checkpoint layout or small maths:
+InternLM2 (fused ``wqkv``, renamed modules), Baichuan2-7B (``W_pack``, normalised LM head) and
+Gemma (GeGLU, ``1 + weight`` norms, scaled embeddings).  The oracle is the HuggingFace
+implementation of the same mathematics on a tiny random model."""
+import pytest
+import torch
+
+tr = pytest.importorskip("transformers")
+
+from vllm_gcu_b200.config import ModelConfig  # noqa: E402
+from vllm_gcu_b200.engine.llm import LLM  # noqa: E402
+from vllm_gcu_b200.engine.request import SamplingParams  # noqa: E402
+
+IDS = [5, 17, 99, 3, 250, 42, 7, 7, 81, 120, 33]
+
+
+def _engine_logits(arch, hf_cfg_dict, weights):
+    d = dict(hf_cfg_dict)
+    d["architectures"] = [arch]
+    mc = ModelConfig.from_hf_dict(d, dtype=torch.float32)
+    llm = LLM(mc, device="cpu", max_num_seqs=2, max_num_batched_tokens=32, max_model_len=64,
+              num_gpu_blocks=16, load_format="none")
+    llm.engine.model.load_weights(weights)
+    llm.engine.runner.keep_logits = True
+    out = llm.generate([IDS], SamplingParams(max_tokens=1, temperature=0.0, ignore_eos=True))
+    return llm.engine.runner.last_logits[0], out[0].outputs[0].token_ids[0]
+
+
+def _tiny_llama(vocab=300, kv=2):
+    cfg = tr.LlamaConfig(vocab_size=vocab, hidden_size=64, intermediate_size=128,
+                         num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=kv,
+                         max_position_embeddings=128, rms_norm_eps=1e-6, tie_word_embeddings=False)
+    torch.manual_seed(0)
+    return cfg, tr.LlamaForCausalLM(cfg).eval().float()
+
+
+def _hf_last_logits(model):
+    with torch.inference_mode():
+        return model(input_ids=torch.tensor([IDS])).logits[0, -1]
+
+
+def test_internlm2_layout_loads_into_the_llama_mathematics():
+    cfg, hf = _tiny_llama()
+    kvh, g, d = 2, 2, 16
+    sd = {}
+    for k, v in hf.state_dict().items():
+        k = (k.replace("model.embed_tokens.", "model.tok_embeddings.").replace("lm_head.", "output.")
+             .replace(".self_attn.o_proj.", ".attention.wo.")
+             .replace(".input_layernorm.", ".attention_norm.")
+             .replace(".post_attention_layernorm.", ".ffn_norm.")
+             .replace(".mlp.gate_proj.", ".feed_forward.w1.").replace(".mlp.up_proj.", ".feed_forward.w3.")
+             .replace(".mlp.down_proj.", ".feed_forward.w2."))
+        sd[k] = v
+    for i in range(2):
+        p = f"model.layers.{i}.self_attn."
+        q = sd.pop(p + "q_proj.weight").view(kvh, g, d, -1)
+        k = sd.pop(p + "k_proj.weight").view(kvh, 1, d, -1)
+        v = sd.pop(p + "v_proj.weight").view(kvh, 1, d, -1)
+        sd[f"model.layers.{i}.attention.wqkv.weight"] = torch.cat([q, k, v], 1).reshape(-1, 64)
+    got, tok = _engine_logits("InternLM2ForCausalLM", cfg.to_dict(), sd.items())
+    want = _hf_last_logits(hf)
+    assert torch.allclose(got, want, atol=2e-4), (got - want).abs().max()
+    assert tok == int(want.argmax())
+
+
+def test_baichuan2_w_pack_and_normalised_head():
+    cfg, hf = _tiny_llama(vocab=125696, kv=4)       # Baichuan: as many KV heads as query heads
+    sd = dict(hf.state_dict())
+    for i in range(2):
+        p = f"model.layers.{i}.self_attn."
+        sd[p + "W_pack.weight"] = torch.cat([sd.pop(p + "q_proj.weight"), sd.pop(p + "k_proj.weight"),
+                                             sd.pop(p + "v_proj.weight")], 0)
+    d = cfg.to_dict()
+    got, tok = _engine_logits("BaichuanForCausalLM", d, sd.items())
+    with torch.inference_mode():
+        h = hf.model(input_ids=torch.tensor([IDS])).last_hidden_state[0, -1]
+        want = torch.nn.functional.normalize(hf.lm_head.weight) @ h
+    assert torch.allclose(got, want, atol=2e-4), (got - want).abs().max()
+    assert tok == int(want.argmax())
+
+
+def test_gemma_matches_transformers():
+    cfg = tr.GemmaConfig(vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                         num_attention_heads=4, num_key_value_heads=1, head_dim=16,
+                         max_position_embeddings=128, rms_norm_eps=1e-6)
+    torch.manual_seed(1)
+    hf = tr.GemmaForCausalLM(cfg).eval().float()
+    with torch.no_grad():                      # non-trivial norm weights (initialised to zero)
+        for n, p in hf.named_parameters():
+            if n.endswith("norm.weight"):
+                p.copy_(torch.randn_like(p) * 0.1)
+    got, tok = _engine_logits("GemmaForCausalLM", cfg.to_dict(), hf.state_dict().items())
+    want = _hf_last_logits(hf)
+    assert torch.allclose(got, want, atol=3e-4), (got - want).abs().max()
+    assert tok == int(want.argmax())

@@ -15,7 +15,10 @@ _REGISTRY: dict[str, str] = {
     "Qwen2ForCausalLM": "vllm_gcu_b200.models.llama:Qwen2ForCausalLM",
     "Qwen3ForCausalLM": "vllm_gcu_b200.models.llama:Qwen3ForCausalLM",
     "Glm4ForCausalLM": "vllm_gcu_b200.models.llama:Glm4ForCausalLM",
-    "InternLM2ForCausalLM": "vllm_gcu_b200.models.llama:LlamaForCausalLM",
+    "InternLM2ForCausalLM": "vllm_gcu_b200.models.llama:InternLM2ForCausalLM",
+    "BaichuanForCausalLM": "vllm_gcu_b200.models.llama:BaichuanForCausalLM",
+    "BaiChuanForCausalLM": "vllm_gcu_b200.models.llama:BaichuanForCausalLM",
+    "GemmaForCausalLM": "vllm_gcu_b200.models.llama:GemmaForCausalLM",
     "YiForCausalLM": "vllm_gcu_b200.models.llama:LlamaForCausalLM",
     "Qwen3MoeForCausalLM": "vllm_gcu_b200.models.moe_models:Qwen3MoeForCausalLM",
     "MixtralForCausalLM": "vllm_gcu_b200.models.moe_models:MixtralForCausalLM",

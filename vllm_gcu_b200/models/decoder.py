@@ -186,8 +186,9 @@ class DecoderLM(nn.Module):
         self.sequence_parallel = bool(cfg.extra.get("sequence_parallel")
                                       or envs.ENABLE_SEQUENCE_PARALLEL)
         if self.is_first_stage or (cfg.tie_word_embeddings and self.is_last_stage):
-            self.embed_tokens = VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, cfg.dtype,
-                                                       device)
+            # a tied embedding also serves as the output projection
+            emb_cls = ParallelLMHead if cfg.tie_word_embeddings else VocabParallelEmbedding
+            self.embed_tokens = emb_cls(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device)
         self.layers = nn.ModuleDict({
             str(i): DecoderLayer(cfg, i, device, f"model.layers.{i}")
             for i in range(self.start_layer, self.end_layer)})
@@ -221,6 +222,9 @@ class DecoderLM(nn.Module):
         ``(hidden, residual)`` pair handed to the next stage."""
         if self.is_first_stage:
             x = inputs_embeds if inputs_embeds is not None else self.embed_tokens(input_ids)
+            scale = getattr(self, "embed_scale", None)
+            if scale is not None and inputs_embeds is None:
+                x = x * torch.tensor(scale, dtype=x.dtype, device=x.device)
             residual = None
         else:
             x, residual = intermediate

@@ -38,3 +38,88 @@ class Glm4ForCausalLM(DecoderLM):
                                   partial_rotary_factor=cfg.partial_rotary_factor
                                   if cfg.partial_rotary_factor < 1.0 else 0.5)
         super().__init__(cfg, device)
+
+
+class InternLM2ForCausalLM(DecoderLM):
+    """InternLM2 / 2.5 checkpoints: Llama mathematics under other tensor names, with q / k / v
+    fused per KV group in ``attention.wqkv`` (rows ``[kv_head][q_0 .. q_{g-1}, k, v][head_dim]``).
+    The reference lists InternLM2 in every precision column
+    (docs/source/user_guide/support_matrix/supported_models.md:7-24)."""
+
+    _RENAME = (("model.tok_embeddings.", "model.embed_tokens."), ("output.", "lm_head."),
+               (".attention.wo.", ".self_attn.o_proj."), (".attention_norm.", ".input_layernorm."),
+               (".ffn_norm.", ".post_attention_layernorm."), (".feed_forward.w1.", ".mlp.gate_proj."),
+               (".feed_forward.w3.", ".mlp.up_proj."), (".feed_forward.w2.", ".mlp.down_proj."))
+
+    def load_special(self, name, tensor, owners) -> bool:
+        if ".attention.wqkv." in name:
+            owner = name.split(".attention.wqkv.")[0] + ".self_attn.qkv_proj"
+            mod = owners.get(owner)
+            if mod is None:
+                return True
+            pname = name.rsplit(".", 1)[1]
+            cfg = self.cfg
+            kvh, g, d = cfg.num_key_value_heads, cfg.num_attention_heads // cfg.num_key_value_heads, \
+                cfg.head_dim
+            w = tensor.reshape(kvh, g + 2, d, *tensor.shape[1:])
+            mod.load_weight(pname, w[:, :g].reshape(kvh * g * d, *tensor.shape[1:]), "q")
+            mod.load_weight(pname, w[:, g].reshape(kvh * d, *tensor.shape[1:]), "k")
+            mod.load_weight(pname, w[:, g + 1].reshape(kvh * d, *tensor.shape[1:]), "v")
+            return True
+        new = name
+        for a, b in self._RENAME:
+            if new.startswith(a) or (a.startswith(".") and a in new):
+                new = new.replace(a, b, 1)
+        if new == name:
+            return False
+        m = self.map_weight_name(new)
+        if m is not None and m[0] in owners:
+            owners[m[0]].load_weight(m[1], tensor, m[2])
+        return True
+
+
+class BaichuanForCausalLM(DecoderLM):
+    """Baichuan / Baichuan2 7B (rotary positions): q, k, v packed in ``W_pack``; Baichuan2
+    normalises the rows of the LM head (its ``NormHead``), which is done once at load.  The
+    13B variants use ALiBi and are rejected."""
+
+    def __init__(self, cfg: ModelConfig, device="cpu"):
+        if cfg.hidden_size > 4096 and cfg.extra.get("position_embedding", "ROPE") != "ROPE":
+            raise ValueError("Baichuan 13B (ALiBi positions) is not supported")
+        super().__init__(cfg, device)
+
+    def load_special(self, name, tensor, owners) -> bool:
+        if ".self_attn.W_pack." in name:
+            owner = name.split(".self_attn.W_pack.")[0] + ".self_attn.qkv_proj"
+            mod = owners.get(owner)
+            if mod is not None:
+                pname = name.rsplit(".", 1)[1]
+                for part, sid in zip(tensor.chunk(3, dim=0), ("q", "k", "v")):
+                    mod.load_weight(pname, part, sid)
+            return True
+        if name == "lm_head.weight" and self.cfg.vocab_size == 125696 and "lm_head" in owners:
+            import torch.nn.functional as F
+            owners["lm_head"].load_weight("weight", F.normalize(tensor.float()).to(tensor.dtype),
+                                          None)
+            return True
+        return False
+
+
+class GemmaForCausalLM(DecoderLM):
+    """Gemma / CodeGemma: GeGLU MLP, RMSNorm with ``(1 + weight)``, embeddings scaled by
+    ``sqrt(hidden_size)``, tied LM head.  The norm offset is folded into the weights at load."""
+
+    def __init__(self, cfg: ModelConfig, device="cpu"):
+        act = {"gelu": "gelu_tanh", "gelu_pytorch_tanh": "gelu_tanh"}.get(cfg.hidden_act,
+                                                                           cfg.hidden_act)
+        cfg = dataclasses.replace(cfg, hidden_act=act, tie_word_embeddings=True)
+        super().__init__(cfg, device)
+        self.embed_scale = float(cfg.hidden_size) ** 0.5
+
+    def load_special(self, name, tensor, owners) -> bool:
+        if name.endswith("norm.weight"):
+            m = self.map_weight_name(name)
+            if m is not None and m[0] in owners:
+                owners[m[0]].load_weight(m[1], (tensor.float() + 1.0).to(tensor.dtype), m[2])
+            return True
+        return name == "lm_head.weight"              # tied to the embedding
