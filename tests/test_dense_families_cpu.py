@@ -93,3 +93,38 @@ def test_gemma_matches_transformers():
     want = _hf_last_logits(hf)
     assert torch.allclose(got, want, atol=3e-4), (got - want).abs().max()
     assert tok == int(want.argmax())
+
+
+def test_chatglm_layout_matches_the_glm_mathematics():
+    """ChatGLM3 / GLM-4-9B original checkpoints: the oracle is transformers' ``GlmForCausalLM``
+    (same mathematics in the HF layout), its weights renamed into the ChatGLM layout."""
+    cfg = tr.GlmConfig(vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                       num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                       partial_rotary_factor=0.5, attention_bias=True, rms_norm_eps=1e-5,
+                       max_position_embeddings=128, tie_word_embeddings=False, pad_token_id=0)
+    torch.manual_seed(2)
+    hf = tr.GlmForCausalLM(cfg).eval().float()
+    src = hf.state_dict()
+    sd = {"transformer.embedding.word_embeddings.weight": src["model.embed_tokens.weight"],
+          "transformer.encoder.final_layernorm.weight": src["model.norm.weight"],
+          "transformer.output_layer.weight": src["lm_head.weight"],
+          "transformer.rotary_pos_emb.inv_freq": torch.zeros(4)}
+    for i in range(2):
+        a, b = f"model.layers.{i}.", f"transformer.encoder.layers.{i}."
+        for kind in ("weight", "bias"):
+            sd[b + "self_attention.query_key_value." + kind] = torch.cat(
+                [src[a + f"self_attn.{p}_proj.{kind}"] for p in "qkv"], 0)
+        sd[b + "self_attention.dense.weight"] = src[a + "self_attn.o_proj.weight"]
+        sd[b + "mlp.dense_h_to_4h.weight"] = src[a + "mlp.gate_up_proj.weight"]
+        sd[b + "mlp.dense_4h_to_h.weight"] = src[a + "mlp.down_proj.weight"]
+        sd[b + "input_layernorm.weight"] = src[a + "input_layernorm.weight"]
+        sd[b + "post_attention_layernorm.weight"] = src[a + "post_attention_layernorm.weight"]
+    chatglm_cfg = {"model_type": "chatglm", "num_layers": 2, "hidden_size": 64,
+                   "ffn_hidden_size": 128, "num_attention_heads": 4, "kv_channels": 16,
+                   "multi_query_attention": True, "multi_query_group_num": 2,
+                   "layernorm_epsilon": 1e-5, "padded_vocab_size": 300, "seq_length": 128,
+                   "add_qkv_bias": True, "rmsnorm": True}
+    got, tok = _engine_logits("ChatGLMModel", chatglm_cfg, sd.items())
+    want = _hf_last_logits(hf)
+    assert torch.allclose(got, want, atol=3e-4), (got - want).abs().max()
+    assert tok == int(want.argmax())

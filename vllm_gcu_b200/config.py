@@ -118,6 +118,22 @@ class ModelConfig:
             d = {**{k: v for k, v in d.items() if k != "text_config"},
                  **{k: v for k, v in d["text_config"].items()
                     if k not in ("architectures", "model_type")}}
+        if archs[0] in ("ChatGLMModel", "ChatGLMForConditionalGeneration"):
+            # ChatGLM2 / 3 / GLM-4-9B configs use their own field names
+            d = dict(d)
+            heads = d["num_attention_heads"]
+            d.setdefault("num_hidden_layers", d.get("num_layers"))
+            d.setdefault("intermediate_size", d.get("ffn_hidden_size"))
+            d.setdefault("num_key_value_heads",
+                         d.get("multi_query_group_num", heads) if d.get("multi_query_attention")
+                         else heads)
+            d.setdefault("head_dim", d.get("kv_channels", d["hidden_size"] // heads))
+            d.setdefault("rms_norm_eps", d.get("layernorm_epsilon", 1e-5))
+            d.setdefault("vocab_size", d.get("padded_vocab_size"))
+            d.setdefault("max_position_embeddings", d.get("seq_length", 8192))
+            d.setdefault("attention_bias", bool(d.get("add_qkv_bias", False)))
+            d.setdefault("rope_theta", 10000.0 * float(d.get("rope_ratio", 1.0)))
+            d.setdefault("tie_word_embeddings", False)
         names = {f.name for f in dataclasses.fields(cls)}
         kw: dict[str, Any] = {"architecture": archs[0]}
         alias = {"n_routed_experts": "num_experts", "num_local_experts": "num_experts",
@@ -138,6 +154,9 @@ class ModelConfig:
             kw.setdefault("partial_rotary_factor", d.get("partial_rotary_factor", 0.5))
         if "Deepseek" in arch:
             kw.setdefault("rope_is_neox", False)
+        if arch.startswith("ChatGLM"):
+            kw.setdefault("rope_is_neox", False)
+            kw.setdefault("partial_rotary_factor", 0.5)
         if "rope_parameters" in d and isinstance(d["rope_parameters"], dict):
             rp = d["rope_parameters"]
             kw.setdefault("rope_theta", rp.get("rope_theta", kw.get("rope_theta", 10000.0)))

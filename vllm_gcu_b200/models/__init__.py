@@ -19,6 +19,8 @@ _REGISTRY: dict[str, str] = {
     "BaichuanForCausalLM": "vllm_gcu_b200.models.llama:BaichuanForCausalLM",
     "BaiChuanForCausalLM": "vllm_gcu_b200.models.llama:BaichuanForCausalLM",
     "GemmaForCausalLM": "vllm_gcu_b200.models.llama:GemmaForCausalLM",
+    "ChatGLMModel": "vllm_gcu_b200.models.llama:ChatGLMForCausalLM",
+    "ChatGLMForConditionalGeneration": "vllm_gcu_b200.models.llama:ChatGLMForCausalLM",
     "YiForCausalLM": "vllm_gcu_b200.models.llama:LlamaForCausalLM",
     "Qwen3MoeForCausalLM": "vllm_gcu_b200.models.moe_models:Qwen3MoeForCausalLM",
     "MixtralForCausalLM": "vllm_gcu_b200.models.moe_models:MixtralForCausalLM",

@@ -123,3 +123,49 @@ class GemmaForCausalLM(DecoderLM):
                 owners[m[0]].load_weight(m[1], (tensor.float() + 1.0).to(tensor.dtype), m[2])
             return True
         return name == "lm_head.weight"              # tied to the embedding
+
+
+class ChatGLMForCausalLM(DecoderLM):
+    """ChatGLM2 / ChatGLM3 / GLM-4-9B in their original checkpoint layout
+    (``transformer.encoder.layers.N.self_attention.query_key_value`` ...): grouped-query
+    attention with q / k / v biases fused in one tensor, interleaved (GPT-J) rotary embedding
+    on the first half of every head, fused ``dense_h_to_4h`` = [gate | up] with SwiGLU."""
+
+    _RENAME = ((".self_attention.dense.", ".self_attn.o_proj."),
+               (".mlp.dense_4h_to_h.", ".mlp.down_proj."))
+
+    def load_special(self, name, tensor, owners) -> bool:
+        if not name.startswith("transformer."):
+            return False
+        if "rotary_pos_emb" in name:
+            return True
+        new = name[len("transformer."):]
+        new = new.replace("encoder.layers.", "model.layers.")
+        if new.startswith("embedding.word_embeddings."):
+            new = "model.embed_tokens." + new.rsplit(".", 1)[1]
+        elif new.startswith("encoder.final_layernorm."):
+            new = "model.norm." + new.rsplit(".", 1)[1]
+        elif new.startswith("output_layer."):
+            new = "lm_head." + new.rsplit(".", 1)[1]
+        pname = new.rsplit(".", 1)[1]
+        cfg = self.cfg
+        if ".self_attention.query_key_value." in new:
+            mod = owners.get(new.split(".self_attention.")[0] + ".self_attn.qkv_proj")
+            if mod is not None:
+                nq = cfg.num_attention_heads * cfg.head_dim
+                nkv = cfg.num_key_value_heads * cfg.head_dim
+                for part, sid in zip(tensor.split([nq, nkv, nkv], dim=0), ("q", "k", "v")):
+                    mod.load_weight(pname, part, sid)
+            return True
+        if ".mlp.dense_h_to_4h." in new:
+            mod = owners.get(new.split(".mlp.")[0] + ".mlp.gate_up_proj")
+            if mod is not None:
+                for sid, part in enumerate(tensor.chunk(2, dim=0)):
+                    mod.load_weight(pname, part, sid)
+            return True
+        for a, b in self._RENAME:
+            new = new.replace(a, b)
+        m = self.map_weight_name(new)
+        if m is not None and m[0] in owners:
+            owners[m[0]].load_weight(m[1], tensor, m[2])
+        return True
