@@ -137,3 +137,34 @@ def test_swap_preemption_on_gpu_reproduces_unpreempted_tokens():
     _native.check_status()
     assert tight.engine.scheduler.num_swaps > 0
     assert got == want
+
+
+def test_gemma_head_dim_256_gpu_tracks_cpu_reference():
+    """Gemma-shaped model (head size 256, GeGLU, tied scaled embedding): decode runs on the
+    256-wide paged kernel, prefill on the torch formulation; logits follow the CPU path."""
+    from vllm_gcu_b200.config import ModelConfig
+    d = dict(architectures=["GemmaForCausalLM"], vocab_size=2048, hidden_size=512,
+             intermediate_size=1024, num_hidden_layers=2, num_attention_heads=4,
+             num_key_value_heads=1, head_dim=256, rms_norm_eps=1e-6,
+             hidden_act="gelu_pytorch_tanh", max_position_embeddings=512)
+    kw = dict(max_num_seqs=4, max_num_batched_tokens=128, max_model_len=256, num_gpu_blocks=64)
+    gpu = LLM(ModelConfig.from_hf_dict(d, dtype=torch.bfloat16), device="cuda",
+              cuda_graph_sizes=[4], **kw)
+    cpu = LLM(ModelConfig.from_hf_dict(d, dtype=torch.bfloat16), device="cpu", **kw)
+    sd = {k: v.detach().cpu() for k, v in gpu.engine.model.state_dict().items()}
+    cpu.engine.model.load_state_dict(sd, strict=False)
+    prompts = _prompts(3, [40, 9, 77], 2048, seed=3)
+    sp = SamplingParams(max_tokens=4, temperature=0.0, ignore_eos=True)
+    og = gpu.generate(prompts, sp)
+    oc = cpu.generate(prompts, sp)
+    torch.cuda.synchronize()
+    _native.check_status()
+    assert [o.outputs[0].token_ids[0] for o in og] == [o.outputs[0].token_ids[0] for o in oc]
+    one = SamplingParams(max_tokens=1, temperature=0.0, ignore_eos=True)
+    gpu.engine.runner.keep_logits = cpu.engine.runner.keep_logits = True
+    gpu.engine.runner.graphs = {}
+    gpu.generate(prompts, one)
+    cpu.generate(prompts, one)
+    lg, lc = gpu.engine.runner.last_logits, cpu.engine.runner.last_logits
+    err = (lg - lc).abs().max().item()
+    assert err < 0.06 * lc.std().item() + 0.03, (err, lc.std().item())

@@ -137,7 +137,15 @@ class PagedAttention(nn.Module):
                            md.seq_lens[:nd], self.scale, out=out[:nd].view(nd, Hq, D),
                            num_splits=md.decode_splits, workspace=md.decode_workspace,
                            kv_quant=kvq)
-        if md.num_prefills > 0:
+        if md.num_prefills > 0 and D not in (64, 128) and kvq is None:
+            # head sizes the prefill kernels do not cover (Gemma-7B: 256): torch formulation
+            npf = T - nd
+            sl = slice(md.num_decodes, md.num_decodes + md.num_prefills)
+            o = ref.varlen_prefill_attention(q[nd:].view(npf, Hq, D), k_cache, v_cache,
+                                             md.block_tables[sl], md.cu_q_prefill,
+                                             md.seq_lens[sl], self.scale, window=self.window)
+            out[nd:] = o.reshape(npf, Hq * D)
+        elif md.num_prefills > 0:
             npf = T - nd
             C.varlen_prefill(q[nd:].view(npf, Hq, D), k_cache, v_cache,
                              md.block_tables[md.num_decodes:md.num_decodes + md.num_prefills],

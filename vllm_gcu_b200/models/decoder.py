@@ -224,7 +224,7 @@ class DecoderLM(nn.Module):
             x = inputs_embeds if inputs_embeds is not None else self.embed_tokens(input_ids)
             scale = getattr(self, "embed_scale", None)
             if scale is not None and inputs_embeds is None:
-                x = x * torch.tensor(scale, dtype=x.dtype, device=x.device)
+                x = x * scale
             residual = None
         else:
             x, residual = intermediate

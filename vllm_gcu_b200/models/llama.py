@@ -10,6 +10,8 @@ from __future__ import annotations
 
 import dataclasses
 
+import torch
+
 from ..config import ModelConfig
 from .decoder import DecoderLM
 
@@ -114,7 +116,9 @@ class GemmaForCausalLM(DecoderLM):
                                                                            cfg.hidden_act)
         cfg = dataclasses.replace(cfg, hidden_act=act, tie_word_embeddings=True)
         super().__init__(cfg, device)
-        self.embed_scale = float(cfg.hidden_size) ** 0.5
+        # rounded to the model dtype first, as the reference implementation multiplies by a
+        # tensor of that dtype
+        self.embed_scale = float(torch.tensor(float(cfg.hidden_size) ** 0.5, dtype=cfg.dtype))
 
     def load_special(self, name, tensor, owners) -> bool:
         if name.endswith("norm.weight"):
