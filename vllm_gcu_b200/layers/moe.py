@@ -20,6 +20,8 @@ result, vllm_gcu/kernels/modular_kernel.py:288-295).
 """
 from __future__ import annotations
 
+import re
+
 from typing import Optional
 
 import torch
@@ -138,8 +140,8 @@ class FusedMoE(nn.Module):
         self.q8_channel = True
         return True
 
-    def load_expert_weight_q8(self, expert_id: int, which: str, weight: torch.Tensor,
-                              scale: Optional[torch.Tensor]) -> bool:
+    def _load_one_q8(self, expert_id: int, which: str, weight: torch.Tensor,
+                     scale: Optional[torch.Tensor]) -> bool:
         """8-bit ``weight [N, K]`` with a per-tensor or per-channel ``scale`` (None: 1)."""
         le = expert_id - self.expert_start
         if le < 0 or le >= self.local_experts:
@@ -164,8 +166,8 @@ class FusedMoE(nn.Module):
             raise ValueError(which)
         return True
 
-    def load_expert_weight_fp8(self, expert_id: int, which: str, weight: torch.Tensor,
-                               scale: torch.Tensor) -> bool:
+    def _load_one_fp8(self, expert_id: int, which: str, weight: torch.Tensor,
+                      scale: torch.Tensor) -> bool:
         """fp8 ``weight [N, K]`` with its ``scale [N/128, K/128]`` (``weight_scale_inv``)."""
         le = expert_id - self.expert_start
         if le < 0 or le >= self.local_experts:
@@ -187,7 +189,30 @@ class FusedMoE(nn.Module):
         return True
 
     # -- weights -------------------------------------------------------------------
+    def set_placement(self, phy2log) -> None:
+        """Physical slot -> logical expert (redundant experts): checkpoint tensors of a logical
+        expert are loaded into every physical slot that holds a replica of it."""
+        self.replicas: dict[int, list[int]] = {}
+        for p_, l_ in enumerate(phy2log.tolist() if hasattr(phy2log, "tolist") else phy2log):
+            self.replicas.setdefault(int(l_), []).append(p_)
+
+    def _slots(self, expert_id: int) -> list:
+        rp = getattr(self, "replicas", None)
+        return rp.get(expert_id, []) if rp else [expert_id]
+
     def load_expert_weight(self, expert_id: int, which: str, full: torch.Tensor) -> bool:
+        """Logical expert id (checkpoint numbering); True when a slot of this rank took it."""
+        return any([self._load_one(p_, which, full) for p_ in self._slots(expert_id)])
+
+    def load_expert_weight_q8(self, expert_id: int, which: str, weight: torch.Tensor,
+                              scale: Optional[torch.Tensor]) -> bool:
+        return any([self._load_one_q8(p_, which, weight, scale) for p_ in self._slots(expert_id)])
+
+    def load_expert_weight_fp8(self, expert_id: int, which: str, weight: torch.Tensor,
+                               scale: torch.Tensor) -> bool:
+        return any([self._load_one_fp8(p_, which, weight, scale) for p_ in self._slots(expert_id)])
+
+    def _load_one(self, expert_id: int, which: str, full: torch.Tensor) -> bool:
         """``which`` in {gate, up, down} (HF ``gate_proj`` / ``up_proj`` / ``down_proj`` or
         Mixtral ``w1`` / ``w3`` / ``w2``).  Returns False when the expert lives elsewhere."""
         le = expert_id - self.expert_start
@@ -325,7 +350,22 @@ class SparseMoeBlock(nn.Module):
                 self.experts.enable_q8_channel(torch.int8)
             elif kind == "fp8":
                 self.experts.enable_q8_channel(torch.float8_e4m3fn)
-        self.eplb = EplbState(cfg.num_experts, num_red, device) if num_red > 0 else None
+        phy2log = None
+        map_path = cfg.extra.get("expert_map_path")
+        if map_path:
+            # static placement file of the reference: (phy2log [moe layers, devices, experts per
+            # device], log2phy), vllm_gcu/models/deepseek_v3/deepseek_v3.py:880-913
+            loaded = torch.load(map_path, map_location="cpu")
+            table = loaded[0] if isinstance(loaded, (tuple, list)) else loaded
+            m_ = re.search(r"layers\.(\d+)\.", prefix + ".")
+            li = (int(m_.group(1)) if m_ else 0) - int(cfg.first_k_dense_replace or 0)
+            phy2log = table[max(li, 0)].reshape(-1).to(torch.int32)
+            assert phy2log.numel() == cfg.num_experts + num_red, \
+                "expert_map_path does not match num_experts + num_redundant_experts"
+        self.eplb = EplbState(cfg.num_experts, num_red, device, phy2log) \
+            if (num_red > 0 or phy2log is not None) else None
+        if self.eplb is not None:
+            self.experts.set_placement(self.eplb.phy2log)
         if cfg.num_shared_experts > 0:
             from ..models.decoder import DenseMLP
             self.shared_experts = DenseMLP(cfg, cfg.hidden_size,
