@@ -49,3 +49,21 @@ def test_static_placement_loads_replicas_and_matches_the_plain_model(tmp_path):
     got = [o.outputs[0].token_ids for o in red.generate(prompts, sp)]
     assert got == want
     assert torch.allclose(red.engine.runner.last_logits, plain.engine.runner.last_logits, atol=1e-4)
+
+
+def test_moe_chunking_gives_the_same_result(monkeypatch):
+    """``VLLM_FUSED_MOE_CHUNK_SIZE``: the routed-expert MLP over chunks of token rows equals the
+    unchunked computation (vllm_gcu/kernels/modular_kernel.py:167-286)."""
+    llm = _llm()
+    moe = next(l.mlp.experts for l in llm.engine.model.layers.values() if hasattr(l.mlp, "experts"))
+    cfg = llm.engine.cfg.model
+    g = torch.Generator().manual_seed(3)
+    T = 37
+    x = torch.randn(T, cfg.hidden_size, generator=g)
+    tw, ti = torch.topk(torch.softmax(torch.randn(T, cfg.num_experts, generator=g), -1),
+                        cfg.num_experts_per_tok, dim=-1)
+    add = torch.randn(T, cfg.hidden_size, generator=g)
+    want = moe(x, tw, ti.to(torch.int32), add=add)
+    monkeypatch.setenv("VLLM_FUSED_MOE_CHUNK_SIZE", "8")
+    got = moe(x, tw, ti.to(torch.int32), add=add)
+    assert torch.allclose(got, want, atol=1e-5)

@@ -43,6 +43,11 @@ environment_variables: dict[str, Callable[[], Any]] = {
     "REJECT_SAMPLER_CHECK": _flag("REJECT_SAMPLER_CHECK"),
     # synthetic round-robin routing (benchmarking expert-parallel balance)
     "FORCE_EP_BALANCE": _flag("FORCE_EP_BALANCE"),
+    # routed-expert MLP processes at most this many token rows at a time (bounds the
+    # permuted / intermediate buffers of very long prefill batches; the reference chunks by
+    # VLLM_FUSED_MOE_CHUNK_SIZE, vllm_gcu/kernels/modular_kernel.py:167-286)
+    "FUSED_MOE_CHUNK_SIZE": lambda: int(
+        os.environ.get("VLLM_FUSED_MOE_CHUNK_SIZE", _get("FUSED_MOE_CHUNK_SIZE", "32768"))),
     # comma-separated list of enabled forward hooks (entry-point group vllm_gcu_b200.hooks)
     "HOOKS": lambda: None if _get("HOOKS") is None else _get("HOOKS").split(","),
     # JSON file mapping GPUs to NICs for multi-node KV transfer

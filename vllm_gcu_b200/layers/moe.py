@@ -257,6 +257,18 @@ class FusedMoE(nn.Module):
         past it produce unspecified output."""
         if x.shape[0] == 0:
             return x if add is None else add
+        from .. import envs
+        chunk = envs.FUSED_MOE_CHUNK_SIZE
+        if chunk > 0 and x.shape[0] > chunk:
+            # chunks of token rows, each with its own clamp of the valid-row count
+            outs = []
+            for lo in range(0, x.shape[0], chunk):
+                hi = min(lo + chunk, x.shape[0])
+                vt = None if valid_tokens is None else (valid_tokens - lo).clamp(0, hi - lo).to(
+                    valid_tokens.dtype)
+                outs.append(self.forward(x[lo:hi], topk_w[lo:hi], topk_ids[lo:hi],
+                                         None if add is None else add[lo:hi], alpha, vt))
+            return torch.cat(outs, dim=0)
         if self.fp8_block:
             return C.fused_experts_fp8(x, self.w13, self.w13_scale, self.w2, self.w2_scale,
                                        topk_w, topk_ids, self.expert_map, add=add, alpha=alpha,
