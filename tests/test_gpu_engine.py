@@ -168,3 +168,28 @@ def test_gemma_head_dim_256_gpu_tracks_cpu_reference():
     lg, lc = gpu.engine.runner.last_logits, cpu.engine.runner.last_logits
     err = (lg - lc).abs().max().item()
     assert err < 0.06 * lc.std().item() + 0.03, (err, lc.std().item())
+
+
+def test_same_batch_twice_is_bitwise_identical():
+    """Determinism run (surfaces races in flag protocols and reductions): the same batch
+    through the same engine twice gives bitwise equal logits and tokens, eager and graphs."""
+    kw = dict(num_hidden_layers=2, hidden_size=512, intermediate_size=1024,
+              num_attention_heads=8, num_key_value_heads=2, head_dim=64, vocab_size=2048,
+              max_num_seqs=8, max_num_batched_tokens=256, max_model_len=256, num_gpu_blocks=128,
+              enable_prefix_caching=False)
+    llm = LLM("llama-3-8b", device="cuda", cuda_graph_sizes=[4, 8], **kw)
+    prompts = _prompts(6, [17, 40, 64, 3, 90, 33], 2048, seed=21)
+    sp = SamplingParams(max_tokens=8, temperature=0.7, top_k=20, top_p=0.9, seed=5,
+                        ignore_eos=True)
+    llm.engine.runner.keep_logits = True
+    runs = []
+    for _ in range(2):
+        outs = llm.generate(prompts, sp)
+        torch.cuda.synchronize()
+        runs.append(([o.outputs[0].token_ids for o in outs],
+                     llm.engine.runner.last_logits.clone()
+                     if llm.engine.runner.last_logits is not None else None))
+    assert runs[0][0] == runs[1][0]
+    if runs[0][1] is not None:
+        assert torch.equal(runs[0][1], runs[1][1])
+    _native.check_status()
