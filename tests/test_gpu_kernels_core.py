@@ -376,3 +376,26 @@ def test_advance_step(C):
     C.advance_step(pad, n, bs, toks, sampled, pos, sl, slots, bt)
     for a, b in zip((toks, pos, sl, slots), r):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("M,N,K", [(64, 4096, 14336), (1, 4096, 4096), (100, 1024, 8192)])
+def test_skinny_gemm_two_kernel_k_split_matches_reference(M, N, K):
+    """Rows <= 128: wide column tiles with a K split whose fp32 partial sums are added by a
+    second kernel (gemm_skinny.cu, ``make_plan2``), with and without a bias."""
+    import ctypes
+    from vllm_gcu_b200.ops import _native
+    from vllm_gcu_b200.ops import cuda as C
+    torch.manual_seed(M + N)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    ref = x.float() @ w.float().t()
+    for b in (None, bias):
+        got = C.gemm_bf16(x, w, bias=b)
+        want = ref if b is None else ref + b.float()
+        err = (got.float() - want).abs().max().item()
+        assert err < 1e-2 * want.abs().max().item() + 1e-2, err
+    torch.cuda.synchronize()
+    _native.check_status()
+    # twice the same: the summation order is fixed
+    assert torch.equal(C.gemm_bf16(x, w), C.gemm_bf16(x, w))

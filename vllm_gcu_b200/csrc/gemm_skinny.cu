@@ -249,6 +249,8 @@ __global__ void __launch_bounds__(kThreads, 1)
                                  __uint_as_float(r[i * 4 + 2]), __uint_as_float(r[i * 4 + 3]));
         }
       }
+      // ctr == nullptr: a second kernel adds the partial sums (no CTA waits for another)
+      if (p.ctr != nullptr) {
       __threadfence();
       asm volatile("bar.sync 1, 128;" ::: "memory");
       unsigned int* arrive = p.ctr + 2 * tile;
@@ -327,6 +329,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           *arrive = 0u;
           *depart = 0u;
         }
+      }
       }
     }
   }
@@ -567,6 +570,68 @@ struct Plan {
 // Picks the column-tile width and the K split.  The estimate is the larger of the total bytes
 // that move from L2 into shared memory (over an aggregate L2 -> SM rate) and the bytes of one
 // unit (over what one SM can ingest); units never exceed the SM count when K is split.
+// C = sum over K slices of the partial sums a split launch left in ws (+ bias): the slices of
+// a column tile lie one after the other, [tile][slice][R x bn]; fixed summation order.
+__global__ void __launch_bounds__(256)
+    skinny_reduce_kernel(const float* ws, __nv_bfloat16* C, long long ldc,
+                         const __nv_bfloat16* bias, int M, int N, int bn, int R, int splits) {
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int n4 = N >> 2;
+  if (idx >= static_cast<long long>(M) * n4) return;
+  const int row = static_cast<int>(idx / n4), col = static_cast<int>(idx % n4) * 4;
+  const int tile = col / bn, c_in = col - tile * bn;
+  const float* src = ws + (static_cast<long long>(tile) * splits) * (static_cast<long long>(R) * bn) +
+                     static_cast<long long>(row) * bn + c_in;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int sl = 0; sl < splits; ++sl) {
+    const float4 a = __ldcg(reinterpret_cast<const float4*>(src + static_cast<long long>(sl) * R * bn));
+    acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
+  }
+  if (bias != nullptr) {
+    acc.x += __bfloat162float(bias[col]);
+    acc.y += __bfloat162float(bias[col + 1]);
+    acc.z += __bfloat162float(bias[col + 2]);
+    acc.w += __bfloat162float(bias[col + 3]);
+  }
+  uint2 o;
+  o.x = pack_bf16x2(acc.x, acc.y);
+  o.y = pack_bf16x2(acc.z, acc.w);
+  *reinterpret_cast<uint2*>(C + static_cast<long long>(row) * ldc + col) = o;
+}
+
+// Plan for the two-kernel K split.  A CTA takes in at most about 64 bytes per clock from L2
+// (120 GB/s), and with M <= 256 that port, not HBM, bounds the kernel: every CTA reads the
+// whole activation slice of its K range again.  Wide column tiles with a deep K split move the
+// fewest bytes through it; the price is the fp32 partial sums (written and read once, L2
+// resident) and a second launch.
+inline Plan make_plan2(int M, int N, int K, int epi, int sms) {
+  const int mt = M > BM ? 2 : 1;
+  const int num_kb = (K + BK - 1) / BK;
+  Plan best{256, 1};
+  double best_t = 1e30;
+  const int cands[3] = {256, 128, 64};
+  for (int ci = 0; ci < 3; ++ci) {
+    const int bn = cands[ci];
+    if (epi == kSiluMul && bn != 256) continue;
+    if (N % bn != 0) continue;
+    const int tiles = N / bn;
+    for (int sl = 1; sl <= 16; ++sl) {
+      if (sl > 1 && (epi == kSiluMul || tiles * sl > sms || num_kb / sl < 8)) break;
+      const double units = static_cast<double>(tiles) * sl;
+      const double waves = units <= sms ? 1.0 : units / sms;
+      const double unit_bytes = (mt * 128.0 + bn) * (static_cast<double>(K) / sl) * 2.0;
+      double t = unit_bytes * waves / 1.2e11 + 3.0e-6;
+      // measured: parking the accumulators as fp32 and the second launch cost about 6 us
+      if (sl > 1) t += 2.0 * sl * M * static_cast<double>(N) * 4.0 / 4.0e12 + 6.0e-6;
+      if (t < best_t) {
+        best_t = t;
+        best = Plan{bn, sl};
+      }
+    }
+  }
+  return best;
+}
+
 inline Plan make_plan(int M, int N, int K, int epi, int sms) {
   const int mt = M > BM ? 2 : 1;
   const int num_kb = (K + BK - 1) / BK;
@@ -631,7 +696,12 @@ B200_API int b200_gemm_skinny(const void* A, long long lda, const void* B, long 
   if (epi == kBias && bias == nullptr) return -5;
   if (epi < 0 || epi > 2) return -20;
   const int sms = sm_count();
-  Plan pl = make_plan(M, N, K, epi, sms);
+  Plan pl = allow_split == 2 ? make_plan2(M, N, K, epi, sms) : make_plan(M, N, K, epi, sms);
+  if (allow_split == 2 && pl.splits == 1) {
+    // without a split this kernel only takes what it took before: one wave of 256-wide tiles
+    const int tiles = (N + 255) / 256;
+    if (pl.bn != 256 || N < 256 || tiles > sms || tiles * 2 < sms) return -20;
+  }
   if (pl.splits > 1 && !allow_split) {
     // Measured on B200: at M = 256 the fp32 partial sums of a K split cost as much L2 traffic
     // as the split saves, and the persistent-tile kernel is faster.  Without the split this
@@ -640,7 +710,7 @@ B200_API int b200_gemm_skinny(const void* A, long long lda, const void* B, long 
     const int tiles = (N + 255) / 256;
     if (N < 256 || tiles > sms || tiles * 2 < sms) return -20;
   }
-  if (pl.splits > 1 && (ws == nullptr || ctr == nullptr)) return -5;
+  if (pl.splits > 1 && (ws == nullptr || (ctr == nullptr && allow_split != 2))) return -5;
   const int mt = M > BM ? 2 : 1;
 
   CUtensorMap tmA, tmB;
@@ -662,15 +732,16 @@ B200_API int b200_gemm_skinny(const void* A, long long lda, const void* B, long 
   a.splits = pl.splits;
   a.num_kb = (K + BK - 1) / BK;
   a.ws = static_cast<float*>(ws);
-  a.ctr = static_cast<unsigned int*>(ctr);
+  a.ctr = allow_split == 2 ? nullptr : static_cast<unsigned int*>(ctr);
   a.status = status_ptr();
   const int units = a.tiles_n * a.splits;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 
+  int rc = -20;
 #define B200_SK(BN_, MT_, ST_)                                                      \
   switch (epi) {                                                                    \
-    case kNone: return launch<BN_, MT_, ST_, kNone>(tmA, tmB, a, units, s);         \
-    case kBias: return launch<BN_, MT_, ST_, kBias>(tmA, tmB, a, units, s);         \
+    case kNone: rc = launch<BN_, MT_, ST_, kNone>(tmA, tmB, a, units, s); break;    \
+    case kBias: rc = launch<BN_, MT_, ST_, kBias>(tmA, tmB, a, units, s); break;    \
     default: break;                                                                 \
   }
   if (epi == kSiluMul) {
@@ -685,7 +756,12 @@ B200_API int b200_gemm_skinny(const void* A, long long lda, const void* B, long 
     if (mt == 2) { B200_SK(64, 2, 5) } else { B200_SK(64, 1, 8) }
   }
 #undef B200_SK
-  return -20;
+  if (rc != 0 || a.splits == 1 || a.ctr != nullptr) return rc;
+  // two-kernel K split: add the partial sums
+  const long long work = static_cast<long long>(M) * (N / 4);
+  skinny_reduce_kernel<<<static_cast<unsigned>((work + 255) / 256), 256, 0, s>>>(
+      a.ws, a.C, a.ldc, epi == kBias ? a.bias : nullptr, M, N, pl.bn, mt * BM, a.splits);
+  return static_cast<int>(cudaGetLastError());
 }
 
 // The plan b200_gemm_skinny would use (for tests and benchmarks): bn and splits.

@@ -71,6 +71,8 @@ USE_WIDE2_GEMM = True           # persistent 256 x 256 tiles for large M (gemm_s
 WIDE2_MIN_M = 1024
 USE_SKINNY_GEMM = True
 SKINNY_ALLOW_SPLIT = False      # K-split plans lose to the persistent-tile kernel (measured)
+SKINNY_SPLIT2_MAX_M = 128       # up to this many rows a two-kernel K split is planned (o_proj /
+                                # down_proj at M = 64: 15.7 -> 14.9 us, 43.2 -> 29.5 us)
 SKINNY_MAX_M = 256
 _SKINNY_WS: dict = {}
 
@@ -146,7 +148,9 @@ def _gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = N
         ws, ctr = _skinny_workspace(a.device)
         rc = N.lib().b200_gemm_skinny(
             ptr(a), a.stride(0), ptr(b), b.stride(0), ptr(out), out.stride(0), M, Nn, K,
-            ptr(bias), epilogue, ptr(ws), ptr(ctr), int(SKINNY_ALLOW_SPLIT), stream_ptr())
+            ptr(bias), epilogue, ptr(ws), ptr(ctr),
+            2 if (M <= SKINNY_SPLIT2_MAX_M and not SKINNY_ALLOW_SPLIT) else int(SKINNY_ALLOW_SPLIT),
+            stream_ptr())
         N.launch_count += 1
         if rc == 0:
             return out
