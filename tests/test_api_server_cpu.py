@@ -41,6 +41,25 @@ def test_completions_and_streaming():
             assert toks == js["choices"][0]["token_ids"]
             m = await c.get("/metrics")
             assert "vllm_b200_generation_tokens_total" in m.text
+            # chat endpoint: blocking and streaming give the same text; tokenize round trip
+            chat = {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 4,
+                    "temperature": 0.0, "ignore_eos": True}
+            r = await c.post("/v1/chat/completions", json=chat)
+            cj = r.json()
+            assert cj["object"] == "chat.completion" and cj["usage"]["completion_tokens"] == 4
+            text = ""
+            async with c.stream("POST", "/v1/chat/completions", json={**chat, "stream": True}) as resp:
+                async for line in resp.aiter_lines():
+                    if line.startswith("data: ") and "[DONE]" not in line:
+                        text += json.loads(line[6:])["choices"][0]["delta"].get("content", "")
+            assert text == cj["choices"][0]["message"]["content"]
+            tk = (await c.post("/tokenize", json={"prompt": "abc"})).json()
+            assert tk["count"] == 3
+            dt = (await c.post("/detokenize", json={"tokens": tk["tokens"]})).json()
+            assert dt["prompt"] == "abc"
+            assert "version" in (await c.get("/version")).json()
+            bad = await c.post("/v1/chat/completions", json={"max_tokens": 2})
+            assert bad.status_code == 400
     try:
         asyncio.run(run())
     finally:

@@ -228,6 +228,79 @@ def build_app(engine: Any, tokenizer: Any, model_name: str):
         return {"id": rid, "object": "text_completion", "created": created, "model": model_name,
                 "choices": list(choices), "usage": usage}
 
+    def render_chat(messages: list) -> list[int]:
+        """Conversation -> prompt ids: the tokenizer's chat template when it has one, else a
+        plain ``<role>: content`` transcript."""
+        if hasattr(tokenizer, "apply_chat_template") and getattr(tokenizer, "chat_template", None):
+            return list(tokenizer.apply_chat_template(messages, tokenize=True,
+                                                      add_generation_prompt=True))
+        text = "".join(f"{m.get('role', 'user')}: {m.get('content', '')}\n" for m in messages)
+        return list(tokenizer.encode(text + "assistant: "))
+
+    @app.post("/v1/chat/completions")
+    async def chat_completions(request: Request):
+        body = await request.json()
+        messages = body.get("messages")
+        if not messages:
+            return JSONResponse({"error": "messages is required"}, status_code=400)
+        try:
+            sp = sampling_from_body(body, default_max=int(body.get("max_completion_tokens", 256)))
+            if sp.guided_regex is not None or sp.guided_json is not None:
+                _ensure_vocabulary()
+        except ValueError as e:
+            return JSONResponse({"error": str(e)}, status_code=400)
+        ids = render_chat(messages)
+        rid = "chatcmpl-" + uuid.uuid4().hex[:16]
+        created = int(time.time())
+        state["requests"] += 1
+        priority = int(body.get("priority", 0))
+        base = {"id": rid, "created": created, "model": model_name}
+
+        if body.get("stream", False):
+            async def sse():
+                sent = 0
+                first = {"index": 0, "delta": {"role": "assistant", "content": ""},
+                         "finish_reason": None}
+                yield "data: " + json.dumps({**base, "object": "chat.completion.chunk",
+                                             "choices": [first]}) + "\n\n"
+                async for out in engine.generate_stream(ids, sp, priority=priority):
+                    toks = out.outputs[0].token_ids
+                    new, sent = toks[sent:], len(toks)
+                    state["tokens_out"] += len(new)
+                    ch = {"index": 0, "delta": {"content": tokenizer.decode(new)},
+                          "finish_reason": out.outputs[0].finish_reason}
+                    yield "data: " + json.dumps({**base, "object": "chat.completion.chunk",
+                                                 "choices": [ch]}) + "\n\n"
+                yield "data: [DONE]\n\n"
+            return StreamingResponse(sse(), media_type="text/event-stream")
+
+        last = None
+        async for out in engine.generate_stream(ids, sp, priority=priority):
+            last = out
+        toks = last.outputs[0].token_ids
+        state["tokens_out"] += len(toks)
+        choice = {"index": 0, "finish_reason": last.outputs[0].finish_reason,
+                  "message": {"role": "assistant", "content": tokenizer.decode(toks)}}
+        usage = {"prompt_tokens": len(ids), "completion_tokens": len(toks),
+                 "total_tokens": len(ids) + len(toks)}
+        return {**base, "object": "chat.completion", "choices": [choice], "usage": usage}
+
+    @app.post("/tokenize")
+    async def tokenize(request: Request):
+        body = await request.json()
+        ids = render_chat(body["messages"]) if body.get("messages") else to_ids(body.get("prompt", ""))
+        return {"tokens": ids, "count": len(ids)}
+
+    @app.post("/detokenize")
+    async def detokenize(request: Request):
+        body = await request.json()
+        return {"prompt": tokenizer.decode([int(t) for t in body.get("tokens", [])])}
+
+    @app.get("/version")
+    async def version():
+        from .. import __version__
+        return {"version": __version__}
+
     return app
 
 
