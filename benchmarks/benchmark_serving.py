@@ -1,4 +1,5 @@
-"""Online serving benchmark against an OpenAI-compatible ``/v1/completions`` endpoint.
+"""Online serving benchmark against an OpenAI-compatible ``/v1/completions`` (or, with
+``--backend openai-chat``, ``/v1/chat/completions``) endpoint.
 
 Poisson (gamma with configurable burstiness) arrivals, random token-id prompts with uniform
 input / output lengths, streaming responses; reports request and token throughput and
@@ -33,7 +34,11 @@ async def one_request(session, url, body, result):
                 if not line.startswith("data: ") or line.endswith("[DONE]"):
                     continue
                 now = time.perf_counter()
-                n_new = len(json.loads(line[6:])["choices"][0].get("token_ids", [1]))
+                choice = json.loads(line[6:])["choices"][0]
+                if "delta" in choice:            # chat endpoint: one chunk per engine step
+                    n_new = 1 if choice["delta"].get("content") else 0
+                else:
+                    n_new = len(choice.get("token_ids", [1]))
                 if n_new == 0:
                     continue
                 if ttft is None:
@@ -43,7 +48,8 @@ async def one_request(session, url, body, result):
                 last = now
                 n_out += n_new
         result.append({"ok": True, "ttft": ttft, "e2e": last - t0, "itl": itl, "n_out": n_out,
-                       "n_in": len(body["prompt"])})
+                       "n_in": len(body["prompt"]) if "prompt" in body
+                       else sum(len(m["content"]) for m in body["messages"])})
     except Exception as e:  # noqa: BLE001
         result.append({"ok": False, "error": repr(e)})
 
@@ -52,7 +58,8 @@ async def run(args):
     import aiohttp
     rng = random.Random(args.seed)
     nprng = np.random.default_rng(args.seed)
-    url = f"http://{args.host}:{args.port}/v1/completions"
+    chat = args.backend == "openai-chat"
+    url = f"http://{args.host}:{args.port}/v1/" + ("chat/completions" if chat else "completions")
     extra = json.loads(args.extra_body) if args.extra_body else {}
     results: list = []
     tasks = []
@@ -62,9 +69,13 @@ async def run(args):
         for i in range(args.num_prompts):
             n_in = rng.randint(*args.input_len_range)
             n_out = rng.randint(*args.output_len_range)
-            body = {"prompt": [rng.randrange(10, args.vocab_size) for _ in range(n_in)],
-                    "max_tokens": n_out, "temperature": args.temperature, "stream": True,
+            body = {"max_tokens": n_out, "temperature": args.temperature, "stream": True,
                     "ignore_eos": True}
+            if chat:     # random printable text of about n_in characters
+                text = "".join(chr(rng.randrange(97, 123)) for _ in range(n_in))
+                body["messages"] = [{"role": "user", "content": text}]
+            else:
+                body["prompt"] = [rng.randrange(10, args.vocab_size) for _ in range(n_in)]
             body.update(extra)
             tasks.append(asyncio.create_task(one_request(session, url, body, results)))
             if args.request_rate != float("inf"):
@@ -101,6 +112,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--host", default="127.0.0.1")
     ap.add_argument("--port", type=int, default=8000)
+    ap.add_argument("--backend", default="openai", choices=["openai", "openai-chat"],
+                    help="/v1/completions with token-id prompts, or /v1/chat/completions")
     ap.add_argument("--num-prompts", type=int, default=1000)
     ap.add_argument("--request-rate", type=float, default=float("inf"))
     ap.add_argument("--burstiness", type=float, default=1.0)
