@@ -186,3 +186,15 @@ def test_moe_checkpoints_awq_fp8_block_and_int8_load_into_the_expert_tensors():
             a, b = m_ref.layers[str(li)].mlp.experts, m_q.layers[str(li)].mlp.experts
             assert torch.allclose(a.w13.data, b.w13.data, atol=1e-5), kind
             assert torch.allclose(a.w2.data, b.w2.data, atol=1e-5), kind
+
+
+def test_expert_storage_by_checkpoint_format():
+    """Which quantised expert formats stay quantised on a GPU (layers/quant/moe.py)."""
+    from vllm_gcu_b200.layers.quant.moe import expert_storage
+    assert expert_storage("fp8", {"quant_method": "fp8", "weight_block_size": [128, 128]}) == "fp8_block"
+    assert expert_storage("fp8_gcu", {"weight_block_size": [64, 64]}) is None
+    assert expert_storage("fp8", {"quant_method": "fp8"}) == "fp8"
+    assert expert_storage("w8a8_gcu", {}) == "int8"
+    assert expert_storage("compressed-tensors", {"quant_method": "compressed-tensors"}) == "int8"
+    assert expert_storage("moe_wna16_gcu", {"quant_method": "awq", "bits": 4}) is None
+    assert expert_storage(None, None) is None
