@@ -216,7 +216,8 @@ def main() -> None:
         value = tot_out / (dev_ms / 1e3)
         e2e = tot_out / (wall_ms / 1e3)
         line = {
-            "metric": "output tok/s per box (offline throughput, 512 req x 1024 in / 256 out)",
+            "metric": (f"output tok/s per box (offline throughput, {args.num_prompts} req x "
+                       f"{args.input_len} in / {args.output_len} out)"),
             "value": round(value, 2), "unit": "tok/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(dev_ms / args.steps, 3), "higher_is_better": True,
