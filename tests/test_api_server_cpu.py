@@ -64,3 +64,41 @@ def test_completions_and_streaming():
         asyncio.run(run())
     finally:
         eng.shutdown()
+
+
+@pytest.mark.timeout(120)
+def test_pooling_endpoints_embed_score_rerank():
+    """/v1/embeddings, /score and /rerank on a tiny XLM-RoBERTa cross-encoder."""
+    httpx = pytest.importorskip("httpx")
+    from vllm_gcu_b200.models import build_pooling_model
+    hf = {"architectures": ["XLMRobertaForSequenceClassification"], "vocab_size": 400,
+          "hidden_size": 32, "num_hidden_layers": 2, "num_attention_heads": 2,
+          "intermediate_size": 64, "max_position_embeddings": 130, "pad_token_id": 1,
+          "num_labels": 1, "type_vocab_size": 1, "layer_norm_eps": 1e-5}
+    import torch
+    torch.manual_seed(0)
+    pooler = build_pooling_model(hf, dtype=torch.float32)
+    for p in pooler.model.parameters():
+        torch.nn.init.normal_(p, std=0.05)
+    app = build_app(None, ByteTokenizer(400), "tiny-reranker", pooler=pooler)
+
+    async def run():
+        transport = httpx.ASGITransport(app=app)
+        async with httpx.AsyncClient(transport=transport, base_url="http://t") as c:
+            e = (await c.post("/v1/embeddings", json={"input": ["ab", "cde"]})).json()
+            assert len(e["data"]) == 2 and e["usage"]["prompt_tokens"] == 5
+            body = {"query": "q", "documents": ["aa", "bbbb", "c"]}
+            sc = (await c.post("/score", json=body)).json()["data"]
+            assert [d["index"] for d in sc] == [0, 1, 2]
+            rr = (await c.post("/rerank", json={**body, "top_n": 2})).json()["results"]
+            want = sorted(sc, key=lambda d: -d["score"])[:2]
+            assert [r["index"] for r in rr] == [d["index"] for d in want]
+            assert rr[0]["relevance_score"] >= rr[1]["relevance_score"]
+    asyncio.run(run())
+    # a generation-only server declines
+    app2 = build_app(None, ByteTokenizer(400), "x")
+
+    async def run2():
+        async with httpx.AsyncClient(transport=httpx.ASGITransport(app=app2), base_url="http://t") as c:
+            assert (await c.post("/score", json={"query": "a", "documents": ["b"]})).status_code == 400
+    asyncio.run(run2())

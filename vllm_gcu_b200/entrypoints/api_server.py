@@ -96,7 +96,7 @@ def _guided_schema(body: dict):
     return None
 
 
-def build_app(engine: Any, tokenizer: Any, model_name: str):
+def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None):
     if FastAPI is None:
         raise RuntimeError("the API server needs the fastapi package")
     app = FastAPI()
@@ -296,6 +296,62 @@ def build_app(engine: Any, tokenizer: Any, model_name: str):
         body = await request.json()
         return {"prompt": tokenizer.decode([int(t) for t in body.get("tokens", [])])}
 
+    # -- pooling models (embedding / cross-encoder): ``pooler`` is a models.roberta.PoolingRunner
+    def _need_pooler():
+        if pooler is None:
+            return JSONResponse({"error": "this server was not started with a pooling model"},
+                                status_code=400)
+        return None
+
+    def _as_ids(x) -> list[int]:
+        return [int(t) for t in x] if isinstance(x, list) and x and isinstance(x[0], int) \
+            else list(tokenizer.encode(str(x)))
+
+    @app.post("/v1/embeddings")
+    async def embeddings(request: Request):
+        err = _need_pooler()
+        if err is not None:
+            return err
+        body = await request.json()
+        inp = body.get("input")
+        items = inp if isinstance(inp, list) and inp and not isinstance(inp[0], int) else [inp]
+        seqs = [_as_ids(x) for x in items]
+        vecs = pooler.run(seqs).float().tolist()
+        return {"object": "list", "model": model_name,
+                "data": [{"object": "embedding", "index": i, "embedding": v}
+                         for i, v in enumerate(vecs)],
+                "usage": {"prompt_tokens": sum(len(q) for q in seqs)}}
+
+    async def _scores(request: Request):
+        body = await request.json()
+        query = body.get("query", body.get("text_1"))
+        docs = body.get("documents", body.get("text_2"))
+        docs = docs if isinstance(docs, list) and docs and not isinstance(docs[0], int) else [docs]
+        q = _as_ids(query)
+        d = [_as_ids(x) for x in docs]
+        sep = int(body.get("sep_token_id", getattr(tokenizer, "sep_token_id", None) or 2))
+        return body, docs, pooler.score(q, d, sep)
+
+    @app.post("/score")
+    async def score(request: Request):
+        err = _need_pooler()
+        if err is not None:
+            return err
+        _, _, sc = await _scores(request)
+        return {"object": "list", "model": model_name,
+                "data": [{"object": "score", "index": i, "score": v} for i, v in enumerate(sc)]}
+
+    @app.post("/rerank")
+    async def rerank(request: Request):
+        err = _need_pooler()
+        if err is not None:
+            return err
+        body, docs, sc = await _scores(request)
+        order = sorted(range(len(sc)), key=lambda i: -sc[i])[: int(body.get("top_n", len(sc)))]
+        return {"model": model_name,
+                "results": [{"index": i, "relevance_score": sc[i], "document": docs[i]}
+                            for i in order]}
+
     @app.get("/version")
     async def version():
         from .. import __version__
@@ -364,6 +420,24 @@ def main() -> None:
                     help="port of the point-to-point KV connector (disaggregated prefill)")
     ap.add_argument("--kv-send-type", default="PUT_ASYNC", choices=["PUT", "PUT_ASYNC", "GET"])
     args = ap.parse_args()
+    import os
+    cfg_path = os.path.join(args.model, "config.json") if os.path.isdir(args.model) else None
+    if cfg_path and os.path.exists(cfg_path):
+        # embedding / reranker checkpoints are served by the pooling runner (no KV cache)
+        from ..models import POOLING_ARCHITECTURES, build_pooling_model
+        hf = json.load(open(cfg_path))
+        if (hf.get("architectures") or [""])[0] in POOLING_ARCHITECTURES:
+            import torch
+            dev = "cuda" if (args.device == "auto" and torch.cuda.is_available()) else \
+                ("cpu" if args.device == "auto" else args.device)
+            pooler = build_pooling_model(hf, dev)
+            from ..utils.weights import iter_safetensors
+            pooler.model.load_weights(iter_safetensors(args.model))
+            tok = load_tokenizer(args.tokenizer or args.model, int(hf.get("vocab_size", 0)))
+            import uvicorn
+            uvicorn.run(build_app(None, tok, args.model, pooler=pooler), host=args.host,
+                        port=args.port, log_level="warning")
+            return
     engine, mc = make_engine(args)
     tok = load_tokenizer(args.tokenizer or (args.model if "/" in args.model else None),
                          mc.vocab_size)
