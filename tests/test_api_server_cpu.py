@@ -58,6 +58,14 @@ def test_completions_and_streaming():
             dt = (await c.post("/detokenize", json={"tokens": tk["tokens"]})).json()
             assert dt["prompt"] == "abc"
             assert "version" in (await c.get("/version")).json()
+            # prompts the scheduler would refuse are answered with 400, not queued
+            r = await c.post("/v1/completions", json={"prompt": [[]], "max_tokens": 2})
+            assert r.status_code == 400
+            r = await c.post("/v1/completions", json={"prompt": [[1] * 500], "max_tokens": 2})
+            assert r.status_code == 400
+            r = await c.post("/v1/completions", json={"prompt": [1, 2], "max_tokens": 2,
+                                                      "temperature": 0.0, "ignore_eos": True})
+            assert r.status_code == 200 and len(r.json()["choices"][0]["token_ids"]) == 2
             bad = await c.post("/v1/chat/completions", json={"max_tokens": 2})
             assert bad.status_code == 400
     try:

@@ -108,3 +108,53 @@ def test_text_prompts_and_chat_with_a_tokenizer():
     import pytest
     with pytest.raises(ValueError):
         _llm().generate("text without a tokenizer", sp)
+
+
+def test_constraints_hold_with_ngram_drafts_in_the_same_batch():
+    """A constrained request gets no draft tokens, and its mask is applied even when another
+    request of the batch is verifying drafts in the same step."""
+    llm = _llm(speculative_method="ngram", num_speculative_tokens=3)
+    base = _prompt(8, 5)
+    rep = base * 3                      # repetitive: the proposer finds drafts for it
+    sps = [SamplingParams(max_tokens=12, temperature=0.0, ignore_eos=True),
+           SamplingParams(max_tokens=12, temperature=0.0, ignore_eos=True,
+                          allowed_token_ids=(5, 6, 7)),
+           SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True,
+                          guided_choice=((11, 12, 13, 14), (11, 15)))]
+    outs = llm.generate([rep, rep, rep], sps)
+    assert set(outs[1].outputs[0].token_ids) <= {5, 6, 7}
+    assert tuple(outs[2].outputs[0].token_ids) in ((11, 12, 13, 14), (11, 15))
+    assert llm.engine.spec_metrics.num_drafts > 0
+
+
+def test_guided_request_added_while_async_steps_are_in_flight():
+    """The engine retires the steps in flight before a request whose mask depends on its own
+    history starts, and goes back to asynchronous scheduling when that request is gone."""
+    llm = _llm(async_scheduling=True)
+    eng = llm.engine
+    bg = eng.add_request(_prompt(12, 6), SamplingParams(max_tokens=40, temperature=0.0,
+                                                         ignore_eos=True))
+    for _ in range(4):
+        eng.step()
+    assert eng._pending, "a step should be in flight"
+    gid = eng.add_request(_prompt(9, 7), SamplingParams(
+        max_tokens=8, temperature=0.0, ignore_eos=True, guided_choice=((11, 12, 13, 14),)))
+    done = {}
+    while eng.has_unfinished():
+        for o in eng.step():
+            if o.finished:
+                done[o.request_id] = o
+    assert list(done[gid].outputs[0].token_ids) == [11, 12, 13, 14]
+    assert len(done[bg].outputs[0].token_ids) == 40
+    assert eng.cfg.scheduler.async_scheduling and eng.scheduler.async_mode
+
+
+def test_empty_prompt_is_rejected_and_does_not_block_the_queue():
+    import pytest
+    llm = _llm()
+    eng = llm.engine
+    with pytest.raises(ValueError):
+        eng.add_request([], SamplingParams(max_tokens=4))
+    out = llm.generate([_prompt(6, 8)], SamplingParams(max_tokens=4, temperature=0.0,
+                                                       ignore_eos=True))[0]
+    assert len(out.outputs[0].token_ids) == 4

@@ -838,6 +838,7 @@ B200_API int b200_merge_attn_states(void* out, float* out_lse, const void* p_out
 #include "no_alloc.h"
 
 #include <cstdio>
+#include <mutex>
 
 namespace {
 
@@ -853,28 +854,41 @@ struct NoAllocPtrs {
   float* lse = nullptr;
 };
 
-// Resolved once per device, with that device current.
+// Resolved once per device, with that device current.  std::call_once orders the stores to
+// the cache entry before every later reader on any host thread.
 int noalloc_ptrs(NoAllocPtrs* res) {
-  static NoAllocPtrs cache[64];
+  constexpr int kMaxDevices = 64;
+  static NoAllocPtrs cache[kMaxDevices];
+  static cudaError_t setup_err[kMaxDevices];
+  static std::once_flag once[kMaxDevices];
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess || dev < 0 || dev >= 64) {
-    snprintf(t_noalloc_err, sizeof(t_noalloc_err), "cudaGetDevice failed (%d)", (int)e);
+  if (e != cudaSuccess) {
+    snprintf(t_noalloc_err, sizeof(t_noalloc_err), "cudaGetDevice failed: %s",
+             cudaGetErrorString(e));
     return B200_NOALLOC_SETUP_FAILED;
   }
-  if (cache[dev].out == nullptr) {
+  if (dev < 0 || dev >= kMaxDevices) {
+    snprintf(t_noalloc_err, sizeof(t_noalloc_err),
+             "device ordinal %d is outside the %d devices this entry point keeps a workspace "
+             "address for", dev, kMaxDevices);
+    return B200_NOALLOC_SETUP_FAILED;
+  }
+  std::call_once(once[dev], [dev]() {
     void* po = nullptr;
     void* pl = nullptr;
-    e = cudaGetSymbolAddress(&po, g_noalloc_out);
-    if (e == cudaSuccess) e = cudaGetSymbolAddress(&pl, g_noalloc_lse);
-    if (e != cudaSuccess || po == nullptr || pl == nullptr) {
-      snprintf(t_noalloc_err, sizeof(t_noalloc_err),
-               "cudaGetSymbolAddress for the built-in workspace failed: %s",
-               cudaGetErrorString(e));
-      return B200_NOALLOC_SETUP_FAILED;
-    }
+    cudaError_t e2 = cudaGetSymbolAddress(&po, g_noalloc_out);
+    if (e2 == cudaSuccess) e2 = cudaGetSymbolAddress(&pl, g_noalloc_lse);
+    if (e2 == cudaSuccess && (po == nullptr || pl == nullptr)) e2 = cudaErrorInvalidSymbol;
+    setup_err[dev] = e2;
     cache[dev].lse = static_cast<float*>(pl);
     cache[dev].out = static_cast<float*>(po);
+  });
+  if (setup_err[dev] != cudaSuccess) {
+    snprintf(t_noalloc_err, sizeof(t_noalloc_err),
+             "cudaGetSymbolAddress for the built-in workspace failed: %s",
+             cudaGetErrorString(setup_err[dev]));
+    return B200_NOALLOC_SETUP_FAILED;
   }
   *res = cache[dev];
   return 0;
@@ -893,7 +907,11 @@ B200_API int b200_paged_decode_noalloc(const void* q, long long ldq, void* out, 
                                        int dtype, void* stream) {
   t_noalloc_err[0] = 0;
   if (B <= 0) return 0;
-  if (num_splits < 1) num_splits = 1;
+  if (num_splits < 1) {
+    snprintf(t_noalloc_err, sizeof(t_noalloc_err), "num_splits must be at least 1 (got %d)",
+             num_splits);
+    return -2;   // the code b200_paged_decode returns for the same argument
+  }
   const long long need_out = static_cast<long long>(B) * Hq * num_splits * HD;
   const long long need_lse = static_cast<long long>(B) * Hq * num_splits;
   if (num_splits > 1 &&

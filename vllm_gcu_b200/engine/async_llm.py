@@ -5,6 +5,7 @@ from __future__ import annotations
 
 import asyncio
 import itertools
+import queue
 import threading
 import time
 from typing import AsyncIterator, Optional, Sequence
@@ -17,7 +18,8 @@ from .request import RequestOutput, SamplingParams
 class AsyncLLM:
     def __init__(self, cfg: EngineConfig):
         self.engine = LLMEngine(cfg)
-        self._lock = threading.Lock()
+        self._lock = threading.Lock()          # guards engine state against stats()
+        self._inbox: queue.SimpleQueue = queue.SimpleQueue()   # ("add", kwargs) / ("abort", rid)
         self._streams: dict[str, tuple[asyncio.AbstractEventLoop, asyncio.Queue]] = {}
         self._ids = itertools.count()
         self._stop = threading.Event()
@@ -30,6 +32,7 @@ class AsyncLLM:
         try:
             while not self._stop.is_set():
                 with self._lock:
+                    self._drain_inbox()
                     busy = self.engine.has_unfinished()
                     outs = self.engine.step() if busy else []
                 for o in outs:
@@ -45,6 +48,33 @@ class AsyncLLM:
             for loop, q in list(self._streams.values()):
                 loop.call_soon_threadsafe(q.put_nowait, e)
 
+    def _drain_inbox(self) -> None:
+        """Applies the submissions and aborts that arrived since the last step (engine thread)."""
+        while True:
+            try:
+                kind, arg = self._inbox.get_nowait()
+            except queue.Empty:
+                return
+            if kind == "abort":
+                self.engine.abort_request(arg)
+                continue
+            try:
+                self.engine.add_request(**arg)
+            except Exception as e:  # noqa: BLE001  (reported to the one caller, not fatal)
+                ent = self._streams.get(arg["request_id"])
+                if ent is not None:
+                    ent[0].call_soon_threadsafe(ent[1].put_nowait, e)
+
+    def validate_prompt(self, prompt_token_ids: Sequence[int]) -> None:
+        """Raises ValueError for a prompt the scheduler would refuse (empty, or longer than
+        the model length); callable from any thread."""
+        n = len(prompt_token_ids)
+        if n == 0:
+            raise ValueError("the prompt is empty")
+        limit = self.engine.cfg.scheduler.max_model_len
+        if n >= limit:
+            raise ValueError(f"prompt of {n} tokens exceeds max_model_len {limit}")
+
     async def generate_stream(self, prompt_token_ids: Sequence[int],
                               sampling_params: Optional[SamplingParams] = None,
                               request_id: Optional[str] = None, priority: int = 0,
@@ -52,34 +82,41 @@ class AsyncLLM:
                               ) -> AsyncIterator[RequestOutput]:
         if self.error is not None:
             raise RuntimeError(f"engine failed: {self.error!r}")
+        self.validate_prompt(prompt_token_ids)
         rid = request_id or f"areq-{next(self._ids)}"
         q: asyncio.Queue = asyncio.Queue()
         self._streams[rid] = (asyncio.get_running_loop(), q)
-        with self._lock:
-            self.engine.add_request(prompt_token_ids, sampling_params, rid, priority,
-                                    lora_id=lora_id, kv_transfer_params=kv_transfer_params)
+        # the engine thread holds its lock for a whole step: hand the request over through the
+        # inbox instead of blocking the event loop on that lock
+        self._inbox.put(("add", dict(prompt_token_ids=prompt_token_ids,
+                                     sampling_params=sampling_params, request_id=rid,
+                                     priority=priority, lora_id=lora_id,
+                                     kv_transfer_params=kv_transfer_params)))
         self._wake.set()
         try:
             while True:
                 item = await q.get()
+                if isinstance(item, ValueError):
+                    raise item
                 if isinstance(item, BaseException):
                     raise RuntimeError(f"engine failed: {item!r}")
                 yield item
                 if item.finished:
                     break
         except asyncio.CancelledError:
-            with self._lock:
-                self.engine.abort_request(rid)
+            self._inbox.put(("abort", rid))
+            self._wake.set()
             raise
         finally:
             self._streams.pop(rid, None)
 
     def stats(self) -> dict:
-        with self._lock:
-            s = dict(self.engine.scheduler.stats())
-            s.update(self.engine.stats)
-            if self.engine.spec_metrics is not None:
-                s["spec_acceptance_rate"] = self.engine.spec_metrics.acceptance_rate
+        # read-only snapshot of counters: taken without the step lock so that a metrics
+        # request never waits for a running step
+        s = dict(self.engine.scheduler.stats())
+        s.update(self.engine.stats)
+        if self.engine.spec_metrics is not None:
+            s["spec_acceptance_rate"] = self.engine.spec_metrics.acceptance_rate
         return s
 
     def shutdown(self) -> None:

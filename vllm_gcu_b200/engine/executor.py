@@ -371,10 +371,20 @@ class AsyncMultiprocExecutor(MultiprocExecutor):
         self._pump = threading.Thread(target=run, daemon=True)
         self._pump.start()
 
+    def validate_prompt(self, prompt_token_ids: Sequence[int]) -> None:
+        """Raises ValueError for a prompt the workers' scheduler would refuse."""
+        n = len(prompt_token_ids)
+        if n == 0:
+            raise ValueError("the prompt is empty")
+        limit = self.cfg.scheduler.max_model_len
+        if n >= limit:
+            raise ValueError(f"prompt of {n} tokens exceeds max_model_len {limit}")
+
     async def generate_stream(self, prompt_token_ids: Sequence[int],
                               sampling_params: Optional[SamplingParams] = None,
                               request_id: Optional[str] = None, priority: int = 0
                               ) -> AsyncIterator[RequestOutput]:
+        self.validate_prompt(prompt_token_ids)
         self._ensure_pump()
         q: asyncio.Queue = asyncio.Queue()
         rid = request_id or f"areq-{self._ids}"

@@ -149,11 +149,10 @@ class LLMEngine:
             if req.eos_token_id is None:     # a guided request ends with EOS once it matches
                 req.eos_token_id = getattr(self.cfg.model, "eos_token_id", None)
             req.guide = self._make_guide(sp_, req.eos_token_id)
-        if (sp_.has_penalties or sp_.logprobs is not None or sp_.prompt_logprobs is not None
-                or sp_.constrained):
+        self.scheduler.add_request(req)
+        if sp_.needs_host_history:
             # these need the ids of every earlier token on the host before the next step
             self._want_sync = True
-        self.scheduler.add_request(req)
         return rid
 
     def set_vocabulary(self, vocab: Sequence[Optional[str]]) -> None:
@@ -262,10 +261,18 @@ class LLMEngine:
                     d = {int(ti[r_, c]): float(tv[r_, c]) for c in range(tv.shape[1])}
                     d.setdefault(int(t_), float(chosen[r_]))
                     req.prompt_logprobs.append(d)
+        if draft:
+            # masks, penalties and log-probabilities are applied to one position per step:
+            # such requests take no draft tokens
+            reqs = self.scheduler.requests
+            draft = {rid: d for rid, d in draft.items()
+                     if rid in reqs and not reqs[rid].sampling_params.needs_host_history}
         outs = self.scheduler.update_from_output(so, toks, draft, lp)
         if self.proposer is not None:
             for s in so.scheduled:
                 r = s.req
+                if r.sampling_params.needs_host_history:
+                    continue
                 if s.will_sample and not r.finished and r.request_id in self.scheduler.requests:
                     room = r.sampling_params.max_tokens - len(r.output_token_ids) - 1
                     r.spec_token_ids = self.proposer.propose(r.all_token_ids)[:max(0, room)]
@@ -290,13 +297,27 @@ class LLMEngine:
 
     def _step_once(self) -> list[RequestOutput]:
         """Runs (or, with async scheduling, launches and retires) one engine step."""
-        if self._want_sync and self.cfg.scheduler.async_scheduling and not self._pending:
+        outs: list[RequestOutput] = []
+        if self._want_sync and self.cfg.scheduler.async_scheduling:
+            # a request whose next token depends on host-side history has arrived: retire
+            # every step in flight first, then run in lock-step until no such request is left
+            while self._pending:
+                outs += self._finish(*self._pending.popleft())
             self.cfg.scheduler.async_scheduling = False
             self.scheduler.async_mode = False
+            self._async_suspended = True
         if not self.cfg.scheduler.async_scheduling:
             item = self._launch()
-            return self._finish(*item) if item is not None else []
-        outs: list[RequestOutput] = []
+            if item is not None:
+                outs += self._finish(*item)
+            if getattr(self, "_async_suspended", False) and not any(
+                    r.sampling_params.needs_host_history
+                    for r in self.scheduler.requests.values()):
+                self._want_sync = False
+                self._async_suspended = False
+                self.cfg.scheduler.async_scheduling = True
+                self.scheduler.async_mode = True
+            return outs
         item = self._launch() if self.scheduler.has_unfinished() else None
         if item is not None:
             self._pending.append(item)

@@ -705,12 +705,17 @@ class ModelRunner:
         return f
 
     def _apply_features(self, hidden: torch.Tensor, logits: torch.Tensor, ns: int,
-                        out_ids: torch.Tensor, before_sampling: bool) -> torch.Tensor:
+                        out_ids: torch.Tensor, before_sampling: bool, width: int = 1
+                        ) -> torch.Tensor:
+        """``logits`` holds ``width`` rows per sampling request (1 + the longest draft of the
+        step).  Requests with sampling extras never carry drafts, so their only live row is
+        the first of their group: row ``r * width``."""
         f = self._features
         if before_sampling:
             if "penalties" in f:
                 from ..layers.sampler import apply_penalties
                 rows, pm, oc, pres, freq, rep_ = f["penalties"]
+                rows = rows * width
                 sub = logits.index_select(0, rows).float()
                 apply_penalties(sub, pm, oc, pres, freq, rep_)
                 logits = logits.clone() if not logits.is_contiguous() else logits
@@ -721,14 +726,16 @@ class ModelRunner:
                     if not ids:
                         continue
                     keep = torch.tensor(ids, device=logits.device).clamp_(0, logits.shape[1] - 1)
-                    row = torch.full_like(logits[r], float("-inf"))
-                    row[keep] = logits[r, keep]
-                    logits[r] = row
+                    row = torch.full_like(logits[r * width], float("-inf"))
+                    row[keep] = logits[r * width, keep]
+                    logits[r * width] = row
             return logits
         if "logprob_k" in f:
             ks = f["logprob_k"]
             kmax = max(ks)
-            chosen, tv, ti = self.sampler.logprobs(logits[:ns], out_ids[:ns].long(), max(kmax, 0))
+            first = logits[:ns * width:width]
+            ids = out_ids[:ns * width:width].long().clamp_(min=0)
+            chosen, tv, ti = self.sampler.logprobs(first, ids, max(kmax, 0))
             f["logprobs_out"] = (chosen.cpu(), tv.cpu(), ti.cpu(), ks)
         if "prompt_logprobs" in f:
             out = {}
@@ -783,8 +790,9 @@ class ModelRunner:
         logits = self.model.compute_logits(rows)
         if self.keep_logits:
             self.last_logits = logits.float().cpu()
-        if feats is not None and width == 1:
-            logits = self._apply_features(hidden, logits, ns, out_ids, before_sampling=True)
+        if feats is not None:
+            logits = self._apply_features(hidden, logits, ns, out_ids, before_sampling=True,
+                                          width=width)
         st = None if all_greedy else SamplingTensors(self.temperature[:ns], self.top_k[:ns],
                                                      self.top_p[:ns], self.seeds[:ns])
         if width == 1:
@@ -793,6 +801,9 @@ class ModelRunner:
                 self._apply_features(hidden, logits, ns, out_ids, before_sampling=False)
         else:
             self._verify(logits, st, ns, width, out_ids)
+            if feats is not None:
+                self._apply_features(hidden, logits, ns, out_ids, before_sampling=False,
+                                     width=width)
         if self.drafter is not None:
             self._draft_mtp(hidden, md, T, ns, width, out_ids)
         if pp.world_size > 1:
@@ -825,8 +836,14 @@ class ModelRunner:
                 probs = torch.where(greedy_rows[:, None, None], onehot, probs)
             idx = nd.long().clamp(max=S)
             bonus_p = probs.gather(1, idx[:, None, None].expand(ns, 1, V)).squeeze(1)
-            bonus = torch.multinomial(bonus_p.clamp_min(0) + 1e-20, 1).squeeze(1)
-            out = self.rejection.random(draft, None, probs[:, :S].contiguous(), bonus, nd)
+            # the per-request seeds of this step fix the draw (same seeds, same tokens)
+            gen = None
+            if st.seeds is not None and st.seeds.numel() > 0:
+                gen = torch.Generator(device=logits.device)
+                gen.manual_seed(int(st.seeds.sum().item()) & 0x7FFFFFFFFFFFFFFF)
+            bonus = torch.multinomial(bonus_p.clamp_min(0) + 1e-20, 1, generator=gen).squeeze(1)
+            out = self.rejection.random(draft, None, probs[:, :S].contiguous(), bonus, nd,
+                                        generator=gen)
         out_ids[:ns * width].copy_(out.reshape(-1))
 
     def _draft_mtp(self, hidden: torch.Tensor, md: AttentionMetadata, T: int, ns: int,

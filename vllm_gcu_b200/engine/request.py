@@ -64,6 +64,15 @@ class SamplingParams:
         return (self.presence_penalty != 0.0 or self.frequency_penalty != 0.0
                 or self.repetition_penalty != 1.0)
 
+    @property
+    def needs_host_history(self) -> bool:
+        """True when sampling the next token needs every earlier token id on the host
+        (penalty histories, guide state, allowed-token masks) or reads the logits back
+        (log-probabilities).  Such a request never runs ahead of its own results and never
+        carries draft tokens."""
+        return (self.has_penalties or self.constrained or self.logprobs is not None
+                or self.prompt_logprobs is not None)
+
 
 class RequestStatus(enum.IntEnum):
     WAITING = 0

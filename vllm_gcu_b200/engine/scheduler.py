@@ -34,6 +34,7 @@ class ScheduledRequest:
     is_new: bool               # first step since admission / resumption
     spec_token_ids: list[int] = field(default_factory=list)
     will_sample: bool = False  # this step produces the next token(s) of the request
+    epoch: int = 0             # the request's preemption count when this step was planned
 
 
 @dataclass
@@ -80,6 +81,10 @@ class Scheduler:
 
     # -- request lifecycle ---------------------------------------------------
     def add_request(self, req: Request) -> None:
+        if req.num_prompt_tokens == 0:
+            # an empty prompt has nothing to prefill: at the head of the queue it would ask for
+            # zero tokens forever and starve every request behind it
+            raise ValueError("the prompt is empty")
         if req.num_prompt_tokens >= self.cfg.max_model_len:
             raise ValueError(f"prompt of {req.num_prompt_tokens} tokens exceeds max_model_len "
                              f"{self.cfg.max_model_len}")
@@ -159,6 +164,7 @@ class Scheduler:
             return
         self.kv.free(victim)
         victim.status = RequestStatus.PREEMPTED
+        victim.preempt_epoch = getattr(victim, "preempt_epoch", 0) + 1
         victim.num_computed_tokens = 0
         victim.num_output_placeholders = 0
         victim.spec_token_ids = []
@@ -217,6 +223,8 @@ class Scheduler:
                 sp = req.sampling_params
                 if len(req.output_token_ids) + req.num_output_placeholders >= sp.max_tokens:
                     want = 0                # the last token is already in flight
+                elif req.num_output_placeholders > 0 and sp.needs_host_history:
+                    want = 0                # its mask / penalties need the token in flight
             if self.separate_prefill_decode and allow_waiting and self.waiting \
                     and req.num_computed_tokens >= req.num_prompt_tokens:
                 want = 0                    # prefill phase: decodes sit this step out
@@ -270,6 +278,13 @@ class Scheduler:
                 n = min(want, budget)
                 if threshold > 0:
                     n = min(n, threshold)
+                if want <= 0:
+                    # nothing left to compute (cannot be scheduled): drop it instead of
+                    # blocking the queue
+                    self.waiting.popleft()
+                    req.status = RequestStatus.FINISHED_ABORTED
+                    self._free(req)
+                    continue
                 if n <= 0 or (not self.cfg.enable_chunked_prefill and n < want):
                     break
                 new_blocks = self.kv.allocate_slots(
@@ -316,6 +331,7 @@ class Scheduler:
         before this one returns (async_scheduler.py:478-515)."""
         for s in out.scheduled:
             req = s.req
+            s.epoch = getattr(req, "preempt_epoch", 0)
             req.num_computed_tokens += s.num_tokens
             will_sample = req.num_computed_tokens >= (req.num_tokens_with_placeholders
                                                       + len(s.spec_token_ids))
@@ -341,6 +357,8 @@ class Scheduler:
                 continue                    # aborted / finished while the step was in flight
             if req.status != RequestStatus.RUNNING:
                 continue
+            if getattr(req, "preempt_epoch", 0) != s.epoch:
+                continue                    # preempted and re-admitted since this step was planned
             toks = list(sampled.get(req.request_id, ()))
             if not s.will_sample:
                 # partial prefill: nothing to emit, tokens are all known -> cacheable

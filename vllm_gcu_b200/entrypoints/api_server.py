@@ -177,6 +177,12 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None):
                 _ensure_vocabulary()
         except ValueError as e:
             return JSONResponse({"error": str(e)}, status_code=400)
+        try:
+            batch_ids = [to_ids(p) for p in batch]
+            for ids_ in batch_ids:
+                engine.validate_prompt(ids_)
+        except (ValueError, TypeError) as e:
+            return JSONResponse({"error": str(e)}, status_code=400)
         rid = "cmpl-" + uuid.uuid4().hex[:16]
         created = int(time.time())
         state["requests"] += len(batch)
@@ -197,7 +203,7 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None):
 
         if body.get("stream", False):
             async def sse():
-                ids = to_ids(batch[0])
+                ids = batch_ids[0]
                 sent = 0
                 async for out in engine.generate_stream(ids, sp, priority=priority, **gen_kw):
                     toks = out.outputs[0].token_ids
@@ -210,8 +216,7 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None):
 
         import asyncio
 
-        async def one(idx: int, p) -> dict:
-            ids = to_ids(p)
+        async def one(idx: int, ids) -> dict:
             last = None
             async for out in engine.generate_stream(ids, sp, priority=priority, **gen_kw):
                 last = out
@@ -221,7 +226,7 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None):
             c["prompt_tokens"] = len(ids)
             return c
 
-        choices = await asyncio.gather(*[one(i, p) for i, p in enumerate(batch)])
+        choices = await asyncio.gather(*[one(i, p) for i, p in enumerate(batch_ids)])
         usage = {"prompt_tokens": sum(c.pop("prompt_tokens") for c in choices),
                  "completion_tokens": sum(len(c["token_ids"]) for c in choices)}
         usage["total_tokens"] = usage["prompt_tokens"] + usage["completion_tokens"]
@@ -250,6 +255,10 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None):
         except ValueError as e:
             return JSONResponse({"error": str(e)}, status_code=400)
         ids = render_chat(messages)
+        try:
+            engine.validate_prompt(ids)
+        except ValueError as e:
+            return JSONResponse({"error": str(e)}, status_code=400)
         rid = "chatcmpl-" + uuid.uuid4().hex[:16]
         created = int(time.time())
         state["requests"] += 1
