@@ -20,7 +20,9 @@ One *step* is one complete pass of that workload through ``LLM.generate``.  Afte
 
 Launch: ``python bench.py`` (1 GPU) or
 ``python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N``.
-``--impl reference`` reports why the reference cannot run on this hardware.
+``--impl reference`` reports why the reference cannot run on this hardware;
+``--impl vllm-stock`` runs the same workload through stock vLLM on the CUDA platform (the
+stand-in baseline, benchmarks/baseline_vllm_stock.py).
 """
 from __future__ import annotations
 
@@ -105,7 +107,7 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=1)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "vllm-stock"])
     ap.add_argument("--model", default="llama-3-8b")
     ap.add_argument("--num-prompts", type=int, default=512)
     ap.add_argument("--input-len", type=int, default=1024)
@@ -120,6 +122,19 @@ def main() -> None:
     if args.impl == "reference":
         run_reference(args)
         return
+    if args.impl == "vllm-stock":
+        # stand-in baseline (stock vLLM on the CUDA platform, none of this repository's code):
+        # the same workload through benchmarks/baseline_vllm_stock.py, in this process slot
+        script = os.path.join(os.path.dirname(os.path.abspath(__file__)), "benchmarks",
+                              "baseline_vllm_stock.py")
+        argv = [sys.executable, script, "--gpus", str(args.gpus), "--steps", str(args.steps),
+                "--warmup", str(args.warmup), "--num-prompts", str(args.num_prompts),
+                "--input-len", str(args.input_len), "--output-len", str(args.output_len),
+                "--max-num-seqs", str(args.max_num_seqs),
+                "--max-num-batched-tokens", str(args.max_num_batched_tokens)]
+        if args.layers > 0:
+            argv += ["--layers", str(args.layers)]
+        os.execv(sys.executable, argv)
 
     import torch
     import torch.distributed as dist

@@ -1,4 +1,11 @@
-"""Latency of the fused GEMM + all-reduce kernel against GEMM followed by an NCCL all-reduce.
+"""Latency of the fused row-parallel kernels against GEMM followed by an NCCL all-reduce.
+
+Three fused forms are timed: GEMM + tile-wise all-reduce (one-shot / two-shot), and
+GEMM + all-reduce + residual add + RMSNorm with row owners (``gemm_ar_norm``), the latter
+over plain peer loads / stores and over multimem (in-switch reduction), against the un-fused
+sequence GEMM, NCCL all-reduce, fused-add RMSNorm kernel.  ``roofline_us`` is the slowest of
+FLOPs / measured bf16 peak, operand bytes / measured HBM bandwidth and the bytes that must
+cross NVLink per direction and GPU / 770 GB/s; ``*_frac`` = roofline / measured.
 
 Launch with one rank per GPU:
   python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
@@ -73,6 +80,12 @@ def main():
     st = init_distributed(tp=world)
     dev = torch.device("cuda", st.local_rank)
     fused = symm.FusedTP(max_tokens=8192, max_n=4096, device=dev)
+    peaks = {"bf16_tflops": 1632.2, "hbm_gbs": 6552.3}
+    try:
+        root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+        peaks.update(json.load(open(os.path.join(root, "MEASURED_PEAKS.json"))))
+    except Exception:
+        pass
     rows = []
     for M in (256, 8192):
         for name, K in (("o_proj", 4096 // world), ("down_proj", 14336 // world)):
@@ -95,6 +108,32 @@ def main():
                 res[mode + "_us"] = timed(lambda i: fused.gemm_all_reduce(x, ws[i]), 5, gr)
                 _native.check_status()
                 fused.force_mode = None
+            # GEMM + all-reduce + residual + RMSNorm: one kernel against three
+            resid = torch.randn(M, N, device=dev).to(torch.bfloat16)
+            nw = torch.ones(N, device=dev, dtype=torch.bfloat16)
+
+            def unfused(i):
+                y = C.gemm_bf16(x, ws[i])
+                dist.all_reduce(y)
+                return C.norm(y, nw, 1e-5, residual=resid)
+            res["nccl_norm_us"] = timed(unfused, 5, gr)
+            for mc in ([False, True] if fused.buf.multicast_ptr else [False]):
+                fused.use_multimem = mc
+                key = "ar_norm_mc_us" if mc else "ar_norm_us"
+                res[key] = timed(lambda i: fused.gemm_ar_norm(x, ws[i], resid, nw, 1e-5,
+                                                              bcast_residual=False), 5, gr)
+                _native.check_status()
+            flop_us = 2.0 * M * N * K / (peaks["bf16_tflops"] * 1e12) * 1e6
+            hbm_us = (N * K + M * K + 2 * M * N) * 2 / (peaks["hbm_gbs"] * 1e9) * 1e6
+            # per GPU and direction: (p-1)/p of the partial matrix in, (p-1)/p of the result in
+            nvl_us = 2.0 * (world - 1) / world * M * N * 2 / 770e9 * 1e6
+            # multimem: the switch adds the partials, 1/p of the matrix comes in reduced
+            nvl_mc_us = ((world - 1) / world + 1.0 / world) * M * N * 2 / 770e9 * 1e6
+            res["roofline_us"] = round(max(flop_us, hbm_us, nvl_us), 2)
+            res["roofline_mc_us"] = round(max(flop_us, hbm_us, nvl_mc_us), 2)
+            res["ar_norm_frac"] = round(res["roofline_us"] / res["ar_norm_us"], 3)
+            if "ar_norm_mc_us" in res:
+                res["ar_norm_mc_frac"] = round(res["roofline_mc_us"] / res["ar_norm_mc_us"], 3)
             rows.append(res)
     if rank == 0:
         print(json.dumps({"world": world, "results": rows}))

@@ -47,15 +47,140 @@ def full_state_dict(cfg, seed=0):
     return sd
 
 
+def dense_last_logits(cfg, sd, prompts, dev, all_positions=False):
+    """fp32 no-cache forward of the full (unsharded) checkpoint: logits at the last position
+    of every prompt, [len(prompts), V] (``all_positions``: a list of [S, V] tensors).  The
+    single-GPU reference of the engine runs."""
+    from vllm_gcu_b200.layers.basic import build_cos_sin_cache
+    from vllm_gcu_b200.ops import ref
+    W = {k: v.to(dev).float() for k, v in sd.items()}
+    D, Hq, Hkv = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
+    cs = build_cos_sin_cache(cfg.rotary_dim, 1024, cfg.rope_theta, cfg.rope_scaling).to(dev)
+    rows = []
+    for p in prompts:
+        ids = torch.tensor(p, device=dev)
+        S = ids.shape[0]
+        x = W["model.embed_tokens.weight"][ids]
+        pos = torch.arange(S, device=dev)
+        residual = None
+        for i in range(cfg.num_hidden_layers):
+            pre = f"model.layers.{i}."
+            if residual is None:
+                residual, h = x, ref.rms_norm(x, W[pre + "input_layernorm.weight"], cfg.rms_norm_eps)
+            else:
+                h, residual = ref.fused_add_rms_norm(x, residual, W[pre + "input_layernorm.weight"],
+                                                     cfg.rms_norm_eps)
+            q = h @ W[pre + "self_attn.q_proj.weight"].t()
+            k = h @ W[pre + "self_attn.k_proj.weight"].t()
+            v = h @ W[pre + "self_attn.v_proj.weight"].t()
+            q, k = ref.rotary_embedding(pos, q, k, D, cs, True)
+            o = ref.dense_causal_attention(q.view(S, Hq, D), k.view(S, Hkv, D), v.view(S, Hkv, D),
+                                           D ** -0.5).reshape(S, Hq * D)
+            h = o @ W[pre + "self_attn.o_proj.weight"].t()
+            h, residual = ref.fused_add_rms_norm(h, residual,
+                                                 W[pre + "post_attention_layernorm.weight"],
+                                                 cfg.rms_norm_eps)
+            gu = torch.cat([h @ W[pre + "mlp.gate_proj.weight"].t(),
+                            h @ W[pre + "mlp.up_proj.weight"].t()], -1)
+            x = ref.silu_and_mul(gu) @ W[pre + "mlp.down_proj.weight"].t()
+        x, _ = ref.fused_add_rms_norm(x, residual, W["model.norm.weight"], cfg.rms_norm_eps)
+        rows.append((x if all_positions else x[-1]) @ W["lm_head.weight"].t())
+    return [r.cpu() for r in rows] if all_positions else torch.stack(rows).cpu()
+
+
+def check_gemm_ar_norm(fused, world, rank, dev):
+    """GEMM + all-reduce + residual + RMSNorm in one kernel against torch, with and without
+    the norm, with the new residual on the owner only / on every rank, over plain peer
+    accesses and (when the allocation has a multicast view) over multimem."""
+    lo_hi = lambda r: (128 * r // world, 128 * (r + 1) // world)
+    modes = [False, True] if fused.buf.multicast_ptr else [False]
+    for use_mc in modes:
+        fused.use_multimem = use_mc
+        for (M, N, K) in [(256, 4096, 512), (7, 1024, 256), (1024, 4096, 1792), (300, 2048, 72)]:
+            g = torch.Generator(device="cuda").manual_seed(100 + rank)
+            x = torch.randn(M, K, device=dev, dtype=torch.bfloat16, generator=g)
+            w = (torch.randn(N, K, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+            g2 = torch.Generator(device="cuda").manual_seed(5)           # same on every rank
+            res = torch.randn(M, N, device=dev, generator=g2).to(torch.bfloat16)
+            nw = (1.0 + 0.1 * torch.randn(N, device=dev, generator=g2)).to(torch.bfloat16)
+            part = (x.float() @ w.float().t()).to(torch.bfloat16).float()
+            dist.all_reduce(part)
+            z = (part + res.float()).to(torch.bfloat16).float()
+            normed = z * torch.rsqrt(z.pow(2).mean(-1, keepdim=True) + 1e-5) * nw.float()
+            for rep, bcast in enumerate([True, False, True]):
+                out, nres = fused.gemm_ar_norm(x, w, res, nw, 1e-5, bcast_residual=bcast)
+                torch.cuda.synchronize()
+                _native.check_status()
+                tag = f"gemm_ar_norm mc={use_mc} {M}x{N}x{K} rep {rep}"
+                err = (out.float() - normed).abs().max().item()
+                assert err < 0.03 * normed.abs().max().item() + 0.03, f"{tag}: out err {err}"
+                rows = torch.arange(M, device=dev)
+                if not bcast:
+                    l, h = lo_hi(rank)
+                    rows = rows[(rows % 128 >= l) & (rows % 128 < h)]
+                rerr = (nres.float()[rows] - z[rows]).abs().max().item() if rows.numel() else 0.0
+                assert rerr < 0.03 * z.abs().max().item() + 0.03, f"{tag}: residual err {rerr}"
+            out, nres = fused.gemm_ar_norm(x, w, None, None)
+            torch.cuda.synchronize()
+            _native.check_status()
+            assert nres is None
+            err = (out.float() - part).abs().max().item()
+            assert err < 0.03 * part.abs().max().item() + 0.03, f"plain reduce {M}x{N}x{K}: {err}"
+    # greedy tokens from vocabulary-parallel logits
+    for B, V in [(256, 16064), (3, 520)]:
+        g = torch.Generator(device="cuda").manual_seed(900 + rank)
+        lg = torch.randn(B, V, device=dev, generator=g).to(torch.bfloat16)
+        valid = V - 8 if rank == world - 1 else V
+        parts = [torch.empty_like(lg) for _ in range(world)]
+        dist.all_gather(parts, lg)
+        parts[-1] = parts[-1][:, :V - 8]
+        want = torch.cat([q.float() for q in parts], dim=1).argmax(-1)
+        want = want + (want // V) * 0        # ids are global: block r starts at r * V
+        for rep in range(3):
+            got = fused.greedy_argmax(lg[:, :valid], valid, rank * V)
+            torch.cuda.synchronize()
+            _native.check_status()
+            assert torch.equal(got, want), f"greedy_argmax B={B} rep {rep}"
+
+
 def main():
+    """Runs the checks; a failing rank does not leave while its peers are still inside a
+    kernel that waits for it: every rank reaches the final barrier, then all exit together."""
     world = int(os.environ["WORLD_SIZE"])
     rank = int(os.environ["RANK"])
     st = init_distributed(tp=world)
+    failed = False
+    try:
+        run_checks(world, rank, st)
+    except BaseException:  # noqa: BLE001
+        import traceback
+        traceback.print_exc()
+        failed = True
+    try:
+        torch.cuda.synchronize()
+    except Exception:  # noqa: BLE001
+        failed = True
+    flag = torch.tensor([int(failed)], device="cuda")
+    dist.all_reduce(flag)
+    dist.barrier()
+    torch.cuda.synchronize()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(1 if int(flag.item()) else 0)
+
+
+def run_checks(world, rank, st):
     dev = torch.device("cuda", st.local_rank)
     torch.manual_seed(0)
 
     # ---- fused GEMM + all-reduce ------------------------------------------------------
     fused = symm.FusedTP(max_tokens=1024, max_n=4096, device=dev)
+    if os.environ.get("B200_TEST_ONLY") == "ar_norm":
+        check_gemm_ar_norm(fused, world, rank, dev)
+        if rank == 0:
+            print(f"gemm + all-reduce + norm ok (multicast view: "
+                  f"{bool(fused.buf.multicast_ptr)})", flush=True)
+        return
     for (M, N, K) in [(256, 4096, 512), (7, 1024, 256), (1024, 4096, 1792), (130, 136, 72)]:
         g = torch.Generator(device="cuda").manual_seed(100 + rank)
         x = torch.randn(M, K, device=dev, dtype=torch.bfloat16, generator=g)
@@ -70,6 +195,9 @@ def main():
             err = (got.float() - want).abs().max().item()
             tol = 0.05 * want.abs().max().item() + 0.05
             assert err < tol, f"gemm_all_reduce {M}x{N}x{K} rep {rep}: err {err} tol {tol}"
+    check_gemm_ar_norm(fused, world, rank, dev)
+    if rank == 0:
+        print("gemm + all-reduce + norm ok", flush=True)
     for n in (8, 4096, 1 << 20):
         x = torch.randn(n, device=dev, dtype=torch.bfloat16)
         want = x.float().clone()
@@ -159,11 +287,44 @@ def main():
         torch.cuda.synchronize()
         _native.check_status()
         results[comm] = llm.engine.runner.last_logits
+    # generation with the greedy shortcut, eagerly and through CUDA graphs.  With random weights
+    # the logits are nearly flat, so a rounding difference may pick another token and the
+    # sequences part ways; what must hold is that every generated token is a (near-)maximum
+    # of the dense fp32 logits given the tokens before it.
+    sp8 = SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True)
+    bad = []
+    for comm, eager in (("nccl", False), ("fused", True), ("fused", False)):
+        get_comm("tp").fused = None
+        get_comm("tp").fused_gather = None
+        llm = LLM("llama-3-8b", tensor_parallel_size=world, comm_backend=comm,
+                  async_scheduling=True, enforce_eager=True, load_format="none", **kw)
+        llm.engine.model.load_weights(sd.items())
+        if not eager:
+            # capture only now: loading re-lays-out some weights into new storage, which a
+            # graph captured before the load would not see
+            llm.engine.cfg.enforce_eager = False
+            llm.engine.runner.capture_graphs([4, 8])
+        outs = llm.generate(prompts, sp8)
+        torch.cuda.synchronize()
+        _native.check_status()
+        seqs = [o.outputs[0].token_ids for o in outs]
+        full = [p_ + t_ for p_, t_ in zip(prompts, seqs)]
+        dense = dense_last_logits(cfg, sd, [f[:-1] for f in full], dev, all_positions=True)
+        for p_, t_, lg in zip(prompts, seqs, dense):
+            tail = lg[len(p_) - 1:]
+            assert tail.shape[0] == len(t_) == 8
+            gap = tail.max(-1).values - tail.gather(-1, torch.tensor(t_)[:, None]).squeeze(-1)
+            tol = 0.06 * lg.std().item() + 0.03
+            if gap.max().item() >= tol:
+                bad.append((comm, "eager" if eager else "graphs", [round(g_, 3) for g_ in gap.tolist()]))
     get_comm("tp").fused = None
     get_comm("tp").fused_gather = None
-    if rank == 0:
-        # single-GPU reference on the same weights (TP groups of size 1 via a fresh state)
-        pass
+    assert not bad, f"generated tokens far from the dense maximum: {bad}"
+    # the single-GPU reference: a dense fp32 forward of the same full checkpoint
+    want = dense_last_logits(cfg, sd, prompts, dev)
+    for name, got in results.items():
+        e = (got - want).abs().max().item()
+        assert e < 0.06 * want.std().item() + 0.03, f"{name} logits vs dense reference: {e}"
     a, b = results["nccl"], results["fused"]
     err = (a - b).abs().max().item()
     assert err < 0.05 * a.std().item() + 0.02, f"fused vs nccl logits differ: {err}"
@@ -172,8 +333,6 @@ def main():
     assert err_sp < 0.05 * a.std().item() + 0.02, f"sequence-parallel logits differ: {err_sp}"
     if rank == 0:
         print(f"tp{world} engine ok (nccl vs fused max logit diff {err:.4f})", flush=True)
-    dist.barrier()
-    dist.destroy_process_group()
 
 
 if __name__ == "__main__":

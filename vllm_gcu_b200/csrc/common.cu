@@ -7,7 +7,8 @@
 
 namespace b200 {
 
-__device__ unsigned int g_status[4] = {0u, 0u, 0u, 0u};
+// [0..3] first error (code, kernel, detail, count); [4] run-time flag-wait budget (0: default)
+__device__ unsigned int g_status[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
 
 unsigned int* status_ptr() {
   static unsigned int* cached[64] = {nullptr};
@@ -100,6 +101,14 @@ B200_API int b200_status_take(unsigned int* out, void* stream) {
   unsigned int zero[4] = {0u, 0u, 0u, 0u};
   e = cudaMemcpyToSymbol(b200::g_status, zero, sizeof(zero));
   return static_cast<int>(e);
+}
+
+// Sets the iteration budget of every wait on a peer- or host-written flag on the current
+// device (0 restores the built-in default of about a second).  Takes effect for kernels
+// launched after the call on the same stream order as a synchronous copy.
+B200_API int b200_set_flag_wait_limit(unsigned int iterations) {
+  return static_cast<int>(
+      cudaMemcpyToSymbol(b200::g_status, &iterations, sizeof(unsigned int), 4 * sizeof(unsigned int)));
 }
 
 B200_API int b200_sm_count() { return b200::sm_count(); }

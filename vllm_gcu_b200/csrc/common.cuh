@@ -43,6 +43,16 @@ __device__ __forceinline__ void report_status(unsigned int* st, unsigned int cod
   atomicAdd(&st[3], 1u);
 }
 
+// Spin budget of waits on flags that another GPU (or the host) writes.  Word [4] of the status
+// block overrides it at run time (0 = this default), see b200_set_flag_wait_limit: a short
+// budget lets a test watch a wait run out without waiting for a second.
+constexpr uint32_t kFlagSpinLimit = 1u << 22;
+__device__ __forceinline__ uint32_t flag_spin_limit(const unsigned int* st) {
+  if (st == nullptr) return kFlagSpinLimit;
+  const uint32_t v = *reinterpret_cast<const volatile unsigned int*>(st + 4);
+  return v != 0u ? v : kFlagSpinLimit;
+}
+
 // Spin budget for mbarrier waits.  try_wait suspends for a hardware-chosen
 // interval each call, so this many polls is on the order of a second.
 constexpr uint32_t kMbarSpinLimit = 1u << 24;

@@ -36,12 +36,15 @@ enum Epilogue : int {
   kEpiAllReduce = 5,  // row-parallel partial product -> tile-wise two-shot all-reduce over peers
   kEpiAllGather = 6,  // column-parallel shard -> every peer's full-width output (peer stores)
   kEpiGatherA = 7,    // A rows are gathered from the peers' shards by extra warps of this kernel
+  kEpiReduceNorm = 8, // row-parallel partial -> row owners reduce (+ residual, RMSNorm) and broadcast
 };
 
 template <int EPI>
-constexpr int kThreadsFor = (EPI == kEpiGatherA || EPI == kEpiAllReduce) ? 320 : 192;
+constexpr int kThreadsFor =
+    (EPI == kEpiGatherA || EPI == kEpiAllReduce || EPI == kEpiReduceNorm) ? 320 : 192;
 template <int EPI>
-constexpr bool kPeerEpi = (EPI == kEpiAllReduce || EPI == kEpiAllGather || EPI == kEpiGatherA);
+constexpr bool kPeerEpi = (EPI == kEpiAllReduce || EPI == kEpiAllGather || EPI == kEpiGatherA ||
+                           EPI == kEpiReduceNorm);
 
 constexpr int kMaxPeers = 8;
 
@@ -58,6 +61,18 @@ struct ArArgs {
   int oneshot;                        // 1: push partials to every peer, reduce locally
   long long slot_elems;               // one-shot: elements per (parity, source rank) slot
   long long col_off;                  // all-gather epilogue: first output column of this rank
+  // row-owner reduce (kEpiReduceNorm): rank r reduces rows [128 r / p, 128 (r + 1) / p) of every
+  // 128-row tile, adds the residual, normalises and stores the rows into every rank
+  __nv_bfloat16* res_out[kMaxPeers];  // [M, N] new residual on rank r (symmetric)
+  const __nv_bfloat16* res_in;        // local [M, ld_res_in] residual (null: none)
+  long long ld_res_in;
+  const __nv_bfloat16* norm_weight;   // [N] (null: plain all-reduce, out = sum + residual)
+  float eps;
+  int bcast_res;                      // 1: the new residual goes to every rank, 0: owner only
+  // multicast (NVLS) views of the same symmetric buffers; null = plain peer loads / stores
+  const __nv_bfloat16* mc_partial;
+  __nv_bfloat16* mc_out;
+  __nv_bfloat16* mc_res;
 };
 
 // All-gather of the A operand inside the GEMM (sequence-parallel input of a column-parallel
@@ -97,6 +112,7 @@ struct Args {
   const int* num_valid_rows;  // device scalar: rows of A that are in use (multiple of BM)
   const float* row_scale;     // optional [M] factor applied to each output row
   int m_rot;                  // M tiles are visited starting at this tile (gathered-A mode)
+  int n_fastest;              // 1: consecutive tiles walk along N (tile = tm * tiles_n + tn)
   ArArgs ar;
   AgArgs ag;
 };
@@ -105,6 +121,13 @@ struct Args {
 template <int BN_>
 __device__ __forceinline__ bool tile_coords(const Args& p, int tile, int& m0, int& n0,
                                             int& b_row) {
+  if (p.n_fastest) {
+    // whole rows of the output complete early, in the order their owners reduce them
+    m0 = (tile / p.tiles_n) * BM;
+    n0 = (tile % p.tiles_n) * BN_;
+    b_row = n0;
+    return true;
+  }
   int tm = tile % p.tiles_m + p.m_rot;
   if (tm >= p.tiles_m) tm -= p.tiles_m;
   m0 = tm * BM;
@@ -121,8 +144,9 @@ __device__ __forceinline__ bool tile_coords(const Args& p, int tile, int& m0, in
 
 // Bounded acquire-wait until *flag reaches `want` (a peer that is one launch ahead may
 // already have written want + 1).  Returns false on timeout.
-__device__ __forceinline__ bool wait_flag_sys(const uint32_t* flag, uint32_t want) {
-  for (uint32_t it = 0; it < (1u << 22); ++it) {
+__device__ __forceinline__ bool wait_flag_sys(const uint32_t* flag, uint32_t want,
+                                              uint32_t limit = kFlagSpinLimit) {
+  for (uint32_t it = 0; it < limit; ++it) {
     uint32_t v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
     if (static_cast<int32_t>(v - want) >= 0) return true;  // epochs only grow
@@ -130,8 +154,10 @@ __device__ __forceinline__ bool wait_flag_sys(const uint32_t* flag, uint32_t wan
   }
   return false;
 }
+// Release store at system scope.  The release orders the writes that precede it in this thread
+// and, through the barrier that every caller places before it, those of the threads that met
+// there (cumulativity); a separate full fence in front of it only doubles the drain.
 __device__ __forceinline__ void signal_flag_sys(uint32_t* flag, uint32_t val) {
-  __threadfence_system();
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(val) : "memory");
 }
 __device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
@@ -212,6 +238,201 @@ __device__ __forceinline__ void reduce_tile(const __nv_bfloat16* const* srcs, in
 }
 
 
+// ---------------------------------------------------------------------------
+// Row-owner reduction (kEpiReduceNorm)
+// ---------------------------------------------------------------------------
+// In-switch reduction / broadcast through the NVLink multicast view of a symmetric buffer.
+__device__ __forceinline__ uint4 mc_ld_reduce_bf16(const void* mc) {
+  uint4 v;
+  asm volatile(
+      "multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+      : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+      : "l"(mc)
+      : "memory");
+  return v;
+}
+__device__ __forceinline__ void mc_st_v4(void* mc, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x),
+               "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ uint32_t ld_relaxed_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Barrier among the 128 threads of warps 6..9 that also ANDs a predicate.
+__device__ __forceinline__ bool aux_bar_and(bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P, Q;\n\t"
+      "setp.ne.u32 P, %1, 0;\n\t"
+      "bar.red.and.pred Q, 2, 128, P;\n\t"
+      "selp.b32 %0, 1, 0, Q;\n\t"
+      "}\n"
+      : "=r"(r)
+      : "r"(static_cast<uint32_t>(pred))
+      : "memory");
+  return r != 0;
+}
+__device__ __forceinline__ void add8(float (&a)[8], const uint4& u) {
+  const float2 x = unpack_bf16x2(u.x), y = unpack_bf16x2(u.y), z = unpack_bf16x2(u.z),
+               w = unpack_bf16x2(u.w);
+  a[0] += x.x; a[1] += x.y; a[2] += y.x; a[3] += y.y;
+  a[4] += z.x; a[5] += z.y; a[6] += w.x; a[7] += w.y;
+}
+__device__ __forceinline__ uint4 pack8(const float (&a)[8]) {
+  uint4 o;
+  o.x = pack_bf16x2(a[0], a[1]);
+  o.y = pack_bf16x2(a[2], a[3]);
+  o.z = pack_bf16x2(a[4], a[5]);
+  o.w = pack_bf16x2(a[6], a[7]);
+  return o;
+}
+
+constexpr int kRnKeep = 8;   // 16-byte chunks of a row one reducer thread holds: N <= 8 * 128 * 8
+
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Release store alone: it orders the writes that precede it in this thread and, through a
+// barrier before it, those of the threads that met there; no separate full fence.
+__device__ __forceinline__ void st_release_sys(uint32_t* flag, uint32_t val) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(val) : "memory");
+}
+
+// One output row, handled by TPR reducer threads (thread `t` of them owns the chunks t,
+// t + TPR, ... of the row): all 128 reducer threads of the CTA for decode-sized problems (one
+// round trip per row), one warp per row when a rank owns many rows (four rows in flight per
+// CTA, no CTA-wide barrier).  Sums the p partial rows (plain peer loads, U chunks x 16 / U
+// ranks in flight, or one multimem.ld_reduce per chunk), adds the residual, rounds to bf16
+// (the new residual) and - with a norm weight - scales by the RMS statistics of the rounded
+// row.  With TPR = 128 the rounded row stays in registers between the two passes (`red`: a
+// 4-float shared scratch for the statistics); with TPR = 32 it is read back from the residual
+// buffer this thread has just written.
+template <int U, int TPR>
+__device__ __forceinline__ void reduce_norm_row(const ArArgs& ar, int row, int N, long long ldc,
+                                                int t, float* red) {
+  constexpr bool kKeep = TPR == 128;
+  constexpr int kIters = kKeep ? kRnKeep : (kRnKeep * 128 / TPR);
+  const int nvec = N >> 3;
+  const int np = ar.p, rank = ar.rank;
+  const long long roff = static_cast<long long>(row) * N;      // partial / res_out rows: pitch N
+  uint4 z[kKeep ? kRnKeep : 1];
+  float sumsq = 0.0f;
+  const bool have_norm = ar.norm_weight != nullptr;
+#pragma unroll
+  for (int j0 = 0; j0 < kIters; j0 += U) {
+    if (t + j0 * TPR >= nvec) break;
+    float acc[U][8];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[u][i] = 0.0f;
+    if (ar.mc_partial != nullptr) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int c = t + (j0 + u) * TPR;
+        v[u] = c < nvec ? mc_ld_reduce_bf16(ar.mc_partial + roff + c * 8) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) add8(acc[u], v[u]);
+    } else {
+      constexpr int kR = 16 / U;                 // ranks per batch of loads
+      for (int r0 = 0; r0 < np; r0 += kR) {
+        uint4 v[kR][U];
+#pragma unroll
+        for (int r = 0; r < kR; ++r)
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const int c = t + (j0 + u) * TPR;
+            v[r][u] = (r0 + r < np && c < nvec)
+                          ? ld_volatile_v4(ar.partial[r0 + r] + roff + c * 8)
+                          : make_uint4(0, 0, 0, 0);
+          }
+#pragma unroll
+        for (int r = 0; r < kR; ++r)
+#pragma unroll
+          for (int u = 0; u < U; ++u) add8(acc[u], v[r][u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int c = t + (j0 + u) * TPR;
+      if (c >= nvec) continue;
+      if (ar.res_in != nullptr) {
+        const uint4 rv = *reinterpret_cast<const uint4*>(
+            ar.res_in + static_cast<long long>(row) * ar.ld_res_in + c * 8);
+        add8(acc[u], rv);
+      }
+      const uint4 o = pack8(acc[u]);
+      if constexpr (kKeep) z[j0 + u] = o;
+      if (have_norm) {
+        // statistics of the rounded values, as an unfused add + RMSNorm would see them
+        float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        add8(f, o);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sumsq += f[i] * f[i];
+        // the new residual: every rank, or the owner only
+        if (ar.bcast_res) {
+          if (ar.mc_res != nullptr) {
+            mc_st_v4(ar.mc_res + roff + c * 8, o);
+            if constexpr (!kKeep) *reinterpret_cast<uint4*>(ar.res_out[rank] + roff + c * 8) = o;
+          } else {
+            for (int r = 0; r < np; ++r)
+              *reinterpret_cast<uint4*>(ar.res_out[r] + roff + c * 8) = o;
+          }
+        } else {
+          *reinterpret_cast<uint4*>(ar.res_out[rank] + roff + c * 8) = o;
+        }
+      } else {
+        const long long ooff = static_cast<long long>(row) * ldc + c * 8;
+        if (ar.mc_out != nullptr) {
+          mc_st_v4(ar.mc_out + ooff, o);
+        } else {
+          for (int r = 0; r < np; ++r) *reinterpret_cast<uint4*>(ar.out[r] + ooff) = o;
+        }
+      }
+    }
+  }
+  if (!have_norm) return;
+  sumsq = warp_sum(sumsq);
+  if constexpr (TPR == 128) {
+    if ((t & 31) == 0) red[t >> 5] = sumsq;
+    gather_bar_sync();
+    sumsq = red[0] + red[1] + red[2] + red[3];
+    gather_bar_sync();                           // `red` is reused by the next row
+  }
+  const float rstd = rsqrtf(sumsq / static_cast<float>(N) + ar.eps);
+#pragma unroll
+  for (int j = 0; j < kIters; ++j) {
+    const int c = t + j * TPR;
+    if (c >= nvec) break;
+    float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if constexpr (kKeep) {
+      add8(f, z[j]);
+    } else {
+      // written by this very thread in the first pass
+      add8(f, ld_volatile_v4(ar.res_out[rank] + roff + c * 8));
+    }
+    float w[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    add8(w, *reinterpret_cast<const uint4*>(ar.norm_weight + c * 8));
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = f[i] * rstd * w[i];
+    const uint4 o = pack8(f);
+    const long long ooff = static_cast<long long>(row) * ldc + c * 8;
+    if (ar.mc_out != nullptr) {
+      mc_st_v4(ar.mc_out + ooff, o);
+    } else {
+      for (int r = 0; r < np; ++r) *reinterpret_cast<uint4*>(ar.out[r] + ooff) = o;
+    }
+  }
+}
+
 template <int BN, int STAGES, int EPI = kEpiNone>
 struct Smem {
   static constexpr int kABytes = BM * BK * 2;
@@ -222,7 +443,9 @@ struct Smem {
   static constexpr int kOutOffset = STAGES * kStageBytes;
   static constexpr int kOutCols = BN < 128 ? BN : 128;   // columns staged per pass
   static constexpr int kOutBytes =
-      (EPI == kEpiAllReduce || EPI == kEpiAllGather) ? BM * kOutCols * 2 : 0;
+      (EPI == kEpiAllReduce || EPI == kEpiAllGather || EPI == kEpiReduceNorm)
+          ? BM * kOutCols * 2
+          : 0;
   static constexpr int kBarOffset = kOutOffset + kOutBytes;
   static constexpr int kTotal = kBarOffset + 256 + 1024;  // barriers + alignment slack
   static_assert(kTotal <= 232448, "exceeds the shared memory of one CTA");
@@ -293,6 +516,7 @@ __global__ void __launch_bounds__(kThreadsFor<EPI>, 1)
   // written by warps 6..9 only (before their named barrier) and read after it, so that all of
   // them leave their loops in the same iteration
   volatile uint32_t* aux_abort = tmem_slot + 2;
+  float* aux_red = reinterpret_cast<float*>(tmem_slot + 4);   // 4 floats of the reducer warps
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -417,6 +641,7 @@ __global__ void __launch_bounds__(kThreadsFor<EPI>, 1)
 
       const int te = threadIdx.x - 192;  // 0..127 among the reducer warps
       const int np = p.ar.p, rank = p.ar.rank;
+      const uint32_t spin = flag_spin_limit(p.status);
       if (p.ar.oneshot) {
         // phase 2 (one-shot): every rank reduces every tile from its own slots
         const __nv_bfloat16* srcs[kMaxPeers];
@@ -427,7 +652,7 @@ __global__ void __launch_bounds__(kThreadsFor<EPI>, 1)
         for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
           bool ok = true;
           if (te < np)
-            ok = wait_flag_sys(p.ar.ready[rank] + static_cast<long long>(t) * np + te, epoch);
+            ok = wait_flag_sys(p.ar.ready[rank] + static_cast<long long>(t) * np + te, epoch, spin);
           if (!ok) {
             report_status(p.status, kStatusFlagTimeout, kKernelId, 0x500u + te);
             *aux_abort = 1u;
@@ -444,7 +669,7 @@ __global__ void __launch_bounds__(kThreadsFor<EPI>, 1)
              t += gridDim.x * np) {
           bool ok = true;
           if (te < np)
-            ok = wait_flag_sys(p.ar.ready[rank] + static_cast<long long>(t) * np + te, epoch);
+            ok = wait_flag_sys(p.ar.ready[rank] + static_cast<long long>(t) * np + te, epoch, spin);
           if (!ok) {
             report_status(p.status, kStatusFlagTimeout, kKernelId, 0x500u + te);
             *aux_abort = 1u;
@@ -459,10 +684,94 @@ __global__ void __launch_bounds__(kThreadsFor<EPI>, 1)
         }
         // phase 3: the result is complete on this rank once every tile reports done
         for (int t = te; t < num_tiles && *aux_abort == 0u; t += 128) {
-          if (!wait_flag_sys(p.ar.done[rank] + t, epoch)) {
+          if (!wait_flag_sys(p.ar.done[rank] + t, epoch, spin)) {
             report_status(p.status, kStatusFlagTimeout, kKernelId, 0x600u);
             *aux_abort = 1u;
           }
+        }
+      }
+    }
+    if constexpr (EPI == kEpiReduceNorm) {
+      // ---------------- row owners (warps 6..9) ----------------
+      // Rank r owns rows [lo, hi) of every 128-row tile.  A row is reduced once every rank
+      // has parked all column tiles of its M tile; the finished row is stored into every rank
+      // and marked done there.  Few rows per rank (decode): one row per CTA, all 128 threads
+      // on it.  Many rows: one row per warp, four rows in flight per CTA.
+      const int te = threadIdx.x - 192;
+      const int wq = te >> 5, ln = te & 31;
+      const int np = p.ar.p, rank = p.ar.rank;
+      const uint32_t spin = flag_spin_limit(p.status);
+      const int lo = BM * rank / np, hi = BM * (rank + 1) / np;
+      const int rpt = hi - lo;
+      const int nflags = p.tiles_n * np;
+      const int my_rows = p.tiles_m * rpt;
+      int tm_ready = -1;                               // last M tile whose flags were seen
+      bool dead = false;
+      if (my_rows <= static_cast<int>(gridDim.x) * 2) {
+        for (int i = blockIdx.x; i < my_rows; i += gridDim.x) {
+          const int tm = i / rpt;
+          const int row = tm * BM + lo + (i - tm * rpt);
+          if (row >= p.M) continue;
+          if (tm != tm_ready) {
+            const uint32_t* fl = p.ar.ready[rank] + static_cast<long long>(tm) * nflags;
+            bool all = false;
+            for (uint32_t it = 0; it < spin && !all; ++it) {
+              bool mine = true;
+              for (int f = te; f < nflags; f += 128)
+                mine = mine && static_cast<int32_t>(ld_acquire_sys_u32(fl + f) - epoch) >= 0;
+              all = aux_bar_and(mine);
+              if (!all && it > 16) __nanosleep(40);
+            }
+            if (!all) {
+              if (te == 0) report_status(p.status, kStatusFlagTimeout, kKernelId, 0x900u);
+              dead = true;
+              break;                                   // the same decision in all 128 threads
+            }
+            tm_ready = tm;
+          }
+          if (np > 4)
+            reduce_norm_row<2, 128>(p.ar, row, p.N, p.ldc, te, aux_red);
+          else
+            reduce_norm_row<4, 128>(p.ar, row, p.N, p.ldc, te, aux_red);
+          gather_bar_sync();
+          if (te < np) st_release_sys(p.ar.done[te] + row, epoch);
+        }
+      } else {
+        for (int i = static_cast<int>(blockIdx.x) * 4 + wq; i < my_rows; i += gridDim.x * 4) {
+          const int tm = i / rpt;
+          const int row = tm * BM + lo + (i - tm * rpt);
+          if (row >= p.M) continue;
+          if (tm != tm_ready) {
+            const uint32_t* fl = p.ar.ready[rank] + static_cast<long long>(tm) * nflags;
+            bool all = false;
+            for (uint32_t it = 0; it < spin && !all; ++it) {
+              bool mine = true;
+              for (int f = ln; f < nflags; f += 32)
+                mine = mine && static_cast<int32_t>(ld_acquire_sys_u32(fl + f) - epoch) >= 0;
+              all = __all_sync(0xffffffffu, mine);
+              if (!all && it > 16) __nanosleep(200);
+            }
+            if (!all) {
+              if (ln == 0) report_status(p.status, kStatusFlagTimeout, kKernelId, 0x901u);
+              dead = true;
+              break;
+            }
+            tm_ready = tm;
+          }
+          if (np > 4)
+            reduce_norm_row<2, 32>(p.ar, row, p.N, p.ldc, ln, aux_red);
+          else
+            reduce_norm_row<4, 32>(p.ar, row, p.N, p.ldc, ln, aux_red);
+          __syncwarp();
+          if (ln < np) st_release_sys(p.ar.done[ln] + row, epoch);
+        }
+      }
+      // the output is complete here once the owner of every row has marked it
+      for (int r = static_cast<int>(blockIdx.x) * 128 + te; !dead && r < p.M;
+           r += gridDim.x * 128) {
+        if (!wait_flag_sys(p.ar.done[rank] + r, epoch, spin)) {
+          report_status(p.status, kStatusFlagTimeout, kKernelId, 0x910u);
+          break;
         }
       }
     }
@@ -628,6 +937,37 @@ __global__ void __launch_bounds__(kThreadsFor<EPI>, 1)
           signal_flag_sys(p.ar.ready[owner] + static_cast<long long>(tile) * p.ar.p + p.ar.rank,
                           epoch);
         }
+      } else if constexpr (EPI == kEpiReduceNorm) {
+        // park the bf16 partial tile in this GPU's own symmetric buffer as rows of the
+        // [M, N] matrix (the owners read whole rows), then tell every rank: each of them
+        // owns rows of this M tile
+        uint8_t* stage = smem + L::kOutOffset;
+        constexpr int SC = L::kOutCols;
+        constexpr int kChunksPerRow = SC / 8;
+        const int te1 = threadIdx.x - 64;
+        __nv_bfloat16* part = p.ar.partial[p.ar.rank];
+#pragma unroll 1
+        for (int h = 0; h < BN / SC; ++h) {
+          stage_tile<SC>(stage, taddr + h * SC, q * 32 + lane);
+          if (h == BN / SC - 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+          }
+          epi_bar_sync();
+#pragma unroll 2
+          for (int v = te1; v < BM * kChunksPerRow; v += 128) {
+            const int rr = v / kChunksPerRow, cc = v % kChunksPerRow;
+            const int grow = m0 + rr, gcol = n0 + h * SC + cc * 8;
+            if (grow >= p.M || gcol >= p.N) continue;
+            *reinterpret_cast<uint4*>(part + static_cast<long long>(grow) * p.N + gcol) =
+                *reinterpret_cast<const uint4*>(stage + stage_off<SC>(rr, cc));
+          }
+          epi_bar_sync();
+        }
+        if (te1 < p.ar.p)
+          st_release_sys(p.ar.ready[te1] + static_cast<long long>(tile) * p.ar.p + p.ar.rank,
+                         epoch);
       } else if constexpr (EPI == kEpiAllGather) {
         // store this rank's column block of the tile into every peer's full-width output;
         // staged so that a warp writes whole row segments (BN * 2 contiguous bytes per row)
@@ -698,7 +1038,7 @@ __global__ void __launch_bounds__(kThreadsFor<EPI>, 1)
           }
         }
       }
-      if constexpr (EPI != kEpiAllReduce && EPI != kEpiAllGather) {
+      if constexpr (EPI != kEpiAllReduce && EPI != kEpiAllGather && EPI != kEpiReduceNorm) {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tempty_bar[acc]);
@@ -830,6 +1170,7 @@ B200_API int b200_gemm_bf16(const void* A, long long lda, const void* B, long lo
   a.num_valid_rows = nullptr;
   a.row_scale = nullptr;
   a.m_rot = 0;
+  a.n_fastest = 0;
   a.ag = AgArgs{};
   a.ar = ArArgs{};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -910,6 +1251,7 @@ B200_API int b200_gemm_bf16_allreduce(const void* A, long long lda, const void* 
   a.num_valid_rows = nullptr;
   a.row_scale = nullptr;
   a.m_rot = 0;
+  a.n_fastest = 0;
   a.ag = AgArgs{};
   for (int i = 0; i < kMaxPeers; ++i) {
     a.ar.partial[i] = i < p ? static_cast<__nv_bfloat16*>(partial[i]) : nullptr;
@@ -927,6 +1269,82 @@ B200_API int b200_gemm_bf16_allreduce(const void* A, long long lda, const void* 
   if (bn == 64) return launch<64, 8, kEpiAllReduce>(tmA, tmB, a, s);
   if (bn == 256) return launch<256, 4, kEpiAllReduce>(tmA, tmB, a, s);
   return launch<128, 6, kEpiAllReduce>(tmA, tmB, a, s);
+}
+
+// Row-parallel GEMM fused with the all-reduce, the residual add and the RMSNorm that follow it
+// in a transformer layer:
+//   z      = sum over ranks ( A_rank[M,K] * B_rank[N,K]^T ) + residual      (rounded to bf16)
+//   out_r  = z * rsqrt(mean(z^2) + eps) * norm_weight    on every rank r    (norm_weight given)
+//   out_r  = z                                           on every rank r    (norm_weight null)
+// Every rank parks its bf16 partial product in its own symmetric buffer; inside every 128-row
+// tile rank r owns rows [128 r / p, 128 (r + 1) / p): reducer warps of the same kernel wait
+// for all column tiles of those rows from all ranks, pull them with plain peer loads (or one
+// in-switch multimem.ld_reduce when the multicast views mc_* are given), and store the
+// finished rows into every rank (peer stores or multimem.st).  The new residual z goes to
+// res_out of the owner only (bcast_res = 0: enough when the next consumer of the residual is
+// again this entry point) or of every rank (bcast_res = 1).  Without a norm weight res_out is
+// not written.
+// partial / out / res_out / ready / done: arrays of p peer-visible addresses (index = rank):
+// partial [M, N] bf16, out [M, ldc], res_out [M, N], ready ceil(M/128) * ceil(N/BN) * p words
+// (BN = b200_gemm_ar_tile_n(M, N)), done M words; epoch_ptr / done_ctr: local words, all zero
+// before the first call.  residual: local [M, ldr] or null.  N <= 8192.  All ranks pass the
+// same shapes.  A launch returns when every row of `out` has arrived on this rank.
+B200_API int b200_gemm_bf16_ar_norm(const void* A, long long lda, const void* B, long long ldb,
+                                    long long ldc, int M, int N, int K, void* const* partial,
+                                    void* const* out, void* const* res_out, void* const* ready,
+                                    void* const* done, void* epoch_ptr, void* done_ctr, int rank,
+                                    int p, const void* residual, long long ldr,
+                                    const void* norm_weight, float eps, int bcast_res,
+                                    const void* mc_partial, void* mc_out, void* mc_res,
+                                    void* stream) {
+  using namespace b200;
+  using namespace b200::gemm;
+  if (M <= 0 || N <= 0) return 0;
+  if (p < 1 || p > kMaxPeers || rank < 0 || rank >= p) return -2;
+  if (K <= 0 || (K % 8) != 0 || (lda % 8) != 0 || (ldb % 8) != 0 || (N % 8) != 0 ||
+      (ldc % 8) != 0 || (ldr % 8) != 0 || N > kRnKeep * 128 * 8)
+    return -2;
+  const int bn = b200_gemm_ar_tile_n(M, N);
+  CUtensorMap tmA, tmB;
+  int r = encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, static_cast<uint64_t>(M),
+                         static_cast<uint64_t>(K), static_cast<uint64_t>(lda) * 2, BM, BK,
+                         CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r != 0) return r < 0 ? -6 : r;
+  r = encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, static_cast<uint64_t>(N),
+                     static_cast<uint64_t>(K), static_cast<uint64_t>(ldb) * 2, bn, BK,
+                     CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r != 0) return r < 0 ? -6 : r;
+  Args a{};
+  a.ldc = ldc;
+  a.M = M; a.N = N; a.K = K;
+  a.tiles_m = (M + BM - 1) / BM;
+  a.tiles_n = (N + bn - 1) / bn;
+  a.status = status_ptr();
+  a.n_fastest = 1;
+  for (int i = 0; i < p; ++i) {
+    a.ar.partial[i] = static_cast<__nv_bfloat16*>(partial[i]);
+    a.ar.out[i] = static_cast<__nv_bfloat16*>(out[i]);
+    a.ar.res_out[i] = res_out ? static_cast<__nv_bfloat16*>(res_out[i]) : nullptr;
+    a.ar.ready[i] = static_cast<uint32_t*>(ready[i]);
+    a.ar.done[i] = static_cast<uint32_t*>(done[i]);
+  }
+  a.ar.epoch_ptr = static_cast<uint32_t*>(epoch_ptr);
+  a.ar.done_ctr = static_cast<uint32_t*>(done_ctr);
+  a.ar.rank = rank;
+  a.ar.p = p;
+  a.ar.res_in = static_cast<const __nv_bfloat16*>(residual);
+  a.ar.ld_res_in = ldr;
+  a.ar.norm_weight = static_cast<const __nv_bfloat16*>(norm_weight);
+  a.ar.eps = eps;
+  a.ar.bcast_res = bcast_res;
+  a.ar.mc_partial = static_cast<const __nv_bfloat16*>(mc_partial);
+  a.ar.mc_out = static_cast<__nv_bfloat16*>(mc_out);
+  a.ar.mc_res = static_cast<__nv_bfloat16*>(mc_res);
+  if (norm_weight != nullptr && res_out == nullptr) return -5;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (bn == 64) return launch<64, 8, kEpiReduceNorm>(tmA, tmB, a, s);
+  if (bn == 256) return launch<256, 4, kEpiReduceNorm>(tmA, tmB, a, s);
+  return launch<128, 6, kEpiReduceNorm>(tmA, tmB, a, s);
 }
 
 namespace {
@@ -1114,6 +1532,7 @@ B200_API int b200_gemm_bf16_grouped(const void* A, long long lda, const void* B,
   a.num_valid_rows = num_valid_rows;
   a.row_scale = row_scale;
   a.m_rot = 0;
+  a.n_fastest = 0;
   a.ag = AgArgs{};
   a.ar = ArArgs{};
   cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -27,7 +27,7 @@ import torch
 
 from ..config import EngineConfig
 from ..layers.attention import AttentionMetadata
-from ..layers.sampler import Sampler, SamplingTensors
+from ..layers.sampler import RowParallelSampler, Sampler, SamplingTensors
 from ..ops import _native
 from .scheduler import ScheduledRequest, SchedulerOutput
 
@@ -98,7 +98,11 @@ class ModelRunner:
         self.max_blocks = -(-sc.max_model_len // self.block_size) + 1
         self.kv_caches: list[torch.Tensor] = []
         self.num_blocks = 0
-        self.sampler = Sampler(cfg.model.vocab_size)
+        tp = cfg.parallel.tensor_parallel_size
+        # under tensor parallelism every rank samples its slice of the batch rows and the ids
+        # are gathered (the reference's DPParallelSampler, vllm_gcu/kernels/sampler.py:13-71)
+        self.sampler = (RowParallelSampler if tp > 1 else Sampler)(cfg.model.vocab_size)
+        self._greedy_shortcut = tp > 1 and hasattr(model, "greedy_tokens")
         self.max_spec = cfg.speculative.num_speculative_tokens if cfg.speculative.method else 0
         self.rejection = None
         self.drafter = None                        # on-device drafter (DeepSeek MTP)
@@ -787,6 +791,15 @@ class ModelRunner:
             rows = hidden[:ns]          # decode-only: row i is the i-th sampling request
         else:
             rows = hidden.index_select(0, self.sample_indices[:ns * width])
+        if (all_greedy and width == 1 and feats is None and not self.keep_logits
+                and self.drafter is None and self._greedy_shortcut):
+            # greedy decoding under tensor parallelism: each rank reduces its vocabulary block
+            # to (max, argmax) per row and only those pairs are exchanged
+            out_ids[:ns].copy_(self.model.greedy_tokens(rows))
+            if pp.world_size > 1:
+                import torch.distributed as dist
+                dist.broadcast(out_ids[:ns * width], pp.ranks[-1], group=pp.device_group)
+            return
         logits = self.model.compute_logits(rows)
         if self.keep_logits:
             self.last_logits = logits.float().cpu()

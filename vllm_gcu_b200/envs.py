@@ -56,6 +56,10 @@ environment_variables: dict[str, Callable[[], Any]] = {
     "ORACLE": lambda: None if _get("ORACLE") is None else _get("ORACLE").split(","),
     # communication backend of the tensor-parallel collectives: fused | nccl
     "COMM": lambda: _get("COMM", "fused"),
+    # in-switch reduction / broadcast (NVLS multimem instructions) inside the fused
+    # tensor-parallel kernels when the symmetric allocation has a multicast view; 0 keeps them
+    # on plain peer loads and stores
+    "MULTIMEM": _flag("MULTIMEM", "1"),
     # NVTX range around every engine step, named by its kind (the reference opens a vendor
     # profiler range per step, vllm_gcu/worker/worker_v1.py:322-335)
     "NVTX": _flag("NVTX"),

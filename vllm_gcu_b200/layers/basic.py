@@ -190,6 +190,11 @@ class ParallelLMHead(VocabParallelEmbedding):
         lg = lg[..., :valid]
         if tp_size() == 1:
             return lg.argmax(-1)
+        if ops.use_native(hidden) and lg.dim() == 2:
+            fused = getattr(get_comm("tp"), "fused", None)
+            ids = fused.greedy_argmax(lg, valid, self.start) if fused is not None else None
+            if ids is not None:
+                return ids
         val, idx = lg.float().max(-1)
         pair = torch.stack([val, (idx + self.start).float()], dim=-1)
         allp = get_comm("tp").all_gather(pair.unsqueeze(0), dim=0)    # [tp, B, 2]

@@ -48,6 +48,13 @@ class DenseMLP(nn.Module):
         if not isinstance(self.gate_up_proj.quant_method, UnquantizedLinearMethod):
             self.gate_up_proj.fuse_silu = False   # quantised GEMMs have no SiLU epilogue yet
 
+    def before_down_proj(self, x: torch.Tensor) -> torch.Tensor:
+        h = self.gate_up_proj(x)
+        if not self.gate_up_proj.fuse_silu:
+            from ..layers.activation import act_and_mul
+            h = act_and_mul(h, self.act)
+        return h
+
     def forward(self, x: torch.Tensor, sp_sizes: Optional[list] = None) -> torch.Tensor:
         """``sp_sizes`` (sequence parallelism): ``x`` holds this rank's rows; the rows are
         gathered for the column-parallel projection and the row-parallel output is
@@ -93,11 +100,15 @@ class GQAAttention(nn.Module):
         self.attn = PagedAttention(self.qkv_proj.num_heads, self.qkv_proj.num_kv_heads, D,
                                    D ** -0.5, rotary, qn, kn, cfg.sliding_window)
 
+    def before_o_proj(self, x: torch.Tensor, kv_cache: torch.Tensor, md: AttentionMetadata
+                      ) -> torch.Tensor:
+        """Attention output of this rank's heads (the input of the row-parallel o_proj)."""
+        return self.attn(self.qkv_proj(x), kv_cache, md)
+
     def forward(self, x: torch.Tensor, kv_cache: torch.Tensor, md: AttentionMetadata,
                 sp_sizes: Optional[list] = None) -> torch.Tensor:
         if sp_sizes is None:
-            qkv = self.qkv_proj(x)
-            return self.o_proj(self.attn(qkv, kv_cache, md))
+            return self.o_proj(self.before_o_proj(x, kv_cache, md))
         # sequence parallelism: rows in, rows out (vllm_gcu/models/deepseek_v3/
         # deepseek_v3.py:611-612,747-748: sp_to_tp before the projections, tp_to_sp after o_proj)
         from ..parallel import sp
@@ -131,6 +142,54 @@ class DecoderLayer(nn.Module):
         if self.sandwich:
             self.post_self_attn_layernorm = RMSNorm(H, cfg.rms_norm_eps, cfg.dtype, device)
             self.post_mlp_layernorm = RMSNorm(H, cfg.rms_norm_eps, cfg.dtype, device)
+
+    # -- tensor parallel with the reductions fused into the GEMMs --------------------------
+    def fusable(self) -> tuple[bool, bool]:
+        """(attention block, MLP block) can use ``FusedTP.gemm_ar_norm``: plain bf16
+        row-parallel projections without bias / LoRA wrapper and plain RMSNorms around them."""
+        from ..layers.linear import UnquantizedLinearMethod
+
+        def row_ok(m) -> bool:
+            return (type(m) is RowParallelLinear and m.bias is None and m.reduce_results
+                    and isinstance(m.quant_method, UnquantizedLinearMethod)
+                    and m.weight.dtype == torch.bfloat16)
+
+        norms_ok = (not self.sandwich and type(self.input_layernorm) is RMSNorm
+                    and type(self.post_attention_layernorm) is RMSNorm)
+        attn_ok = norms_ok and isinstance(self.self_attn, GQAAttention) \
+            and row_ok(self.self_attn.o_proj)
+        mlp_ok = attn_ok and isinstance(self.mlp, DenseMLP) and row_ok(self.mlp.down_proj)
+        return attn_ok, mlp_ok
+
+    def forward_fused_tp(self, x: torch.Tensor, residual: Optional[torch.Tensor],
+                         kv_cache: torch.Tensor, md: AttentionMetadata, fused,
+                         x_is_normed: bool, next_norm: Optional[RMSNorm]):
+        """Layer forward where o_proj and down_proj run as one kernel each with their
+        all-reduce, the residual add and the RMSNorm that follows them.  ``x_is_normed``: ``x``
+        already went through this layer's input norm (the previous layer's down_proj did it).
+        Returns ``(x, residual, x_is_normed)`` for the next layer; ``next_norm`` is the norm
+        that follows this layer (the next layer's input norm, or the final norm)."""
+        _, mlp_ok = self.fusable()
+        if x_is_normed:
+            h = x
+        elif residual is None:
+            residual = x
+            h = self.input_layernorm(x)
+        else:
+            h, residual = self.input_layernorm(x, residual)
+        a = self.self_attn.before_o_proj(h, kv_cache, md)
+        pn = self.post_attention_layernorm
+        # the new residual is needed on every rank only if a plain norm reads it next
+        fuse_mlp = mlp_ok and next_norm is not None
+        h, residual = fused.gemm_ar_norm(a, self.self_attn.o_proj.weight, residual, pn.weight,
+                                         pn.eps, bcast_residual=not fuse_mlp)
+        if not fuse_mlp:
+            h = self.mlp(h)
+            return h, residual, False
+        h = self.mlp.before_down_proj(h)
+        h, residual = fused.gemm_ar_norm(h, self.mlp.down_proj.weight, residual,
+                                         next_norm.weight, next_norm.eps, bcast_residual=False)
+        return h, residual, True
 
     def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor], kv_cache: torch.Tensor,
                 md: AttentionMetadata, sp_sizes: Optional[list] = None):
@@ -236,11 +295,28 @@ class DecoderLM(nn.Module):
             total = x.shape[0]
             sp_sizes = sp.scatter(total, tp_size())
             x = sp.slice_tensor_sp(x)
-        for j, i in enumerate(range(self.start_layer, self.end_layer)):
-            x, residual = self.layers[str(i)](x, residual, kv_caches[j], md, sp_sizes)
+        fused = self._fused_tp(x) if sp_sizes is None else None
+        normed = False
+        ids = list(range(self.start_layer, self.end_layer))
+        for j, i in enumerate(ids):
+            layer = self.layers[str(i)]
+            if fused is not None and layer.fusable()[0]:
+                if j + 1 < len(ids):
+                    nxt = self.layers[str(ids[j + 1])]
+                    next_norm = nxt.input_layernorm if nxt.fusable()[0] else None
+                else:
+                    next_norm = self.norm if self.is_last_stage and type(self.norm) is RMSNorm \
+                        else None
+                x, residual, normed = layer.forward_fused_tp(x, residual, kv_caches[j], md, fused,
+                                                             normed, next_norm)
+            else:
+                assert not normed
+                x, residual = layer(x, residual, kv_caches[j], md, sp_sizes)
         if not self.is_last_stage:
             return x, residual
-        if residual is None:
+        if normed:
+            pass                        # the last down_proj applied the final norm
+        elif residual is None:
             x = self.norm(x)
         else:
             x, _ = self.norm(x, residual)
@@ -248,6 +324,20 @@ class DecoderLM(nn.Module):
             from ..parallel import sp
             x = sp.sp_to_tp(x, sum(sp_sizes))
         return x
+
+    def _fused_tp(self, x: torch.Tensor):
+        """The tensor-parallel workspace when this step can run the fused
+        GEMM + all-reduce + norm kernels (GPU, TP > 1, ``comm_backend="fused"``, the token
+        count fits the workspace); None otherwise."""
+        if tp_size() <= 1 or not x.is_cuda or x.dtype != torch.bfloat16 or x.shape[0] == 0:
+            return None
+        from ..parallel.communicator import get_comm
+        fused = getattr(get_comm("tp"), "fused", None)
+        if fused is None or not getattr(fused, "fuse_norm", True):
+            return None
+        if x.shape[0] > fused.max_tokens or x.shape[1] > min(fused.max_n, 8192):
+            return None
+        return fused
 
     def _head(self) -> ParallelLMHead:
         return self.lm_head if self.lm_head is not None else self.embed_tokens  # type: ignore

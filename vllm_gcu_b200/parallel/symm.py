@@ -56,6 +56,12 @@ def _register_sigs() -> None:
     lib.b200_gemm_bf16_gather_a.restype = I
     lib.b200_gemm_bf16_gather_a.argtypes = [P, L, P, P, L, P, L, P, L, I, I, I, P, P, P, P, P, P,
                                             I, I, P]
+    F = ctypes.c_float
+    lib.b200_gemm_bf16_ar_norm.restype = I
+    lib.b200_gemm_bf16_ar_norm.argtypes = [P, L, P, L, L, I, I, I, P, P, P, P, P, P, P, I, I, P, L,
+                                           P, F, I, P, P, P, P]
+    lib.b200_argmax_allgather.restype = I
+    lib.b200_argmax_allgather.argtypes = [P, L, I, I, I, P, I, P, P, I, I, P, P]
     lib.b200_allreduce.restype = I
     lib.b200_allreduce.argtypes = [P, P, P, P, P, P, L, I, I, I, P]
     _SIG_DONE = True
@@ -93,6 +99,7 @@ class SymmetricBuffer:
 class FusedTP:
     BM = 128
     ONESHOT_MAX_TOKENS = 1024
+    ARGMAX_ROWS = 1024
 
     def __init__(self, max_tokens: int, max_n: int, device: torch.device, group_name: str = "tp"):
         _register_sigs()
@@ -121,11 +128,21 @@ class FusedTP:
         self.off_ready = self.part_bytes + 2 * self.out_bytes
         self.off_done = self.off_ready + self.ready_bytes
         self.off_ar_flag = self.off_done + self.done_bytes                   # stand-alone all-reduce
-        total = self.off_ar_flag + 4096
+        # row-owner reduce + norm: new-residual buffers (double buffered) and one flag per row
+        self.off_res = [self.off_ar_flag + 4096, self.off_ar_flag + 4096 + self.out_bytes]
+        self.off_row_done = self.off_res[1] + self.out_bytes
+        # greedy sampling: 2 (epoch parity) x p x ARGMAX_ROWS records of 16 bytes
+        self.off_argmax = -(-(self.off_row_done + rows * 4) // 256) * 256
+        total = self.off_argmax + 2 * self.p * self.ARGMAX_ROWS * 16 + 256
         self.buf = SymmetricBuffer(total, pg, device)
         self.local_words = torch.zeros(16, dtype=torch.int32, device=device)  # epoch, ctr, ...
         self.out_sel = 0
+        self.res_sel = 0
         self.force_mode: Optional[str] = None     # benchmarks: "oneshot" | "twoshot"
+        from .. import envs
+        # in-switch reduction and broadcast (NVLS multimem) when the allocation has a multicast
+        # view; VLLM_B200_MULTIMEM=0 keeps the kernels on plain peer loads and stores
+        self.use_multimem = bool(self.buf.multicast_ptr) and bool(getattr(envs, "MULTIMEM", True))
         dist.barrier(group=pg)
         torch.cuda.synchronize()
 
@@ -164,6 +181,82 @@ class FusedTP:
              residual.stride(0) if residual is not None else 0,
              int(self._oneshot(M)), self.slot_elems, stream_ptr())
         return out_local.view(*shape[:-1], N)
+
+    def gemm_ar_norm(self, x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor],
+                     norm_weight: Optional[torch.Tensor], eps: float = 1e-6,
+                     bcast_residual: bool = True
+                     ) -> Optional[tuple[torch.Tensor, Optional[torch.Tensor]]]:
+        """Row-parallel GEMM + all-reduce + residual add + RMSNorm in one kernel
+        (``b200_gemm_bf16_ar_norm``): returns ``(normed, new_residual)`` as views of the
+        symmetric workspace, or None when the problem does not fit (the caller then runs the
+        un-fused sequence).  ``new_residual`` holds valid rows on every rank only with
+        ``bcast_residual``; otherwise each rank holds the rows it owns
+        (``[128 r / p, 128 (r + 1) / p)`` of every 128-row tile), which is all the next call of
+        this method reads.  Without ``norm_weight`` the result is the plain all-reduced sum
+        (+ residual) and ``new_residual`` is None.  Replaces ``RowParallelLinear`` +
+        ``all_reduce`` + ``fused_add_rms_norm`` of the reference
+        (vllm_gcu/distributed/gcu_communicator.py:88-111, vllm_gcu/kernels/layernorm.py:10-41)."""
+        if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+            return None
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        M, K = x2.shape
+        N = w.shape[0]
+        if M == 0 or M > self.max_tokens or N > self.max_n or N > 8192 or K % 8 or N % 8:
+            return None
+        if residual is not None:
+            residual = residual.reshape(-1, N)
+            if residual.stride(-1) != 1 or residual.stride(0) % 8 or residual.dtype != x.dtype:
+                return None
+        lib = _native.lib()
+        bn = lib.b200_gemm_ar_tile_n(M, N)
+        if (-(-M // self.BM)) * (-(-N // bn)) > self.max_tiles:
+            return None
+        self.out_sel ^= 1
+        off_out = self.off_out[self.out_sel]
+        off_res = 0
+        if norm_weight is not None:
+            self.res_sel ^= 1
+            off_res = self.off_res[self.res_sel]
+        mc = self.buf.multicast_ptr if self.use_multimem else 0
+        words = self.local_words.data_ptr()
+        call("b200_gemm_bf16_ar_norm", ptr(x2), x2.stride(0), ptr(w), w.stride(0), N, M, N, K,
+             _ptr_array(self.buf.peer_ptrs(self.off_part)),
+             _ptr_array(self.buf.peer_ptrs(off_out)),
+             _ptr_array(self.buf.peer_ptrs(off_res)) if norm_weight is not None else None,
+             _ptr_array(self.buf.peer_ptrs(self.off_ready)),
+             _ptr_array(self.buf.peer_ptrs(self.off_row_done)),
+             words, words + 4, self.rank, self.p, ptr(residual),
+             residual.stride(0) if residual is not None else 0, ptr(norm_weight), float(eps),
+             int(bool(bcast_residual)),
+             mc + self.off_part if mc else None, mc + off_out if mc else None,
+             mc + off_res if (mc and norm_weight is not None) else None, stream_ptr())
+        out = self.buf.local[off_out:off_out + M * N * 2].view(torch.bfloat16).view(M, N)
+        res = None
+        if norm_weight is not None:
+            res = self.buf.local[off_res:off_res + M * N * 2].view(torch.bfloat16).view(M, N)
+        return out.view(*x.shape[:-1], N), res
+
+    def greedy_argmax(self, local_logits: torch.Tensor, valid: int, vocab_offset: int
+                      ) -> Optional[torch.Tensor]:
+        """Token ids ``[B]`` (int64) of the maximum over the vocabulary-parallel logits: every
+        rank passes its ``[B, V/p]`` block, ``valid`` = number of real (un-padded) columns in
+        it and ``vocab_offset`` = id of its first column.  16 bytes per row and rank cross
+        NVLink instead of the logits (``b200_argmax_allgather``); the reference exchanges
+        sampled ids, not logits, in the same spirit (vllm_gcu/kernels/sampler.py:13-71)."""
+        if local_logits.dtype != torch.bfloat16 or local_logits.dim() != 2 \
+                or local_logits.stride(1) != 1 or local_logits.stride(0) % 8:
+            return None
+        B = local_logits.shape[0]
+        if B == 0 or B > self.ARGMAX_ROWS:
+            return None
+        out = torch.empty(B, dtype=torch.int64, device=local_logits.device)
+        words = self.local_words.data_ptr()
+        call("b200_argmax_allgather", ptr(local_logits), local_logits.stride(0), B, int(valid),
+             int(vocab_offset), _ptr_array(self.buf.peer_ptrs(self.off_argmax)), self.ARGMAX_ROWS,
+             words + 32, words + 36, self.rank, self.p, ptr(out), stream_ptr())
+        return out
 
     def _oneshot(self, M: int) -> bool:
         fits = -(-M // self.BM) * self.BM <= self.oneshot_rows
