@@ -117,12 +117,25 @@ def main():
                 dist.all_reduce(y)
                 return C.norm(y, nw, 1e-5, residual=resid)
             res["nccl_norm_us"] = timed(unfused, 5, gr)
-            for mc in ([False, True] if fused.buf.multicast_ptr else [False]):
+            variants = [("ar_norm_pull_us", False, 0), ("ar_norm_push_us", False, 1),
+                        ("ar_norm_pushall_us", False, 2), ("ar_norm_ll_us", False, 3),
+                        ("ar_norm_us", False, None)]
+            if fused.buf.multicast_ptr:
+                variants.append(("ar_norm_mc_us", True, 0))
+            for key, mc, mode in variants:
+                if mode in (1, 2, 3) and M > 1024:
+                    continue            # the push transports are for decode-sized problems
                 fused.use_multimem = mc
-                key = "ar_norm_mc_us" if mc else "ar_norm_us"
+                fused.force_rn_mode = mode
+                fused.row_owner = True if mode is None else None
                 res[key] = timed(lambda i: fused.gemm_ar_norm(x, ws[i], resid, nw, 1e-5,
                                                               bcast_residual=False), 5, gr)
                 _native.check_status()
+            fused.force_rn_mode = None
+            fused.row_owner = None
+            fused.use_multimem = bool(fused.buf.multicast_ptr)
+            res["ar_norm_default_us"] = timed(lambda i: fused.gemm_ar_norm(
+                x, ws[i], resid, nw, 1e-5, bcast_residual=False), 5, gr)
             flop_us = 2.0 * M * N * K / (peaks["bf16_tflops"] * 1e12) * 1e6
             hbm_us = (N * K + M * K + 2 * M * N) * 2 / (peaks["hbm_gbs"] * 1e9) * 1e6
             # per GPU and direction: (p-1)/p of the partial matrix in, (p-1)/p of the result in

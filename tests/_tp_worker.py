@@ -93,9 +93,13 @@ def check_gemm_ar_norm(fused, world, rank, dev):
     the norm, with the new residual on the owner only / on every rank, over plain peer
     accesses and (when the allocation has a multicast view) over multimem."""
     lo_hi = lambda r: (128 * r // world, 128 * (r + 1) // world)
-    modes = [False, True] if fused.buf.multicast_ptr else [False]
-    for use_mc in modes:
+    modes = [(False, 0), (False, 1), (False, 2), (False, 3), (False, None)]
+    if fused.buf.multicast_ptr:
+        modes.append((True, 0))
+    for use_mc, rn_mode in modes:
         fused.use_multimem = use_mc
+        fused.force_rn_mode = rn_mode
+        fused.row_owner = True if rn_mode is None else None
         for (M, N, K) in [(256, 4096, 512), (7, 1024, 256), (1024, 4096, 1792), (300, 2048, 72)]:
             g = torch.Generator(device="cuda").manual_seed(100 + rank)
             x = torch.randn(M, K, device=dev, dtype=torch.bfloat16, generator=g)
@@ -107,15 +111,15 @@ def check_gemm_ar_norm(fused, world, rank, dev):
             dist.all_reduce(part)
             z = (part + res.float()).to(torch.bfloat16).float()
             normed = z * torch.rsqrt(z.pow(2).mean(-1, keepdim=True) + 1e-5) * nw.float()
-            for rep, bcast in enumerate([True, False, True]):
+            for rep, bcast in enumerate([True, False, True, False, False]):
                 out, nres = fused.gemm_ar_norm(x, w, res, nw, 1e-5, bcast_residual=bcast)
                 torch.cuda.synchronize()
                 _native.check_status()
-                tag = f"gemm_ar_norm mc={use_mc} {M}x{N}x{K} rep {rep}"
+                tag = f"gemm_ar_norm mc={use_mc} mode={rn_mode} {M}x{N}x{K} rep {rep}"
                 err = (out.float() - normed).abs().max().item()
                 assert err < 0.03 * normed.abs().max().item() + 0.03, f"{tag}: out err {err}"
                 rows = torch.arange(M, device=dev)
-                if not bcast:
+                if not bcast and fused._rn_mode(M, N, 64) != 2:
                     l, h = lo_hi(rank)
                     rows = rows[(rows % 128 >= l) & (rows % 128 < h)]
                 rerr = (nres.float()[rows] - z[rows]).abs().max().item() if rows.numel() else 0.0
@@ -126,6 +130,24 @@ def check_gemm_ar_norm(fused, world, rank, dev):
             assert nres is None
             err = (out.float() - part).abs().max().item()
             assert err < 0.03 * part.abs().max().item() + 0.03, f"plain reduce {M}x{N}x{K}: {err}"
+    fused.force_rn_mode = None
+    fused.row_owner = None
+    # the default policy (may run as GEMM + all-reduce followed by the norm kernel)
+    g = torch.Generator(device="cuda").manual_seed(100 + rank)
+    x = torch.randn(256, 512, device=dev, dtype=torch.bfloat16, generator=g)
+    w = (torch.randn(4096, 512, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+    g2 = torch.Generator(device="cuda").manual_seed(5)
+    res = torch.randn(256, 4096, device=dev, generator=g2).to(torch.bfloat16)
+    nw = (1.0 + 0.1 * torch.randn(4096, device=dev, generator=g2)).to(torch.bfloat16)
+    part = (x.float() @ w.float().t()).to(torch.bfloat16).float()
+    dist.all_reduce(part)
+    z = (part + res.float()).to(torch.bfloat16).float()
+    normed = z * torch.rsqrt(z.pow(2).mean(-1, keepdim=True) + 1e-5) * nw.float()
+    out, _ = fused.gemm_ar_norm(x, w, res.clone(), nw, 1e-5, bcast_residual=True)
+    torch.cuda.synchronize()
+    _native.check_status()
+    err = (out.float() - normed).abs().max().item()
+    assert err < 0.03 * normed.abs().max().item() + 0.03, f"default policy: out err {err}"
     # greedy tokens from vocabulary-parallel logits
     for B, V in [(256, 16064), (3, 520)]:
         g = torch.Generator(device="cuda").manual_seed(900 + rank)

@@ -22,27 +22,36 @@ class _Ws:
     """Plain device tensors standing in for the symmetric buffers of a one-rank group."""
 
     def __init__(self, rows, n, dev):
-        self.partial = torch.zeros(rows, n, dtype=torch.bfloat16, device=dev)
+        self.partial = torch.zeros(2 * rows, n, dtype=torch.bfloat16, device=dev)   # two parities
         self.out = torch.zeros(rows, n, dtype=torch.bfloat16, device=dev)
         self.res = torch.zeros(rows, n, dtype=torch.bfloat16, device=dev)
         self.ready = torch.zeros(rows // 128 * (n // 64) + 64, dtype=torch.int32, device=dev)
         self.done = torch.zeros(rows, dtype=torch.int32, device=dev)
         self.words = torch.zeros(16, dtype=torch.int32, device=dev)
+        self.base = torch.zeros(rows // 128 + 1, dtype=torch.int32, device=dev)
+        # sentinel-tagged transport (mode 3): three rotating buffers each way
+        self.cap = rows * n
+        self.ll_slots = torch.full((3 * self.cap // 2,), -2147450880, dtype=torch.int32, device=dev)
+        self.ll_out = torch.full((3 * self.cap // 2,), -2147450880, dtype=torch.int32, device=dev)
+        self.ll_used = torch.zeros(6, dtype=torch.int64, device=dev)
 
 
-def _run(ws, x, w, residual, norm_w, eps, bcast):
+def _run(ws, x, w, residual, norm_w, eps, bcast, mode=0):
     from vllm_gcu_b200.parallel import symm
     symm._register_sigs()
     M, K = x.shape
     N = w.shape[0]
     wp = ws.words.data_ptr()
+    ll = mode == 3
     _native.call("b200_gemm_bf16_ar_norm", x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0),
-                 N, M, N, K, _arr(ws.partial), _arr(ws.out),
+                 N, M, N, K, _arr(ws.ll_slots if ll else ws.partial),
+                 _arr(ws.ll_out if ll else ws.out),
                  _arr(ws.res) if norm_w is not None else None, _arr(ws.ready), _arr(ws.done),
-                 wp, wp + 16, 0, 1, None if residual is None else residual.data_ptr(),
+                 ws.base.data_ptr(), wp, wp + 16, 0, 1, None if residual is None else residual.data_ptr(),
                  0 if residual is None else residual.stride(0),
-                 None if norm_w is None else norm_w.data_ptr(), float(eps), int(bcast),
-                 None, None, None, _native.stream_ptr())
+                 None if norm_w is None else norm_w.data_ptr(), float(eps), int(bcast), mode,
+                 None, None, None, ws.out.data_ptr(), ws.cap, ws.ll_used.data_ptr(),
+                 _native.stream_ptr())
 
 
 @pytest.mark.parametrize("M,N,K", [(8, 4096, 512), (256, 4096, 1792), (300, 2048, 1024),
@@ -59,8 +68,12 @@ def test_gemm_reduce_norm_one_rank(M, N, K, mode):
     ws = _Ws(rows, N, dev)
     use_res = mode in ("norm", "plain_res")
     use_norm = mode.startswith("norm")
-    for it in range(2):                       # the second call runs on the advanced epoch
-        _run(ws, x, w, res if use_res else None, nw if use_norm else None, 1e-5, it)
+    for it in range(8):                       # later calls run on advanced epochs / rotated buffers
+        # transports: owners pull / rows pushed to the owner / rows pushed to everyone /
+        # sentinel-tagged push (needs the residual to stay with the owner)
+        mode = (M + it) % 4
+        _run(ws, x, w, res if use_res else None, nw if use_norm else None, 1e-5,
+             0 if mode == 3 else it % 2, mode=mode)
         torch.cuda.synchronize()
         _native.check_status()
         z = x.float() @ w.float().t()

@@ -69,6 +69,24 @@ struct ArArgs {
   const __nv_bfloat16* norm_weight;   // [N] (null: plain all-reduce, out = sum + residual)
   float eps;
   int bcast_res;                      // 1: the new residual goes to every rank, 0: owner only
+  // how the partial rows reach their reducer:
+  //   0 pull      every rank parks its partial matrix locally, owners read the rows from the peers
+  //   1 push      the epilogue stores each row into the slot (parity, source rank) of its owner
+  //   2 push-all  every rank receives all rows and reduces all of them (one hop, no broadcast)
+  int rn_mode;
+  long long slot_rows;                // push: rows per (parity, source) slot on a receiver
+  // kEpiReduceNorm counts arrivals instead of keeping a flag per tile: ready[r][tm] is a counter
+  // on rank r that every rank bumps once per finished column tile of M tile tm; ready_base[tm]
+  // (local) is its value before this launch, advanced by the last CTA of the launch
+  uint32_t* ready_base;
+  // mode 3 ("data carries its own arrival"): no flags and no fences.  The transport buffers
+  // hold a sentinel word until real data lands in them; partial[r] / out[r] then point to
+  // three rotating buffers of ll_cap elements each on rank r (rows pushed to their owner /
+  // finished rows pushed to everyone), the finished rows are copied into ll_out_local, and
+  // ll_used[2 * b], ll_used[2 * b + 1] remember how much of buffer b a launch has dirtied
+  __nv_bfloat16* ll_out_local;        // [M, ldc] result on this rank
+  long long ll_cap;
+  long long* ll_used;
   // multicast (NVLS) views of the same symmetric buffers; null = plain peer loads / stores
   const __nv_bfloat16* mc_partial;
   __nv_bfloat16* mc_out;
@@ -303,6 +321,19 @@ __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
 __device__ __forceinline__ void st_release_sys(uint32_t* flag, uint32_t val) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(val) : "memory");
 }
+__device__ __forceinline__ void red_release_sys_add(uint32_t* ctr, uint32_t val) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(ctr), "r"(val) : "memory");
+}
+// Bounded wait until the arrival counter has advanced by `need` beyond `base` (one polling
+// thread; peers that are a launch ahead only push it further).
+__device__ __forceinline__ bool wait_count_sys(const uint32_t* ctr, uint32_t base, uint32_t need,
+                                               uint32_t limit) {
+  for (uint32_t it = 0; it < limit; ++it) {
+    if (static_cast<int32_t>(ld_acquire_sys_u32(ctr) - base - need) >= 0) return true;
+    if (it > 32) __nanosleep(40);
+  }
+  return false;
+}
 
 // One output row, handled by TPR reducer threads (thread `t` of them owns the chunks t,
 // t + TPR, ... of the row): all 128 reducer threads of the CTA for decode-sized problems (one
@@ -314,13 +345,17 @@ __device__ __forceinline__ void st_release_sys(uint32_t* flag, uint32_t val) {
 // 4-float shared scratch for the statistics); with TPR = 32 it is read back from the residual
 // buffer this thread has just written.
 template <int U, int TPR>
-__device__ __forceinline__ void reduce_norm_row(const ArArgs& ar, int row, int N, long long ldc,
-                                                int t, float* red) {
+__device__ __noinline__ void reduce_norm_row(const ArArgs& ar, int row, int N, long long ldc,
+                                                int t, float* red, long long push_off) {
   constexpr bool kKeep = TPR == 128;
   constexpr int kIters = kKeep ? kRnKeep : (kRnKeep * 128 / TPR);
   const int nvec = N >> 3;
   const int np = ar.p, rank = ar.rank;
   const long long roff = static_cast<long long>(row) * N;      // partial / res_out rows: pitch N
+  const bool push = ar.rn_mode != 0;
+  const int ndst = ar.rn_mode == 2 ? 1 : np;                   // push-all: results stay local
+  // source s of this row: pull = rank s's parked matrix, push = slot s of the local buffer
+  const long long slot_pitch = ar.slot_rows * static_cast<long long>(N);
   uint4 z[kKeep ? kRnKeep : 1];
   float sumsq = 0.0f;
   const bool have_norm = ar.norm_weight != nullptr;
@@ -332,7 +367,7 @@ __device__ __forceinline__ void reduce_norm_row(const ArArgs& ar, int row, int N
     for (int u = 0; u < U; ++u)
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[u][i] = 0.0f;
-    if (ar.mc_partial != nullptr) {
+    if (ar.mc_partial != nullptr && !push) {
       uint4 v[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
@@ -342,7 +377,7 @@ __device__ __forceinline__ void reduce_norm_row(const ArArgs& ar, int row, int N
 #pragma unroll
       for (int u = 0; u < U; ++u) add8(acc[u], v[u]);
     } else {
-      constexpr int kR = 16 / U;                 // ranks per batch of loads
+      constexpr int kR = 8 / U;                  // ranks per batch of loads (8 loads in flight)
       for (int r0 = 0; r0 < np; r0 += kR) {
         uint4 v[kR][U];
 #pragma unroll
@@ -350,9 +385,11 @@ __device__ __forceinline__ void reduce_norm_row(const ArArgs& ar, int row, int N
 #pragma unroll
           for (int u = 0; u < U; ++u) {
             const int c = t + (j0 + u) * TPR;
-            v[r][u] = (r0 + r < np && c < nvec)
-                          ? ld_volatile_v4(ar.partial[r0 + r] + roff + c * 8)
-                          : make_uint4(0, 0, 0, 0);
+            const __nv_bfloat16* src =
+                push ? ar.partial[rank] + push_off + (r0 + r) * slot_pitch
+                     : ar.partial[(r0 + r) < np ? (r0 + r) : 0] + roff;
+            v[r][u] = (r0 + r < np && c < nvec) ? ld_volatile_v4(src + c * 8)
+                                                : make_uint4(0, 0, 0, 0);
           }
 #pragma unroll
         for (int r = 0; r < kR; ++r)
@@ -378,7 +415,7 @@ __device__ __forceinline__ void reduce_norm_row(const ArArgs& ar, int row, int N
 #pragma unroll
         for (int i = 0; i < 8; ++i) sumsq += f[i] * f[i];
         // the new residual: every rank, or the owner only
-        if (ar.bcast_res) {
+        if (ar.bcast_res && ndst > 1) {
           if (ar.mc_res != nullptr) {
             mc_st_v4(ar.mc_res + roff + c * 8, o);
             if constexpr (!kKeep) *reinterpret_cast<uint4*>(ar.res_out[rank] + roff + c * 8) = o;
@@ -391,7 +428,9 @@ __device__ __forceinline__ void reduce_norm_row(const ArArgs& ar, int row, int N
         }
       } else {
         const long long ooff = static_cast<long long>(row) * ldc + c * 8;
-        if (ar.mc_out != nullptr) {
+        if (ndst == 1) {
+          *reinterpret_cast<uint4*>(ar.out[rank] + ooff) = o;
+        } else if (ar.mc_out != nullptr) {
           mc_st_v4(ar.mc_out + ooff, o);
         } else {
           for (int r = 0; r < np; ++r) *reinterpret_cast<uint4*>(ar.out[r] + ooff) = o;
@@ -408,29 +447,178 @@ __device__ __forceinline__ void reduce_norm_row(const ArArgs& ar, int row, int N
     gather_bar_sync();                           // `red` is reused by the next row
   }
   const float rstd = rsqrtf(sumsq / static_cast<float>(N) + ar.eps);
+  constexpr int kB = 4;                          // chunks per batch of the second pass
 #pragma unroll
-  for (int j = 0; j < kIters; ++j) {
-    const int c = t + j * TPR;
-    if (c >= nvec) break;
-    float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    if constexpr (kKeep) {
-      add8(f, z[j]);
-    } else {
-      // written by this very thread in the first pass
-      add8(f, ld_volatile_v4(ar.res_out[rank] + roff + c * 8));
+  for (int j0 = 0; j0 < kIters; j0 += kB) {
+    if (t + j0 * TPR >= nvec) break;
+    uint4 zz[kB], ww[kB];
+#pragma unroll
+    for (int u = 0; u < kB; ++u) {
+      const int c = t + (j0 + u) * TPR;
+      if (c >= nvec) continue;
+      if constexpr (kKeep) {
+        zz[u] = z[j0 + u];
+      } else {
+        zz[u] = ld_volatile_v4(ar.res_out[rank] + roff + c * 8);   // written by this thread
+      }
+      ww[u] = *reinterpret_cast<const uint4*>(ar.norm_weight + c * 8);
     }
-    float w[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    add8(w, *reinterpret_cast<const uint4*>(ar.norm_weight + c * 8));
 #pragma unroll
-    for (int i = 0; i < 8; ++i) f[i] = f[i] * rstd * w[i];
-    const uint4 o = pack8(f);
-    const long long ooff = static_cast<long long>(row) * ldc + c * 8;
-    if (ar.mc_out != nullptr) {
-      mc_st_v4(ar.mc_out + ooff, o);
-    } else {
-      for (int r = 0; r < np; ++r) *reinterpret_cast<uint4*>(ar.out[r] + ooff) = o;
+    for (int u = 0; u < kB; ++u) {
+      const int c = t + (j0 + u) * TPR;
+      if (c >= nvec) continue;
+      float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      float w[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      add8(f, zz[u]);
+      add8(w, ww[u]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = f[i] * rstd * w[i];
+      const uint4 o = pack8(f);
+      const long long ooff = static_cast<long long>(row) * ldc + c * 8;
+      if (ndst == 1) {
+        *reinterpret_cast<uint4*>(ar.out[rank] + ooff) = o;
+      } else if (ar.mc_out != nullptr) {
+        mc_st_v4(ar.mc_out + ooff, o);
+      } else {
+        for (int r = 0; r < np; ++r) *reinterpret_cast<uint4*>(ar.out[r] + ooff) = o;
+      }
     }
   }
+}
+
+
+// ---- mode 3: sentinel-tagged transport -----------------------------------------------------
+// A 32-bit word of two bf16 negative zeros marks "not written yet"; writers turn that one bit
+// pattern into two positive zeros, so real data never looks like the sentinel.  Every 32-bit
+// word is checked on the receiving side: stores of aligned 32-bit words are never torn.
+constexpr uint32_t kLLSentinel = 0x80008000u;
+__device__ __forceinline__ uint4 ll_sanitize(uint4 v) {
+  v.x = v.x == kLLSentinel ? 0u : v.x;
+  v.y = v.y == kLLSentinel ? 0u : v.y;
+  v.z = v.z == kLLSentinel ? 0u : v.z;
+  v.w = v.w == kLLSentinel ? 0u : v.w;
+  return v;
+}
+__device__ __forceinline__ bool ll_valid(const uint4& v) {
+  return v.x != kLLSentinel && v.y != kLLSentinel && v.z != kLLSentinel && v.w != kLLSentinel;
+}
+__device__ __forceinline__ void st_volatile_v4(void* p, const uint4& v) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+// One owned row in mode 3, all 128 reducer threads on it.  `src` = first source slot of the
+// row in the local receive buffer (slot s at src + s * slot_pitch), `dst_off` = offset of the
+// row in every rank's result transport buffer.  Returns false if a wait ran out.
+template <int U>
+__device__ __noinline__ bool ll_reduce_row(const ArArgs& ar, const __nv_bfloat16* src,
+                                           long long slot_pitch, long long buf_off, int row,
+                                           int N, int te, float* red, uint32_t spin) {
+  const int nvec = N >> 3;
+  const int np = ar.p, rank = ar.rank;
+  const long long roff = static_cast<long long>(row) * N;
+  uint4 z[kRnKeep];
+  float sumsq = 0.0f;
+  bool alive = true;
+  const bool have_norm = ar.norm_weight != nullptr;
+  constexpr int kR = 8 / U;
+  // what does not depend on the peers is fetched before the wait: the residual and the norm
+  // weights of this thread's first chunks
+  constexpr int kPf = 4;
+  uint4 res_pf[kPf], w_pf[kPf];
+#pragma unroll
+  for (int j = 0; j < kPf; ++j) {
+    const int c = te + j * 128;
+    res_pf[j] = (ar.res_in != nullptr && c < nvec)
+                    ? *reinterpret_cast<const uint4*>(
+                          ar.res_in + static_cast<long long>(row) * ar.ld_res_in + c * 8)
+                    : make_uint4(0, 0, 0, 0);
+    w_pf[j] = (have_norm && c < nvec) ? *reinterpret_cast<const uint4*>(ar.norm_weight + c * 8)
+                                      : make_uint4(0, 0, 0, 0);
+  }
+#pragma unroll
+  for (int j0 = 0; j0 < kRnKeep; j0 += U) {
+    if (te + j0 * 128 >= nvec) break;
+    float acc[U][8];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[u][i] = 0.0f;
+    for (int r0 = 0; r0 < np; r0 += kR) {
+      uint4 v[kR][U];
+      bool ok = false;
+      for (uint32_t it = 0; it < spin && !ok; ++it) {
+        ok = true;
+#pragma unroll
+        for (int r = 0; r < kR; ++r)
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const int c = te + (j0 + u) * 128;
+            const bool in = r0 + r < np && c < nvec;
+            v[r][u] = in ? ld_volatile_v4(src + (r0 + r) * slot_pitch + c * 8)
+                         : make_uint4(0, 0, 0, 0);
+          }
+#pragma unroll
+        for (int r = 0; r < kR; ++r)
+#pragma unroll
+          for (int u = 0; u < U; ++u) ok = ok && ll_valid(v[r][u]);
+        if (!ok && it > 8) __nanosleep(20);
+      }
+      alive = alive && ok;
+#pragma unroll
+      for (int r = 0; r < kR; ++r)
+#pragma unroll
+        for (int u = 0; u < U; ++u) add8(acc[u], v[r][u]);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int c = te + (j0 + u) * 128;
+      if (c >= nvec) continue;
+      if (j0 + u < kPf) {
+        add8(acc[u], res_pf[j0 + u]);            // zeros when there is no residual
+      } else if (ar.res_in != nullptr) {
+        add8(acc[u], *reinterpret_cast<const uint4*>(
+                         ar.res_in + static_cast<long long>(row) * ar.ld_res_in + c * 8));
+      }
+      const uint4 o = pack8(acc[u]);
+      z[j0 + u] = o;
+      if (have_norm) {
+        float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        add8(f, o);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sumsq += f[i] * f[i];
+        *reinterpret_cast<uint4*>(ar.res_out[rank] + roff + c * 8) = o;   // owner keeps the residual
+      }
+    }
+  }
+  float rstd = 1.0f;
+  if (have_norm) {
+    sumsq = warp_sum(sumsq);
+    if ((te & 31) == 0) red[te >> 5] = sumsq;
+    gather_bar_sync();
+    sumsq = red[0] + red[1] + red[2] + red[3];
+    gather_bar_sync();
+    rstd = rsqrtf(sumsq / static_cast<float>(N) + ar.eps);
+  }
+#pragma unroll
+  for (int j = 0; j < kRnKeep; ++j) {
+    const int c = te + j * 128;
+    if (c >= nvec) break;
+    uint4 o = z[j];
+    if (have_norm) {
+      float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      float w[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      add8(f, o);
+      add8(w, j < kPf ? w_pf[j] : *reinterpret_cast<const uint4*>(ar.norm_weight + c * 8));
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = f[i] * rstd * w[i];
+      o = pack8(f);
+    }
+    o = ll_sanitize(o);
+    for (int r = 0; r < np; ++r) st_volatile_v4(ar.out[r] + buf_off + roff + c * 8, o);
+  }
+  return alive;
 }
 
 template <int BN, int STAGES, int EPI = kEpiNone>
@@ -447,7 +635,8 @@ struct Smem {
           ? BM * kOutCols * 2
           : 0;
   static constexpr int kBarOffset = kOutOffset + kOutBytes;
-  static constexpr int kTotal = kBarOffset + 256 + 1024;  // barriers + alignment slack
+  static constexpr int kArBytes = EPI == kEpiReduceNorm ? 640 : 0;   // shared copy of ArArgs
+  static constexpr int kTotal = kBarOffset + 256 + kArBytes + 1024;  // barriers + alignment slack
   static_assert(kTotal <= 232448, "exceeds the shared memory of one CTA");
 };
 
@@ -517,6 +706,9 @@ __global__ void __launch_bounds__(kThreadsFor<EPI>, 1)
   // them leave their loops in the same iteration
   volatile uint32_t* aux_abort = tmem_slot + 2;
   float* aux_red = reinterpret_cast<float*>(tmem_slot + 4);   // 4 floats of the reducer warps
+  // copy of the peer-address block for the out-of-line row functions of the reducer warps
+  // (taking the address of the kernel parameter itself would move all of it to local memory)
+  ArArgs* ar_s = reinterpret_cast<ArArgs*>(smem + L::kBarOffset + 256);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -693,35 +885,102 @@ __global__ void __launch_bounds__(kThreadsFor<EPI>, 1)
     }
     if constexpr (EPI == kEpiReduceNorm) {
       // ---------------- row owners (warps 6..9) ----------------
-      // Rank r owns rows [lo, hi) of every 128-row tile.  A row is reduced once every rank
-      // has parked all column tiles of its M tile; the finished row is stored into every rank
-      // and marked done there.  Few rows per rank (decode): one row per CTA, all 128 threads
-      // on it.  Many rows: one row per warp, four rows in flight per CTA.
+      // Rank r owns rows [lo, hi) of every 128-row tile (push-all mode: every rank owns all
+      // rows).  A row is reduced once every rank has delivered all column tiles of its M tile;
+      // the finished row is stored into every rank and marked done there.  Few rows per rank
+      // (decode): one row at a time per CTA, all 128 threads on it.  Many rows: one row per
+      // warp, four rows in flight per CTA; the done flags of a group of rows go out with one
+      // release, so the drain of the remote stores is paid once per group.
       const int te = threadIdx.x - 192;
       const int wq = te >> 5, ln = te & 31;
       const int np = p.ar.p, rank = p.ar.rank;
       const uint32_t spin = flag_spin_limit(p.status);
-      const int lo = BM * rank / np, hi = BM * (rank + 1) / np;
+      static_assert(sizeof(ArArgs) <= 640 && sizeof(ArArgs) % 4 == 0, "shared copy of ArArgs");
+      for (int w = te; w < static_cast<int>(sizeof(ArArgs) / 4); w += 128)
+        reinterpret_cast<uint32_t*>(ar_s)[w] = reinterpret_cast<const uint32_t*>(&p.ar)[w];
+      gather_bar_sync();
+      const ArArgs& ars = *ar_s;
+      const bool all_own = p.ar.rn_mode == 2;
+      const int lo = all_own ? 0 : BM * rank / np, hi = all_own ? BM : BM * (rank + 1) / np;
       const int rpt = hi - lo;
       const int nflags = p.tiles_n * np;
       const int my_rows = p.tiles_m * rpt;
+      const long long par_off =
+          static_cast<long long>(epoch & 1u) * np * p.ar.slot_rows * static_cast<long long>(p.N);
       int tm_ready = -1;                               // last M tile whose flags were seen
       bool dead = false;
-      if (my_rows <= static_cast<int>(gridDim.x) * 2) {
+      if (p.ar.rn_mode == 3) {
+        // sentinel-tagged transport: no flag, no fence; every thread waits for its own data
+        const long long buf_off = static_cast<long long>(epoch % 3u) * p.ar.ll_cap;
+        const long long slot_pitch = p.ar.slot_rows * static_cast<long long>(p.N);
+        for (int i = blockIdx.x; i < my_rows; i += gridDim.x) {
+          const int tm = i / rpt;
+          const int row = tm * BM + lo + (i - tm * rpt);
+          if (row >= p.M) continue;
+          const __nv_bfloat16* src =
+              p.ar.partial[rank] + buf_off + static_cast<long long>(i) * p.N;
+          const bool ok = np > 4 ? ll_reduce_row<2>(ars, src, slot_pitch, buf_off, row, p.N, te,
+                                                    aux_red, spin)
+                                 : ll_reduce_row<4>(ars, src, slot_pitch, buf_off, row, p.N, te,
+                                                    aux_red, spin);
+          if (!aux_bar_and(ok)) {
+            if (te == 0) report_status(p.status, kStatusFlagTimeout, kKernelId, 0x920u);
+            dead = true;
+            break;
+          }
+        }
+        // collect the finished rows (from every owner) out of the transport buffer
+        const int nvec = p.N >> 3;
+        for (int r = blockIdx.x; !dead && r < p.M; r += gridDim.x) {
+          const __nv_bfloat16* srow = p.ar.out[rank] + buf_off + static_cast<long long>(r) * p.N;
+          bool ok_all = true;
+          for (int c0 = te; c0 < nvec; c0 += 128 * 4) {
+            uint4 v[4];
+            bool ok = false;
+            for (uint32_t it = 0; it < spin && !ok; ++it) {
+              ok = true;
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const int c = c0 + u * 128;
+                v[u] = c < nvec ? ld_volatile_v4(srow + c * 8) : make_uint4(0, 0, 0, 0);
+                ok = ok && ll_valid(v[u]);
+              }
+              if (!ok && it > 8) __nanosleep(20);
+            }
+            ok_all = ok_all && ok;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int c = c0 + u * 128;
+              if (c < nvec)
+                *reinterpret_cast<uint4*>(p.ar.ll_out_local +
+                                          static_cast<long long>(r) * p.ldc + c * 8) = v[u];
+            }
+          }
+          if (!ok_all) {
+            report_status(p.status, kStatusFlagTimeout, kKernelId, 0x921u);
+            break;
+          }
+        }
+      } else if (min(my_rows, p.M) <= static_cast<int>(gridDim.x) * 2) {
+        int done_rows[2] = {-1, -1};
+        int nd = 0;
+        auto flush_cta = [&]() {
+          gather_bar_sync();                           // every thread's stores precede the release
+          if (!all_own && te < nd * np)
+            st_release_sys(p.ar.done[te % np] + done_rows[te / np], epoch);
+          nd = 0;
+        };
         for (int i = blockIdx.x; i < my_rows; i += gridDim.x) {
           const int tm = i / rpt;
           const int row = tm * BM + lo + (i - tm * rpt);
           if (row >= p.M) continue;
           if (tm != tm_ready) {
-            const uint32_t* fl = p.ar.ready[rank] + static_cast<long long>(tm) * nflags;
-            bool all = false;
-            for (uint32_t it = 0; it < spin && !all; ++it) {
-              bool mine = true;
-              for (int f = te; f < nflags; f += 128)
-                mine = mine && static_cast<int32_t>(ld_acquire_sys_u32(fl + f) - epoch) >= 0;
-              all = aux_bar_and(mine);
-              if (!all && it > 16) __nanosleep(40);
-            }
+            // one thread polls the arrival counter of this M tile; the barrier hands its
+            // verdict (and, by cumulativity, its acquire) to the other 127
+            bool ok = true;
+            if (te == 0)
+              ok = wait_count_sys(p.ar.ready[rank] + tm, p.ar.ready_base[tm], nflags, spin);
+            const bool all = aux_bar_and(ok);
             if (!all) {
               if (te == 0) report_status(p.status, kStatusFlagTimeout, kKernelId, 0x900u);
               dead = true;
@@ -729,28 +988,34 @@ __global__ void __launch_bounds__(kThreadsFor<EPI>, 1)
             }
             tm_ready = tm;
           }
+          const long long push_off = par_off + static_cast<long long>(i) * p.N;
           if (np > 4)
-            reduce_norm_row<2, 128>(p.ar, row, p.N, p.ldc, te, aux_red);
+            reduce_norm_row<2, 128>(ars, row, p.N, p.ldc, te, aux_red, push_off);
           else
-            reduce_norm_row<4, 128>(p.ar, row, p.N, p.ldc, te, aux_red);
-          gather_bar_sync();
-          if (te < np) st_release_sys(p.ar.done[te] + row, epoch);
+            reduce_norm_row<4, 128>(ars, row, p.N, p.ldc, te, aux_red, push_off);
+          if (nd == 0) done_rows[0] = row; else done_rows[1] = row;
+          if (++nd == 2) flush_cta();
         }
+        if (!dead && nd > 0) flush_cta();
       } else {
+        const int group = 32 / np;                     // rows whose flags one release covers
+        int grow_[16];
+        int ng = 0;
+        auto flush = [&]() {
+          __syncwarp();
+          if (!all_own && ln < ng * np) st_release_sys(p.ar.done[ln % np] + grow_[ln / np], epoch);
+          __syncwarp();
+          ng = 0;
+        };
         for (int i = static_cast<int>(blockIdx.x) * 4 + wq; i < my_rows; i += gridDim.x * 4) {
           const int tm = i / rpt;
           const int row = tm * BM + lo + (i - tm * rpt);
           if (row >= p.M) continue;
           if (tm != tm_ready) {
-            const uint32_t* fl = p.ar.ready[rank] + static_cast<long long>(tm) * nflags;
-            bool all = false;
-            for (uint32_t it = 0; it < spin && !all; ++it) {
-              bool mine = true;
-              for (int f = ln; f < nflags; f += 32)
-                mine = mine && static_cast<int32_t>(ld_acquire_sys_u32(fl + f) - epoch) >= 0;
-              all = __all_sync(0xffffffffu, mine);
-              if (!all && it > 16) __nanosleep(200);
-            }
+            bool ok = true;
+            if (ln == 0)
+              ok = wait_count_sys(p.ar.ready[rank] + tm, p.ar.ready_base[tm], nflags, spin);
+            const bool all = __all_sync(0xffffffffu, ok);
             if (!all) {
               if (ln == 0) report_status(p.status, kStatusFlagTimeout, kKernelId, 0x901u);
               dead = true;
@@ -758,17 +1023,22 @@ __global__ void __launch_bounds__(kThreadsFor<EPI>, 1)
             }
             tm_ready = tm;
           }
+          const long long push_off = par_off + static_cast<long long>(i) * p.N;
           if (np > 4)
-            reduce_norm_row<2, 32>(p.ar, row, p.N, p.ldc, ln, aux_red);
+            reduce_norm_row<2, 32>(ars, row, p.N, p.ldc, ln, aux_red, push_off);
           else
-            reduce_norm_row<4, 32>(p.ar, row, p.N, p.ldc, ln, aux_red);
-          __syncwarp();
-          if (ln < np) st_release_sys(p.ar.done[ln] + row, epoch);
+            reduce_norm_row<4, 32>(ars, row, p.N, p.ldc, ln, aux_red, push_off);
+          // grow_ is indexed with a loop-carried count: keep it in registers by unrolling
+#pragma unroll
+          for (int k = 0; k < 16; ++k)
+            if (k == ng) grow_[k] = row;
+          if (++ng == group) flush();
         }
+        if (!dead && ng > 0) flush();
       }
       // the output is complete here once the owner of every row has marked it
-      for (int r = static_cast<int>(blockIdx.x) * 128 + te; !dead && r < p.M;
-           r += gridDim.x * 128) {
+      for (int r = static_cast<int>(blockIdx.x) * 128 + te;
+           p.ar.rn_mode != 3 && !all_own && !dead && r < p.M; r += gridDim.x * 128) {
         if (!wait_flag_sys(p.ar.done[rank] + r, epoch, spin)) {
           report_status(p.status, kStatusFlagTimeout, kKernelId, 0x910u);
           break;
@@ -849,6 +1119,28 @@ __global__ void __launch_bounds__(kThreadsFor<EPI>, 1)
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     int acc = 0;
     uint32_t acc_phase = 0;
+    if constexpr (EPI == kEpiReduceNorm) {
+      if (p.ar.rn_mode == 3) {
+        // While the tensor cores work on the first tile: put the sentinel back into the
+        // transport buffers that the launch after the next one will use.  They were last
+        // written two launches ago, and every word written then has been read since.
+        const int te0 = threadIdx.x - 64;
+        const uint32_t b = epoch % 3u, c = (epoch + 2u) % 3u;
+        const uint4 sent = make_uint4(kLLSentinel, kLLSentinel, kLLSentinel, kLLSentinel);
+        const long long n0 = p.ar.ll_used[2 * c] >> 3, n1 = p.ar.ll_used[2 * c + 1] >> 3;
+        uint4* s0 = reinterpret_cast<uint4*>(p.ar.partial[p.ar.rank] + c * p.ar.ll_cap);
+        uint4* s1 = reinterpret_cast<uint4*>(p.ar.out[p.ar.rank] + c * p.ar.ll_cap);
+        const long long stride = static_cast<long long>(gridDim.x) * 128;
+        for (long long v = static_cast<long long>(blockIdx.x) * 128 + te0; v < n0; v += stride)
+          s0[v] = sent;
+        for (long long v = static_cast<long long>(blockIdx.x) * 128 + te0; v < n1; v += stride)
+          s1[v] = sent;
+        if (blockIdx.x == 0 && te0 == 0) {
+          p.ar.ll_used[2 * b] = static_cast<long long>(p.ar.p) * p.ar.slot_rows * p.N;
+          p.ar.ll_used[2 * b + 1] = static_cast<long long>(p.M) * p.N;
+        }
+      }
+    }
     if constexpr (EPI == kEpiAllGather) {
       // A peer's output buffer may be overwritten once that peer has started this launch
       // (its stream is then past the consumers of the previous result).
@@ -938,14 +1230,22 @@ __global__ void __launch_bounds__(kThreadsFor<EPI>, 1)
                           epoch);
         }
       } else if constexpr (EPI == kEpiReduceNorm) {
-        // park the bf16 partial tile in this GPU's own symmetric buffer as rows of the
-        // [M, N] matrix (the owners read whole rows), then tell every rank: each of them
-        // owns rows of this M tile
+        // deliver the bf16 partial tile as rows of the [M, N] matrix (the owners read whole
+        // rows): pull mode parks it in this GPU's own symmetric buffer; the push modes store
+        // every row into the slot (epoch parity, this rank) of its owner / of every rank.
+        // Then tell every rank: each of them owns rows of this M tile.
         uint8_t* stage = smem + L::kOutOffset;
         constexpr int SC = L::kOutCols;
         constexpr int kChunksPerRow = SC / 8;
         const int te1 = threadIdx.x - 64;
-        __nv_bfloat16* part = p.ar.partial[p.ar.rank];
+        const int np = p.ar.p, rank = p.ar.rank;
+        const int mode = p.ar.rn_mode;
+        const int tm = m0 / BM;
+        const int rpt = mode == 2 ? BM : BM / np;          // push modes need 128 % p == 0
+        const long long slot_base =
+            mode == 3 ? static_cast<long long>(rank) * p.ar.slot_rows
+                      : (static_cast<long long>(epoch & 1u) * np + rank) * p.ar.slot_rows;
+        const long long ll_off = static_cast<long long>(epoch % 3u) * p.ar.ll_cap;
 #pragma unroll 1
         for (int h = 0; h < BN / SC; ++h) {
           stage_tile<SC>(stage, taddr + h * SC, q * 32 + lane);
@@ -960,14 +1260,27 @@ __global__ void __launch_bounds__(kThreadsFor<EPI>, 1)
             const int rr = v / kChunksPerRow, cc = v % kChunksPerRow;
             const int grow = m0 + rr, gcol = n0 + h * SC + cc * 8;
             if (grow >= p.M || gcol >= p.N) continue;
-            *reinterpret_cast<uint4*>(part + static_cast<long long>(grow) * p.N + gcol) =
-                *reinterpret_cast<const uint4*>(stage + stage_off<SC>(rr, cc));
+            const uint4 u = *reinterpret_cast<const uint4*>(stage + stage_off<SC>(rr, cc));
+            if (mode == 0) {
+              *reinterpret_cast<uint4*>(p.ar.partial[rank] +
+                                        static_cast<long long>(grow) * p.N + gcol) = u;
+            } else if (mode == 1) {
+              const int o = rr / rpt;
+              const long long ro = slot_base + static_cast<long long>(tm) * rpt + (rr - o * rpt);
+              *reinterpret_cast<uint4*>(p.ar.partial[o] + ro * p.N + gcol) = u;
+            } else if (mode == 3) {
+              const int o = rr / rpt;
+              const long long ro = slot_base + static_cast<long long>(tm) * rpt + (rr - o * rpt);
+              st_volatile_v4(p.ar.partial[o] + ll_off + ro * p.N + gcol, ll_sanitize(u));
+            } else {
+              const long long ro = slot_base + static_cast<long long>(tm) * BM + rr;
+              for (int r = 0; r < np; ++r)
+                *reinterpret_cast<uint4*>(p.ar.partial[r] + ro * p.N + gcol) = u;
+            }
           }
           epi_bar_sync();
         }
-        if (te1 < p.ar.p)
-          st_release_sys(p.ar.ready[te1] + static_cast<long long>(tile) * p.ar.p + p.ar.rank,
-                         epoch);
+        if (mode != 3 && te1 < np) red_release_sys_add(p.ar.ready[te1] + tm, 1u);
       } else if constexpr (EPI == kEpiAllGather) {
         // store this rank's column block of the tile into every peer's full-width output;
         // staged so that a warp writes whole row segments (BN * 2 contiguous bytes per row)
@@ -1071,6 +1384,11 @@ __global__ void __launch_bounds__(kThreadsFor<EPI>, 1)
       __threadfence();
       if (atomicAdd(p.ar.done_ctr, 1u) == gridDim.x - 1) {
         *p.ar.done_ctr = 0u;
+        if (EPI == kEpiReduceNorm && p.ar.rn_mode != 3) {
+          // every CTA of this launch has read its bases: move them past this launch's arrivals
+          for (int tm = 0; tm < p.tiles_m; ++tm)
+            p.ar.ready_base[tm] += static_cast<uint32_t>(p.tiles_n * p.ar.p);
+        }
         __threadfence();
         *reinterpret_cast<volatile uint32_t*>(p.ar.epoch_ptr) = epoch;
       }
@@ -1284,19 +1602,36 @@ B200_API int b200_gemm_bf16_allreduce(const void* A, long long lda, const void* 
 // res_out of the owner only (bcast_res = 0: enough when the next consumer of the residual is
 // again this entry point) or of every rank (bcast_res = 1).  Without a norm weight res_out is
 // not written.
+// rn_mode selects how the partial rows travel: 0 = every rank parks its partial matrix in its
+// own buffer and the owners pull their rows (the mode for many rows; the only one that can use
+// mc_partial); 1 = the epilogue pushes every row into the owner's buffer, slot
+// (launch parity, source rank), and the owner reduces from local memory (decode-sized
+// problems: one NVLink round trip less on the critical path); 2 = every row is pushed to
+// every rank and every rank reduces all rows (one hop, nothing is broadcast afterwards; done
+// is not used).  Modes 1 and 2 need 128 % p == 0 and a partial buffer of
+// 2 * p * ceil(M/128) * (128 / p) * N elements (mode 2: 2 * p * ceil(M/128) * 128 * N).
+// 3 = like 1, but nothing is flagged or fenced: the transport buffers hold a sentinel word
+// (two bf16 negative zeros) wherever no data has landed yet and every receiver polls the data
+// itself, which takes the release / acquire round trips off the critical path of a decode
+// step.  partial[r] and out[r] then name three rotating transport buffers of ll_cap elements
+// each on rank r (all filled with 0x80008000 words before the first call; the kernel restores
+// the sentinel itself afterwards), the result lands in ll_out_local [M, ldc] (local),
+// ll_used is 6 local zero-initialised 64-bit words; bcast_res must be 0 and
+// ceil(M/128) * 128 * N <= ll_cap.
 // partial / out / res_out / ready / done: arrays of p peer-visible addresses (index = rank):
-// partial [M, N] bf16, out [M, ldc], res_out [M, N], ready ceil(M/128) * ceil(N/BN) * p words
-// (BN = b200_gemm_ar_tile_n(M, N)), done M words; epoch_ptr / done_ctr: local words, all zero
-// before the first call.  residual: local [M, ldr] or null.  N <= 8192.  All ranks pass the
+// partial [M, N] bf16, out [M, ldc], res_out [M, N], ready ceil(M/128) words (arrival
+// counters), done M words; ready_base: local ceil(M/128) words; epoch_ptr / done_ctr: local
+// words; all zero before the first call and private to this entry point.  residual: local [M, ldr] or null.  N <= 8192.  All ranks pass the
 // same shapes.  A launch returns when every row of `out` has arrived on this rank.
 B200_API int b200_gemm_bf16_ar_norm(const void* A, long long lda, const void* B, long long ldb,
                                     long long ldc, int M, int N, int K, void* const* partial,
                                     void* const* out, void* const* res_out, void* const* ready,
-                                    void* const* done, void* epoch_ptr, void* done_ctr, int rank,
-                                    int p, const void* residual, long long ldr,
-                                    const void* norm_weight, float eps, int bcast_res,
-                                    const void* mc_partial, void* mc_out, void* mc_res,
-                                    void* stream) {
+                                    void* const* done, void* ready_base, void* epoch_ptr,
+                                    void* done_ctr, int rank, int p, const void* residual,
+                                    long long ldr, const void* norm_weight, float eps,
+                                    int bcast_res, int rn_mode, const void* mc_partial, void* mc_out,
+                                    void* mc_res, void* ll_out_local, long long ll_cap,
+                                    void* ll_used, void* stream) {
   using namespace b200;
   using namespace b200::gemm;
   if (M <= 0 || N <= 0) return 0;
@@ -1304,6 +1639,13 @@ B200_API int b200_gemm_bf16_ar_norm(const void* A, long long lda, const void* B,
   if (K <= 0 || (K % 8) != 0 || (lda % 8) != 0 || (ldb % 8) != 0 || (N % 8) != 0 ||
       (ldc % 8) != 0 || (ldr % 8) != 0 || N > kRnKeep * 128 * 8)
     return -2;
+  if (rn_mode < 0 || rn_mode > 3 || (rn_mode != 0 && (BM % p) != 0)) return -2;
+  if (rn_mode == 3) {
+    const long long tiles_m = (M + BM - 1) / BM;
+    if (ll_out_local == nullptr || ll_used == nullptr || bcast_res != 0 ||
+        tiles_m * BM * static_cast<long long>(N) > ll_cap || (ll_cap % 8) != 0)
+      return -2;
+  }
   const int bn = b200_gemm_ar_tile_n(M, N);
   CUtensorMap tmA, tmB;
   int r = encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, static_cast<uint64_t>(M),
@@ -1337,6 +1679,12 @@ B200_API int b200_gemm_bf16_ar_norm(const void* A, long long lda, const void* B,
   a.ar.norm_weight = static_cast<const __nv_bfloat16*>(norm_weight);
   a.ar.eps = eps;
   a.ar.bcast_res = bcast_res;
+  a.ar.rn_mode = rn_mode;
+  a.ar.ready_base = static_cast<uint32_t*>(ready_base);
+  a.ar.ll_out_local = static_cast<__nv_bfloat16*>(ll_out_local);
+  a.ar.ll_cap = ll_cap;
+  a.ar.ll_used = static_cast<long long*>(ll_used);
+  a.ar.slot_rows = static_cast<long long>(a.tiles_m) * (rn_mode == 2 ? BM : BM / p);
   a.ar.mc_partial = static_cast<const __nv_bfloat16*>(mc_partial);
   a.ar.mc_out = static_cast<__nv_bfloat16*>(mc_out);
   a.ar.mc_res = static_cast<__nv_bfloat16*>(mc_res);

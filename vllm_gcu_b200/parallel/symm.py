@@ -27,6 +27,7 @@ Every wait inside the kernels is bounded; a timeout is reported through the stat
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -58,8 +59,8 @@ def _register_sigs() -> None:
                                             I, I, P]
     F = ctypes.c_float
     lib.b200_gemm_bf16_ar_norm.restype = I
-    lib.b200_gemm_bf16_ar_norm.argtypes = [P, L, P, L, L, I, I, I, P, P, P, P, P, P, P, I, I, P, L,
-                                           P, F, I, P, P, P, P]
+    lib.b200_gemm_bf16_ar_norm.argtypes = [P, L, P, L, L, I, I, I, P, P, P, P, P, P, P, P, I, I, P, L,
+                                           P, F, I, I, P, P, P, P, L, P, P]
     lib.b200_argmax_allgather.restype = I
     lib.b200_argmax_allgather.argtypes = [P, L, I, I, I, P, I, P, P, I, I, P, P]
     lib.b200_allreduce.restype = I
@@ -100,6 +101,7 @@ class FusedTP:
     BM = 128
     ONESHOT_MAX_TOKENS = 1024
     ARGMAX_ROWS = 1024
+    LL_MAX_ROWS = 1024
 
     def __init__(self, max_tokens: int, max_n: int, device: torch.device, group_name: str = "tp"):
         _register_sigs()
@@ -132,13 +134,30 @@ class FusedTP:
         self.off_res = [self.off_ar_flag + 4096, self.off_ar_flag + 4096 + self.out_bytes]
         self.off_row_done = self.off_res[1] + self.out_bytes
         # greedy sampling: 2 (epoch parity) x p x ARGMAX_ROWS records of 16 bytes
-        self.off_argmax = -(-(self.off_row_done + rows * 4) // 256) * 256
-        total = self.off_argmax + 2 * self.p * self.ARGMAX_ROWS * 16 + 256
+        self.off_rn_cnt = -(-(self.off_row_done + rows * 4) // 256) * 256    # arrival counters
+        self.off_argmax = -(-(self.off_rn_cnt + (rows // self.BM) * 4) // 256) * 256
+        # sentinel-tagged transport of decode-sized gemm_ar_norm calls: three rotating buffers
+        # for the rows pushed to their owners and three for the finished rows
+        self.ll_cap = min(rows, self.LL_MAX_ROWS) * max_n               # elements per buffer
+        self.off_ll_slots = -(-(self.off_argmax + 2 * self.p * self.ARGMAX_ROWS * 16) // 256) * 256
+        self.off_ll_out = self.off_ll_slots + 3 * self.ll_cap * 2
+        total = self.off_ll_out + 3 * self.ll_cap * 2 + 256
         self.buf = SymmetricBuffer(total, pg, device)
         self.local_words = torch.zeros(16, dtype=torch.int32, device=device)  # epoch, ctr, ...
+        self.rn_base = torch.zeros(rows // self.BM + 1, dtype=torch.int32, device=device)
+        self.ll_used = torch.zeros(6, dtype=torch.int64, device=device)
+        ll = self.buf.local[self.off_ll_slots:self.off_ll_out + 3 * self.ll_cap * 2]
+        ll.view(torch.int32).fill_(-2147450880)          # 0x80008000: "nothing has landed here"
         self.out_sel = 0
         self.res_sel = 0
         self.force_mode: Optional[str] = None     # benchmarks: "oneshot" | "twoshot"
+        self.force_rn_mode: Optional[int] = None  # benchmarks / tests: transport of gemm_ar_norm
+        self.row_owner: Optional[bool] = None     # benchmarks / tests: force the choice
+        # thousands of rows with four or more ranks: owners pull their rows (through the
+        # switch when the allocation has a multicast view); VLLM_B200_TP_LARGE_M=ar keeps
+        # the tile-wise all-reduce + norm kernel
+        self.large_m_row_owner = os.environ.get("VLLM_B200_TP_LARGE_M", "rn") != "ar"
+        self.sm_count = int(_native.lib().b200_sm_count())
         from .. import envs
         # in-switch reduction and broadcast (NVLS multimem) when the allocation has a multicast
         # view; VLLM_B200_MULTIMEM=0 keeps the kernels on plain peer loads and stores
@@ -211,6 +230,21 @@ class FusedTP:
                 return None
         lib = _native.lib()
         bn = lib.b200_gemm_ar_tile_n(M, N)
+        if not self._row_owner_pays(M, N, bn):
+            # GEMM + tile-wise all-reduce, then the norm kernel: every rank ends up with the
+            # whole new residual
+            from ..ops import cuda as C
+            y = self.gemm_all_reduce(x2, w, None if norm_weight is not None else residual)
+            if y is None:
+                return None
+            if norm_weight is None:
+                return y.view(*x.shape[:-1], N), None
+            if residual is None:
+                return C.norm(y, norm_weight, eps).view(*x.shape[:-1], N), y
+            if residual.data_ptr() == x2.data_ptr():
+                residual = residual.clone()
+            out = C.norm(y, norm_weight, eps, residual=residual)
+            return out.view(*x.shape[:-1], N), residual
         if (-(-M // self.BM)) * (-(-N // bn)) > self.max_tiles:
             return None
         self.out_sel ^= 1
@@ -219,19 +253,23 @@ class FusedTP:
         if norm_weight is not None:
             self.res_sel ^= 1
             off_res = self.off_res[self.res_sel]
-        mc = self.buf.multicast_ptr if self.use_multimem else 0
+        mode = self._rn_mode(M, N, bn, bool(bcast_residual) and norm_weight is not None)
+        mc = self.buf.multicast_ptr if (self.use_multimem and mode == 0) else 0
+        off_part = self.off_ll_slots if mode == 3 else self.off_part
+        off_dst = self.off_ll_out if mode == 3 else off_out
         words = self.local_words.data_ptr()
         call("b200_gemm_bf16_ar_norm", ptr(x2), x2.stride(0), ptr(w), w.stride(0), N, M, N, K,
-             _ptr_array(self.buf.peer_ptrs(self.off_part)),
-             _ptr_array(self.buf.peer_ptrs(off_out)),
+             _ptr_array(self.buf.peer_ptrs(off_part)),
+             _ptr_array(self.buf.peer_ptrs(off_dst)),
              _ptr_array(self.buf.peer_ptrs(off_res)) if norm_weight is not None else None,
-             _ptr_array(self.buf.peer_ptrs(self.off_ready)),
-             _ptr_array(self.buf.peer_ptrs(self.off_row_done)),
-             words, words + 4, self.rank, self.p, ptr(residual),
+             _ptr_array(self.buf.peer_ptrs(self.off_rn_cnt)),
+             _ptr_array(self.buf.peer_ptrs(self.off_row_done)), ptr(self.rn_base),
+             words + 40, words + 44, self.rank, self.p, ptr(residual),
              residual.stride(0) if residual is not None else 0, ptr(norm_weight), float(eps),
-             int(bool(bcast_residual)),
+             int(bool(bcast_residual) and norm_weight is not None), mode,
              mc + self.off_part if mc else None, mc + off_out if mc else None,
-             mc + off_res if (mc and norm_weight is not None) else None, stream_ptr())
+             mc + off_res if (mc and norm_weight is not None) else None,
+             self.buf.ptrs[self.rank] + off_out, self.ll_cap, ptr(self.ll_used), stream_ptr())
         out = self.buf.local[off_out:off_out + M * N * 2].view(torch.bfloat16).view(M, N)
         res = None
         if norm_weight is not None:
@@ -257,6 +295,49 @@ class FusedTP:
              int(vocab_offset), _ptr_array(self.buf.peer_ptrs(self.off_argmax)), self.ARGMAX_ROWS,
              words + 32, words + 36, self.rank, self.p, ptr(out), stream_ptr())
         return out
+
+    def _few_rows(self, M: int, N: int, bn: int) -> bool:
+        tiles_m = -(-M // self.BM)
+        grid = min(tiles_m * -(-N // bn), self.sm_count)
+        return min(tiles_m * max(1, self.BM // self.p), M) <= 2 * grid
+
+    def _row_owner_pays(self, M: int, N: int, bn: int) -> bool:
+        """Whether ``gemm_ar_norm`` runs as the one row-owner kernel or as GEMM + tile-wise
+        all-reduce followed by the norm kernel.  Measured with two ranks the latter is as fast
+        for decode-sized problems (one hop against two) and faster for thousands of rows (the
+        four reducer warps of a CTA cannot keep enough rows in flight when a rank owns half of
+        them); with four or more ranks pushing every partial to every rank costs (p - 1) times
+        the traffic and the row owners win."""
+        if self.row_owner is not None:
+            return bool(self.row_owner)
+        if self.force_rn_mode is not None:
+            return True
+        if self.p < 4:
+            return False
+        if self._few_rows(M, N, bn):
+            return True
+        return self.large_m_row_owner
+
+    def _rn_mode(self, M: int, N: int, bn: int, bcast_residual: bool = False) -> int:
+        """Transport of ``gemm_ar_norm`` for this problem.  Decode-sized problems (few rows per
+        rank): 3 = rows pushed to their owners through sentinel-tagged buffers, no flags and no
+        fences (needs the residual to stay with its owner); otherwise 1 = rows pushed to their
+        owners with arrival counters.  Many rows: 0 = owners pull whole rows (the
+        multimem-capable transport).  2 (every rank reduces everything) only on request."""
+        tiles_m = -(-M // self.BM)
+        if self.force_rn_mode is not None:
+            mode = self.force_rn_mode
+        else:
+            mode = 3 if self._few_rows(M, N, bn) else 0
+        if mode and self.BM % self.p:
+            mode = 0
+        if mode == 3 and (bcast_residual or tiles_m * self.BM * N > self.ll_cap):
+            mode = 1
+        if mode == 2 and 2 * self.p * tiles_m * self.BM * N * 2 > self.part_bytes:
+            mode = 1
+        if mode == 1 and 2 * tiles_m * self.BM * N * 2 > self.part_bytes:
+            mode = 0
+        return mode
 
     def _oneshot(self, M: int) -> bool:
         fits = -(-M // self.BM) * self.BM <= self.oneshot_rows
