@@ -33,7 +33,7 @@ def test_llama_bf16_gpu_matches_cpu_reference():
         if getattr(mod, "_interleaved", False):
             w = sd[name + ".weight"]
             I = w.shape[0] // 2
-            w4 = w.view(I // 128, 2, 128, w.shape[1])
+            w4 = w.view(I // 32, 2, 32, w.shape[1])
             sd[name + ".weight"] = torch.cat([w4[:, 0].reshape(I, -1), w4[:, 1].reshape(I, -1)])
     cpu.engine.model.load_state_dict(sd, strict=False)
     out_cpu = cpu.generate(prompts, sp)

@@ -65,7 +65,7 @@ def test_gemm_skinny_decode_shapes(C, M, N, K, monkeypatch):
     _close(C.gemm_bf16(a, b, bias=bias), want + bias.float(), 2e-2, 3e-2)
     if N % 256 == 0:
         got = C.gemm_bf16(a, b, epilogue=C.EPI_SILU_MUL)
-        w4 = want.view(M, N // 256, 2, 128)
+        w4 = want.view(M, N // 64, 2, 32)
         _close(got, (torch.nn.functional.silu(w4[:, :, 0]) * w4[:, :, 1]).reshape(M, N // 2),
                3e-2, 3e-2)
 
@@ -82,7 +82,7 @@ def test_gemm_wide2_large_m(C, M, N, K):
     bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
     _close(C.gemm_bf16(a, b, bias=bias), want + bias.float(), 2e-2, 3e-2)
     got = C.gemm_bf16(a, b, epilogue=C.EPI_SILU_MUL)
-    w4 = want.view(M, N // 256, 2, 128)
+    w4 = want.view(M, N // 64, 2, 32)
     _close(got, (torch.nn.functional.silu(w4[:, :, 0]) * w4[:, :, 1]).reshape(M, N // 2),
            3e-2, 3e-2)
 

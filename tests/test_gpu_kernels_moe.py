@@ -120,7 +120,7 @@ def test_qwen3_moe_engine_gpu_vs_cpu():
             w = sd[name + ".w13"]
             E, I2, H = w.shape
             I = I2 // 2
-            w4 = w.view(E, I // 128, 2, 128, H)
+            w4 = w.view(E, I // ref.GATE_UP_BLOCK, 2, ref.GATE_UP_BLOCK, H)
             sd[name + ".w13"] = torch.cat([w4[:, :, 0].reshape(E, I, H),
                                            w4[:, :, 1].reshape(E, I, H)], 1)
     cpu.engine.model.load_state_dict(sd, strict=False)

@@ -11,7 +11,7 @@
 //   * accumulators live in tensor memory, double buffered (2 x BN fp32 columns)
 //     so the epilogue of tile i overlaps the main loop of tile i+1;
 //   * epilogues: plain, +bias, SiLU(gate)*up for a gate/up weight interleaved in
-//     blocks of 128 rows, +residual, fp32 output.
+//     blocks of 32 rows, +residual, fp32 output.
 //
 // Replaces the vendor matmul behind every unquantised linear layer of the
 // reference (vllm_gcu/kernels/linear.py, upstream UnquantizedLinearMethod) and
@@ -1164,17 +1164,17 @@ __global__ void __launch_bounds__(kThreadsFor<EPI>, 1)
           tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
 
       if constexpr (EPI == kEpiSiluMul) {
-        // tile columns [0,128) = gate block, [128,256) = matching up block
-        static_assert(EPI != kEpiSiluMul || BN == 256, "SiLU-mul epilogue needs BN = 256");
+        // every 64-column group of the tile = 32 gate columns, then the 32 matching up columns
+        static_assert(EPI != kEpiSiluMul || BN % 64 == 0, "SiLU-mul epilogue: 64-column groups");
         const int out_n0 = (n0 >> 1);
         const int out_n = p.N >> 1;
         __nv_bfloat16* crow =
             reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < BN / 64; ++c) {
           uint32_t g[32], u[32];
-          tmem_ld_32x32(taddr + c * 32, g);
-          tmem_ld_32x32(taddr + 128 + c * 32, u);
+          tmem_ld_32x32(taddr + c * 64, g);
+          tmem_ld_32x32(taddr + c * 64 + 32, u);
           tmem_ld_wait();
           float v[32];
 #pragma unroll
@@ -1420,7 +1420,7 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const Args& a, cudaSt
 
 // C[M,N] (bf16, or fp32 when epi == 4) = A[M,K] * B[N,K]^T with epilogue `epi`:
 //   0 none, 1 + bias[N], 2 SiLU(gate)*up (B rows interleaved gate/up in blocks
-//   of 128; C is [M, N/2]), 3 + residual[M,N], 4 fp32 output.
+//   of 32, N a multiple of 64; C is [M, N/2]), 3 + residual[M,N], 4 fp32 output.
 // lda / ldb / ldc / ldr are row pitches in elements.  K, lda, ldb must be
 // multiples of 8; N, ldc multiples of 8; all base pointers 16-byte aligned.
 // Returns 0 on success, a CUDA error code, or a negative argument error.
@@ -1436,7 +1436,7 @@ B200_API int b200_gemm_bf16(const void* A, long long lda, const void* B, long lo
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) |
        reinterpret_cast<uintptr_t>(C)) & 15)
     return -3;
-  if (epi == kEpiSiluMul && (N % 256) != 0) return -4;
+  if (epi == kEpiSiluMul && (N % 64) != 0) return -4;
   if (epi == kEpiBias && bias == nullptr) return -5;
   if (epi == kEpiResidual && residual == nullptr) return -5;
 
@@ -1445,12 +1445,14 @@ B200_API int b200_gemm_bf16(const void* A, long long lda, const void* B, long lo
   // work; for decode-sized M a width that yields one full wave wins (6144 columns: 96).
   const int tiles_m = (M + BM - 1) / BM;
   int bn = 256;
-  if (epi != kEpiSiluMul) {
+  {
     const int cands[4] = {256, 128, 96, 64};
     long long best = -1;
     for (int i = 0; i < 4; ++i) {
       const int c = cands[i];
       if (c == 256 && (N % 256) != 0) continue;
+      // the SiLU-mul epilogue pairs 32 + 32 columns: whole 64-column groups per tile
+      if (epi == kEpiSiluMul && ((c % 64) != 0 || (N % c) != 0)) continue;
       const long long tiles = static_cast<long long>(tiles_m) * ((N + c - 1) / c);
       const long long waves = (tiles + sm_count() - 1) / sm_count();
       const long long cost = waves * (c + 32);
@@ -1505,6 +1507,8 @@ B200_API int b200_gemm_bf16(const void* A, long long lda, const void* B, long lo
     B200_GEMM_CASE(kEpiResidual)
     B200_GEMM_CASE(kEpiFp32)
     case kEpiSiluMul:
+      if (bn == 64) return launch<64, 8, kEpiSiluMul>(tmA, tmB, a, s);
+      if (bn == 128) return launch<128, 6, kEpiSiluMul>(tmA, tmB, a, s);
       return launch<256, 4, kEpiSiluMul>(tmA, tmB, a, s);
     default:
       return -7;
@@ -1835,7 +1839,7 @@ B200_API int b200_gemm_bf16_gather_a(void* const* shard, long long lds, const in
 // tiles at or past *num_valid_rows are skipped, so M_cap may be a static upper bound).
 // epi 0: C[M_cap, N] = A * B_e^T (optionally scaled per row by row_scale);
 // epi 2: SiLU(gate) * up with the gate / up rows of every expert interleaved in blocks of
-// 128 (C is [M_cap, N / 2]).  N must be a multiple of the tile width (256 for epi 2,
+// 32 (C is [M_cap, N / 2]).  N must be a multiple of the tile width (256 for epi 2,
 // else 128 or 64).
 B200_API int b200_gemm_bf16_grouped(const void* A, long long lda, const void* B, long long ldb,
                                     void* C, long long ldc, int M_cap, int N, int K, int E,

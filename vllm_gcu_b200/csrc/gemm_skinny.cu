@@ -16,7 +16,7 @@
 //     (o_proj, down_proj).  The CTAs of a column tile write fp32 partial sums to an L2-resident
 //     workspace, meet at a counter (bounded wait), and each reduces a row slice of the tile
 //     in a fixed order (bitwise reproducible), applying the epilogue;
-//   * epilogues: none, + bias, SiLU(gate) * up (gate / up interleaved in blocks of 128 rows).
+//   * epilogues: none, + bias, SiLU(gate) * up (gate / up interleaved in blocks of 32 rows).
 //
 // Replaces the vendor matmul behind the decode path of every unquantised linear layer of the
 // reference (vllm_gcu/kernels/linear.py; SiluAndMul of vllm_gcu/kernels/activation.py:20-32
@@ -185,9 +185,10 @@ __global__ void __launch_bounds__(kThreads, 1)
           const int out_n = p.N >> 1;
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
+            // 64-column group c of the tile: 32 gate columns, then the 32 matching up columns
             uint32_t g[32], u[32];
-            tmem_ld_32x32(taddr + c * 32, g);
-            tmem_ld_32x32(taddr + 128 + c * 32, u);
+            tmem_ld_32x32(taddr + c * 64, g);
+            tmem_ld_32x32(taddr + c * 64 + 32, u);
             tmem_ld_wait();
             float v[32];
 #pragma unroll
@@ -280,12 +281,14 @@ __global__ void __launch_bounds__(kThreads, 1)
           const int out_n = p.N >> 1;
           for (int e = te; e < (r1 - r0) * kV; e += 128) {
             const int row = r0 + e / kV, c4 = (e % kV) * 4;
+            // output column c4 of the tile: gate at (c4 / 32) * 64 + c4 % 32, up 32 further
+            const int gcol = (c4 >> 5) * 64 + (c4 & 31);
             float4 g = make_float4(0.f, 0.f, 0.f, 0.f), u = g;
             for (int s = 0; s < p.splits; ++s) {
               const float* src = base + static_cast<long long>(s) * (R * BN) +
-                                 static_cast<long long>(row) * BN + c4;
+                                 static_cast<long long>(row) * BN + gcol;
               const float4 a = __ldcg(reinterpret_cast<const float4*>(src));
-              const float4 b = __ldcg(reinterpret_cast<const float4*>(src + 128));
+              const float4 b = __ldcg(reinterpret_cast<const float4*>(src + 32));
               g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
               u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
             }
@@ -498,9 +501,10 @@ __global__ void __launch_bounds__(kThreads, 1)
           const int out_n = p.N >> 1;
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
+            // 64-column group c of the tile: 32 gate columns, then the 32 matching up columns
             uint32_t g[32], u[32];
-            tmem_ld_32x32(taddr + c * 32, g);
-            tmem_ld_32x32(taddr + 128 + c * 32, u);
+            tmem_ld_32x32(taddr + c * 64, g);
+            tmem_ld_32x32(taddr + c * 64 + 32, u);
             tmem_ld_wait();
             float v[32];
 #pragma unroll
@@ -672,7 +676,7 @@ B200_API int b200_gemm_skinny_workspace(int N, long long* ws_bytes, int* ctr_wor
 }
 
 // C[M,N] (bf16) = A[M,K] * B[N,K]^T for M <= 256 with epilogue epi: 0 none, 1 + bias[N],
-// 2 SiLU(gate)*up (B rows interleaved gate/up in blocks of 128; C is [M, N/2]).
+// 2 SiLU(gate)*up (B rows interleaved gate/up in blocks of 32; C is [M, N/2]).
 // Row pitches in elements; K, lda, ldb, N, ldc multiples of 8; 16-byte aligned pointers.
 // ws / ctr: see b200_gemm_skinny_workspace (ctr must be zero before the first call; the kernel
 // leaves it zero).  Launches on one stream may share the workspace; concurrent streams need
@@ -774,7 +778,7 @@ B200_API int b200_gemm_skinny_plan(int M, int N, int K, int epi, int* bn, int* s
 }
 
 // C[M,N] = A[M,K] * B[N,K]^T with persistent 256 x 256 tiles (large M).  N must be a multiple
-// of 256 (epi 2: gate / up interleaved in blocks of 128, C is [M, N/2]); other constraints as
+// of 256 (epi 2: gate / up interleaved in blocks of 32, C is [M, N/2]); other constraints as
 // b200_gemm_bf16.  Returns -20 when the shape does not qualify.
 B200_API int b200_gemm_wide2(const void* A, long long lda, const void* B, long long ldb, void* C,
                              long long ldc, int M, int N, int K, const void* bias, int epi,

@@ -54,7 +54,7 @@ class UnquantizedLinearMethod(LinearMethod):
         if getattr(layer, "fuse_silu", False) and not getattr(layer, "_interleaved", False):
             w = layer.weight.data
             half = w.shape[0] // 2
-            if half % 128 == 0 and w.dtype == torch.bfloat16:
+            if half % ref.GATE_UP_BLOCK == 0 and w.dtype == torch.bfloat16:
                 layer.weight.data = ref.interleave_gate_up(w[:half], w[half:]).contiguous()
                 layer._interleaved = True
 

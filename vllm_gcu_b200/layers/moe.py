@@ -234,8 +234,9 @@ class FusedMoE(nn.Module):
         return True
 
     def finalize(self) -> None:
-        """GPU layout: gate / up rows of every expert interleaved in blocks of 128 so the
-        grouped GEMM applies SiLU(gate) * up in its epilogue."""
+        """GPU layout: gate / up rows of every expert interleaved in blocks of
+        ``ref.GATE_UP_BLOCK`` rows so the grouped GEMM applies SiLU(gate) * up in its epilogue
+        (its tiles are 256 columns wide: 2 * I must be a multiple of 256)."""
         if self._interleaved or not self.w13.is_cuda or self.w13.dtype != torch.bfloat16:
             return
         I = self.inter
@@ -243,8 +244,9 @@ class FusedMoE(nn.Module):
             return
         w = self.w13.data
         E = w.shape[0]
-        g = w[:, :I].reshape(E, I // 128, 128, -1)
-        u = w[:, I:].reshape(E, I // 128, 128, -1)
+        B = ref.GATE_UP_BLOCK
+        g = w[:, :I].reshape(E, I // B, B, -1)
+        u = w[:, I:].reshape(E, I // B, B, -1)
         self.w13.data = torch.stack([g, u], dim=2).reshape(E, 2 * I, -1).contiguous()
         self._interleaved = True
 
@@ -282,9 +284,7 @@ class FusedMoE(nn.Module):
                                    add=add, alpha=alpha, valid_tokens=valid_tokens)
         w13 = self.w13
         if self._interleaved:    # undo the GPU layout for the reference path
-            E, I = w13.shape[0], self.inter
-            w4 = w13.view(E, I // 128, 2, 128, -1)
-            w13 = torch.cat([w4[:, :, 0].reshape(E, I, -1), w4[:, :, 1].reshape(E, I, -1)], dim=1)
+            w13 = ref.deinterleave_gate_up(w13)
         y = ref.fused_experts(x, w13, self.w2, topk_w, topk_ids, self.expert_map)
         if alpha != 1.0:
             y = (y.float() * alpha).to(x.dtype)

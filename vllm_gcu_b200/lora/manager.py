@@ -93,9 +93,8 @@ class LoRALinear(nn.Module):
             from ..layers.activation import act_and_mul
             w = base.weight
             if getattr(base, "_interleaved", False):
-                I = w.shape[0] // 2
-                w4 = w.view(I // 128, 2, 128, w.shape[1])
-                w = torch.cat([w4[:, 0].reshape(I, -1), w4[:, 1].reshape(I, -1)])
+                from ..ops import ref as _ref
+                w = _ref.deinterleave_gate_up(w)
             y = torch.nn.functional.linear(x, w, base.bias)
             self.punica.add_lora_linear(y, x, list(self.lora_a), list(self.lora_b), 1.0,
                                         self.slices)

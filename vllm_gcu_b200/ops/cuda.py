@@ -117,7 +117,7 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = No
         a2 = a.reshape(-1, a.shape[-1])
         want = ref.gemm(a2, b, bias=bias, residual=residual, out_dtype=torch.float32)
         if bias is None and residual is None and epilogue == EPI_SILU_MUL:
-            w4 = want.view(want.shape[0], -1, 2, 128)
+            w4 = want.view(want.shape[0], -1, 2, ref.GATE_UP_BLOCK)
             want = (torch.nn.functional.silu(w4[:, :, 0]) * w4[:, :, 1]).reshape(want.shape[0], -1)
         oracle_compare("gemm_bf16", res, want, 3e-2, 3e-2 * max(1.0, float(want.abs().mean())))
     return res
@@ -144,7 +144,9 @@ def _gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = N
         out = torch.empty((M, out_cols), device=a.device,
                           dtype=torch.float32 if epilogue == EPI_FP32 else torch.bfloat16)
     assert out.stride(-1) == 1 and out.shape[-1] == out_cols
-    if M <= SKINNY_MAX_M and USE_SKINNY_GEMM and epilogue in (EPI_NONE, EPI_BIAS, EPI_SILU_MUL):
+    silu_256 = epilogue != EPI_SILU_MUL or Nn % 256 == 0     # these two kernels: 256-wide tiles
+    if M <= SKINNY_MAX_M and USE_SKINNY_GEMM and silu_256 \
+            and epilogue in (EPI_NONE, EPI_BIAS, EPI_SILU_MUL):
         ws, ctr = _skinny_workspace(a.device)
         rc = N.lib().b200_gemm_skinny(
             ptr(a), a.stride(0), ptr(b), b.stride(0), ptr(out), out.stride(0), M, Nn, K,
@@ -675,7 +677,7 @@ def fused_experts(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_w: 
     """Routed-expert MLP on the native path: align -> permute -> grouped GEMM1 with the
     SiLU-mul epilogue -> grouped GEMM2 scaled by the routing weight -> un-permute + sum
     (+ ``add``, e.g. the shared-expert output).  ``w13`` must hold gate/up interleaved in
-    blocks of 128 per expert (``ref.interleave_gate_up``)."""
+    blocks of ``ref.GATE_UP_BLOCK`` rows per expert (``ref.interleave_gate_up``)."""
     T, H = x.shape
     k = topk_ids.shape[1]
     E = w13.shape[0]

@@ -468,7 +468,13 @@ def gemm(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None,
     return y.to(out_dtype or a.dtype)
 
 
-def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor, block: int = 128
+#: rows per block of the gate / up interleaving that the fused SiLU-mul GEMM epilogues expect:
+#: 32 gate rows, the matching 32 up rows, and so on, so that every 64-column group of an output
+#: tile holds matching halves whatever the tile width (64, 128 or 256)
+GATE_UP_BLOCK = 32
+
+
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor, block: int = GATE_UP_BLOCK
                        ) -> torch.Tensor:
     """Weight layout of the fused SiLU-mul GEMM epilogue: alternating blocks of
     ``block`` gate rows and the matching ``block`` up rows."""
@@ -479,8 +485,18 @@ def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor, block: int = 12
     return torch.stack([g, u], dim=1).reshape(2 * I, K)
 
 
-def gemm_silu_mul_interleaved(a: torch.Tensor, w_inter: torch.Tensor, block: int = 128
-                              ) -> torch.Tensor:
+def deinterleave_gate_up(w_inter: torch.Tensor, block: int = GATE_UP_BLOCK) -> torch.Tensor:
+    """Inverse of :func:`interleave_gate_up` along dim -2: ``[..., 2 I, K]`` interleaved ->
+    ``[..., 2 I, K]`` with all gate rows first."""
+    *lead, N2, K = w_inter.shape
+    w4 = w_inter.reshape(*lead, N2 // (2 * block), 2, block, K)
+    g = w4[..., 0, :, :].reshape(*lead, N2 // 2, K)
+    u = w4[..., 1, :, :].reshape(*lead, N2 // 2, K)
+    return torch.cat([g, u], dim=-2)
+
+
+def gemm_silu_mul_interleaved(a: torch.Tensor, w_inter: torch.Tensor,
+                              block: int = GATE_UP_BLOCK) -> torch.Tensor:
     y = a.float() @ w_inter.float().t()
     M, N2 = y.shape
     y = y.reshape(M, N2 // (2 * block), 2, block)
