@@ -52,6 +52,9 @@ def main() -> None:
     ap.add_argument("--attention-backend", default=None,
                     help="vLLM attention backend name (default: vLLM's own choice)")
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model")
+    ap.add_argument("--prefill-only-pass", action="store_true",
+                    help="also time one pass with a single output token per request (attributes "
+                         "the total to prefill and decode)")
     args = ap.parse_args()
 
     os.environ["VLLM_PLUGINS"] = ""                   # stock code path only
@@ -91,11 +94,11 @@ def main() -> None:
         ids = torch.randint(0, cfg["vocab_size"], (args.num_prompts, args.input_len), generator=g)
         return [{"prompt_token_ids": row} for row in ids.tolist()]
 
-    def one_pass(seed: int):
+    def one_pass(seed: int, params=None):
         ps = prompts(seed)
         torch.cuda.synchronize()
         t0 = time.perf_counter()
-        outs = llm.generate(ps, sp, use_tqdm=False)
+        outs = llm.generate(ps, params or sp, use_tqdm=False)
         torch.cuda.synchronize()
         dt = time.perf_counter() - t0
         return sum(len(o.outputs[0].token_ids) for o in outs), dt
@@ -107,6 +110,11 @@ def main() -> None:
         n, dt = one_pass(2000 + k)
         tot_out += n
         tot_s += dt
+    prefill_s = None
+    if args.prefill_only_pass:
+        sp1 = SamplingParams(max_tokens=1, temperature=0.0, ignore_eos=True, detokenize=False)
+        one_pass(3000, sp1)
+        _, prefill_s = one_pass(3001, sp1)
     if world > 1:
         import torch.distributed as dist
         t = torch.tensor([tot_s], dtype=torch.float64, device="cuda")
@@ -132,6 +140,7 @@ def main() -> None:
                        "attention_backend": args.attention_backend or "default",
                        "layers_override": args.layers or None},
             "e2e": {"value": round(value, 2), "unit": "tok/s"},
+            "prefill_only_pass_ms": None if prefill_s is None else round(prefill_s * 1e3, 1),
         }), flush=True)
     sys.stdout.flush()
     sys.stderr.flush()

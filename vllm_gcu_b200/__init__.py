@@ -19,12 +19,28 @@ def register_platform_plugins() -> str:
 
 
 def register_custom_models() -> None:
-    """Registers the quantisation configs of this package with vLLM (the model classes of the
-    built-in engine use their own registry, ``vllm_gcu_b200.models``)."""
+    """General plugin hook (runs in every vLLM process): registers this package's attention
+    backend under ``AttentionBackendEnum.CUSTOM``, its layer kernels (RMSNorm, SiLU-and-mul,
+    unquantised GEMM) and its quantisation configs with vLLM.  The model classes of the
+    built-in engine use their own registry (``vllm_gcu_b200.models``); under vLLM the upstream
+    model definitions run on these kernels."""
     try:
         from .runtime import vllm_quant
         vllm_quant.register_all()
     except Exception:   # vLLM absent or too old: the built-in engine is unaffected
+        pass
+    try:
+        from vllm.v1.attention.backends.registry import AttentionBackendEnum, register_backend
+        register_backend(AttentionBackendEnum.CUSTOM,
+                         "vllm_gcu_b200.runtime.vllm_attention.B200AttentionBackend")
+    except Exception:
+        pass
+    try:
+        import os
+        if os.environ.get("VLLM_B200_VLLM_NATIVE_OPS", "1") != "0":
+            from .runtime import vllm_ops
+            vllm_ops.register_ops()
+    except Exception:
         pass
 
 

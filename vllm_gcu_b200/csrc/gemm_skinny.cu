@@ -23,6 +23,8 @@
 // folded into the gate-up projection).
 #include "common.cuh"
 
+#include <cstdlib>
+
 namespace b200 {
 namespace skinny {
 
@@ -373,8 +375,24 @@ struct WideArgs {
   const __nv_bfloat16* bias;
   int M, N, K;
   int tiles_m, tiles_n, num_kb;
+  int group_m;          // M tiles per raster group (see wide_tile)
   unsigned int* status;
 };
+
+// Tile order of the persistent CTAs: groups of `group_m` row panels, and inside a group the
+// row index runs fastest.  The ~148 tiles that are in flight at one time then cover about
+// group_m row panels x 148 / group_m column panels instead of all row panels x a few column
+// panels, which is the smallest set of A and B panels (the square) for that many tiles: fewer
+// bytes per wave from L2 and DRAM.
+__device__ __forceinline__ void wide_tile(const WideArgs& p, int tile, int& tm, int& tn) {
+  const int group = p.group_m * p.tiles_n;
+  const int g = tile / group;
+  const int first = g * p.group_m;
+  const int gm = min(p.tiles_m - first, p.group_m);
+  const int r = tile - g * group;
+  tm = first + r % gm;
+  tn = r / gm;
+}
 
 template <int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -425,7 +443,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-        const int m0 = (tile % p.tiles_m) * (MT * BM), n0 = (tile / p.tiles_m) * BN;
+        int tm, tn;
+        wide_tile(p, tile, tm, tn);
+        const int m0 = tm * (MT * BM), n0 = tn * BN;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, p.status, kKernelId, 0x900u + stage,
                          abort_flag)) {
@@ -487,7 +507,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int q = warp & 3;
     uint32_t tphase = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-      const int m0 = (tile % p.tiles_m) * (MT * BM), n0 = (tile / p.tiles_m) * BN;
+      int tm, tn;
+      wide_tile(p, tile, tm, tn);
+      const int m0 = tm * (MT * BM), n0 = tn * BN;
       if (!mbar_wait(tfull_bar, tphase, p.status, kKernelId, 0x930u, abort_flag)) break;
       tc_fence_after();
 #pragma unroll 1
@@ -810,6 +832,13 @@ B200_API int b200_gemm_wide2(const void* A, long long lda, const void* B, long l
   a.tiles_n = N / 256;
   a.num_kb = (K + BK - 1) / BK;
   a.status = status_ptr();
+  {
+    int gm = 1;
+    while (gm * gm < sm_count()) ++gm;      // ~ sqrt(number of tiles in flight)
+    const char* env = getenv("VLLM_B200_GEMM_GROUP_M");
+    if (env != nullptr && atoi(env) > 0) gm = atoi(env);
+    a.group_m = gm < a.tiles_m ? gm : a.tiles_m;
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (epi == kSiluMul) return launch_wide2<kSiluMul>(tmA, tmB, a, s);
   if (epi == kBias) return launch_wide2<kBias>(tmA, tmB, a, s);

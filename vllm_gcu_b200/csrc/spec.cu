@@ -5,6 +5,7 @@
 //                      target token at the first mismatch or the bonus token
 //   rejection_random   accept draft token x with probability min(1, p_target(x) / p_draft(x))
 //                      (p_draft = 1 for draft-free proposers), else emit the recovered token
+//   recovered_tokens   the token emitted in place of a rejected draft token
 //   expand_batch_to_tokens  repeat a per-request value for each of its tokens
 //
 // Output rows are int32 [max_spec_len + 1], pre-filled with -1.
@@ -64,6 +65,48 @@ __global__ void rejection_random_kernel(int* out, const int* draft_ids, const fl
   if (!rejected) o[n] = static_cast<int>(bonus_ids[b]);
 }
 
+// Recovered token of one (request, draft position): argmax over the vocabulary of
+// max(0, p_target - p_draft) / noise (noise ~ Exp(1)); for draft-free proposers the draft
+// token itself is excluded instead of subtracting a draft distribution.  One CTA per row;
+// ties go to the smaller id, as torch.argmax does.
+__global__ void __launch_bounds__(256)
+    recovered_tokens_kernel(int* out, const int* draft_ids, const float* draft_probs,
+                            const float* target_probs, const float* noise, int V) {
+  __shared__ float s_val[8];
+  __shared__ int s_idx[8];
+  const long long row = blockIdx.x;
+  const float* pt = target_probs + row * V;
+  const float* pd = draft_probs ? draft_probs + row * V : nullptr;
+  const float* nz = noise + row * V;
+  const int skip = pd ? -1 : draft_ids[row];
+  float best = -1.0f;
+  int bi = 0x7fffffff;
+  for (int v = threadIdx.x; v < V; v += blockDim.x) {
+    float a = pd ? fmaxf(pt[v] - pd[v], 0.0f) : (v == skip ? 0.0f : pt[v]);
+    a = a / fmaxf(nz[v], 1e-30f);
+    if (a > best) { best = a; bi = v; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { s_val[threadIdx.x >> 5] = best; s_idx[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    best = threadIdx.x < (blockDim.x >> 5) ? s_val[threadIdx.x] : -1.0f;
+    bi = threadIdx.x < (blockDim.x >> 5) ? s_idx[threadIdx.x] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (threadIdx.x == 0) out[row] = bi == 0x7fffffff ? 0 : bi;
+  }
+}
+
 __global__ void expand_batch_kernel(long long* out, const long long* x, const int* cu_num_tokens,
                                     int B, long long replace_from, long long replace_to) {
   const int b = blockIdx.x;
@@ -95,6 +138,19 @@ B200_API int b200_rejection_random(int* out, const int* draft_ids, const float* 
   if (B <= 0) return 0;
   b200::spec::rejection_random_kernel<<<(B + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
       out, draft_ids, draft_probs, target_probs, bonus_ids, recovered_ids, uniform, num_draft, B, S, V);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// out[b, i] (int32 [B, S]) = recovered token of draft position i of request b; probs and noise
+// are fp32 [B, S, V] (draft_probs may be null for draft-free proposers).  Reference:
+// vllm_gcu/patch/patch_0_9_2/rejection_sampler.py:94-120,174 (sample_recovered_tokens).
+B200_API int b200_sample_recovered_tokens(int* out, const int* draft_ids,
+                                          const float* draft_probs, const float* target_probs,
+                                          const float* noise, int B, int S, int V, void* stream) {
+  if (B <= 0 || S <= 0) return 0;
+  if (V <= 0) return -2;
+  b200::spec::recovered_tokens_kernel<<<B * S, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      out, draft_ids, draft_probs, target_probs, noise, V);
   return static_cast<int>(cudaGetLastError());
 }
 

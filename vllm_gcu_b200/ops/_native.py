@@ -131,6 +131,7 @@ class _Sigs:
     b200_rejection_greedy = [P, P, P, P, P, I, I, P]
     b200_rejection_random = [P, P, P, P, P, P, P, P, I, I, I, P]
     b200_expand_batch_to_tokens = [P, P, P, I, L, L, P]
+    b200_sample_recovered_tokens = [P, P, P, P, P, I, I, I, P]
 
 
 def ptr(t: Optional[torch.Tensor]) -> Optional[int]:

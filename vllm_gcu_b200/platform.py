@@ -116,8 +116,8 @@ def _make_platform_class():
     The class extends vLLM's CUDA platform, so upstream code that asks ``is_cuda()`` keeps
     working, and overrides what this package provides: the configuration policy, the list of
     quantisation names, the device communicator and the punica wrapper.  Attention backends
-    of vLLM's own engine stay the upstream ones; this package's paged / MLA kernels serve its
-    built-in engine (``vllm_gcu_b200.engine``)."""
+    (``get_attn_backend_cls`` returns ``runtime.vllm_attention.B200AttentionBackend`` for the
+    configurations it covers), the worker class, the layer kernels (``runtime.vllm_ops``)."""
     global _PLATFORM_CLS
     if _PLATFORM_CLS is not None:
         return _PLATFORM_CLS
@@ -155,7 +155,22 @@ def _make_platform_class():
 
         @classmethod
         def get_punica_wrapper(cls) -> str:
-            return "vllm_gcu_b200.lora.punica.PunicaWrapperB200"
+            return "vllm_gcu_b200.runtime.vllm_punica.PunicaWrapperB200"
+
+        @classmethod
+        def get_attn_backend_cls(cls, selected_backend, attn_selector_config, num_heads=None
+                                 ) -> str:
+            """This package's paged attention backend for what it covers (decoder attention,
+            head size 64 / 128, 16-bit KV cache); everything else, and an explicitly selected
+            upstream backend, goes to the CUDA platform's choice (vllm_gcu/gcu.py:70-104)."""
+            import os
+            from .runtime import vllm_attention as va
+            explicit = selected_backend is not None and \
+                getattr(selected_backend, "name", "") != "CUSTOM"
+            if (not explicit and os.environ.get("VLLM_B200_ATTENTION", "1") != "0"
+                    and va.accepts(attn_selector_config)):
+                return va.BACKEND_PATH
+            return super().get_attn_backend_cls(selected_backend, attn_selector_config, num_heads)
 
         @classmethod
         def verify_quantization(cls, quant: str) -> None:
@@ -185,6 +200,17 @@ def _make_platform_class():
                 additional_config=dict(getattr(vllm_config, "additional_config", None) or {}),
             )
             d = apply_platform_policy(inp)
+            import os
+            if pc.worker_cls in ("auto", "vllm.v1.worker.gpu_worker.Worker"):
+                pc.worker_cls = "vllm_gcu_b200.runtime.vllm_worker.B200Worker"
+            if os.environ.get("VLLM_B200_VLLM_NATIVE_OPS", "1") != "0" and cg is not None:
+                # the layer kernels of this package are eager launches: no tracing compiler in
+                # front of them (CUDA graphs of decode batches stay available)
+                try:
+                    from vllm.config.compilation import CompilationMode
+                    cg.mode = CompilationMode.NONE
+                except Exception:  # noqa: BLE001
+                    pass
             if cc is not None and getattr(cc, "block_size", None) is None:
                 cc.block_size = d.block_size
             if hasattr(pc, "disable_custom_all_reduce"):

@@ -72,7 +72,16 @@ class RejectionSampler:
         dev = draft_ids.device
         uniform = torch.rand((B, S), device=dev, generator=generator)
         noise = torch.empty((B, S, V), device=dev).exponential_(generator=generator)
-        recovered = ref.sample_recovered_tokens(draft_ids, draft_probs, target_probs, noise)
+        if ops.use_native(draft_ids):
+            recovered = torch.empty((B, S), dtype=torch.int32, device=dev)
+            call("b200_sample_recovered_tokens", ptr(recovered), ptr(draft_ids.contiguous()),
+                 ptr(draft_probs.contiguous() if draft_probs is not None else None),
+                 ptr(target_probs.contiguous()), ptr(noise), B, S, V, stream_ptr())
+            if envs.REJECT_SAMPLER_CHECK:
+                want = ref.sample_recovered_tokens(draft_ids, draft_probs, target_probs, noise)
+                assert torch.equal(recovered.cpu(), want.cpu()), "recovered tokens mismatch"
+        else:
+            recovered = ref.sample_recovered_tokens(draft_ids, draft_probs, target_probs, noise)
         if ops.use_native(draft_ids):
             out = torch.empty((B, S + 1), dtype=torch.int32, device=dev)
             call("b200_rejection_random", ptr(out), ptr(draft_ids.contiguous()),
