@@ -8,7 +8,7 @@ mixed_step, so Nsight Compute can list the kernels of one kind of step with thei
 (one metric, one pass, nothing saved or restored):
 
   ncu --metrics gpu__time_duration.sum --clock-control none --nvtx \
-      --nvtx-include "decode_step/" -c 700 --csv --log-file gpurun_out/decode_launches.csv \
+      --nvtx-include "decode_step/" -c 700 --csv --log-file <output dir>/decode_launches.csv \
       python benchmarks/kernels/engine_steps_case.py --batch 256 --input-len 1024 --output-len 4
 """
 import argparse

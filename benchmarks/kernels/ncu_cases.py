@@ -14,7 +14,7 @@ launches the kernel of interest a handful of times:
   python benchmarks/kernels/ncu_cases.py --case wna16_decode   # fused 4-bit de-quantising GEMM
 
 Capture (one GPU):
-  ncu --set full --clock-control none -k regex:<kernel> -s 2 -c 2 -o gpurun_out/<name> \
+  ncu --set full --clock-control none -k regex:<kernel> -s 2 -c 2 -o <output dir>/<name> \
       python benchmarks/kernels/ncu_cases.py --case <case>
 """
 import argparse

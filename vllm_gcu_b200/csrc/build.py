@@ -53,8 +53,6 @@ def _compile_one(src: Path, force: bool, verbose: bool) -> Path:
     obj = OBJ_DIR / (src.stem + ".o")
     stamp = OBJ_DIR / (src.stem + ".sha")
     flags = list(NVCC_FLAGS)
-    if os.environ.get("B200_BOUNDS", "0") == "1":
-        flags += ["-DB200_BOUNDS=1"]
     if verbose:
         flags += ["-Xptxas", "-v"]
     dig = _digest(src, " ".join(flags))

@@ -121,7 +121,11 @@ class PagedAttention(nn.Module):
         ks_t = vs_t = None
         if k_cache.element_size() == 1:
             if k_cache.dtype == torch.int8 and self.k_scale == 1.0 and self.v_scale == 1.0:
-                self.k_scale = self.v_scale = 1.0 / 16.0     # no calibrated scales were loaded
+                # no calibrated scales were loaded: a fixed step that keeps |x| < 8 in range
+                self.k_scale = self.v_scale = 1.0 / 16.0
+                import warnings
+                warnings.warn("int8 KV cache without loaded k/v scales: using 1/16 for both; "
+                              "load calibrated scales for accuracy", stacklevel=2)
             if self._scale_t is None or self._scale_t.device != q.device:
                 self._scale_t = torch.tensor([self.k_scale, self.v_scale], dtype=torch.float32,
                                              device=q.device)
