@@ -214,3 +214,24 @@ def test_feed_tokens(C):
     want[dst[:3].long()] = prev[src[:3].long()]
     C.feed_tokens(ids, prev, dst, src, 3)                 # only the first n pairs are live
     assert torch.equal(ids, want)
+
+
+@pytest.mark.parametrize("D", [128, 64])
+def test_cascade_attention_matches_the_full_pass(C, D):
+    """Shared-prefix attention (one non-causal pass over the common blocks + causal passes over
+    the suffixes, merged by log-sum-exp) against one ordinary pass over everything."""
+    from vllm_gcu_b200.layers.attention import cascade_attention
+    g = torch.Generator(device=DEV).manual_seed(6)
+    nb, bs, Hq, Hkv = 64, 16, 8, 2
+    kc = torch.randn(nb, bs, Hkv, D, device=DEV, generator=g).to(torch.bfloat16)
+    vc = torch.randn(nb, bs, Hkv, D, device=DEV, generator=g).to(torch.bfloat16)
+    prefix = list(range(20, 36))                            # 256 shared tokens
+    rows = [prefix + [1, 2, 3, 0], prefix + [4, 0, 0, 0], prefix + [5, 6, 0, 0], prefix + [7, 8, 9, 10]]
+    bt = torch.tensor(rows, dtype=torch.int32, device=DEV)
+    q_lens = [33, 1, 1, 64]
+    seq_lens = torch.tensor([256 + 40, 256 + 3, 256 + 17, 256 + 64], dtype=torch.int32, device=DEV)
+    cu = torch.tensor([0, 33, 34, 35, 99], dtype=torch.int32, device=DEV)
+    q = torch.randn(99, Hq, D, device=DEV, generator=g).to(torch.bfloat16)
+    want = ref.varlen_prefill_attention(q, kc, vc, bt, cu, seq_lens, D ** -0.5)
+    got = cascade_attention(q, kc, vc, bt, cu, seq_lens, D ** -0.5, 256, q_lens, native=True)
+    _close(got, want, 3e-2, 3e-2)

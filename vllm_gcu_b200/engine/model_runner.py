@@ -127,6 +127,12 @@ class ModelRunner:
         self._mm_inputs = None                     # (inputs_embeds, mrope positions) of a step
         from .. import envs
         self.nvtx = bool(envs.NVTX) and self.is_cuda
+        # shared-prefix (cascade) attention for steps that do not replay a CUDA graph: used
+        # when every request of the step starts with at least this many identical cached
+        # tokens (0 = never)
+        self.cascade_min_tokens = int(cfg.additional_config.get("cascade_min_tokens", 256)) \
+            if getattr(cfg, "additional_config", None) is not None else 256
+        self.cascade_steps = 0
         self.last_logits: Optional[torch.Tensor] = None
         self._alloc_buffers()
 
@@ -564,6 +570,16 @@ class ModelRunner:
                 self.input_ids[self.feed_dst[:nf].long()] = prev_sampled[self.feed_src[:nf].long()]
 
         out_ids = self.sampled[cur]
+        common_prefix = 0
+        if (not use_graph and self.cascade_min_tokens > 0 and B >= 4 and not mm_step
+                and not self.max_spec and self.model.kv_cache_spec()["type"] == "gqa"):
+            nblk = int(starts.min()) // bs          # only tokens that are already in the cache
+            if nblk * bs >= self.cascade_min_tokens:
+                same = (self.bt_host[rows, :nblk] == self.bt_host[rows[0], :nblk][None, :]).all(0)
+                k = nblk if bool(same.all()) else int(np.argmin(same))
+                if k * bs >= self.cascade_min_tokens:
+                    common_prefix = k * bs
+                    self.cascade_steps += 1
         md = AttentionMetadata(
             num_tokens=T, num_decodes=B_pad - npf if use_graph else nd, num_prefills=npf,
             num_decode_tokens=(B_pad if use_graph else nd),
@@ -576,7 +592,10 @@ class ModelRunner:
             decode_splits=self._decode_splits(B_pad if use_graph else max(nd, 1), max_seq_len),
             decode_workspace=self.decode_ws,
             sample_indices=self.sample_indices[:max(ns * width, 1)],
-            q_lens_cpu=[int(x) for x in ntok], seq_lens_cpu=[int(x) for x in seq_after])
+            q_lens_cpu=[int(x) for x in ntok], seq_lens_cpu=[int(x) for x in seq_after],
+            common_prefix_len=common_prefix,
+            cu_q_all=torch.tensor(tok_off, dtype=torch.int32, device=self.device)
+            if common_prefix else None)
 
         self._features = self._build_features(order, samplers, tok_off) if feat else None
         self._mm_inputs = self._build_mm_inputs(mm_chunks, T) if mm_chunks else None

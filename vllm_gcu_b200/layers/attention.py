@@ -52,6 +52,48 @@ class AttentionMetadata:
     # rows gathered per section are cached here by the first layer of a step
     mrope_positions: Optional[torch.Tensor] = None
     mrope_cos_sin: Optional[torch.Tensor] = None
+    # shared-prefix (cascade) attention: every request of the step starts with the same
+    # ``common_prefix_len`` cached tokens (a multiple of the block size; 0 = off) and
+    # ``cu_q_all`` holds the query offsets of all requests, decodes included
+    common_prefix_len: int = 0
+    cu_q_all: Optional[torch.Tensor] = None
+
+
+def cascade_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                      block_tables: torch.Tensor, cu_q: torch.Tensor, seq_lens: torch.Tensor,
+                      scale: float, common_prefix_len: int, q_lens_cpu: list[int],
+                      native: bool) -> torch.Tensor:
+    """Attention of a batch whose requests all start with the same ``common_prefix_len``
+    cached tokens: one pass of all query tokens over the shared prefix (read once instead of
+    once per request, no causal mask: every query lies behind it), one causal pass per request
+    over its own suffix, merged by their log-sum-exp values.  q ``[T, Hq, D]``; ``cu_q`` /
+    ``seq_lens`` / ``block_tables`` describe all requests (the reference's cascade path,
+    vllm_gcu/v1/attention/flash_attn.py:97-177)."""
+    bs = k_cache.shape[1]
+    assert common_prefix_len > 0 and common_prefix_len % bs == 0
+    T = q.shape[0]
+    nb = common_prefix_len // bs
+    dev = q.device
+    one_cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
+    one_len = torch.tensor([common_prefix_len], dtype=torch.int32, device=dev)
+    suffix_lens = (seq_lens - common_prefix_len).to(torch.int32)
+    suffix_bt = block_tables[:, nb:].contiguous()
+    if native:
+        p_out, p_lse = C.varlen_prefill(q, k_cache, v_cache, block_tables[:1, :nb].contiguous(),
+                                        one_cu, one_len, scale, -(-T // 64), causal=False,
+                                        return_lse=True, num_q_tiles_128=-(-T // 128))
+        s_out, s_lse = C.varlen_prefill(
+            q, k_cache, v_cache, suffix_bt, cu_q, suffix_lens, scale,
+            sum(-(-n // 64) for n in q_lens_cpu), return_lse=True,
+            num_q_tiles_128=sum(-(-n // 128) for n in q_lens_cpu))
+        out, _ = C.merge_attn_states(p_out, p_lse, s_out, s_lse, want_lse=False)
+        return out
+    p_out, p_lse = ref.varlen_prefill_attention(q, k_cache, v_cache, block_tables[:1, :nb],
+                                                one_cu, one_len, scale, causal=False,
+                                                return_lse=True)
+    s_out, s_lse = ref.varlen_prefill_attention(q, k_cache, v_cache, suffix_bt, cu_q, suffix_lens,
+                                                scale, return_lse=True)
+    return ref.merge_attn_states(p_out, p_lse, s_out, s_lse)[0]
 
 
 def allocate_kv_cache(num_layers: int, num_blocks: int, block_size: int, kv_heads: int,
@@ -136,6 +178,14 @@ class PagedAttention(nn.Module):
                            k_cache, v_cache, ks_t, vs_t)
         out = torch.empty((T, Hq * D), dtype=q.dtype, device=q.device)
         nd = md.num_decode_tokens
+        if md.common_prefix_len > 0 and kvq is None and D in (64, 128) and not self.window:
+            B = md.num_decodes + md.num_prefills
+            n_real = sum(md.q_lens_cpu[:B])
+            o = cascade_attention(q[:n_real].view(n_real, Hq, D), k_cache, v_cache,
+                                  md.block_tables[:B], md.cu_q_all, md.seq_lens[:B], self.scale,
+                                  md.common_prefix_len, md.q_lens_cpu[:B], native=True)
+            out[:n_real] = o.reshape(n_real, Hq * D)
+            return out
         if nd > 0:
             C.paged_decode(q[:nd].view(nd, Hq, D), k_cache, v_cache, md.block_tables[:nd],
                            md.seq_lens[:nd], self.scale, out=out[:nd].view(nd, Hq, D),
@@ -178,6 +228,12 @@ class PagedAttention(nn.Module):
         cu[1:] = torch.tensor(q_lens, dtype=torch.int32).cumsum(0)
         n_real = int(cu[-1])
         out = torch.zeros((T, Hq * D), dtype=q.dtype, device=q.device)
+        if md.common_prefix_len > 0 and not self.window:
+            o = cascade_attention(q[:n_real].reshape(n_real, Hq, D), k_cache, v_cache,
+                                  md.block_tables[:B], cu, md.seq_lens[:B], self.scale,
+                                  md.common_prefix_len, q_lens, native=False)
+            out[:n_real] = o.reshape(n_real, Hq * D)
+            return out
         o = ref.varlen_prefill_attention(q[:n_real].reshape(n_real, Hq, D), k_cache, v_cache,
                                          md.block_tables[:B], cu, md.seq_lens[:B], self.scale,
                                          window=self.window)
