@@ -170,10 +170,14 @@ def main():
     kernel that waits for it: every rank reaches the final barrier, then all exit together."""
     world = int(os.environ["WORLD_SIZE"])
     rank = int(os.environ["RANK"])
-    st = init_distributed(tp=world)
+    pp_mode = os.environ.get("B200_TEST_ONLY") == "pp"
+    st = init_distributed(tp=1, pp=world) if pp_mode else init_distributed(tp=world)
     failed = False
     try:
-        run_checks(world, rank, st)
+        if pp_mode:
+            run_pp_check(world, rank, st)
+        else:
+            run_checks(world, rank, st)
     except BaseException:  # noqa: BLE001
         import traceback
         traceback.print_exc()
@@ -189,6 +193,37 @@ def main():
     sys.stdout.flush()
     sys.stderr.flush()
     os._exit(1 if int(flag.item()) else 0)
+
+
+def run_pp_check(world, rank, st):
+    """Pipeline parallelism on GPUs: the stages hand (hidden, residual) over NCCL p2p on a side
+    stream; every generated token must be a (near-)maximum of the dense fp32 logits."""
+    dev = torch.device("cuda", st.local_rank)
+    kw = dict(num_hidden_layers=4, hidden_size=1024, intermediate_size=2048,
+              num_attention_heads=8, num_key_value_heads=2, head_dim=128, vocab_size=4096,
+              max_num_seqs=8, max_num_batched_tokens=256, max_model_len=256, num_gpu_blocks=128)
+    cfg = preset("llama-3-8b", **{k: v for k, v in kw.items() if k in (
+        "num_hidden_layers", "hidden_size", "intermediate_size", "num_attention_heads",
+        "num_key_value_heads", "head_dim", "vocab_size")})
+    sd = full_state_dict(cfg)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 4096, (n,), generator=g).tolist() for n in (33, 64, 5, 120)]
+    llm = LLM("llama-3-8b", pipeline_parallel_size=world, enforce_eager=True, load_format="none",
+              **kw)
+    llm.engine.model.load_weights(sd.items())
+    outs = llm.generate(prompts, SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True))
+    torch.cuda.synchronize()
+    _native.check_status()
+    seqs = [o.outputs[0].token_ids for o in outs]
+    full = [p_ + t_ for p_, t_ in zip(prompts, seqs)]
+    dense = dense_last_logits(cfg, sd, [f[:-1] for f in full], dev, all_positions=True)
+    for p_, t_, lg in zip(prompts, seqs, dense):
+        tail = lg[len(p_) - 1:]
+        assert len(t_) == 8
+        gap = tail.max(-1).values - tail.gather(-1, torch.tensor(t_)[:, None]).squeeze(-1)
+        assert gap.max().item() < 0.06 * lg.std().item() + 0.03, f"pp{world}: {gap}"
+    if rank == 0:
+        print(f"pp{world} engine ok", flush=True)
 
 
 def run_checks(world, rank, st):

@@ -42,6 +42,18 @@ def test_gemm_allreduce_norm_over_multimem_two_gpus():
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2,
                     reason="needs >= 2 GPUs")
+def test_pipeline_parallel_two_gpus():
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", B200_TEST_ONLY="pp")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+           "--master-addr", "127.0.0.1", "--master-port", "29617",
+           os.path.join(ROOT, "tests", "_tp_worker.py")]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert "pp2 engine ok" in res.stdout
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2,
+                    reason="needs >= 2 GPUs")
 def test_expert_parallel_fused_dispatch_two_gpus():
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     n = min(torch.cuda.device_count(), 8)

@@ -61,3 +61,30 @@ def test_ngram_proposer():
     p = NgramProposer(3, 3, 1)
     assert p.propose([1, 2, 3, 9, 1, 2, 3]) == [9, 1, 2]
     assert p.propose([1, 2, 3]) == []
+
+
+def test_medusa_and_mlp_speculator_heads_are_lossless_under_greedy():
+    """Draft heads propose from the target's hidden state; whatever they propose, greedy
+    verification keeps the output identical to plain decoding."""
+    _, base = _run("tiny-llama", n_out=12)
+    for method in ("medusa", "mlp_speculator"):
+        llm, spec = _run("tiny-llama", n_out=12, speculative_method=method,
+                         num_speculative_tokens=2)
+        assert spec == base, method
+        m = llm.engine.spec_metrics
+        assert m.num_drafts > 0 and m.num_draft_tokens == 2 * m.num_drafts
+
+
+def test_draft_heads_propose_shapes():
+    from vllm_gcu_b200.spec import MedusaProposer, MLPSpeculatorProposer
+    h = torch.randn(5, 64)
+    last = torch.randint(0, 100, (5,))
+    for cls in (MedusaProposer, MLPSpeculatorProposer):
+        p = cls(64, 100, 3, dtype=torch.float32)
+        p.init_random(1)
+        out = p.propose(h, last)
+        assert out.shape == (5, 3) and out.dtype == torch.int64
+        sd = {k: v.clone() for k, v in p.state_dict().items()}
+        q = cls(64, 100, 3, dtype=torch.float32)
+        assert len(q.load_weights(sd.items())) == len(sd)
+        assert torch.equal(q.propose(h, last), out)

@@ -85,6 +85,18 @@ class LLMEngine:
                     drafter.load_weights(iter_safetensors(cfg.model_path))
                 drafter.eval()
                 self.runner.drafter = drafter
+            elif sp.method in ("medusa", "mlp_speculator"):
+                from ..spec import MedusaProposer, MLPSpeculatorProposer
+                mc_ = cfg.model
+                cls = MedusaProposer if sp.method == "medusa" else MLPSpeculatorProposer
+                heads = cls(mc_.hidden_size, mc_.vocab_size, sp.num_speculative_tokens,
+                            dtype=mc_.dtype, device=self.device)
+                if sp.draft_model:
+                    from ..utils.weights import iter_safetensors
+                    heads.load_weights(iter_safetensors(sp.draft_model))
+                else:
+                    heads.init_random(cfg.seed)
+                self.runner.head_drafter = heads.eval()
             else:
                 raise ValueError(f"unknown speculative method {sp.method!r}")
         num_blocks = self.runner.profile_num_blocks()
@@ -370,6 +382,7 @@ class LLM:
                  enable_expert_parallel: bool = False, dtype: Optional[str] = None,
                  cuda_graph_sizes: Optional[list[int]] = None,
                  speculative_method: Optional[str] = None, num_speculative_tokens: int = 0,
+                 speculative_model: Optional[str] = None,
                  prompt_lookup_max: int = 4, prompt_lookup_min: int = 1,
                  enable_lora: bool = False, max_loras: int = 4, max_lora_rank: int = 16,
                  additional_config: Optional[dict] = None, tokenizer=None, **model_overrides):
@@ -404,7 +417,8 @@ class LLM:
                                     comm_backend=comm_backend,
                                     enable_expert_parallel=enable_expert_parallel),
             speculative=SpeculativeConfig(speculative_method, num_speculative_tokens,
-                                          prompt_lookup_max, prompt_lookup_min),
+                                          prompt_lookup_max, prompt_lookup_min,
+                                          speculative_model),
             device=device, seed=seed, enforce_eager=enforce_eager,
             cuda_graph_sizes=cuda_graph_sizes,
             load_format=load_format or ("safetensors" if model_path else "dummy"),

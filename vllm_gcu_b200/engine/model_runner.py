@@ -47,12 +47,13 @@ class StepHandle:
     extra: dict = field(default_factory=dict)
 
     def draft_tokens(self) -> Optional[dict[str, list[int]]]:
-        """Draft token proposed by the on-device drafter for every sampling request."""
+        """Draft tokens proposed by the on-device drafter for every sampling request."""
         if self.draft_host is None or self.num_sampled == 0:
             return None
         self.wait()
-        arr = self.draft_host[: self.num_sampled].numpy()
-        return {rid: [int(arr[i])] for i, rid in enumerate(self.req_ids)}
+        k = int(self.extra.get("draft_width", 1))
+        arr = self.draft_host[: self.num_sampled * k].numpy().reshape(self.num_sampled, k)
+        return {rid: [int(t) for t in arr[i]] for i, rid in enumerate(self.req_ids)}
 
     def ready(self) -> bool:
         return self.event is None or self.event.query()
@@ -106,6 +107,7 @@ class ModelRunner:
         self.max_spec = cfg.speculative.num_speculative_tokens if cfg.speculative.method else 0
         self.rejection = None
         self.drafter = None                        # on-device drafter (DeepSeek MTP)
+        self.head_drafter = None                   # Medusa heads / MLP speculator (spec/heads.py)
         self.lora = None                           # LoRAManager when multi-LoRA is enabled
         self.drafter_caches: list[torch.Tensor] = []
         if self.max_spec:
@@ -186,8 +188,9 @@ class ModelRunner:
         self.sampled = [torch.zeros(S * W, dtype=torch.int64, device=dev) for _ in range(2)]
         self.sampled_host = [torch.zeros(S * W, dtype=torch.int64, pin_memory=pin)
                              for _ in range(2)]
-        self.draft_out = torch.zeros(S, dtype=torch.int64, device=dev)
-        self.draft_host = torch.zeros(S, dtype=torch.int64, pin_memory=pin)
+        self.draft_out = torch.zeros(S * max(1, self.max_spec), dtype=torch.int64, device=dev)
+        self.draft_host = torch.zeros(S * max(1, self.max_spec), dtype=torch.int64,
+                                      pin_memory=pin)
         self.decode_ws: Optional[tuple[torch.Tensor, torch.Tensor]] = None
         # host-side block table, one row per live request
         self.bt_rows: dict[str, int] = {}
@@ -378,7 +381,8 @@ class ModelRunner:
             nd_graph = max(nd, int(get_state().dp_max_tokens or 0))
         use_graph = (self.is_cuda and npf == 0 and bool(self.graphs)
                      and nd_graph <= self.graph_sizes[-1]
-                     and self.drafter is None and not batch_has_lora and not feat)
+                     and self.drafter is None and self.head_drafter is None
+                     and not batch_has_lora and not feat)
         B_pad = _pad_batch(nd_graph, self.graph_sizes) if use_graph else B
         T = T_real + (B_pad - B)
 
@@ -620,9 +624,10 @@ class ModelRunner:
         if ns:
             host[:ns * width].copy_(out_ids[:ns * width], non_blocking=True)
             self.d2h_bytes += ns * width * 8
-            if self.drafter is not None:
-                self.draft_host[:ns].copy_(self.draft_out[:ns], non_blocking=True)
-                self.d2h_bytes += ns * 8
+            if self.drafter is not None or self.head_drafter is not None:
+                dk = self.head_drafter.k if self.head_drafter is not None else 1
+                self.draft_host[:ns * dk].copy_(self.draft_out[:ns * dk], non_blocking=True)
+                self.d2h_bytes += ns * dk * 8
         if self.is_cuda:
             if ev1 is not None:
                 ev1.record()
@@ -633,14 +638,16 @@ class ModelRunner:
             event.record()
         self.prev_index = {order[j].req.request_id: r for r, j in enumerate(samplers)}
         self.step_counter += 1
-        extra = {"num_draft": nspec}
+        extra = {"num_draft": nspec,
+                 "draft_width": self.head_drafter.k if self.head_drafter is not None else 1}
         if self._features is not None:
             extra["logprobs"] = self._features.pop("logprobs_out", None)
             extra["prompt_logprobs"] = self._features.pop("prompt_logprobs_out", None)
             self._features = None
         return StepHandle([order[j].req.request_id for j in samplers], ns, host, event,
                           width, device_ms_events=(ev0, ev1) if ev0 is not None else None,
-                          draft_host=self.draft_host if self.drafter is not None else None,
+                          draft_host=self.draft_host if (self.drafter is not None or
+                                                         self.head_drafter is not None) else None,
                           extra=extra)
 
     def _build_mm_inputs(self, mm_chunks, T: int):
@@ -778,16 +785,7 @@ class ModelRunner:
         pp = get_state().pp
         inter = None
         if pp.world_size > 1 and not self.model.is_first_stage:
-            # pipeline hand-off: (hidden, residual) of the previous stage over NCCL p2p
-            # (vllm_gcu/worker/worker_v1.py:341-360)
-            import torch.distributed as dist
-            H = self.cfg.model.hidden_size
-            x = torch.empty((T, H), dtype=self.cfg.model.dtype, device=self.device)
-            r = torch.empty_like(x)
-            src = pp.ranks[pp.rank_in_group - 1]
-            dist.recv(x, src, group=pp.device_group)
-            dist.recv(r, src, group=pp.device_group)
-            inter = (x, r)
+            inter = self._pp_recv(pp, T)
         mm = getattr(self, "_mm_inputs", None)
         hidden = self.model(self.input_ids[:T], md, self.kv_caches, intermediate=inter,
                             inputs_embeds=mm[0] if mm is not None else None)
@@ -795,9 +793,7 @@ class ModelRunner:
             import torch.distributed as dist
             last = pp.ranks[-1]
             if not self.model.is_last_stage:
-                dst = pp.ranks[pp.rank_in_group + 1]
-                dist.send(hidden[0].contiguous(), dst, group=pp.device_group)
-                dist.send(hidden[1].contiguous(), dst, group=pp.device_group)
+                self._pp_send(pp, hidden)
                 if ns:      # every stage needs the sampled ids (stop checks, next inputs)
                     dist.broadcast(out_ids[:ns * width], last, group=pp.device_group)
                 return
@@ -811,7 +807,8 @@ class ModelRunner:
         else:
             rows = hidden.index_select(0, self.sample_indices[:ns * width])
         if (all_greedy and width == 1 and feats is None and not self.keep_logits
-                and self.drafter is None and self._greedy_shortcut):
+                and self.drafter is None and self.head_drafter is None
+                and self._greedy_shortcut):
             # greedy decoding under tensor parallelism: each rank reduces its vocabulary block
             # to (max, argmax) per row and only those pairs are exchanged
             out_ids[:ns].copy_(self.model.greedy_tokens(rows))
@@ -838,9 +835,62 @@ class ModelRunner:
                                      width=width)
         if self.drafter is not None:
             self._draft_mtp(hidden, md, T, ns, width, out_ids)
+        if self.head_drafter is not None:
+            self._draft_heads(hidden, ns, width, out_ids)
         if pp.world_size > 1:
             import torch.distributed as dist
             dist.broadcast(out_ids[:ns * width], pp.ranks[-1], group=pp.device_group)
+
+    # -- pipeline hand-off ------------------------------------------------------------------
+    # (hidden, residual) travel between stages over NCCL p2p (vllm_gcu/worker/worker_v1.py:
+    # 341-360).  On GPUs the transfers run on a side stream tied to the compute stream by
+    # events: a stage's compute stream is not held up by its own sends (it can take the next
+    # step while they drain), and a receive is posted as soon as the step starts.
+    def _pp_side_stream(self):
+        if not self.is_cuda:
+            return None
+        if getattr(self, "_pp_stream", None) is None:
+            self._pp_stream = torch.cuda.Stream()
+        return self._pp_stream
+
+    def _pp_recv(self, pp, T: int):
+        import torch.distributed as dist
+        H = self.cfg.model.hidden_size
+        x = torch.empty((T, H), dtype=self.cfg.model.dtype, device=self.device)
+        r = torch.empty_like(x)
+        src = pp.ranks[pp.rank_in_group - 1]
+        side = self._pp_side_stream()
+        if side is None:
+            dist.recv(x, src, group=pp.device_group)
+            dist.recv(r, src, group=pp.device_group)
+            return x, r
+        cur = torch.cuda.current_stream()
+        side.wait_stream(cur)                    # the buffers exist before the receives use them
+        with torch.cuda.stream(side):
+            dist.recv(x, src, group=pp.device_group)
+            dist.recv(r, src, group=pp.device_group)
+            done = side.record_event()
+        x.record_stream(side)
+        r.record_stream(side)
+        cur.wait_event(done)
+        return x, r
+
+    def _pp_send(self, pp, hidden) -> None:
+        import torch.distributed as dist
+        dst = pp.ranks[pp.rank_in_group + 1]
+        h0, h1 = hidden[0].contiguous(), hidden[1].contiguous()
+        side = self._pp_side_stream()
+        if side is None:
+            dist.send(h0, dst, group=pp.device_group)
+            dist.send(h1, dst, group=pp.device_group)
+            return
+        ready = torch.cuda.current_stream().record_event()
+        with torch.cuda.stream(side):
+            side.wait_event(ready)
+            dist.send(h0, dst, group=pp.device_group)
+            dist.send(h1, dst, group=pp.device_group)
+        h0.record_stream(side)
+        h1.record_stream(side)
 
     def _verify(self, logits: torch.Tensor, st: Optional[SamplingTensors], ns: int, width: int,
                 out_ids: torch.Tensor) -> None:
@@ -877,6 +927,18 @@ class ModelRunner:
             out = self.rejection.random(draft, None, probs[:, :S].contiguous(), bonus, nd,
                                         generator=gen)
         out_ids[:ns * width].copy_(out.reshape(-1))
+
+    def _draft_heads(self, hidden: torch.Tensor, ns: int, width: int, out_ids: torch.Tensor
+                     ) -> None:
+        """Medusa heads / MLP speculator: drafts from the hidden row of the last accepted
+        position and the token emitted there."""
+        toks = out_ids[:ns * width].view(ns, width)
+        n_emit = (toks >= 0).sum(dim=1).clamp(min=1)
+        last_tok = toks.gather(1, (n_emit - 1)[:, None]).squeeze(1)
+        rows0 = self.sample_indices[:ns * width].view(ns, width)[:, 0]
+        h = hidden.index_select(0, rows0 + n_emit - 1)
+        k = self.head_drafter.k
+        self.draft_out[:ns * k].copy_(self.head_drafter.propose(h, last_tok).reshape(-1))
 
     def _draft_mtp(self, hidden: torch.Tensor, md: AttentionMetadata, T: int, ns: int,
                    width: int, out_ids: torch.Tensor) -> None:

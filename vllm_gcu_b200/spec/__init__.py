@@ -7,5 +7,6 @@ replaces the v1 rejection-sampler kernels with native ops
 (vllm_gcu/patch/patch_0_9_2/rejection_sampler.py:174-466).  Here the proposer runs inside the
 model runner right after the target step and the verification is one kernel per step.
 """
+from .heads import MedusaProposer, MLPSpeculatorProposer  # noqa: F401
 from .ngram import NgramProposer  # noqa: F401
 from .rejection import RejectionSampler, SpecMetrics  # noqa: F401
