@@ -179,3 +179,65 @@ def test_pipeline_parallel_matches_single_stage(tmp_path):
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     mp.spawn(_worker_pp, args=(2, port, "_check_pp"), nprocs=2, join=True)
+
+
+def _check_etp(rank, world):
+    """ETP: data-parallel attention without EP.  Every rank holds a slice of every expert's
+    intermediate dimension; rows are gathered over DP and the sums scattered back."""
+    from vllm_gcu_b200.config import preset
+    from vllm_gcu_b200.layers.moe import SparseMoeBlock
+    from vllm_gcu_b200.ops import ref
+    from vllm_gcu_b200.parallel.state import get_state
+    st = get_state()
+    cfg = preset("tiny-qwen3-moe", num_experts=8, num_experts_per_tok=2)
+    cfg.extra["dp_attention"] = True
+    torch.manual_seed(0)
+    blk = SparseMoeBlock(cfg, "cpu", "m")
+    assert blk.use_etp and not blk.use_ep
+    E, I, H = cfg.num_experts, cfg.moe_intermediate_size, cfg.hidden_size
+    assert blk.experts.inter == I // world
+    assert blk.experts.shard_index == st.dp.rank_in_group * st.tp.world_size + st.tp.rank_in_group
+    g = torch.Generator().manual_seed(1)
+    w13 = torch.randn(E, 2 * I, H, generator=g) * 0.05
+    w2 = torch.randn(E, H, I, generator=g) * 0.05
+    gate = torch.randn(E, H, generator=g) * 0.5
+    blk.gate.weight.data.copy_(gate)
+    for e in range(E):
+        blk.experts.load_expert_weight(e, "gate", w13[e, :I])
+        blk.experts.load_expert_weight(e, "up", w13[e, I:])
+        blk.experts.load_expert_weight(e, "down", w2[e])
+    # ranks of one TP group hold the same rows; replicas hold different ones, one is idle
+    d = st.dp.rank_in_group
+    for trial in range(2):
+        T = 0 if (d == 1 and trial == 0) else 4 + d + trial
+        x = torch.randn(T, H, generator=torch.Generator().manual_seed(10 + d + 7 * trial))
+        got = blk(x)
+        logits = x @ gate.t()
+        if T:
+            w, ids = ref.topk_softmax(logits, 2, True)
+            want = ref.fused_experts(x, w13, w2, w, ids)
+        else:
+            want = x
+        assert got.shape == x.shape
+        assert torch.allclose(got, want, atol=1e-5, rtol=1e-4), (got - want).abs().max()
+
+
+def _worker_etp(rank, world, port, tp):
+    sys.path.insert(0, ROOT)
+    os.environ.update({"RANK": str(rank), "WORLD_SIZE": str(world), "LOCAL_RANK": str(rank),
+                       "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port)})
+    from vllm_gcu_b200.parallel.state import init_distributed
+    init_distributed(tp=tp, dp=world // tp, backend="gloo", enable_ep=False)
+    _check_etp(rank, world)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+@pytest.mark.parametrize("world,tp", [(2, 1), (4, 2)])
+def test_etp_gather_scatter_matches_reference(world, tp):
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_worker_etp, args=(world, port, tp), nprocs=world, join=True)

@@ -3,6 +3,8 @@
 Failures are injected on the host (a worker that raises, a worker process that exits); no
 device is involved.
 """
+import os
+
 import pytest
 import torch
 
@@ -96,3 +98,68 @@ def test_dp2_ep_executor_keeps_idle_replica_in_step():
     # the first prompt gives the same tokens whether or not the other replica has work:
     # a request only sees its own tokens and the (replicated or expert-sharded) weights
     assert many[0].outputs[0].token_ids == one[0].outputs[0].token_ids
+
+
+def _moe_checkpoint(path, mc):
+    """Random Qwen3-MoE weights under HuggingFace names (one tensor per expert projection)."""
+    from vllm_gcu_b200.models import build_model
+    from vllm_gcu_b200.utils.weights import write_safetensors
+    src = build_model(mc, "cpu")
+    src.init_random(3, std=0.05)
+    D, Hq, Hkv = mc.head_dim, mc.num_attention_heads, mc.num_key_value_heads
+    I = mc.moe_intermediate_size
+    out = {}
+    for name, p_ in src.state_dict().items():
+        if name.startswith(("layers.", "embed_tokens.", "norm.")):
+            name = "model." + name
+        if ".qkv_proj.weight" in name:
+            q, k, v = p_.split([Hq * D, Hkv * D, Hkv * D], 0)
+            for n, t in (("q_proj", q), ("k_proj", k), ("v_proj", v)):
+                out[name.replace("qkv_proj", n)] = t.clone()
+        elif name.endswith(".experts.w13"):
+            for e in range(p_.shape[0]):
+                base = name[:-len("w13")] + f"{e}."
+                out[base + "gate_proj.weight"] = p_[e, :I].clone()
+                out[base + "up_proj.weight"] = p_[e, I:].clone()
+        elif name.endswith(".experts.w2"):
+            for e in range(p_.shape[0]):
+                out[name[:-len("w2")] + f"{e}.down_proj.weight"] = p_[e].clone()
+        else:
+            out[name] = p_.clone()
+    write_safetensors(os.path.join(path, "model.safetensors"), out)
+
+
+@pytest.mark.timeout(300)
+def test_dp2_etp_executor_matches_single_process(tmp_path):
+    """ETP (data-parallel attention, no expert parallelism): experts are sharded over the two
+    replicas, rows are gathered and the sums scattered back every MoE layer.  The tokens are
+    those of one unsharded engine, with one replica idle or both busy."""
+    from vllm_gcu_b200.engine.llm import LLMEngine
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    g = torch.Generator().manual_seed(6)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (9, 30, 4, 21)]
+    _moe_checkpoint(str(tmp_path), preset("tiny-qwen3-moe"))
+    cfg = _dp_cfg()
+    cfg.parallel.enable_expert_parallel = False
+    cfg.load_format, cfg.model_path = "safetensors", str(tmp_path)
+    ex = MultiprocExecutor(cfg)
+    try:
+        one = ex.generate(prompts[:1], sp, timeout_s=120)
+        many = ex.generate(prompts, sp, timeout_s=120)
+        ex.check_health()
+    finally:
+        ex.shutdown()
+    single = _dp_cfg()
+    single.parallel = ParallelConfig()
+    single.model.extra.pop("dp_attention")
+    single.load_format, single.model_path = "safetensors", str(tmp_path)
+    eng = LLMEngine(single)
+    for i_, p_ in enumerate(prompts):
+        eng.add_request(p_, sp, request_id=str(i_))
+    want = {}
+    while eng.has_unfinished():
+        for o in eng.step():
+            if o.finished:
+                want[int(o.request_id)] = o.outputs[0].token_ids
+    assert [o.outputs[0].token_ids for o in many] == [want[i_] for i_ in range(len(prompts))]
+    assert one[0].outputs[0].token_ids == want[0]

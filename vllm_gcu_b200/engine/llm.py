@@ -41,6 +41,9 @@ class LLMEngine:
         else:
             self.device = torch.device(cfg.device)
         torch.manual_seed(cfg.seed)
+        if pc.data_parallel_size > 1:
+            # every replica holds different tokens: MoE layers dispatch (EP) or gather (ETP)
+            cfg.model.extra.setdefault("dp_attention", True)
         self.model = build_model(cfg.model, self.device)
         if cfg.load_format == "dummy":
             self.model.init_random(cfg.seed)

@@ -966,6 +966,8 @@ class ModelRunner:
         if dp and any(type(getattr(m, "dispatcher", None)).__name__ == "AllToAllDispatcher"
                       for m in self.model.modules()):
             return      # the library all-to-all sizes its exchange on the host: eager only
+        if dp and any(getattr(m, "use_etp", False) for m in self.model.modules()):
+            return      # ETP gathers rows of host-known counts over the DP group: eager only
         if sizes is None:
             sizes = [1, 2, 4, 8] + list(range(16, self.max_seqs + 1, 16))
         sizes = sorted({s for s in sizes if s <= self.max_seqs})

@@ -13,7 +13,12 @@ Parallel layouts (vllm_gcu/kernels/prepare_finalize.py:19-610, patch_0_9_2/moe_l
   hidden states): each rank owns ``E / ep`` contiguous experts, computes their contribution
   for all tokens and the partial sums are all-reduced – no dispatch is needed;
 * EP with data-parallel attention (every rank holds different tokens): tokens travel to the
-  ranks that own their experts and back, see ``layers/moe_ep.py``.
+  ranks that own their experts and back, see ``layers/moe_ep.py``;
+* "ETP" – data-parallel attention without EP (vllm_gcu/distributed/gcu_communicator.py:65-83,
+  113-126): the intermediate dimension of every expert is sharded over all ``dp * tp`` ranks,
+  the hidden states and router logits of every replica are gathered (all-gather-v over the
+  DP group), each rank computes its slice for all tokens, and a reduce-scatter-v over DP
+  followed by the TP all-reduce brings every replica the full sum for its own rows.
 
 ``SparseMoeBlock`` = router gate + ``FusedMoE`` (+ shared experts whose output seeds the
 result, vllm_gcu/kernels/modular_kernel.py:288-295).
@@ -32,7 +37,8 @@ from ..config import ModelConfig
 from ..ops import cuda as C
 from ..ops import ref
 from ..parallel.communicator import get_comm
-from ..parallel.state import ep_rank, ep_size, get_state, tp_rank, tp_size
+from ..parallel.state import (ep_rank, ep_size, exchange_dp_rows, get_state, tp_rank,
+                              tp_size)
 from .linear import ReplicatedLinear
 
 
@@ -72,7 +78,7 @@ def select_experts(router_logits: torch.Tensor, cfg: ModelConfig,
 
 class FusedMoE(nn.Module):
     def __init__(self, num_experts: int, hidden: int, inter: int, dtype, device,
-                 use_ep: bool, prefix: str = "", num_redundant: int = 0):
+                 use_ep: bool, prefix: str = "", num_redundant: int = 0, etp: bool = False):
         super().__init__()
         self.global_experts = num_experts + num_redundant
         self.hidden, self.inter_full = hidden, inter
@@ -83,15 +89,22 @@ class FusedMoE(nn.Module):
             self.local_experts = self.global_experts // ep
             self.expert_start = r * self.local_experts
             self.inter = inter
+            self.shard_index = 0
             emap = torch.full((self.global_experts,), -1, dtype=torch.int32)
             emap[self.expert_start:self.expert_start + self.local_experts] = torch.arange(
                 self.local_experts, dtype=torch.int32)
             self.register_buffer("expert_map", emap.to(device), persistent=False)
         else:
-            tp = tp_size()
-            assert inter % tp == 0
+            # the intermediate dimension is cut into `shards` slices: over TP, or over all
+            # dp * tp ranks in ETP mode (slice index = dp_rank * tp + tp_rank)
+            shards, self.shard_index = tp_size(), tp_rank()
+            if etp:
+                dpg = get_state().dp
+                shards, self.shard_index = dpg.world_size * tp_size(), \
+                    dpg.rank_in_group * tp_size() + tp_rank()
+            assert inter % shards == 0
             self.local_experts, self.expert_start = self.global_experts, 0
-            self.inter = inter // tp
+            self.inter = inter // shards
             self.expert_map = None
         E, I, H = self.local_experts, self.inter, hidden
         self.w13 = nn.Parameter(torch.empty(E, 2 * I, H, dtype=dtype, device=device),
@@ -147,7 +160,7 @@ class FusedMoE(nn.Module):
         if le < 0 or le >= self.local_experts:
             return False
         I = self.inter
-        lo = 0 if (self.use_ep or tp_size() == 1) else tp_rank() * I
+        lo = self.shard_index * I
         N = weight.shape[0]
         sc = torch.ones(N, dtype=torch.float32, device=weight.device) if scale is None else \
             scale.to(torch.float32).reshape(-1)
@@ -173,7 +186,7 @@ class FusedMoE(nn.Module):
         if le < 0 or le >= self.local_experts:
             return False
         I = self.inter
-        lo = 0 if (self.use_ep or tp_size() == 1) else tp_rank() * I
+        lo = self.shard_index * I
         b0, nb = lo // 128, I // 128
         if which == "gate":
             self.w13.data[le, :I].copy_(weight[lo:lo + I])
@@ -219,10 +232,7 @@ class FusedMoE(nn.Module):
         if le < 0 or le >= self.local_experts:
             return False
         I = self.inter
-        if self.use_ep or tp_size() == 1:
-            lo = 0
-        else:
-            lo = tp_rank() * I
+        lo = self.shard_index * I
         if which == "gate":
             self.w13.data[le, :I].copy_(full[lo:lo + I])
         elif which == "up":
@@ -351,8 +361,14 @@ class SparseMoeBlock(nn.Module):
         else:
             self.e_score_correction_bias = None
         num_red = int(cfg.extra.get("num_redundant_experts", 0))
+        self.dp_attention = bool(cfg.extra.get("dp_attention", False))
+        # data-parallel attention without EP: experts sharded over dp * tp
+        # (gcu_communicator.py:65-68 turns this on under the same condition)
+        self.use_etp = (self.dp_attention and not self.use_ep and st.dp.world_size > 1
+                        and bool(cfg.extra.get("etp", True)))
         self.experts = FusedMoE(cfg.num_experts, cfg.hidden_size, cfg.moe_intermediate_size,
-                                cfg.dtype, device, self.use_ep, prefix + ".experts", num_red)
+                                cfg.dtype, device, self.use_ep, prefix + ".experts", num_red,
+                                etp=self.use_etp)
         if cfg.quantization and cfg.dtype == torch.bfloat16 and cfg.extra.get("q8_experts", True):
             from .quant.moe import expert_storage
             kind = expert_storage(cfg.quantization, cfg.quant_config)
@@ -386,7 +402,6 @@ class SparseMoeBlock(nn.Module):
                                            reduce_results=False)
         else:
             self.shared_experts = None
-        self.dp_attention = bool(cfg.extra.get("dp_attention", False))
         self.dispatcher = None
         if self.use_ep and self.dp_attention:
             from .moe_ep import AllToAllDispatcher, FusedEPDispatcher
@@ -406,10 +421,34 @@ class SparseMoeBlock(nn.Module):
         else:
             raise KeyError(name)
 
+    def _forward_etp(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
+        """Gather every replica's rows, run this rank's slice of all experts over them, and
+        scatter the sums back (dispatch / combine of gcu_communicator.py:113-126 with the
+        all-gather-v manager of :22-31)."""
+        st = get_state()
+        dp = get_comm("dp")
+        # the model publishes the row counts once per forward; a block used on its own asks
+        # for them itself (every rank takes the same branch)
+        sizes = st.dp_rows if st.dp_rows is not None else exchange_dp_rows(x.shape[0])
+        xg = dp.all_gather_v(x, sizes)
+        lg = dp.all_gather_v(logits, sizes)
+        shared = self.shared_experts(x) if self.shared_experts is not None else None
+        if xg.shape[0]:
+            topk_w, topk_ids = select_experts(lg, self.cfg, self.e_score_correction_bias, None)
+            yg = self.experts(xg, topk_w, topk_ids)
+        else:
+            yg = xg
+        out = dp.reduce_scatter_v(yg, sizes)
+        if shared is not None:
+            out = out + shared
+        return get_comm("tp").all_reduce(out) if tp_size() > 1 else out
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         shape = x.shape
         x = x.reshape(-1, shape[-1])
         logits = self.gate(x)
+        if self.use_etp:
+            return self._forward_etp(x, logits).view(shape)
         topk_w, topk_ids = select_experts(logits, self.cfg, self.e_score_correction_bias,
                                           self.eplb)
         from .. import envs

@@ -298,6 +298,13 @@ class DecoderLM(nn.Module):
         fused = self._fused_tp(x) if sp_sizes is None else None
         normed = False
         ids = list(range(self.start_layer, self.end_layer))
+        if getattr(self, "_etp", None) is None:
+            self._etp = any(getattr(m, "use_etp", False) for m in self.modules())
+        if self._etp and sp_sizes is None:
+            # ETP experts gather / scatter rows over the DP group: one host exchange of the
+            # row counts per forward instead of one per layer
+            from ..parallel.state import exchange_dp_rows
+            get_state().dp_rows = exchange_dp_rows(x.shape[0])
         for j, i in enumerate(ids):
             layer = self.layers[str(i)]
             if fused is not None and layer.fusable()[0]:
@@ -312,6 +319,8 @@ class DecoderLM(nn.Module):
             else:
                 assert not normed
                 x, residual = layer(x, residual, kv_caches[j], md, sp_sizes)
+        if self._etp:
+            get_state().dp_rows = None
         if not self.is_last_stage:
             return x, residual
         if normed:

@@ -61,6 +61,9 @@ class ParallelState:
         # data-parallel attention: largest token count of any DP rank in the current step
         # (None outside a DP step); bounds the rows an expert-parallel rank can receive
         self.dp_max_tokens = None
+        # rows of the current forward on every DP rank (ETP gather / scatter sizes); set by
+        # the model for the duration of one forward
+        self.dp_rows = None
 
     def reset(self) -> None:
         self.__init__()
@@ -129,6 +132,19 @@ def init_distributed(tp: int = 1, pp: int = 1, dp: int = 1, backend: Optional[st
                                   for p in range(pp)], rank, backend, with_cpu)
     st.initialized = True
     return st
+
+
+def exchange_dp_rows(n: int) -> list[int]:
+    """Row count of every data-parallel rank for the forward that is about to run (host
+    all-gather, the counterpart of ``cu_tokens_across_dp_cpu`` in
+    vllm_gcu/patch/patch_0_9_2/forward_context.py:10-43)."""
+    dpg = _STATE.dp
+    if dpg.world_size == 1:
+        return [int(n)]
+    mine = torch.tensor([int(n)], dtype=torch.int64)
+    parts = [torch.zeros_like(mine) for _ in range(dpg.world_size)]
+    dist.all_gather(parts, mine, group=dpg.cpu_group or dpg.device_group)
+    return [int(p[0]) for p in parts]
 
 
 def destroy_distributed() -> None:
