@@ -76,6 +76,8 @@ def main():
     from vllm import LLM, SamplingParams
     from vllm.platforms import current_platform
     assert type(current_platform).__name__ == "B200Platform", type(current_platform)
+    assert current_platform.get_nixl_supported_devices() == {"cuda": ("cuda", "cpu")}
+    assert current_platform.get_nixl_memory_type() == "VRAM"
     from vllm_gcu_b200.ops import _native
 
     d = tempfile.mkdtemp(prefix="tiny_llama_cfg_")

@@ -200,3 +200,67 @@ def test_disaggregated_prefill_one_prefill_one_decode_instance():
     finally:
         cp.close()
         cd.close()
+
+
+def test_disaggregated_prefill_first_token_reuse_and_block_granular(monkeypatch):
+    """The two switches of the reference's NIXL patch: with first-token reuse the decode
+    instance computes no prompt token at all (it continues from the prefill instance's first
+    output token); with full-KV transfer off it takes whole blocks only and recomputes the
+    tail.  Both give the tokens of a single engine."""
+    import torch
+    from vllm_gcu_b200.engine.llm import LLM
+    from vllm_gcu_b200.engine.request import SamplingParams
+    kw = dict(device="cpu", max_num_seqs=4, max_num_batched_tokens=64, max_model_len=128,
+              num_gpu_blocks=64, dtype="float32", seed=0)
+    g = torch.Generator().manual_seed(11)
+    prompt = torch.randint(0, 32000, (37,), generator=g).tolist()
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    want = LLM("tiny-llama", **kw).generate([prompt], sp)[0].outputs[0].token_ids
+    monkeypatch.setenv("VLLM_B200_NIXL_ENABLE_FIRST_TOKEN_REUSE", "1")
+    pre, dec = LLM("tiny-llama", **kw), LLM("tiny-llama", **kw)
+    cp, cd = P2PKVConnector(send_type="PUT"), P2PKVConnector(send_type="PUT")
+    try:
+        pre.engine.attach_kv_connector(cp)
+        dd = dec.engine.attach_kv_connector(cd, recv_timeout_s=5.0)
+
+        def prefill(rid):
+            pre.engine.add_request(prompt, SamplingParams(max_tokens=1, temperature=0.0,
+                                                          ignore_eos=True), request_id=rid,
+                                   kv_transfer_params={"do_remote_decode": True,
+                                                       "remote": cd.addr})
+            params = None
+            while pre.engine.has_unfinished():
+                for o in pre.engine.step():
+                    if o.finished:
+                        params = o.kv_transfer_params
+            return params
+
+        def decode(rid, params, max_tokens):
+            dec.engine.add_request(list(prompt), SamplingParams(max_tokens=max_tokens,
+                                                                temperature=0.0, ignore_eos=True),
+                                   request_id=rid, kv_transfer_params=params)
+            n0 = dec.engine.stats["prefill_tokens"]
+            got = None
+            while dec.engine.has_unfinished():
+                for o in dec.engine.step():
+                    if o.finished:
+                        got = o.outputs[0].token_ids
+            return got, dec.engine.stats["prefill_tokens"] - n0
+
+        params = prefill("p-1")
+        assert params["do_remote_prefill"] and params["remote_request_id"] == "p-1"
+        assert params["first_token"] == want[0] and params["remote"] == cp.addr
+        # the first token is part of the decode instance's prompt: it produces the other five
+        got, _ = decode("d-1", params, 5)
+        assert dd.stats["injected"] == 1 and dd.stats["first_token_reused"] == 1
+        assert got == want[1:]
+        # whole blocks only: 32 of 37 prompt tokens are taken, 5 are computed again
+        monkeypatch.setenv("VLLM_B200_NIXL_ENABLE_FIRST_TOKEN_REUSE", "0")
+        monkeypatch.setenv("VLLM_B200_NIXL_ENABLE_FULL_KV_TRANSFER", "0")
+        params = prefill("p-2")
+        assert params["first_token"] is None
+        got, _ = decode("d-2", params, 6)
+        assert got == want and dd.stats["injected"] == 2
+    finally:
+        cp.close()
+        cd.close()

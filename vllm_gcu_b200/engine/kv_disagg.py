@@ -15,7 +15,20 @@ v0 ``SimpleConnector`` wiring, vllm_gcu/distributed/kv_transfer/connector.py:122
 
 Request side: ``kv_transfer_params = {"do_remote_decode": True, "remote": "host:port"}`` on
 the prefill instance; ``{"do_remote_prefill": True, "remote": ..., "remote_request_id": ...}``
-on the decode instance.
+on the decode instance.  The finished output of the prefill instance carries the parameters
+for the decode instance (``RequestOutput.kv_transfer_params``), as the reference's patched
+NIXL scheduler side does (vllm_gcu/patch/patch_0_9_2/nixl_connector.py:98-155).
+
+Two switches of that patch are kept (``VLLM_B200_NIXL_ENABLE_*``, nixl_connector.py:71-90,
+127-143):
+
+* *full KV transfer* – the KV of a partly filled last block travels too.  This connector
+  moves rows per token, so that is what it always does; with the switch off the decode
+  instance takes whole blocks only and recomputes the rest, which is the stock behaviour the
+  patch changes.
+* *first-token reuse* – the prefill instance hands its first output token over with the
+  parameters; the decode instance appends it to the prompt, takes the KV of the whole prompt
+  and starts decoding at that token: no prompt token is computed twice.
 """
 from __future__ import annotations
 
@@ -83,7 +96,15 @@ class DisaggCoordinator:
         p = req.kv_transfer_params or {}
         if not p.get("do_remote_prefill"):
             return
-        n = req.num_prompt_tokens - 1
+        from .. import envs
+        n_prompt = req.num_prompt_tokens
+        first = p.get("first_token") if envs.NIXL_ENABLE_FIRST_TOKEN_REUSE else None
+        if first is not None:
+            n = n_prompt                             # the whole prompt; next input = first token
+        else:
+            n = n_prompt - 1                         # the last prompt token gives the first output
+        if not envs.NIXL_ENABLE_FULL_KV_TRANSFER and first is None:
+            n = min(n, n_prompt // self.engine.runner.block_size * self.engine.runner.block_size)
         if n <= 0:
             return
         kv = self.connector.recv_tensor(p.get("remote_request_id", req.request_id),
@@ -92,6 +113,9 @@ class DisaggCoordinator:
         if kv is None or kv.shape[-2] < n:
             self.stats["fallback"] += 1
             return                                   # local prefill
+        if first is not None:
+            req.prompt_token_ids.append(int(first))
+            self.stats["first_token_reused"] = self.stats.get("first_token_reused", 0) + 1
         blocks = sched.kv.allocate_slots(req, n)
         if blocks is None:
             self.stats["fallback"] += 1
@@ -114,3 +138,11 @@ class DisaggCoordinator:
         self.connector.send_tensor(req.request_id, kv.cpu() if self.connector.device.type == "cpu"
                                    else kv, p.get("remote", ""))
         self.stats["sent"] += 1
+        from .. import envs
+        out = {"do_remote_prefill": True, "do_remote_decode": False,
+               "remote": getattr(self.connector, "addr", None),
+               "remote_request_id": req.request_id, "num_tokens": n,
+               "tp_size": self.engine.cfg.parallel.tensor_parallel_size, "first_token": None}
+        if envs.NIXL_ENABLE_FIRST_TOKEN_REUSE and req.output_token_ids:
+            out["first_token"] = int(req.output_token_ids[0])
+        req.kv_transfer_params_out = out

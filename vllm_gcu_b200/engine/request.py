@@ -99,6 +99,7 @@ class Request:
     lora_id: int = -1
     is_idle: bool = False                     # keep-alive request of a DP replica
     kv_transfer_params: Optional[dict] = None
+    kv_transfer_params_out: Optional[dict] = None   # prefill instance: what the decode one needs
     # multimodal inputs: embeddings of the placeholder tokens (row i belongs to prompt position
     # mm_positions[i]), M-RoPE (t, h, w) positions of the prompt ``[3, n_prompt]`` and the
     # offset added to the position of every later token
@@ -175,6 +176,7 @@ class RequestOutput:
     num_cached_tokens: int = 0
     prompt_logprobs: Optional[list] = None
     metrics: dict[str, float] = field(default_factory=dict)
+    kv_transfer_params: Optional[dict] = None       # disaggregated prefill: for the decode side
 
 
 def check_stop(req: Request, max_model_len: int) -> bool:

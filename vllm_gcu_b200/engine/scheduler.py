@@ -412,7 +412,8 @@ class Scheduler:
         comp = CompletionOutput(0, req.output_token_ids, reason,
                                 req.logprobs if req.logprobs else None, cum)
         return RequestOutput(req.request_id, req.prompt_token_ids, [comp], req.finished,
-                             req.num_cached_tokens, req.prompt_logprobs)
+                             req.num_cached_tokens, req.prompt_logprobs,
+                             kv_transfer_params=req.kv_transfer_params_out)
 
     # -- stats -------------------------------------------------------------------
     def stats(self) -> dict[str, float]:

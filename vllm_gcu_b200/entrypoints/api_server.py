@@ -224,14 +224,21 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None):
             state["tokens_out"] += len(toks)
             c = chunk(idx, toks, last.outputs[0].finish_reason)["choices"][0]
             c["prompt_tokens"] = len(ids)
+            c["kv_transfer_params"] = getattr(last, "kv_transfer_params", None)
             return c
 
         choices = await asyncio.gather(*[one(i, p) for i, p in enumerate(batch_ids)])
         usage = {"prompt_tokens": sum(c.pop("prompt_tokens") for c in choices),
                  "completion_tokens": sum(len(c["token_ids"]) for c in choices)}
         usage["total_tokens"] = usage["prompt_tokens"] + usage["completion_tokens"]
-        return {"id": rid, "object": "text_completion", "created": created, "model": model_name,
+        resp = {"id": rid, "object": "text_completion", "created": created, "model": model_name,
                 "choices": list(choices), "usage": usage}
+        kv_out = [c.pop("kv_transfer_params") for c in choices]
+        if kv_out and kv_out[0]:
+            # prefill instance of a disaggregated pair: what the proxy passes on to the decode
+            # instance (peer address, request id, first token)
+            resp["kv_transfer_params"] = kv_out[0]
+        return resp
 
     def render_chat(messages: list) -> list[int]:
         """Conversation -> prompt ids: the tokenizer's chat template when it has one, else a

@@ -66,7 +66,11 @@ environment_variables: dict[str, Callable[[], Any]] = {
     # pin every worker process to its own slice of the CPU cores (the reference's optional
     # worker affinity, vllm_gcu/worker/worker_v1.py:259-260)
     "CPU_AFFINITY": _flag("CPU_AFFINITY"),
-    "NIXL_ENABLE_FULL_KV_TRANSFER": _flag("NIXL_ENABLE_FULL_KV_TRANSFER"),
+    # disaggregated prefill (vllm_gcu/envs.py:30-36, used by patch_0_9_2/nixl_connector.py):
+    # the decode instance takes the KV of a partly filled last block too (0: whole blocks
+    # only, the rest is recomputed) ...
+    "NIXL_ENABLE_FULL_KV_TRANSFER": _flag("NIXL_ENABLE_FULL_KV_TRANSFER", "1"),
+    # ... and starts at the first output token the prefill instance already produced
     "NIXL_ENABLE_FIRST_TOKEN_REUSE": _flag("NIXL_ENABLE_FIRST_TOKEN_REUSE"),
 }
 

@@ -157,6 +157,18 @@ def _make_platform_class():
         def get_punica_wrapper(cls) -> str:
             return "vllm_gcu_b200.runtime.vllm_punica.PunicaWrapperB200"
 
+        # vLLM's NIXL connector asks the platform which KV buffer devices it can register.
+        # The reference has to allocate its KV cache as host-accessible device memory for
+        # this (vllm_gcu/worker/worker_v1.py:191-221); B200 device memory registers with
+        # NIXL / UCX as it is (GPUDirect), so the stock allocation is kept.
+        @classmethod
+        def get_nixl_supported_devices(cls) -> dict:
+            return {"cuda": ("cuda", "cpu")}
+
+        @classmethod
+        def get_nixl_memory_type(cls):
+            return "VRAM"
+
         @classmethod
         def get_attn_backend_cls(cls, selected_backend, attn_selector_config, num_heads=None
                                  ) -> str:
