@@ -71,12 +71,72 @@ def test_baichuan2_w_pack_and_normalised_head():
         sd[p + "W_pack.weight"] = torch.cat([sd.pop(p + "q_proj.weight"), sd.pop(p + "k_proj.weight"),
                                              sd.pop(p + "v_proj.weight")], 0)
     d = cfg.to_dict()
+    d["position_embedding"] = "ROPE"     # a 7B checkpoint (hidden size 4096) selects this itself
     got, tok = _engine_logits("BaichuanForCausalLM", d, sd.items())
     with torch.inference_mode():
         h = hf.model(input_ids=torch.tensor([IDS])).last_hidden_state[0, -1]
         want = torch.nn.functional.normalize(hf.lm_head.weight) @ h
     assert torch.allclose(got, want, atol=2e-4), (got - want).abs().max()
     assert tok == int(want.argmax())
+
+
+def test_baichuan_13b_alibi_positions():
+    """Baichuan 13B: no rotary embedding, ALiBi biases slope_h * (j - i) on the scores.  The
+    oracle is the dense mathematics written out here on the weights of a tiny Llama; the engine
+    runs it through the paged KV cache, chunked (prefill of 8 tokens, then the rest)."""
+    from vllm_gcu_b200.layers.attention import alibi_slopes
+    cfg, hf = _tiny_llama(vocab=300, kv=4)
+    sd = dict(hf.state_dict())
+    for i in range(2):
+        p = f"model.layers.{i}.self_attn."
+        sd[p + "W_pack.weight"] = torch.cat([sd[p + "q_proj.weight"], sd[p + "k_proj.weight"],
+                                             sd[p + "v_proj.weight"]], 0)
+    d = cfg.to_dict()
+    d["architectures"] = ["BaichuanForCausalLM"]     # hidden size != 4096: the ALiBi variant
+    mc = ModelConfig.from_hf_dict(d, dtype=torch.float32)
+    llm = LLM(mc, device="cpu", max_num_seqs=2, max_num_batched_tokens=8, max_model_len=64,
+              num_gpu_blocks=16, load_format="none")
+    assert llm.engine.model.layers["0"].self_attn.attn.alibi is not None
+    assert llm.engine.model.layers["0"].self_attn.attn.rotary is None
+    llm.engine.model.load_weights((k, v) for k, v in sd.items()
+                                  if not k.endswith(("q_proj.weight", "k_proj.weight",
+                                                     "v_proj.weight")))
+    llm.engine.runner.keep_logits = True
+    out = llm.generate([IDS], SamplingParams(max_tokens=3, temperature=0.0, ignore_eos=True))
+    toks = out[0].outputs[0].token_ids
+
+    def rms(x, w):
+        return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6) * w
+
+    def dense(ids):
+        n, H, D = len(ids), 4, 16
+        x = sd["model.embed_tokens.weight"][torch.tensor(ids)]
+        pos = torch.arange(n)
+        bias = alibi_slopes(H)[:, None, None] * (pos[None, :] - pos[:, None]).float()[None]
+        causal = pos[None, :] <= pos[:, None]
+        for i in range(2):
+            p = f"model.layers.{i}."
+            h = rms(x, sd[p + "input_layernorm.weight"])
+            q = (h @ sd[p + "self_attn.q_proj.weight"].t()).view(n, H, D).transpose(0, 1)
+            k = (h @ sd[p + "self_attn.k_proj.weight"].t()).view(n, H, D).transpose(0, 1)
+            v = (h @ sd[p + "self_attn.v_proj.weight"].t()).view(n, H, D).transpose(0, 1)
+            s_ = q @ k.transpose(1, 2) * D ** -0.5 + bias
+            s_ = s_.masked_fill(~causal[None], float("-inf"))
+            a = (torch.softmax(s_, -1) @ v).transpose(0, 1).reshape(n, H * D)
+            x = x + a @ sd[p + "self_attn.o_proj.weight"].t()
+            h = rms(x, sd[p + "post_attention_layernorm.weight"])
+            g = torch.nn.functional.silu(h @ sd[p + "mlp.gate_proj.weight"].t())
+            x = x + (g * (h @ sd[p + "mlp.up_proj.weight"].t())) @ sd[p + "mlp.down_proj.weight"].t()
+        return rms(x, sd["model.norm.weight"])[-1] @ sd["lm_head.weight"].t()
+
+    seq = list(IDS)
+    with torch.inference_mode():
+        for t in toks:
+            want = dense(seq)
+            assert t == int(want.argmax())
+            seq.append(t)
+    got = llm.engine.runner.last_logits[0]
+    assert torch.allclose(got, want, atol=2e-4), (got - want).abs().max()
 
 
 def test_gemma_matches_transformers():

@@ -238,6 +238,44 @@ def test_varlen_prefill(C, Hq, Hkv, D):
     _close(lse, lse_r, 1e-2, 1e-2)
 
 
+@pytest.mark.parametrize("Hq,Hkv,D", [(8, 8, 128), (12, 4, 64)])
+def test_alibi_decode_and_prefill(C, Hq, Hkv, D):
+    """ALiBi slopes in the decode kernel (with and without KV splits) and in the prefill kernel
+    (cached prefixes, causal): slope * (key position - query position) added to the scores."""
+    from vllm_gcu_b200.layers.attention import alibi_slopes
+    torch.manual_seed(23)
+    slopes = alibi_slopes(Hq).cuda()
+    assert slopes.shape == (Hq,) and float(slopes[0]) == pytest.approx(2.0 ** (-8.0 / 8), rel=1e-6)
+    lens = [1, 17, 64, 65, 300, 1000, 33]
+    B = len(lens)
+    kc, vc, bt = _make_paged(B, lens, Hkv, D, 16)
+    q = torch.randn(B, Hq, D, device="cuda", dtype=torch.bfloat16)
+    sl = torch.tensor(lens, device="cuda", dtype=torch.int32)
+    scale = D ** -0.5
+    want = ref.paged_attention_decode(q, kc, vc, bt, sl, scale, alibi_slopes=slopes)
+    plain = ref.paged_attention_decode(q, kc, vc, bt, sl, scale)
+    assert (want.float() - plain.float()).abs().max() > 0.05     # the bias matters here
+    for splits in (1, 4):
+        got = C.paged_decode(q, kc, vc, bt, sl, scale, num_splits=splits, alibi_slopes=slopes)
+        _close(got, want, 2e-2, 2e-2)
+    q_lens = [5, 64, 130, 1, 77]
+    ctx = [0, 16, 50, 200, 3]
+    lens = [a + b for a, b in zip(q_lens, ctx)]
+    kc, vc, bt = _make_paged(len(lens), lens, Hkv, D, 16)
+    T = sum(q_lens)
+    q = torch.randn(T, Hq, D, device="cuda", dtype=torch.bfloat16)
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), device="cuda",
+                      dtype=torch.int32)
+    sl = torch.tensor(lens, device="cuda", dtype=torch.int32)
+    tiles = sum((x + 63) // 64 for x in q_lens)
+    got, lse = C.varlen_prefill(q, kc, vc, bt, cu, sl, scale, tiles, return_lse=True,
+                                alibi_slopes=slopes)
+    want, lse_r = ref.varlen_prefill_attention(q, kc, vc, bt, cu, sl, scale, return_lse=True,
+                                               alibi_slopes=slopes)
+    _close(got, want, 2e-2, 2e-2)
+    _close(lse, lse_r, 1e-2, 1e-2)
+
+
 @pytest.mark.parametrize("Hq,Hkv", [(8, 2), (4, 4), (8, 1)])
 @pytest.mark.parametrize("window", [0, 100])
 def test_fmha_prefill_tcgen05(C, Hq, Hkv, window):

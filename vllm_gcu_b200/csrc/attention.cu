@@ -152,6 +152,7 @@ struct DecodeArgs {
   long long ldq, ldo;
   int B, Hq, Hkv, num_splits;
   float scale;
+  const float* alibi;   // optional [Hq] slopes: score += slope * (key position - query position)
 };
 
 template <typename T, int HD>
@@ -209,6 +210,12 @@ __global__ void __launch_bounds__(kThreads) paged_decode_kernel(const DecodeArgs
   float m_run[2] = {-INFINITY, -INFINITY};
   float l_run[2] = {0.0f, 0.0f};
   const float sl2 = a.scale * kLog2e;
+  // ALiBi: the query sits at position seq_len - 1 (log2 domain like the scores)
+  float al[2] = {0.0f, 0.0f};
+  if (a.alibi != nullptr) {
+    if (g < G) al[0] = a.alibi[kvh * G + g] * kLog2e;
+    if (g + 8 < G) al[1] = a.alibi[kvh * G + g + 8] * kLog2e;
+  }
 
   const int ntiles = (end - start + kTile - 1) / kTile;
   load_kv_tile<T, HD>(stage[0], stage[0] + kTile * kStride, a.kv, b, kvh, start, end);
@@ -248,7 +255,9 @@ __global__ void __launch_bounds__(kThreads) paged_decode_kernel(const DecodeArgs
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int tok = tok0 + j * 8 + 2 * tig + (e & 1);
-          const float v = (tok < end) ? s[j][e] * sl2 : -INFINITY;
+          const float v = (tok < end)
+                              ? s[j][e] * sl2 + al[e >> 1] * static_cast<float>(tok - (seq_len - 1))
+                              : -INFINITY;
           s[j][e] = v;
           mx[e >> 1] = fmaxf(mx[e >> 1], v);
         }
@@ -382,6 +391,7 @@ struct PrefillArgs {
   int causal;
   int window;             // sliding window (<= 0: none)
   float scale;
+  const float* alibi;     // optional [Hq] slopes, see DecodeArgs
 };
 
 template <typename T, int HD>
@@ -445,6 +455,7 @@ __global__ void __launch_bounds__(kThreads) varlen_prefill_kernel(const PrefillA
   float m_run[2] = {-INFINITY, -INFINITY};
   float l_run[2] = {0.0f, 0.0f};
   const float sl2 = a.scale * kLog2e;
+  const float al = a.alibi != nullptr ? a.alibi[head] * kLog2e : 0.0f;
 
   // keys this CTA can see
   const int last_row = min(q_len, s_qt * kQTile + kQTile) - 1;
@@ -494,7 +505,7 @@ __global__ void __launch_bounds__(kThreads) varlen_prefill_kernel(const PrefillA
           bool ok = tok < kv_end;
           if (a.causal) ok = ok && tok <= pos;
           if (a.window > 0) ok = ok && tok > pos - a.window;
-          const float v = ok ? s[j][e] * sl2 : -INFINITY;
+          const float v = ok ? s[j][e] * sl2 + al * static_cast<float>(tok - pos) : -INFINITY;
           s[j][e] = v;
           mx[e >> 1] = fmaxf(mx[e >> 1], v);
         }
@@ -666,7 +677,7 @@ static int paged_decode_impl(const void* q, long long ldq, void* out, long long 
                              const int* seq_lens, float* tmp_out, float* tmp_lse,
                              int num_splits, int B, int Hq, int Hkv, int HD, float scale,
                              int dtype, int qmode, float k_scale, float v_scale, float k_zp,
-                             float v_zp, void* stream) {
+                             float v_zp, void* stream, const float* alibi = nullptr) {
   if (B <= 0) return 0;
   if (Hkv <= 0 || Hq % Hkv != 0 || Hq / Hkv > 16) return -2;
   if (num_splits < 1) return -2;
@@ -680,6 +691,7 @@ static int paged_decode_impl(const void* q, long long ldq, void* out, long long 
   a.kv.k_zp = k_zp; a.kv.v_zp = v_zp;
   a.ldq = ldq; a.ldo = ldo; a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.num_splits = num_splits;
   a.scale = scale;
+  a.alibi = alibi;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 #define B200_DEC(TT, H) return launch_decode<TT, H>(a, s)
   if (dtype == 0) {
@@ -706,6 +718,24 @@ B200_API int b200_paged_decode(const void* q, long long ldq, void* out, long lon
                            block_tables, max_blocks, block_size, seq_lens, tmp_out, tmp_lse,
                            num_splits, B, Hq, Hkv, HD, scale, dtype, 0, 1.0f, 1.0f, 0.0f, 0.0f,
                            stream);
+}
+
+// Decode attention with ALiBi position biases: `alibi` holds one fp32 slope per query head and
+// slope * (key position - query position) is added to every score before the softmax (the
+// `alibi_slopes` operand of the reference's paged_attention_v1,
+// vllm_gcu/attention/ops/paged_attn.py:78-162).  A null `alibi` is plain attention.
+B200_API int b200_paged_decode_alibi(const void* q, long long ldq, void* out, long long ldo,
+                                     const void* k_cache, const void* v_cache,
+                                     long long slot_stride, long long head_stride,
+                                     long long num_slots, const int* block_tables, int max_blocks,
+                                     int block_size, const int* seq_lens, float* tmp_out,
+                                     float* tmp_lse, int num_splits, int B, int Hq, int Hkv,
+                                     int HD, float scale, int dtype, const float* alibi,
+                                     void* stream) {
+  return paged_decode_impl(q, ldq, out, ldo, k_cache, v_cache, slot_stride, head_stride, num_slots,
+                           block_tables, max_blocks, block_size, seq_lens, tmp_out, tmp_lse,
+                           num_splits, B, Hq, Hkv, HD, scale, dtype, 0, 1.0f, 1.0f, 0.0f, 0.0f,
+                           stream, alibi);
 }
 
 // Decode attention over an 8-bit KV cache (same layout, one byte per element; slot_stride and
@@ -758,7 +788,8 @@ static int varlen_prefill_impl(const void* q, long long ldq, void* out, long lon
                                const int* block_tables, int max_blocks, int block_size, int B,
                                int T, int num_q_tiles, int Hq, int Hkv, int HD, float scale,
                                int causal, int window, int dtype, int qmode, float k_scale,
-                               float v_scale, float k_zp, float v_zp, void* stream) {
+                               float v_scale, float k_zp, float v_zp, void* stream,
+                               const float* alibi = nullptr) {
   if (B <= 0 || T <= 0 || num_q_tiles <= 0) return 0;
   if (Hkv <= 0 || Hq % Hkv != 0) return -2;
   PrefillArgs a;
@@ -770,6 +801,7 @@ static int varlen_prefill_impl(const void* q, long long ldq, void* out, long lon
   a.kv.k_zp = k_zp; a.kv.v_zp = v_zp;
   a.ldq = ldq; a.ldo = ldo; a.B = B; a.T = T; a.Hq = Hq; a.Hkv = Hkv; a.causal = causal;
   a.window = window; a.scale = scale;
+  a.alibi = alibi;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 #define B200_PRE(TT, H) return launch_prefill<TT, H>(a, num_q_tiles, s)
   if (dtype == 0) {
@@ -794,6 +826,24 @@ B200_API int b200_varlen_prefill(const void* q, long long ldq, void* out, long l
                              head_stride, num_slots, block_tables, max_blocks, block_size, B, T,
                              num_q_tiles, Hq, Hkv, HD, scale, causal, window, dtype, 0, 1.0f, 1.0f,
                              0.0f, 0.0f, stream);
+}
+
+// Prefill attention with ALiBi position biases (context_attention_forward with alibi slopes
+// and memory_efficient_attention_alibi of the reference, vllm_gcu/attention/ops/paged_attn.py:
+// 195-210); see b200_paged_decode_alibi.
+B200_API int b200_varlen_prefill_alibi(const void* q, long long ldq, void* out, long long ldo,
+                                       float* lse, const int* cu_q, const int* seq_lens,
+                                       const void* k_cache, const void* v_cache,
+                                       long long slot_stride, long long head_stride,
+                                       long long num_slots, const int* block_tables,
+                                       int max_blocks, int block_size, int B, int T,
+                                       int num_q_tiles, int Hq, int Hkv, int HD, float scale,
+                                       int causal, int window, int dtype, const float* alibi,
+                                       void* stream) {
+  return varlen_prefill_impl(q, ldq, out, ldo, lse, cu_q, seq_lens, k_cache, v_cache, slot_stride,
+                             head_stride, num_slots, block_tables, max_blocks, block_size, B, T,
+                             num_q_tiles, Hq, Hkv, HD, scale, causal, window, dtype, 0, 1.0f, 1.0f,
+                             0.0f, 0.0f, stream, alibi);
 }
 
 // Prefill attention over an 8-bit KV cache; see b200_paged_decode_q8kv for qmode and scales.

@@ -102,11 +102,33 @@ def allocate_kv_cache(num_layers: int, num_blocks: int, block_size: int, kv_head
             for _ in range(num_layers)]
 
 
+def alibi_slopes(num_heads: int) -> torch.Tensor:
+    """ALiBi slopes of all heads, fp32 ``[num_heads]``: a geometric sequence 2^(-8 i / n) for the
+    largest power of two n <= num_heads, then every other term of the sequence for 2n (the
+    published recipe; Baichuan-13B, BLOOM and MPT checkpoints assume it)."""
+    import math
+    n = 2 ** math.floor(math.log2(num_heads))
+    base = 2.0 ** (-(2.0 ** -(math.log2(n) - 3)))
+    slopes = torch.pow(torch.tensor(base, dtype=torch.float32), torch.arange(1, n + 1))
+    if n != num_heads:
+        extra_base = 2.0 ** (-(2.0 ** -(math.log2(2 * n) - 3)))
+        rem = min(n, num_heads - n)
+        extra = torch.pow(torch.tensor(extra_base, dtype=torch.float32),
+                          torch.arange(1, 1 + 2 * rem, 2))
+        slopes = torch.cat([slopes, extra])
+    return slopes.float()
+
+
 class PagedAttention(nn.Module):
     def __init__(self, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                  rotary: Optional[RotaryEmbedding], q_norm: Optional[RMSNorm] = None,
-                 k_norm: Optional[RMSNorm] = None, sliding_window: int = 0):
+                 k_norm: Optional[RMSNorm] = None, sliding_window: int = 0,
+                 alibi: Optional[torch.Tensor] = None):
         super().__init__()
+        # ALiBi slopes of this rank's heads (fp32 [num_heads]); the kernels add
+        # slope * (key position - query position) to the scores
+        # (vllm_gcu/attention/ops/paged_attn.py:78-162 passes them to both attention ops)
+        self.register_buffer("alibi", alibi, persistent=False)
         self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
         self.scale = scale
         self.rotary = rotary
@@ -178,7 +200,8 @@ class PagedAttention(nn.Module):
                            k_cache, v_cache, ks_t, vs_t)
         out = torch.empty((T, Hq * D), dtype=q.dtype, device=q.device)
         nd = md.num_decode_tokens
-        if md.common_prefix_len > 0 and kvq is None and D in (64, 128) and not self.window:
+        if (md.common_prefix_len > 0 and kvq is None and D in (64, 128) and not self.window
+                and self.alibi is None):
             B = md.num_decodes + md.num_prefills
             n_real = sum(md.q_lens_cpu[:B])
             o = cascade_attention(q[:n_real].view(n_real, Hq, D), k_cache, v_cache,
@@ -190,14 +213,15 @@ class PagedAttention(nn.Module):
             C.paged_decode(q[:nd].view(nd, Hq, D), k_cache, v_cache, md.block_tables[:nd],
                            md.seq_lens[:nd], self.scale, out=out[:nd].view(nd, Hq, D),
                            num_splits=md.decode_splits, workspace=md.decode_workspace,
-                           kv_quant=kvq)
+                           kv_quant=kvq, alibi_slopes=self.alibi)
         if md.num_prefills > 0 and D not in (64, 128) and kvq is None:
             # head sizes the prefill kernels do not cover (Gemma-7B: 256): torch formulation
             npf = T - nd
             sl = slice(md.num_decodes, md.num_decodes + md.num_prefills)
             o = ref.varlen_prefill_attention(q[nd:].view(npf, Hq, D), k_cache, v_cache,
                                              md.block_tables[sl], md.cu_q_prefill,
-                                             md.seq_lens[sl], self.scale, window=self.window)
+                                             md.seq_lens[sl], self.scale, window=self.window,
+                                             alibi_slopes=self.alibi)
             out[nd:] = o.reshape(npf, Hq * D)
         elif md.num_prefills > 0:
             npf = T - nd
@@ -207,7 +231,7 @@ class PagedAttention(nn.Module):
                              md.seq_lens[md.num_decodes:md.num_decodes + md.num_prefills],
                              self.scale, md.num_q_tiles, out=out[nd:].view(npf, Hq, D),
                              window=self.window, num_q_tiles_128=md.num_q_tiles_128,
-                             kv_quant=kvq)
+                             kv_quant=kvq, alibi_slopes=self.alibi)
         return out
 
     # -- CPU reference ----------------------------------------------------------
@@ -228,7 +252,7 @@ class PagedAttention(nn.Module):
         cu[1:] = torch.tensor(q_lens, dtype=torch.int32).cumsum(0)
         n_real = int(cu[-1])
         out = torch.zeros((T, Hq * D), dtype=q.dtype, device=q.device)
-        if md.common_prefix_len > 0 and not self.window:
+        if md.common_prefix_len > 0 and not self.window and self.alibi is None:
             o = cascade_attention(q[:n_real].reshape(n_real, Hq, D), k_cache, v_cache,
                                   md.block_tables[:B], cu, md.seq_lens[:B], self.scale,
                                   md.common_prefix_len, q_lens, native=False)
@@ -236,6 +260,6 @@ class PagedAttention(nn.Module):
             return out
         o = ref.varlen_prefill_attention(q[:n_real].reshape(n_real, Hq, D), k_cache, v_cache,
                                          md.block_tables[:B], cu, md.seq_lens[:B], self.scale,
-                                         window=self.window)
+                                         window=self.window, alibi_slopes=self.alibi)
         out[:n_real] = o.reshape(n_real, Hq * D)
         return out

@@ -19,7 +19,7 @@ from ..config import ModelConfig
 from ..layers.attention import AttentionMetadata, PagedAttention
 from ..layers.basic import ParallelLMHead, RMSNorm, RotaryEmbedding, VocabParallelEmbedding
 from ..layers.linear import (MergedColumnParallelLinear, QKVParallelLinear, RowParallelLinear)
-from ..parallel.state import get_state, tp_size
+from ..parallel.state import get_state, tp_rank, tp_size
 
 
 def get_linear_method(cfg: ModelConfig, prefix: str):
@@ -90,15 +90,25 @@ class GQAAttention(nn.Module):
             cfg.num_attention_heads * D, cfg.hidden_size, bias=False, dtype=cfg.dtype,
             device=device, quant_method=get_linear_method(cfg, prefix + ".o_proj"),
             prefix=prefix + ".o_proj")
-        rotary = RotaryEmbedding(D, cfg.rotary_dim, cfg.max_position_embeddings, cfg.rope_theta,
-                                 cfg.rope_is_neox, cfg.rope_scaling, cfg.dtype, device)
+        alibi = None
+        if str(cfg.extra.get("position_embedding", "ROPE")).upper() == "ALIBI":
+            # linear position biases instead of rotary embeddings; heads are sharded over TP
+            from ..layers.attention import alibi_slopes
+            nh = self.qkv_proj.num_heads
+            alibi = alibi_slopes(cfg.num_attention_heads)[tp_rank() * nh:(tp_rank() + 1) * nh] \
+                .contiguous().to(device)
+            rotary = None
+        else:
+            rotary = RotaryEmbedding(D, cfg.rotary_dim, cfg.max_position_embeddings,
+                                     cfg.rope_theta, cfg.rope_is_neox, cfg.rope_scaling,
+                                     cfg.dtype, device)
         qn = kn = None
         if cfg.qk_norm:
             qn = RMSNorm(D, cfg.rms_norm_eps, cfg.dtype, device)
             kn = RMSNorm(D, cfg.rms_norm_eps, cfg.dtype, device)
         self.q_norm, self.k_norm = qn, kn
         self.attn = PagedAttention(self.qkv_proj.num_heads, self.qkv_proj.num_kv_heads, D,
-                                   D ** -0.5, rotary, qn, kn, cfg.sliding_window)
+                                   D ** -0.5, rotary, qn, kn, cfg.sliding_window, alibi)
 
     def before_o_proj(self, x: torch.Tensor, kv_cache: torch.Tensor, md: AttentionMetadata
                       ) -> torch.Tensor:

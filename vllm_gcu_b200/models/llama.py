@@ -81,13 +81,16 @@ class InternLM2ForCausalLM(DecoderLM):
 
 
 class BaichuanForCausalLM(DecoderLM):
-    """Baichuan / Baichuan2 7B (rotary positions): q, k, v packed in ``W_pack``; Baichuan2
-    normalises the rows of the LM head (its ``NormHead``), which is done once at load.  The
-    13B variants use ALiBi and are rejected."""
+    """Baichuan / Baichuan2: q, k, v packed in ``W_pack``; Baichuan2 normalises the rows of the
+    LM head (its ``NormHead``), which is done once at load.  The 7B models use rotary
+    positions; the 13B models (architecture ``BaichuanForCausalLM`` with a hidden size other
+    than 4096) use ALiBi position biases, which the attention kernels take as per-head slopes."""
 
     def __init__(self, cfg: ModelConfig, device="cpu"):
-        if cfg.hidden_size > 4096 and cfg.extra.get("position_embedding", "ROPE") != "ROPE":
-            raise ValueError("Baichuan 13B (ALiBi positions) is not supported")
+        if "position_embedding" not in cfg.extra:
+            alibi = cfg.architecture == "BaichuanForCausalLM" and cfg.hidden_size != 4096
+            cfg = dataclasses.replace(cfg, extra={**cfg.extra, "position_embedding":
+                                                  "ALIBI" if alibi else "ROPE"})
         super().__init__(cfg, device)
 
     def load_special(self, name, tensor, owners) -> bool:

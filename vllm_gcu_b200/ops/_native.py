@@ -93,6 +93,10 @@ class _Sigs:
     b200_swap_blocks = [P, P, P, I, L, P]
     b200_decode_num_splits = [I, I, I]
     b200_paged_decode = [P, L, P, L, P, P, L, L, L, P, I, I, P, P, P, I, I, I, I, I, F, I, P]
+    b200_paged_decode_alibi = [P, L, P, L, P, P, L, L, L, P, I, I, P, P, P, I, I, I, I, I, F, I, P,
+                               P]
+    b200_varlen_prefill_alibi = [P, L, P, L, P, P, P, P, P, L, L, L, P, I, I, I, I, I, I, I, I, F,
+                                 I, I, I, P, P]
     b200_paged_decode_q8kv = [P, L, P, L, P, P, L, L, L, P, I, I, P, P, P, I, I, I, I, I, F, I,
                               I, F, F, F, F, P]
     b200_varlen_prefill_q8kv = [P, L, P, L, P, P, P, P, P, L, L, L, P, I, I, I, I, I, I, I, I, F,

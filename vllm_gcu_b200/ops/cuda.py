@@ -377,10 +377,11 @@ def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                  block_tables: torch.Tensor, seq_lens: torch.Tensor, scale: float,
                  out: Optional[torch.Tensor] = None, num_splits: int = 0,
                  workspace: Optional[tuple[torch.Tensor, torch.Tensor]] = None,
-                 max_seq_len: int = 0, kv_quant: Optional[tuple] = None) -> torch.Tensor:
+                 max_seq_len: int = 0, kv_quant: Optional[tuple] = None,
+                 alibi_slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
     res = _paged_decode(q, k_cache, v_cache, block_tables, seq_lens, scale, out, num_splits,
-                        workspace, max_seq_len, kv_quant)
-    if (oracle_enabled("paged_decode") and k_cache.element_size() > 1
+                        workspace, max_seq_len, kv_quant, alibi_slopes)
+    if (oracle_enabled("paged_decode") and k_cache.element_size() > 1 and alibi_slopes is None
             and not torch.cuda.is_current_stream_capturing()):
         from . import ref
         live = seq_lens > 0
@@ -394,9 +395,12 @@ def _paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                   block_tables: torch.Tensor, seq_lens: torch.Tensor, scale: float,
                   out: Optional[torch.Tensor] = None, num_splits: int = 0,
                   workspace: Optional[tuple[torch.Tensor, torch.Tensor]] = None,
-                  max_seq_len: int = 0, kv_quant: Optional[tuple] = None) -> torch.Tensor:
+                  max_seq_len: int = 0, kv_quant: Optional[tuple] = None,
+                  alibi_slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
     """q ``[B, Hq, D]`` (row stride free), caches ``[blocks, bs, Hkv, D]``.  For fp8 / int8
-    caches ``kv_quant = (k_scale, v_scale, k_zero_point, v_zero_point)`` (floats)."""
+    caches ``kv_quant = (k_scale, v_scale, k_zero_point, v_zero_point)`` (floats).
+    ``alibi_slopes`` fp32 ``[Hq]`` adds slope * (key position - query position) to the scores
+    (bf16 / fp16 caches)."""
     B, Hq, D = q.shape
     nb, bs, Hkv, _ = k_cache.shape
     assert q.stride(2) == 1 and q.stride(1) == D
@@ -417,6 +421,12 @@ def _paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
             ptr(v_cache), k_cache.stride(1), k_cache.stride(2), nb * bs, ptr(block_tables),
             block_tables.stride(0), bs, ptr(seq_lens), ptr(tmp_out), ptr(tmp_lse), num_splits,
             B, Hq, Hkv, D, float(scale), DTYPE_CODE[q.dtype], stream_ptr())
+    if alibi_slopes is not None:
+        if k_cache.element_size() == 1:
+            raise NotImplementedError("ALiBi attention over an 8-bit KV cache")
+        assert alibi_slopes.dtype == torch.float32 and alibi_slopes.numel() == Hq
+        call("b200_paged_decode_alibi", *args[:-1], ptr(alibi_slopes), stream_ptr())
+        return out
     if k_cache.element_size() == 1:
         ks, vs, kz, vz = kv_quant or (1.0, 1.0, 0.0, 0.0)
         call("b200_paged_decode_q8kv", *args[:-1], 1 if k_cache.dtype == FP8 else 2, float(ks),
@@ -441,10 +451,13 @@ def varlen_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor
                    block_tables: torch.Tensor, cu_q: torch.Tensor, seq_lens: torch.Tensor,
                    scale: float, num_q_tiles: int, out: Optional[torch.Tensor] = None,
                    causal: bool = True, window: int = 0, return_lse: bool = False,
-                   num_q_tiles_128: Optional[int] = None, kv_quant: Optional[tuple] = None):
+                   num_q_tiles_128: Optional[int] = None, kv_quant: Optional[tuple] = None,
+                   alibi_slopes: Optional[torch.Tensor] = None):
     res = _varlen_prefill(q, k_cache, v_cache, block_tables, cu_q, seq_lens, scale, num_q_tiles,
-                          out, causal, window, return_lse, num_q_tiles_128, kv_quant)
-    if oracle_enabled("varlen_prefill") and k_cache.element_size() > 1 and causal:
+                          out, causal, window, return_lse, num_q_tiles_128, kv_quant,
+                          alibi_slopes)
+    if (oracle_enabled("varlen_prefill") and k_cache.element_size() > 1 and causal
+            and alibi_slopes is None):
         from . import ref
         want = ref.varlen_prefill_attention(q, k_cache, v_cache, block_tables, cu_q, seq_lens,
                                             scale, window=window)
@@ -456,15 +469,27 @@ def _varlen_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                     block_tables: torch.Tensor, cu_q: torch.Tensor, seq_lens: torch.Tensor,
                     scale: float, num_q_tiles: int, out: Optional[torch.Tensor] = None,
                     causal: bool = True, window: int = 0, return_lse: bool = False,
-                    num_q_tiles_128: Optional[int] = None, kv_quant: Optional[tuple] = None):
+                    num_q_tiles_128: Optional[int] = None, kv_quant: Optional[tuple] = None,
+                    alibi_slopes: Optional[torch.Tensor] = None):
     """q ``[T, Hq, D]``; ``num_q_tiles`` >= sum_b ceil(q_len_b / 64) (host-known);
-    ``num_q_tiles_128`` the same for 128-row tiles (defaults to the 64-row bound)."""
+    ``num_q_tiles_128`` the same for 128-row tiles (defaults to the 64-row bound).
+    ``alibi_slopes``: see ``paged_decode``."""
     T, Hq, D = q.shape
     nb, bs, Hkv, _ = k_cache.shape
     assert q.stride(2) == 1 and q.stride(1) == D
     if out is None:
         out = torch.empty((T, Hq, D), device=q.device, dtype=q.dtype)
     lse = torch.empty((Hq, T), device=q.device, dtype=torch.float32) if return_lse else None
+    if alibi_slopes is not None:
+        if k_cache.element_size() == 1:
+            raise NotImplementedError("ALiBi attention over an 8-bit KV cache")
+        assert alibi_slopes.dtype == torch.float32 and alibi_slopes.numel() == Hq
+        call("b200_varlen_prefill_alibi", ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(lse),
+             ptr(cu_q), ptr(seq_lens), ptr(k_cache), ptr(v_cache), k_cache.stride(1),
+             k_cache.stride(2), nb * bs, ptr(block_tables), block_tables.stride(0), bs,
+             block_tables.shape[0], T, num_q_tiles, Hq, Hkv, D, float(scale), int(causal),
+             int(window), DTYPE_CODE[q.dtype], ptr(alibi_slopes), stream_ptr())
+        return (out, lse) if return_lse else out
     if k_cache.element_size() == 1:
         ks, vs, kz, vz = kv_quant or (1.0, 1.0, 0.0, 0.0)
         call("b200_varlen_prefill_q8kv", ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(lse),

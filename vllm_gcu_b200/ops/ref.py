@@ -362,10 +362,11 @@ def _gather_kv(k_cache: torch.Tensor, v_cache: torch.Tensor, block_table_row: to
 
 def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                            block_tables: torch.Tensor, seq_lens: torch.Tensor, scale: float,
-                           k_scale=None, v_scale=None) -> torch.Tensor:
+                           k_scale=None, v_scale=None, alibi_slopes=None) -> torch.Tensor:
     """One query token per sequence; q ``[B, Hq, D]``; flash-layout caches
     (csrc/src/paged_attention_v1.cpp:68 semantics on the layout of
-    csrc/src/reshape_and_cache_flash.cpp)."""
+    csrc/src/reshape_and_cache_flash.cpp).  ``alibi_slopes`` fp32 ``[Hq]``: slope times
+    (key position - query position) is added to the scores."""
     B, Hq, D = q.shape
     Hkv = k_cache.shape[2]
     G = Hq // Hkv
@@ -378,6 +379,9 @@ def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
         k = k.repeat_interleave(G, dim=1)
         v = v.repeat_interleave(G, dim=1)
         s = torch.einsum("hd,nhd->hn", q[b].float(), k) * scale
+        if alibi_slopes is not None:
+            rel = torch.arange(n, device=q.device, dtype=torch.float32) - (n - 1)
+            s = s + alibi_slopes.float()[:, None] * rel[None, :]
         p = torch.softmax(s, dim=-1)
         out[b] = torch.einsum("hn,nhd->hd", p, v).to(q.dtype)
     return out
@@ -386,7 +390,7 @@ def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
 def varlen_prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                              block_tables: torch.Tensor, cu_q: torch.Tensor,
                              seq_lens: torch.Tensor, scale: float, causal: bool = True,
-                             window: int = 0, return_lse: bool = False):
+                             window: int = 0, return_lse: bool = False, alibi_slopes=None):
     """Attention of the new tokens of each sequence (``cu_q`` offsets into q
     ``[T, Hq, D]``) over all ``seq_lens[b]`` cached tokens, causal with respect to
     absolute positions (csrc/src/context_attention_forward.cpp:49)."""
@@ -407,6 +411,8 @@ def varlen_prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: to
         s = torch.einsum("qhd,nhd->hqn", q[q0:q1].float(), k) * scale
         qpos = torch.arange(n - ql, n, device=q.device)[:, None]
         kpos = torch.arange(n, device=q.device)[None, :]
+        if alibi_slopes is not None:
+            s = s + alibi_slopes.float()[:, None, None] * (kpos - qpos).float()[None]
         mask = torch.ones(ql, n, dtype=torch.bool, device=q.device)
         if causal:
             mask &= kpos <= qpos

@@ -165,9 +165,12 @@ class B200AttentionImpl(AttentionImpl[B200AttentionMetadata]):
                  logits_soft_cap: Optional[float] = None,
                  attn_type: str = AttentionType.DECODER,
                  kv_sharing_target_layer_name: Optional[str] = None, **kw) -> None:
-        if alibi_slopes is not None or logits_soft_cap:
-            raise NotImplementedError("ALiBi slopes / logit soft caps are not supported by the "
-                                      "B200 attention backend")
+        if logits_soft_cap:
+            raise NotImplementedError("logit soft caps are not supported by the B200 attention "
+                                      "backend")
+        # ALiBi slopes (one per head of this rank) go to the kernels as an fp32 vector
+        self.alibi = None if alibi_slopes is None else \
+            torch.as_tensor(alibi_slopes, dtype=torch.float32)
         if kv_sharing_target_layer_name is not None:
             raise NotImplementedError("KV sharing between layers is not supported")
         self.num_heads = num_heads
@@ -199,14 +202,18 @@ class B200AttentionImpl(AttentionImpl[B200AttentionMetadata]):
         q = query[:T].reshape(T, Hq, D)
         out = output[:T].view(T, Hq, D)
         k_cache, v_cache = kv_cache[0], kv_cache[1]
+        if self.alibi is not None and self.alibi.device != q.device:
+            self.alibi = self.alibi.to(q.device)
         nd = md.num_decode_tokens
         if nd > 0:
             C.paged_decode(q[:nd], k_cache, v_cache, md.block_table[:md.num_decodes],
                            md.seq_lens[:md.num_decodes], self.scale, out=out[:nd],
-                           num_splits=md.decode_splits, workspace=md.decode_workspace)
+                           num_splits=md.decode_splits, workspace=md.decode_workspace,
+                           alibi_slopes=self.alibi)
         if md.num_prefills > 0:
             lo, hi = md.num_decodes, md.num_decodes + md.num_prefills
             C.varlen_prefill(q[nd:], k_cache, v_cache, md.block_table[lo:hi], md.cu_q_prefill,
                              md.seq_lens[lo:hi], self.scale, md.num_q_tiles, out=out[nd:],
-                             window=self.window, num_q_tiles_128=md.num_q_tiles_128)
+                             window=self.window, num_q_tiles_128=md.num_q_tiles_128,
+                             alibi_slopes=self.alibi)
         return output
