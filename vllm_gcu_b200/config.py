@@ -112,12 +112,13 @@ class ModelConfig:
     @classmethod
     def from_hf_dict(cls, d: dict, **overrides) -> "ModelConfig":
         archs = d.get("architectures") or ["LlamaForCausalLM"]
-        if isinstance(d.get("text_config"), dict):
-            # multimodal configs nest the language model's fields; vision_config, token ids
-            # and everything else stay reachable through ``extra``
-            d = {**{k: v for k, v in d.items() if k != "text_config"},
-                 **{k: v for k, v in d["text_config"].items()
-                    if k not in ("architectures", "model_type")}}
+        for nested in ("text_config", "language_config"):
+            if isinstance(d.get(nested), dict):
+                # multimodal configs nest the language model's fields; vision_config, token
+                # ids and everything else stay reachable through ``extra``
+                d = {**{k: v for k, v in d.items() if k != nested},
+                     **{k: v for k, v in d[nested].items()
+                        if k not in ("architectures", "model_type")}}
         if archs[0] in ("ChatGLMModel", "ChatGLMForConditionalGeneration"):
             # ChatGLM2 / 3 / GLM-4-9B configs use their own field names
             d = dict(d)

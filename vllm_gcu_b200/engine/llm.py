@@ -152,8 +152,11 @@ class LLMEngine:
             prep = getattr(self.model, "prepare_request", None)
             if prep is None:
                 raise ValueError(f"{self.cfg.model.architecture} takes no multimodal input")
+            # second operand: patch grids (Qwen2.5-VL) or tile counts per image (DeepSeek-VL2)
+            grids = multi_modal_data.get("image_grid_thw",
+                                         multi_modal_data.get("images_spatial_crop"))
             for k, v in prep(req.prompt_token_ids, multi_modal_data["pixel_values"],
-                             multi_modal_data["image_grid_thw"]).items():
+                             grids).items():
                 setattr(req, k, v)
         if kv_transfer_params:
             req.kv_transfer_params = dict(kv_transfer_params)

@@ -34,6 +34,7 @@ _REGISTRY: dict[str, str] = {
     "QuantDeepseekForCausalLM": "vllm_gcu_b200.models.moe_models:DeepseekMoeForCausalLM",
     "DeepseekV2ForCausalLM": "vllm_gcu_b200.models.deepseek:DeepseekV3ForCausalLM",
     "DeepseekV3ForCausalLM": "vllm_gcu_b200.models.deepseek:DeepseekV3ForCausalLM",
+    "DeepseekVLV2ForCausalLM": "vllm_gcu_b200.models.deepseek_vl2:DeepseekVLV2ForCausalLM",
     "DeepSeekMTPModel": "vllm_gcu_b200.models.deepseek_mtp:DeepSeekMTP",
     # pooling models (no KV cache; built by build_pooling_model)
     "XLMRobertaForSequenceClassification":
