@@ -9,6 +9,9 @@ launches the kernel of interest a handful of times:
   python benchmarks/kernels/ncu_cases.py --case prefill_attn   # 8 x 1024 tokens, causal
   python benchmarks/kernels/ncu_cases.py --case gemm_fp8       # 4096 x 4096 x 4096 fp8
   python benchmarks/kernels/ncu_cases.py --case gemm_ar_single # fused all-reduce epilogue, p = 1
+  python benchmarks/kernels/ncu_cases.py --case gemm_ar_norm_single      # + residual + RMSNorm,
+                                                                        # 8192 rows, owners pull
+  python benchmarks/kernels/ncu_cases.py --case gemm_ar_norm_single_ll   # 256 rows, tagged push
   python benchmarks/kernels/ncu_cases.py --case mla_decode     # latent attention, 128 heads
   python benchmarks/kernels/ncu_cases.py --case mla_decode_small  # latent attention, 16 heads
   python benchmarks/kernels/ncu_cases.py --case wna16_decode   # fused 4-bit de-quantising GEMM
@@ -100,6 +103,44 @@ def main():
                 words.data_ptr(), words.data_ptr() + 16, 0, 1, None, 0, 1, M * N,
                 torch.cuda.current_stream().cuda_stream)
             assert rc == 0, rc
+    elif a.case in ("gemm_ar_norm_single", "gemm_ar_norm_single_ll"):
+        # row-parallel GEMM + all-reduce + residual + RMSNorm in one kernel, one-rank group
+        # (down_proj shard of Llama-3-8B at 8 ranks: K = 1792): park the partial rows, raise
+        # the flags (or tag the rows), the row owners reduce, add the residual, normalise
+        import ctypes
+        from vllm_gcu_b200.parallel import symm
+        symm._register_sigs()
+        ll = a.case.endswith("_ll")
+        M, N, K = (256, 4096, 1792) if ll else (8192, 4096, 1792)
+        x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02
+        res = torch.randn(M, N, device=dev, dtype=torch.bfloat16)
+        nw = torch.ones(N, device=dev, dtype=torch.bfloat16)
+        partial = torch.zeros(2 * M, N, dtype=torch.bfloat16, device=dev)
+        out = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+        res_out = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+        ready = torch.zeros(M // 128 * (N // 64) + 64, dtype=torch.int32, device=dev)
+        done = torch.zeros(M, dtype=torch.int32, device=dev)
+        words = torch.zeros(16, dtype=torch.int32, device=dev)
+        base = torch.zeros(M // 128 + 1, dtype=torch.int32, device=dev)
+        cap = M * N
+        tag = -2147450880                      # 0x80008000: two bf16 "row not written" marks
+        ll_slots = torch.full((3 * cap // 2,), tag, dtype=torch.int32, device=dev)
+        ll_out = torch.full((3 * cap // 2,), tag, dtype=torch.int32, device=dev)
+        ll_used = torch.zeros(6, dtype=torch.int64, device=dev)
+
+        def arr(t):
+            v = (ctypes.c_void_p * 8)()
+            v[0] = t.data_ptr()
+            return v
+
+        def fn():
+            wp = words.data_ptr()
+            _native.call("b200_gemm_bf16_ar_norm", x.data_ptr(), K, w.data_ptr(), K, N, M, N, K,
+                         arr(ll_slots if ll else partial), arr(ll_out if ll else out),
+                         arr(res_out), arr(ready), arr(done), base.data_ptr(), wp, wp + 16, 0, 1,
+                         res.data_ptr(), N, nw.data_ptr(), 1e-5, 0, 3 if ll else 0, None, None,
+                         None, out.data_ptr(), cap, ll_used.data_ptr(), _native.stream_ptr())
     elif a.case in ("mla_decode", "mla_decode_small"):
         # latent attention, B = 256, ctx = 1152: 340 MB of latent cache (larger than L2);
         # 128 heads (data-parallel attention) or 16 heads (tensor parallel 8)

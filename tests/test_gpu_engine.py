@@ -193,3 +193,41 @@ def test_same_batch_twice_is_bitwise_identical():
     if runs[0][1] is not None:
         assert torch.equal(runs[0][1], runs[1][1])
     _native.check_status()
+
+
+@pytest.mark.parametrize("scheme", ["fp8_token", "fp8_block", "fp8_static"])
+def test_norm_and_activation_kernels_emit_quantised_rows(scheme, monkeypatch):
+    """8-bit linear layers: the RMSNorm in front of qkv / gate_up and the gated activation in
+    front of down_proj write fp8 rows and scales themselves.  Same logits as with separate
+    quantisation kernels (both quantise the same fp32 values up to the 16-bit rounding of the
+    intermediate), with fewer launches."""
+    qc = {"fp8_token": {}, "fp8_block": {"weight_block_size": [128, 128]},
+          "fp8_static": {"activation_scheme": "static"}}[scheme]
+    kw = dict(num_hidden_layers=2, hidden_size=512, intermediate_size=1024,
+              num_attention_heads=8, num_key_value_heads=2, head_dim=64, vocab_size=2048,
+              max_num_seqs=8, max_num_batched_tokens=256, max_model_len=256, num_gpu_blocks=128,
+              quantization="fp8", quant_config=qc, enforce_eager=True, seed=0)
+    one = SamplingParams(max_tokens=1, temperature=0.0, ignore_eos=True)
+    prompts = _prompts(3, [70, 33, 128], 2048, seed=5)
+    logits, launches = {}, {}
+    for fuse in ("1", "0"):
+        monkeypatch.setenv("VLLM_B200_FUSE_ACT_QUANT", fuse)
+        llm = LLM("llama-3-8b", device="cuda", **kw)
+        if scheme == "fp8_static":
+            for m in llm.engine.model.modules():
+                if hasattr(m, "input_scale"):
+                    m.input_scale.data.fill_(0.05)
+        llm.engine.runner.keep_logits = True
+        n0 = _native.launch_count
+        llm.generate(prompts, one)
+        launches[fuse] = _native.launch_count - n0
+        logits[fuse] = llm.engine.runner.last_logits.float().clone()
+        _native.check_status()
+    # per layer: the two norms absorb their quantisation kernels; the gated activation absorbs
+    # its one for group and static scales (it has no per-token mode)
+    saved = 2 if scheme == "fp8_token" else 3
+    assert launches["1"] <= launches["0"] - 2 * saved, launches
+    err = (logits["1"] - logits["0"]).abs().max().item()
+    spread = logits["0"].std().item()
+    assert err < 0.1 * spread + 0.02, (err, spread)
+    assert logits["1"].isfinite().all()

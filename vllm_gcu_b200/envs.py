@@ -69,6 +69,9 @@ environment_variables: dict[str, Callable[[], Any]] = {
     # disaggregated prefill (vllm_gcu/envs.py:30-36, used by patch_0_9_2/nixl_connector.py):
     # the decode instance takes the KV of a partly filled last block too (0: whole blocks
     # only, the rest is recomputed) ...
+    # 8-bit linear layers take their input already quantised from the norm / activation kernel
+    # in front of them (0: separate quantisation kernels, for comparison)
+    "FUSE_ACT_QUANT": _flag("FUSE_ACT_QUANT", "1"),
     "NIXL_ENABLE_FULL_KV_TRANSFER": _flag("NIXL_ENABLE_FULL_KV_TRANSFER", "1"),
     # ... and starts at the first output token the prefill instance already produced
     "NIXL_ENABLE_FIRST_TOKEN_REUSE": _flag("NIXL_ENABLE_FIRST_TOKEN_REUSE"),

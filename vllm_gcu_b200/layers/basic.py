@@ -39,6 +39,18 @@ class RMSNorm(nn.Module):
             return ref.rms_norm(x, self.weight, self.eps)
         return ref.fused_add_rms_norm(x, residual, self.weight, self.eps)
 
+    def forward_quant(self, x: torch.Tensor, residual: Optional[torch.Tensor], mode: str,
+                      scale: Optional[torch.Tensor] = None):
+        """(Residual add +) RMSNorm + activation quantisation in one kernel, for a consumer
+        GEMM with 8-bit activations (the fusions the reference's compile pass performs,
+        vllm_gcu/compilation/fusion.py:889-1023).  GPU only.  Returns
+        ``(x_q, x_scale, residual)``; ``x_scale`` is per row (``[T, 1]``), per 128-wide group
+        (``[T, H / 128]``) or the static scale repeated per row."""
+        out = C.norm(x, self.weight, self.eps, residual=residual, quant=mode, scale=scale)
+        if isinstance(out, tuple):
+            return out[0], out[1], residual
+        return out, scale.reshape(1).expand(x.shape[0]).contiguous(), residual
+
     def load_weight(self, name: str, full: torch.Tensor, shard_id=None) -> None:
         self.weight.data.copy_(full)
 

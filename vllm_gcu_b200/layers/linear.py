@@ -43,6 +43,12 @@ class LinearMethod:
     def process_weights_after_loading(self, layer: "LinearBase") -> None:
         pass
 
+    def input_quant(self, layer: "LinearBase"):
+        """``(mode, static scale or None)`` when ``apply`` quantises its input and also accepts
+        it already quantised (``x`` 8-bit plus ``x_scale=``), so that the producing norm /
+        activation kernel can emit the quantised rows itself; None otherwise."""
+        return None
+
 
 class UnquantizedLinearMethod(LinearMethod):
     def create_weights(self, layer: "LinearBase") -> None:
@@ -274,7 +280,7 @@ class RowParallelLinear(LinearBase):
             y = fused.gemm_all_reduce(x, self.weight)
             if y is not None:
                 return y
-        y = self.quant_method.apply(self, x, skip_bias=True)
+        y = self.quant_method.apply(self, x, skip_bias=True, **kw)
         y = comm.all_reduce(y)
         if self.bias is not None:   # added once, after the reduction
             y = y + self.bias

@@ -105,6 +105,13 @@ class Fp8LinearMethod(LinearMethod):
             return True
         return False
 
+    def input_quant(self, layer: LinearBase):
+        if self.block:
+            return ("fp8_group128", None) if self.block[1] == 128 else None
+        if self.static_act:
+            return "fp8_static", layer.input_scale
+        return "fp8_token", None
+
     def apply(self, layer: LinearBase, x: torch.Tensor, skip_bias=False, x_scale=None, **kw):
         """``x`` may already be fp8 with ``x_scale`` given (producer fused the quantisation,
         vllm_gcu/kernels/quantization/fp8.py:50-69)."""
@@ -181,11 +188,18 @@ class Int8LinearMethod(LinearMethod):
             return True
         return False
 
-    def apply(self, layer, x, skip_bias=False, **kw):
+    def input_quant(self, layer):
+        return ("int8_static", layer.in_scale) if self.static_act else ("int8_token", None)
+
+    def apply(self, layer, x, skip_bias=False, x_scale=None, **kw):
         bias = None if skip_bias else layer.bias
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
         N = layer.weight.shape[0]
+        if ops.use_native(x2) and x2.dtype == torch.int8:
+            # the producing norm / activation kernel quantised the rows already
+            y = C.gemm_q8(x2, layer.weight, x_scale.reshape(-1), layer.out_scales, bias, kind=2)
+            return y.view(*shape[:-1], N)
         if ops.use_native(x2):
             if self.static_act:
                 q = C.activation(x2, "identity", mode="plain", quant="int8_static",

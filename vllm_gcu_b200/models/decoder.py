@@ -19,6 +19,7 @@ from ..config import ModelConfig
 from ..layers.attention import AttentionMetadata, PagedAttention
 from ..layers.basic import ParallelLMHead, RMSNorm, RotaryEmbedding, VocabParallelEmbedding
 from ..layers.linear import (MergedColumnParallelLinear, QKVParallelLinear, RowParallelLinear)
+from ..ops import cuda as C
 from ..parallel.state import get_state, tp_rank, tp_size
 
 
@@ -28,6 +29,26 @@ def get_linear_method(cfg: ModelConfig, prefix: str):
         return None
     from ..layers.quant import get_quant_config
     return get_quant_config(cfg).get_linear_method(prefix)
+
+
+def fused_input_quant(linear, x: torch.Tensor, width: Optional[int] = None):
+    """``(mode, static scale)`` when the kernel that produces ``linear``'s input (a norm or a
+    gated activation of ``width`` output columns) should emit it quantised: the layer runs on
+    8-bit activations, the tensors are on the GPU in a 16-bit type, and the width suits the
+    mode.  The reference gets the same effect from its compile-time fusion pass
+    (vllm_gcu/compilation/fusion.py:889-1023)."""
+    from .. import envs, ops
+    if not (ops.use_native(x) and x.dtype in (torch.bfloat16, torch.float16)):
+        return None
+    if not type(linear).__module__.endswith("layers.linear"):
+        return None            # wrapped layers (LoRA) need the 16-bit rows as well
+    iq = linear.quant_method.input_quant(linear)
+    if iq is None or not envs.FUSE_ACT_QUANT:
+        return None
+    width = x.shape[-1] if width is None else width
+    if width % 8 != 0 or (iq[0] == "fp8_group128" and width % 128 != 0):
+        return None
+    return iq
 
 
 class DenseMLP(nn.Module):
@@ -55,18 +76,37 @@ class DenseMLP(nn.Module):
             h = act_and_mul(h, self.act)
         return h
 
-    def forward(self, x: torch.Tensor, sp_sizes: Optional[list] = None) -> torch.Tensor:
+    def _act_quant(self, h: torch.Tensor):
+        """Gated activation, fused with the quantisation of down_proj's input when that layer
+        runs on 8-bit activations in a mode the activation kernel can emit (128-wide fp8 groups
+        or a static scale).  Returns ``(tensor, kwargs for down_proj)``."""
+        from ..layers.activation import act_and_mul
+        iq = fused_input_quant(self.down_proj, h, h.shape[-1] // 2)
+        if iq is not None and iq[0] in C.ACT_QUANT and self.act in C.ACT_CODES:
+            out = C.activation(h, self.act, "act_mul", quant=iq[0], scale=iq[1])
+            if isinstance(out, tuple):
+                return out[0], {"x_scale": out[1]}
+            return out, {"x_scale": iq[1].reshape(1).expand(out.shape[0]).contiguous()}
+        return act_and_mul(h, self.act), {}
+
+    def forward(self, x: torch.Tensor, sp_sizes: Optional[list] = None,
+                x_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``sp_sizes`` (sequence parallelism): ``x`` holds this rank's rows; the rows are
         gathered for the column-parallel projection and the row-parallel output is
-        reduce-scattered back to rows."""
+        reduce-scattered back to rows.  ``x_scale``: ``x`` is already quantised for
+        gate_up_proj (see ``fused_input_quant``)."""
+        kw = {}
         if sp_sizes is not None:
             from ..parallel import sp
             h = sp.sp_gather_linear(self.gate_up_proj, x, sp_sizes)
         else:
-            h = self.gate_up_proj(x)
+            h = self.gate_up_proj(x) if x_scale is None else self.gate_up_proj(x, x_scale=x_scale)
         if not self.gate_up_proj.fuse_silu:
-            from ..layers.activation import act_and_mul
-            h = act_and_mul(h, self.act)
+            if sp_sizes is None:
+                h, kw = self._act_quant(h)
+            else:
+                from ..layers.activation import act_and_mul
+                h = act_and_mul(h, self.act)
         if sp_sizes is not None:
             from ..parallel import sp
             keep, self.down_proj.reduce_results = self.down_proj.reduce_results, False
@@ -75,7 +115,7 @@ class DenseMLP(nn.Module):
             finally:
                 self.down_proj.reduce_results = keep
             return sp.reduce_scatter_rows(y, sp_sizes)
-        return self.down_proj(h)
+        return self.down_proj(h, **kw)
 
 
 class GQAAttention(nn.Module):
@@ -110,15 +150,17 @@ class GQAAttention(nn.Module):
         self.attn = PagedAttention(self.qkv_proj.num_heads, self.qkv_proj.num_kv_heads, D,
                                    D ** -0.5, rotary, qn, kn, cfg.sliding_window, alibi)
 
-    def before_o_proj(self, x: torch.Tensor, kv_cache: torch.Tensor, md: AttentionMetadata
-                      ) -> torch.Tensor:
+    def before_o_proj(self, x: torch.Tensor, kv_cache: torch.Tensor, md: AttentionMetadata,
+                      x_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Attention output of this rank's heads (the input of the row-parallel o_proj)."""
-        return self.attn(self.qkv_proj(x), kv_cache, md)
+        qkv = self.qkv_proj(x) if x_scale is None else self.qkv_proj(x, x_scale=x_scale)
+        return self.attn(qkv, kv_cache, md)
 
     def forward(self, x: torch.Tensor, kv_cache: torch.Tensor, md: AttentionMetadata,
-                sp_sizes: Optional[list] = None) -> torch.Tensor:
+                sp_sizes: Optional[list] = None, x_scale: Optional[torch.Tensor] = None
+                ) -> torch.Tensor:
         if sp_sizes is None:
-            return self.o_proj(self.before_o_proj(x, kv_cache, md))
+            return self.o_proj(self.before_o_proj(x, kv_cache, md, x_scale))
         # sequence parallelism: rows in, rows out (vllm_gcu/models/deepseek_v3/
         # deepseek_v3.py:611-612,747-748: sp_to_tp before the projections, tp_to_sp after o_proj)
         from ..parallel import sp
@@ -203,21 +245,42 @@ class DecoderLayer(nn.Module):
 
     def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor], kv_cache: torch.Tensor,
                 md: AttentionMetadata, sp_sizes: Optional[list] = None):
-        if residual is None:
-            residual = x
-            h = self.input_layernorm(x)
+        # 8-bit qkv / gate_up projections take their input quantised by the norm kernel
+        iq_attn = iq_mlp = None
+        if sp_sizes is None and x.shape[0] > 0 and type(self.input_layernorm) is RMSNorm:
+            if isinstance(self.self_attn, GQAAttention):
+                iq_attn = fused_input_quant(self.self_attn.qkv_proj, x)
+            if isinstance(self.mlp, DenseMLP) and type(self.post_attention_layernorm) is RMSNorm:
+                iq_mlp = fused_input_quant(self.mlp.gate_up_proj, x)
+        if iq_attn is not None:
+            if residual is None:
+                residual = x
+                h, xs, _ = self.input_layernorm.forward_quant(x, None, *iq_attn)
+            else:
+                h, xs, residual = self.input_layernorm.forward_quant(x, residual, *iq_attn)
+            h = self.self_attn(h, kv_cache, md, x_scale=xs)
         else:
-            h, residual = self.input_layernorm(x, residual)
-        if sp_sizes is not None and isinstance(self.self_attn, GQAAttention):
-            h = self.self_attn(h, kv_cache, md, sp_sizes)
-        elif sp_sizes is not None:
-            from ..parallel import sp
-            full = self.self_attn(sp.sp_to_tp(h, sum(sp_sizes)), kv_cache, md)
-            h = sp.slice_tensor_sp(full)
-        else:
-            h = self.self_attn(h, kv_cache, md)
+            if residual is None:
+                residual = x
+                h = self.input_layernorm(x)
+            else:
+                h, residual = self.input_layernorm(x, residual)
+            if sp_sizes is not None and isinstance(self.self_attn, GQAAttention):
+                h = self.self_attn(h, kv_cache, md, sp_sizes)
+            elif sp_sizes is not None:
+                from ..parallel import sp
+                full = self.self_attn(sp.sp_to_tp(h, sum(sp_sizes)), kv_cache, md)
+                h = sp.slice_tensor_sp(full)
+            else:
+                h = self.self_attn(h, kv_cache, md)
         if self.sandwich:
             h = self.post_self_attn_layernorm(h)
+        if iq_mlp is not None:
+            h, xs, residual = self.post_attention_layernorm.forward_quant(h, residual, *iq_mlp)
+            h = self.mlp(h, x_scale=xs)
+            if self.sandwich:
+                h = self.post_mlp_layernorm(h)
+            return h, residual
         h, residual = self.post_attention_layernorm(h, residual)
         if sp_sizes is not None and isinstance(self.mlp, DenseMLP):
             h = self.mlp(h, sp_sizes)
