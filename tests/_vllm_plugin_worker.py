@@ -6,7 +6,9 @@ Checks: the active platform is ``B200Platform``; vLLM's worker is ``B200Worker``
 attention backend of every layer is ``B200AttentionBackend``; greedy generation of a small
 Llama (weights set to N(0, 0.02) after the dummy load) launches this package's kernels and
 every generated token is a (near-)maximum of a dense fp32 forward of the same weights; the
-built-in engine of this package, given the same weights, passes the same check.
+built-in engine of this package, given the same weights, passes the same check; vLLM's kernel
+chooser selects this package's fp8 / int8 linear kernels, whose results match an fp32 product,
+and an fp8-quantised engine runs on them.
 """
 import json
 import os
@@ -72,6 +74,88 @@ def near_max(cfg, sd, prompts, seqs, dev, tag):
         assert gap.max().item() < tol, f"{tag}: generated token far from the maximum: {gap}"
 
 
+def check_linear_kernels(dev):
+    """The fp8 / int8 kernel classes this package puts at the head of vLLM's kernel lists:
+    selected by vLLM's own chooser, results against an fp32 product of the de-quantised
+    operands."""
+    import vllm.model_executor.kernels.linear as vk
+    from vllm.model_executor.layers.quantization.utils.quant_utils import (
+        kFp8DynamicTokenSym, kFp8StaticTensorSym)
+    from vllm.platforms import PlatformEnum
+    assert vk._POSSIBLE_FP8_KERNELS[PlatformEnum.CUDA][0].__name__ == "B200FP8ScaledMMLinearKernel"
+    assert vk._POSSIBLE_INT8_KERNELS[PlatformEnum.CUDA][0].__name__ == "B200Int8ScaledMMLinearKernel"
+    g = torch.Generator(device=dev).manual_seed(11)
+    M, N, K = 77, 768, 512
+    x = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
+    w = torch.randn(N, K, device=dev, generator=g) * 0.05
+    bias = torch.randn(N, device=dev, generator=g).to(torch.bfloat16)
+    f8 = torch.float8_e4m3fn
+    for static in (False, True):
+        k = vk.init_fp8_linear_kernel(
+            activation_quant_key=kFp8StaticTensorSym if static else kFp8DynamicTokenSym,
+            weight_quant_key=kFp8StaticTensorSym, input_dtype=torch.bfloat16,
+            out_dtype=torch.bfloat16, weight_shape=(N, K), module_name="check")
+        assert type(k).__name__ == "B200FP8ScaledMMLinearKernel", type(k)
+        # two fused shards with one scale each
+        ws = torch.stack([w[:256].abs().max(), w[256:].abs().max()]) / 448.0
+        per_row = torch.cat([ws[0].expand(256), ws[1].expand(N - 256)])
+        qw = (w / per_row[:, None]).to(f8)
+        layer = torch.nn.Module()
+        layer.weight = torch.nn.Parameter(qw.t(), requires_grad=False)
+        layer.weight_scale = torch.nn.Parameter(ws.clone(), requires_grad=False)
+        layer.logical_widths = [256, N - 256]
+        layer.input_scale = torch.nn.Parameter(x.float().abs().max() / 448.0,
+                                               requires_grad=False) if static else None
+        k.process_weights_after_loading(layer)
+        y = k.apply_weights(layer, x, bias).float()
+        want = x.float() @ (qw.float() * per_row[:, None]).t() + bias.float()
+        err = (y - want).abs().max().item()
+        assert err < 0.08 * want.abs().max().item(), ("fp8", static, err)
+    for static in (False, True):
+        k = vk.init_int8_linear_kernel(is_channelwise=True, is_static_input_scheme=static,
+                                       input_symmetric=True, module_name="check")
+        assert type(k).__name__ == "B200Int8ScaledMMLinearKernel", type(k)
+        ws = w.abs().amax(1, keepdim=True) / 127.0
+        qw = torch.round(w / ws).clamp(-128, 127).to(torch.int8)
+        layer = torch.nn.Module()
+        layer.weight = torch.nn.Parameter(qw, requires_grad=False)
+        layer.weight_scale = torch.nn.Parameter(ws.clone(), requires_grad=False)
+        layer.logical_widths = [N]
+        layer.input_scale = torch.nn.Parameter((x.float().abs().max() / 127.0).reshape(1),
+                                               requires_grad=False) if static else None
+        layer.input_zero_point = None
+        layer.azp_adj = None
+        k.process_weights_after_loading(layer)
+        y = k.apply_weights(layer, x, bias).float()
+        want = x.float() @ (qw.float() * ws).t() + bias.float()
+        err = (y - want).abs().max().item()
+        assert err < 0.05 * want.abs().max().item(), ("int8", static, err)
+
+
+def check_fp8_engine(d, prompts):
+    """vLLM with ``quantization="fp8"`` (weights quantised at load): every linear layer picks
+    this package's fp8 kernel and generation launches it."""
+    from vllm import LLM, SamplingParams
+    from vllm_gcu_b200.ops import _native
+    llm = LLM(model=d, load_format="dummy", skip_tokenizer_init=True, dtype="bfloat16",
+              quantization="fp8", enforce_eager=True, max_model_len=256, max_num_seqs=8,
+              block_size=16, max_num_batched_tokens=256, gpu_memory_utilization=0.25,
+              enable_prefix_caching=False, seed=0)
+
+    def kernels(model):
+        return sorted({type(m.quant_method.fp8_linear).__name__ for m in model.modules()
+                       if hasattr(getattr(m, "quant_method", None), "fp8_linear")})
+    assert llm.apply_model(kernels)[0] == ["B200FP8ScaledMMLinearKernel"], \
+        llm.apply_model(kernels)
+    sp = SamplingParams(max_tokens=4, temperature=0.0, ignore_eos=True, detokenize=False)
+    n0 = _native.launch_count
+    outs = llm.generate([{"prompt_token_ids": p} for p in prompts], sp, use_tqdm=False)
+    torch.cuda.synchronize()
+    _native.check_status()
+    assert all(len(o.outputs[0].token_ids) == 4 for o in outs)
+    return _native.launch_count - n0
+
+
 def main():
     from vllm import LLM, SamplingParams
     from vllm.platforms import current_platform
@@ -83,6 +167,13 @@ def main():
     d = tempfile.mkdtemp(prefix="tiny_llama_cfg_")
     with open(os.path.join(d, "config.json"), "w") as f:
         json.dump(CFG, f)
+    if os.environ.get("B200_PLUGIN_CHECK", "base") == "fp8":
+        g = torch.Generator().manual_seed(3)
+        prompts = [torch.randint(0, 4096, (n,), generator=g).tolist() for n in (33, 64, 5, 120)]
+        launched_fp8 = check_fp8_engine(d, prompts)
+        print(f"vllm fp8 ok: {launched_fp8} native launches with fp8 weights", flush=True)
+        sys.stdout.flush()
+        os._exit(0)
     llm = LLM(model=d, load_format="dummy", skip_tokenizer_init=True, dtype="bfloat16",
               enforce_eager=True, max_model_len=256, max_num_seqs=8, block_size=16,
               max_num_batched_tokens=256, gpu_memory_utilization=0.25,
@@ -127,8 +218,12 @@ def main():
     seqs2 = [o.outputs[0].token_ids for o in outs2]
     near_max(cfg, hf, prompts, seqs2, dev, "built-in engine")
     same = sum(a == b for s1, s2 in zip(seqs, seqs2) for a, b in zip(s1, s2))
+    from vllm.config import set_current_vllm_config
+    with set_current_vllm_config(vcfg):              # kernel objects build vLLM custom ops
+        check_linear_kernels(dev)
     print(f"vllm plugin ok: {launched} native launches under vLLM, "
-          f"{same}/{8 * len(prompts)} tokens equal to the built-in engine", flush=True)
+          f"{same}/{8 * len(prompts)} tokens equal to the built-in engine; fp8 and int8 "
+          f"linear kernels selected and checked", flush=True)
     sys.stdout.flush()
     os._exit(0)
 

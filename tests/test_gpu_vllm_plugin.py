@@ -22,10 +22,7 @@ b200_models = vllm_gcu_b200:register_custom_models
 """
 
 
-@pytest.mark.skipif(not torch.cuda.is_available(), reason="needs a GPU")
-@pytest.mark.timeout(900)
-def test_vllm_engine_runs_on_the_plugin(tmp_path):
-    pytest.importorskip("vllm")
+def _run_worker(tmp_path, check: str):
     info = tmp_path / "vllm_gcu_b200-0.1.0.dist-info"
     info.mkdir()
     (info / "METADATA").write_text("Metadata-Version: 2.1\nName: vllm-gcu-b200\nVersion: 0.1.0\n")
@@ -33,7 +30,23 @@ def test_vllm_engine_runs_on_the_plugin(tmp_path):
     env = dict(os.environ)
     env["PYTHONPATH"] = os.pathsep.join([str(tmp_path), ROOT, env.get("PYTHONPATH", "")])
     env.pop("VLLM_PLUGINS", None)
+    env["B200_PLUGIN_CHECK"] = check
     res = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "_vllm_plugin_worker.py")],
                          env=env, capture_output=True, text=True, timeout=850)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-5000:]
-    assert "vllm plugin ok" in res.stdout
+    return res.stdout
+
+
+@pytest.mark.skipif(not torch.cuda.is_available(), reason="needs a GPU")
+@pytest.mark.timeout(900)
+def test_vllm_engine_runs_on_the_plugin(tmp_path):
+    pytest.importorskip("vllm")
+    assert "vllm plugin ok" in _run_worker(tmp_path, "base")
+
+
+@pytest.mark.skipif(not torch.cuda.is_available(), reason="needs a GPU")
+@pytest.mark.timeout(900)
+def test_vllm_fp8_engine_runs_on_the_plugin_kernels(tmp_path):
+    """``quantization="fp8"`` under vLLM: the linear layers select this package's fp8 kernel."""
+    pytest.importorskip("vllm")
+    assert "vllm fp8 ok" in _run_worker(tmp_path, "fp8")

@@ -21,7 +21,7 @@ def register_platform_plugins() -> str:
 def register_custom_models() -> None:
     """General plugin hook (runs in every vLLM process): registers this package's attention
     backend under ``AttentionBackendEnum.CUSTOM``, its layer kernels (RMSNorm, SiLU-and-mul,
-    unquantised GEMM) and its quantisation configs with vLLM.  The model classes of the
+    unquantised GEMM, fp8 / int8 scaled GEMMs) and its quantisation configs with vLLM.  The model classes of the
     built-in engine use their own registry (``vllm_gcu_b200.models``); under vLLM the upstream
     model definitions run on these kernels."""
     try:
@@ -40,6 +40,8 @@ def register_custom_models() -> None:
         if os.environ.get("VLLM_B200_VLLM_NATIVE_OPS", "1") != "0":
             from .runtime import vllm_ops
             vllm_ops.register_ops()
+            from .runtime import vllm_linear_kernels
+            vllm_linear_kernels.register_linear_kernels()
     except Exception:
         pass
 
