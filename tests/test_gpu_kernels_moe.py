@@ -251,3 +251,82 @@ def test_fused_experts_q8_channel_matches_dequantised_reference(dtype):
     err = (got.float() - want).abs().max().item()
     tol = (0.03 if dtype == torch.int8 else 0.08) * want.abs().max().item() + 0.02
     assert err < tol, (err, want.abs().max().item())
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("T,k", [(16, 2), (150, 2), (700, 2)])
+def test_fused_experts_wna16_packed_matches_dequantised_reference(bits, T, k):
+    """Experts kept as packed 4 / 8-bit integers with per-group scales (AWQ / GPTQ layouts):
+    the grouped de-quantising GEMM for decode-sized batches and the scratch + bf16 grouped
+    GEMM for large ones, against the fp32 reference on the de-quantised weights.  One expert
+    gets no token; an expert map hides two experts (expert parallelism)."""
+    from vllm_gcu_b200.ops import cuda as C
+    torch.manual_seed(13 + bits + T)
+    dev = "cuda"
+    E, H, I, g = 8, 512, 256, 128
+    top = 1 << bits
+
+    def make(n, kk):
+        q = torch.randint(0, top, (E, n, kk), device=dev, dtype=torch.uint8)
+        s = (torch.rand(E, n, kk // g, device=dev) * (0.4 / top) + 0.1 / top).to(torch.bfloat16)
+        z = (torch.randint(0, top, (E, n, kk // g), device=dev).float() * s.float()).to(
+            torch.bfloat16)
+        w = q.float() * s.float().repeat_interleave(g, -1) - z.float().repeat_interleave(g, -1)
+        packed = (q[..., 0::2] | (q[..., 1::2] << 4)).contiguous() if bits == 4 else q
+        return packed, s.contiguous(), z.contiguous(), w
+
+    q13, s13, z13, w13 = make(2 * I, H)
+    q2, s2, z2, w2 = make(H, I)
+    x = (torch.randn(T, H, device=dev) * 0.5).to(torch.bfloat16)
+    logits = torch.randn(T, E, device=dev)
+    logits[:, 5] = -1e9                                  # expert 5 gets nothing
+    tw, ti = torch.topk(torch.softmax(logits, -1), k, dim=-1)
+    ti = ti.to(torch.int32)
+    fused = T * k <= C.WNA16_GROUPED_MAX_ROWS_PER_EXPERT * E
+    assert fused == (T <= 150)
+    for emap in (None, torch.tensor([0, 1, -1, 2, 3, 4, -1, 5], device=dev, dtype=torch.int32)):
+        if emap is None:
+            args = (q13, s13, z13, q2, s2, z2)
+            w13_r, w2_r = w13, w2
+        else:
+            keep = (emap >= 0).nonzero().flatten()
+            args = tuple(t[keep].contiguous() for t in (q13, s13, z13, q2, s2, z2))
+            w13_r, w2_r = w13[keep], w2[keep]
+        add = torch.randn(T, H, device=dev).to(torch.bfloat16)
+        got = C.fused_experts_wna16(x, *args, g, bits, tw.float(), ti, emap, add=add)
+        torch.cuda.synchronize()
+        _native.check_status()
+        want = ref.fused_experts(x.float(), w13_r, w2_r, tw.float(), ti, emap).float() \
+            + add.float()
+        err = (got.float() - want).abs().max().item()
+        assert err < 0.03 * want.abs().max().item() + 0.03, (bits, T, emap is None, err,
+                                                             want.abs().max().item())
+
+
+def test_packed_wna16_experts_through_the_moe_layer():
+    """``FusedMoE.enable_wna16`` on the GPU: the packed layer equals the same experts
+    de-quantised into a bf16 layer."""
+    from vllm_gcu_b200.layers.moe import FusedMoE
+    torch.manual_seed(21)
+    dev = "cuda"
+    E, H, I, g, bits = 4, 256, 128, 64, 4
+    packed = FusedMoE(E, H, I, torch.bfloat16, dev, False)
+    plain = FusedMoE(E, H, I, torch.bfloat16, dev, False)
+    assert packed.enable_wna16(bits, g)
+    for e in range(E):
+        for which, (n, kk) in (("gate", (I, H)), ("up", (I, H)), ("down", (H, I))):
+            q = torch.randint(0, 16, (n, kk), device=dev, dtype=torch.uint8)
+            s = (torch.rand(n, kk // g, device=dev) * 0.02 + 0.005).to(torch.bfloat16)
+            zs = (torch.randint(0, 16, (n, kk // g), device=dev).float() * s.float()).to(
+                torch.bfloat16)
+            w = q.float() * s.float().repeat_interleave(g, 1) - zs.float().repeat_interleave(g, 1)
+            assert packed.load_expert_weight_wna16(e, which, q, s, zs)
+            plain.load_expert_weight(e, which, w.to(torch.bfloat16))
+    plain.finalize()
+    packed.finalize()
+    x = (torch.randn(33, H, device=dev) * 0.5).to(torch.bfloat16)
+    tw, ti = torch.topk(torch.softmax(torch.randn(33, E, device=dev), -1), 2, dim=-1)
+    a = packed(x, tw.float(), ti.to(torch.int32)).float()
+    b = plain(x, tw.float(), ti.to(torch.int32)).float()
+    torch.cuda.synchronize()
+    assert (a - b).abs().max().item() < 0.03 * b.abs().max().item() + 0.02

@@ -196,5 +196,53 @@ def test_expert_storage_by_checkpoint_format():
     assert expert_storage("fp8", {"quant_method": "fp8"}) == "fp8"
     assert expert_storage("w8a8_gcu", {}) == "int8"
     assert expert_storage("compressed-tensors", {"quant_method": "compressed-tensors"}) == "int8"
-    assert expert_storage("moe_wna16_gcu", {"quant_method": "awq", "bits": 4}) is None
+    assert expert_storage("moe_wna16_gcu", {"quant_method": "awq", "bits": 4}) == "wna16"
     assert expert_storage(None, None) is None
+
+
+def test_packed_wna16_experts_equal_dequantised_experts():
+    """AWQ / GPTQ experts kept packed (integers + per-group scales, the layout of the grouped
+    de-quantising GEMM) give the output of the experts de-quantised at load."""
+    from vllm_gcu_b200.layers.moe import FusedMoE
+    from vllm_gcu_b200.layers.quant.moe import dequant_wna16, expert_storage, unpack_wna16
+    assert expert_storage("moe_wna16_gcu", {"quant_method": "awq", "bits": 4}) == "wna16"
+    assert expert_storage("gptq", {"quant_method": "gptq", "bits": 8}) == "wna16"
+    assert expert_storage("gptq", {"quant_method": "gptq", "bits": 4, "desc_act": True}) is None
+    assert expert_storage("gptq", {"quant_method": "gptq", "bits": 3}) is None
+    torch.manual_seed(5)
+    E, I, H, g = 4, 128, 64, 32
+    for kind, bits in (("awq", 4), ("gptq", 4), ("gptq", 8)):
+        packed = FusedMoE(E, H, I, torch.float32, "cpu", False)
+        plain = FusedMoE(E, H, I, torch.float32, "cpu", False)
+        assert packed.enable_wna16(bits, g, any_device=True)
+        assert not FusedMoE(E, H, 96, torch.float32, "cpu", False).enable_wna16(bits, g, True)
+        for e in range(E):
+            for which, (N_, K_) in (("gate", (I, H)), ("up", (I, H)), ("down", (H, I))):
+                top = 1 << bits
+                q = torch.randint(0, top, (K_, N_), dtype=torch.int64)
+                z = torch.randint(0, top, (K_ // g, N_), dtype=torch.int64)
+                s = torch.rand(K_ // g, N_) * 0.02 + 0.01
+                if kind == "awq":
+                    qw, qz = _awq_pack(q), _awq_pack(z)
+                else:
+                    per = 32 // bits
+                    qw = torch.zeros(K_ // per, N_, dtype=torch.int64)
+                    for i in range(per):
+                        qw |= q[i::per] << (bits * i)
+                    qz = torch.zeros(K_ // g, N_ // per, dtype=torch.int64)
+                    for i in range(per):
+                        qz |= (z[:, i::per] - 1) << (bits * i)   # GPTQ stores zero - 1
+                    qw, qz = _to_i32(qw), _to_i32(qz)
+                want = dequant_wna16(kind, bits, g, qw, qz, s, torch.float32)
+                qi, sc, zs = unpack_wna16(kind, bits, qw, qz, s)
+                assert qi.dtype == torch.uint8 and qi.shape == (N_, K_)
+                got = qi.float() * sc.repeat_interleave(g, 1) - zs.repeat_interleave(g, 1)
+                assert torch.allclose(got, want, atol=1e-6)
+                assert packed.load_expert_weight_wna16(e, which, qi, sc, zs)
+                plain.load_expert_weight(e, which, want)
+        x = torch.randn(9, H)
+        ids = torch.randint(0, E, (9, 2), dtype=torch.int32)
+        w = torch.rand(9, 2)
+        assert packed.w13.numel() == 0 and packed.w13_q.shape == (E, 2 * I, H // (2 if bits == 4 else 1))
+        a, b = packed(x, w, ids), plain(x, w, ids)
+        assert (a - b).abs().max() <= 1e-5 * b.abs().max(), (kind, bits, (a - b).abs().max())

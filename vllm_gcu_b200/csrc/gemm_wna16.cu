@@ -43,6 +43,14 @@ struct Args {
   int splits;                     // K split over blockIdx.y; > 1: fp32 partial sums to ws
   float* ws;                      // [splits, M, N]
   unsigned int* status;
+  // grouped mode (mixture-of-experts): A holds expert-sorted rows in tiles of 128, tile t
+  // (= blockIdx.z) multiplies the weights of expert expert_ids[t]; qw / scales / zs carry a
+  // leading expert dimension.  Null expert_ids: one dense weight matrix.
+  const int* expert_ids;          // [M / 128]
+  const int* num_post_pad;        // device scalar: rows in use (a multiple of 128)
+  const float* row_scale;         // optional [M]: factor applied to every output row
+  long long w_stride;             // bytes between experts in qw
+  long long s_stride;             // elements between experts in scales / zs
 };
 
 // The loop empty -> TMA load -> full -> MMA -> empty takes about 2 us; with S stages a K block
@@ -74,6 +82,18 @@ __global__ void __launch_bounds__(kThreads)
   constexpr uint32_t kTmemCols = MT * BN <= 64 ? 64 : 128;
   constexpr uint32_t kIdesc = make_idesc(BM, BN, 1, 1);
   constexpr int kBytesPer = BITS == 4 ? 16 : 32;      // packed bytes of 32 weights
+
+  // grouped mode: this CTA's row tile and expert (the whole CTA leaves before any barrier,
+  // tensor-memory allocation or copy when the tile is past the rows in use)
+  const int tile_m = p.expert_ids != nullptr ? static_cast<int>(blockIdx.z) : 0;
+  long long w_off = 0, s_off = 0;
+  if (p.expert_ids != nullptr) {
+    if (tile_m * BM >= *p.num_post_pad) return;
+    const int expert = p.expert_ids[tile_m];
+    if (expert < 0) return;
+    w_off = static_cast<long long>(expert) * p.w_stride;
+    s_off = static_cast<long long>(expert) * p.s_stride;
+  }
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
@@ -125,7 +145,8 @@ __global__ void __launch_bounds__(kThreads)
         mbar_expect_tx(&full_bar[stage], MT * L::kABytes);
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
-          tma_load_2d(sa + mt * L::kABytes, &tmA, &full_bar[stage], (kb_lo + kb) * BK, mt * BM);
+          tma_load_2d(sa + mt * L::kABytes, &tmA, &full_bar[stage], (kb_lo + kb) * BK,
+                      (tile_m + mt) * BM);
         if (++stage == kStages) {
           stage = 0;
           phase ^= 1u;
@@ -183,9 +204,9 @@ __global__ void __launch_bounds__(kThreads)
       const int n = n0 + lane + 32 * r;
       n_ok[r] = n < p.N;
       const long long nn = n_ok[r] ? n : 0;
-      qrow[r] = p.qw + nn * (BITS == 4 ? p.K / 2 : p.K);
-      srow[r] = p.scales + nn * groups;
-      zrow[r] = p.zs + nn * groups;
+      qrow[r] = p.qw + w_off + nn * (BITS == 4 ? p.K / 2 : p.K);
+      srow[r] = p.scales + s_off + nn * groups;
+      zrow[r] = p.zs + s_off + nn * groups;
     }
     uint4 ring[kDepth][2][kVec];
     __nv_bfloat16 ring_s[kDepth][2][2], ring_z[kDepth][2][2];
@@ -305,7 +326,7 @@ __global__ void __launch_bounds__(kThreads)
     if (have) {
 #pragma unroll 1
       for (int mt = 0; mt < MT; ++mt) {
-        const int r = mt * BM + q * 32 + lane;
+        const int r = (tile_m + mt) * BM + q * 32 + lane;
         const uint32_t taddr =
             tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(mt * BN);
 #pragma unroll 1
@@ -323,13 +344,14 @@ __global__ void __launch_bounds__(kThreads)
             continue;
           }
           __nv_bfloat16* crow = p.C + static_cast<long long>(r) * p.ldc + col;
+          const float rs = p.row_scale != nullptr ? p.row_scale[r] : 1.0f;
           if (col + 32 <= p.N && (p.ldc & 7) == 0) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               float v[8];
 #pragma unroll
               for (int e = 0; e < 8; ++e) {
-                v[e] = __uint_as_float(acc[i * 8 + e]);
+                v[e] = __uint_as_float(acc[i * 8 + e]) * rs;
                 if (p.bias != nullptr) v[e] += __bfloat162float(p.bias[col + i * 8 + e]);
               }
               uint4 u;
@@ -343,7 +365,7 @@ __global__ void __launch_bounds__(kThreads)
 #pragma unroll
             for (int e = 0; e < 32; ++e) {
               if (col + e < p.N) {
-                float v = __uint_as_float(acc[e]);
+                float v = __uint_as_float(acc[e]) * rs;
                 if (p.bias != nullptr) v += __bfloat162float(p.bias[col + e]);
                 crow[e] = __float2bfloat16(v);
               }
@@ -395,7 +417,7 @@ static int launch(const CUtensorMap& tmA, const Args& a, cudaStream_t s) {
     if (e != cudaSuccess) return static_cast<int>(e);
     configured[dev] = true;
   }
-  dim3 grid((a.N + BN - 1) / BN, a.splits);
+  dim3 grid((a.N + BN - 1) / BN, a.splits, a.expert_ids != nullptr ? (a.M + BM - 1) / BM : 1);
   kern<<<grid, 64 + 32 * STAGES, L::kTotal, s>>>(tmA, a);
   int e = static_cast<int>(cudaGetLastError());
   if (e != 0 || a.splits == 1) return e;
@@ -443,6 +465,8 @@ B200_API int b200_gemm_wna16(const void* A, long long lda, const void* qw, const
   a.ldc = ldc; a.M = M; a.N = N; a.K = K; a.g = g;
   a.splits = ws != nullptr ? plan_splits(N, K) : 1;
   a.ws = ws;
+  a.expert_ids = nullptr; a.num_post_pad = nullptr; a.row_scale = nullptr;
+  a.w_stride = 0; a.s_stride = 0;
 
   a.status = status_ptr();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -455,4 +479,52 @@ B200_API int b200_gemm_wna16(const void* A, long long lda, const void* qw, const
                : (wide ? launch<4, 1, 4>(tmA, a, s) : launch<4, 1, 8>(tmA, a, s));
   return two ? launch<8, 2, 4>(tmA, a, s)
              : (wide ? launch<8, 1, 4>(tmA, a, s) : launch<8, 1, 8>(tmA, a, s));
+}
+
+// Grouped form for mixture-of-experts layers whose experts stay packed (the reference's
+// moe_wna16 path, vllm_gcu/kernels/quantization/moe_wna16.py:487-572): A [M_cap, K] bf16 holds
+// the expert-sorted rows in tiles of 128 (`b200_moe_align` / `b200_moe_permute`), tile t uses
+// expert expert_ids[t]; qw [E, N, K/2] (or [E, N, K] for 8 bit), scales / zs [E, N, K/g];
+// num_post_pad is the device scalar with the rows in use; row_scale (optional, [M_cap])
+// multiplies every output row (the routing weight, second GEMM).  C [M_cap, N] bf16; rows of
+// tiles past num_post_pad are not written.  Returns -20 for shapes the kernel does not cover.
+B200_API int b200_gemm_wna16_grouped(const void* A, long long lda, const void* qw,
+                                     const void* scales, const void* zs, void* C, long long ldc,
+                                     int M_cap, int N, int K, int E, int g, int bits,
+                                     const int* expert_ids, const int* num_post_pad,
+                                     const float* row_scale, void* stream) {
+  using namespace b200;
+  using namespace b200::wna16;
+  if (M_cap <= 0 || N <= 0 || E <= 0) return 0;
+  if ((M_cap % BM) != 0 || K <= 0 || (K % BK) != 0 || g < 32 || (g & (g - 1)) != 0 ||
+      (K % g) != 0 || (bits != 4 && bits != 8) || (lda % 8) != 0 ||
+      expert_ids == nullptr || num_post_pad == nullptr ||
+      ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(qw)) & 15))
+    return -20;
+  const long long w_stride = static_cast<long long>(N) * (bits == 4 ? K / 2 : K);
+  if ((w_stride & 15) != 0) return -20;
+  CUtensorMap tmA;
+  int r = encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A,
+                         static_cast<uint64_t>(M_cap), static_cast<uint64_t>(K),
+                         static_cast<uint64_t>(lda) * 2, BM, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r != 0) return r < 0 ? -6 : r;
+  Args a;
+  a.qw = static_cast<const uint8_t*>(qw);
+  a.scales = static_cast<const __nv_bfloat16*>(scales);
+  a.zs = static_cast<const __nv_bfloat16*>(zs);
+  a.bias = nullptr;
+  a.C = static_cast<__nv_bfloat16*>(C);
+  a.ldc = ldc; a.M = M_cap; a.N = N; a.K = K; a.g = g;
+  a.splits = 1;
+  a.ws = nullptr;
+  a.status = status_ptr();
+  a.expert_ids = expert_ids; a.num_post_pad = num_post_pad; a.row_scale = row_scale;
+  a.w_stride = w_stride;
+  a.s_stride = static_cast<long long>(N) * (K / g);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const long long ctas = static_cast<long long>((N + BN - 1) / BN) * (M_cap / BM);
+  const int sms = sm_count() > 0 ? sm_count() : 148;
+  const bool wide = 2 * ctas > 3 * sms;
+  if (bits == 4) return wide ? launch<4, 1, 4>(tmA, a, s) : launch<4, 1, 8>(tmA, a, s);
+  return wide ? launch<8, 1, 4>(tmA, a, s) : launch<8, 1, 8>(tmA, a, s);
 }

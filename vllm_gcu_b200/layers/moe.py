@@ -115,6 +115,70 @@ class FusedMoE(nn.Module):
         self._interleaved = False
         self.fp8_block = False
         self.q8_channel = False
+        self.wna16 = None           # (bits, group) when the experts stay packed
+
+    def enable_wna16(self, bits: int, group: int, any_device: bool = False) -> bool:
+        """Keeps the experts as packed 4 / 8-bit integers with per-group scales (AWQ / GPTQ /
+        ``moe_wna16`` checkpoints, vllm_gcu/kernels/quantization/moe_wna16.py:26-643) instead
+        of de-quantising them at load: a quarter (an eighth of fp32) of the bf16 footprint; the
+        grouped GEMM de-quantises on the fly.  Layout per expert as for the dense layers: ``q``
+        uint8 ``[N, K/2]`` (low nibble = even k) or ``[N, K]``, ``s`` and ``z = zero * scale``
+        bf16 ``[N, K/g]``.  Returns False when the shapes or the device do not allow it
+        (``any_device``: also off the GPU, where the forward de-quantises per call)."""
+        E, I, H = self.local_experts, self.inter, self.hidden
+        g = int(group)
+        if bits not in (4, 8) or g < 32 or g & (g - 1) or H % 64 or I % 64 or H % g or I % g:
+            return False
+        if not any_device and (not self.w13.is_cuda or self.w13.dtype != torch.bfloat16):
+            return False
+        dev = self.w13.device
+        self._wna16_dtype = self.w13.dtype
+        pk = 2 if bits == 4 else 1
+
+        def buf(*shape, dtype):
+            return nn.Parameter(torch.zeros(*shape, dtype=dtype, device=dev), requires_grad=False)
+        self.w13_q = buf(E, 2 * I, H // pk, dtype=torch.uint8)
+        sdt = self._wna16_dtype
+        self.w13_s = buf(E, 2 * I, H // g, dtype=sdt)
+        self.w13_z = buf(E, 2 * I, H // g, dtype=sdt)
+        self.w2_q = buf(E, H, I // pk, dtype=torch.uint8)
+        self.w2_s = buf(E, H, I // g, dtype=sdt)
+        self.w2_z = buf(E, H, I // g, dtype=sdt)
+        self.w13 = nn.Parameter(torch.empty(0, dtype=sdt, device=dev), requires_grad=False)
+        self.w2 = nn.Parameter(torch.empty(0, dtype=sdt, device=dev), requires_grad=False)
+        self.wna16 = (int(bits), g)
+        return True
+
+    def load_expert_weight_wna16(self, expert_id: int, which: str, q: torch.Tensor,
+                                 scale: torch.Tensor, zs: torch.Tensor) -> bool:
+        """Unpacked integers ``q [N, K]`` (uint8), ``scale`` and ``zs = zero * scale``
+        ``[N, K/g]`` of one projection of a logical expert."""
+        return any([self._load_one_wna16(p_, which, q, scale, zs) for p_ in self._slots(expert_id)])
+
+    def _load_one_wna16(self, expert_id: int, which: str, q: torch.Tensor, scale: torch.Tensor,
+                        zs: torch.Tensor) -> bool:
+        le = expert_id - self.expert_start
+        if le < 0 or le >= self.local_experts:
+            return False
+        bits, g = self.wna16
+        I = self.inter
+        lo = self.shard_index * I
+
+        def pack(t):
+            t = t.to(torch.uint8)
+            return (t[:, 0::2] | (t[:, 1::2] << 4)).contiguous() if bits == 4 else t
+        if which in ("gate", "up"):
+            r0 = 0 if which == "gate" else I
+            self.w13_q.data[le, r0:r0 + I].copy_(pack(q[lo:lo + I]))
+            self.w13_s.data[le, r0:r0 + I].copy_(scale[lo:lo + I])
+            self.w13_z.data[le, r0:r0 + I].copy_(zs[lo:lo + I])
+        elif which == "down":
+            self.w2_q.data[le].copy_(pack(q[:, lo:lo + I]))
+            self.w2_s.data[le].copy_(scale[:, lo // g:(lo + I) // g])
+            self.w2_z.data[le].copy_(zs[:, lo // g:(lo + I) // g])
+        else:
+            raise ValueError(which)
+        return True
 
     def enable_fp8_block(self) -> bool:
         """Keeps the experts as fp8 e4m3 with 128 x 128 block scales (the layout of DeepSeek-V3
@@ -247,7 +311,8 @@ class FusedMoE(nn.Module):
         """GPU layout: gate / up rows of every expert interleaved in blocks of
         ``ref.GATE_UP_BLOCK`` rows so the grouped GEMM applies SiLU(gate) * up in its epilogue
         (its tiles are 256 columns wide: 2 * I must be a multiple of 256)."""
-        if self._interleaved or not self.w13.is_cuda or self.w13.dtype != torch.bfloat16:
+        if self.wna16 or self._interleaved or not self.w13.is_cuda \
+                or self.w13.dtype != torch.bfloat16:
             return
         I = self.inter
         if I % 128 != 0 or self.hidden % 64 != 0:
@@ -289,6 +354,26 @@ class FusedMoE(nn.Module):
             return C.fused_experts_q8(x, self.w13, self.w13_scale, self.w2, self.w2_scale,
                                       topk_w, topk_ids, self.expert_map, add=add, alpha=alpha,
                                       valid_tokens=valid_tokens)
+        if self.wna16 and not (ops.use_native(x) and x.dtype == torch.bfloat16):
+            # reference path: de-quantise this call's experts (w = q * scale - zs)
+            bits, g = self.wna16
+
+            def deq(q, s_, z_):
+                if bits == 4:
+                    q = torch.stack([q & 0xF, q >> 4], dim=-1).flatten(-2)
+                return (q.float() * s_.float().repeat_interleave(g, -1)
+                        - z_.float().repeat_interleave(g, -1)).to(x.dtype)
+            y = ref.fused_experts(x, deq(self.w13_q, self.w13_s, self.w13_z),
+                                  deq(self.w2_q, self.w2_s, self.w2_z), topk_w, topk_ids,
+                                  self.expert_map)
+            if alpha != 1.0:
+                y = (y.float() * alpha).to(x.dtype)
+            return y if add is None else y + add
+        if self.wna16:
+            return C.fused_experts_wna16(x, self.w13_q, self.w13_s, self.w13_z, self.w2_q,
+                                         self.w2_s, self.w2_z, self.wna16[1], self.wna16[0],
+                                         topk_w, topk_ids, self.expert_map, add=add, alpha=alpha,
+                                         valid_tokens=valid_tokens)
         if self._interleaved and ops.use_native(x):
             return C.fused_experts(x, self.w13, self.w2, topk_w, topk_ids, self.expert_map,
                                    add=add, alpha=alpha, valid_tokens=valid_tokens)
@@ -378,6 +463,10 @@ class SparseMoeBlock(nn.Module):
                 self.experts.enable_q8_channel(torch.int8)
             elif kind == "fp8":
                 self.experts.enable_q8_channel(torch.float8_e4m3fn)
+            elif kind == "wna16":
+                qc = cfg.quant_config or {}
+                self.experts.enable_wna16(int(qc.get("bits", qc.get("w_bit", 4))),
+                                          int(qc.get("group_size", qc.get("q_group_size", 128))))
         phy2log = None
         map_path = cfg.extra.get("expert_map_path")
         if map_path:

@@ -6,8 +6,10 @@ w8a8 (w8a8.py:174-342) and w4a8 (w4a8.py) expert tensors by re-arranging them at
 and running a quantised grouped GEMM.  Here the expert tensors of those checkpoint formats
 are read unchanged.  On a GPU, fp8 experts with 128 x 128 block scales and int8 / fp8 experts
 with per-channel scales stay quantised and run through the grouped 8-bit tcgen05 GEMM
-(``expert_storage``); AWQ / GPTQ experts, and every format on the CPU path, are de-quantised
-**once at load time** into the bf16 expert tensors of the bf16 grouped GEMM (bf16 footprint).
+(``expert_storage``); AWQ / GPTQ experts stay packed 4 / 8-bit integers with their per-group
+scales and run through the grouped de-quantising GEMM (``b200_gemm_wna16_grouped``); every
+format on the CPU path (and shapes the kernels do not cover) is de-quantised **once at load
+time** into the bf16 expert tensors of the bf16 grouped GEMM (bf16 footprint).
 File formats and the routing / expert-parallel behaviour are the same either way.
 
 ``QuantExpertLoader`` collects the pieces of one expert projection (``qweight`` / ``qzeros``
@@ -75,10 +77,28 @@ def dequant_wna16(kind: str, bits: int, group: int, qweight: torch.Tensor, qzero
     return ((w.to(torch.float32) - zf) * sf).t().contiguous().to(dtype)
 
 
+def unpack_wna16(kind: str, bits: int, qweight: torch.Tensor, qzeros: torch.Tensor,
+                 scales: torch.Tensor, sym: bool = False):
+    """AWQ / GPTQ tensors of one projection -> integers ``q [N, K]`` (uint8), ``scale
+    [N, K/g]`` and ``zs = zero * scale [N, K/g]`` (the device layout of the de-quantising
+    GEMMs before nibble packing): ``w = q * scale - zs``."""
+    from . import unpack_awq, unpack_gptq
+    if kind == "awq":
+        w, z = unpack_awq(qweight, qzeros)              # [K, N], [K/g, N]
+    else:
+        w, z = unpack_gptq(qweight, qzeros, bits)
+        if sym:
+            z = torch.full_like(z, 1 << (bits - 1))
+    sc = scales.t().contiguous()                         # [N, K/g]
+    zs = (z.t().to(torch.float32) * sc.to(torch.float32)).to(sc.dtype).contiguous()
+    return w.t().contiguous().to(torch.uint8), sc, zs
+
+
 def expert_storage(quant_name: Optional[str], quant_cfg: Optional[dict]) -> Optional[str]:
     """How a GPU keeps the experts of a checkpoint format: ``"fp8_block"`` (fp8, 128 x 128
-    scales), ``"fp8"`` / ``"int8"`` (one scale per output channel) or None (de-quantised to
-    bf16 at load: AWQ / GPTQ / unknown block shapes)."""
+    scales), ``"fp8"`` / ``"int8"`` (one scale per output channel), ``"wna16"`` (AWQ / GPTQ
+    integers with per-group scales, packed) or None (de-quantised to bf16 at load: act-order
+    GPTQ, unknown block shapes)."""
     n = (quant_name or "").replace("_gcu", "")
     q = quant_cfg or {}
     method = {"compressed-tensors": "w8a8"}.get(q.get("quant_method", n), q.get("quant_method", n))
@@ -89,6 +109,12 @@ def expert_storage(quant_name: Optional[str], quant_cfg: Optional[dict]) -> Opti
         return "fp8"
     if method == "w8a8":
         return "int8"
+    if n in ("moe_wna16", "w4a8"):
+        method = q.get("quant_method", "awq") if q.get("quant_method") in ("awq", "gptq") \
+            else "awq"
+    if method in ("awq", "gptq") and int(q.get("bits", q.get("w_bit", 4))) in (4, 8) \
+            and not q.get("desc_act", False):
+        return "wna16"
     return None
 
 
@@ -126,6 +152,12 @@ class QuantExpertLoader:
             if self.group > 0 and not torch.equal(g, want):
                 raise ValueError("GPTQ act-order (shuffled g_idx) is not supported")
         if not all(p in d for p in _PIECES[self.kind]):
+            return
+        if self.kind in ("awq", "gptq") and getattr(moe, "wna16", None):
+            q, sc, zs = unpack_wna16(self.kind, self.bits, d["qweight"], d["qzeros"], d["scales"],
+                                     self.sym)
+            del self.pending[key]
+            moe.load_expert_weight_wna16(expert, which, q, sc, zs)
             return
         if self.kind in ("awq", "gptq"):
             w = dequant_wna16(self.kind, self.bits, self.group, d["qweight"], d["qzeros"],

@@ -110,6 +110,7 @@ class _Sigs:
     b200_mla_attention = [P, P, P, L, P, P, P, I, I, I, I, I, I, I, P, F, P]
     b200_gemm_wna16 = [P, L, P, P, P, P, P, L, I, I, I, I, I, P, P]
     b200_gemm_wna16_workspace = [I, I, I]
+    b200_gemm_wna16_grouped = [P, L, P, P, P, P, L, I, I, I, I, I, I, P, P, P, P]
     b200_sample = [P, L, I, I, I, P, P, P, P, P, L, P, P]
     b200_top_k_top_p = [P, L, I, I, I, P, P, P]
     b200_advance_step = [I, I, I, P, P, P, P, P, P, I, I, P]

@@ -777,6 +777,88 @@ def fused_experts_fp8(x: torch.Tensor, w13: torch.Tensor, w13_scale: torch.Tenso
     return out
 
 
+#: average rows per local expert up to which packed 4 / 8-bit experts run through the fused
+#: de-quantising grouped GEMM; above it the layer's experts are de-quantised into a scratch
+#: shared by all layers and the bf16 grouped GEMM runs (every row tile of the fused kernel
+#: de-quantises its expert's weights again, which only pays while tiles per expert are few)
+WNA16_GROUPED_MAX_ROWS_PER_EXPERT = 96
+_WNA16_SCRATCH: dict = {}
+
+
+def gemm_wna16_grouped(a: torch.Tensor, qw: torch.Tensor, scales: torch.Tensor, zs: torch.Tensor,
+                       expert_ids: torch.Tensor, npp: torch.Tensor, group: int, bits: int,
+                       row_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Grouped de-quantising GEMM: ``a [cap, K]`` bf16 rows sorted by expert in tiles of 128,
+    ``qw [E, N, K/2]`` (4 bit, low nibble = even k) or ``[E, N, K]`` (8 bit) uint8,
+    ``scales`` / ``zs`` ``[E, N, K/g]`` bf16 (``w = q * scale - zs``).  Returns bf16
+    ``[cap, N]`` (rows of tiles past ``npp`` are not written)."""
+    cap, K = a.shape
+    E, Nn = qw.shape[0], qw.shape[1]
+    assert qw.is_contiguous() and scales.is_contiguous() and zs.is_contiguous()
+    assert a.stride(1) == 1 and a.dtype == torch.bfloat16 and scales.dtype == torch.bfloat16
+    out = torch.empty((cap, Nn), device=a.device, dtype=torch.bfloat16)
+    call("b200_gemm_wna16_grouped", ptr(a), a.stride(0), ptr(qw), ptr(scales), ptr(zs), ptr(out),
+         out.stride(0), cap, Nn, K, E, int(group), int(bits), ptr(expert_ids), ptr(npp),
+         ptr(row_scale), stream_ptr())
+    return out
+
+
+def _wna16_scratch(name: str, shape, device) -> torch.Tensor:
+    n = 1
+    for d in shape:
+        n *= d
+    buf = _WNA16_SCRATCH.get((name, device))
+    if buf is None or buf.numel() < n:
+        buf = torch.empty(n, dtype=torch.bfloat16, device=device)
+        _WNA16_SCRATCH[(name, device)] = buf
+    return buf[:n].view(*shape)
+
+
+def fused_experts_wna16(x: torch.Tensor, q13: torch.Tensor, s13: torch.Tensor, z13: torch.Tensor,
+                        q2: torch.Tensor, s2: torch.Tensor, z2: torch.Tensor, group: int,
+                        bits: int, topk_w: torch.Tensor, topk_ids: torch.Tensor,
+                        expert_map: Optional[torch.Tensor] = None,
+                        add: Optional[torch.Tensor] = None, alpha: float = 1.0,
+                        valid_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Routed-expert MLP whose experts stay packed as 4 / 8-bit integers with per-group scales
+    (AWQ / GPTQ / ``moe_wna16`` checkpoints; vllm_gcu/kernels/quantization/moe_wna16.py:487-572):
+    align -> permute -> grouped de-quantising GEMM1 -> SiLU-mul -> grouped de-quantising GEMM2
+    scaled by the routing weight -> un-permute + sum.  ``q13 [E, 2I, H/2]`` gate rows first,
+    ``q2 [E, H, I/2]`` (``[.., K]`` for 8 bit)."""
+    T, H = x.shape
+    k = topk_ids.shape[1]
+    E, N13 = q13.shape[0], q13.shape[1]
+    numel = T * k
+    cap = moe_align_cap(numel, E)
+    sorted_ids, expert_ids, npp, pos_of = moe_align(topk_ids, E, cap, expert_map, valid_tokens)
+    a_sorted = torch.empty((cap, H), device=x.device, dtype=x.dtype)
+    call("b200_moe_permute", ptr(x), x.stride(0), ptr(a_sorted), H, ptr(sorted_ids), ptr(npp),
+         numel, k, H, cap, DTYPE_CODE[x.dtype], stream_ptr())
+    row_w = torch.empty(cap, device=x.device, dtype=torch.float32)
+    call("b200_moe_row_weights", ptr(sorted_ids), ptr(topk_w), ptr(npp), ptr(row_w), numel, cap,
+         stream_ptr())
+    if numel <= WNA16_GROUPED_MAX_ROWS_PER_EXPERT * E:
+        h = gemm_wna16_grouped(a_sorted, q13, s13, z13, expert_ids, npp, group, bits)
+        hm = activation(h, "silu", "act_mul", valid_rows=npp)
+        y = gemm_wna16_grouped(hm, q2, s2, z2, expert_ids, npp, group, bits, row_scale=row_w)
+    else:
+        I = N13 // 2
+        w13 = _wna16_scratch("w13", (E, N13, H), x.device)
+        w2 = _wna16_scratch("w2", (E, H, I), x.device)
+        weight_dequant(q13.view(E * N13, -1), s13.view(E * N13, -1), z13.view(E * N13, -1),
+                       w13.view(E * N13, H), group, bits)
+        weight_dequant(q2.view(E * H, -1), s2.view(E * H, -1), z2.view(E * H, -1),
+                       w2.view(E * H, I), group, bits)
+        h = gemm_bf16_grouped(a_sorted, w13, expert_ids, npp)
+        hm = activation(h, "silu", "act_mul", valid_rows=npp)
+        y = gemm_bf16_grouped(hm, w2, expert_ids, npp, row_scale=row_w)
+    out = torch.empty((T, H), device=x.device, dtype=x.dtype)
+    call("b200_moe_unpermute_sum", ptr(y), y.stride(0), ptr(pos_of), ptr(add),
+         add.stride(0) if add is not None else 0, ptr(out), H, ptr(valid_tokens), T, k, H,
+         float(alpha), DTYPE_CODE[x.dtype], stream_ptr())
+    return out
+
+
 def fused_experts_q8(x: torch.Tensor, w13: torch.Tensor, w13_scale: torch.Tensor,
                      w2: torch.Tensor, w2_scale: torch.Tensor, topk_w: torch.Tensor,
                      topk_ids: torch.Tensor, expert_map: Optional[torch.Tensor] = None,
