@@ -19,9 +19,78 @@ from vllm_gcu_b200.ops import ref  # noqa: E402
 from vllm_gcu_b200.parallel.state import init_distributed  # noqa: E402
 
 
+def check_etp(world: int, rank: int) -> None:
+    """ETP on GPUs: data-parallel attention without expert parallelism.  Every rank holds a
+    slice of every expert's intermediate dimension; the MoE block gathers the rows of all
+    replicas (all-gather-v over NCCL), runs its slice and scatters the sums back
+    (reduce-scatter-v).  Oracle: all experts on one device in fp32."""
+    from vllm_gcu_b200.config import preset
+    from vllm_gcu_b200.layers.moe import SparseMoeBlock
+    st = init_distributed(tp=1, dp=world, enable_ep=False)
+    dev = torch.device("cuda", st.local_rank)
+    cfg = preset("tiny-qwen3-moe", hidden_size=512, num_experts=8, num_experts_per_tok=2,
+                 moe_intermediate_size=128 * world, dtype=torch.bfloat16)
+    cfg.extra["dp_attention"] = True
+    blk = SparseMoeBlock(cfg, dev, "m")
+    assert blk.use_etp and blk.experts.inter == 128
+    E, I, H = cfg.num_experts, cfg.moe_intermediate_size, cfg.hidden_size
+    g = torch.Generator().manual_seed(1)
+    w13 = (torch.randn(E, 2 * I, H, generator=g) * 0.05).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, generator=g) * 0.05).to(torch.bfloat16)
+    gate = (torch.randn(E, H, generator=g) * 0.5).to(torch.bfloat16)
+    blk.gate.weight.data.copy_(gate)
+    for e in range(E):
+        blk.experts.load_expert_weight(e, "gate", w13[e, :I].to(dev))
+        blk.experts.load_expert_weight(e, "up", w13[e, I:].to(dev))
+        blk.experts.load_expert_weight(e, "down", w2[e].to(dev))
+    blk.experts.finalize()
+    for it, counts in enumerate([[37 + 11 * r for r in range(world)],
+                                 [0 if r == 0 else 64 for r in range(world)],
+                                 [200] * world]):
+        T = counts[rank]
+        x = (torch.randn(T, H, generator=torch.Generator().manual_seed(100 * it + rank)) * 0.5
+             ).to(torch.bfloat16)
+        with torch.inference_mode():
+            got = blk(x.to(dev))
+            if T:
+                # routing of the oracle: the same router kernel on the same logits (bf16 logits
+                # tie now and then, and a tie may be broken either way)
+                w, ids = C.moe_topk(blk.gate(x.to(dev)), 2, cfg.norm_topk_prob)
+                w, ids = w.cpu(), ids.cpu()
+        torch.cuda.synchronize()
+        _native.check_status()
+        assert got.shape == x.shape
+        if T:
+            want = ref.fused_experts(x.float(), w13.float(), w2.float(), w, ids).float()
+            err = (got.float().cpu() - want).abs().max().item()
+            tol = 0.03 * want.abs().max().item() + 0.03
+            if err >= tol and os.environ.get("B200_ETP_DIAG"):
+                # the same routing through the native kernels on unsharded experts
+                w13i = torch.stack([ref.interleave_gate_up(w13[e, :I], w13[e, I:])
+                                    for e in range(E)]).to(dev).contiguous()
+                nat = C.fused_experts(x.to(dev), w13i, w2.to(dev).contiguous(), w.to(dev),
+                                      ids.to(dev)).float().cpu()
+                per_tok = (got.float().cpu() - want).abs().amax(-1)
+                print(f"[diag rank {rank} case {it}] native-vs-ref "
+                      f"{(nat - want).abs().max().item():.4f} etp-vs-native "
+                      f"{(got.float().cpu() - nat).abs().max().item():.4f} bad tokens "
+                      f"{(per_tok > tol).nonzero().flatten().tolist()} of {T}; "
+                      f"ratio got/want {(got.float().cpu().norm() / want.norm()).item():.4f}",
+                      flush=True)
+            assert err < tol, f"etp case {it} rank {rank}: err {err} tol {tol}"
+        dist.barrier()
+    if rank == 0:
+        print(f"etp{world} gather/scatter ok", flush=True)
+    dist.barrier()
+    sys.stdout.flush()
+    os._exit(0)
+
+
 def main():
     world = int(os.environ["WORLD_SIZE"])
     rank = int(os.environ["RANK"])
+    if os.environ.get("B200_EP_MODE") == "etp":
+        check_etp(world, rank)
     st = init_distributed(tp=1, dp=world, enable_ep=True)
     dev = torch.device("cuda", st.local_rank)
     E, k, H, I = 8 * world, 4, 512, 256

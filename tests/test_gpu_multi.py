@@ -63,3 +63,17 @@ def test_expert_parallel_fused_dispatch_two_gpus():
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert "fused dispatch/combine ok" in res.stdout
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2,
+                    reason="needs >= 2 GPUs")
+def test_etp_gather_scatter_two_gpus():
+    """Data-parallel attention without expert parallelism: experts sharded over the replicas,
+    rows gathered and sums scattered back over NCCL."""
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", B200_EP_MODE="etp")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+           "--master-addr", "127.0.0.1", "--master-port", "29619",
+           os.path.join(ROOT, "tests", "_ep_worker.py")]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert "gather/scatter ok" in res.stdout
