@@ -116,7 +116,8 @@ __device__ __forceinline__ void load_kv_tile(T* sK, T* sV, const KvView& kv, int
     const int tok = t0 + row;
     T* dk = sK + row * kStride + ch * 8;
     T* dv = sV + row * kStride + ch * 8;
-    bool ok = tok < kv_end;
+    // a sequence longer than its block-table row reads zeros past the row, never the next row
+    bool ok = tok < kv_end && tok / kv.block_size < kv.max_blocks;
     long long slot = 0;
     if (ok) {
       const int blk = bt[tok / kv.block_size];
