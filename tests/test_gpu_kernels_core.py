@@ -71,9 +71,10 @@ def test_gemm_skinny_decode_shapes(C, M, N, K, monkeypatch):
 
 
 @pytest.mark.parametrize("M,N,K", [(1100, 512, 320), (2048, 1024, 4096), (1024, 256, 64)])
-def test_gemm_wide2_large_m(C, M, N, K):
+def test_gemm_wide2_large_m(C, M, N, K, monkeypatch):
     """Persistent 256 x 256 tile kernel (large M, N a multiple of 256): plain, bias and
     SiLU-mul epilogues, ragged last row tile."""
+    monkeypatch.setattr(C, "USE_PAIR_GEMM", False)
     assert C.USE_WIDE2_GEMM and M >= C.WIDE2_MIN_M
     a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
     b = (torch.randn(N, K, device="cuda") / math.sqrt(K)).to(torch.bfloat16)
@@ -85,6 +86,38 @@ def test_gemm_wide2_large_m(C, M, N, K):
     w4 = want.view(M, N // 64, 2, 32)
     _close(got, (torch.nn.functional.silu(w4[:, :, 0]) * w4[:, :, 1]).reshape(M, N // 2),
            3e-2, 3e-2)
+
+
+@pytest.mark.parametrize("mt", ["1", "2"])
+@pytest.mark.parametrize("M,N,K", [(1100, 512, 320 + 64), (2048, 1024, 4096), (1024, 256, 64),
+                                   (4096, 3584, 4096), (8192, 768, 512)])
+def test_gemm_cta_pair_large_m(C, M, N, K, mt, monkeypatch):
+    """One output tile per pair of CTAs (`tcgen05.mma.cta_group::2`, a cluster of two): plain,
+    bias and SiLU-mul epilogues, ragged last row tile, both tile shapes (256 x 256 with two
+    accumulator sets, 512 x 256 with one), repeated launches."""
+    monkeypatch.setenv("VLLM_B200_PAIR_MT", mt)
+    assert C.USE_PAIR_GEMM and M >= C.WIDE2_MIN_M
+    torch.manual_seed(M + N + K)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = (torch.randn(N, K, device="cuda") / math.sqrt(K)).to(torch.bfloat16)
+    want = ref.gemm(a, b, out_dtype=torch.float32)
+    direct = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    rc = _native.lib().b200_gemm_pair(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0),
+                                      direct.data_ptr(), N, M, N, K, None, 0,
+                                      _native.stream_ptr())
+    assert rc == 0, rc                         # the pair kernel takes this shape on this device
+    _close(direct, want, 2e-2, 2e-2)
+    first = C.gemm_bf16(a, b)
+    _close(first, want, 2e-2, 2e-2)
+    assert torch.equal(C.gemm_bf16(a, b), first)
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    _close(C.gemm_bf16(a, b, bias=bias), want + bias.float(), 2e-2, 3e-2)
+    got = C.gemm_bf16(a, b, epilogue=C.EPI_SILU_MUL)
+    w4 = want.view(M, N // 64, 2, 32)
+    _close(got, (torch.nn.functional.silu(w4[:, :, 0]) * w4[:, :, 1]).reshape(M, N // 2),
+           3e-2, 3e-2)
+    torch.cuda.synchronize()
+    _native.check_status()
 
 
 def test_gemm_bf16_epilogues(C):

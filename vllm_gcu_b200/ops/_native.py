@@ -125,6 +125,7 @@ class _Sigs:
     b200_gemm_skinny = [P, L, P, L, P, L, I, I, I, P, I, P, P, I, P]
     b200_gemm_skinny_workspace = [I, P, P]
     b200_gemm_wide2 = [P, L, P, L, P, L, I, I, I, P, I, P]
+    b200_gemm_pair = [P, L, P, L, P, L, I, I, I, P, I, P]
     b200_gemm_skinny_plan = [I, I, I, I, P, P]
     b200_gemm_q8 = [P, L, P, L, P, L, I, I, I, P, L, P, L, P, I, P]
     b200_gemm_q8_grouped = [P, L, P, L, P, L, I, I, I, I, P, L, P, L, P, P, P, I, P]

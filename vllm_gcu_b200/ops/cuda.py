@@ -67,6 +67,7 @@ def oracle_compare(name: str, got: torch.Tensor, want: torch.Tensor, rtol: float
 
 
 # Decode-sized activations (M <= 256) take the weight-streaming kernel of gemm_skinny.cu.
+USE_PAIR_GEMM = True            # 256 x 256 tile per CTA pair, cta_group::2 (gemm_pair.cu)
 USE_WIDE2_GEMM = True           # persistent 256 x 256 tiles for large M (gemm_skinny.cu)
 WIDE2_MIN_M = 1024
 USE_SKINNY_GEMM = True
@@ -158,6 +159,16 @@ def _gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = N
             return out
         if rc != -20:
             raise N.NativeError(f"b200_gemm_skinny failed with code {rc}")
+    if (USE_PAIR_GEMM and M >= WIDE2_MIN_M and Nn % 256 == 0 and K % 64 == 0
+            and epilogue in (EPI_NONE, EPI_BIAS, EPI_SILU_MUL) and _wide2_pays(M, Nn)):
+        # one 256 x 256 tile per pair of CTAs (gemm_pair.cu); -20 = shape or device not covered
+        rc = N.lib().b200_gemm_pair(ptr(a), a.stride(0), ptr(b), b.stride(0), ptr(out),
+                                    out.stride(0), M, Nn, K, ptr(bias), epilogue, stream_ptr())
+        N.launch_count += 1
+        if rc == 0:
+            return out
+        if rc != -20:
+            raise N.NativeError(f"b200_gemm_pair failed with code {rc}")
     if (USE_WIDE2_GEMM and M >= WIDE2_MIN_M and Nn % 256 == 0
             and epilogue in (EPI_NONE, EPI_BIAS, EPI_SILU_MUL) and _wide2_pays(M, Nn)):
         rc = N.lib().b200_gemm_wide2(ptr(a), a.stride(0), ptr(b), b.stride(0), ptr(out),
