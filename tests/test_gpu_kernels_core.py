@@ -50,6 +50,7 @@ def test_gemm_skinny_decode_shapes(C, M, N, K, monkeypatch):
     same result as the fp32 reference, also on repeated launches (the counters must come back
     to zero) and identical to the persistent-tile kernel within bf16 rounding."""
     assert C.USE_SKINNY_GEMM and M <= C.SKINNY_MAX_M
+    monkeypatch.setattr(C, "USE_PAIR_GEMM", False)          # (wide shapes would go to CTA pairs)
     monkeypatch.setattr(C, "SKINNY_ALLOW_SPLIT", True)      # exercise the split-K path too
     a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
     b = (torch.randn(N, K, device="cuda") / math.sqrt(K)).to(torch.bfloat16)
@@ -90,13 +91,15 @@ def test_gemm_wide2_large_m(C, M, N, K, monkeypatch):
 
 @pytest.mark.parametrize("mt", ["1", "2"])
 @pytest.mark.parametrize("M,N,K", [(1100, 512, 320 + 64), (2048, 1024, 4096), (1024, 256, 64),
-                                   (4096, 3584, 4096), (8192, 768, 512)])
+                                   (4096, 3584, 4096), (8192, 768, 512), (256, 28672, 512),
+                                   (200, 16384, 256), (600, 8192, 128)])
 def test_gemm_cta_pair_large_m(C, M, N, K, mt, monkeypatch):
     """One output tile per pair of CTAs (`tcgen05.mma.cta_group::2`, a cluster of two): plain,
     bias and SiLU-mul epilogues, ragged last row tile, both tile shapes (256 x 256 with two
     accumulator sets, 512 x 256 with one), repeated launches."""
     monkeypatch.setenv("VLLM_B200_PAIR_MT", mt)
-    assert C.USE_PAIR_GEMM and M >= C.WIDE2_MIN_M
+    assert C.USE_PAIR_GEMM and (M >= C.WIDE2_MIN_M or
+                                -(-M // 256) * (N // 256) >= C.PAIR_MIN_TILES)
     torch.manual_seed(M + N + K)
     a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
     b = (torch.randn(N, K, device="cuda") / math.sqrt(K)).to(torch.bfloat16)
