@@ -2,6 +2,7 @@
 import json
 import os
 
+import pytest
 import torch
 
 from vllm_gcu_b200.config import ModelConfig, preset
@@ -62,3 +63,33 @@ def test_safetensors_roundtrip_and_engine_load(tmp_path):
     assert all(torch.equal(got[k], want[k]) for k in want)
     outs = llm.generate([[1, 2, 3, 4, 5]], SamplingParams(max_tokens=4))
     assert len(outs[0].outputs[0].token_ids) == 4
+
+
+def test_kv_cache_scales_from_checkpoint_and_parameter_file(tmp_path):
+    """Scales of an 8-bit KV cache: ``k_scale`` / ``v_scale`` / ``kv_scale`` tensors of a
+    checkpoint, and the quantisation-parameter file (scaling_factor[tp_rank][layer]) in its
+    three value forms."""
+    cfg = preset("tiny-llama")
+    model = build_model(cfg, "cpu")
+    model.init_random(0)
+    loaded = model.load_weights([("model.layers.0.self_attn.k_scale", torch.tensor(0.03)),
+                                 ("model.layers.0.self_attn.v_scale", torch.tensor([0.05])),
+                                 ("model.layers.1.self_attn.attn.kv_scale", torch.tensor(0.07))])
+    assert len(loaded) == 3
+    a0, a1 = model.layers["0"].self_attn.attn, model.layers["1"].self_attn.attn
+    assert (a0.k_scale, a0.v_scale) == (pytest.approx(0.03), pytest.approx(0.05))
+    assert (a1.k_scale, a1.v_scale) == (pytest.approx(0.07), pytest.approx(0.07))
+    path = tmp_path / "int8_kv_cache.json"
+    path.write_text(json.dumps({"model_type": "llama", "kv_cache": {
+        "dtype": "int8", "scaling_factor": {"0": {"0": 0.011, "1": [0.02, 0.04]},
+                                            "1": {"0": 9.0, "1": 9.0}}}}))
+    llm = LLM("tiny-llama", device="cpu", max_num_seqs=2, max_num_batched_tokens=32,
+              max_model_len=64, num_gpu_blocks=16, quantization_param_path=str(path))
+    l0 = llm.engine.model.layers["0"].self_attn.attn
+    l1 = llm.engine.model.layers["1"].self_attn.attn
+    assert (l0.k_scale, l0.v_scale) == (pytest.approx(0.011), pytest.approx(0.011))
+    assert (l1.k_scale, l1.v_scale) == (pytest.approx(0.02), pytest.approx(0.04))
+    path.write_text(json.dumps({"kv_cache": {"scaling_factor": {"0": {
+        "1": {"k_scale": 0.5, "v_scale": 0.25}}}}}))
+    assert llm.engine.model.load_kv_cache_scales(str(path)) == 1
+    assert (l1.k_scale, l1.v_scale) == (0.5, 0.25)

@@ -299,6 +299,7 @@ class EngineConfig:
     cuda_graph_sizes: Optional[list[int]] = None
     load_format: str = "dummy"             # "dummy" (random init) | "safetensors"
     model_path: Optional[str] = None
+    quantization_param_path: Optional[str] = None   # JSON with the scales of an 8-bit KV cache
     additional_config: dict = field(default_factory=dict)
 
     def __post_init__(self) -> None:

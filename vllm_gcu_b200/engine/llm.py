@@ -52,6 +52,8 @@ class LLMEngine:
         elif cfg.load_format == "safetensors":
             from ..utils.weights import iter_safetensors
             self.model.load_weights(iter_safetensors(cfg.model_path))
+        if cfg.quantization_param_path:
+            self.model.load_kv_cache_scales(cfg.quantization_param_path)
         self.model.eval()
         if pc.world_size > 1 and pc.comm_backend == "fused" and self.device.type == "cuda":
             from ..parallel import symm
@@ -391,7 +393,8 @@ class LLM:
                  speculative_model: Optional[str] = None,
                  prompt_lookup_max: int = 4, prompt_lookup_min: int = 1,
                  enable_lora: bool = False, max_loras: int = 4, max_lora_rank: int = 16,
-                 additional_config: Optional[dict] = None, tokenizer=None, **model_overrides):
+                 additional_config: Optional[dict] = None, tokenizer=None,
+                 quantization_param_path: Optional[str] = None, **model_overrides):
         model_path = None
         if isinstance(model, ModelConfig):
             mc = model
@@ -428,7 +431,8 @@ class LLM:
             device=device, seed=seed, enforce_eager=enforce_eager,
             cuda_graph_sizes=cuda_graph_sizes,
             load_format=load_format or ("safetensors" if model_path else "dummy"),
-            model_path=model_path, additional_config=additional_config or {})
+            model_path=model_path, additional_config=additional_config or {},
+            quantization_param_path=quantization_param_path)
         self.engine = LLMEngine(cfg)
         # text in / text out: a tokenizer object (``encode`` / ``decode``) or a directory
         # with tokenizer files; by default the tokenizer next to the checkpoint

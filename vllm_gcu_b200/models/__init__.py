@@ -22,6 +22,9 @@ _REGISTRY: dict[str, str] = {
     "ChatGLMModel": "vllm_gcu_b200.models.llama:ChatGLMForCausalLM",
     "ChatGLMForConditionalGeneration": "vllm_gcu_b200.models.llama:ChatGLMForCausalLM",
     "YiForCausalLM": "vllm_gcu_b200.models.llama:LlamaForCausalLM",
+    # the reference registers this name for a customer's Llama variant
+    # (vllm_gcu/models/__init__.py:29-31); the architecture is Llama's
+    "CustomerLlaMAForCausalLM": "vllm_gcu_b200.models.llama:LlamaForCausalLM",
     "Qwen3MoeForCausalLM": "vllm_gcu_b200.models.moe_models:Qwen3MoeForCausalLM",
     "MixtralForCausalLM": "vllm_gcu_b200.models.moe_models:MixtralForCausalLM",
     "QuantMixtralForCausalLM": "vllm_gcu_b200.models.moe_models:MixtralForCausalLM",

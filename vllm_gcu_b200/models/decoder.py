@@ -474,6 +474,9 @@ class DecoderLM(nn.Module):
         owners = self.named_loadables()
         loaded: set[str] = set()
         for name, tensor in weights:
+            if self._load_kv_scale(name, tensor):
+                loaded.add(name)
+                continue
             if self.load_special(name, tensor, owners):
                 loaded.add(name)
                 continue
@@ -491,6 +494,56 @@ class DecoderLM(nn.Module):
             fin()
         self.finalize_weights()
         return loaded
+
+    def _load_kv_scale(self, name: str, tensor: torch.Tensor) -> bool:
+        """Per-tensor scales of an 8-bit KV cache stored in the checkpoint
+        (``...self_attn.k_scale`` / ``v_scale``, or one ``kv_scale`` for both; also under
+        ``...self_attn.attn.``): value = stored * scale."""
+        for suf in ("k_scale", "v_scale", "kv_scale"):
+            for mid in (".self_attn.", ".self_attn.attn."):
+                if name.endswith(mid + suf) and name.startswith("model.layers."):
+                    layer = self.layers[name.split(".")[2]] if name.split(".")[2] in self.layers \
+                        else None
+                    attn = getattr(getattr(layer, "self_attn", None), "attn", None)
+                    if attn is not None and hasattr(attn, "k_scale"):
+                        v = float(tensor.float().reshape(-1)[0])
+                        if suf in ("k_scale", "kv_scale"):
+                            attn.k_scale = v
+                        if suf in ("v_scale", "kv_scale"):
+                            attn.v_scale = v
+                        attn._scale_t = None
+                    return True
+        return False
+
+    def load_kv_cache_scales(self, path: str) -> int:
+        """Scales of an 8-bit KV cache from a quantisation-parameter file
+        (``--quantization-param-path`` of the reference's launch lines, e.g.
+        vllm_gcu/models/glm/glm.md ``int8_kv_cache.json``; schema of
+        ``load_kv_cache_scales`` that vllm_gcu/models/deepseek_moe_quant/deepseek_moe_quant.py:
+        487-489 calls): ``{"kv_cache": {"dtype": ..., "scaling_factor": {tp_rank: {layer: s}}}}``
+        where ``s`` is one number for keys and values, a ``[k, v]`` pair or
+        ``{"k_scale": .., "v_scale": ..}``.  Returns the number of layers that got scales."""
+        import json
+        from ..parallel.state import tp_rank as _tp_rank
+        with open(path) as f:
+            doc = json.load(f)
+        table = (doc.get("kv_cache") or {}).get("scaling_factor") or {}
+        per_layer = table.get(str(_tp_rank()), table.get("0", {}))
+        n = 0
+        for idx, val in per_layer.items():
+            layer = self.layers[str(idx)] if str(idx) in self.layers else None
+            attn = getattr(getattr(layer, "self_attn", None), "attn", None)
+            if attn is None or not hasattr(attn, "k_scale"):
+                continue
+            if isinstance(val, dict):
+                k, v = val.get("k_scale", val.get("k", 1.0)), val.get("v_scale", val.get("v", 1.0))
+            elif isinstance(val, (list, tuple)):
+                k, v = val[0], val[-1]
+            else:
+                k = v = val
+            attn.k_scale, attn.v_scale, attn._scale_t = float(k), float(v), None
+            n += 1
+        return n
 
     def finalize_weights(self) -> None:
         for mod in self.modules():
