@@ -154,3 +154,35 @@ def test_image_rows_merge_like_extra_tokens(mla):
     want = twin.engine.runner.last_logits[0]
     assert torch.allclose(got[:320], want[:320], atol=1e-4), (got[:320] - want[:320]).abs().max()
     assert out[0].outputs[0].token_ids[0] == int(got.argmax())
+
+
+def test_image_tiling_and_placeholder_expansion():
+    """The processor side: best candidate resolution, global view + local tiles, and one
+    placeholder per embedding row."""
+    cands = [[56, 56], [112, 56], [56, 112], [112, 112], [168, 56]]
+    assert M.select_best_resolution((200, 100), cands) == (112, 56)
+    assert M.select_best_resolution((50, 50), cands) == (56, 56)
+    assert M.select_best_resolution((60, 300), cands) == (56, 112)
+    img = torch.rand(3, 100, 200)
+    px, crops = M.process_images([img, torch.rand(3, 40, 40)], cands, image_size=56)
+    assert crops == [(2, 1), (1, 1)] and px.shape == (1 + 2 + 1 + 1, 3, 56, 56)
+    assert float(px.min()) >= -1.0 - 1e-6 and float(px.max()) <= 1.0 + 1e-6
+    # the wide image fills the 112 x 56 canvas: its two local tiles are its left and right half
+    left = torch.nn.functional.interpolate(img[None], size=(56, 112), mode="bicubic",
+                                           align_corners=False, antialias=True)[0].clamp(0, 1)
+    assert torch.allclose(px[1], (left[:, :, :56] - 0.5) / 0.5, atol=1e-5)
+    assert torch.allclose(px[2], (left[:, :, 56:] - 0.5) / 0.5, atol=1e-5)
+    # the global view letter-boxes the image with the mean colour (0 after normalisation)
+    assert torch.allclose(px[0][:, 0], torch.zeros(3, 56), atol=1e-6)
+    d = _hf_config(False)
+    d["candidate_resolutions"] = cands
+    mc = ModelConfig.from_hf_dict(d, dtype=torch.float32)
+    llm = LLM(mc, device="cpu", max_num_seqs=2, max_num_batched_tokens=64, max_model_len=256,
+              num_gpu_blocks=64, seed=0)
+    model = llm.engine.model
+    ids, mm = model.prepare_images([img, torch.rand(3, 40, 40)], [5, 300, 6, 300, 7])
+    n0, n1 = model.num_image_tokens((2, 1)), model.num_image_tokens((1, 1))
+    assert ids == [5] + [300] * n0 + [6] + [300] * n1 + [7]
+    out = llm.generate([{"prompt_token_ids": ids, "multi_modal_data": mm}],
+                       SamplingParams(max_tokens=2, temperature=0.0, ignore_eos=True))
+    assert len(out[0].outputs[0].token_ids) == 2

@@ -165,6 +165,59 @@ def tile_embeddings(feats: torch.Tensor, crops: Sequence[Sequence[int]], newline
     return torch.cat(out, dim=0)
 
 
+def select_best_resolution(image_size: Sequence[int], candidates: Sequence[Sequence[int]]
+                           ) -> tuple[int, int]:
+    """The candidate ``(width, height)`` that keeps the most of the image's resolution when the
+    image is scaled to fit inside it, ties broken by the least unused area (the rule of the
+    DeepSeek-VL2 processor)."""
+    ow, oh = int(image_size[0]), int(image_size[1])
+    best, best_fit, min_waste = None, -1, float("inf")
+    for w, h in candidates:
+        scale = min(w / ow, h / oh)
+        dw, dh = int(ow * scale), int(oh * scale)
+        eff = min(dw * dh, ow * oh)
+        waste = w * h - eff
+        if eff > best_fit or (eff == best_fit and waste < min_waste):
+            best, best_fit, min_waste = (int(w), int(h)), eff, waste
+    return best
+
+
+def _fit_and_pad(img: torch.Tensor, width: int, height: int, fill: float) -> torch.Tensor:
+    """``img [3, H, W]`` scaled (aspect ratio kept, bicubic) to fit ``width x height`` and
+    centred on a canvas of that size filled with ``fill``."""
+    _, h, w = img.shape
+    scale = min(width / w, height / h)
+    nw, nh = max(1, min(width, round(w * scale))), max(1, min(height, round(h * scale)))
+    r = F.interpolate(img[None], size=(nh, nw), mode="bicubic", align_corners=False,
+                      antialias=True)[0].clamp(0.0, 1.0)
+    out = torch.full((3, height, width), fill, dtype=img.dtype)
+    y0, x0 = (height - nh) // 2, (width - nw) // 2
+    out[:, y0:y0 + nh, x0:x0 + nw] = r
+    return out
+
+
+def process_images(images: Sequence[torch.Tensor], candidate_resolutions: Sequence[Sequence[int]],
+                   image_size: int = 384, mean: float = 0.5, std: float = 0.5):
+    """Tiles images the way the model expects them: per image one global view (the whole image
+    fitted into ``image_size x image_size``) followed by the local tiles of the image fitted
+    into the best candidate resolution, row by row.  ``images``: float ``[3, H, W]`` in
+    [0, 1].  Returns ``(pixel_values [tiles, 3, S, S]`` normalised with ``mean`` / ``std``,
+    ``images_spatial_crop [(num_w, num_h), ...])``."""
+    tiles, crops = [], []
+    S = int(image_size)
+    for img in images:
+        img = img.float()
+        bw, bh = select_best_resolution((img.shape[2], img.shape[1]), candidate_resolutions)
+        tiles.append(_fit_and_pad(img, S, S, mean))
+        local = _fit_and_pad(img, bw, bh, mean)
+        for y in range(0, bh, S):
+            for x in range(0, bw, S):
+                tiles.append(local[:, y:y + S, x:x + S])
+        crops.append((bw // S, bh // S))
+    px = (torch.stack(tiles) - mean) / std
+    return px, crops
+
+
 class _VL2Mixin:
     """Vision side of DeepSeek-VL2 on top of one of the DeepSeek language models."""
 
@@ -204,6 +257,22 @@ class _VL2Mixin:
         num_w, num_h = int(crop[0]), int(crop[1])
         local = (num_h * h) * (num_w * h + 1) if num_w * num_h > 0 else 0
         return h * (h + 1) + 1 + local
+
+    def prepare_images(self, images: Sequence[torch.Tensor], prompt_token_ids: Sequence[int]):
+        """From raw images to engine inputs: tiles the images and expands every single image
+        placeholder of the prompt to as many placeholders as that image has embedding rows.
+        Returns ``(prompt_token_ids, multi_modal_data)`` for ``LLM.generate``."""
+        cands = self.cfg.extra.get("candidate_resolutions") or [[self.vision_cfg.image_size] * 2]
+        px, crops = process_images(images, cands, self.vision_cfg.image_size)
+        out, k = [], 0
+        for t in prompt_token_ids:
+            if t == self.image_token_id and k < len(crops):
+                out.extend([self.image_token_id] * self.num_image_tokens(crops[k]))
+                k += 1
+            else:
+                out.append(int(t))
+        assert k == len(crops), "one image placeholder per image is expected in the prompt"
+        return out, {"pixel_values": px, "images_spatial_crop": crops}
 
     def encode_images(self, pixel_values: torch.Tensor, images_spatial_crop) -> torch.Tensor:
         feats = self.projector(self.vision(pixel_values))
