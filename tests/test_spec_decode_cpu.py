@@ -88,3 +88,46 @@ def test_draft_heads_propose_shapes():
         q = cls(64, 100, 3, dtype=torch.float32)
         assert len(q.load_weights(sd.items())) == len(sd)
         assert torch.equal(q.propose(h, last), out)
+
+
+def test_eagle_spec_decode_is_lossless_and_loads_its_checkpoint(tmp_path):
+    """EAGLE draft head (fc + one decoder layer without input norm, target's embedding and LM
+    head): greedy outputs are those of the target alone; a head whose weights make it repeat
+    the target's own next-token computation is loaded from a checkpoint in the EAGLE layout."""
+    from vllm_gcu_b200.spec import EagleDrafter
+    from vllm_gcu_b200.utils.weights import write_safetensors
+    _, base = _run("tiny-llama", n_out=12)
+    llm, spec = _run("tiny-llama", n_out=12, speculative_method="eagle",
+                     num_speculative_tokens=1)
+    assert base == spec
+    m = llm.engine.spec_metrics
+    assert m.num_drafts > 0
+    d = llm.engine.runner.drafter
+    assert isinstance(d, EagleDrafter) and len(llm.engine.runner.drafter_caches) == 1
+    # checkpoint round trip in the EAGLE layout (q / k / v and gate / up as separate tensors)
+    cfg = llm.engine.cfg.model
+    D, Hq, Hkv, I = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads, \
+        cfg.intermediate_size
+    sd = {}
+    for name, p in d.state_dict().items():
+        if ".qkv_proj.weight" in name:
+            q, k, v = p.split([Hq * D, Hkv * D, Hkv * D], 0)
+            for n, t in (("q_proj", q), ("k_proj", k), ("v_proj", v)):
+                sd[name.replace("qkv_proj", n)] = t.clone() + 0.01
+        elif ".gate_up_proj.weight" in name:
+            g, u = p.split([I, I], 0)
+            sd[name.replace("gate_up_proj", "gate_proj")] = g.clone() + 0.01
+            sd[name.replace("gate_up_proj", "up_proj")] = u.clone() + 0.01
+        elif "input_layernorm" not in name:
+            sd[name] = p.clone() + 0.01
+    sd["embed_tokens.weight"] = torch.zeros(4, 4)            # ignored: the target's is shared
+    write_safetensors(str(tmp_path / "model.safetensors"), sd)
+    before = {k: v.clone() for k, v in d.state_dict().items()}
+    llm2, spec2 = _run("tiny-llama", n_out=12, speculative_method="eagle",
+                       num_speculative_tokens=1, speculative_model=str(tmp_path))
+    assert spec2 == base
+    after = llm2.engine.runner.drafter.state_dict()
+    for k, v in before.items():
+        if "input_layernorm" in k:
+            continue
+        assert torch.allclose(after[k], v + 0.01, atol=1e-6), k

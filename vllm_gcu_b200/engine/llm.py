@@ -90,6 +90,17 @@ class LLMEngine:
                     drafter.load_weights(iter_safetensors(cfg.model_path))
                 drafter.eval()
                 self.runner.drafter = drafter
+            elif sp.method == "eagle":
+                from ..spec.eagle import EagleDrafter
+                if sp.num_speculative_tokens != 1:
+                    raise ValueError("the EAGLE drafter proposes one token per step")
+                drafter = EagleDrafter(cfg.model, self.device, target=self.model)
+                if sp.draft_model:
+                    from ..utils.weights import iter_safetensors
+                    drafter.load_weights(iter_safetensors(sp.draft_model))
+                else:
+                    drafter.init_random(cfg.seed)
+                self.runner.drafter = drafter.eval()
             elif sp.method in ("medusa", "mlp_speculator"):
                 from ..spec import MedusaProposer, MLPSpeculatorProposer
                 mc_ = cfg.model
