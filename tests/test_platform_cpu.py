@@ -67,3 +67,16 @@ def test_utilities():
     for name in ("fp8_gcu", "awq_gcu", "gptq_gcu", "w8a8_gcu", "moe_wna16_gcu", "w4a8_gcu"):
         assert name in SUPPORTED_QUANTIZATION
     assert torch.float8_e4m3fn is not None
+
+
+def test_host_sanitizer_build_options():
+    """``csrc/build.py --sanitize``: flags, separate object directory and library name."""
+    import pytest
+    from vllm_gcu_b200.csrc import build as B
+    assert B.sanitize_flags(None) == []
+    fl = B.sanitize_flags("address")
+    assert fl[0] == "-Xcompiler" and "-fsanitize=address" in fl[1]
+    assert B.lib_path_for(None).name == "_b200.so"
+    assert B.lib_path_for("thread").name == "_b200.thread.so"
+    with pytest.raises(ValueError):
+        B.sanitize_flags("memory")

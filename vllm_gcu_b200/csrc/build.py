@@ -6,7 +6,14 @@ are linked into one shared library next to the Python package, where
 ``vllm_gcu_b200.ops._native`` loads it with ctypes.  nvcc cross-compiles, so
 the build runs on a machine without a GPU.
 
-Usage: ``python -m vllm_gcu_b200.csrc.build [--force] [--verbose] [-j N]``
+Usage: ``python -m vllm_gcu_b200.csrc.build [--force] [--verbose] [-j N] [--sanitize KIND]``
+
+``--sanitize address|thread|undefined`` instruments the host side of the library (launch
+wrappers, tensor-map encoding, workspace caches, status word plumbing) with the compiler's
+sanitizer and writes ``_b200.<kind>.so`` beside the normal build; run with it through
+``VLLM_B200_NATIVE_LIB=<that file>`` and the sanitizer runtime preloaded, e.g.
+``LD_PRELOAD=$(gcc -print-file-name=libasan.so) VLLM_B200_NATIVE_LIB=... python -m pytest ...``.
+Device code is not instrumented (the device-side checker is a separate tool).
 """
 from __future__ import annotations
 
@@ -48,11 +55,29 @@ def _digest(path: Path, extra: str) -> str:
     return h.hexdigest()
 
 
-def _compile_one(src: Path, force: bool, verbose: bool) -> Path:
-    OBJ_DIR.mkdir(exist_ok=True)
-    obj = OBJ_DIR / (src.stem + ".o")
-    stamp = OBJ_DIR / (src.stem + ".sha")
-    flags = list(NVCC_FLAGS)
+SANITIZERS = {"address": "-fsanitize=address", "thread": "-fsanitize=thread",
+              "undefined": "-fsanitize=undefined"}
+
+
+def sanitize_flags(kind: str | None) -> list[str]:
+    """Extra nvcc flags of a host-sanitizer build (empty for the normal build)."""
+    if not kind:
+        return []
+    if kind not in SANITIZERS:
+        raise ValueError(f"unknown sanitizer {kind!r}; known: {sorted(SANITIZERS)}")
+    return ["-Xcompiler", f"{SANITIZERS[kind]},-fno-omit-frame-pointer,-g"]
+
+
+def lib_path_for(kind: str | None) -> Path:
+    return LIB_PATH if not kind else PKG / f"_b200.{kind}.so"
+
+
+def _compile_one(src: Path, force: bool, verbose: bool, sanitize: str | None = None) -> Path:
+    obj_dir = OBJ_DIR if not sanitize else CSRC / f"build_{sanitize}"
+    obj_dir.mkdir(exist_ok=True)
+    obj = obj_dir / (src.stem + ".o")
+    stamp = obj_dir / (src.stem + ".sha")
+    flags = list(NVCC_FLAGS) + sanitize_flags(sanitize)
     if verbose:
         flags += ["-Xptxas", "-v"]
     dig = _digest(src, " ".join(flags))
@@ -68,23 +93,27 @@ def _compile_one(src: Path, force: bool, verbose: bool) -> Path:
     return obj
 
 
-def build(force: bool = False, verbose: bool = False, jobs: int | None = None) -> Path:
+def build(force: bool = False, verbose: bool = False, jobs: int | None = None,
+          sanitize: str | None = None) -> Path:
     """Compiles what changed and links the library.  Returns its path."""
     srcs = sorted(CSRC.glob("*.cu"))
     if not srcs:
         raise RuntimeError("no CUDA sources found")
     jobs = jobs or min(len(srcs), os.cpu_count() or 4)
     with cf.ThreadPoolExecutor(max_workers=jobs) as ex:
-        objs = list(ex.map(lambda s: _compile_one(s, force, verbose), srcs))
+        objs = list(ex.map(lambda s: _compile_one(s, force, verbose, sanitize), srcs))
     newest = max(o.stat().st_mtime for o in objs)
-    if force or not LIB_PATH.exists() or LIB_PATH.stat().st_mtime < newest:
-        cmd = [nvcc_path(), "-shared", "-o", str(LIB_PATH), *map(str, objs),
+    out = lib_path_for(sanitize)
+    if force or not out.exists() or out.stat().st_mtime < newest:
+        cmd = [nvcc_path(), "-shared", "-o", str(out), *map(str, objs),
                "-gencode", "arch=compute_100a,code=sm_100a", "-lcudart"]
+        if sanitize:
+            cmd += ["-Xcompiler", SANITIZERS[sanitize]]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             sys.stderr.write(res.stdout + res.stderr)
             raise RuntimeError("link failed")
-    return LIB_PATH
+    return out
 
 
 def main() -> None:
@@ -92,8 +121,10 @@ def main() -> None:
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
     ap.add_argument("-j", type=int, default=None)
+    ap.add_argument("--sanitize", default=None, choices=sorted(SANITIZERS),
+                    help="host-side sanitizer build into _b200.<kind>.so")
     a = ap.parse_args()
-    print(build(a.force, a.verbose, a.j))
+    print(build(a.force, a.verbose, a.j, a.sanitize))
 
 
 if __name__ == "__main__":

@@ -15,7 +15,10 @@ from typing import Optional
 
 import torch
 
-_LIB_PATH = Path(__file__).resolve().parent.parent / "_b200.so"
+# VLLM_B200_NATIVE_LIB selects another build of the same library (e.g. a host-sanitizer build,
+# see csrc/build.py)
+_LIB_PATH = Path(os.environ["VLLM_B200_NATIVE_LIB"]) if os.environ.get("VLLM_B200_NATIVE_LIB") \
+    else Path(__file__).resolve().parent.parent / "_b200.so"
 _lock = threading.Lock()
 _lib: Optional[ctypes.CDLL] = None
 _tried = False
