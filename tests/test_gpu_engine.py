@@ -231,3 +231,38 @@ def test_norm_and_activation_kernels_emit_quantised_rows(scheme, monkeypatch):
     spread = logits["0"].std().item()
     assert err < 0.1 * spread + 0.02, (err, spread)
     assert logits["1"].isfinite().all()
+
+
+@pytest.mark.parametrize("method,model", [("ngram", "llama"), ("eagle", "llama"),
+                                          ("medusa", "llama"), ("mtp", "tiny-deepseek")])
+def test_speculative_decoding_on_gpu(method, model):
+    """Draft proposers on the GPU path (n-gram on the host; EAGLE / MTP drafters with their own
+    KV cache; Medusa heads): drafts are proposed and verified, every request gets its tokens,
+    and the output starts like the greedy output without drafts (later tokens may differ where
+    two logits are nearly tied: verification scores several positions in one pass)."""
+    if model == "llama":
+        name = "llama-3-8b"
+        kw = dict(num_hidden_layers=2, hidden_size=512, intermediate_size=1024,
+                  num_attention_heads=8, num_key_value_heads=2, head_dim=64, vocab_size=2048)
+    else:
+        name, kw = model, dict(dtype="bfloat16")
+    kw.update(max_num_seqs=8, max_num_batched_tokens=256, max_model_len=256, num_gpu_blocks=128,
+              seed=0)
+    V = kw.get("vocab_size", 1024)
+    g = torch.Generator().manual_seed(2)
+    base = torch.randint(0, V, (12,), generator=g).tolist()
+    prompts = [base * 3 + base[:5], base[::-1] * 2 + base[:3], base * 2]
+    sp = SamplingParams(max_tokens=16, temperature=0.0, ignore_eos=True)
+    plain = LLM(name, device="cuda", enforce_eager=True, **kw).generate(prompts, sp)
+    k = 3 if method in ("ngram", "medusa") else 1
+    llm = LLM(name, device="cuda", enforce_eager=True, speculative_method=method,
+              num_speculative_tokens=k, **kw)
+    outs = llm.generate(prompts, sp)
+    torch.cuda.synchronize()
+    _native.check_status()
+    m = llm.engine.spec_metrics
+    assert m.num_drafts > 0 and m.num_draft_tokens > 0
+    for a, b in zip(outs, plain):
+        ta, tb = a.outputs[0].token_ids, b.outputs[0].token_ids
+        assert len(ta) == len(tb) == 16
+        assert ta[:2] == tb[:2], (method, ta, tb)
