@@ -147,6 +147,18 @@ def _gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = N
         out = torch.empty((M, out_cols), device=a.device,
                           dtype=torch.float32 if epilogue == EPI_FP32 else torch.bfloat16)
     assert out.stride(-1) == 1 and out.shape[-1] == out_cols
+    if (K % 8 or Nn % 8 or a.stride(0) % 8 or b.stride(0) % 8 or out.stride(0) % 8) \
+            and epilogue != EPI_SILU_MUL:
+        # rows that are not a multiple of 16 bytes cannot be described to TMA (a router over
+        # four experts, an odd head count): the library GEMM takes these rare, tiny shapes
+        y = torch.matmul(a.float() if epilogue == EPI_FP32 else a,
+                         (b.float() if epilogue == EPI_FP32 else b).t())
+        if bias is not None:
+            y = y + bias
+        if residual is not None:
+            y = y + residual
+        out.copy_(y)
+        return out
     if (USE_PAIR_GEMM and PAIR_MIN_M <= M < WIDE2_MIN_M and Nn % 256 == 0 and K % 64 == 0
             and epilogue in (EPI_NONE, EPI_BIAS, EPI_SILU_MUL)
             and -(-M // 256) * (Nn // 256) >= PAIR_MIN_TILES):
