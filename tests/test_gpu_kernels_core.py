@@ -123,6 +123,35 @@ def test_gemm_cta_pair_large_m(C, M, N, K, mt, monkeypatch):
     _native.check_status()
 
 
+@pytest.mark.parametrize("M,N,K,epi", [(256, 4096, 4096, 0), (256, 6144, 1024, 0),
+                                       (200, 1024, 2048, 1), (512, 4096, 4096, 0),
+                                       (130, 2048, 1024, 2)])
+def test_gemm_cta_pair_k_split(C, M, N, K, epi, monkeypatch):
+    """K split of the CTA-pair kernel (one tile and K slice per pair, fp32 partial sums meet at
+    a counter, every CTA reduces a row slice): off by default (measured slower than the
+    weight-streaming kernel), kept correct: same result as the reference, bitwise equal on
+    repeated launches (the counters return to zero)."""
+    monkeypatch.setattr(C, "USE_PAIR_SPLIT", True)
+    torch.manual_seed(M + N + K)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = (torch.randn(N, K, device="cuda") / math.sqrt(K)).to(torch.bfloat16)
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16) if epi == 1 else None
+    wsp = C._pair_split_workspace(a.device)
+    assert wsp is not None
+    want = ref.gemm(a, b, out_dtype=torch.float32)
+    if epi == 1:
+        want = want + bias.float()
+    if epi == 2:
+        w4 = want.view(M, N // 64, 2, 32)
+        want = (torch.nn.functional.silu(w4[:, :, 0]) * w4[:, :, 1]).reshape(M, N // 2)
+    first = C.gemm_bf16(a, b, bias=bias, epilogue=epi)
+    _close(first, want, 3e-2, 3e-2)
+    assert torch.equal(C.gemm_bf16(a, b, bias=bias, epilogue=epi), first)
+    torch.cuda.synchronize()
+    assert int(wsp[1].abs().sum()) == 0
+    _native.check_status()
+
+
 def test_gemm_bf16_epilogues(C):
     torch.manual_seed(1)
     M, N, K = 200, 1024, 512

@@ -129,6 +129,8 @@ class _Sigs:
     b200_gemm_skinny_workspace = [I, P, P]
     b200_gemm_wide2 = [P, L, P, L, P, L, I, I, I, P, I, P]
     b200_gemm_pair = [P, L, P, L, P, L, I, I, I, P, I, P]
+    b200_gemm_pair_split = [P, L, P, L, P, L, I, I, I, P, I, P, P, P]
+    b200_gemm_pair_split_workspace = [P, P]
     b200_gemm_skinny_plan = [I, I, I, I, P, P]
     b200_gemm_q8 = [P, L, P, L, P, L, I, I, I, P, L, P, L, P, I, P]
     b200_gemm_q8_grouped = [P, L, P, L, P, L, I, I, I, I, P, L, P, L, P, P, P, I, P]

@@ -68,6 +68,7 @@ def oracle_compare(name: str, got: torch.Tensor, want: torch.Tensor, rtol: float
 
 # Decode-sized activations (M <= 256) take the weight-streaming kernel of gemm_skinny.cu.
 USE_PAIR_GEMM = True            # 256 x 256 tile per CTA pair, cta_group::2 (gemm_pair.cu)
+USE_PAIR_SPLIT = False          # K split over pairs for few-tile decode GEMMs (gemm_pair.cu)
 PAIR_MIN_M = 129                # below the large-M threshold the pair kernel runs when ...
 PAIR_MIN_TILES = 48             # ... its tiles can occupy most of the 74 SM pairs
 USE_WIDE2_GEMM = True           # persistent 256 x 256 tiles for large M (gemm_skinny.cu)
@@ -108,6 +109,24 @@ def _skinny_workspace(device: torch.device):
         w = (torch.empty(nbytes.value // 4, dtype=torch.float32, device=device),
              torch.zeros(nctr.value, dtype=torch.int32, device=device))
         _SKINNY_WS[key] = w
+    return w
+
+
+_PAIR_SPLIT_WS: dict = {}
+
+
+def _pair_split_workspace(device: torch.device):
+    """Per (device, stream) workspace of the pair kernel's K split: fp32 partial sums and
+    zeroed counters; None when the device cannot co-schedule clusters of two."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    w = _PAIR_SPLIT_WS.get(key, 0)
+    if w == 0:
+        nfl, nctr = ctypes.c_longlong(), ctypes.c_int()
+        rc = N.lib().b200_gemm_pair_split_workspace(ctypes.byref(nfl), ctypes.byref(nctr))
+        w = None if rc != 0 else (
+            torch.empty(nfl.value, dtype=torch.float32, device=device),
+            torch.zeros(nctr.value, dtype=torch.int32, device=device))
+        _PAIR_SPLIT_WS[key] = w
     return w
 
 
@@ -171,6 +190,20 @@ def _gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = N
             return out
         if rc != -20:
             raise N.NativeError(f"b200_gemm_pair failed with code {rc}")
+    if (USE_PAIR_SPLIT and PAIR_MIN_M <= M <= 512 and Nn % 256 == 0 and K % 64 == 0
+            and epilogue in (EPI_NONE, EPI_BIAS, EPI_SILU_MUL)
+            and -(-M // 256) * (Nn // 256) < PAIR_MIN_TILES):
+        # few 256 x 256 tiles (qkv, o_proj, down_proj at decode batch sizes): K split over pairs
+        wsp = _pair_split_workspace(a.device)
+        if wsp is not None:
+            rc = N.lib().b200_gemm_pair_split(ptr(a), a.stride(0), ptr(b), b.stride(0), ptr(out),
+                                              out.stride(0), M, Nn, K, ptr(bias), epilogue,
+                                              ptr(wsp[0]), ptr(wsp[1]), stream_ptr())
+            N.launch_count += 1
+            if rc == 0:
+                return out
+            if rc != -20:
+                raise N.NativeError(f"b200_gemm_pair_split failed with code {rc}")
     silu_256 = epilogue != EPI_SILU_MUL or Nn % 256 == 0     # these two kernels: 256-wide tiles
     if M <= SKINNY_MAX_M and USE_SKINNY_GEMM and silu_256 \
             and epilogue in (EPI_NONE, EPI_BIAS, EPI_SILU_MUL):
