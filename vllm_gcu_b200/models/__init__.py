@@ -30,6 +30,8 @@ _REGISTRY: dict[str, str] = {
     "QuantMixtralForCausalLM": "vllm_gcu_b200.models.moe_models:MixtralForCausalLM",
     "Qwen2_5_VLForConditionalGeneration":
         "vllm_gcu_b200.models.qwen2_5_vl:Qwen2_5_VLForConditionalGeneration",
+    "Qwen2VLForConditionalGeneration":
+        "vllm_gcu_b200.models.qwen2_vl:Qwen2VLForConditionalGeneration",
     "GotOcr2ForConditionalGeneration":
         "vllm_gcu_b200.models.got_ocr2:GotOcr2ForConditionalGeneration",
     "GOTQwenForCausalLM": "vllm_gcu_b200.models.got_ocr2:GotOcr2ForConditionalGeneration",
