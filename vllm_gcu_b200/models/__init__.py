@@ -32,6 +32,7 @@ _REGISTRY: dict[str, str] = {
         "vllm_gcu_b200.models.qwen2_5_vl:Qwen2_5_VLForConditionalGeneration",
     "Qwen2VLForConditionalGeneration":
         "vllm_gcu_b200.models.qwen2_vl:Qwen2VLForConditionalGeneration",
+    "LlavaForConditionalGeneration": "vllm_gcu_b200.models.llava:LlavaForConditionalGeneration",
     "GotOcr2ForConditionalGeneration":
         "vllm_gcu_b200.models.got_ocr2:GotOcr2ForConditionalGeneration",
     "GOTQwenForCausalLM": "vllm_gcu_b200.models.got_ocr2:GotOcr2ForConditionalGeneration",
