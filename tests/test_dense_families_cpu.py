@@ -188,3 +188,37 @@ def test_chatglm_layout_matches_the_glm_mathematics():
     want = _hf_last_logits(hf)
     assert torch.allclose(got, want, atol=3e-4), (got - want).abs().max()
     assert tok == int(want.argmax())
+
+
+def test_gpt_bigcode_matches_transformers():
+    """StarCoder / WizardCoder architecture: learnt positions, LayerNorm, multi-query
+    attention, plain GELU MLP with biases, tied LM head."""
+    cfg = tr.GPTBigCodeConfig(vocab_size=300, n_positions=128, n_embd=64, n_layer=2, n_head=4,
+                              n_inner=128, activation_function="gelu_pytorch_tanh",
+                              multi_query=True, layer_norm_epsilon=1e-5, resid_pdrop=0.0,
+                              embd_pdrop=0.0, attn_pdrop=0.0)
+    torch.manual_seed(3)
+    hf = tr.GPTBigCodeForCausalLM(cfg).eval().float()
+    with torch.no_grad():                      # biases and norm offsets start at zero
+        for n, p in hf.named_parameters():
+            if n.endswith(".bias"):
+                p.copy_(torch.randn_like(p) * 0.05)
+    got, tok = _engine_logits("GPTBigCodeForCausalLM", cfg.to_dict(), hf.state_dict().items())
+    want = _hf_last_logits(hf)
+    assert torch.allclose(got, want, atol=3e-4), (got - want).abs().max()
+    assert tok == int(want.argmax())
+    # decode steps through the paged cache agree with a full recompute
+    from vllm_gcu_b200.config import ModelConfig as MC
+    from vllm_gcu_b200.engine.llm import LLM as L
+    d = cfg.to_dict()
+    d["architectures"] = ["GPTBigCodeForCausalLM"]
+    llm = L(MC.from_hf_dict(d, dtype=torch.float32), device="cpu", max_num_seqs=2,
+            max_num_batched_tokens=8, max_model_len=64, num_gpu_blocks=16, load_format="none")
+    llm.engine.model.load_weights(hf.state_dict().items())
+    toks = llm.generate([IDS], SamplingParams(max_tokens=4, temperature=0.0, ignore_eos=True)
+                        )[0].outputs[0].token_ids
+    seq = list(IDS)
+    for t in toks:
+        with torch.inference_mode():
+            assert t == int(hf(input_ids=torch.tensor([seq])).logits[0, -1].argmax())
+        seq.append(t)

@@ -119,6 +119,21 @@ class ModelConfig:
                 d = {**{k: v for k, v in d.items() if k != nested},
                      **{k: v for k, v in d[nested].items()
                         if k not in ("architectures", "model_type")}}
+        if archs[0] == "GPTBigCodeForCausalLM":
+            # GPT-2 style field names; multi-query attention = one key / value head
+            d = dict(d)
+            heads = d["n_head"]
+            d.setdefault("hidden_size", d["n_embd"])
+            d.setdefault("num_hidden_layers", d["n_layer"])
+            d.setdefault("num_attention_heads", heads)
+            d.setdefault("num_key_value_heads", 1 if d.get("multi_query", True) else heads)
+            d.setdefault("intermediate_size", d.get("n_inner") or 4 * d["n_embd"])
+            d.setdefault("max_position_embeddings", d.get("n_positions", 8192))
+            d.setdefault("rms_norm_eps", d.get("layer_norm_epsilon", 1e-5))
+            d.setdefault("hidden_act", d.get("activation_function", "gelu_pytorch_tanh"))
+            d.setdefault("head_dim", d["n_embd"] // heads)
+            d["tie_word_embeddings"] = True
+            d["attention_bias"] = True
         if archs[0] in ("ChatGLMModel", "ChatGLMForConditionalGeneration"):
             # ChatGLM2 / 3 / GLM-4-9B configs use their own field names
             d = dict(d)

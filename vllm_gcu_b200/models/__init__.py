@@ -25,6 +25,7 @@ _REGISTRY: dict[str, str] = {
     # the reference registers this name for a customer's Llama variant
     # (vllm_gcu/models/__init__.py:29-31); the architecture is Llama's
     "CustomerLlaMAForCausalLM": "vllm_gcu_b200.models.llama:LlamaForCausalLM",
+    "GPTBigCodeForCausalLM": "vllm_gcu_b200.models.gpt_bigcode:GPTBigCodeForCausalLM",
     "Qwen3MoeForCausalLM": "vllm_gcu_b200.models.moe_models:Qwen3MoeForCausalLM",
     "MixtralForCausalLM": "vllm_gcu_b200.models.moe_models:MixtralForCausalLM",
     "QuantMixtralForCausalLM": "vllm_gcu_b200.models.moe_models:MixtralForCausalLM",

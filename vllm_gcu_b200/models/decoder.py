@@ -570,7 +570,8 @@ class DecoderLM(nn.Module):
             if p.dtype not in (torch.float32, torch.bfloat16, torch.float16):
                 continue
             if name.endswith("norm.weight") or ".q_norm." in name or ".k_norm." in name \
-                    or name.endswith("layernorm.weight"):
+                    or name.endswith("layernorm.weight") \
+                    or (".ln_" in name and name.endswith(".weight")):
                 p.data.fill_(1.0)
             elif name.endswith(".bias") or "e_score_correction_bias" in name:
                 p.data.zero_()
