@@ -84,3 +84,35 @@ def test_deepseek_vl2_vision_side_on_gpu():
     torch.cuda.synchronize()
     _native.check_status()
     assert len(out[0].outputs[0].token_ids) == 4
+
+
+def test_gpt_bigcode_gpu_tracks_cpu_reference():
+    """LayerNorm (+ residual) and plain GELU kernels, learnt positions, multi-query attention."""
+    d = {"architectures": ["GPTBigCodeForCausalLM"], "vocab_size": 2048, "n_positions": 512,
+         "n_embd": 512, "n_layer": 2, "n_head": 8, "n_inner": 1024, "multi_query": True}
+    kw = dict(max_num_seqs=4, max_num_batched_tokens=64, max_model_len=256, num_gpu_blocks=64,
+              load_format="dummy", seed=0)
+    gpu = LLM(ModelConfig.from_hf_dict(d, dtype=torch.bfloat16), device="cuda",
+              enforce_eager=True, **kw)
+    cpu = LLM(ModelConfig.from_hf_dict(d, dtype=torch.float32), device="cpu", **kw)
+    _copy_weights(gpu.engine.model, cpu.engine.model)
+    with torch.no_grad():                      # non-trivial biases on both sides
+        for (n, pg), (_, pc) in zip(sorted(gpu.engine.model.named_parameters()),
+                                    sorted(cpu.engine.model.named_parameters())):
+            if n.endswith(".bias"):
+                b = torch.randn(pg.shape, generator=torch.Generator().manual_seed(len(n))) * 0.05
+                pg.copy_(b.to(pg.dtype))
+                pc.copy_(pg.float().cpu())
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (100, 33, 7)]
+    one = SamplingParams(max_tokens=3, temperature=0.0, ignore_eos=True)
+    gpu.engine.runner.keep_logits = True
+    cpu.engine.runner.keep_logits = True
+    og = gpu.generate(prompts, one)
+    oc = cpu.generate(prompts, one)
+    torch.cuda.synchronize()
+    _native.check_status()
+    lg, lc = gpu.engine.runner.last_logits.float().cpu(), cpu.engine.runner.last_logits.float()
+    err = (lg - lc).abs().max().item()
+    assert err < 0.06 * lc.std().item() + 0.03, (err, lc.std().item())
+    assert [o.outputs[0].token_ids[0] for o in og] == [o.outputs[0].token_ids[0] for o in oc]
