@@ -68,6 +68,14 @@ def test_completions_and_streaming():
             assert r.status_code == 200 and len(r.json()["choices"][0]["token_ids"]) == 2
             bad = await c.post("/v1/chat/completions", json={"max_tokens": 2})
             assert bad.status_code == 400
+            # a decoder engine answers /v1/embeddings with last-token vectors of unit length
+            e = (await c.post("/v1/embeddings", json={"input": [[1, 2, 3, 4], [9, 8, 7]]})).json()
+            assert len(e["data"]) == 2 and e["usage"]["prompt_tokens"] == 7
+            v0, v1 = (e["data"][i]["embedding"] for i in (0, 1))
+            assert len(v0) == cfg.model.hidden_size
+            assert abs(sum(x * x for x in v0) - 1.0) < 1e-3 and v0 != v1
+            again = (await c.post("/v1/embeddings", json={"input": [[1, 2, 3, 4]]})).json()
+            assert max(abs(a - b) for a, b in zip(again["data"][0]["embedding"], v0)) < 1e-4
     try:
         asyncio.run(run())
     finally:

@@ -222,3 +222,40 @@ def test_gpt_bigcode_matches_transformers():
         with torch.inference_mode():
             assert t == int(hf(input_ids=torch.tensor([seq])).logits[0, -1].argmax())
         seq.append(t)
+
+
+def test_qwen2_embedding_checkpoint_matches_transformers():
+    """gte-Qwen2 style embedding: bare ``Qwen2Model`` tensor names, last-token pooling,
+    L2-normalised; prompts of different lengths run through the scheduler together."""
+    cfg = tr.Qwen2Config(vocab_size=300, hidden_size=64, intermediate_size=128,
+                         num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                         max_position_embeddings=128, rms_norm_eps=1e-6)
+    torch.manual_seed(3)
+    hf = tr.Qwen2Model(cfg).eval().float()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if n.endswith("bias") or n.endswith("norm.weight"):
+                p.copy_(torch.randn_like(p) * 0.2 + (1.0 if "norm" in n else 0.0))
+    d = cfg.to_dict()
+    d["architectures"] = ["Qwen2Model"]
+    mc = ModelConfig.from_hf_dict(d, dtype=torch.float32)
+    llm = LLM(mc, device="cpu", max_num_seqs=4, max_num_batched_tokens=16, max_model_len=64,
+              num_gpu_blocks=32, load_format="none")
+    loaded = llm.engine.model.load_weights(hf.state_dict().items())
+    assert "model.layers.0.self_attn.q_proj.bias" in loaded and "model.norm.weight" in loaded
+    prompts = [IDS, IDS[:4], IDS[2:] + [9, 9, 200, 1, 4, 77, 12, 13]]   # last one is chunked
+    got = llm.embed(prompts)
+    assert got.shape == (3, 64)
+    for g, p in zip(got, prompts):
+        with torch.inference_mode():
+            want = hf(input_ids=torch.tensor([p])).last_hidden_state[0, -1]
+        want = torch.nn.functional.normalize(want, dim=-1)
+        assert torch.allclose(g, want, atol=2e-4), (g - want).abs().max()
+    # pooling and generating requests share a batch; only the pooling one carries a vector
+    out = llm.generate([IDS, IDS[:4]],
+                       [SamplingParams(max_tokens=3, temperature=0.0, ignore_eos=True),
+                        SamplingParams(max_tokens=8, pooling=True)])
+    assert len(out[0].outputs[0].token_ids) == 3 and out[0].embedding is None
+    assert len(out[1].outputs[0].token_ids) == 1
+    e = torch.nn.functional.normalize(out[1].embedding, dim=-1)
+    assert torch.allclose(e, got[1], atol=1e-5)

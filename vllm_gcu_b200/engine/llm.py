@@ -159,6 +159,10 @@ class LLMEngine:
         (``{"pixel_values": [n_patches, C*Tp*P*P], "image_grid_thw": [n_images, 3]}``); the
         prompt must already contain one placeholder token per merged patch."""
         rid = request_id if request_id is not None else f"req-{next(self._ids)}"
+        if sampling_params is not None and sampling_params.pooling \
+                and sampling_params.max_tokens != 1:
+            import dataclasses
+            sampling_params = dataclasses.replace(sampling_params, max_tokens=1, min_tokens=0)
         req = Request(rid, list(prompt_token_ids), sampling_params or SamplingParams(),
                       eos_token_id=eos_token_id, priority=priority, lora_id=lora_id)
         if multi_modal_data:
@@ -264,6 +268,7 @@ class LLMEngine:
     def _finish(self, so: SchedulerOutput, handle: StepHandle) -> list[RequestOutput]:
         toks = handle.token_ids()
         draft = handle.draft_tokens()
+        so_req = {s.req.request_id: s.req for s in so.scheduled}
         if self.spec_metrics is not None:
             for rid, nd in zip(handle.req_ids, handle.extra.get("num_draft", [])):
                 if nd:
@@ -299,6 +304,15 @@ class LLMEngine:
             draft = {rid: d for rid, d in draft.items()
                      if rid in reqs and not reqs[rid].sampling_params.needs_host_history}
         outs = self.scheduler.update_from_output(so, toks, draft, lp)
+        hid = handle.extra.get("hidden")
+        if hid is not None:
+            rows = {rid: i for i, rid in enumerate(handle.req_ids)}
+            hid = hid.cpu()
+            for o in outs:
+                i = rows.get(o.request_id)
+                r = so_req.get(o.request_id)
+                if i is not None and r is not None and r.sampling_params.pooling:
+                    o.embedding = hid[i]
         if self.proposer is not None:
             for s in so.scheduled:
                 r = s.req
@@ -381,6 +395,21 @@ class LLMEngine:
         finally:
             self.scheduler.emit_partial = prev
         return [final[r] for r in order]
+
+
+    def embed(self, prompts: Iterable[Sequence[int]], normalize: bool = True) -> torch.Tensor:
+        """Embeddings from a decoder checkpoint (gte-Qwen2 in the reference's model table,
+        docs/source/user_guide/support_matrix/supported_models.md:22): the final-norm hidden
+        state of each prompt's last token, L2-normalised, as a float32 [n, hidden] tensor on
+        the host.  Prompts run through the normal scheduler (chunked prefill, prefix cache,
+        batching) as one-token requests; the sampled token is discarded."""
+        prompts = [list(p) for p in prompts]
+        outs = self.generate(prompts, SamplingParams(temperature=0.0, max_tokens=1,
+                                                     ignore_eos=True, pooling=True))
+        vec = torch.stack([o.embedding for o in outs])
+        if normalize:
+            vec = torch.nn.functional.normalize(vec, dim=-1)
+        return vec
 
 
 class LLM:
@@ -496,6 +525,13 @@ class LLM:
             from .guided import vocabulary_of
             vocab = vocabulary_of(vocab, self.engine.cfg.model.vocab_size)
         self.engine.set_vocabulary(vocab)
+
+    def embed(self, prompts, normalize: bool = True):
+        """Last-token embeddings of text or token-id prompts from a decoder checkpoint
+        (:meth:`LLMEngine.embed`)."""
+        if isinstance(prompts, str):
+            prompts = [prompts]
+        return self.engine.embed([self._encode(p) for p in prompts], normalize=normalize)
 
     def generate(self, prompts, sampling_params=None) -> list[RequestOutput]:
         """One ``RequestOutput`` per prompt.  ``n`` / ``best_of`` > 1 run that many sampled

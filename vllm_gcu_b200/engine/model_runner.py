@@ -125,6 +125,8 @@ class ModelRunner:
         self.timing_events: Optional[list] = None  # set to a list to time every step
         self.timing_meta: list = []                # (decodes, prefills, tokens) per timed step
         self.keep_logits = False                   # debugging / tests: keep last step's logits
+        self.keep_hidden = False                   # a pooling request samples in this step:
+        self._last_hidden = None                   # keep the sampled rows' final hidden states
         self._features = None                      # per-step sampling extras (penalties, logprobs)
         self._mm_inputs = None                     # (inputs_embeds, mrope positions) of a step
         from .. import envs
@@ -371,6 +373,7 @@ class ModelRunner:
                    or s.req.sampling_params.logprobs is not None
                    or s.req.sampling_params.prompt_logprobs is not None
                    or s.req.sampling_params.constrained for s in sched)
+        self.keep_hidden = any(s.req.sampling_params.pooling for s in sched)
         # Data-parallel replicas pick the graph by the largest token count of any replica in
         # this step (known from the exchange that precedes every step): the expert-parallel
         # receive area inside the graph is sized by the padded batch, so it must cover what
@@ -382,7 +385,7 @@ class ModelRunner:
         use_graph = (self.is_cuda and npf == 0 and bool(self.graphs)
                      and nd_graph <= self.graph_sizes[-1]
                      and self.drafter is None and self.head_drafter is None
-                     and not batch_has_lora and not feat)
+                     and not batch_has_lora and not feat and not self.keep_hidden)
         B_pad = _pad_batch(nd_graph, self.graph_sizes) if use_graph else B
         T = T_real + (B_pad - B)
 
@@ -640,6 +643,9 @@ class ModelRunner:
         self.step_counter += 1
         extra = {"num_draft": nspec,
                  "draft_width": self.head_drafter.k if self.head_drafter is not None else 1}
+        if self.keep_hidden and ns and self._last_hidden is not None:
+            extra["hidden"] = self._last_hidden[:ns * width:width]     # row i = i-th sampler
+            self._last_hidden = None
         if self._features is not None:
             extra["logprobs"] = self._features.pop("logprobs_out", None)
             extra["prompt_logprobs"] = self._features.pop("prompt_logprobs_out", None)
@@ -806,6 +812,8 @@ class ModelRunner:
             rows = hidden[:ns]          # decode-only: row i is the i-th sampling request
         else:
             rows = hidden.index_select(0, self.sample_indices[:ns * width])
+        if self.keep_hidden:
+            self._last_hidden = rows.float()
         if (all_greedy and width == 1 and feats is None and not self.keep_logits
                 and self.drafter is None and self.head_drafter is None
                 and self._greedy_shortcut):

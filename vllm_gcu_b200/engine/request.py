@@ -37,6 +37,9 @@ class SamplingParams:
     # be a JSON document of the schema; needs an engine that knows its vocabulary
     guided_regex: Optional[str] = None
     guided_json: Optional[Any] = None
+    # pooling request (embedding from a decoder checkpoint): the output carries the final
+    # hidden state of the last prompt token; the request ends after its first step
+    pooling: bool = False
     extra_args: dict[str, Any] = field(default_factory=dict)
 
     @property
@@ -177,6 +180,7 @@ class RequestOutput:
     prompt_logprobs: Optional[list] = None
     metrics: dict[str, float] = field(default_factory=dict)
     kv_transfer_params: Optional[dict] = None       # disaggregated prefill: for the decode side
+    embedding: Optional[Any] = None                 # pooling requests: float32 [hidden] on the host
 
 
 def check_stop(req: Request, max_model_len: int) -> bool:

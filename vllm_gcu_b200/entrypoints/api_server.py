@@ -13,6 +13,7 @@ Run: ``python -m vllm_gcu_b200.entrypoints.api_server --model llama-3-8b --port 
 from __future__ import annotations
 
 import argparse
+import asyncio
 import json
 import time
 import uuid
@@ -323,16 +324,34 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None):
         return [int(t) for t in x] if isinstance(x, list) and x and isinstance(x[0], int) \
             else list(tokenizer.encode(str(x)))
 
+    async def _decoder_embedding(ids: list[int]) -> list[float]:
+        """Last-token embedding from the generation engine (decoder checkpoints published as
+        embedding models): one pooling request through the same scheduler as completions."""
+        import torch
+        final = None
+        async for out in engine.generate_stream(ids, SamplingParams(max_tokens=1, pooling=True)):
+            final = out
+        vec = final.embedding.float()
+        return torch.nn.functional.normalize(vec, dim=-1).tolist()
+
     @app.post("/v1/embeddings")
     async def embeddings(request: Request):
-        err = _need_pooler()
-        if err is not None:
-            return err
         body = await request.json()
         inp = body.get("input")
         items = inp if isinstance(inp, list) and inp and not isinstance(inp[0], int) else [inp]
         seqs = [_as_ids(x) for x in items]
-        vecs = pooler.run(seqs).float().tolist()
+        if pooler is None and engine is not None and hasattr(engine, "generate_stream"):
+            try:
+                for q in seqs:
+                    engine.validate_prompt(q)
+            except ValueError as e:
+                return JSONResponse({"error": str(e)}, status_code=400)
+            vecs = list(await asyncio.gather(*[_decoder_embedding(q) for q in seqs]))
+        else:
+            err = _need_pooler()
+            if err is not None:
+                return err
+            vecs = pooler.run(seqs).float().tolist()
         return {"object": "list", "model": model_name,
                 "data": [{"object": "embedding", "index": i, "embedding": v}
                          for i, v in enumerate(vecs)],

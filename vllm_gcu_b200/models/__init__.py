@@ -13,6 +13,8 @@ _REGISTRY: dict[str, str] = {
     "LlamaForCausalLM": "vllm_gcu_b200.models.llama:LlamaForCausalLM",
     "MistralForCausalLM": "vllm_gcu_b200.models.llama:LlamaForCausalLM",
     "Qwen2ForCausalLM": "vllm_gcu_b200.models.llama:Qwen2ForCausalLM",
+    "Qwen2Model": "vllm_gcu_b200.models.llama:Qwen2EmbeddingModel",
+    "Qwen2EmbeddingModel": "vllm_gcu_b200.models.llama:Qwen2EmbeddingModel",
     "Qwen3ForCausalLM": "vllm_gcu_b200.models.llama:Qwen3ForCausalLM",
     "Glm4ForCausalLM": "vllm_gcu_b200.models.llama:Glm4ForCausalLM",
     "InternLM2ForCausalLM": "vllm_gcu_b200.models.llama:InternLM2ForCausalLM",

@@ -27,6 +27,22 @@ class Qwen2ForCausalLM(DecoderLM):
         super().__init__(cfg, device)
 
 
+class Qwen2EmbeddingModel(Qwen2ForCausalLM):
+    """Qwen2 checkpoints published as embedding models (gte-Qwen2: listed in
+    docs/source/user_guide/support_matrix/supported_models.md:22).  The mathematics is the
+    Qwen2 decoder; the vector of a text is the final-norm hidden state of its last token
+    (``LLMEngine.embed``).  Checkpoints saved from the bare ``Qwen2Model`` carry tensor names
+    without the ``model.`` prefix and no LM head."""
+
+    def load_weights(self, weights):
+        def named():
+            for name, t in weights:
+                if not name.startswith(("model.", "lm_head.")):
+                    name = "model." + name
+                yield name, t
+        return super().load_weights(named())
+
+
 class Qwen3ForCausalLM(DecoderLM):
     def __init__(self, cfg: ModelConfig, device="cpu"):
         if not cfg.qk_norm:
