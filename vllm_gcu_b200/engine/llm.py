@@ -170,8 +170,9 @@ class LLMEngine:
             if prep is None:
                 raise ValueError(f"{self.cfg.model.architecture} takes no multimodal input")
             # second operand: patch grids (Qwen2.5-VL) or tile counts per image (DeepSeek-VL2)
-            grids = multi_modal_data.get("image_grid_thw",
-                                         multi_modal_data.get("images_spatial_crop"))
+            # or original image sizes (LLaVA-NeXT)
+            grids = multi_modal_data.get("image_grid_thw", multi_modal_data.get(
+                "images_spatial_crop", multi_modal_data.get("image_sizes")))
             for k, v in prep(req.prompt_token_ids, multi_modal_data["pixel_values"],
                              grids).items():
                 setattr(req, k, v)

@@ -36,6 +36,8 @@ _REGISTRY: dict[str, str] = {
     "Qwen2VLForConditionalGeneration":
         "vllm_gcu_b200.models.qwen2_vl:Qwen2VLForConditionalGeneration",
     "LlavaForConditionalGeneration": "vllm_gcu_b200.models.llava:LlavaForConditionalGeneration",
+    "LlavaNextForConditionalGeneration":
+        "vllm_gcu_b200.models.llava:LlavaNextForConditionalGeneration",
     "GotOcr2ForConditionalGeneration":
         "vllm_gcu_b200.models.got_ocr2:GotOcr2ForConditionalGeneration",
     "GOTQwenForCausalLM": "vllm_gcu_b200.models.got_ocr2:GotOcr2ForConditionalGeneration",

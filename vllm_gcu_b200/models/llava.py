@@ -1,4 +1,4 @@
-"""LLaVA-1.5 style models: CLIP vision transformer + two-layer MLP projector + a Llama language
+"""LLaVA-1.5 and LLaVA-NeXT style models: CLIP vision transformer + two-layer MLP projector + a Llama language
 model.  The reference lists LLaVA in its support matrix and serves it through vLLM's upstream
 class (docs/source/user_guide/support_matrix/supported_models.md).
 
@@ -197,3 +197,112 @@ class LlavaForConditionalGeneration(LlamaForCausalLM):
                 n = "model." + n[len("language_model."):]
             lm.append((n, t))
         return loaded | super().load_weights(lm)
+
+
+def anyres_grid(image_size: Sequence[int], pinpoints: Sequence[Sequence[int]], tile: int
+                ) -> tuple[int, int]:
+    """(tile rows, tile columns) of the high-resolution view of an image of ``(height, width)``
+    pixels: the ``(height, width)`` candidate that keeps the most of the image's resolution,
+    in tiles of ``tile`` pixels."""
+    from .deepseek_vl2 import select_best_resolution
+    h, w = int(image_size[0]), int(image_size[1])
+    bw, bh = select_best_resolution((w, h), [(int(pw), int(ph)) for ph, pw in pinpoints])
+    return bh // tile, bw // tile
+
+
+def crop_to_aspect(grid: torch.Tensor, image_size: Sequence[int]) -> torch.Tensor:
+    """``grid [rows, cols, C]`` covers an image of ``(height, width)`` pixels that was scaled to
+    fit and centred; the rows (or columns) that only saw padding are cut off."""
+    oh, ow = int(image_size[0]), int(image_size[1])
+    rows, cols = grid.shape[0], grid.shape[1]
+    if ow / oh > cols / rows:
+        keep = int(round(oh * (cols / ow), 7))
+        pad = (rows - keep) // 2
+        return grid[pad:rows - pad]
+    keep = int(round(ow * (rows / oh), 7))
+    pad = (cols - keep) // 2
+    return grid[:, pad:cols - pad]
+
+
+class LlavaNextForConditionalGeneration(LlavaForConditionalGeneration):
+    """LLaVA-NeXT (LLaVA-1.6): every image is seen as one down-scaled base view plus a grid of
+    full-resolution tiles chosen from ``image_grid_pinpoints``.  The tile features are laid
+    out as one 2-D map, rows or columns that only saw padding are dropped, a learnt
+    ``image_newline`` row ends every row of the map, and the result follows the base view's
+    features.  ``multi_modal_data``: ``pixel_values [views, 3, S, S]`` (base view first; a
+    list of such tensors for several images) and ``image_sizes [[height, width], ...]``."""
+
+    def __init__(self, cfg: ModelConfig, device="cpu"):
+        super().__init__(cfg, device)
+        self.pinpoints = [list(p) for p in cfg.extra.get(
+            "image_grid_pinpoints", [[336, 672], [672, 336], [672, 672], [1008, 336], [336, 1008]])]
+        if self.is_first_stage:
+            self.image_newline = nn.Parameter(torch.zeros(cfg.hidden_size, dtype=cfg.dtype,
+                                                          device=device), requires_grad=False)
+
+    def num_image_tokens(self, image_size: Sequence[int], views: int) -> int:
+        side = self.vision_cfg.image_size // self.vision_cfg.patch_size
+        base = side * side + (0 if self.select == "default" else 1)
+        if views == 1:
+            return base + 1
+        gh, gw = anyres_grid(image_size, self.pinpoints, self.vision_cfg.image_size)
+        probe = torch.empty(gh * side, gw * side, 0)
+        kept = crop_to_aspect(probe, image_size)
+        return base + kept.shape[0] * (kept.shape[1] + 1)
+
+    def pack_views(self, feats: torch.Tensor, image_size: Sequence[int]) -> torch.Tensor:
+        """``feats [views, tokens, C]`` of one image -> ``[rows, C]`` in prompt order."""
+        nl = self.image_newline.to(feats.dtype)
+        if feats.shape[0] == 1:
+            return torch.cat([feats[0], nl[None]], dim=0)
+        side = self.vision_cfg.image_size // self.vision_cfg.patch_size
+        gh, gw = anyres_grid(image_size, self.pinpoints, self.vision_cfg.image_size)
+        C = feats.shape[-1]
+        tiles = feats[1:]
+        if tiles.shape[0] != gh * gw or tiles.shape[1] != side * side:
+            raise ValueError(f"{tiles.shape[0]} tiles of {tiles.shape[1]} rows do not form a "
+                             f"{gh} x {gw} grid of {side} x {side} patches")
+        grid = tiles.reshape(gh, gw, side, side, C).permute(0, 2, 1, 3, 4) \
+            .reshape(gh * side, gw * side, C)
+        grid = crop_to_aspect(grid, image_size)
+        grid = torch.cat([grid, nl.expand(grid.shape[0], 1, C)], dim=1)
+        return torch.cat([feats[0], grid.reshape(-1, C)], dim=0)
+
+    def encode_images(self, pixel_values, image_sizes=None) -> torch.Tensor:
+        images = list(pixel_values) if isinstance(pixel_values, (list, tuple)) or \
+            pixel_values.dim() == 5 else [pixel_values]
+        if image_sizes is None:
+            raise ValueError("LLaVA-NeXT needs image_sizes with its pixel_values")
+        sizes = torch.as_tensor(image_sizes).reshape(-1, 2).tolist()
+        out = []
+        for views, size in zip(images, sizes):
+            feats = self.vision_tower(views)
+            if self.select == "default":
+                feats = feats[:, 1:]
+            with torch.inference_mode():
+                h = self.projector["linear_2"](_act(self.projector_act,
+                                                    self.projector["linear_1"](feats)))
+                out.append(self.pack_views(h, size))
+        return torch.cat(out, dim=0)
+
+    def prepare_request(self, prompt_token_ids: Sequence[int], pixel_values,
+                        image_grid_thw=None) -> dict:
+        emb = self.encode_images(pixel_values, image_grid_thw)
+        positions = [i for i, t in enumerate(prompt_token_ids) if t == self.image_token_id]
+        assert len(positions) == emb.shape[0], \
+            f"{len(positions)} placeholder tokens for {emb.shape[0]} image feature rows"
+        first = pixel_values[0] if isinstance(pixel_values, (list, tuple)) else pixel_values
+        salt = hash((first.detach().float().cpu().numpy().tobytes(),
+                     tuple(torch.as_tensor(image_grid_thw).reshape(-1).tolist())))
+        return {"mm_embeds": emb, "mm_positions": positions, "cache_salt": salt}
+
+    def load_weights(self, weights: Iterable[tuple[str, torch.Tensor]]) -> set[str]:
+        rest, loaded = [], set()
+        for name, t in weights:
+            if name in ("image_newline", "model.image_newline"):
+                if self.is_first_stage:
+                    self.image_newline.data.copy_(t)
+                loaded.add(name)
+            else:
+                rest.append((name, t))
+        return loaded | super().load_weights(rest)
