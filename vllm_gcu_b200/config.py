@@ -112,11 +112,13 @@ class ModelConfig:
     @classmethod
     def from_hf_dict(cls, d: dict, **overrides) -> "ModelConfig":
         archs = d.get("architectures") or ["LlamaForCausalLM"]
-        for nested in ("text_config", "language_config"):
+        for nested in ("text_config", "language_config", "llm_config"):
             if isinstance(d.get(nested), dict):
                 # multimodal configs nest the language model's fields; vision_config, token
                 # ids and everything else stay reachable through ``extra``
+                inner_arch = (d[nested].get("architectures") or [None])[0]
                 d = {**{k: v for k, v in d.items() if k != nested},
+                     "llm_architecture": inner_arch, "llm_model_type": d[nested].get("model_type"),
                      **{k: v for k, v in d[nested].items()
                         if k not in ("architectures", "model_type")}}
         if archs[0] == "GPTBigCodeForCausalLM":

@@ -38,6 +38,8 @@ _REGISTRY: dict[str, str] = {
     "LlavaForConditionalGeneration": "vllm_gcu_b200.models.llava:LlavaForConditionalGeneration",
     "LlavaNextForConditionalGeneration":
         "vllm_gcu_b200.models.llava:LlavaNextForConditionalGeneration",
+    "InternVLChatModel": "vllm_gcu_b200.models.internvl:InternVLChatModel",
+    "InternVLForConditionalGeneration": "vllm_gcu_b200.models.internvl:InternVLChatModel",
     "GotOcr2ForConditionalGeneration":
         "vllm_gcu_b200.models.got_ocr2:GotOcr2ForConditionalGeneration",
     "GOTQwenForCausalLM": "vllm_gcu_b200.models.got_ocr2:GotOcr2ForConditionalGeneration",
