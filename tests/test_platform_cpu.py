@@ -80,3 +80,29 @@ def test_host_sanitizer_build_options():
     assert B.lib_path_for("thread").name == "_b200.thread.so"
     with pytest.raises(ValueError):
         B.sanitize_flags("memory")
+
+
+def test_vllm_model_registry_gets_the_extra_architectures():
+    """The general-plugin hook registers the reference's extra architecture names with vLLM's
+    ``ModelRegistry`` (lazily, by string), and the DeepSeek-VL2 class reads both spellings of
+    the separator parameter."""
+    import pytest
+    pytest.importorskip("vllm")
+    from vllm import ModelRegistry
+    from vllm_gcu_b200.runtime import vllm_models
+    done = vllm_models.register_models()
+    archs = set(ModelRegistry.get_supported_archs())
+    assert set(done) <= archs and "QuantMixtralForCausalLM" in archs
+    for arch, target in vllm_models.ALIASES.items():
+        ent = ModelRegistry.models[arch]
+        assert f"{ent.module_name}:{ent.class_name}" == target
+    import importlib
+    for target in vllm_models.ALIASES.values():       # every target resolves to a class
+        mod, _, cls = target.partition(":")
+        assert isinstance(getattr(importlib.import_module(mod), cls), type)
+    from vllm_gcu_b200.runtime.vllm_deepseek_vl2 import _OTHER, _OWN, DeepseekVLV2ForCausalLMB200
+    names = [(_OTHER, None), (_OWN, None), ("language.model.embed_tokens.weight", None),
+             ("vision.blocks.0.attn.qkv.weight", None)]
+    got = [n for n, _ in DeepseekVLV2ForCausalLMB200.hf_to_vllm_mapper.apply(names)]
+    assert got == [_OWN, _OWN, "language_model.model.embed_tokens.weight",
+                   "vision.blocks.0.attn.qkv.weight"]

@@ -21,7 +21,8 @@ def register_platform_plugins() -> str:
 def register_custom_models() -> None:
     """General plugin hook (runs in every vLLM process): registers this package's attention
     backend under ``AttentionBackendEnum.CUSTOM``, its layer kernels (RMSNorm, SiLU-and-mul,
-    unquantised GEMM, fp8 / int8 scaled GEMMs) and its quantisation configs with vLLM.  The model classes of the
+    unquantised GEMM, fp8 / int8 scaled GEMMs), its quantisation configs and the architecture
+    names upstream lacks (``runtime/vllm_models.py``) with vLLM.  The model classes of the
     built-in engine use their own registry (``vllm_gcu_b200.models``); under vLLM the upstream
     model definitions run on these kernels."""
     try:
@@ -33,6 +34,11 @@ def register_custom_models() -> None:
         from vllm.v1.attention.backends.registry import AttentionBackendEnum, register_backend
         register_backend(AttentionBackendEnum.CUSTOM,
                          "vllm_gcu_b200.runtime.vllm_attention.B200AttentionBackend")
+    except Exception:
+        pass
+    try:
+        from .runtime import vllm_models
+        vllm_models.register_models()
     except Exception:
         pass
     try:
