@@ -34,15 +34,24 @@ def test_tp2_executor_matches_single_process():
     sp = SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True)
     ex = MultiprocExecutor(_cfg(2))
     try:
+        # commands reach both ranks through one shared-memory ring
+        from vllm_gcu_b200.utils import shm_ring
+        assert (ex.rings is not None) == shm_ring.available()
         outs = ex.generate(_prompts(), sp)
         ex.check_health()
     finally:
         ex.shutdown()
+    assert ex.rings is None
     # The TP workers initialise their shards from per-shard seeds, so compare structure and
     # determinism rather than token identity with a TP=1 engine.
     assert [len(o.outputs[0].token_ids) for o in outs] == [8, 8, 8]
-    ex2 = MultiprocExecutor(_cfg(2))
+    os.environ["VLLM_B200_SHM_BROADCAST"] = "0"      # same result over pipe-backed queues
     try:
+        ex2 = MultiprocExecutor(_cfg(2))
+    finally:
+        del os.environ["VLLM_B200_SHM_BROADCAST"]
+    try:
+        assert ex2.rings is None
         outs2 = ex2.generate(_prompts(), sp)
     finally:
         ex2.shutdown()

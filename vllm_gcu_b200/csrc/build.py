@@ -125,6 +125,8 @@ def main() -> None:
                     help="host-side sanitizer build into _b200.<kind>.so")
     a = ap.parse_args()
     print(build(a.force, a.verbose, a.j, a.sanitize))
+    from ..utils.shm_ring import build_host_library
+    print(build_host_library(a.force))          # host/shm_ring.cpp -> _b200_host.so (g++)
 
 
 if __name__ == "__main__":

@@ -109,12 +109,14 @@ def _worker_main(rank: int, world: int, port: int, cfg: EngineConfig, cmd_q, out
         while not stop:
             hb.value = time.monotonic()
             # 1) agree on the commands applied before this step
+            # every rank takes what has arrived (a shared-memory ring is bounded: a rank that
+            # left commands in it would hold up the writer), the lead decides how many apply
+            while True:
+                try:
+                    pending.append(cmd_q.get_nowait())
+                except queue.Empty:
+                    break
             if rank == lead:
-                while True:
-                    try:
-                        pending.append(cmd_q.get_nowait())
-                    except queue.Empty:
-                        break
                 if not pending and not engine.has_unfinished() and not (
                         dp > 1 and engine.dp_global_busy):
                     try:
@@ -175,7 +177,21 @@ class MultiprocExecutor:
         self.world = cfg.parallel.world_size
         ctx = mp.get_context("spawn")
         self.out_q = ctx.Queue()
-        self.cmd_qs = [ctx.Queue() for _ in range(self.world)]
+        self.dp = cfg.parallel.data_parallel_size
+        self.per_replica = self.world // self.dp
+        # commands travel through one shared-memory broadcast ring per replica (every rank of
+        # a replica reads every command of that replica); pipe-backed queues when the native
+        # host library is not available or VLLM_B200_SHM_BROADCAST=0
+        from .. import envs
+        from ..utils import shm_ring
+        self.rings = None
+        self._use_rings = bool(envs.SHM_BROADCAST) and shm_ring.available()
+        if self._use_rings:
+            self.rings = [shm_ring.RingWriter(self.per_replica) for _ in range(self.dp)]
+            self.cmd_qs = [self.rings[r // self.per_replica].reader(r % self.per_replica)
+                           for r in range(self.world)]
+        else:
+            self.cmd_qs = [ctx.Queue() for _ in range(self.world)]
         self.hbs = [ctx.Value("d", time.monotonic()) for _ in range(self.world)]
         port = _free_port()
         self.procs = [ctx.Process(target=_worker_main, daemon=True,
@@ -187,8 +203,6 @@ class MultiprocExecutor:
         self.dead: Optional[str] = None
         self._lock = threading.Lock()
         self._ids = 0
-        self.dp = cfg.parallel.data_parallel_size
-        self.per_replica = self.world // self.dp
         self._replica_of: dict[str, int] = {}
         self._in_flight = [0] * self.dp
         ready = 0
@@ -244,8 +258,22 @@ class MultiprocExecutor:
         if self.dead:
             raise EngineDeadError(self.dead)
         with self._lock:
-            for q in self.cmd_qs:
-                q.put(cmd)
+            for d in range(self.dp):
+                self._send(d, cmd)
+
+    def _send(self, replica: int, cmd: _Cmd, timeout: Optional[float] = None) -> None:
+        """Hands ``cmd`` to every rank of ``replica`` (caller holds the lock)."""
+        if self._use_rings:
+            if self.rings is None:
+                raise EngineDeadError(self.dead or "the executor was shut down")
+            try:
+                self.rings[replica].put(cmd, timeout)
+            except TimeoutError as e:
+                self.dead = self.dead or f"command ring of replica {replica}: {e}"
+                raise EngineDeadError(self.dead)
+            return
+        for r in range(replica * self.per_replica, (replica + 1) * self.per_replica):
+            self.cmd_qs[r].put(cmd)
 
     # -- API -----------------------------------------------------------------------
     def add_request(self, prompt_token_ids: Sequence[int],
@@ -265,8 +293,7 @@ class MultiprocExecutor:
             d = min(range(self.dp), key=lambda i: self._in_flight[i])
             self._in_flight[d] += 1
             self._replica_of[request_id] = d
-            for r in range(d * self.per_replica, (d + 1) * self.per_replica):
-                self.cmd_qs[r].put(cmd)
+            self._send(d, cmd)
         return request_id
 
     def abort_request(self, request_id: str) -> None:
@@ -316,9 +343,9 @@ class MultiprocExecutor:
         return [final[i] for i in ids]
 
     def shutdown(self) -> None:
-        for q in self.cmd_qs:
+        for d in range(self.dp):
             try:
-                q.put(_Cmd("stop"))
+                self._send(d, _Cmd("stop"), timeout=1.0)
             except Exception:
                 pass
         t_end = time.monotonic() + 5.0
@@ -331,6 +358,9 @@ class MultiprocExecutor:
             p.join(2.0)
             if p.is_alive():
                 p.kill()
+        rings, self.rings = self.rings, None
+        for ring in rings or ():
+            ring.close()
 
     def __del__(self):
         try:

@@ -72,6 +72,9 @@ environment_variables: dict[str, Callable[[], Any]] = {
     # 8-bit linear layers take their input already quantised from the norm / activation kernel
     # in front of them (0: separate quantisation kernels, for comparison)
     "FUSE_ACT_QUANT": _flag("FUSE_ACT_QUANT", "1"),
+    # the executor's commands reach the workers through a shared-memory broadcast ring
+    # (0: one pipe-backed queue per worker)
+    "SHM_BROADCAST": _flag("SHM_BROADCAST", "1"),
     "NIXL_ENABLE_FULL_KV_TRANSFER": _flag("NIXL_ENABLE_FULL_KV_TRANSFER", "1"),
     # ... and starts at the first output token the prefill instance already produced
     "NIXL_ENABLE_FIRST_TOKEN_REUSE": _flag("NIXL_ENABLE_FIRST_TOKEN_REUSE"),
