@@ -5,7 +5,9 @@ Poisson (gamma with configurable burstiness) arrivals, random token-id prompts w
 input / output lengths, streaming responses; reports request and token throughput and
 mean / median / p99 of TTFT, TPOT, ITL and end-to-end latency
 (benchmarks/benchmark_serving.py:414-562 of the reference, including its ``--extra-body``
-and ``--strict-in-out-len`` conveniences).
+and ``--strict-in-out-len`` conveniences).  ``--goodput ttft:200 tpot:50`` counts the requests
+that met every given service-level objective (milliseconds); ``--max-concurrency`` caps the
+requests in flight; several ``--ports`` spread the requests over as many servers.
 
 Example:
   python -m vllm_gcu_b200.entrypoints.api_server --model llama-3-8b --port 8000 &
@@ -59,7 +61,15 @@ async def run(args):
     rng = random.Random(args.seed)
     nprng = np.random.default_rng(args.seed)
     chat = args.backend == "openai-chat"
-    url = f"http://{args.host}:{args.port}/v1/" + ("chat/completions" if chat else "completions")
+    path = "/v1/" + ("chat/completions" if chat else "completions")
+    urls = [f"http://{args.host}:{p}{path}" for p in (args.ports or [args.port])]
+    gate = asyncio.Semaphore(args.max_concurrency) if args.max_concurrency else None
+
+    async def limited(session, url, body, results):
+        if gate is None:
+            return await one_request(session, url, body, results)
+        async with gate:
+            return await one_request(session, url, body, results)
     extra = json.loads(args.extra_body) if args.extra_body else {}
     results: list = []
     tasks = []
@@ -77,21 +87,46 @@ async def run(args):
             else:
                 body["prompt"] = [rng.randrange(10, args.vocab_size) for _ in range(n_in)]
             body.update(extra)
-            tasks.append(asyncio.create_task(one_request(session, url, body, results)))
+            tasks.append(asyncio.create_task(
+                limited(session, urls[i % len(urls)], body, results)))
             if args.request_rate != float("inf"):
                 theta = 1.0 / (args.request_rate * args.burstiness)
                 await asyncio.sleep(float(nprng.gamma(shape=args.burstiness, scale=theta)))
         await asyncio.gather(*tasks)
         dur = time.perf_counter() - t_start
+    res = summarise(results, dur, parse_goodput(args.goodput))
+    print(json.dumps(res, indent=1))
+    if args.output_json:
+        with open(args.output_json, "w") as f:
+            json.dump(res, f)
+    return res
+
+
+def parse_goodput(pairs) -> dict:
+    """``["ttft:200", "tpot:50"]`` -> ``{"ttft": 0.2, "tpot": 0.05}`` (seconds)."""
+    out = {}
+    for p in pairs or ():
+        name, _, ms = p.partition(":")
+        if name not in ("ttft", "tpot", "e2el"):
+            raise ValueError(f"unknown service-level objective {name!r} (ttft, tpot, e2el)")
+        out[name] = float(ms) / 1e3
+    return out
+
+
+def summarise(results: list, dur: float, slo: dict | None = None) -> dict:
+    """Throughput and latency statistics of finished requests; with ``slo`` also the rate of
+    requests that met every objective."""
     ok = [r for r in results if r["ok"]]
     if not ok:
-        print(json.dumps({"completed": 0, "errors": [r.get("error") for r in results][:3]}))
-        return
-    ttft = np.array([r["ttft"] for r in ok if r["ttft"] is not None])
+        return {"completed": 0, "failed": len(results),
+                "errors": [r.get("error") for r in results][:3]}
+    for r in ok:
+        r["tpot"] = ((r["e2e"] - r["ttft"]) / max(1, r["n_out"] - 1)
+                     if r["ttft"] is not None and r["n_out"] > 1 else None)
+    ttft = np.array([r["ttft"] for r in ok if r["ttft"] is not None] or [0.0])
     e2e = np.array([r["e2e"] for r in ok])
-    tpot = np.array([(r["e2e"] - r["ttft"]) / max(1, r["n_out"] - 1) for r in ok
-                     if r["ttft"] is not None and r["n_out"] > 1])
-    itl = np.array([x for r in ok for x in r["itl"]]) if any(r["itl"] for r in ok) else np.array([0.0])
+    tpot = np.array([r["tpot"] for r in ok if r["tpot"] is not None] or [0.0])
+    itl = np.array([x for r in ok for x in r["itl"]] or [0.0])
 
     def st(x):
         return {"mean_ms": float(x.mean() * 1e3), "median_ms": float(np.median(x) * 1e3),
@@ -102,16 +137,25 @@ async def run(args):
            "output_token_throughput": sum(r["n_out"] for r in ok) / dur,
            "total_token_throughput": sum(r["n_out"] + r["n_in"] for r in ok) / dur,
            "ttft": st(ttft), "tpot": st(tpot), "itl": st(itl), "e2el": st(e2e)}
-    print(json.dumps(res, indent=1))
-    if args.output_json:
-        with open(args.output_json, "w") as f:
-            json.dump(res, f)
+    if slo:
+        good = sum(1 for r in ok
+                   if ("ttft" not in slo or (r["ttft"] is not None and r["ttft"] <= slo["ttft"]))
+                   and ("tpot" not in slo or r["tpot"] is None or r["tpot"] <= slo["tpot"])
+                   and ("e2el" not in slo or r["e2e"] <= slo["e2el"]))
+        res["request_goodput"] = good / dur
+        res["good_requests"] = good
+    return res
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--host", default="127.0.0.1")
     ap.add_argument("--port", type=int, default=8000)
+    ap.add_argument("--ports", type=int, nargs="+", default=None,
+                    help="several servers: requests are spread over them in turn")
+    ap.add_argument("--max-concurrency", type=int, default=None)
+    ap.add_argument("--goodput", nargs="+", default=None,
+                    help="service-level objectives in ms, e.g. ttft:200 tpot:50 e2el:5000")
     ap.add_argument("--backend", default="openai", choices=["openai", "openai-chat"],
                     help="/v1/completions with token-id prompts, or /v1/chat/completions")
     ap.add_argument("--num-prompts", type=int, default=1000)

@@ -1,0 +1,123 @@
+"""The serving benchmark tools against live HTTP servers on the CPU engine (tiny model):
+``benchmark_serving.py`` over two servers with a concurrency cap and goodput objectives,
+``benchmark_serving_prioritization.py`` with its lowest-priority background load, and the
+data-parallel router in front of both servers."""
+import argparse
+import asyncio
+import importlib.util
+import os
+import socket
+import sys
+import threading
+import time
+
+import pytest
+
+pytest.importorskip("aiohttp")
+uvicorn = pytest.importorskip("uvicorn")
+
+from vllm_gcu_b200.config import CacheConfig, EngineConfig, SchedulerConfig, preset  # noqa: E402
+from vllm_gcu_b200.engine.async_llm import AsyncLLM  # noqa: E402
+from vllm_gcu_b200.entrypoints.api_server import ByteTokenizer, build_app  # noqa: E402
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _load(name):
+    path = os.path.join(ROOT, "benchmarks", name + ".py")
+    sys.path.insert(0, os.path.dirname(path))
+    spec = importlib.util.spec_from_file_location(name, path)
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+class _Server:
+    def __init__(self, app):
+        self.port = _free_port()
+        self.server = uvicorn.Server(uvicorn.Config(app, host="127.0.0.1", port=self.port,
+                                                    log_level="error"))
+        self.thread = threading.Thread(target=self.server.run, daemon=True)
+        self.thread.start()
+        t_end = time.monotonic() + 30
+        while not self.server.started and time.monotonic() < t_end:
+            time.sleep(0.02)
+        assert self.server.started
+
+    def stop(self):
+        self.server.should_exit = True
+        self.thread.join(10)
+
+
+@pytest.fixture(scope="module")
+def servers():
+    engines, srv = [], []
+    for _ in range(2):
+        cfg = EngineConfig(model=preset("tiny-llama"), cache=CacheConfig(num_gpu_blocks=128),
+                           scheduler=SchedulerConfig(max_num_seqs=8, max_num_batched_tokens=64,
+                                                     max_model_len=128, policy="priority"),
+                           device="cpu")
+        eng = AsyncLLM(cfg)
+        engines.append(eng)
+        srv.append(_Server(build_app(eng, ByteTokenizer(32000), "tiny-llama")))
+    yield srv
+    for s in srv:
+        s.stop()
+    for e in engines:
+        e.shutdown()
+
+
+@pytest.mark.timeout(180)
+def test_serving_benchmark_over_two_servers(servers):
+    bs = _load("benchmark_serving")
+    args = argparse.Namespace(
+        host="127.0.0.1", port=servers[0].port, ports=[s.port for s in servers],
+        backend="openai", num_prompts=6, request_rate=float("inf"), burstiness=1.0,
+        input_len_range=[4, 12], output_len_range=[3, 6], vocab_size=32000, temperature=0.0,
+        extra_body=None, seed=0, output_json=None, max_concurrency=3,
+        goodput=["ttft:60000", "tpot:60000"])
+    res = asyncio.run(bs.run(args))
+    assert res["completed"] == 6 and res["failed"] == 0
+    assert res["good_requests"] == 6 and res["request_goodput"] > 0
+    assert res["output_token_throughput"] > 0 and res["ttft"]["median_ms"] > 0
+    strict = bs.summarise([{"ok": True, "ttft": 0.5, "e2e": 1.0, "itl": [0.1], "n_out": 6,
+                            "n_in": 4}], 1.0, bs.parse_goodput(["ttft:100"]))
+    assert strict["good_requests"] == 0 and strict["tpot"]["mean_ms"] == pytest.approx(100.0)
+    with pytest.raises(ValueError):
+        bs.parse_goodput(["latency:5"])
+
+
+@pytest.mark.timeout(180)
+def test_prioritization_benchmark_keeps_background_load(servers):
+    bp = _load("benchmark_serving_prioritization")
+    res = bp.main(["--ports", *[str(s.port) for s in servers], "--num-prompts", "5",
+                   "--input-len-range", "4", "10", "--output-len-range", "3", "5",
+                   "--background-tokens", "4", "--goodput", "e2el:60000"])
+    assert res["completed"] == 5 and res["failed"] == 0
+    assert res["background_requests"] >= 2 and res["good_requests"] == 5
+
+
+@pytest.mark.timeout(180)
+def test_router_spreads_requests_and_forwards_streams(servers):
+    rt = _load("router")
+    router = rt.Router([f"127.0.0.1:{s.port}" for s in servers])
+    front = _Server(router.app())
+    try:
+        bs = _load("benchmark_serving")
+        args = argparse.Namespace(
+            host="127.0.0.1", port=front.port, ports=None, backend="openai", num_prompts=4,
+            request_rate=float("inf"), burstiness=1.0, input_len_range=[4, 8],
+            output_len_range=[3, 4], vocab_size=32000, temperature=0.0, extra_body=None,
+            seed=1, output_json=None, max_concurrency=None, goodput=None)
+        res = asyncio.run(bs.run(args))
+        assert res["completed"] == 4 and res["failed"] == 0
+        assert router.active == [0, 0]
+    finally:
+        front.stop()
