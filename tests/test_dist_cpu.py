@@ -241,3 +241,88 @@ def test_etp_gather_scatter_matches_reference(world, tp):
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     mp.spawn(_worker_etp, args=(world, port, tp), nprocs=world, join=True)
+
+
+def _check_ep_tp(rank, world, shared):
+    """Expert parallelism over dp x tp ranks with tensor-parallel attention inside a replica:
+    each tensor-parallel rank dispatches its own slice of the replica's rows, so a token
+    reaches every destination rank once per replica; with shared experts their partial sums
+    and the routed rows leave through one all-reduce."""
+    from vllm_gcu_b200.config import preset
+    from vllm_gcu_b200.layers.moe import SparseMoeBlock
+    from vllm_gcu_b200.ops import ref
+    from vllm_gcu_b200.parallel.state import get_state
+    st = get_state()
+    cfg = preset("tiny-qwen3-moe", num_experts=8, num_experts_per_tok=2,
+                 num_shared_experts=shared)
+    cfg.extra["dp_attention"] = True
+    torch.manual_seed(0)
+    blk = SparseMoeBlock(cfg, "cpu", "m")
+    assert blk.use_ep and blk.dispatcher is not None
+    E, I, H = cfg.num_experts, cfg.moe_intermediate_size, cfg.hidden_size
+    Is = I * max(shared, 1)
+    g = torch.Generator().manual_seed(1)
+    w13 = torch.randn(E, 2 * I, H, generator=g) * 0.05
+    w2 = torch.randn(E, H, I, generator=g) * 0.05
+    gate = torch.randn(E, H, generator=g) * 0.5
+    sw_gu = torch.randn(2 * Is, H, generator=g) * 0.05
+    sw_d = torch.randn(H, Is, generator=g) * 0.05
+    blk.gate.weight.data.copy_(gate)
+    for e in range(E):
+        blk.experts.load_expert_weight(e, "gate", w13[e, :I])
+        blk.experts.load_expert_weight(e, "up", w13[e, I:])
+        blk.experts.load_expert_weight(e, "down", w2[e])
+    if shared:
+        blk.shared_experts.gate_up_proj.load_weight("weight", sw_gu[:Is], 0)
+        blk.shared_experts.gate_up_proj.load_weight("weight", sw_gu[Is:], 1)
+        blk.shared_experts.down_proj.load_weight("weight", sw_d, None)
+    seen = {"rows": 0}
+    inner = blk.experts.forward
+
+    def counting(xr, *a, **kw):
+        seen["rows"] += xr.shape[0]
+        return inner(xr, *a, **kw)
+    blk.experts.forward = counting
+    d = st.dp.rank_in_group
+    per_rank = E // world
+    for trial in range(3):
+        # one replica idle in the first trial; a single row (fewer rows than TP ranks) last
+        T = 0 if (d == 1 and trial == 0) else (1 if trial == 2 else 4 + d + trial)
+        x = torch.randn(T, H, generator=torch.Generator().manual_seed(10 + d + 7 * trial))
+        seen["rows"] = 0
+        got = blk(x)
+        visits = 0
+        if T:
+            w, ids = ref.topk_softmax(x @ gate.t(), 2, True)
+            want = ref.fused_experts(x, w13, w2, w, ids)
+            if shared:
+                gu = x @ sw_gu.t()
+                want = want + (torch.nn.functional.silu(gu[:, :Is]) * gu[:, Is:]) @ sw_d.t()
+            assert torch.allclose(got, want, atol=1e-5, rtol=1e-4), (got - want).abs().max()
+            visits = sum(len({int(e) // per_rank for e in row}) for row in ids.tolist())
+        assert got.shape == x.shape
+        # rows that reached any rank's experts = token visits, counted once per replica
+        tot = torch.tensor([seen["rows"], visits if st.tp.rank_in_group == 0 else 0])
+        dist.all_reduce(tot)
+        assert int(tot[0]) == int(tot[1]), tot.tolist()
+
+
+def _worker_ep_tp(rank, world, port, tp, shared):
+    sys.path.insert(0, ROOT)
+    os.environ.update({"RANK": str(rank), "WORLD_SIZE": str(world), "LOCAL_RANK": str(rank),
+                       "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port)})
+    from vllm_gcu_b200.parallel.state import init_distributed
+    init_distributed(tp=tp, dp=world // tp, backend="gloo", enable_ep=True)
+    _check_ep_tp(rank, world, shared)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+@pytest.mark.parametrize("shared", [0, 1])
+def test_expert_parallel_with_tensor_parallel_replicas(shared):
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_worker_ep_tp, args=(4, port, 2, shared), nprocs=4, join=True)

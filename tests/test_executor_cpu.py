@@ -172,3 +172,36 @@ def test_dp2_etp_executor_matches_single_process(tmp_path):
                 want[int(o.request_id)] = o.outputs[0].token_ids
     assert [o.outputs[0].token_ids for o in many] == [want[i_] for i_ in range(len(prompts))]
     assert one[0].outputs[0].token_ids == want[0]
+
+
+@pytest.mark.timeout(400)
+def test_dp2_tp2_ep_executor_matches_single_process(tmp_path):
+    """Expert parallelism over four ranks arranged as two replicas of two tensor-parallel
+    ranks: every tensor-parallel rank dispatches its slice of the replica's rows (decode steps
+    leave one of them with no row at all); the tokens are those of one unsharded engine."""
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    g = torch.Generator().manual_seed(6)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (9, 30, 4, 21)]
+    _moe_checkpoint(str(tmp_path), preset("tiny-qwen3-moe"))
+    cfg = _dp_cfg()
+    cfg.parallel.tensor_parallel_size = 2
+    cfg.load_format, cfg.model_path = "safetensors", str(tmp_path)
+    ex = MultiprocExecutor(cfg)
+    try:
+        many = ex.generate(prompts, sp, timeout_s=200)
+        ex.check_health()
+    finally:
+        ex.shutdown()
+    single = _dp_cfg()
+    single.parallel = ParallelConfig()
+    single.model.extra.pop("dp_attention")
+    single.load_format, single.model_path = "safetensors", str(tmp_path)
+    eng = LLMEngine(single)
+    for i_, p_ in enumerate(prompts):
+        eng.add_request(p_, sp, request_id=str(i_))
+    want = {}
+    while eng.has_unfinished():
+        for o in eng.step():
+            if o.finished:
+                want[int(o.request_id)] = o.outputs[0].token_ids
+    assert [o.outputs[0].token_ids for o in many] == [want[i_] for i_ in range(len(prompts))]

@@ -75,6 +75,9 @@ environment_variables: dict[str, Callable[[], Any]] = {
     # the executor's commands reach the workers through a shared-memory broadcast ring
     # (0: one pipe-backed queue per worker)
     "SHM_BROADCAST": _flag("SHM_BROADCAST", "1"),
+    # expert parallelism with tensor-parallel attention inside a replica: every tensor-parallel
+    # rank dispatches its own slice of the replica's rows (0: every rank dispatches all rows)
+    "EP_TP_SLICE": _flag("EP_TP_SLICE", "1"),
     "NIXL_ENABLE_FULL_KV_TRANSFER": _flag("NIXL_ENABLE_FULL_KV_TRANSFER", "1"),
     # ... and starts at the first output token the prefill instance already produced
     "NIXL_ENABLE_FIRST_TOKEN_REUSE": _flag("NIXL_ENABLE_FIRST_TOKEN_REUSE"),

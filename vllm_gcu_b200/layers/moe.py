@@ -541,6 +541,35 @@ class SparseMoeBlock(nn.Module):
         topk_w, topk_ids = select_experts(logits, self.cfg, self.e_score_correction_bias,
                                           self.eplb)
         from .. import envs
+        # Tensor-parallel ranks of one replica hold the same rows after attention.  Each of
+        # them dispatches only its own slice of the rows (uneven split, as sequence
+        # parallelism uses), so a token visits its experts once per replica instead of once
+        # per tensor-parallel rank; the slices are put together again below.
+        tp = tp_size()
+        sliced = self.dispatcher is not None and tp > 1 and envs.EP_TP_SLICE
+        xd, wd, idd = x, topk_w, topk_ids
+        if sliced:
+            from ..parallel.sp import scatter
+            sizes = scatter(x.shape[0], tp)
+            lo = sum(sizes[:tp_rank()])
+            hi = lo + sizes[tp_rank()]
+            xd, wd, idd = x[lo:hi], topk_w[lo:hi], topk_ids[lo:hi]
+
+        def merge(routed: torch.Tensor, shared_) -> torch.Tensor:
+            """Sliced mode: routed rows of this rank + TP-partial shared-expert output of all
+            rows -> full output on every rank."""
+            if shared_ is None:
+                return get_comm("tp").all_gather_v(routed, sizes)
+            shared_[lo:hi] += routed.to(shared_.dtype)      # a fresh tensor of this call
+            return get_comm("tp").all_reduce(shared_)
+
+        def unsliced(out_: torch.Tensor, shared_) -> torch.Tensor:
+            """Every rank dispatched all rows: the routed sum is whole on every rank, only the
+            shared experts' output is a partial sum over the tensor-parallel ranks."""
+            if tp > 1 and shared_ is not None:
+                out_ = out_ - shared_ + get_comm("tp").all_reduce(shared_.clone())
+            return out_
+
         side = None
         if (self.shared_experts is not None and self.dispatcher is not None and x.is_cuda
                 and envs.ENABLE_PARALLEL_COMPUTE and not torch.cuda.is_current_stream_capturing()):
@@ -556,22 +585,26 @@ class SparseMoeBlock(nn.Module):
             shared = self.shared_experts(x) if self.shared_experts is not None else None
         if side is not None:
             # the dispatcher adds `shared` in its combine step: join before that
-            xr = self.dispatcher.ws.dispatch(x, topk_w.float(), topk_ids.to(torch.int32),
+            xr = self.dispatcher.ws.dispatch(xd, wd.float(), idd.to(torch.int32),
                                              get_state().dp_max_tokens) \
                 if hasattr(self.dispatcher, "ws") else None
             torch.cuda.current_stream().wait_stream(side)
             if xr is not None:
                 rx, rw, rids, total = xr
                 yr = self.experts(rx, rw, rids, valid_tokens=total)
+                if sliced:
+                    return merge(self.dispatcher.ws.combine(yr, xd.shape[0], None),
+                                 shared).view(shape)
                 out = self.dispatcher.ws.combine(yr, x.shape[0], shared)
-                tp_partial = tp_size() > 1
-                return (get_comm("tp").all_reduce(out) if tp_partial else out).view(shape)
+                return unsliced(out, shared).view(shape)
         if self.dispatcher is not None:
-            # tokens differ per rank: all-to-all dispatch / combine; the shared experts are
-            # replicated so their (TP-partial) output only needs the TP reduction below
+            # tokens differ per rank: all-to-all dispatch / combine, seeded with the shared
+            # experts' output (a replica without tensor parallelism holds them whole)
+            if sliced:
+                routed = self.dispatcher(xd, wd, idd, None, get_state().dp_max_tokens)
+                return merge(routed, shared).view(shape)
             out = self.dispatcher(x, topk_w, topk_ids, shared, get_state().dp_max_tokens)
-            tp_partial = shared is not None and tp_size() > 1
-            return (get_comm("tp").all_reduce(out) if tp_partial else out).view(shape)
+            return unsliced(out, shared).view(shape)
         # For plain top-k routing the scaling factor is applied on the combined output;
         # the grouped router already folded it into the weights.
         out = self.experts(x, topk_w, topk_ids, add=shared)
