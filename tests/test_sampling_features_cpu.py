@@ -158,3 +158,22 @@ def test_empty_prompt_is_rejected_and_does_not_block_the_queue():
     out = llm.generate([_prompt(6, 8)], SamplingParams(max_tokens=4, temperature=0.0,
                                                        ignore_eos=True))[0]
     assert len(out.outputs[0].token_ids) == 4
+
+
+def test_seeded_sampling_depends_on_the_request_only():
+    """A request with a seed draws the same tokens whatever shares its steps and whether the
+    engine schedules ahead of its results or not: the draw of its i-th token is a function of
+    (seed, i) alone."""
+    sp = SamplingParams(max_tokens=10, temperature=0.9, top_p=0.95, top_k=50, seed=11,
+                        ignore_eos=True)
+    other = SamplingParams(max_tokens=7, temperature=1.2, seed=3, ignore_eos=True)
+    p, q, r = _prompt(17, 2), _prompt(40, 3), _prompt(5, 4)
+    llm = _llm()
+    alone = llm.generate([p], sp)[0].outputs[0].token_ids
+    mixed = llm.generate([q, p, r], [other, sp, other])[1].outputs[0].token_ids
+    assert alone == mixed and len(alone) == 10
+    ahead = _llm(async_scheduling=True).generate([q, p, r], [other, sp, other])
+    assert ahead[1].outputs[0].token_ids == alone
+    different = llm.generate([p], SamplingParams(max_tokens=10, temperature=0.9, top_p=0.95,
+                                                 top_k=50, seed=12, ignore_eos=True))
+    assert different[0].outputs[0].token_ids != alone

@@ -523,8 +523,7 @@ class ModelRunner:
                 f32[self.max_seqs + r] = sp.top_p
                 i32[o_tk + r] = sp.top_k
                 base = sp.seed if sp.seed is not None else zlib.crc32(req.request_id.encode())
-                i64[o_seed + r] = (base * 1000003 + len(req.output_token_ids)
-                                   + req.num_output_placeholders) & 0x7FFFFFFFFFFFFFFF
+                i64[o_seed + r] = (base * 1000003 + order[j].sample_index) & 0x7FFFFFFFFFFFFFFF
         # per-sequence metadata
         i32[o_sl:o_sl + B] = seq_after
         if B_pad > B:

@@ -35,6 +35,7 @@ class ScheduledRequest:
     spec_token_ids: list[int] = field(default_factory=list)
     will_sample: bool = False  # this step produces the next token(s) of the request
     epoch: int = 0             # the request's preemption count when this step was planned
+    sample_index: int = 0      # index of the first output token this step produces
 
 
 @dataclass
@@ -336,6 +337,9 @@ class Scheduler:
             will_sample = req.num_computed_tokens >= (req.num_tokens_with_placeholders
                                                       + len(s.spec_token_ids))
             s.will_sample = will_sample
+            # tokens already produced or in flight: the same number whether earlier steps have
+            # been retired yet or not, so a seeded draw does not depend on the scheduling mode
+            s.sample_index = len(req.output_token_ids) + req.num_output_placeholders
             if self.async_mode and will_sample:
                 req.num_output_placeholders += 1 + len(s.spec_token_ids)
             if s.spec_token_ids:

@@ -75,11 +75,16 @@ class Sampler(nn.Module):
         if st is None:
             ids = logits.float().argmax(-1)
         else:
-            g = None
+            noise = None
             if st.seeds is not None and st.seeds.numel() > 0:
+                # one generator per row, as in the kernel: a request's draw depends on its own
+                # seed only, not on which other requests share the step
+                noise = torch.empty(logits.shape, dtype=torch.float32, device=logits.device)
                 g = torch.Generator(device=logits.device)
-                g.manual_seed(int(st.seeds.sum().item()) & 0x7FFFFFFF)
-            ids = ref.sample(logits, st.temperature, st.top_k, st.top_p, generator=g)
+                for r, sd in enumerate(st.seeds.tolist()):
+                    g.manual_seed(int(sd) & 0x7FFFFFFFFFFFFFFF)
+                    noise[r].exponential_(generator=g)
+            ids = ref.sample(logits, st.temperature, st.top_k, st.top_p, noise=noise)
         if out is not None:
             out.copy_(ids)
             return out
