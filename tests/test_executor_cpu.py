@@ -205,3 +205,39 @@ def test_dp2_tp2_ep_executor_matches_single_process(tmp_path):
             if o.finished:
                 want[int(o.request_id)] = o.outputs[0].token_ids
     assert [o.outputs[0].token_ids for o in many] == [want[i_] for i_ in range(len(prompts))]
+
+
+@pytest.mark.timeout(400)
+def test_tp4_with_two_kv_heads_and_a_small_vocabulary_matches_transformers(tmp_path):
+    """More tensor-parallel ranks than KV heads (each KV head lives on two ranks) and a
+    vocabulary that leaves the last rank's padded shard without a real column: the greedy
+    tokens are those of the HuggingFace model with the same weights."""
+    tr = pytest.importorskip("transformers")
+    from vllm_gcu_b200.config import ModelConfig
+    from vllm_gcu_b200.utils.weights import write_safetensors
+    hc = tr.LlamaConfig(vocab_size=300, hidden_size=64, intermediate_size=128,
+                        num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=2,
+                        max_position_embeddings=128, rms_norm_eps=1e-6,
+                        tie_word_embeddings=False)
+    torch.manual_seed(0)
+    hf = tr.LlamaForCausalLM(hc).eval().float()
+    write_safetensors(os.path.join(str(tmp_path), "model.safetensors"),
+                      {k: v.clone() for k, v in hf.state_dict().items()})
+    d = hc.to_dict()
+    d["architectures"] = ["LlamaForCausalLM"]
+    cfg = _cfg(4)
+    cfg.model = ModelConfig.from_hf_dict(d, dtype=torch.float32)
+    cfg.load_format, cfg.model_path = "safetensors", str(tmp_path)
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, 300, (n,), generator=g).tolist() for n in (17, 40, 5)]
+    ex = MultiprocExecutor(cfg)
+    try:
+        outs = ex.generate(prompts, SamplingParams(max_tokens=8, temperature=0.0,
+                                                   ignore_eos=True), timeout_s=300)
+    finally:
+        ex.shutdown()
+    for p, o in zip(prompts, outs):
+        with torch.inference_mode():
+            want = hf.generate(torch.tensor([p]), max_new_tokens=8, do_sample=False,
+                               pad_token_id=0)[0, len(p):].tolist()
+        assert o.outputs[0].token_ids == want

@@ -202,6 +202,11 @@ class ParallelLMHead(VocabParallelEmbedding):
         lg = lg[..., :valid]
         if tp_size() == 1:
             return lg.argmax(-1)
+        if valid == 0:
+            # a vocabulary smaller than the padded shards leaves the last ranks without a real
+            # column: they take part in the exchange with a value that never wins
+            lg = lg.new_full((*lg.shape[:-1], 1), float("-inf"))
+            valid = 1
         if ops.use_native(hidden) and lg.dim() == 2:
             fused = getattr(get_comm("tp"), "fused", None)
             ids = fused.greedy_argmax(lg, valid, self.start) if fused is not None else None
