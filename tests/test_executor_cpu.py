@@ -238,6 +238,7 @@ def test_tp4_with_two_kv_heads_and_a_small_vocabulary_matches_transformers(tmp_p
         ex.shutdown()
     for p, o in zip(prompts, outs):
         with torch.inference_mode():
-            want = hf.generate(torch.tensor([p]), max_new_tokens=8, do_sample=False,
-                               pad_token_id=0)[0, len(p):].tolist()
+            ids = torch.tensor([p])
+            want = hf.generate(ids, attention_mask=torch.ones_like(ids), max_new_tokens=8,
+                               do_sample=False, pad_token_id=299)[0, len(p):].tolist()
         assert o.outputs[0].token_ids == want
