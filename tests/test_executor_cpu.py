@@ -242,3 +242,80 @@ def test_tp4_with_two_kv_heads_and_a_small_vocabulary_matches_transformers(tmp_p
             want = hf.generate(ids, attention_mask=torch.ones_like(ids), max_new_tokens=8,
                                do_sample=False, pad_token_id=299)[0, len(p):].tolist()
         assert o.outputs[0].token_ids == want
+
+
+def _deepseek_checkpoint(path, mc):
+    """Random DeepSeek-V3 style weights under HuggingFace names: separate ``q_a_proj`` /
+    ``kv_a_proj_with_mqa``, gate / up halves, one tensor per expert projection, the routing
+    bias below ``mlp.gate``."""
+    from vllm_gcu_b200.models import build_model
+    from vllm_gcu_b200.utils.weights import write_safetensors
+    src = build_model(mc, "cpu")
+    src.init_random(3, std=0.08)
+    out = {}
+    for name, p_ in src.state_dict().items():
+        if name.startswith(("layers.", "embed_tokens.", "norm.")):
+            name = "model." + name
+        if name.endswith("qkv_a_proj.weight"):
+            out[name.replace("qkv_a_proj", "q_a_proj")] = p_[:mc.q_lora_rank].clone()
+            out[name.replace("qkv_a_proj", "kv_a_proj_with_mqa")] = p_[mc.q_lora_rank:].clone()
+        elif name.endswith(".experts.w13"):
+            half = p_.shape[1] // 2
+            for e in range(p_.shape[0]):
+                out[name[:-3] + f"{e}.gate_proj.weight"] = p_[e, :half].clone()
+                out[name[:-3] + f"{e}.up_proj.weight"] = p_[e, half:].clone()
+        elif name.endswith(".experts.w2"):
+            for e in range(p_.shape[0]):
+                out[name[:-2] + f"{e}.down_proj.weight"] = p_[e].clone()
+        elif name.endswith("gate_up_proj.weight"):
+            half = p_.shape[0] // 2
+            out[name.replace("gate_up_proj", "gate_proj")] = p_[:half].clone()
+            out[name.replace("gate_up_proj", "up_proj")] = p_[half:].clone()
+        elif name.endswith("mlp.e_score_correction_bias"):
+            g = torch.Generator().manual_seed(len(out))
+            out[name.replace("mlp.e_score", "mlp.gate.e_score")] = \
+                torch.randn(p_.shape, generator=g) * 0.1
+        else:
+            out[name] = p_.clone()
+    write_safetensors(os.path.join(path, "model.safetensors"), out)
+
+
+@pytest.mark.timeout(400)
+@pytest.mark.parametrize("layout", ["tp2", "dp2_tp2_ep"])
+def test_deepseek_parallel_layouts_match_single_process(tmp_path, layout):
+    """Latent attention, grouped routing with a bias and shared experts, sharded over two
+    tensor-parallel ranks, and over two replicas of two tensor-parallel ranks with expert
+    parallelism across all four: the tokens of the unsharded engine."""
+    sp = SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True)
+    g = torch.Generator().manual_seed(6)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (9, 30, 4, 21)]
+    _deepseek_checkpoint(str(tmp_path), preset("tiny-deepseek", dtype="float32"))
+
+    def cfg(par, dp_attention=False):
+        mc = preset("tiny-deepseek", dtype="float32")
+        if dp_attention:
+            mc.extra["dp_attention"] = True
+        c = EngineConfig(model=mc, cache=CacheConfig(block_size=16, num_gpu_blocks=64),
+                         scheduler=SchedulerConfig(max_num_seqs=8, max_num_batched_tokens=64,
+                                                   max_model_len=128),
+                         parallel=par, device="cpu", seed=0)
+        c.load_format, c.model_path = "safetensors", str(tmp_path)
+        return c
+
+    eng = LLMEngine(cfg(ParallelConfig()))
+    for i_, p_ in enumerate(prompts):
+        eng.add_request(p_, sp, request_id=str(i_))
+    want = {}
+    while eng.has_unfinished():
+        for o in eng.step():
+            if o.finished:
+                want[int(o.request_id)] = o.outputs[0].token_ids
+    par = ParallelConfig(tensor_parallel_size=2, comm_backend="nccl") if layout == "tp2" else \
+        ParallelConfig(data_parallel_size=2, tensor_parallel_size=2,
+                       enable_expert_parallel=True, comm_backend="nccl")
+    ex = MultiprocExecutor(cfg(par, dp_attention=layout != "tp2"))
+    try:
+        got = ex.generate(prompts, sp, timeout_s=300)
+    finally:
+        ex.shutdown()
+    assert [o.outputs[0].token_ids for o in got] == [want[i_] for i_ in range(len(prompts))]
