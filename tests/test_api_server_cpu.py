@@ -118,3 +118,80 @@ def test_pooling_endpoints_embed_score_rerank():
         async with httpx.AsyncClient(transport=httpx.ASGITransport(app=app2), base_url="http://t") as c:
             assert (await c.post("/score", json={"query": "a", "documents": ["b"]})).status_code == 400
     asyncio.run(run2())
+
+
+@pytest.mark.timeout(180)
+def test_lora_adapters_are_loaded_and_selected_by_model_name(tmp_path):
+    """``/v1/load_lora_adapter`` reads a PEFT-layout directory; a request whose ``model`` is
+    the adapter's name runs with it (same tokens as the offline engine with that adapter),
+    other requests run the base model; unloading makes the name unknown again."""
+    httpx = pytest.importorskip("httpx")
+    import sys
+    import os
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from test_lora_cpu import _adapter
+    from vllm_gcu_b200.engine.llm import LLM
+    from vllm_gcu_b200.engine.request import SamplingParams
+    from vllm_gcu_b200.lora import LoRARequest
+    from vllm_gcu_b200.utils.weights import write_safetensors
+    cfg = EngineConfig(model=preset("tiny-llama"), cache=CacheConfig(num_gpu_blocks=64),
+                       scheduler=SchedulerConfig(max_num_seqs=8, max_num_batched_tokens=64,
+                                                 max_model_len=128), device="cpu")
+    cfg.additional_config["lora"] = {"max_loras": 2, "max_lora_rank": 8}
+    tensors, conf = _adapter(cfg.model, 1)
+    tensors = {k: v * 6.0 for k, v in tensors.items()}
+    adir = tmp_path / "adapter"
+    adir.mkdir()
+    (adir / "adapter_config.json").write_text(json.dumps(conf))
+    write_safetensors(str(adir / "adapter_model.safetensors"), tensors)
+    prompt = list(range(100, 120))
+    off = LLM("tiny-llama", device="cpu", max_num_seqs=4, max_num_batched_tokens=64,
+              max_model_len=128, num_gpu_blocks=32, enable_lora=True, max_loras=2,
+              max_lora_rank=8)
+    off.engine.add_lora(LoRARequest("a", 1, str(adir)))
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    rid = off.engine.add_request(prompt, sp, lora_id=1)
+    rid0 = off.engine.add_request(prompt, sp)
+    want = {}
+    while off.engine.has_unfinished():
+        for o in off.engine.step():
+            if o.finished:
+                want[o.request_id] = o.outputs[0].token_ids
+    assert want[rid] != want[rid0]
+    eng = AsyncLLM(cfg)
+    app = build_app(eng, ByteTokenizer(32000), "tiny-llama")
+
+    async def run():
+        transport = httpx.ASGITransport(app=app)
+        async with httpx.AsyncClient(transport=transport, base_url="http://t") as c:
+            body = {"prompt": prompt, "max_tokens": 6, "temperature": 0.0, "ignore_eos": True}
+            r = await c.post("/v1/load_lora_adapter", json={"lora_name": "sql"})
+            assert r.status_code == 400
+            r = await c.post("/v1/load_lora_adapter",
+                             json={"lora_name": "bad", "lora_path": str(tmp_path / "none")})
+            assert r.status_code == 400
+            r = await c.post("/v1/load_lora_adapter",
+                             json={"lora_name": "sql", "lora_path": str(adir)})
+            assert r.status_code == 200 and r.json()["lora_int_id"] == 1
+            ms = (await c.get("/v1/models")).json()["data"]
+            assert [m["id"] for m in ms] == ["tiny-llama", "sql"]
+            with_a = (await c.post("/v1/completions", json={**body, "model": "sql"})).json()
+            base = (await c.post("/v1/completions", json={**body, "model": "tiny-llama"})).json()
+            assert with_a["choices"][0]["token_ids"] == want[rid]
+            assert base["choices"][0]["token_ids"] == want[rid0]
+            chat = {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 4,
+                    "temperature": 0.0, "ignore_eos": True}
+            ca = (await c.post("/v1/chat/completions", json={**chat, "model": "sql"})).json()
+            cb = (await c.post("/v1/chat/completions", json=chat)).json()
+            assert ca["model"] == "sql" and ca["choices"][0]["message"]["content"] != \
+                cb["choices"][0]["message"]["content"]
+            r = await c.post("/v1/unload_lora_adapter", json={"lora_name": "sql"})
+            assert r.status_code == 200
+            again = (await c.post("/v1/completions", json={**body, "model": "sql"})).json()
+            assert again["choices"][0]["token_ids"] == want[rid0]
+            assert (await c.post("/v1/unload_lora_adapter",
+                                 json={"lora_name": "sql"})).status_code == 404
+    try:
+        asyncio.run(run())
+    finally:
+        eng.shutdown()

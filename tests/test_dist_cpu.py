@@ -17,7 +17,11 @@ def _worker(rank, world, port, fn_name):
     os.environ.update({"RANK": str(rank), "WORLD_SIZE": str(world), "LOCAL_RANK": str(rank),
                        "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port)})
     from vllm_gcu_b200.parallel.state import init_distributed
-    init_distributed(tp=world, backend="gloo", enable_ep=True)
+    if fn_name == "_check_ep":
+        # data-parallel attention: every rank is a replica of its own with its own tokens
+        init_distributed(tp=1, dp=world, backend="gloo", enable_ep=True)
+    else:
+        init_distributed(tp=world, backend="gloo", enable_ep=True)
     globals()[fn_name](rank, world)
     dist.barrier()
     dist.destroy_process_group()

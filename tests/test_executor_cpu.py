@@ -319,3 +319,75 @@ def test_deepseek_parallel_layouts_match_single_process(tmp_path, layout):
     finally:
         ex.shutdown()
     assert [o.outputs[0].token_ids for o in got] == [want[i_] for i_ in range(len(prompts))]
+
+
+@pytest.mark.timeout(400)
+def test_tp2_multi_lora_matches_single_process(tmp_path):
+    """LoRA adapters under tensor parallelism: the executor hands the full adapter tensors to
+    every worker, each keeps its shard (B rows of column-parallel layers, A columns of
+    row-parallel ones, KV slices by KV-head owner); a batch mixing two adapters and none gives
+    the tokens of the unsharded engine with the same adapters."""
+    tr = pytest.importorskip("transformers")
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from test_lora_cpu import _adapter
+    from vllm_gcu_b200.config import ModelConfig
+    from vllm_gcu_b200.lora import LoRARequest
+    from vllm_gcu_b200.utils.weights import write_safetensors
+    hc = tr.LlamaConfig(vocab_size=512, hidden_size=64, intermediate_size=128,
+                        num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                        max_position_embeddings=128, rms_norm_eps=1e-6,
+                        tie_word_embeddings=False)
+    torch.manual_seed(0)
+    hf = tr.LlamaForCausalLM(hc).eval().float()
+    write_safetensors(os.path.join(str(tmp_path), "model.safetensors"),
+                      {k: v.clone() for k, v in hf.state_dict().items()})
+    d = hc.to_dict()
+    d["architectures"] = ["LlamaForCausalLM"]
+
+    def cfg(tp):
+        c = _cfg(tp)
+        c.model = ModelConfig.from_hf_dict(d, dtype=torch.float32)
+        c.load_format, c.model_path = "safetensors", str(tmp_path)
+        c.additional_config["lora"] = {"max_loras": 2, "max_lora_rank": 8}
+        return c
+
+    mc = cfg(1).model
+    a1, c1 = _adapter(mc, 1)
+    a2, c2 = _adapter(mc, 2, r=8)
+    for t in (a1, a2):                      # large enough to change the greedy tokens
+        for k in t:
+            t[k] = t[k] * 4.0
+    g = torch.Generator().manual_seed(7)
+    prompts = [torch.randint(0, 512, (20,), generator=g).tolist() for _ in range(3)]
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    eng = LLMEngine(cfg(1))
+    eng.add_lora(LoRARequest("a1", 1, ""), a1, c1)
+    eng.add_lora(LoRARequest("a2", 2, ""), a2, c2)
+    ids = [eng.add_request(p, sp, lora_id=l) for p, l in zip(prompts, (1, -1, 2))]
+    want = {}
+    while eng.has_unfinished():
+        for o in eng.step():
+            if o.finished:
+                want[o.request_id] = o.outputs[0].token_ids
+    plain = [eng.add_request(p, sp) for p in prompts]
+    while eng.has_unfinished():
+        for o in eng.step():
+            if o.finished:
+                want[o.request_id] = o.outputs[0].token_ids
+    assert want[ids[0]] != want[plain[0]] and want[ids[2]] != want[plain[2]]
+    ex = MultiprocExecutor(cfg(2))
+    try:
+        ex.add_lora(LoRARequest("a1", 1, ""), a1, c1)
+        ex.add_lora(LoRARequest("a2", 2, ""), a2, c2)
+        rids = [ex.add_request(p, sp, lora_id=l) for p, l in zip(prompts, (1, -1, 2))]
+        got = {}
+        for _ in range(600):
+            for o in ex.poll(0.1):
+                if o.finished:
+                    got[o.request_id] = o.outputs[0].token_ids
+            if len(got) == 3:
+                break
+    finally:
+        ex.shutdown()
+    assert [got[r] for r in rids] == [want[i] for i in ids]

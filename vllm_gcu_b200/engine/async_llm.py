@@ -58,6 +58,14 @@ class AsyncLLM:
             if kind == "abort":
                 self.engine.abort_request(arg)
                 continue
+            if kind == "lora":
+                req, tensors, config, done = arg
+                try:
+                    self.engine.add_lora(req, tensors, config)
+                    done.set_result(None) if not done.done() else None
+                except Exception as e:  # noqa: BLE001  (reported to the caller of add_lora)
+                    done.set_exception(e) if not done.done() else None
+                continue
             try:
                 self.engine.add_request(**arg)
             except Exception as e:  # noqa: BLE001  (reported to the one caller, not fatal)
@@ -109,6 +117,15 @@ class AsyncLLM:
             raise
         finally:
             self._streams.pop(rid, None)
+
+    def add_lora(self, lora_request, tensors=None, config=None, timeout: float = 600.0) -> None:
+        """Loads a LoRA adapter between two engine steps (the engine thread applies it);
+        blocks until it is in place and re-raises a loading error."""
+        import concurrent.futures
+        done: concurrent.futures.Future = concurrent.futures.Future()
+        self._inbox.put(("lora", (lora_request, tensors, config, done)))
+        self._wake.set()
+        done.result(timeout)
 
     def stats(self) -> dict:
         # read-only snapshot of counters: taken without the step lock so that a metrics

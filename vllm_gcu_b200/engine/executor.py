@@ -57,7 +57,7 @@ def _free_port() -> int:
 
 @dataclass
 class _Cmd:
-    kind: str                       # add | abort | stop | inject
+    kind: str                       # add | abort | lora | stop | inject
     payload: Any = None
 
 
@@ -139,6 +139,8 @@ def _worker_main(rank: int, world: int, port: int, cfg: EngineConfig, cmd_q, out
                     engine.add_request(prompt, sp, request_id=rid, priority=prio, lora_id=lora)
                 elif c.kind == "abort":
                     engine.abort_request(c.payload)
+                elif c.kind == "lora":
+                    engine.add_lora(*c.payload)
                 elif c.kind == "stop":
                     stop = True
                 elif c.kind == "inject":
@@ -299,6 +301,13 @@ class MultiprocExecutor:
     def abort_request(self, request_id: str) -> None:
         self._broadcast(_Cmd("abort", request_id))
 
+    def add_lora(self, lora_request, tensors=None, config=None) -> None:
+        """Loads a LoRA adapter in every worker (each keeps its tensor-parallel shard of the
+        full adapter tensors); later requests select it with ``lora_id``.  The command takes its
+        place in the same ordered stream as the requests, so a request added afterwards finds
+        the adapter loaded on every rank."""
+        self._broadcast(_Cmd("lora", (lora_request, tensors, config)))
+
     def inject_fault(self, what: str, rank: int) -> None:
         """Test hook: make worker ``rank`` raise an exception or exit at its next step."""
         self._broadcast(_Cmd("inject", (what, rank)))
@@ -412,15 +421,15 @@ class AsyncMultiprocExecutor(MultiprocExecutor):
 
     async def generate_stream(self, prompt_token_ids: Sequence[int],
                               sampling_params: Optional[SamplingParams] = None,
-                              request_id: Optional[str] = None, priority: int = 0
-                              ) -> AsyncIterator[RequestOutput]:
+                              request_id: Optional[str] = None, priority: int = 0,
+                              lora_id: int = -1) -> AsyncIterator[RequestOutput]:
         self.validate_prompt(prompt_token_ids)
         self._ensure_pump()
         q: asyncio.Queue = asyncio.Queue()
         rid = request_id or f"areq-{self._ids}"
         self._ids += 1
         self._streams[rid] = q
-        self.add_request(prompt_token_ids, sampling_params, rid, priority)
+        self.add_request(prompt_token_ids, sampling_params, rid, priority, lora_id)
         try:
             while True:
                 item = await q.get()

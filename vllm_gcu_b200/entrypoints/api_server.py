@@ -97,7 +97,8 @@ def _guided_schema(body: dict):
     return None
 
 
-def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None):
+def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None,
+              lora_modules: Optional[dict] = None):
     if FastAPI is None:
         raise RuntimeError("the API server needs the fastapi package")
     app = FastAPI()
@@ -115,9 +116,62 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None):
             return JSONResponse({"status": "dead", "detail": str(err)}, status_code=503)
         return {"status": "ok"}
 
+    # LoRA adapters by name: a request selects one through its "model" field (the way the
+    # reference's multi-LoRA serving example addresses adapters, benchmarks/multilora_inference.py)
+    adapters: dict[str, int] = {}
+    state["next_lora_id"] = 1
+    for name_, path_ in (lora_modules or {}).items():
+        from ..lora import LoRARequest
+        engine.add_lora(LoRARequest(name_, state["next_lora_id"], path_))
+        adapters[name_] = state["next_lora_id"]
+        state["next_lora_id"] += 1
+
+    def lora_of(body: dict) -> int:
+        name = body.get("model")
+        if name in adapters:
+            return adapters[name]
+        return -1
+
+    def gen_kwargs(body: dict) -> dict:
+        lid = lora_of(body)
+        return {"lora_id": lid} if lid >= 0 else {}
+
     @app.get("/v1/models")
     async def models():
-        return {"object": "list", "data": [{"id": model_name, "object": "model"}]}
+        data = [{"id": model_name, "object": "model"}]
+        data += [{"id": n, "object": "model", "parent": model_name} for n in adapters]
+        return {"object": "list", "data": data}
+
+    @app.post("/v1/load_lora_adapter")
+    async def load_lora_adapter(request: Request):
+        body = await request.json()
+        name, path = body.get("lora_name"), body.get("lora_path")
+        if not name or not path:
+            return JSONResponse({"error": "lora_name and lora_path are required"}, status_code=400)
+        if name in adapters:
+            return JSONResponse({"error": f"adapter {name!r} is already loaded"}, status_code=400)
+        if not hasattr(engine, "add_lora"):
+            return JSONResponse({"error": "this engine cannot load adapters"}, status_code=400)
+        from ..lora import LoRARequest
+        lid = state["next_lora_id"]
+        try:
+            await asyncio.get_running_loop().run_in_executor(
+                None, engine.add_lora, LoRARequest(name, lid, path))
+        except Exception as e:  # noqa: BLE001  (bad path, rank too large, LoRA not enabled)
+            return JSONResponse({"error": f"loading {name!r} failed: {e}"}, status_code=400)
+        state["next_lora_id"] = lid + 1
+        adapters[name] = lid
+        return {"status": "ok", "lora_name": name, "lora_int_id": lid}
+
+    @app.post("/v1/unload_lora_adapter")
+    async def unload_lora_adapter(request: Request):
+        body = await request.json()
+        name = body.get("lora_name")
+        if name not in adapters:
+            return JSONResponse({"error": f"adapter {name!r} is not loaded"}, status_code=404)
+        # the slot is reused by least-recently-used eviction; the name stops resolving now
+        del adapters[name]
+        return {"status": "ok", "lora_name": name}
 
     def _ensure_vocabulary() -> None:
         """Guided requests need the text of every token; built on first use."""
@@ -190,9 +244,9 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None):
         priority = int(body.get("priority", 0))
         # disaggregated prefill: the proxy names the request and the peer instance
         kvp = body.get("kv_transfer_params")
-        gen_kw = {}
+        gen_kw = gen_kwargs(body)
         if kvp:
-            gen_kw = {"kv_transfer_params": kvp}
+            gen_kw["kv_transfer_params"] = kvp
             if body.get("request_id") and len(batch) == 1:
                 gen_kw["request_id"] = str(body["request_id"])
 
@@ -271,7 +325,8 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None):
         created = int(time.time())
         state["requests"] += 1
         priority = int(body.get("priority", 0))
-        base = {"id": rid, "created": created, "model": model_name}
+        base = {"id": rid, "created": created, "model": body.get("model") or model_name}
+        lora_kw = gen_kwargs(body)
 
         if body.get("stream", False):
             async def sse():
@@ -280,7 +335,7 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None):
                          "finish_reason": None}
                 yield "data: " + json.dumps({**base, "object": "chat.completion.chunk",
                                              "choices": [first]}) + "\n\n"
-                async for out in engine.generate_stream(ids, sp, priority=priority):
+                async for out in engine.generate_stream(ids, sp, priority=priority, **lora_kw):
                     toks = out.outputs[0].token_ids
                     new, sent = toks[sent:], len(toks)
                     state["tokens_out"] += len(new)
@@ -292,7 +347,7 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None):
             return StreamingResponse(sse(), media_type="text/event-stream")
 
         last = None
-        async for out in engine.generate_stream(ids, sp, priority=priority):
+        async for out in engine.generate_stream(ids, sp, priority=priority, **lora_kw):
             last = out
         toks = last.outputs[0].token_ids
         state["tokens_out"] += len(toks)
@@ -418,6 +473,9 @@ def make_engine(args) -> tuple[Any, ModelConfig]:
                                   async_scheduling=not args.no_async_scheduling),
         parallel=ParallelConfig(tensor_parallel_size=args.tensor_parallel_size),
         device=args.device, enforce_eager=args.enforce_eager, load_format=fmt, model_path=path)
+    if getattr(args, "enable_lora", False):
+        cfg.additional_config["lora"] = {"max_loras": args.max_loras,
+                                         "max_lora_rank": args.max_lora_rank}
     if args.tensor_parallel_size > 1:
         from ..engine.executor import AsyncMultiprocExecutor
         return AsyncMultiprocExecutor(cfg), mc
@@ -454,6 +512,11 @@ def main() -> None:
     ap.add_argument("--kv-port", type=int, default=0,
                     help="port of the point-to-point KV connector (disaggregated prefill)")
     ap.add_argument("--kv-send-type", default="PUT_ASYNC", choices=["PUT", "PUT_ASYNC", "GET"])
+    ap.add_argument("--enable-lora", action="store_true")
+    ap.add_argument("--max-loras", type=int, default=4)
+    ap.add_argument("--max-lora-rank", type=int, default=16)
+    ap.add_argument("--lora-modules", nargs="*", default=[], metavar="NAME=PATH",
+                    help="adapters loaded at start-up; requests select one by model name")
     args = ap.parse_args()
     import os
     cfg_path = os.path.join(args.model, "config.json") if os.path.isdir(args.model) else None
@@ -477,8 +540,9 @@ def main() -> None:
     tok = load_tokenizer(args.tokenizer or (args.model if "/" in args.model else None),
                          mc.vocab_size)
     import uvicorn
-    uvicorn.run(build_app(engine, tok, args.model), host=args.host, port=args.port,
-                log_level="warning")
+    app = build_app(engine, tok, args.model, lora_modules=dict(
+        m.split("=", 1) for m in args.lora_modules))
+    uvicorn.run(app, host=args.host, port=args.port, log_level="warning")
 
 
 if __name__ == "__main__":
