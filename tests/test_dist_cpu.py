@@ -12,6 +12,16 @@ import torch.multiprocessing as mp
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
+def _leave():
+    """End of a worker with several process groups: after the last barrier the process exits
+    without tearing the groups down (their background threads have aborted the interpreter's
+    own shutdown now and then); everything a peer still needs has been sent by then."""
+    import time
+    dist.barrier()
+    time.sleep(0.2)
+    os._exit(0)
+
+
 def _worker(rank, world, port, fn_name):
     sys.path.insert(0, ROOT)
     os.environ.update({"RANK": str(rank), "WORLD_SIZE": str(world), "LOCAL_RANK": str(rank),
@@ -233,8 +243,7 @@ def _worker_etp(rank, world, port, tp):
     from vllm_gcu_b200.parallel.state import init_distributed
     init_distributed(tp=tp, dp=world // tp, backend="gloo", enable_ep=False)
     _check_etp(rank, world)
-    dist.barrier()
-    dist.destroy_process_group()
+    _leave()
 
 
 @pytest.mark.timeout(300)
@@ -318,8 +327,7 @@ def _worker_ep_tp(rank, world, port, tp, shared):
     from vllm_gcu_b200.parallel.state import init_distributed
     init_distributed(tp=tp, dp=world // tp, backend="gloo", enable_ep=True)
     _check_ep_tp(rank, world, shared)
-    dist.barrier()
-    dist.destroy_process_group()
+    _leave()
 
 
 @pytest.mark.timeout(300)
