@@ -78,6 +78,9 @@ environment_variables: dict[str, Callable[[], Any]] = {
     # expert parallelism with tensor-parallel attention inside a replica: every tensor-parallel
     # rank dispatches its own slice of the replica's rows (0: every rank dispatches all rows)
     "EP_TP_SLICE": _flag("EP_TP_SLICE", "1"),
+    # expert-parallel dispatch of block-scaled fp8 models sends rows as fp8 with their group
+    # scales (half the bytes of bf16 rows) and de-quantises them on arrival
+    "EP_FP8_DISPATCH": _flag("EP_FP8_DISPATCH", "0"),
     "NIXL_ENABLE_FULL_KV_TRANSFER": _flag("NIXL_ENABLE_FULL_KV_TRANSFER", "1"),
     # ... and starts at the first output token the prefill instance already produced
     "NIXL_ENABLE_FIRST_TOKEN_REUSE": _flag("NIXL_ENABLE_FIRST_TOKEN_REUSE"),

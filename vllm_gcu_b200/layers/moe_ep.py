@@ -33,6 +33,41 @@ from ..parallel.communicator import get_comm
 from ..parallel.state import get_state
 
 
+def packed_width(hidden: int) -> int:
+    """Width, in 16-bit elements, of a row that carries ``hidden`` fp8 values and one fp32
+    scale per 128 of them."""
+    return hidden // 2 + hidden // 64
+
+
+def pack_fp8_rows(x: torch.Tensor) -> torch.Tensor:
+    """``x [T, H]`` -> ``[T, H/2 + H/64]`` 16-bit words: the row quantised to fp8 e4m3 in groups
+    of 128 with one fp32 scale per group, scales behind the values in the same row, so that the
+    row moves through the dispatch as one piece (the reference sends quantised rows with their
+    scales packed alongside, vllm_gcu/kernels/prepare_finalize.py:281-304,343).  About half the
+    bytes of the bf16 row."""
+    T, H = x.shape
+    assert H % 128 == 0
+    if ops.use_native(x) and x.dtype == torch.bfloat16:
+        q, s = C.activation(x, "identity", "plain", quant="fp8_group128")
+    else:
+        q, s = ref.per_token_group_fp8_quant(x, 128)
+    out = torch.empty((T, packed_width(H)), dtype=torch.int16, device=x.device)
+    out[:, :H // 2] = q.contiguous().view(torch.int16).view(T, H // 2)
+    out[:, H // 2:] = s.float().contiguous().view(torch.int16).view(T, H // 64)
+    return out
+
+
+def unpack_fp8_rows(packed: torch.Tensor, hidden: int, dtype: torch.dtype) -> torch.Tensor:
+    """Inverse of :func:`pack_fp8_rows`: the de-quantised ``[T, hidden]`` rows.  Quantising
+    them again in groups of 128 reproduces the same codes and scales, so experts that quantise
+    their input see exactly what they would have seen without the detour."""
+    T = packed.shape[0]
+    packed = packed.contiguous()
+    q = packed[:, :hidden // 2].contiguous().view(torch.float8_e4m3fn).view(T, hidden // 128, 128)
+    s = packed[:, hidden // 2:].contiguous().view(torch.float32).view(T, hidden // 128, 1)
+    return (q.float() * s).view(T, hidden).to(dtype)
+
+
 def ep_route(topk_ids: torch.Tensor, experts_per_rank: int, ep: int):
     """(send counts list[int], token indices rank-major int64 tensor)."""
     if topk_ids.shape[0] == 0:
@@ -45,6 +80,17 @@ def ep_route(topk_ids: torch.Tensor, experts_per_rank: int, ep: int):
     return cnt.tolist(), idx.long()
 
 
+def fp8_payload_wanted(experts, cfg) -> bool:
+    """Rows travel as fp8 when the experts quantise their input to fp8 in groups of 128 anyway
+    (block-scaled fp8 checkpoints) and ``VLLM_B200_EP_FP8_DISPATCH`` asks for it;
+    ``extra["ep_fp8_dispatch"]`` overrides the flag for one model."""
+    from .. import envs
+    want = cfg.extra.get("ep_fp8_dispatch")
+    if want is None:
+        want = envs.EP_FP8_DISPATCH and bool(getattr(experts, "fp8_block", False))
+    return bool(want) and cfg.hidden_size % 128 == 0
+
+
 class AllToAllDispatcher:
     def __init__(self, experts, cfg):
         self.experts = experts
@@ -53,6 +99,8 @@ class AllToAllDispatcher:
         self.ep = st.ep.world_size
         self.rank = st.ep.rank_in_group
         self.epr = experts.local_experts
+        self.fp8_payload = fp8_payload_wanted(experts, cfg)
+        self.bytes_sent = 0                    # hidden-state bytes handed to the exchange
 
     def __call__(self, x: torch.Tensor, topk_w: torch.Tensor, topk_ids: torch.Tensor,
                  shared: Optional[torch.Tensor],
@@ -76,7 +124,12 @@ class AllToAllDispatcher:
         xs = x[tok_idx]
         ids_s = topk_ids[tok_idx]
         w_s = topk_w[tok_idx]
+        if self.fp8_payload:
+            xs = pack_fp8_rows(xs)
+        self.bytes_sent += xs.numel() * xs.element_size()
         xr = comm.all_to_all_v(xs, send_counts, recv_counts)
+        if self.fp8_payload:
+            xr = unpack_fp8_rows(xr, H, x.dtype)
         ids_r = comm.all_to_all_v(ids_s, send_counts, recv_counts)
         w_r = comm.all_to_all_v(w_s, send_counts, recv_counts)
         # local experts: one output row per received row
@@ -174,7 +227,9 @@ class EPWorkspace:
         buffers (``ep * max_tokens_per_rank`` rows) and the device scalar of valid rows."""
         from ..ops._native import call, ptr, stream_ptr
         T, H = x.shape
-        assert T <= self.max_tokens and H == self.H and x.dtype == torch.bfloat16
+        # rows narrower than the workspace's hidden size (packed fp8 payloads) use the front of
+        # the receive area with their own pitch
+        assert T <= self.max_tokens and H <= self.H and H % 8 == 0 and x.dtype == torch.bfloat16
         assert topk_ids.dtype == torch.int32 and topk_w.dtype == torch.float32
         if T and x.stride(1) != 1:
             x = x.contiguous()
@@ -189,7 +244,9 @@ class EPWorkspace:
              self._parr(self.off_recv_ids), self._parr(self.off_recv_w),
              self._parr(self.off_flags), w, w + 4, ptr(self.meta), stream_ptr())
         rows = self.ep * min(self.max_tokens, max_tokens_per_rank or self.max_tokens)
-        return self.recv_x[:rows], self.recv_w[:rows], self.recv_ids[:rows], self.recv_total
+        recv_x = self.recv_x[:rows] if H == self.H else \
+            self.recv_x.view(-1)[:rows * H].view(rows, H)
+        return recv_x, self.recv_w[:rows], self.recv_ids[:rows], self.recv_total
 
     def combine(self, y: torch.Tensor, T: int, add: Optional[torch.Tensor], alpha: float = 1.0
                 ) -> torch.Tensor:
@@ -213,13 +270,25 @@ class FusedEPDispatcher:
         self.experts = experts
         self.ws = EPWorkspace.get(cfg.hidden_size, cfg.num_experts_per_tok,
                                   experts.local_experts, max_tokens, device)
+        self.fp8_payload = fp8_payload_wanted(experts, cfg)
+        self.hidden = cfg.hidden_size
 
     def __call__(self, x: torch.Tensor, topk_w: torch.Tensor, topk_ids: torch.Tensor,
                  shared: Optional[torch.Tensor],
                  max_tokens_per_rank: Optional[int] = None) -> torch.Tensor:
         T = x.shape[0]
-        xr, w_r, ids_r, total = self.ws.dispatch(x, topk_w.float(), topk_ids.to(torch.int32),
-                                                 max_tokens_per_rank)
+        if self.fp8_payload:
+            # quantised rows with their scales ride through the same dispatch kernel as narrower
+            # 16-bit rows; the receive area is reinterpreted and de-quantised on arrival
+            packed = pack_fp8_rows(x).view(torch.bfloat16)
+            pr, w_r, ids_r, total = self.ws.dispatch(packed, topk_w.float(),
+                                                     topk_ids.to(torch.int32),
+                                                     max_tokens_per_rank)
+            xr = unpack_fp8_rows(pr.view(torch.int16), self.hidden, x.dtype)
+        else:
+            xr, w_r, ids_r, total = self.ws.dispatch(x, topk_w.float(),
+                                                     topk_ids.to(torch.int32),
+                                                     max_tokens_per_rank)
         if any(getattr(self.experts, f, False) for f in ("_interleaved", "fp8_block", "q8_channel")):
             yr = self.experts(xr, w_r, ids_r, valid_tokens=total)
         else:           # layout without the grouped-GEMM path: run on the valid rows only
