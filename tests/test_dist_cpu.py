@@ -27,7 +27,7 @@ def _worker(rank, world, port, fn_name):
     os.environ.update({"RANK": str(rank), "WORLD_SIZE": str(world), "LOCAL_RANK": str(rank),
                        "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port)})
     from vllm_gcu_b200.parallel.state import init_distributed
-    if fn_name == "_check_ep":
+    if fn_name in ("_check_ep", "_check_ep_fp8"):
         # data-parallel attention: every rank is a replica of its own with its own tokens
         init_distributed(tp=1, dp=world, backend="gloo", enable_ep=True)
     else:
@@ -338,3 +338,51 @@ def test_expert_parallel_with_tensor_parallel_replicas(shared):
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     mp.spawn(_worker_ep_tp, args=(4, port, 2, shared), nprocs=4, join=True)
+
+
+def _check_ep_fp8(rank, world):
+    """fp8 dispatch payload: rows cross the exchange quantised in groups of 128 with their
+    scales in the same row (about half the bytes); the result is the routed-expert output of
+    the de-quantised rows."""
+    from vllm_gcu_b200.config import preset
+    from vllm_gcu_b200.layers.moe import SparseMoeBlock
+    from vllm_gcu_b200.layers.moe_ep import pack_fp8_rows, packed_width, unpack_fp8_rows
+    from vllm_gcu_b200.ops import ref
+    cfg = preset("tiny-qwen3-moe", num_experts=8, num_experts_per_tok=2)
+    cfg.extra["dp_attention"] = True
+    H = cfg.hidden_size
+    sent = {}
+    for mode in (False, True):
+        cfg.extra["ep_fp8_dispatch"] = mode
+        torch.manual_seed(0)
+        blk = SparseMoeBlock(cfg, "cpu", "m")
+        assert blk.dispatcher.fp8_payload is mode
+        E, I = cfg.num_experts, cfg.moe_intermediate_size
+        g = torch.Generator().manual_seed(1)
+        w13 = torch.randn(E, 2 * I, H, generator=g) * 0.05
+        w2 = torch.randn(E, H, I, generator=g) * 0.05
+        gate = torch.randn(E, H, generator=g) * 0.5
+        blk.gate.weight.data.copy_(gate)
+        for e in range(E):
+            blk.experts.load_expert_weight(e, "gate", w13[e, :I])
+            blk.experts.load_expert_weight(e, "up", w13[e, I:])
+            blk.experts.load_expert_weight(e, "down", w2[e])
+        T = 0 if rank == 1 else 6 + rank
+        x = torch.randn(T, H, generator=torch.Generator().manual_seed(10 + rank))
+        got = blk(x)
+        sent[mode] = blk.dispatcher.bytes_sent
+        if T:
+            w, ids = ref.topk_softmax(x @ gate.t(), 2, True)
+            seen = unpack_fp8_rows(pack_fp8_rows(x), H, x.dtype) if mode else x
+            want = ref.fused_experts(seen, w13, w2, w, ids)
+            assert torch.allclose(got, want, atol=1e-5, rtol=1e-4), (got - want).abs().max()
+            exact = ref.fused_experts(x, w13, w2, w, ids)
+            assert (got - exact).abs().max() < 0.05 * exact.abs().max() + 1e-3
+    if sent[False]:
+        # fp32 rows on this path: H * 4 bytes against H + H / 32 bytes
+        assert sent[True] * 4 * H == sent[False] * 2 * packed_width(H)
+
+
+@pytest.mark.timeout(300)
+def test_expert_parallel_fp8_dispatch_payload():
+    _spawn("_check_ep_fp8", 2)

@@ -125,11 +125,11 @@ class AllToAllDispatcher:
         ids_s = topk_ids[tok_idx]
         w_s = topk_w[tok_idx]
         if self.fp8_payload:
-            xs = pack_fp8_rows(xs)
+            xs = pack_fp8_rows(xs).view(torch.uint8)      # bytes: every backend moves them
         self.bytes_sent += xs.numel() * xs.element_size()
         xr = comm.all_to_all_v(xs, send_counts, recv_counts)
         if self.fp8_payload:
-            xr = unpack_fp8_rows(xr, H, x.dtype)
+            xr = unpack_fp8_rows(xr.view(torch.int16), H, x.dtype)
         ids_r = comm.all_to_all_v(ids_s, send_counts, recv_counts)
         w_r = comm.all_to_all_v(w_s, send_counts, recv_counts)
         # local experts: one output row per received row
