@@ -106,3 +106,34 @@ def test_vllm_model_registry_gets_the_extra_architectures():
     got = [n for n, _ in DeepseekVLV2ForCausalLMB200.hf_to_vllm_mapper.apply(names)]
     assert got == [_OWN, _OWN, "language_model.model.embed_tokens.weight",
                    "vision.blocks.0.attn.qkv.weight"]
+
+
+def test_vllm_worker_step_hooks(monkeypatch):
+    """The vLLM worker subclass wraps every step: the status word is read every n-th step and
+    an error recorded by a kernel surfaces as an exception of the step."""
+    import pytest
+    pytest.importorskip("vllm")
+    try:
+        from vllm_gcu_b200.runtime.vllm_worker import B200Worker
+    except Exception as e:  # noqa: BLE001 - vLLM's GPU worker does not import on this machine
+        pytest.skip(f"vLLM's GPU worker cannot be imported here: {e}")
+    from vllm_gcu_b200.ops import _native
+    w = object.__new__(B200Worker)
+    calls = []
+    checks = []
+    monkeypatch.setattr(_native, "check_status", lambda: checks.append(len(calls)))
+    monkeypatch.setenv("VLLM_B200_CHECK_STATUS_EVERY", "2")
+
+    def inner(a, b=0):
+        calls.append((a, b))
+        return a + b
+    assert [w._step(inner, i, b=1) for i in range(5)] == [1, 2, 3, 4, 5]
+    assert calls == [(i, 1) for i in range(5)] and checks == [2, 4]
+
+    def failing():
+        raise KeyError("boom")
+    with pytest.raises(KeyError):
+        w._step(failing)
+    monkeypatch.setenv("VLLM_B200_CHECK_STATUS_EVERY", "0")
+    w._step(inner, 1)
+    assert checks == [2, 4]

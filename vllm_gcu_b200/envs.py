@@ -81,6 +81,9 @@ environment_variables: dict[str, Callable[[], Any]] = {
     # expert-parallel dispatch of block-scaled fp8 models sends rows as fp8 with their group
     # scales (half the bytes of bf16 rows) and de-quantises them on arrival
     "EP_FP8_DISPATCH": _flag("EP_FP8_DISPATCH", "0"),
+    # under vLLM: the worker reads the native status word (one device-to-host copy) every this
+    # many steps and raises when a kernel reported a wait that ran out (0 = never)
+    "CHECK_STATUS_EVERY": lambda: int(_get("CHECK_STATUS_EVERY", "0")),
     "NIXL_ENABLE_FULL_KV_TRANSFER": _flag("NIXL_ENABLE_FULL_KV_TRANSFER", "1"),
     # ... and starts at the first output token the prefill instance already produced
     "NIXL_ENABLE_FIRST_TOKEN_REUSE": _flag("NIXL_ENABLE_FIRST_TOKEN_REUSE"),
