@@ -8,6 +8,7 @@ sizes and the way one request is built (pixel layout, placeholder count):
 
   qwen2_5_vl   Qwen2.5-VL   windowed vision transformer, M-RoPE; ``--grid h w`` patches
   qwen2_vl     Qwen2-VL / QVQ  full-attention vision transformer, M-RoPE; ``--grid h w``
+  glm4v        GLM-4.1V     interpolated positions, convolution merge, M-RoPE; ``--grid h w``
   llava        LLaVA-1.5    CLIP tower, one ``--image-size`` view
   llava_next   LLaVA-NeXT   CLIP tower, base view + 2 x 2 tiles
   internvl     InternVL2 / 2.5  InternViT, ``--tiles`` tiles of ``--image-size``
@@ -77,6 +78,23 @@ def qwen2_vl(a):
                                temporal_patch_size=2),
          "image_token_id": IMG, "video_token_id": 291, "vision_start_token_id": VSTART,
          "vision_end_token_id": VEND}
+    return d, _qwen_request
+
+
+def glm4v(a):
+    hd = a.hidden // max(a.hidden // 64, 2)
+    quarter = hd // 4                       # rotary pairs on half of the head, split t / h / w
+    sec = [quarter - 2 * (quarter // 3), quarter // 3, quarter // 3]
+    d = {"architectures": ["Glm4vForConditionalGeneration"],
+         "text_config": _text(a, attention_bias=True, rope_parameters={
+             "rope_type": "default", "rope_theta": 10000.0, "mrope_section": sec,
+             "partial_rotary_factor": 0.5}),
+         "vision_config": dict(depth=a.vision_layers, hidden_size=a.vision_hidden,
+                               intermediate_size=a.vision_hidden * 2, num_heads=_vheads(a),
+                               in_channels=3, image_size=a.image_size, patch_size=14,
+                               spatial_merge_size=2, temporal_patch_size=2,
+                               out_hidden_size=a.hidden),
+         "image_token_id": IMG, "image_start_token_id": VSTART, "image_end_token_id": VEND}
     return d, _qwen_request
 
 
@@ -165,7 +183,7 @@ def deepseek_vl2(a):
     return d, request
 
 
-FAMILIES = {f.__name__: f for f in (qwen2_5_vl, qwen2_vl, llava, llava_next, internvl,
+FAMILIES = {f.__name__: f for f in (qwen2_5_vl, qwen2_vl, glm4v, llava, llava_next, internvl,
                                     deepseek_vl2)}
 
 

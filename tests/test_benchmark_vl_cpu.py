@@ -17,7 +17,7 @@ def _load():
 
 @pytest.mark.timeout(300)
 @pytest.mark.parametrize("family,image_tokens", [
-    ("qwen2_5_vl", 6), ("qwen2_vl", 6), ("llava", 16), ("llava_next", 88), ("internvl", 12),
+    ("qwen2_5_vl", 6), ("qwen2_vl", 6), ("glm4v", 6), ("llava", 16), ("llava_next", 88), ("internvl", 12),
     ("deepseek_vl2", 17)])
 def test_every_family_runs(family, image_tokens):
     res = _load().main(["--family", family, "--device", "cpu", "--layers", "2", "--hidden", "128",

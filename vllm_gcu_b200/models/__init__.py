@@ -38,6 +38,8 @@ _REGISTRY: dict[str, str] = {
     "LlavaForConditionalGeneration": "vllm_gcu_b200.models.llava:LlavaForConditionalGeneration",
     "LlavaNextForConditionalGeneration":
         "vllm_gcu_b200.models.llava:LlavaNextForConditionalGeneration",
+    "Glm4vForConditionalGeneration":
+        "vllm_gcu_b200.models.glm4v:Glm4vForConditionalGeneration",
     "InternVLChatModel": "vllm_gcu_b200.models.internvl:InternVLChatModel",
     "InternVLForConditionalGeneration": "vllm_gcu_b200.models.internvl:InternVLChatModel",
     "GotOcr2ForConditionalGeneration":
