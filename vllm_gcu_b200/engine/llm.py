@@ -269,7 +269,6 @@ class LLMEngine:
     def _finish(self, so: SchedulerOutput, handle: StepHandle) -> list[RequestOutput]:
         toks = handle.token_ids()
         draft = handle.draft_tokens()
-        so_req = {s.req.request_id: s.req for s in so.scheduled}
         if self.spec_metrics is not None:
             for rid, nd in zip(handle.req_ids, handle.extra.get("num_draft", [])):
                 if nd:
@@ -307,6 +306,7 @@ class LLMEngine:
         outs = self.scheduler.update_from_output(so, toks, draft, lp)
         hid = handle.extra.get("hidden")
         if hid is not None:
+            so_req = {s.req.request_id: s.req for s in so.scheduled}
             rows = {rid: i for i, rid in enumerate(handle.req_ids)}
             hid = hid.cpu()
             for o in outs:
