@@ -3,6 +3,7 @@ import asyncio
 import json
 
 import pytest
+import torch
 
 from vllm_gcu_b200.config import CacheConfig, EngineConfig, SchedulerConfig, preset
 from vllm_gcu_b200.engine.async_llm import AsyncLLM
@@ -191,6 +192,68 @@ def test_lora_adapters_are_loaded_and_selected_by_model_name(tmp_path):
             assert again["choices"][0]["token_ids"] == want[rid0]
             assert (await c.post("/v1/unload_lora_adapter",
                                  json={"lora_name": "sql"})).status_code == 404
+    try:
+        asyncio.run(run())
+    finally:
+        eng.shutdown()
+
+
+def _server_args(*argv):
+    import argparse
+    from vllm_gcu_b200.entrypoints.api_server import add_engine_arguments
+    ap = argparse.ArgumentParser()
+    add_engine_arguments(ap)
+    return ap.parse_args(list(argv))
+
+
+def test_server_command_line_reaches_the_engine_configuration():
+    from vllm_gcu_b200.entrypoints.api_server import engine_config
+    a = _server_args("--model", "tiny-qwen3-moe", "--device", "cpu", "-dp", "2", "-tp", "2",
+                     "--enable-expert-parallel", "--num-scheduler-steps", "4",
+                     "--scheduling-policy", "priority", "--num-cpu-blocks", "8",
+                     "--no-enable-prefix-caching", "--kv-cache-dtype", "int8",
+                     "--speculative-method", "ngram", "--num-speculative-tokens", "3",
+                     "--additional-config", '{"cascade_min_tokens": 64}', "--seed", "5",
+                     "--enable-lora", "--max-loras", "2", "--dtype", "float32",
+                     "--comm-backend", "nccl")
+    c = engine_config(a)
+    assert c.parallel.world_size == 4 and c.parallel.enable_expert_parallel
+    assert c.parallel.comm_backend == "nccl" and c.model.extra["dp_attention"] is True
+    assert c.scheduler.num_scheduler_steps == 4 and c.scheduler.policy == "priority"
+    assert c.cache.num_cpu_blocks == 8 and not c.cache.enable_prefix_caching
+    assert c.model.kv_cache_dtype == "int8" and c.model.dtype == torch.float32
+    assert c.speculative.method == "ngram" and c.speculative.num_speculative_tokens == 3
+    assert c.additional_config["cascade_min_tokens"] == 64 and c.seed == 5
+    assert c.additional_config["lora"] == {"max_loras": 2, "max_lora_rank": 16}
+    q = engine_config(_server_args("--model", "tiny-llama", "--device", "cpu",
+                                   "--quantization", "fp8_block"))
+    assert q.model.quantization == "fp8" and q.model.quant_config["weight_block_size"] == [128, 128]
+
+
+@pytest.mark.timeout(300)
+def test_server_on_a_data_parallel_expert_parallel_engine():
+    """``-dp 2 --enable-expert-parallel`` starts one worker process per replica behind the same
+    HTTP front end; concurrent requests are spread over the replicas and all finish."""
+    httpx = pytest.importorskip("httpx")
+    from vllm_gcu_b200.entrypoints.api_server import make_engine
+    a = _server_args("--model", "tiny-qwen3-moe", "--device", "cpu", "-dp", "2",
+                     "--enable-expert-parallel", "--comm-backend", "nccl", "--num-gpu-blocks",
+                     "64", "--max-num-seqs", "8", "--max-num-batched-tokens", "64",
+                     "--max-model-len", "128", "--dtype", "float32")
+    a.host, a.kv_port = "127.0.0.1", 0
+    eng, mc = make_engine(a)
+    app = build_app(eng, ByteTokenizer(mc.vocab_size), "tiny-qwen3-moe")
+
+    async def run():
+        transport = httpx.ASGITransport(app=app)
+        async with httpx.AsyncClient(transport=transport, base_url="http://t", timeout=120) as c:
+            body = {"prompt": [[1, 2, 3, 4], [9, 8, 7], [5, 6, 7, 8, 9, 10]], "max_tokens": 5,
+                    "temperature": 0.0, "ignore_eos": True}
+            js = (await c.post("/v1/completions", json=body)).json()
+            assert [len(ch["token_ids"]) for ch in js["choices"]] == [5, 5, 5]
+            one = (await c.post("/v1/completions", json={**body, "prompt": [1, 2, 3, 4]})).json()
+            assert one["choices"][0]["token_ids"] == js["choices"][0]["token_ids"]
+            assert (await c.get("/health")).json()["status"] == "ok"
     try:
         asyncio.run(run())
     finally:

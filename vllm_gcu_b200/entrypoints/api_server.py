@@ -20,6 +20,7 @@ import uuid
 from typing import Any, Optional
 
 from ..config import (CacheConfig, EngineConfig, ModelConfig, ParallelConfig, SchedulerConfig,
+                      SpeculativeConfig,
                       preset)
 from ..engine.request import SamplingParams
 
@@ -450,33 +451,76 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None,
     return app
 
 
-def make_engine(args) -> tuple[Any, ModelConfig]:
+def engine_config(args) -> EngineConfig:
+    """``EngineConfig`` from the server's command line (the options of ``vllm serve`` that the
+    reference's tutorials use: parallel sizes, expert parallelism, scheduler steps and policy,
+    quantisation, KV-cache dtype, swap space, speculative decoding, ``--additional-config``)."""
     import os
-    overrides = {}
+    overrides: dict = {}
     if args.num_hidden_layers:
         overrides["num_hidden_layers"] = args.num_hidden_layers
+    if getattr(args, "kv_cache_dtype", "auto") != "auto":
+        overrides["kv_cache_dtype"] = args.kv_cache_dtype
+    quant = getattr(args, "quantization", None)
+    if quant == "fp8_block":
+        overrides.update(quantization="fp8", quant_config={"quant_method": "fp8",
+                                                           "weight_block_size": [128, 128]})
+    elif quant and not os.path.isdir(args.model):
+        overrides.update(quantization=quant, quant_config={"quant_method": quant})
     if os.path.isdir(args.model):
         mc = ModelConfig.from_pretrained(args.model, **overrides)
         path, fmt = args.model, "safetensors"
     else:
         mc = preset(args.model, **overrides)
         path, fmt = None, "dummy"
-    cfg = EngineConfig(
+    if getattr(args, "dtype", None):
+        from ..config import to_dtype
+        mc.dtype = to_dtype(args.dtype)
+    dp = int(getattr(args, "data_parallel_size", 1))
+    if dp > 1:
+        mc.extra["dp_attention"] = True
+    extra_cfg = json.loads(args.additional_config) if getattr(args, "additional_config", None) \
+        else {}
+    if getattr(args, "enable_lora", False):
+        extra_cfg["lora"] = {"max_loras": args.max_loras, "max_lora_rank": args.max_lora_rank}
+    spec = SpeculativeConfig()
+    if getattr(args, "speculative_method", None):
+        spec = SpeculativeConfig(args.speculative_method, int(args.num_speculative_tokens),
+                                 draft_model=getattr(args, "speculative_model", None))
+    return EngineConfig(
         model=mc,
         cache=CacheConfig(block_size=args.block_size,
                           gpu_memory_utilization=args.gpu_memory_utilization,
-                          num_gpu_blocks=args.num_gpu_blocks),
+                          num_gpu_blocks=args.num_gpu_blocks,
+                          num_cpu_blocks=int(getattr(args, "num_cpu_blocks", 0)),
+                          enable_prefix_caching=not getattr(args, "no_enable_prefix_caching",
+                                                            False)),
         scheduler=SchedulerConfig(max_num_seqs=args.max_num_seqs,
                                   max_num_batched_tokens=args.max_num_batched_tokens,
                                   max_model_len=args.max_model_len or mc.max_position_embeddings,
                                   policy=args.scheduling_policy,
-                                  async_scheduling=not args.no_async_scheduling),
-        parallel=ParallelConfig(tensor_parallel_size=args.tensor_parallel_size),
-        device=args.device, enforce_eager=args.enforce_eager, load_format=fmt, model_path=path)
-    if getattr(args, "enable_lora", False):
-        cfg.additional_config["lora"] = {"max_loras": args.max_loras,
-                                         "max_lora_rank": args.max_lora_rank}
-    if args.tensor_parallel_size > 1:
+                                  async_scheduling=not args.no_async_scheduling,
+                                  num_scheduler_steps=int(getattr(args, "num_scheduler_steps", 1))),
+        parallel=ParallelConfig(tensor_parallel_size=args.tensor_parallel_size,
+                                pipeline_parallel_size=int(getattr(args, "pipeline_parallel_size",
+                                                                   1)),
+                                data_parallel_size=dp,
+                                enable_expert_parallel=bool(getattr(args, "enable_expert_parallel",
+                                                                    False)),
+                                comm_backend=getattr(args, "comm_backend", "fused")),
+        speculative=spec, device=args.device, seed=int(getattr(args, "seed", 0)),
+        enforce_eager=args.enforce_eager, load_format=fmt, model_path=path,
+        additional_config=extra_cfg)
+
+
+def make_engine(args) -> tuple[Any, ModelConfig]:
+    cfg = engine_config(args)
+    mc = cfg.model
+    sc, pc = cfg.scheduler, cfg.parallel
+    if sc.async_scheduling and (sc.num_scheduler_steps > 1 or pc.pipeline_parallel_size > 1
+                                or cfg.speculative.method):
+        sc.async_scheduling = False        # the platform policy's exclusions
+    if pc.world_size > 1:
         from ..engine.executor import AsyncMultiprocExecutor
         return AsyncMultiprocExecutor(cfg), mc
     from ..engine.async_llm import AsyncLLM
@@ -491,30 +535,56 @@ def make_engine(args) -> tuple[Any, ModelConfig]:
     return eng, mc
 
 
-def main() -> None:
-    ap = argparse.ArgumentParser(description=__doc__)
+def add_engine_arguments(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--model", default="llama-3-8b")
     ap.add_argument("--tokenizer", default=None)
-    ap.add_argument("--host", default="127.0.0.1")
-    ap.add_argument("--port", type=int, default=8000)
-    ap.add_argument("--tensor-parallel-size", type=int, default=1)
+    ap.add_argument("--tensor-parallel-size", "-tp", type=int, default=1)
+    ap.add_argument("--pipeline-parallel-size", "-pp", type=int, default=1)
+    ap.add_argument("--data-parallel-size", "-dp", type=int, default=1,
+                    help="replicas with their own attention and KV cache (one process per GPU)")
+    ap.add_argument("--enable-expert-parallel", action="store_true",
+                    help="experts spread over all dp x tp ranks instead of sharded")
+    ap.add_argument("--comm-backend", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--max-num-seqs", type=int, default=256)
     ap.add_argument("--max-num-batched-tokens", type=int, default=8192)
     ap.add_argument("--max-model-len", type=int, default=0)
     ap.add_argument("--block-size", type=int, default=16)
     ap.add_argument("--gpu-memory-utilization", type=float, default=0.9)
     ap.add_argument("--num-gpu-blocks", type=int, default=None)
+    ap.add_argument("--num-cpu-blocks", type=int, default=0,
+                    help="host blocks for swapping pre-empted requests (0: recompute)")
+    ap.add_argument("--no-enable-prefix-caching", action="store_true")
     ap.add_argument("--scheduling-policy", default="fcfs", choices=["fcfs", "priority"])
+    ap.add_argument("--num-scheduler-steps", type=int, default=1)
     ap.add_argument("--no-async-scheduling", action="store_true")
     ap.add_argument("--enforce-eager", action="store_true")
     ap.add_argument("--device", default="auto")
+    ap.add_argument("--dtype", default=None)
+    ap.add_argument("--kv-cache-dtype", default="auto", choices=["auto", "fp8", "int8"])
+    ap.add_argument("--quantization", default=None,
+                    help="for architecture presets with random weights: fp8, fp8_block, w8a8; "
+                         "checkpoints carry their own quantization_config")
+    ap.add_argument("--speculative-method", default=None,
+                    choices=[None, "ngram", "mtp", "eagle", "medusa", "mlp_speculator"])
+    ap.add_argument("--num-speculative-tokens", type=int, default=1)
+    ap.add_argument("--speculative-model", default=None)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--additional-config", default=None,
+                    help='JSON, e.g. \'{"cascade_min_tokens": 512}\'')
     ap.add_argument("--num-hidden-layers", type=int, default=0)
-    ap.add_argument("--kv-port", type=int, default=0,
-                    help="port of the point-to-point KV connector (disaggregated prefill)")
-    ap.add_argument("--kv-send-type", default="PUT_ASYNC", choices=["PUT", "PUT_ASYNC", "GET"])
     ap.add_argument("--enable-lora", action="store_true")
     ap.add_argument("--max-loras", type=int, default=4)
     ap.add_argument("--max-lora-rank", type=int, default=16)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__)
+    add_engine_arguments(ap)
+    ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--port", type=int, default=8000)
+    ap.add_argument("--kv-port", type=int, default=0,
+                    help="port of the point-to-point KV connector (disaggregated prefill)")
+    ap.add_argument("--kv-send-type", default="PUT_ASYNC", choices=["PUT", "PUT_ASYNC", "GET"])
     ap.add_argument("--lora-modules", nargs="*", default=[], metavar="NAME=PATH",
                     help="adapters loaded at start-up; requests select one by model name")
     args = ap.parse_args()
