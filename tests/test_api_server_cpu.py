@@ -69,6 +69,20 @@ def test_completions_and_streaming():
             assert r.status_code == 200 and len(r.json()["choices"][0]["token_ids"]) == 2
             bad = await c.post("/v1/chat/completions", json={"max_tokens": 2})
             assert bad.status_code == 400
+            # n / best_of: seeded samples, the best n by cumulative log-probability; logprobs
+            many = {"prompt": [1, 2, 3, 4], "max_tokens": 4, "temperature": 1.0, "seed": 3,
+                    "ignore_eos": True, "n": 2, "best_of": 4, "logprobs": 1}
+            r1 = (await c.post("/v1/completions", json=many)).json()
+            r2 = (await c.post("/v1/completions", json=many)).json()
+            assert [ch["index"] for ch in r1["choices"]] == [0, 1]
+            assert [ch["token_ids"] for ch in r1["choices"]] == \
+                [ch["token_ids"] for ch in r2["choices"]]
+            lp = [sum(ch["logprobs"]["token_logprobs"]) for ch in r1["choices"]]
+            assert lp[0] >= lp[1] and len(r1["choices"][0]["logprobs"]["top_logprobs"]) == 4
+            assert r1["usage"]["completion_tokens"] == 8 and r1["usage"]["prompt_tokens"] == 4
+            for bad_body in ({**many, "stream": True}, {**many, "best_of": 1},
+                             {**many, "use_beam_search": True}):
+                assert (await c.post("/v1/completions", json=bad_body)).status_code == 400
             # a decoder engine answers /v1/embeddings with last-token vectors of unit length
             e = (await c.post("/v1/embeddings", json={"input": [[1, 2, 3, 4], [9, 8, 7]]})).json()
             assert len(e["data"]) == 2 and e["usage"]["prompt_tokens"] == 7

@@ -239,6 +239,15 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None,
                 engine.validate_prompt(ids_)
         except (ValueError, TypeError) as e:
             return JSONResponse({"error": str(e)}, status_code=400)
+        n = int(body.get("n") or 1)
+        best_of = int(body.get("best_of") or n)
+        if body.get("use_beam_search"):
+            return JSONResponse({"error": "beam search is offered by the offline LLM class "
+                                          "(LLM.beam_search), not by the server"}, status_code=400)
+        if n < 1 or best_of < n:
+            return JSONResponse({"error": "best_of must be at least n >= 1"}, status_code=400)
+        if best_of > 1 and body.get("stream", False):
+            return JSONResponse({"error": "n / best_of > 1 cannot be streamed"}, status_code=400)
         rid = "cmpl-" + uuid.uuid4().hex[:16]
         created = int(time.time())
         state["requests"] += len(batch)
@@ -270,20 +279,49 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None,
                 yield "data: [DONE]\n\n"
             return StreamingResponse(sse(), media_type="text/event-stream")
 
-        import asyncio
+        import dataclasses
 
-        async def one(idx: int, ids) -> dict:
-            last = None
-            async for out in engine.generate_stream(ids, sp, priority=priority, **gen_kw):
-                last = out
-            toks = last.outputs[0].token_ids
-            state["tokens_out"] += len(toks)
-            c = chunk(idx, toks, last.outputs[0].finish_reason)["choices"][0]
-            c["prompt_tokens"] = len(ids)
-            c["kv_transfer_params"] = getattr(last, "kv_transfer_params", None)
+        def with_logprobs(c: dict, comp) -> dict:
+            if sp.logprobs is not None and comp.logprobs:
+                c["logprobs"] = {
+                    "tokens": [tokenizer.decode([t]) for t in comp.token_ids],
+                    "token_logprobs": [d.get(t) for t, d in zip(comp.token_ids, comp.logprobs)],
+                    "top_logprobs": [{tokenizer.decode([k]): v for k, v in d.items()}
+                                     for d in comp.logprobs]}
             return c
 
-        choices = await asyncio.gather(*[one(i, p) for i, p in enumerate(batch_ids)])
+        async def sample(ids, sp_c):
+            last = None
+            async for out in engine.generate_stream(ids, sp_c, priority=priority, **gen_kw):
+                last = out
+            return last
+
+        async def one(idx: int, ids) -> list[dict]:
+            """The ``n`` choices of one prompt: ``best_of`` seeded samples ranked by their
+            cumulative log-probability when more were asked for than are returned."""
+            if best_of == 1:
+                lasts = [await sample(ids, sp)]
+            else:
+                base = (sp.seed if sp.seed is not None else 0) * 7919
+                need_lp = sp.logprobs if sp.logprobs is not None else (0 if best_of > n else None)
+                lasts = list(await asyncio.gather(*[
+                    sample(ids, dataclasses.replace(sp, seed=base + c + 1, logprobs=need_lp))
+                    for c in range(best_of)]))
+                if best_of > n:
+                    lasts.sort(key=lambda o: -(o.outputs[0].cumulative_logprob or 0.0))
+                    lasts = lasts[:n]
+            out = []
+            for j, last in enumerate(lasts):
+                comp = last.outputs[0]
+                state["tokens_out"] += len(comp.token_ids)
+                c = chunk(idx * n + j, comp.token_ids, comp.finish_reason)["choices"][0]
+                c["prompt_tokens"] = len(ids) if j == 0 else 0
+                c["kv_transfer_params"] = getattr(last, "kv_transfer_params", None)
+                out.append(with_logprobs(c, comp))
+            return out
+
+        groups = await asyncio.gather(*[one(i, p) for i, p in enumerate(batch_ids)])
+        choices = [c for g in groups for c in g]
         usage = {"prompt_tokens": sum(c.pop("prompt_tokens") for c in choices),
                  "completion_tokens": sum(len(c["token_ids"]) for c in choices)}
         usage["total_tokens"] = usage["prompt_tokens"] + usage["completion_tokens"]
