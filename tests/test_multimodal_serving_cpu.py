@@ -1,0 +1,182 @@
+"""Images in chat requests on the CPU engine: a ``data:`` URL in the message parts reaches the
+vision tower through the server (a processor in the HuggingFace call convention for LLaVA, the
+model's own tiling for InternVL), with the same tokens as the offline engine on the same pixels;
+the multi-process executor carries the tensors to its workers."""
+import asyncio
+import base64
+import io
+
+import pytest
+import torch
+
+from vllm_gcu_b200.config import CacheConfig, EngineConfig, ModelConfig, SchedulerConfig
+from vllm_gcu_b200.engine.async_llm import AsyncLLM
+from vllm_gcu_b200.engine.llm import LLM
+from vllm_gcu_b200.engine.request import SamplingParams
+from vllm_gcu_b200.entrypoints.api_server import ByteTokenizer, build_app
+from vllm_gcu_b200.entrypoints.multimodal import (HFProcessorAdapter, ModelProcessorAdapter,
+                                                  load_image, split_messages)
+
+IMG = 290
+
+
+def _png_url(seed: int, size=(40, 30)) -> str:
+    from PIL import Image
+    import numpy as np
+    arr = np.random.default_rng(seed).integers(0, 255, (size[1], size[0], 3), dtype=np.uint8)
+    buf = io.BytesIO()
+    Image.fromarray(arr).save(buf, format="PNG")
+    return "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+
+
+def _llava_config() -> ModelConfig:
+    d = {"architectures": ["LlavaForConditionalGeneration"],
+         "text_config": dict(vocab_size=300, hidden_size=64, intermediate_size=128,
+                             num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                             max_position_embeddings=256, tie_word_embeddings=False,
+                             rms_norm_eps=1e-6),
+         "vision_config": dict(hidden_size=32, intermediate_size=64, num_hidden_layers=3,
+                               num_attention_heads=2, image_size=28, patch_size=14,
+                               hidden_act="quick_gelu"),
+         "image_token_index": IMG, "vision_feature_layer": -2,
+         "vision_feature_select_strategy": "default"}
+    return ModelConfig.from_hf_dict(d, dtype=torch.float32)
+
+
+class _Processor:
+    """Stand-in with the call convention of a HuggingFace processor: chat template, placeholder
+    expansion (4 rows per image), 28 x 28 pixel tensors."""
+    image_processor = object()
+
+    def apply_chat_template(self, messages, add_generation_prompt=True, tokenize=False):
+        text = ""
+        for m in messages:
+            parts = m["content"] if isinstance(m["content"], list) else \
+                [{"type": "text", "text": m["content"]}]
+            text += "".join("<image>" if p["type"] == "image" else p["text"] for p in parts) + "\n"
+        return text
+
+    def __call__(self, text, images=None, return_tensors="pt"):
+        import numpy as np
+        ids = []
+        for piece in text[0].split("<image>"):
+            ids += [3 + b for b in piece.encode()] + [IMG] * 4
+        ids = ids[:-4]
+        px = [torch.from_numpy(np.asarray(im.resize((28, 28)), dtype=np.float32) / 127.5 - 1.0)
+              .permute(2, 0, 1) for im in images or []]
+        return {"input_ids": torch.tensor([ids]), "pixel_values": torch.stack(px)}
+
+
+def test_message_parts_and_image_loading(tmp_path):
+    url = _png_url(0)
+    assert load_image(url).size == (40, 30)
+    load_image(url).save(tmp_path / "a.png")
+    assert load_image(str(tmp_path / "a.png")).size == (40, 30)
+    assert load_image("file://" + str(tmp_path / "a.png")).size == (40, 30)
+    with pytest.raises(ValueError):
+        load_image("https://example.com/a.png")
+    msgs, images = split_messages([
+        {"role": "system", "content": "be brief"},
+        {"role": "user", "content": [{"type": "text", "text": "what is "},
+                                     {"type": "image_url", "image_url": {"url": url}},
+                                     {"type": "text", "text": "?"}]}])
+    assert len(images) == 1 and msgs[0]["content"] == "be brief"
+    assert [p["type"] for p in msgs[1]["content"]] == ["text", "image", "text"]
+    with pytest.raises(ValueError):
+        split_messages([{"role": "user", "content": [{"type": "audio"}]}])
+
+
+@pytest.mark.timeout(180)
+def test_chat_with_an_image_matches_the_offline_engine():
+    httpx = pytest.importorskip("httpx")
+    mc = _llava_config()
+    cfg = EngineConfig(model=mc, cache=CacheConfig(num_gpu_blocks=64),
+                       scheduler=SchedulerConfig(max_num_seqs=4, max_num_batched_tokens=32,
+                                                 max_model_len=128), device="cpu", seed=0)
+    eng = AsyncLLM(cfg)
+    adapter = HFProcessorAdapter(_Processor())
+    app = build_app(eng, ByteTokenizer(300), "tiny-llava", mm_processor=adapter)
+    url = _png_url(1)
+    messages = [{"role": "user", "content": [{"type": "text", "text": "see "},
+                                             {"type": "image_url", "image_url": {"url": url}},
+                                             {"type": "text", "text": " ok"}]}]
+    ids, mm = adapter(*split_messages(messages))
+    assert ids.count(IMG) == 4 and mm["pixel_values"].shape == (1, 3, 28, 28)
+    off = LLM(_llava_config(), device="cpu", max_num_seqs=4, max_num_batched_tokens=32,
+              max_model_len=128, num_gpu_blocks=64, seed=0)
+    sp = SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True)
+    want = off.generate([{"prompt_token_ids": ids, "multi_modal_data": mm}], sp)[0]
+    plain = off.generate([[t for t in ids if t != IMG]], sp)[0]
+    assert want.outputs[0].token_ids != plain.outputs[0].token_ids
+
+    async def run():
+        transport = httpx.ASGITransport(app=app)
+        async with httpx.AsyncClient(transport=transport, base_url="http://t") as c:
+            body = {"messages": messages, "max_tokens": 5, "temperature": 0.0,
+                    "ignore_eos": True}
+            r = await c.post("/v1/chat/completions", json=body)
+            assert r.status_code == 200, r.text
+            text = r.json()["choices"][0]["message"]["content"]
+            assert text == ByteTokenizer(300).decode(want.outputs[0].token_ids)
+            bad = {**body, "messages": [{"role": "user", "content": [
+                {"type": "image_url", "image_url": {"url": "https://example.com/x.png"}}]}]}
+            assert (await c.post("/v1/chat/completions", json=bad)).status_code == 400
+    try:
+        asyncio.run(run())
+    finally:
+        eng.shutdown()
+
+
+def test_model_side_tiling_adapter_builds_engine_inputs():
+    """InternVL in its original layout tiles images itself: one placeholder per image in the
+    transcript is expanded to the rows of that image's tiles."""
+    d = {"architectures": ["InternVLChatModel"],
+         "llm_config": dict(architectures=["Qwen2ForCausalLM"], vocab_size=300, hidden_size=64,
+                            intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                            num_key_value_heads=2, max_position_embeddings=512,
+                            rms_norm_eps=1e-6, tie_word_embeddings=False),
+         "vision_config": dict(hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                               num_attention_heads=2, image_size=28, patch_size=7),
+         "downsample_ratio": 0.5, "img_context_token_id": IMG, "max_dynamic_patch": 4}
+    llm = LLM(ModelConfig.from_hf_dict(d, dtype=torch.float32), device="cpu", max_num_seqs=4,
+              max_num_batched_tokens=64, max_model_len=256, num_gpu_blocks=64)
+    adapter = ModelProcessorAdapter(llm.engine.model, ByteTokenizer(300))
+    msgs, images = split_messages([{"role": "user", "content": [
+        {"type": "image_url", "image_url": {"url": _png_url(2, size=(84, 28))}},
+        {"type": "text", "text": "hi"}]}])
+    ids, mm = adapter(msgs, images)
+    tiles = mm["pixel_values"].shape[0]
+    assert tiles == 4 and ids.count(IMG) == tiles * llm.engine.model.tokens_per_tile   # 3 + thumb
+    out = llm.generate([{"prompt_token_ids": ids, "multi_modal_data": mm}],
+                       SamplingParams(max_tokens=3, temperature=0.0, ignore_eos=True))
+    assert len(out[0].outputs[0].token_ids) == 3
+
+
+@pytest.mark.timeout(300)
+def test_executor_carries_image_tensors_to_its_workers():
+    from vllm_gcu_b200.config import ParallelConfig
+    from vllm_gcu_b200.engine.executor import MultiprocExecutor
+    cfg = EngineConfig(model=_llava_config(), cache=CacheConfig(num_gpu_blocks=64),
+                       scheduler=SchedulerConfig(max_num_seqs=4, max_num_batched_tokens=32,
+                                                 max_model_len=128),
+                       parallel=ParallelConfig(tensor_parallel_size=2, comm_backend="nccl"),
+                       device="cpu", seed=0)
+    ids = [5, 6] + [IMG] * 4 + [7, 8]
+    g = torch.Generator().manual_seed(0)
+    px = [torch.randn(1, 3, 28, 28, generator=g) for _ in range(2)]
+    sp = SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True)
+    ex = MultiprocExecutor(cfg)
+    try:
+        rids = [ex.add_request(ids, sp, multi_modal_data={"pixel_values": p})
+                for p in (px[0], px[1], px[0])]
+        got = {}
+        for _ in range(600):
+            for o in ex.poll(0.1):
+                if o.finished:
+                    got[o.request_id] = o.outputs[0].token_ids
+            if len(got) == 3:
+                break
+    finally:
+        ex.shutdown()
+    a, b, c = (got[r] for r in rids)
+    assert len(a) == 5 and a == c and a != b       # the pixels decide the continuation

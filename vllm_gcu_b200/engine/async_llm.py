@@ -86,7 +86,8 @@ class AsyncLLM:
     async def generate_stream(self, prompt_token_ids: Sequence[int],
                               sampling_params: Optional[SamplingParams] = None,
                               request_id: Optional[str] = None, priority: int = 0,
-                              lora_id: int = -1, kv_transfer_params: Optional[dict] = None
+                              lora_id: int = -1, kv_transfer_params: Optional[dict] = None,
+                              multi_modal_data: Optional[dict] = None
                               ) -> AsyncIterator[RequestOutput]:
         if self.error is not None:
             raise RuntimeError(f"engine failed: {self.error!r}")
@@ -99,7 +100,8 @@ class AsyncLLM:
         self._inbox.put(("add", dict(prompt_token_ids=prompt_token_ids,
                                      sampling_params=sampling_params, request_id=rid,
                                      priority=priority, lora_id=lora_id,
-                                     kv_transfer_params=kv_transfer_params)))
+                                     kv_transfer_params=kv_transfer_params,
+                                     multi_modal_data=multi_modal_data)))
         self._wake.set()
         try:
             while True:

@@ -135,8 +135,10 @@ def _worker_main(rank: int, world: int, port: int, cfg: EngineConfig, cmd_q, out
             batch, pending = pending[:n], pending[n:]
             for c in batch:
                 if c.kind == "add":
-                    rid, prompt, sp, prio, lora = c.payload
-                    engine.add_request(prompt, sp, request_id=rid, priority=prio, lora_id=lora)
+                    rid, prompt, sp, prio, lora = c.payload[:5]
+                    mm = c.payload[5] if len(c.payload) > 5 else None
+                    engine.add_request(prompt, sp, request_id=rid, priority=prio, lora_id=lora,
+                                       multi_modal_data=mm)
                 elif c.kind == "abort":
                     engine.abort_request(c.payload)
                 elif c.kind == "lora":
@@ -280,12 +282,14 @@ class MultiprocExecutor:
     # -- API -----------------------------------------------------------------------
     def add_request(self, prompt_token_ids: Sequence[int],
                     sampling_params: Optional[SamplingParams] = None,
-                    request_id: Optional[str] = None, priority: int = 0, lora_id: int = -1) -> str:
+                    request_id: Optional[str] = None, priority: int = 0, lora_id: int = -1,
+                    multi_modal_data: Optional[dict] = None) -> str:
         if request_id is None:
             request_id = f"req-{self._ids}"
             self._ids += 1
         cmd = _Cmd("add", (request_id, list(prompt_token_ids),
-                           sampling_params or SamplingParams(), priority, lora_id))
+                           sampling_params or SamplingParams(), priority, lora_id,
+                           multi_modal_data))
         if self.dp == 1:
             self._broadcast(cmd)
             return request_id
@@ -422,14 +426,16 @@ class AsyncMultiprocExecutor(MultiprocExecutor):
     async def generate_stream(self, prompt_token_ids: Sequence[int],
                               sampling_params: Optional[SamplingParams] = None,
                               request_id: Optional[str] = None, priority: int = 0,
-                              lora_id: int = -1) -> AsyncIterator[RequestOutput]:
+                              lora_id: int = -1, multi_modal_data: Optional[dict] = None
+                              ) -> AsyncIterator[RequestOutput]:
         self.validate_prompt(prompt_token_ids)
         self._ensure_pump()
         q: asyncio.Queue = asyncio.Queue()
         rid = request_id or f"areq-{self._ids}"
         self._ids += 1
         self._streams[rid] = q
-        self.add_request(prompt_token_ids, sampling_params, rid, priority, lora_id)
+        self.add_request(prompt_token_ids, sampling_params, rid, priority, lora_id,
+                         multi_modal_data)
         try:
             while True:
                 item = await q.get()

@@ -99,7 +99,9 @@ def _guided_schema(body: dict):
 
 
 def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None,
-              lora_modules: Optional[dict] = None):
+              lora_modules: Optional[dict] = None, mm_processor: Any = None):
+    """``mm_processor(messages, images) -> (prompt_token_ids, multi_modal_data)`` turns chat
+    messages with image parts into engine inputs (``entrypoints/multimodal.py``)."""
     if FastAPI is None:
         raise RuntimeError("the API server needs the fastapi package")
     app = FastAPI()
@@ -355,17 +357,27 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None,
                 _ensure_vocabulary()
         except ValueError as e:
             return JSONResponse({"error": str(e)}, status_code=400)
-        ids = render_chat(messages)
+        mm_kw: dict = {}
         try:
+            from .multimodal import split_messages
+            messages, images = split_messages(messages)
+            if images:
+                if mm_processor is None:
+                    raise ValueError("this server was not started with a multimodal processor")
+                ids, mm = mm_processor(messages, images)
+                mm_kw = {"multi_modal_data": mm}
+            else:
+                ids = render_chat([{**m, "content": "".join(p.get("text", "") for p in m["content"])}
+                                   if isinstance(m.get("content"), list) else m for m in messages])
             engine.validate_prompt(ids)
-        except ValueError as e:
+        except (ValueError, KeyError, OSError) as e:
             return JSONResponse({"error": str(e)}, status_code=400)
         rid = "chatcmpl-" + uuid.uuid4().hex[:16]
         created = int(time.time())
         state["requests"] += 1
         priority = int(body.get("priority", 0))
         base = {"id": rid, "created": created, "model": body.get("model") or model_name}
-        lora_kw = gen_kwargs(body)
+        lora_kw = {**gen_kwargs(body), **mm_kw}
 
         if body.get("stream", False):
             async def sse():
@@ -648,8 +660,13 @@ def main() -> None:
     tok = load_tokenizer(args.tokenizer or (args.model if "/" in args.model else None),
                          mc.vocab_size)
     import uvicorn
+    from .multimodal import default_processor
+    import os as _os
+    inner = getattr(getattr(engine, "engine", None), "model", None)
     app = build_app(engine, tok, args.model, lora_modules=dict(
-        m.split("=", 1) for m in args.lora_modules))
+        m.split("=", 1) for m in args.lora_modules),
+        mm_processor=default_processor(args.model if _os.path.isdir(args.model) else None,
+                                       inner, tok))
     uvicorn.run(app, host=args.host, port=args.port, log_level="warning")
 
 
