@@ -180,3 +180,21 @@ def test_executor_carries_image_tensors_to_its_workers():
         ex.shutdown()
     a, b, c = (got[r] for r in rids)
     assert len(a) == 5 and a == c and a != b       # the pixels decide the continuation
+
+
+def test_offline_prompt_with_a_pil_image():
+    """The offline form of upstream vLLM: a text prompt with the placeholder and the image as a
+    PIL object; the processor expands and encodes it."""
+    llm = LLM(_llava_config(), device="cpu", max_num_seqs=4, max_num_batched_tokens=32,
+              max_model_len=128, num_gpu_blocks=64, seed=0,
+              mm_processor=HFProcessorAdapter(_Processor()))
+    img = load_image(_png_url(1))
+    sp = SamplingParams(max_tokens=4, temperature=0.0, ignore_eos=True)
+    a = llm.generate([{"prompt": "see <image> ok", "multi_modal_data": {"image": img}}], sp)[0]
+    ids, mm = HFProcessorAdapter(_Processor()).from_text("see <image> ok", [img])
+    b = llm.generate([{"prompt_token_ids": ids, "multi_modal_data": mm}], sp)[0]
+    assert a.outputs[0].token_ids == b.outputs[0].token_ids and a.prompt_token_ids == ids
+    with pytest.raises(ValueError):
+        LLM(_llava_config(), device="cpu", max_num_seqs=4, max_num_batched_tokens=32,
+            max_model_len=128, num_gpu_blocks=64).generate(
+            [{"prompt": "x <image>", "multi_modal_data": {"image": img}}], sp)

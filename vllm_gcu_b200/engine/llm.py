@@ -435,7 +435,8 @@ class LLM:
                  prompt_lookup_max: int = 4, prompt_lookup_min: int = 1,
                  enable_lora: bool = False, max_loras: int = 4, max_lora_rank: int = 16,
                  additional_config: Optional[dict] = None, tokenizer=None,
-                 quantization_param_path: Optional[str] = None, **model_overrides):
+                 quantization_param_path: Optional[str] = None, mm_processor=None,
+                 **model_overrides):
         model_path = None
         if isinstance(model, ModelConfig):
             mc = model
@@ -488,9 +489,24 @@ class LLM:
                 self.tokenizer = None
         elif tokenizer is not None:
             self.tokenizer = tokenizer
+        # images given as PIL objects (``multi_modal_data={"image": ...}``) go through the
+        # checkpoint's HuggingFace processor when it has one (entrypoints/multimodal.py)
+        self.mm_processor = mm_processor
+        if mm_processor is None and model_path:
+            from ..entrypoints.multimodal import default_processor
+            self.mm_processor = default_processor(model_path, self.engine.model, self.tokenizer)
 
     def _encode(self, prompt):
         """Prompts may be token-id lists, dicts with ``prompt_token_ids`` or text."""
+        if isinstance(prompt, dict) and "image" in (prompt.get("multi_modal_data") or {}) \
+                and "prompt" in prompt:
+            if self.mm_processor is None or not hasattr(self.mm_processor, "from_text"):
+                raise ValueError("raw images need a multimodal processor "
+                                 "(LLM(..., mm_processor=...))")
+            images = prompt["multi_modal_data"]["image"]
+            images = list(images) if isinstance(images, (list, tuple)) else [images]
+            ids, mm = self.mm_processor.from_text(prompt["prompt"], images)
+            return {"prompt_token_ids": ids, "multi_modal_data": mm}
         if isinstance(prompt, str):
             if self.tokenizer is None:
                 raise ValueError("text prompts need a tokenizer (LLM(..., tokenizer=...))")

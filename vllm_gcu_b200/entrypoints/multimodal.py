@@ -74,6 +74,11 @@ class HFProcessorAdapter:
     def __call__(self, messages: Sequence[dict], images: Sequence) -> tuple[list[int], dict]:
         text = self.processor.apply_chat_template(list(messages), add_generation_prompt=True,
                                                   tokenize=False)
+        return self.from_text(text, images)
+
+    def from_text(self, text: str, images: Sequence) -> tuple[list[int], dict]:
+        """A prompt that already carries the model's image placeholders (the offline form:
+        ``{"prompt": "<image>\\nDescribe.", "multi_modal_data": {"image": pil_image}}``)."""
         enc = self.processor(text=[text], images=list(images) or None, return_tensors="pt")
         ids = [int(t) for t in enc["input_ids"][0]]
         mm = {k: enc[k] for k in self.KEYS if k in enc}
