@@ -391,3 +391,67 @@ def test_tp2_multi_lora_matches_single_process(tmp_path):
     finally:
         ex.shutdown()
     assert [got[r] for r in rids] == [want[i] for i in ids]
+
+
+@pytest.mark.timeout(400)
+def test_pp2_tp2_random_schedule_matches_transformers_weights(tmp_path):
+    """Two pipeline stages of two tensor-parallel ranks under a small KV pool with priorities,
+    swapping and staggered arrivals: every request gets the tokens of the unsharded engine."""
+    import random
+    tr = pytest.importorskip("transformers")
+    from vllm_gcu_b200.config import ModelConfig
+    from vllm_gcu_b200.utils.weights import write_safetensors
+    hc = tr.LlamaConfig(vocab_size=512, hidden_size=64, intermediate_size=128,
+                        num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,
+                        max_position_embeddings=256, rms_norm_eps=1e-6,
+                        tie_word_embeddings=False)
+    torch.manual_seed(0)
+    hf = tr.LlamaForCausalLM(hc).eval().float()
+    write_safetensors(os.path.join(str(tmp_path), "model.safetensors"),
+                      {k: v.clone() for k, v in hf.state_dict().items()})
+    d = hc.to_dict()
+    d["architectures"] = ["LlamaForCausalLM"]
+
+    def cfg(par, blocks, seqs, budget, cpu_blocks=0, policy="fcfs"):
+        c = EngineConfig(model=ModelConfig.from_hf_dict(d, dtype=torch.float32),
+                         cache=CacheConfig(block_size=16, num_gpu_blocks=blocks,
+                                           num_cpu_blocks=cpu_blocks),
+                         scheduler=SchedulerConfig(max_num_seqs=seqs, policy=policy,
+                                                   max_num_batched_tokens=budget,
+                                                   max_model_len=256),
+                         parallel=par, device="cpu", seed=0)
+        c.load_format, c.model_path = "safetensors", str(tmp_path)
+        return c
+
+    rng = random.Random(1)
+    g = torch.Generator().manual_seed(1)
+    n = 7
+    prompts = [torch.randint(0, 512, (rng.randint(3, 70),), generator=g).tolist()
+               for _ in range(n)]
+    sps = [SamplingParams(max_tokens=rng.randint(1, 20), temperature=0.0, ignore_eos=True)
+           for _ in prompts]
+    eng = LLMEngine(cfg(ParallelConfig(), 256, 16, 256))
+    for i, p in enumerate(prompts):
+        eng.add_request(p, sps[i], request_id=str(i))
+    want = {}
+    while eng.has_unfinished():
+        for o in eng.step():
+            if o.finished:
+                want[int(o.request_id)] = o.outputs[0].token_ids
+    par = ParallelConfig(pipeline_parallel_size=2, tensor_parallel_size=2, comm_backend="nccl")
+    ex = MultiprocExecutor(cfg(par, 12, 4, 32, cpu_blocks=16, policy="priority"))
+    try:
+        pending, ids, got = list(range(n)), {}, {}
+        for _ in range(3000):
+            for _ in range(rng.randint(0, 3)):
+                if pending:
+                    i = pending.pop()
+                    ids[ex.add_request(prompts[i], sps[i], priority=rng.randint(0, 2))] = i
+            for o in ex.poll(0.02):
+                if o.finished:
+                    got[ids[o.request_id]] = o.outputs[0].token_ids
+            if len(got) == n:
+                break
+    finally:
+        ex.shutdown()
+    assert got == want
