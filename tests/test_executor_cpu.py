@@ -455,3 +455,69 @@ def test_pp2_tp2_random_schedule_matches_transformers_weights(tmp_path):
     finally:
         ex.shutdown()
     assert got == want
+
+
+def _free_port_pair():
+    import socket
+    for _ in range(50):
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            p = s.getsockname()[1]
+        try:
+            with socket.socket() as s2:
+                s2.bind(("127.0.0.1", p + 1))
+            return p
+        except OSError:
+            continue
+    raise RuntimeError("no two adjacent free ports")
+
+
+@pytest.mark.timeout(400)
+def test_disaggregated_prefill_between_two_tensor_parallel_instances():
+    """1P1D with both instances sharded over two ranks: every worker opens its own connector
+    (base port + rank), rank r of the prefill instance ships its KV shard to rank r of the
+    decode instance; the decode instance takes the prompt's KV over, and the tokens are those
+    of one instance working alone."""
+    g = torch.Generator().manual_seed(8)
+    prompt = torch.randint(0, 32000, (37,), generator=g).tolist()
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+
+    def cfg(port=None):
+        c = _cfg(2)
+        if port:
+            c.additional_config["kv_connector"] = {"host": "127.0.0.1", "port": port,
+                                                   "send_type": "PUT", "recv_timeout_s": 10.0}
+        return c
+
+    def finish(ex, rid):
+        for _ in range(1200):
+            for o in ex.poll(0.05):
+                if o.finished and o.request_id == rid:
+                    return o
+        raise AssertionError("request did not finish")
+
+    alone = MultiprocExecutor(cfg())
+    try:
+        want = alone.generate([prompt], sp)[0].outputs[0].token_ids
+    finally:
+        alone.shutdown()
+    pp, dp_ = _free_port_pair(), _free_port_pair()
+    pre, dec = MultiprocExecutor(cfg(pp)), MultiprocExecutor(cfg(dp_))
+    try:
+        rid = pre.add_request(prompt, SamplingParams(max_tokens=1, temperature=0.0,
+                                                     ignore_eos=True), request_id="r-77",
+                              kv_transfer_params={"do_remote_decode": True,
+                                                  "remote": f"127.0.0.1:{dp_}"})
+        first = finish(pre, rid)
+        assert first.outputs[0].token_ids == want[:1]
+        handoff = first.kv_transfer_params
+        assert handoff["remote"] == f"127.0.0.1:{pp}" and handoff["remote_request_id"] == rid
+        did = dec.add_request(prompt, sp, request_id="d-1", kv_transfer_params={
+            "do_remote_prefill": True, "remote": handoff["remote"],
+            "remote_request_id": handoff["remote_request_id"]})
+        out = finish(dec, did)
+        assert out.outputs[0].token_ids == want
+        assert out.num_cached_tokens == len(prompt) - 1      # taken over, not recomputed
+    finally:
+        pre.shutdown()
+        dec.shutdown()

@@ -264,3 +264,15 @@ def test_disaggregated_prefill_first_token_reuse_and_block_granular(monkeypatch)
     finally:
         cp.close()
         cd.close()
+
+
+def test_connector_on_an_explicit_port_reports_its_address():
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    c = P2PKVConnector(port=port)
+    try:
+        assert c.port == port and c.addr == f"127.0.0.1:{port}"
+    finally:
+        c.close()

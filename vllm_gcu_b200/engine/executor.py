@@ -61,6 +61,12 @@ class _Cmd:
     payload: Any = None
 
 
+def _rank_address(addr: str, rank: int) -> str:
+    """``host:port`` of an instance's rank 0 -> the address of its rank ``rank``."""
+    host, _, port = addr.rpartition(":")
+    return f"{host}:{int(port) + rank}"
+
+
 def _worker_main(rank: int, world: int, port: int, cfg: EngineConfig, cmd_q, out_q, hb,
                  backend: Optional[str]) -> None:
     """Entry point of a worker process."""
@@ -103,6 +109,18 @@ def _worker_main(rank: int, world: int, port: int, cfg: EngineConfig, cmd_q, out
                 g = dist.new_group(ranks, backend="gloo") if len(ranks) > 1 else None
                 if rank in ranks:
                     ctrl = g
+        kvc = cfg.additional_config.get("kv_connector")
+        connector = None
+        if kvc:
+            # disaggregated prefill with sharded instances: rank r of one instance talks to rank
+            # r of the other, on the instance's base port + r (both sides use the same layout)
+            from ..parallel.kv_transfer import P2PKVConnector
+            connector = P2PKVConnector(host=kvc.get("host", "127.0.0.1"),
+                                       port=int(kvc["port"]) + rank,
+                                       send_type=kvc.get("send_type", "PUT_ASYNC"),
+                                       device=str(engine.device))
+            engine.attach_kv_connector(connector,
+                                       recv_timeout_s=float(kvc.get("recv_timeout_s", 30.0)))
         out_q.put(("READY", rank, engine.runner.num_blocks))
         pending: list[_Cmd] = []
         stop = False
@@ -137,8 +155,12 @@ def _worker_main(rank: int, world: int, port: int, cfg: EngineConfig, cmd_q, out
                 if c.kind == "add":
                     rid, prompt, sp, prio, lora = c.payload[:5]
                     mm = c.payload[5] if len(c.payload) > 5 else None
+                    kvp = c.payload[6] if len(c.payload) > 6 else None
+                    if kvp and kvp.get("remote"):
+                        # the front end names the peer instance by its base address
+                        kvp = dict(kvp, remote=_rank_address(kvp["remote"], rank))
                     engine.add_request(prompt, sp, request_id=rid, priority=prio, lora_id=lora,
-                                       multi_modal_data=mm)
+                                       multi_modal_data=mm, kv_transfer_params=kvp)
                 elif c.kind == "abort":
                     engine.abort_request(c.payload)
                 elif c.kind == "lora":
@@ -159,6 +181,12 @@ def _worker_main(rank: int, world: int, port: int, cfg: EngineConfig, cmd_q, out
             if engine.has_unfinished() or dp > 1:
                 outs = engine.step()          # dp > 1: every replica joins the exchange
                 if rank == lead and outs:
+                    if connector is not None:
+                        for o in outs:          # answers name the instance by its base address
+                            if o.kv_transfer_params and o.kv_transfer_params.get("remote"):
+                                o.kv_transfer_params = dict(
+                                    o.kv_transfer_params,
+                                    remote=_rank_address(o.kv_transfer_params["remote"], -rank))
                     out_q.put(("OUT", outs))
         out_q.put(("STOPPED", rank, None))
     except SystemExit:
@@ -283,13 +311,14 @@ class MultiprocExecutor:
     def add_request(self, prompt_token_ids: Sequence[int],
                     sampling_params: Optional[SamplingParams] = None,
                     request_id: Optional[str] = None, priority: int = 0, lora_id: int = -1,
-                    multi_modal_data: Optional[dict] = None) -> str:
+                    multi_modal_data: Optional[dict] = None,
+                    kv_transfer_params: Optional[dict] = None) -> str:
         if request_id is None:
             request_id = f"req-{self._ids}"
             self._ids += 1
         cmd = _Cmd("add", (request_id, list(prompt_token_ids),
                            sampling_params or SamplingParams(), priority, lora_id,
-                           multi_modal_data))
+                           multi_modal_data, kv_transfer_params))
         if self.dp == 1:
             self._broadcast(cmd)
             return request_id
@@ -426,7 +455,8 @@ class AsyncMultiprocExecutor(MultiprocExecutor):
     async def generate_stream(self, prompt_token_ids: Sequence[int],
                               sampling_params: Optional[SamplingParams] = None,
                               request_id: Optional[str] = None, priority: int = 0,
-                              lora_id: int = -1, multi_modal_data: Optional[dict] = None
+                              lora_id: int = -1, multi_modal_data: Optional[dict] = None,
+                              kv_transfer_params: Optional[dict] = None
                               ) -> AsyncIterator[RequestOutput]:
         self.validate_prompt(prompt_token_ids)
         self._ensure_pump()
@@ -435,7 +465,7 @@ class AsyncMultiprocExecutor(MultiprocExecutor):
         self._ids += 1
         self._streams[rid] = q
         self.add_request(prompt_token_ids, sampling_params, rid, priority, lora_id,
-                         multi_modal_data)
+                         multi_modal_data, kv_transfer_params)
         try:
             while True:
                 item = await q.get()

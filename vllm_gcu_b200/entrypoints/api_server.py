@@ -572,6 +572,10 @@ def make_engine(args) -> tuple[Any, ModelConfig]:
         sc.async_scheduling = False        # the platform policy's exclusions
     if pc.world_size > 1:
         from ..engine.executor import AsyncMultiprocExecutor
+        if getattr(args, "kv_port", 0):
+            # every worker opens its own connector on kv_port + rank
+            cfg.additional_config["kv_connector"] = {"host": args.host, "port": args.kv_port,
+                                                     "send_type": args.kv_send_type}
         return AsyncMultiprocExecutor(cfg), mc
     from ..engine.async_llm import AsyncLLM
     eng = AsyncLLM(cfg)

@@ -89,8 +89,11 @@ class P2PKVConnector:
         self.device = torch.device(device)
         self.ctx = zmq.Context.instance()
         self.router = self.ctx.socket(zmq.ROUTER)
-        self.port = self.router.bind_to_random_port(f"tcp://{host}") if port == 0 else \
-            (self.router.bind(f"tcp://{host}:{port}") or port)
+        if port == 0:
+            self.port = self.router.bind_to_random_port(f"tcp://{host}")
+        else:
+            self.router.bind(f"tcp://{host}:{port}")
+            self.port = int(port)
         self.addr = f"{host}:{self.port}"
         self.peers: dict[str, zmq.Socket] = {}
         self.peer_locks: dict[str, threading.Lock] = {}
