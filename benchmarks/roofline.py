@@ -70,6 +70,8 @@ def main():
     # expert-parallel dispatch / combine (DeepSeek-V3 shapes, 128 tokens per rank, k = 8)
     for name, rows_per_rank, width in (("EP dispatch (bf16 rows + ids + weights)", 128 * 8,
                                         7168 * 2 + 64),
+                                       ("EP dispatch (fp8 rows + group scales + ids + weights)",
+                                        128 * 8, 7168 + 7168 // 128 * 4 + 64),
                                        ("EP combine (bf16 rows)", 128 * 8, 7168 * 2)):
         b = rows_per_rank * width * (p - 1) / p
         t = b / (LINK_GBS * 1e9)
