@@ -31,6 +31,8 @@ async def one_request(session, url, body, result):
     n_out = 0
     try:
         async with session.post(url, json=body) as resp:
+            if resp.status != 200:
+                raise RuntimeError(f"HTTP {resp.status}: {(await resp.text())[:200]}")
             async for raw in resp.content:
                 line = raw.decode().strip()
                 if not line.startswith("data: ") or line.endswith("[DONE]"):
@@ -50,10 +52,61 @@ async def one_request(session, url, body, result):
                 last = now
                 n_out += n_new
         result.append({"ok": True, "ttft": ttft, "e2e": last - t0, "itl": itl, "n_out": n_out,
-                       "n_in": len(body["prompt"]) if "prompt" in body
+                       "n_in": (len(body["prompt"]) if not isinstance(body["prompt"], str)
+                                else max(1, len(body["prompt"]) // 4)) if "prompt" in body
                        else sum(len(m["content"]) for m in body["messages"])})
     except Exception as e:  # noqa: BLE001
         result.append({"ok": False, "error": repr(e)})
+
+
+def _count(tokenizer, text: str) -> int:
+    """Token count of ``text`` (about four characters per token without a tokenizer)."""
+    if tokenizer is not None:
+        return len(tokenizer.encode(text))
+    return max(1, len(text) // 4)
+
+
+def load_dataset_requests(args, rng) -> list:
+    """(prompt, output length) pairs from a dataset file, as the reference's load generator
+    samples them (benchmarks/benchmark_serving.py:100-220 of the reference): ``sharegpt`` takes
+    the first two turns of each conversation (the reply's length is the output length),
+    ``sonnet`` builds prompts from randomly chosen lines of a text file."""
+    tokenizer = None
+    if getattr(args, "tokenizer", None):
+        from transformers import AutoTokenizer
+        tokenizer = AutoTokenizer.from_pretrained(args.tokenizer)
+    out = []
+    if args.dataset_name == "sharegpt":
+        with open(args.dataset_path, encoding="utf-8") as f:
+            data = json.load(f)
+        convs = [d["conversations"] for d in data if len(d.get("conversations", [])) >= 2]
+        rng.shuffle(convs)
+        for c in convs:
+            prompt, reply = c[0]["value"], c[1]["value"]
+            n_in, n_out = _count(tokenizer, prompt), _count(tokenizer, reply)
+            if n_in < 4 or n_out < 4 or n_in > args.max_input_len or \
+                    n_in + n_out > args.max_input_len + args.max_output_len:
+                continue                          # the reference prunes the same extremes
+            out.append((prompt, args.fixed_output_len or n_out))
+            if len(out) == args.num_prompts:
+                break
+    elif args.dataset_name == "sonnet":
+        with open(args.dataset_path, encoding="utf-8") as f:
+            lines = [ln.strip() for ln in f if ln.strip()]
+        per_line = sum(_count(tokenizer, ln) for ln in lines) / max(1, len(lines))
+        n_lines = max(1, int(args.sonnet_input_len / per_line))
+        n_prefix = min(n_lines, int(args.sonnet_prefix_len / per_line))
+        prefix = lines[:n_prefix]
+        for _ in range(args.num_prompts):
+            body = [rng.choice(lines) for _ in range(n_lines - n_prefix)]
+            text = "Pick as many lines as you can from these poem lines:\n" + \
+                "\n".join(prefix + body)
+            out.append((text, args.fixed_output_len or args.sonnet_output_len))
+    else:
+        raise ValueError(f"unknown dataset {args.dataset_name!r}")
+    if len(out) < args.num_prompts:
+        out = (out * (args.num_prompts // max(1, len(out)) + 1))[:args.num_prompts]
+    return out
 
 
 async def run(args):
@@ -74,14 +127,23 @@ async def run(args):
     results: list = []
     tasks = []
     timeout = aiohttp.ClientTimeout(total=6 * 3600)
+    dataset = load_dataset_requests(args, rng) \
+        if getattr(args, "dataset_name", "random") != "random" else None
     async with aiohttp.ClientSession(timeout=timeout) as session:
         t_start = time.perf_counter()
         for i in range(args.num_prompts):
             n_in = rng.randint(*args.input_len_range)
             n_out = rng.randint(*args.output_len_range)
+            if dataset is not None:
+                n_out = dataset[i][1]
             body = {"max_tokens": n_out, "temperature": args.temperature, "stream": True,
                     "ignore_eos": True}
-            if chat:     # random printable text of about n_in characters
+            if dataset is not None:
+                if chat:
+                    body["messages"] = [{"role": "user", "content": dataset[i][0]}]
+                else:
+                    body["prompt"] = dataset[i][0]
+            elif chat:     # random printable text of about n_in characters
                 text = "".join(chr(rng.randrange(97, 123)) for _ in range(n_in))
                 body["messages"] = [{"role": "user", "content": text}]
             else:
@@ -164,6 +226,19 @@ def main():
     ap.add_argument("--input-len-range", type=int, nargs=2, default=[256, 2048])
     ap.add_argument("--output-len-range", type=int, nargs=2, default=[64, 512])
     ap.add_argument("--vocab-size", type=int, default=32000)
+    ap.add_argument("--dataset-name", default="random", choices=["random", "sharegpt", "sonnet"])
+    ap.add_argument("--dataset-path", default=None)
+    ap.add_argument("--tokenizer", default=None,
+                    help="tokenizer directory for counting dataset tokens (else 4 chars / token)")
+    ap.add_argument("--max-input-len", type=int, default=1024)
+    ap.add_argument("--max-output-len", type=int, default=1024)
+    ap.add_argument("--fixed-output-len", type=int, default=None)
+    ap.add_argument("--sonnet-input-len", type=int, default=550)
+    ap.add_argument("--sonnet-output-len", type=int, default=150)
+    ap.add_argument("--sonnet-prefix-len", type=int, default=200)
+    ap.add_argument("--strict-in-out-len", action="store_true",
+                    help="accepted for compatibility: requests always run to max_tokens "
+                         "(ignore_eos) and token-id prompts have exact lengths")
     ap.add_argument("--temperature", type=float, default=0.0)
     ap.add_argument("--extra-body", default=None)
     ap.add_argument("--seed", type=int, default=0)

@@ -82,7 +82,7 @@ def test_serving_benchmark_over_two_servers(servers):
         backend="openai", num_prompts=6, request_rate=float("inf"), burstiness=1.0,
         input_len_range=[4, 12], output_len_range=[3, 6], vocab_size=32000, temperature=0.0,
         extra_body=None, seed=0, output_json=None, max_concurrency=3,
-        goodput=["ttft:60000", "tpot:60000"])
+        goodput=["ttft:60000", "tpot:60000"], dataset_name="random")
     res = asyncio.run(bs.run(args))
     assert res["completed"] == 6 and res["failed"] == 0
     assert res["good_requests"] == 6 and res["request_goodput"] > 0
@@ -115,9 +115,43 @@ def test_router_spreads_requests_and_forwards_streams(servers):
             host="127.0.0.1", port=front.port, ports=None, backend="openai", num_prompts=4,
             request_rate=float("inf"), burstiness=1.0, input_len_range=[4, 8],
             output_len_range=[3, 4], vocab_size=32000, temperature=0.0, extra_body=None,
-            seed=1, output_json=None, max_concurrency=None, goodput=None)
+            seed=1, output_json=None, max_concurrency=None, goodput=None, dataset_name="random")
         res = asyncio.run(bs.run(args))
         assert res["completed"] == 4 and res["failed"] == 0
         assert router.active == [0, 0]
     finally:
         front.stop()
+
+
+@pytest.mark.timeout(180)
+def test_serving_benchmark_with_dataset_files(servers, tmp_path):
+    """ShareGPT-style conversations and a text file of lines as prompt sources (text prompts
+    are tokenised by the server)."""
+    import json as _json
+    bs = _load("benchmark_serving")
+    share = [{"conversations": [{"from": "human", "value": f"question number {i} " * 3},
+                                {"from": "gpt", "value": "an answer " * (2 + i)}]}
+             for i in range(6)]
+    share.append({"conversations": [{"from": "human", "value": "too short"}]})
+    (tmp_path / "share.json").write_text(_json.dumps(share))
+    (tmp_path / "poem.txt").write_text("\n".join(f"line {i} of the poem" for i in range(20)))
+    base = dict(host="127.0.0.1", port=servers[0].port, ports=None, backend="openai",
+                num_prompts=4, request_rate=float("inf"), burstiness=1.0,
+                input_len_range=[4, 8], output_len_range=[3, 4], vocab_size=32000,
+                temperature=0.0, extra_body=None, seed=0, output_json=None,
+                max_concurrency=None, goodput=None, tokenizer=None, max_input_len=100,
+                max_output_len=100, fixed_output_len=None, sonnet_input_len=12,
+                sonnet_output_len=5, sonnet_prefix_len=4)
+    a = argparse.Namespace(**base, dataset_name="sharegpt", dataset_path=str(tmp_path / "share.json"))
+    reqs = bs.load_dataset_requests(a, __import__("random").Random(0))
+    assert len(reqs) == 4 and all(isinstance(p, str) and n >= 4 for p, n in reqs)
+    res = asyncio.run(bs.run(a))
+    assert res["completed"] == 4 and res["failed"] == 0
+    b = argparse.Namespace(**base, dataset_name="sonnet", dataset_path=str(tmp_path / "poem.txt"))
+    res = asyncio.run(bs.run(b))
+    assert res["completed"] == 4 and res["output_token_throughput"] > 0
+    # a prompt the server refuses counts as a failed request, not as an empty success
+    c = argparse.Namespace(**{**base, "sonnet_input_len": 400}, dataset_name="sonnet",
+                           dataset_path=str(tmp_path / "poem.txt"))
+    res = asyncio.run(bs.run(c))
+    assert res["completed"] == 0 and res["failed"] == 4
