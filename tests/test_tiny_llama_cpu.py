@@ -69,3 +69,27 @@ def test_chunked_prefill_and_async_scheduling_agree():
     _, _, asyn = _run(True, 24)
     for a, b, c in zip(base, chunked, asyn):
         assert a.outputs[0].token_ids == b.outputs[0].token_ids == c.outputs[0].token_ids
+
+
+def test_step_times_are_logged_by_batch_size(monkeypatch, caplog):
+    """``VLLM_B200_LOG_FORWARD_TIME_EVERY``: the engine keeps step wall times per batch size
+    and logs their medians periodically."""
+    import logging
+    import torch
+    from vllm_gcu_b200.engine.llm import LLM
+    from vllm_gcu_b200.engine.request import SamplingParams
+    monkeypatch.setenv("VLLM_B200_LOG_FORWARD_TIME_EVERY", "4")
+    llm = LLM("tiny-llama", device="cpu", max_num_seqs=4, max_num_batched_tokens=64,
+              max_model_len=128, num_gpu_blocks=64, dtype="float32")
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 32000, (n,), generator=g).tolist() for n in (9, 20)]
+    lg = logging.getLogger("vllm_gcu_b200")
+    lg.addHandler(caplog.handler)
+    try:
+        with caplog.at_level(logging.INFO, logger="vllm_gcu_b200"):
+            llm.generate(prompts, SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True))
+    finally:
+        lg.removeHandler(caplog.handler)
+    times = llm.engine._step_times
+    assert sum(len(v) for v in times.values()) == llm.engine.stats["steps"] and 2 in times
+    assert any("median step time by batch size" in r.getMessage() for r in caplog.records)

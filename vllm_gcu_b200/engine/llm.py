@@ -343,6 +343,32 @@ class LLMEngine:
 
     def _step_once(self) -> list[RequestOutput]:
         """Runs (or, with async scheduling, launches and retires) one engine step."""
+        from .. import envs
+        every = envs.LOG_FORWARD_TIME_EVERY
+        if every <= 0:
+            return self._step_inner()
+        t0 = time.perf_counter()
+        n_before = self.stats["steps"]
+        outs = self._step_inner()
+        if self.stats["steps"] > n_before:
+            self.record_step_time(self.scheduler.num_running_last, time.perf_counter() - t0,
+                                  every)
+        return outs
+
+    def record_step_time(self, batch: int, seconds: float, every: int) -> None:
+        """Step wall times by batch size; their medians are logged every ``every`` steps
+        (vllm_gcu/patch/patch_0_8_0/forward_context.py:62-92 keeps the same statistic)."""
+        log = self.__dict__.setdefault("_step_times", {})
+        log.setdefault(int(batch), []).append(seconds)
+        total = sum(len(v) for v in log.values())
+        if total % every == 0:
+            import statistics
+            from ..utils import logger
+            logger.info("median step time by batch size: %s", ", ".join(
+                f"{b}: {statistics.median(v) * 1e3:.2f} ms ({len(v)})"
+                for b, v in sorted(log.items())))
+
+    def _step_inner(self) -> list[RequestOutput]:
         outs: list[RequestOutput] = []
         if self._want_sync and self.cfg.scheduler.async_scheduling:
             # a request whose next token depends on host-side history has arrived: retire

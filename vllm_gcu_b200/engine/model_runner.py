@@ -228,7 +228,17 @@ class ModelRunner:
         if n < 16:
             raise RuntimeError(f"not enough GPU memory for the KV cache ({budget} bytes)")
         cap = self.max_seqs * self.max_blocks * 4
-        return int(min(n, cap))
+        n = int(min(n, cap))
+        try:        # the memory budget, as the reference logs it at start-up
+            from ..utils import logger
+            gib = float(1 << 30)
+            logger.info("memory budget: %.1f GiB total x %.2f; weights + peak activations "
+                        "%.1f GiB; KV cache %.1f GiB = %d blocks of %d bytes",
+                        total / gib, cc.gpu_memory_utilization, weights_and_act / gib,
+                        n * bytes_per_block / gib, n, bytes_per_block)
+        except Exception:  # noqa: BLE001 - a log line never stops the engine
+            pass
+        return n
 
     def init_kv_cache(self, num_blocks: int) -> None:
         spec = self.model.kv_cache_spec()

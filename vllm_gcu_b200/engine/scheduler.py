@@ -73,6 +73,7 @@ class Scheduler:
         self.num_lookahead_tokens = num_lookahead_tokens
         self.step_id = 0
         self.num_preemptions = 0
+        self.num_running_last = 0          # requests in the most recent scheduler output
         # host blocks of the swap space (CacheConfig.num_cpu_blocks > 0 turns preemption by
         # recomputation into preemption by swapping where the victim's state allows it)
         self.cpu_free: list[int] = list(range(int(getattr(cache_cfg, "num_cpu_blocks", 0) or 0)))
@@ -330,6 +331,7 @@ class Scheduler:
     def _update_after_schedule(self, out: SchedulerOutput) -> None:
         """Advances ``num_computed_tokens`` right away so the next step can be planned
         before this one returns (async_scheduler.py:478-515)."""
+        self.num_running_last = len(out.scheduled)
         for s in out.scheduled:
             req = s.req
             s.epoch = getattr(req, "preempt_epoch", 0)

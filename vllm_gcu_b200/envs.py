@@ -84,6 +84,9 @@ environment_variables: dict[str, Callable[[], Any]] = {
     # under vLLM: the worker reads the native status word (one device-to-host copy) every this
     # many steps and raises when a kernel reported a wait that ran out (0 = never)
     "CHECK_STATUS_EVERY": lambda: int(_get("CHECK_STATUS_EVERY", "0")),
+    # log the median wall time of an engine step per batch size every this many steps
+    # (0 = off; the reference logs median forward time per batch size periodically)
+    "LOG_FORWARD_TIME_EVERY": lambda: int(_get("LOG_FORWARD_TIME_EVERY", "0")),
     "NIXL_ENABLE_FULL_KV_TRANSFER": _flag("NIXL_ENABLE_FULL_KV_TRANSFER", "1"),
     # ... and starts at the first output token the prefill instance already produced
     "NIXL_ENABLE_FIRST_TOKEN_REUSE": _flag("NIXL_ENABLE_FIRST_TOKEN_REUSE"),
