@@ -18,7 +18,8 @@ def init_logger(name: str = "vllm_gcu_b200") -> logging.Logger:
     """Package logger with the module prefix (vllm_gcu/__init__.py:35-71)."""
     logger = logging.getLogger(name)
     if not logger.handlers:
-        h = logging.StreamHandler(sys.stdout)
+        # stderr: tools of this package print their results (JSON lines) on stdout
+        h = logging.StreamHandler(sys.stderr)
         h.setFormatter(logging.Formatter(_FORMAT, datefmt="%m-%d %H:%M:%S"))
         logger.addHandler(h)
         logger.setLevel(os.environ.get("VLLM_LOGGING_LEVEL", "INFO"))
