@@ -119,3 +119,21 @@ def test_two_reader_processes():
         for p in procs:
             p.join(10.0)
         w.close()
+
+
+def test_unlinked_ring_keeps_working_and_leaves_no_file():
+    import os
+    w = shm_ring.RingWriter(readers=1, slots=4, slot_bytes=64)
+    r = w.reader(0)
+    path = w.region.path
+    try:
+        r.attach()
+        assert os.path.exists(path)
+        w.unlink()
+        assert not os.path.exists(path)
+        w.put(("still", "works"))
+        assert r.get(timeout=1.0) == ("still", "works")
+        with pytest.raises(FileNotFoundError):
+            w.reader(0).attach()          # nobody can attach after the name is gone
+    finally:
+        r.close(), w.close()

@@ -121,6 +121,8 @@ def _worker_main(rank: int, world: int, port: int, cfg: EngineConfig, cmd_q, out
                                        device=str(engine.device))
             engine.attach_kv_connector(connector,
                                        recv_timeout_s=float(kvc.get("recv_timeout_s", 30.0)))
+        if hasattr(cmd_q, "attach"):
+            cmd_q.attach()            # the front end drops the ring's file name after READY
         out_q.put(("READY", rank, engine.runner.num_blocks))
         pending: list[_Cmd] = []
         stop = False
@@ -247,6 +249,8 @@ class MultiprocExecutor:
                 ready += 1
             elif msg[0] == "FAILURE":
                 self._fail(f"worker {msg[1]} failed during start-up:\n{msg[2]}")
+        for ring in self.rings or ():
+            ring.unlink()             # every reader is attached: no file outlives the processes
 
     # -- plumbing ------------------------------------------------------------------
     def _get(self, timeout: float):

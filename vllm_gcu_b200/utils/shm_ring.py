@@ -99,6 +99,16 @@ class _Region:
         self._anchor = ctypes.c_char.from_buffer(self.map)
         self.base = ctypes.addressof(self._anchor)
 
+    def unlink(self) -> None:
+        """Removes the backing file's name; existing mappings stay valid.  Called once every
+        reader has attached, so that no file is left behind however the processes end."""
+        if self.owner:
+            try:
+                os.unlink(self.path)
+            except FileNotFoundError:
+                pass
+            self.owner = False
+
     def close(self) -> None:
         self.base = None          # the native calls answer a null base with an error code
         if self.map is not None:
@@ -133,6 +143,8 @@ class RingWriter:
         size = (size + mmap.PAGESIZE - 1) // mmap.PAGESIZE * mmap.PAGESIZE
         path = f"/dev/shm/b200_ring_{os.getpid()}_{_counter}_{time.monotonic_ns() & 0xffffff:x}"
         self.region = _Region(path, size, create=True)
+        import atexit
+        atexit.register(self.region.close)        # normal interpreter exit before unlink()
         rc = lib.b200_ring_init(self.region.base, size, slots, slot_bytes, readers)
         if rc != OK:
             self.region.close()
@@ -158,6 +170,10 @@ class RingWriter:
             raise TimeoutError("a reader of the command ring stopped taking messages")
         if rc != OK:
             raise RuntimeError(f"ring write failed ({rc})")
+
+    def unlink(self) -> None:
+        """To be called when all readers have attached (they cannot attach afterwards)."""
+        self.region.unlink()
 
     def backlog(self, index: int) -> int:
         if self.region.base is None:
@@ -191,6 +207,10 @@ class RingReader:
 
     def __setstate__(self, st):
         self.__init__(st["path"], st["index"], st["slot_bytes"])
+
+    def attach(self) -> None:
+        """Maps the region now (readers otherwise attach on first use)."""
+        self._attach()
 
     def _attach(self):
         if self._region is None:
