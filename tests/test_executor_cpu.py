@@ -521,3 +521,41 @@ def test_disaggregated_prefill_between_two_tensor_parallel_instances():
     finally:
         pre.shutdown()
         dec.shutdown()
+
+
+def _front_end_that_gets_killed(q):
+    ex = MultiprocExecutor(_cfg(2))
+    q.put([p.pid for p in ex.procs])
+    import time
+    time.sleep(600)
+
+
+@pytest.mark.timeout(300)
+def test_workers_exit_when_the_front_end_is_killed():
+    """A front end that dies without shutting down (SIGKILL) must not leave its workers
+    running: they notice the missing parent at their next loop iteration and exit."""
+    import multiprocessing as mp
+    import signal
+    import time
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    front = ctx.Process(target=_front_end_that_gets_killed, args=(q,))
+    front.start()
+    pids = q.get(timeout=240)
+    os.kill(front.pid, signal.SIGKILL)
+    front.join(10)
+
+    def alive(pid):
+        try:
+            os.kill(pid, 0)
+        except ProcessLookupError:
+            return False
+        try:                                    # a zombie waiting for its new parent counts as gone
+            with open(f"/proc/{pid}/stat") as f:
+                return f.read().split(") ")[-1].split()[0] != "Z"
+        except OSError:
+            return False
+    deadline = time.monotonic() + 30
+    while time.monotonic() < deadline and any(alive(p) for p in pids):
+        time.sleep(0.2)
+    assert not any(alive(p) for p in pids)

@@ -68,8 +68,9 @@ def _rank_address(addr: str, rank: int) -> str:
 
 
 def _worker_main(rank: int, world: int, port: int, cfg: EngineConfig, cmd_q, out_q, hb,
-                 backend: Optional[str]) -> None:
-    """Entry point of a worker process."""
+                 backend: Optional[str], parent_pid: int = 0) -> None:
+    """Entry point of a worker process.  ``parent_pid``: the front end; a worker that finds
+    itself re-parented (the front end was killed) exits instead of holding its GPU."""
     fired = {"v": False}
 
     def _on_signal(signum, frame):
@@ -128,6 +129,8 @@ def _worker_main(rank: int, world: int, port: int, cfg: EngineConfig, cmd_q, out
         stop = False
         while not stop:
             hb.value = time.monotonic()
+            if parent_pid and os.getppid() != parent_pid:
+                os._exit(0)                   # the front end is gone
             # 1) agree on the commands applied before this step
             # every rank takes what has arrived (a shared-memory ring is bounded: a rank that
             # left commands in it would hold up the writer), the lead decides how many apply
@@ -230,7 +233,7 @@ class MultiprocExecutor:
         port = _free_port()
         self.procs = [ctx.Process(target=_worker_main, daemon=True,
                                   args=(r, self.world, port, cfg, self.cmd_qs[r], self.out_q,
-                                        self.hbs[r], backend))
+                                        self.hbs[r], backend, os.getpid()))
                       for r in range(self.world)]
         for p in self.procs:
             p.start()

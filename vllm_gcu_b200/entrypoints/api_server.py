@@ -671,7 +671,10 @@ def main() -> None:
         m.split("=", 1) for m in args.lora_modules),
         mm_processor=default_processor(args.model if _os.path.isdir(args.model) else None,
                                        inner, tok))
-    uvicorn.run(app, host=args.host, port=args.port, log_level="warning")
+    try:
+        uvicorn.run(app, host=args.host, port=args.port, log_level="warning")
+    finally:
+        engine.shutdown()          # worker processes / the engine thread end with the server
 
 
 if __name__ == "__main__":
