@@ -130,6 +130,11 @@ async def run(args):
     dataset = load_dataset_requests(args, rng) \
         if getattr(args, "dataset_name", "random") != "random" else None
     async with aiohttp.ClientSession(timeout=timeout) as session:
+        bases = [u[:u.index("/v1/")] for u in urls]
+        if getattr(args, "profile", False):        # the servers' profiler brackets the run
+            for b in bases:
+                async with session.post(b + "/start_profile") as r:
+                    await r.read()
         t_start = time.perf_counter()
         for i in range(args.num_prompts):
             n_in = rng.randint(*args.input_len_range)
@@ -156,7 +161,12 @@ async def run(args):
                 await asyncio.sleep(float(nprng.gamma(shape=args.burstiness, scale=theta)))
         await asyncio.gather(*tasks)
         dur = time.perf_counter() - t_start
-    res = summarise(results, dur, parse_goodput(args.goodput))
+        if getattr(args, "profile", False):
+            for b in bases:
+                async with session.post(b + "/stop_profile") as r:
+                    await r.read()
+    pcts = tuple(float(p) for p in str(getattr(args, "metric_percentiles", "99")).split(","))
+    res = summarise(results, dur, parse_goodput(args.goodput), pcts)
     print(json.dumps(res, indent=1))
     if args.output_json:
         with open(args.output_json, "w") as f:
@@ -175,7 +185,8 @@ def parse_goodput(pairs) -> dict:
     return out
 
 
-def summarise(results: list, dur: float, slo: dict | None = None) -> dict:
+def summarise(results: list, dur: float, slo: dict | None = None,
+              percentiles: tuple = (99,)) -> dict:
     """Throughput and latency statistics of finished requests; with ``slo`` also the rate of
     requests that met every objective."""
     ok = [r for r in results if r["ok"]]
@@ -191,8 +202,11 @@ def summarise(results: list, dur: float, slo: dict | None = None) -> dict:
     itl = np.array([x for r in ok for x in r["itl"]] or [0.0])
 
     def st(x):
-        return {"mean_ms": float(x.mean() * 1e3), "median_ms": float(np.median(x) * 1e3),
-                "p99_ms": float(np.percentile(x, 99) * 1e3)}
+        d = {"mean_ms": float(x.mean() * 1e3), "median_ms": float(np.median(x) * 1e3),
+             "std_ms": float(x.std() * 1e3)}
+        for p in percentiles:
+            d[f"p{p:g}_ms"] = float(np.percentile(x, p) * 1e3)
+        return d
 
     res = {"completed": len(ok), "failed": len(results) - len(ok), "duration_s": dur,
            "request_throughput": len(ok) / dur,
@@ -236,6 +250,10 @@ def main():
     ap.add_argument("--sonnet-input-len", type=int, default=550)
     ap.add_argument("--sonnet-output-len", type=int, default=150)
     ap.add_argument("--sonnet-prefix-len", type=int, default=200)
+    ap.add_argument("--metric-percentiles", default="99",
+                    help="comma-separated percentiles of every latency metric, e.g. 50,90,99")
+    ap.add_argument("--profile", action="store_true",
+                    help="call the servers' /start_profile and /stop_profile around the run")
     ap.add_argument("--strict-in-out-len", action="store_true",
                     help="accepted for compatibility: requests always run to max_tokens "
                          "(ignore_eos) and token-id prompts have exact lengths")

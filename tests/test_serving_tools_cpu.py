@@ -82,9 +82,11 @@ def test_serving_benchmark_over_two_servers(servers):
         backend="openai", num_prompts=6, request_rate=float("inf"), burstiness=1.0,
         input_len_range=[4, 12], output_len_range=[3, 6], vocab_size=32000, temperature=0.0,
         extra_body=None, seed=0, output_json=None, max_concurrency=3,
-        goodput=["ttft:60000", "tpot:60000"], dataset_name="random")
+        goodput=["ttft:60000", "tpot:60000"], dataset_name="random",
+        metric_percentiles="50,99", profile=False)
     res = asyncio.run(bs.run(args))
     assert res["completed"] == 6 and res["failed"] == 0
+    assert res["ttft"]["p50_ms"] <= res["ttft"]["p99_ms"] and "std_ms" in res["e2el"]
     assert res["good_requests"] == 6 and res["request_goodput"] > 0
     assert res["output_token_throughput"] > 0 and res["ttft"]["median_ms"] > 0
     strict = bs.summarise([{"ok": True, "ttft": 0.5, "e2e": 1.0, "itl": [0.1], "n_out": 6,
