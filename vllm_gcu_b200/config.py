@@ -108,6 +108,22 @@ class ModelConfig:
         kvh = max(1, self.num_key_value_heads // tp_size)
         return self.num_hidden_layers * 2 * kvh * self.head_dim * es
 
+    @property
+    def eos_token_ids(self) -> tuple[int, ...]:
+        """End-of-sequence ids of the checkpoint (``eos_token_id`` of ``config.json``, an int or
+        a list, plus those of ``generation_config.json``); empty for architecture presets."""
+        out: list[int] = []
+        for src in (self.extra.get("eos_token_id"), self.extra.get("generation_eos_token_id")):
+            for t in (src if isinstance(src, (list, tuple)) else [src]):
+                if isinstance(t, int) and t >= 0 and t not in out:
+                    out.append(t)
+        return tuple(out)
+
+    @property
+    def eos_token_id(self) -> Optional[int]:
+        ids = self.eos_token_ids
+        return ids[0] if ids else None
+
     # -- construction ----------------------------------------------------
     @classmethod
     def from_hf_dict(cls, d: dict, **overrides) -> "ModelConfig":
@@ -194,6 +210,13 @@ class ModelConfig:
         p = Path(path)
         d = json.loads((p / "config.json").read_text())
         cfg = cls.from_hf_dict(d, **overrides)
+        gpath = p / "generation_config.json"
+        if gpath.exists():
+            try:
+                cfg.extra["generation_eos_token_id"] = json.loads(gpath.read_text()).get(
+                    "eos_token_id")
+            except (OSError, ValueError):
+                pass
         qpath = p / "quantize_config.json"
         if cfg.quant_config is None and qpath.exists():
             cfg.quant_config = json.loads(qpath.read_text())

@@ -163,7 +163,19 @@ class LLMEngine:
                 and sampling_params.max_tokens != 1:
             import dataclasses
             sampling_params = dataclasses.replace(sampling_params, max_tokens=1, min_tokens=0)
-        req = Request(rid, list(prompt_token_ids), sampling_params or SamplingParams(),
+        sampling_params = sampling_params or SamplingParams()
+        if eos_token_id is None and not sampling_params.ignore_eos:
+            # the checkpoint's end-of-sequence ids stop a request like any stop token; the
+            # first one is also what a guided request emits once its pattern is complete
+            eos = self.cfg.model.eos_token_ids
+            if eos:
+                eos_token_id = eos[0]
+                more = tuple(t for t in eos[1:] if t not in sampling_params.stop_token_ids)
+                if more:
+                    import dataclasses
+                    sampling_params = dataclasses.replace(
+                        sampling_params, stop_token_ids=tuple(sampling_params.stop_token_ids) + more)
+        req = Request(rid, list(prompt_token_ids), sampling_params,
                       eos_token_id=eos_token_id, priority=priority, lora_id=lora_id)
         if multi_modal_data:
             prep = getattr(self.model, "prepare_request", None)
@@ -439,6 +451,26 @@ class LLMEngine:
         return vec
 
 
+def decode_text(tokenizer, token_ids) -> str:
+    """Output text without special tokens (the end-of-sequence marker that ended a request is
+    part of its token ids, not of its text)."""
+    try:
+        return tokenizer.decode(list(token_ids), skip_special_tokens=True)
+    except TypeError:                       # tokenizers without that option
+        return tokenizer.decode(list(token_ids))
+
+
+def chat_template_ids(tokenizer, messages) -> list[int]:
+    """Prompt ids of a conversation rendered with the tokenizer's chat template.  Depending on
+    the tokenizer library's version the call returns the ids or an encoding that holds them."""
+    out = tokenizer.apply_chat_template(list(messages), tokenize=True, add_generation_prompt=True)
+    if hasattr(out, "keys"):
+        out = out["input_ids"]
+    if out and isinstance(out[0], (list, tuple)):
+        out = out[0]
+    return [int(t) for t in out]
+
+
 class LLM:
     """Convenience wrapper mirroring the offline-inference entry point users of the
     reference call (``vllm.LLM``): build from a preset / HF config / checkpoint directory and
@@ -547,7 +579,7 @@ class LLM:
         if self.tokenizer is not None:
             for o in outs:
                 for c in o.outputs:
-                    c.text = self.tokenizer.decode(c.token_ids)
+                    c.text = decode_text(self.tokenizer, c.token_ids)
         return outs
 
     def chat(self, messages, sampling_params=None) -> list[RequestOutput]:
@@ -556,9 +588,7 @@ class LLM:
         if self.tokenizer is None or not hasattr(self.tokenizer, "apply_chat_template"):
             raise ValueError("chat() needs a tokenizer with a chat template")
         convs = messages if messages and isinstance(messages[0], list) else [messages]
-        prompts = [list(self.tokenizer.apply_chat_template(c, tokenize=True,
-                                                           add_generation_prompt=True))
-                   for c in convs]
+        prompts = [chat_template_ids(self.tokenizer, c) for c in convs]
         return self.generate(prompts, sampling_params)
 
     def set_vocabulary(self, vocab) -> None:

@@ -22,6 +22,7 @@ from typing import Any, Optional
 from ..config import (CacheConfig, EngineConfig, ModelConfig, ParallelConfig, SchedulerConfig,
                       SpeculativeConfig,
                       preset)
+from ..engine.llm import decode_text
 from ..engine.request import SamplingParams
 
 try:        # module level so that FastAPI can resolve the handler annotations
@@ -265,7 +266,7 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None,
         def chunk(idx: int, toks: list[int], finish: Optional[str]) -> dict:
             return {"id": rid, "object": "text_completion", "created": created,
                     "model": model_name,
-                    "choices": [{"index": idx, "text": tokenizer.decode(toks),
+                    "choices": [{"index": idx, "text": decode_text(tokenizer, toks),
                                  "token_ids": toks, "finish_reason": finish}]}
 
         if body.get("stream", False):
@@ -340,8 +341,8 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None,
         """Conversation -> prompt ids: the tokenizer's chat template when it has one, else a
         plain ``<role>: content`` transcript."""
         if hasattr(tokenizer, "apply_chat_template") and getattr(tokenizer, "chat_template", None):
-            return list(tokenizer.apply_chat_template(messages, tokenize=True,
-                                                      add_generation_prompt=True))
+            from ..engine.llm import chat_template_ids
+            return chat_template_ids(tokenizer, messages)
         text = "".join(f"{m.get('role', 'user')}: {m.get('content', '')}\n" for m in messages)
         return list(tokenizer.encode(text + "assistant: "))
 
@@ -390,7 +391,7 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None,
                     toks = out.outputs[0].token_ids
                     new, sent = toks[sent:], len(toks)
                     state["tokens_out"] += len(new)
-                    ch = {"index": 0, "delta": {"content": tokenizer.decode(new)},
+                    ch = {"index": 0, "delta": {"content": decode_text(tokenizer, new)},
                           "finish_reason": out.outputs[0].finish_reason}
                     yield "data: " + json.dumps({**base, "object": "chat.completion.chunk",
                                                  "choices": [ch]}) + "\n\n"
@@ -403,7 +404,7 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None,
         toks = last.outputs[0].token_ids
         state["tokens_out"] += len(toks)
         choice = {"index": 0, "finish_reason": last.outputs[0].finish_reason,
-                  "message": {"role": "assistant", "content": tokenizer.decode(toks)}}
+                  "message": {"role": "assistant", "content": decode_text(tokenizer, toks)}}
         usage = {"prompt_tokens": len(ids), "completion_tokens": len(toks),
                  "total_tokens": len(ids) + len(toks)}
         return {**base, "object": "chat.completion", "choices": [choice], "usage": usage}
