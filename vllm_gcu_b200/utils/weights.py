@@ -51,7 +51,7 @@ def write_safetensors(path: str, tensors: dict[str, torch.Tensor], metadata: dic
     blobs = []
     for name, t in tensors.items():
         t = t.detach().cpu().contiguous()
-        raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""
         header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape),
                         "data_offsets": [off, off + len(raw)]}
         off += len(raw)
