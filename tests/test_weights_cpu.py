@@ -93,3 +93,32 @@ def test_kv_cache_scales_from_checkpoint_and_parameter_file(tmp_path):
         "1": {"k_scale": 0.5, "v_scale": 0.25}}}}}))
     assert llm.engine.model.load_kv_cache_scales(str(path)) == 1
     assert (l1.k_scale, l1.v_scale) == (0.5, 0.25)
+
+
+def test_sharded_safetensors_and_pickled_checkpoints_load(tmp_path):
+    """Checkpoint directories in the layouts found in the wild: several safetensors shards with
+    an index and tied embeddings, and a pickled ``pytorch_model.bin``."""
+    import pytest
+    tr = pytest.importorskip("transformers")
+    from vllm_gcu_b200.engine.llm import LLM
+    from vllm_gcu_b200.engine.request import SamplingParams
+    hc = tr.LlamaConfig(vocab_size=320, hidden_size=64, intermediate_size=128,
+                        num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,
+                        max_position_embeddings=128, rms_norm_eps=1e-6, tie_word_embeddings=True)
+    torch.manual_seed(0)
+    hf = tr.LlamaForCausalLM(hc).eval().float()
+    ids = [5, 17, 99, 3, 250, 42, 7]
+    want = hf.generate(torch.tensor([ids]), attention_mask=torch.ones(1, len(ids), dtype=torch.long),
+                       max_new_tokens=5, do_sample=False, pad_token_id=0)[0, len(ids):].tolist()
+    a, b = tmp_path / "shards", tmp_path / "pickled"
+    hf.save_pretrained(str(a), safe_serialization=True, max_shard_size="100KB")
+    assert (a / "model.safetensors.index.json").exists()
+    b.mkdir()
+    (b / "config.json").write_text((a / "config.json").read_text())
+    torch.save(hf.state_dict(), str(b / "pytorch_model.bin"))
+    for d in (a, b):
+        llm = LLM(str(d), device="cpu", max_num_seqs=4, max_num_batched_tokens=64,
+                  max_model_len=128, num_gpu_blocks=64, dtype="float32")
+        got = llm.generate([ids], SamplingParams(max_tokens=5, temperature=0.0,
+                                                 ignore_eos=True))[0].outputs[0].token_ids
+        assert got == want

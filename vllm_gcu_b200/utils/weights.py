@@ -74,7 +74,19 @@ def iter_safetensors(model_dir: str) -> Iterator[tuple[str, torch.Tensor]]:
     else:
         files = sorted(p.name for p in d.glob("*.safetensors"))
     if not files:
-        raise FileNotFoundError(f"no .safetensors files in {model_dir}")
+        # older checkpoints: pickled state dicts (``pytorch_model.bin``, sharded or not)
+        bin_index = d / "pytorch_model.bin.index.json"
+        if bin_index.exists():
+            bins = sorted(set(json.loads(bin_index.read_text())["weight_map"].values()))
+        else:
+            bins = sorted(p.name for p in list(d.glob("pytorch_model*.bin")) + list(d.glob("*.pt")))
+        if not bins:
+            raise FileNotFoundError(f"no .safetensors or .bin files in {model_dir}")
+        for fn in bins:
+            state = torch.load(str(d / fn), map_location="cpu", weights_only=True)
+            yield from state.items()
+            del state
+        return
     for fn in files:
         yield from read_safetensors(str(d / fn))
 
