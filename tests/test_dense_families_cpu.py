@@ -259,3 +259,34 @@ def test_qwen2_embedding_checkpoint_matches_transformers():
     assert len(out[1].outputs[0].token_ids) == 1
     e = torch.nn.functional.normalize(out[1].embedding, dim=-1)
     assert torch.allclose(e, got[1], atol=1e-5)
+
+
+@pytest.mark.parametrize("rope", [
+    {"rope_type": "llama3", "rope_theta": 10000.0, "factor": 8.0, "low_freq_factor": 1.0,
+     "high_freq_factor": 4.0, "original_max_position_embeddings": 64},
+    {"rope_type": "yarn", "rope_theta": 10000.0, "factor": 8.0,
+     "original_max_position_embeddings": 64},
+    {"rope_type": "linear", "rope_theta": 10000.0, "factor": 2.0},
+    {"rope_type": "default", "rope_theta": 50000.0}], ids=lambda r: r["rope_type"])
+def test_rope_scaling_variants_match_transformers(rope):
+    """Llama-3.1 frequency scaling, YaRN, linear scaling and a plain base, on a prompt longer
+    than the original context."""
+    cfg = tr.LlamaConfig(vocab_size=320, hidden_size=64, intermediate_size=128,
+                         num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                         max_position_embeddings=512, rms_norm_eps=1e-6,
+                         tie_word_embeddings=False, rope_parameters=rope)
+    torch.manual_seed(0)
+    hf = tr.LlamaForCausalLM(cfg).eval().float()
+    d = cfg.to_dict()
+    d["architectures"] = ["LlamaForCausalLM"]
+    mc = ModelConfig.from_hf_dict(d, dtype=torch.float32)
+    llm = LLM(mc, device="cpu", max_num_seqs=2, max_num_batched_tokens=512, max_model_len=512,
+              num_gpu_blocks=64, load_format="none")
+    llm.engine.model.load_weights(hf.state_dict().items())
+    ids = torch.randint(0, 320, (200,), generator=torch.Generator().manual_seed(1)).tolist()
+    llm.engine.runner.keep_logits = True
+    llm.generate([ids], SamplingParams(max_tokens=1, temperature=0.0, ignore_eos=True))
+    got = llm.engine.runner.last_logits[0]
+    with torch.inference_mode():
+        want = hf(input_ids=torch.tensor([ids])).logits[0, -1]
+    assert torch.allclose(got, want, atol=1e-4), (got - want).abs().max()
