@@ -290,3 +290,43 @@ def test_rope_scaling_variants_match_transformers(rope):
     with torch.inference_mode():
         want = hf(input_ids=torch.tensor([ids])).logits[0, -1]
     assert torch.allclose(got, want, atol=1e-4), (got - want).abs().max()
+
+
+@pytest.mark.parametrize("kind", ["qwen2_mixed", "qwen2_off", "mistral"])
+def test_sliding_window_layers_follow_the_checkpoint_config(kind):
+    """Qwen2 checkpoints switch the window on per layer (``use_sliding_window`` with
+    ``max_window_layers``) or carry a value that is not in force; Mistral windows every layer.
+    Logits of a prompt longer than the window against transformers."""
+    common = dict(vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=3,
+                  num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=256,
+                  rms_norm_eps=1e-6, tie_word_embeddings=False)
+    torch.manual_seed(0)
+    if kind == "mistral":
+        cfg = tr.MistralConfig(sliding_window=16, **common)
+        hf, arch, want_windows = tr.MistralForCausalLM(cfg), "MistralForCausalLM", [16, 16, 16]
+        d = cfg.to_dict()
+    else:
+        on = kind == "qwen2_mixed"
+        cfg = tr.Qwen2Config(use_sliding_window=on, sliding_window=16, max_window_layers=1,
+                             **common)
+        hf, arch = tr.Qwen2ForCausalLM(cfg), "Qwen2ForCausalLM"
+        want_windows = [0, 16, 16] if on else [0, 0, 0]
+        d = cfg.to_dict()
+        if not on:      # as such checkpoints are on disk: the value is there, the switch is off
+            d.update(sliding_window=16, use_sliding_window=False)
+            d.pop("layer_types", None)
+    hf = hf.eval().float()
+    d["architectures"] = [arch]
+    mc = ModelConfig.from_hf_dict(d, dtype=torch.float32)
+    assert [mc.window_for_layer(i) for i in range(3)] == want_windows
+    llm = LLM(mc, device="cpu", max_num_seqs=2, max_num_batched_tokens=32, max_model_len=256,
+              num_gpu_blocks=64, load_format="none")
+    llm.engine.model.load_weights(hf.state_dict().items())
+    ids = torch.randint(0, 320, (70,), generator=torch.Generator().manual_seed(1)).tolist()
+    llm.engine.runner.keep_logits = True
+    out = llm.generate([ids], SamplingParams(max_tokens=3, temperature=0.0, ignore_eos=True))[0]
+    with torch.inference_mode():
+        t = torch.tensor([ids])
+        want = hf.generate(t, attention_mask=torch.ones_like(t), max_new_tokens=3,
+                           do_sample=False, pad_token_id=0)[0, len(ids):].tolist()
+    assert out.outputs[0].token_ids == want

@@ -108,6 +108,24 @@ class ModelConfig:
         kvh = max(1, self.num_key_value_heads // tp_size)
         return self.num_hidden_layers * 2 * kvh * self.head_dim * es
 
+    def window_for_layer(self, layer_idx: int) -> int:
+        """Sliding-window length of one layer (0 = full attention).  Checkpoints name the
+        layers that use the window by ``layer_types``, or by ``use_sliding_window`` with
+        ``max_window_layers`` (Qwen2: the layers from that index on); a ``sliding_window`` value
+        next to ``use_sliding_window: false`` is not in force."""
+        w = int(self.sliding_window or 0)
+        if w <= 0:
+            return 0
+        types = self.extra.get("layer_types")
+        if isinstance(types, (list, tuple)) and layer_idx < len(types):
+            return w if "sliding" in str(types[layer_idx]) else 0
+        use = self.extra.get("use_sliding_window")
+        if use is False:
+            return 0
+        if use is True and self.extra.get("max_window_layers") is not None:
+            return w if layer_idx >= int(self.extra["max_window_layers"]) else 0
+        return w
+
     @property
     def eos_token_ids(self) -> tuple[int, ...]:
         """End-of-sequence ids of the checkpoint (``eos_token_id`` of ``config.json``, an int or

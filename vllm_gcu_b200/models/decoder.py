@@ -148,7 +148,8 @@ class GQAAttention(nn.Module):
             kn = RMSNorm(D, cfg.rms_norm_eps, cfg.dtype, device)
         self.q_norm, self.k_norm = qn, kn
         self.attn = PagedAttention(self.qkv_proj.num_heads, self.qkv_proj.num_kv_heads, D,
-                                   D ** -0.5, rotary, qn, kn, cfg.sliding_window, alibi)
+                                   D ** -0.5, rotary, qn, kn, cfg.window_for_layer(layer_idx),
+                                   alibi)
 
     def before_o_proj(self, x: torch.Tensor, kv_cache: torch.Tensor, md: AttentionMetadata,
                       x_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
