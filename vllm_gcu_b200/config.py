@@ -97,8 +97,14 @@ class ModelConfig:
         return int(d * self.partial_rotary_factor)
 
     def is_moe_layer(self, layer_idx: int) -> bool:
-        return (self.is_moe and layer_idx >= self.first_k_dense_replace
-                and layer_idx % self.moe_layer_freq == 0)
+        if not self.is_moe or layer_idx < self.first_k_dense_replace \
+                or layer_idx % self.moe_layer_freq != 0:
+            return False
+        # Qwen MoE configs: dense layers listed by index, experts on every n-th layer
+        if layer_idx in (self.extra.get("mlp_only_layers") or ()):
+            return False
+        step = int(self.extra.get("decoder_sparse_step") or 1)
+        return (layer_idx + 1) % step == 0
 
     def kv_bytes_per_token(self, tp_size: int = 1) -> int:
         es = 1 if self.kv_cache_dtype.startswith("fp8") or self.kv_cache_dtype == "int8" else \
@@ -206,6 +212,12 @@ class ModelConfig:
             kw.setdefault("partial_rotary_factor", d.get("partial_rotary_factor", 0.5))
         if "Deepseek" in arch:
             kw.setdefault("rope_is_neox", False)
+        if arch in ("DeepseekV3ForCausalLM", "DeepSeekMTPModel") or \
+                d.get("model_type") == "deepseek_v3":
+            # configs written by newer libraries leave the V3 routing to the model type:
+            # sigmoid scores, group-limited top-k with a learnt selection bias
+            kw.setdefault("scoring_func", "sigmoid")
+            kw.setdefault("topk_method", "noaux_tc")
         if arch.startswith("ChatGLM"):
             kw.setdefault("rope_is_neox", False)
             kw.setdefault("partial_rotary_factor", 0.5)

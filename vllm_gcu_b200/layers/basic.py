@@ -97,9 +97,17 @@ def build_cos_sin_cache(rot_dim: int, max_pos: int, base: float,
                     / max(high - low, 1e-3)).clamp(0, 1)
             mask = 1.0 - ramp
             inv_freq = inv_freq / factor * (1 - mask) + inv_freq * mask
-            if kind == "deepseek_yarn":
-                mscale = (_yarn_mscale(factor, rope_scaling.get("mscale", 1.0))
-                          / _yarn_mscale(factor, rope_scaling.get("mscale_all_dim", 0.0)))
+            # magnitude of cos / sin: an explicit attention_factor, else the ratio of the two
+            # mscale terms when the checkpoint gives both (DeepSeek-V2 / V3 configs, whose type
+            # is plain "yarn"; the mscale_all_dim part goes into the softmax scale of the
+            # attention layer instead), else the plain YaRN factor
+            af = rope_scaling.get("attention_factor")
+            ms, ms_all = rope_scaling.get("mscale"), rope_scaling.get("mscale_all_dim")
+            if af is not None:
+                mscale = float(af)
+            elif kind == "deepseek_yarn" or (ms and ms_all):
+                mscale = (_yarn_mscale(factor, float(ms if ms is not None else 1.0))
+                          / _yarn_mscale(factor, float(ms_all or 0.0)))
             else:
                 mscale = _yarn_mscale(factor)
     t = torch.arange(max_pos, dtype=torch.float32) / t_scale

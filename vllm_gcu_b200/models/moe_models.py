@@ -25,6 +25,8 @@ _QEXPERT_RE = re.compile(r"^(model\.layers\.\d+\.)(mlp|block_sparse_moe)\.expert
                          r"out_scales|input_scale|in_scales)$")
 _WHICH = {"gate_proj": "gate", "up_proj": "up", "down_proj": "down",
           "w1": "gate", "w3": "up", "w2": "down"}
+_FUSED_EXPERTS_RE = re.compile(
+    r"^model\.layers\.(\d+)\.(?:mlp|block_sparse_moe)\.experts\.(gate_up_proj|down_proj)$")
 
 
 class MoeDecoderLM(DecoderLM):
@@ -62,6 +64,21 @@ class MoeDecoderLM(DecoderLM):
                 return True
             moe = self.layers[str(layer)].mlp.experts
             moe.load_expert_weight(int(m.group(3)), _WHICH[m.group(4)], tensor)
+            return True
+        mf = _FUSED_EXPERTS_RE.match(name)
+        if mf is not None:
+            # all experts of a layer in one tensor (checkpoints written by newer transformers):
+            # gate_up_proj [E, 2I, H] with the gate rows first, down_proj [E, H, I]
+            layer = int(mf.group(1))
+            if self.start_layer <= layer < self.end_layer:
+                moe = self.layers[str(layer)].mlp.experts
+                for e in range(tensor.shape[0]):
+                    if mf.group(2) == "gate_up_proj":
+                        half = tensor.shape[1] // 2
+                        moe.load_expert_weight(e, "gate", tensor[e, :half])
+                        moe.load_expert_weight(e, "up", tensor[e, half:])
+                    else:
+                        moe.load_expert_weight(e, "down", tensor[e])
             return True
         if ".block_sparse_moe.gate." in name:
             return self._load_renamed(name.replace(".block_sparse_moe.gate.", ".mlp.gate."),
