@@ -330,3 +330,51 @@ def test_sliding_window_layers_follow_the_checkpoint_config(kind):
         want = hf.generate(t, attention_mask=torch.ones_like(t), max_new_tokens=3,
                            do_sample=False, pad_token_id=0)[0, len(ids):].tolist()
     assert out.outputs[0].token_ids == want
+
+
+def _random_norms_and_biases(hf):
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if "norm" in n:
+                p.copy_(torch.randn_like(p) * 0.2 + 1.0)
+            elif n.endswith("bias"):
+                p.copy_(torch.randn_like(p) * 0.2)
+    return hf.eval().float()
+
+
+@pytest.mark.parametrize("kind", ["qwen3", "qwen2", "glm4", "mistral", "llama_biases",
+                                  "llama_gelu_mha"])
+def test_families_with_their_own_config_classes(kind):
+    """Each family built from its HuggingFace config class with non-default options: explicit
+    head sizes, tied embeddings, biases on q / k / v only (Qwen2, GLM-4) or on all four
+    attention projections and the MLP (Llama ``attention_bias`` / ``mlp_bias``), GELU."""
+    common = dict(vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                  num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=256,
+                  rms_norm_eps=1e-6)
+    torch.manual_seed(0)
+    if kind == "qwen3":
+        c, cls, arch = tr.Qwen3Config(**common, head_dim=32, tie_word_embeddings=True), \
+            tr.Qwen3ForCausalLM, "Qwen3ForCausalLM"
+    elif kind == "qwen2":
+        c, cls, arch = tr.Qwen2Config(**common, tie_word_embeddings=False), \
+            tr.Qwen2ForCausalLM, "Qwen2ForCausalLM"
+    elif kind == "glm4":
+        c, cls, arch = tr.Glm4Config(**common, head_dim=16, tie_word_embeddings=False,
+                                     attention_bias=True, pad_token_id=0), \
+            tr.Glm4ForCausalLM, "Glm4ForCausalLM"
+    elif kind == "mistral":
+        c, cls, arch = tr.MistralConfig(**common, head_dim=32, tie_word_embeddings=False,
+                                        sliding_window=None), \
+            tr.MistralForCausalLM, "MistralForCausalLM"
+    elif kind == "llama_biases":
+        c, cls, arch = tr.LlamaConfig(**common, tie_word_embeddings=False, attention_bias=True,
+                                      mlp_bias=True), tr.LlamaForCausalLM, "LlamaForCausalLM"
+    else:
+        c, cls, arch = tr.LlamaConfig(**{**common, "num_key_value_heads": 4},
+                                      tie_word_embeddings=False, hidden_act="gelu"), \
+            tr.LlamaForCausalLM, "LlamaForCausalLM"
+    hf = _random_norms_and_biases(cls(c))
+    got, tok = _engine_logits(arch, c.to_dict(), hf.state_dict().items())
+    want = _hf_last_logits(hf)
+    assert torch.allclose(got, want, atol=2e-5), (got - want).abs().max()
+    assert tok == int(want.argmax())

@@ -118,6 +118,13 @@ class DenseMLP(nn.Module):
         return self.down_proj(h, **kw)
 
 
+_QKV_BIAS_ONLY = frozenset({
+    "Qwen2ForCausalLM", "Qwen2Model", "Qwen2EmbeddingModel", "Qwen2VLForConditionalGeneration",
+    "Qwen2_5_VLForConditionalGeneration", "Glm4ForCausalLM", "Glm4vForConditionalGeneration",
+    "ChatGLMModel", "ChatGLMForConditionalGeneration", "GotOcr2ForConditionalGeneration",
+    "GOTQwenForCausalLM", "InternVLChatModel", "InternVLForConditionalGeneration"})
+
+
 class GQAAttention(nn.Module):
     def __init__(self, cfg: ModelConfig, layer_idx: int, device, prefix: str):
         super().__init__()
@@ -126,8 +133,13 @@ class GQAAttention(nn.Module):
             cfg.hidden_size, D, cfg.num_attention_heads, cfg.num_key_value_heads,
             bias=cfg.attention_bias, dtype=cfg.dtype, device=device,
             quant_method=get_linear_method(cfg, prefix + ".qkv_proj"), prefix=prefix + ".qkv_proj")
+        # ``attention_bias`` of Llama / Qwen3 / Gemma / InternLM2 configs covers the output
+        # projection too; Qwen2 and the GLM families have biases on q / k / v only
+        o_bias = cfg.extra.get("o_proj_bias")
+        if o_bias is None:
+            o_bias = bool(cfg.attention_bias) and cfg.architecture not in _QKV_BIAS_ONLY
         self.o_proj = RowParallelLinear(
-            cfg.num_attention_heads * D, cfg.hidden_size, bias=False, dtype=cfg.dtype,
+            cfg.num_attention_heads * D, cfg.hidden_size, bias=bool(o_bias), dtype=cfg.dtype,
             device=device, quant_method=get_linear_method(cfg, prefix + ".o_proj"),
             prefix=prefix + ".o_proj")
         alibi = None
