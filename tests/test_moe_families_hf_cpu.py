@@ -75,3 +75,17 @@ def test_deepseek_v3(rope):
                 t.copy_(torch.randn_like(t) * 0.1)
     mc = _check(hf, c.to_dict(), "DeepseekV3ForCausalLM", prompt_len=150)
     assert mc.scoring_func == "sigmoid" and mc.topk_method == "noaux_tc"
+
+
+@pytest.mark.parametrize("q_lora,scale", [(None, 1.0), (None, 16.0), (48, 1.0)])
+def test_deepseek_v2(q_lora, scale):
+    """DeepSeek-V2 / V2-Lite: plain softmax top-k routing with a scaling factor, two shared
+    experts, and (Lite) no query down-projection: ``q_proj`` is a layer of its own."""
+    torch.manual_seed(0)
+    c = tr.DeepseekV2Config(**COMMON, num_hidden_layers=3, num_key_value_heads=4,
+                            moe_intermediate_size=32, n_routed_experts=8, n_shared_experts=2,
+                            num_experts_per_tok=2, first_k_dense_replace=1, kv_lora_rank=32,
+                            q_lora_rank=q_lora, qk_nope_head_dim=16, qk_rope_head_dim=8,
+                            v_head_dim=16, topk_method="greedy", n_group=1, topk_group=1,
+                            routed_scaling_factor=scale, norm_topk_prob=False)
+    _check(tr.DeepseekV2ForCausalLM(c).eval().float(), c.to_dict(), "DeepseekV2ForCausalLM")

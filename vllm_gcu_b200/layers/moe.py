@@ -60,12 +60,16 @@ def select_experts(router_logits: torch.Tensor, cfg: ModelConfig,
         return w, ids
     grouped = cfg.n_group > 1 or cfg.scoring_func == "sigmoid" or bias is not None
     scale = cfg.routed_scaling_factor if grouped else 1.0
+    # plain softmax top-k with a scaling factor (DeepSeek-V2 "greedy" routing): the router
+    # paths below fold the factor in only for the grouped form
+    post = float(cfg.routed_scaling_factor) if not grouped else 1.0
     if ops.use_native(router_logits):
-        return C.moe_topk(router_logits, k, cfg.norm_topk_prob, cfg.n_group, cfg.topk_group, bias,
-                          cfg.scoring_func == "sigmoid", scale,
-                          log2phy=eplb.log2phy if eplb is not None else None,
-                          replica_count=eplb.replica_count if eplb is not None else None,
-                          load=eplb.load if eplb is not None else None)
+        w, ids = C.moe_topk(router_logits, k, cfg.norm_topk_prob, cfg.n_group, cfg.topk_group,
+                            bias, cfg.scoring_func == "sigmoid", scale,
+                            log2phy=eplb.log2phy if eplb is not None else None,
+                            replica_count=eplb.replica_count if eplb is not None else None,
+                            load=eplb.load if eplb is not None else None)
+        return (w * post if post != 1.0 else w), ids
     if grouped:
         w, ids = ref.grouped_topk(router_logits, k, cfg.norm_topk_prob, max(cfg.n_group, 1),
                                   max(cfg.topk_group, 1), bias, cfg.scoring_func, scale)
@@ -73,7 +77,7 @@ def select_experts(router_logits: torch.Tensor, cfg: ModelConfig,
         w, ids = ref.topk_softmax(router_logits, k, cfg.norm_topk_prob)
     if eplb is not None:
         ids = ref.eplb_map_to_physical(ids, eplb.log2phy, eplb.replica_count, eplb.load)
-    return w, ids
+    return (w * post if post != 1.0 else w), ids
 
 
 class FusedMoE(nn.Module):

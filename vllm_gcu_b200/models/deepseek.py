@@ -238,6 +238,11 @@ class DeepseekV3ForCausalLM(MoeDecoderLM):
                 owner, _, pname = name.replace(".kv_a_proj_with_mqa.",
                                                ".qkv_a_proj.").rpartition(".")
                 return owner, pname, 1
+        elif ".self_attn.q_proj." in name or ".self_attn.kv_a_proj_with_mqa." in name:
+            # no query down-projection (DeepSeek-V2-Lite): q_proj is a layer of its own here,
+            # not a shard of a fused qkv projection
+            owner, _, pname = name.rpartition(".")
+            return owner, pname, None
         return super().map_weight_name(name)
 
     def load_special(self, name, tensor, owners) -> bool:
