@@ -118,3 +118,49 @@ def test_server_on_the_checkpoint(ckpt):
         asyncio.run(run())
     finally:
         eng.shutdown()
+
+
+def test_stop_strings_offline_and_through_the_server(ckpt):
+    """``stop`` strings end a request as soon as its text contains one: the text is cut in front
+    of it (or behind it with ``include_stop_str_in_output``) and no further tokens are
+    generated; the server honours the OpenAI ``stop`` field the same way."""
+    from vllm_gcu_b200 import SamplingParams
+    httpx = pytest.importorskip("httpx")
+    llm = _llm(ckpt)
+    base = SamplingParams(max_tokens=30, temperature=0.0, ignore_eos=True)
+    full = llm.generate("the quick brown fox", base)[0].outputs[0]
+    assert len(full.token_ids) == 30 and len(full.text) > 8
+    needle = full.text[5:8]                              # a piece that will appear
+    where = full.text.find(needle)
+    import dataclasses
+    cut = llm.generate("the quick brown fox", dataclasses.replace(base, stop=(needle,)))[0]
+    c = cut.outputs[0]
+    assert c.text == full.text[:where] and c.finish_reason == "stop"
+    assert len(c.token_ids) < 30 and c.token_ids == full.token_ids[:len(c.token_ids)]
+    keep = llm.generate("the quick brown fox", dataclasses.replace(
+        base, stop=(needle, "never-there"), include_stop_str_in_output=True))[0].outputs[0]
+    assert keep.text == full.text[:where + len(needle)]
+    miss = llm.generate("the quick brown fox", dataclasses.replace(base, stop=("@@@@",)))[0]
+    assert miss.outputs[0].text == full.text and miss.outputs[0].finish_reason == "length"
+    # the server: same cut, and the engine is free again right away
+    from vllm_gcu_b200.engine.async_llm import AsyncLLM
+    from vllm_gcu_b200.entrypoints.api_server import build_app, load_tokenizer
+    eng = AsyncLLM(llm.engine.cfg)
+    app = build_app(eng, load_tokenizer(ckpt, 0), "tiny")
+
+    async def run():
+        transport = httpx.ASGITransport(app=app)
+        async with httpx.AsyncClient(transport=transport, base_url="http://t") as cl:
+            body = {"prompt": "the quick brown fox", "max_tokens": 30, "temperature": 0.0,
+                    "ignore_eos": True, "stop": [needle]}
+            r = (await cl.post("/v1/completions", json=body)).json()["choices"][0]
+            assert r["text"] == full.text[:where] and r["finish_reason"] == "stop"
+            assert len(r["token_ids"]) < 30
+            r2 = (await cl.post("/v1/completions", json={**body, "stop": needle,
+                                                         "include_stop_str_in_output": True}))
+            assert r2.json()["choices"][0]["text"] == full.text[:where + len(needle)]
+    import asyncio as _a
+    try:
+        _a.run(run())
+    finally:
+        eng.shutdown()

@@ -316,6 +316,7 @@ class LLMEngine:
             draft = {rid: d for rid, d in draft.items()
                      if rid in reqs and not reqs[rid].sampling_params.needs_host_history}
         outs = self.scheduler.update_from_output(so, toks, draft, lp)
+        outs = self._apply_stop_strings(so, outs)
         hid = handle.extra.get("hidden")
         if hid is not None:
             so_req = {s.req.request_id: s.req for s in so.scheduled}
@@ -334,6 +335,47 @@ class LLMEngine:
                 if s.will_sample and not r.finished and r.request_id in self.scheduler.requests:
                     room = r.sampling_params.max_tokens - len(r.output_token_ids) - 1
                     r.spec_token_ids = self.proposer.propose(r.all_token_ids)[:max(0, room)]
+        return outs
+
+    detokenizer = None     # callable(token ids) -> text; set by LLM / the server for stop strings
+
+    def _apply_stop_strings(self, so: SchedulerOutput, outs: list[RequestOutput]
+                            ) -> list[RequestOutput]:
+        """Requests whose sampling parameters name stop strings end as soon as their output
+        text contains one; the text is cut in front of it (``include_stop_str_in_output``
+        keeps it) and the tokens after the match are dropped from the count that matters to the
+        caller only in the text: token ids are returned as generated."""
+        if self.detokenizer is None:
+            return outs
+        by_id = None
+        for s in so.scheduled:
+            r = s.req
+            sp = r.sampling_params
+            if not sp.stop or not s.will_sample or not r.output_token_ids:
+                continue
+            text = self.detokenizer(r.output_token_ids)
+            cut = min((text.find(t) + (len(t) if sp.include_stop_str_in_output else 0)
+                       for t in sp.stop if t and t in text), default=-1)
+            if cut < 0:
+                continue
+            if by_id is None:
+                by_id = {o.request_id: i for i, o in enumerate(outs)}
+            final = None
+            if r.finished:                       # ended on its own in this very step
+                i = by_id.get(r.request_id)
+                final = outs[i] if i is not None else None
+            else:
+                final = self.scheduler.stop_request(r.request_id)
+                if final is not None:
+                    self.runner.release([r.request_id])
+                    i = by_id.get(r.request_id)
+                    if i is not None:
+                        outs[i] = final
+                    else:
+                        outs.append(final)
+            if final is not None:
+                final.outputs[0].text = text[:cut]
+                final.outputs[0].finish_reason = "stop"
         return outs
 
     def step(self) -> list[RequestOutput]:
@@ -547,6 +589,9 @@ class LLM:
                 self.tokenizer = None
         elif tokenizer is not None:
             self.tokenizer = tokenizer
+        if self.tokenizer is not None:
+            tok_ = self.tokenizer
+            self.engine.detokenizer = lambda ids: decode_text(tok_, ids)
         # images given as PIL objects (``multi_modal_data={"image": ...}``) go through the
         # checkpoint's HuggingFace processor when it has one (entrypoints/multimodal.py)
         self.mm_processor = mm_processor
@@ -579,7 +624,8 @@ class LLM:
         if self.tokenizer is not None:
             for o in outs:
                 for c in o.outputs:
-                    c.text = decode_text(self.tokenizer, c.token_ids)
+                    if not c.text:           # a stop string already cut this one's text
+                        c.text = decode_text(self.tokenizer, c.token_ids)
         return outs
 
     def chat(self, messages, sampling_params=None) -> list[RequestOutput]:

@@ -23,6 +23,9 @@ class SamplingParams:
     seed: Optional[int] = None
     ignore_eos: bool = False
     stop_token_ids: tuple[int, ...] = ()
+    # stop strings: generation ends when the output text contains one (needs an engine that can
+    # detokenise: LLM with a tokenizer, or the server); the text is cut in front of it
+    stop: tuple[str, ...] = ()
     include_stop_str_in_output: bool = False
     logprobs: Optional[int] = None
     prompt_logprobs: Optional[int] = None

@@ -108,6 +108,18 @@ class Scheduler:
         items.insert(pos, req)
         self.waiting = deque(items)
 
+    def stop_request(self, request_id: str) -> Optional[RequestOutput]:
+        """Ends a running request as stopped (a stop string appeared in its text) and returns
+        its final output; None when the request is unknown or already over."""
+        req = self.requests.get(request_id)
+        if req is None or req.finished:
+            return None
+        req.status = RequestStatus.FINISHED_STOPPED
+        import time as _t
+        req.finish_time = _t.monotonic()
+        self._free(req)
+        return self._make_output(req, 0)
+
     def abort_request(self, request_id: str) -> None:
         req = self.requests.get(request_id)
         if req is None or req.finished:

@@ -67,7 +67,9 @@ def sampling_from_body(body: dict, default_max: int = 16) -> SamplingParams:
         frequency_penalty=float(body.get("frequency_penalty", 0.0)),
         repetition_penalty=float(body.get("repetition_penalty", 1.0)),
         seed=body.get("seed"), ignore_eos=bool(body.get("ignore_eos", False)),
-        stop_token_ids=stop_ids, logprobs=body.get("logprobs"),
+        stop_token_ids=stop_ids, stop=_stop_strings(body),
+        include_stop_str_in_output=bool(body.get("include_stop_str_in_output", False)),
+        logprobs=body.get("logprobs"),
         prompt_logprobs=body.get("prompt_logprobs"),
         allowed_token_ids=(tuple(int(t) for t in body["allowed_token_ids"])
                            if body.get("allowed_token_ids") else None),
@@ -75,6 +77,20 @@ def sampling_from_body(body: dict, default_max: int = 16) -> SamplingParams:
                        if body.get("guided_choice_token_ids") else None),
         guided_regex=_guided_pattern(body), guided_json=_guided_schema(body),
         extra_args=extra)
+
+
+def _stop_strings(body: dict) -> tuple:
+    stop = body.get("stop")
+    if not stop:
+        return ()
+    return (str(stop),) if isinstance(stop, str) else tuple(str(t) for t in stop if t)
+
+
+def cut_at_stop(text: str, sp: SamplingParams) -> tuple[str, bool]:
+    """``text`` up to its first stop string (kept with ``include_stop_str_in_output``)."""
+    cut = min((text.find(t) + (len(t) if sp.include_stop_str_in_output else 0)
+               for t in sp.stop if t in text), default=-1)
+    return (text[:cut], True) if cut >= 0 else (text, False)
 
 
 def _guided_pattern(body: dict) -> Optional[str]:
@@ -107,6 +123,23 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None,
         raise RuntimeError("the API server needs the fastapi package")
     app = FastAPI()
     state = {"profiler": None, "requests": 0, "tokens_out": 0, "t0": time.time()}
+
+    inner_engine = getattr(engine, "engine", None)
+    if inner_engine is not None and hasattr(inner_engine, "_apply_stop_strings"):
+        # stop strings end a request inside the engine; engines in worker processes generate
+        # on and the text is cut here
+        inner_engine.detokenizer = lambda ids: decode_text(tokenizer, ids)
+
+    def text_of(comp, sp_: SamplingParams) -> tuple[str, Optional[str]]:
+        """(text, finish reason) of a finished completion with the stop strings applied."""
+        if comp.text is not None:
+            return comp.text, comp.finish_reason
+        text = decode_text(tokenizer, comp.token_ids)
+        if sp_.stop:
+            text, hit = cut_at_stop(text, sp_)
+            if hit:
+                return text, "stop"
+        return text, comp.finish_reason
 
     def to_ids(p) -> list[int]:
         if isinstance(p, str):
@@ -318,6 +351,7 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None,
                 comp = last.outputs[0]
                 state["tokens_out"] += len(comp.token_ids)
                 c = chunk(idx * n + j, comp.token_ids, comp.finish_reason)["choices"][0]
+                c["text"], c["finish_reason"] = text_of(comp, sp)
                 c["prompt_tokens"] = len(ids) if j == 0 else 0
                 c["kv_transfer_params"] = getattr(last, "kv_transfer_params", None)
                 out.append(with_logprobs(c, comp))
@@ -403,8 +437,9 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None,
             last = out
         toks = last.outputs[0].token_ids
         state["tokens_out"] += len(toks)
-        choice = {"index": 0, "finish_reason": last.outputs[0].finish_reason,
-                  "message": {"role": "assistant", "content": decode_text(tokenizer, toks)}}
+        content, reason = text_of(last.outputs[0], sp)
+        choice = {"index": 0, "finish_reason": reason,
+                  "message": {"role": "assistant", "content": content}}
         usage = {"prompt_tokens": len(ids), "completion_tokens": len(toks),
                  "total_tokens": len(ids) + len(toks)}
         return {**base, "object": "chat.completion", "choices": [choice], "usage": usage}
