@@ -164,3 +164,26 @@ def test_stop_strings_offline_and_through_the_server(ckpt):
         _a.run(run())
     finally:
         eng.shutdown()
+
+
+def test_server_uses_the_checkpoints_sampling_defaults(ckpt, tmp_path):
+    """``generation_config.json`` of the checkpoint: its temperature / top-k / top-p /
+    repetition penalty apply to requests that do not set them."""
+    import json
+    import os
+    import shutil
+    from vllm_gcu_b200.config import ModelConfig
+    from vllm_gcu_b200.entrypoints.api_server import sampling_from_body
+    d = str(tmp_path / "c")
+    shutil.copytree(ckpt, d)
+    with open(os.path.join(d, "generation_config.json"), "w") as f:
+        json.dump({"do_sample": True, "temperature": 0.7, "top_p": 0.8, "top_k": 20,
+                   "repetition_penalty": 1.05, "eos_token_id": [2, 5]}, f)
+    mc = ModelConfig.from_pretrained(d)
+    gd = mc.extra["generation_defaults"]
+    assert gd == {"temperature": 0.7, "top_p": 0.8, "top_k": 20, "repetition_penalty": 1.05}
+    assert mc.eos_token_ids == (2, 5)
+    sp = sampling_from_body({"max_tokens": 4}, defaults=gd)
+    assert (sp.temperature, sp.top_p, sp.top_k, sp.repetition_penalty) == (0.7, 0.8, 20, 1.05)
+    sp = sampling_from_body({"max_tokens": 4, "temperature": 0.0, "top_k": 0}, defaults=gd)
+    assert sp.temperature == 0.0 and sp.top_k == 0 and sp.top_p == 0.8

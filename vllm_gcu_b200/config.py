@@ -243,8 +243,13 @@ class ModelConfig:
         gpath = p / "generation_config.json"
         if gpath.exists():
             try:
-                cfg.extra["generation_eos_token_id"] = json.loads(gpath.read_text()).get(
-                    "eos_token_id")
+                gen = json.loads(gpath.read_text())
+                cfg.extra["generation_eos_token_id"] = gen.get("eos_token_id")
+                # sampling defaults the checkpoint recommends; the server applies them to
+                # requests that leave the field out
+                cfg.extra["generation_defaults"] = {
+                    k: gen[k] for k in ("temperature", "top_p", "top_k", "repetition_penalty")
+                    if gen.get(k) is not None and gen.get("do_sample", True)}
             except (OSError, ValueError):
                 pass
         qpath = p / "quantize_config.json"

@@ -55,7 +55,12 @@ def load_tokenizer(path: Optional[str], vocab_size: int):
     return ByteTokenizer(vocab_size)
 
 
-def sampling_from_body(body: dict, default_max: int = 16) -> SamplingParams:
+def sampling_from_body(body: dict, default_max: int = 16,
+                       defaults: Optional[dict] = None) -> SamplingParams:
+    """``defaults``: the checkpoint's recommended sampling values (``generation_config.json``),
+    used for the fields a request leaves out."""
+    if defaults:
+        body = {**defaults, **body}
     extra = dict(body.get("extra_args") or {})
     stop_ids = tuple(body.get("stop_token_ids") or ())
     return SamplingParams(
@@ -129,6 +134,11 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None,
         # stop strings end a request inside the engine; engines in worker processes generate
         # on and the text is cut here
         inner_engine.detokenizer = lambda ids: decode_text(tokenizer, ids)
+
+    model_cfg = getattr(getattr(inner_engine, "cfg", None) or getattr(engine, "cfg", None),
+                        "model", None)
+    gen_defaults = dict(getattr(model_cfg, "extra", {}).get("generation_defaults") or {}) \
+        if model_cfg is not None else {}
 
     def text_of(comp, sp_: SamplingParams) -> tuple[str, Optional[str]]:
         """(text, finish reason) of a finished completion with the stop strings applied."""
@@ -264,7 +274,7 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None,
         batch = prompt if (isinstance(prompt, list) and prompt and
                            isinstance(prompt[0], (list, str))) else [prompt]
         try:
-            sp = sampling_from_body(body)
+            sp = sampling_from_body(body, defaults=gen_defaults)
             if sp.guided_regex is not None or sp.guided_json is not None:
                 _ensure_vocabulary()
         except ValueError as e:
@@ -387,7 +397,8 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None,
         if not messages:
             return JSONResponse({"error": "messages is required"}, status_code=400)
         try:
-            sp = sampling_from_body(body, default_max=int(body.get("max_completion_tokens", 256)))
+            sp = sampling_from_body(body, default_max=int(body.get("max_completion_tokens", 256)),
+                                    defaults=gen_defaults)
             if sp.guided_regex is not None or sp.guided_json is not None:
                 _ensure_vocabulary()
         except ValueError as e:
