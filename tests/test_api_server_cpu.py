@@ -69,6 +69,9 @@ def test_completions_and_streaming():
             assert r.status_code == 200 and len(r.json()["choices"][0]["token_ids"]) == 2
             bad = await c.post("/v1/chat/completions", json={"max_tokens": 2})
             assert bad.status_code == 400
+            bad = await c.post("/v1/completions", content=b"{not json",
+                               headers={"Content-Type": "application/json"})
+            assert bad.status_code == 400 and "JSON" in bad.json()["error"]
             # n / best_of: seeded samples, the best n by cumulative log-probability; logprobs
             many = {"prompt": [1, 2, 3, 4], "max_tokens": 4, "temperature": 1.0, "seed": 3,
                     "ignore_eos": True, "n": 2, "best_of": 4, "logprobs": 1}

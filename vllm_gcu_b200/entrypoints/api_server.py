@@ -127,6 +127,12 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None,
     if FastAPI is None:
         raise RuntimeError("the API server needs the fastapi package")
     app = FastAPI()
+
+    @app.exception_handler(json.JSONDecodeError)
+    async def _bad_json(request: Request, exc: json.JSONDecodeError):
+        return JSONResponse({"error": f"the request body is not valid JSON: {exc}"},
+                            status_code=400)
+
     state = {"profiler": None, "requests": 0, "tokens_out": 0, "t0": time.time()}
 
     inner_engine = getattr(engine, "engine", None)
