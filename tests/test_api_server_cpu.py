@@ -69,6 +69,19 @@ def test_completions_and_streaming():
             assert r.status_code == 200 and len(r.json()["choices"][0]["token_ids"]) == 2
             bad = await c.post("/v1/chat/completions", json={"max_tokens": 2})
             assert bad.status_code == 400
+            # requests that must be refused before they reach the engine (an id outside the
+            # vocabulary would index past the embedding table)
+            for body_, word in (({"prompt": [1, 999999], "max_tokens": 2}, "vocabulary"),
+                                ({"prompt": [1, -4], "max_tokens": 2}, "vocabulary"),
+                                ({"prompt": [1, 2], "max_tokens": 0}, "max_tokens"),
+                                ({"prompt": [1, 2], "max_tokens": 2, "logprobs": 1000}, "logprobs"),
+                                ({"prompt": [1, 2], "max_tokens": 2, "guided_regex": "([a-z"},
+                                 "]"),
+                                ({"prompt": [1, 2], "max_tokens": 2, "temperature": "hot"},
+                                 "float")):
+                r = await c.post("/v1/completions", json=body_)
+                assert r.status_code == 400 and word in r.json()["error"], (body_, r.text)
+            assert (await c.get("/health")).json()["status"] == "ok"
             bad = await c.post("/v1/completions", content=b"{not json",
                                headers={"Content-Type": "application/json"})
             assert bad.status_code == 400 and "JSON" in bad.json()["error"]

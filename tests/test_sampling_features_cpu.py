@@ -177,3 +177,16 @@ def test_seeded_sampling_depends_on_the_request_only():
     different = llm.generate([p], SamplingParams(max_tokens=10, temperature=0.9, top_p=0.95,
                                                  top_k=50, seed=12, ignore_eos=True))
     assert different[0].outputs[0].token_ids != alone
+
+
+def test_token_ids_outside_the_vocabulary_are_refused():
+    import pytest
+    llm = _llm()
+    sp = SamplingParams(max_tokens=2, temperature=0.0, ignore_eos=True)
+    for bad in ([1, 2, 32000], [5, -1]):
+        with pytest.raises(ValueError, match="vocabulary"):
+            llm.engine.add_request(bad, sp)
+    with pytest.raises(ValueError, match="max_tokens"):
+        llm.engine.add_request([1, 2], SamplingParams(max_tokens=0))
+    out = llm.generate([[1, 2, 31999]], sp)[0]            # the engine is unharmed
+    assert len(out.outputs[0].token_ids) == 2

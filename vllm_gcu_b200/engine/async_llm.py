@@ -73,7 +73,7 @@ class AsyncLLM:
                 if ent is not None:
                     ent[0].call_soon_threadsafe(ent[1].put_nowait, e)
 
-    def validate_prompt(self, prompt_token_ids: Sequence[int]) -> None:
+    def validate_prompt(self, prompt_token_ids: Sequence[int], multimodal: bool = False) -> None:
         """Raises ValueError for a prompt the scheduler would refuse (empty, or longer than
         the model length); callable from any thread."""
         n = len(prompt_token_ids)
@@ -82,6 +82,9 @@ class AsyncLLM:
         limit = self.engine.cfg.scheduler.max_model_len
         if n >= limit:
             raise ValueError(f"prompt of {n} tokens exceeds max_model_len {limit}")
+        from .llm import check_token_ids
+        check_token_ids(prompt_token_ids, self.engine.cfg.model.vocab_size,
+                        allow_placeholders=multimodal)
 
     async def generate_stream(self, prompt_token_ids: Sequence[int],
                               sampling_params: Optional[SamplingParams] = None,

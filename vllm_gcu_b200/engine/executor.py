@@ -323,6 +323,11 @@ class MultiprocExecutor:
         if request_id is None:
             request_id = f"req-{self._ids}"
             self._ids += 1
+        from .llm import check_token_ids
+        check_token_ids(prompt_token_ids, self.cfg.model.vocab_size,
+                        allow_placeholders=bool(multi_modal_data))
+        if sampling_params is not None and sampling_params.max_tokens < 1:
+            raise ValueError("max_tokens must be at least 1")
         cmd = _Cmd("add", (request_id, list(prompt_token_ids),
                            sampling_params or SamplingParams(), priority, lora_id,
                            multi_modal_data, kv_transfer_params))
@@ -450,7 +455,7 @@ class AsyncMultiprocExecutor(MultiprocExecutor):
         self._pump = threading.Thread(target=run, daemon=True)
         self._pump.start()
 
-    def validate_prompt(self, prompt_token_ids: Sequence[int]) -> None:
+    def validate_prompt(self, prompt_token_ids: Sequence[int], multimodal: bool = False) -> None:
         """Raises ValueError for a prompt the workers' scheduler would refuse."""
         n = len(prompt_token_ids)
         if n == 0:
@@ -458,6 +463,9 @@ class AsyncMultiprocExecutor(MultiprocExecutor):
         limit = self.cfg.scheduler.max_model_len
         if n >= limit:
             raise ValueError(f"prompt of {n} tokens exceeds max_model_len {limit}")
+        from .llm import check_token_ids
+        check_token_ids(prompt_token_ids, self.cfg.model.vocab_size,
+                        allow_placeholders=multimodal)
 
     async def generate_stream(self, prompt_token_ids: Sequence[int],
                               sampling_params: Optional[SamplingParams] = None,

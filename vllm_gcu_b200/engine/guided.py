@@ -496,6 +496,15 @@ def json_schema_to_regex(schema, depth: int = 0) -> str:
     raise ValueError(f"unsupported schema: {schema!r}")
 
 
+def check_guided(guided_regex=None, guided_json=None) -> None:
+    """Raises ValueError (``RegexSyntaxError``) for a pattern or schema the guide cannot be
+    built from; cheap, so that a server can refuse the request before it reaches the engine."""
+    if guided_json is not None:
+        guided_regex = json_schema_to_regex(guided_json)
+    if guided_regex is not None:
+        _Parser(guided_regex).parse()
+
+
 def vocabulary_of(tokenizer, vocab_size: int) -> list:
     """Token texts of a tokenizer, index = token id (None where a token cannot be used as
     text: specials, ids past the tokenizer's table, pieces that are not valid UTF-8 alone)."""

@@ -159,6 +159,10 @@ class LLMEngine:
         (``{"pixel_values": [n_patches, C*Tp*P*P], "image_grid_thw": [n_images, 3]}``); the
         prompt must already contain one placeholder token per merged patch."""
         rid = request_id if request_id is not None else f"req-{next(self._ids)}"
+        check_token_ids(prompt_token_ids, self.cfg.model.vocab_size,
+                        allow_placeholders=bool(multi_modal_data))
+        if sampling_params is not None and sampling_params.max_tokens < 1:
+            raise ValueError("max_tokens must be at least 1")
         if sampling_params is not None and sampling_params.pooling \
                 and sampling_params.max_tokens != 1:
             import dataclasses
@@ -491,6 +495,18 @@ class LLMEngine:
         if normalize:
             vec = torch.nn.functional.normalize(vec, dim=-1)
         return vec
+
+
+def check_token_ids(prompt_token_ids, vocab_size: int, allow_placeholders: bool = False) -> None:
+    """Raises ValueError for a token id outside the vocabulary: such an id would index past the
+    embedding table.  Prompts with multimodal data may carry placeholder ids beyond the text
+    vocabulary (their rows are replaced by the vision embeddings), negative ids never."""
+    if len(prompt_token_ids) == 0:
+        return
+    lo, hi = min(prompt_token_ids), max(prompt_token_ids)
+    if lo < 0 or (hi >= vocab_size and not allow_placeholders):
+        bad = lo if lo < 0 else hi
+        raise ValueError(f"token id {bad} is outside the vocabulary of {vocab_size} entries")
 
 
 def decode_text(tokenizer, token_ids) -> str:

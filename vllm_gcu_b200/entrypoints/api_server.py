@@ -62,6 +62,11 @@ def sampling_from_body(body: dict, default_max: int = 16,
     if defaults:
         body = {**defaults, **body}
     extra = dict(body.get("extra_args") or {})
+    if int(body.get("max_tokens", default_max)) < 1:
+        raise ValueError("max_tokens must be at least 1")
+    lp = body.get("logprobs")
+    if lp is not None and not isinstance(lp, bool) and not 0 <= int(lp) <= 20:
+        raise ValueError("logprobs must be between 0 and 20")
     stop_ids = tuple(body.get("stop_token_ids") or ())
     return SamplingParams(
         max_tokens=int(body.get("max_tokens", default_max)),
@@ -282,6 +287,8 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None,
         try:
             sp = sampling_from_body(body, defaults=gen_defaults)
             if sp.guided_regex is not None or sp.guided_json is not None:
+                from ..engine.guided import check_guided
+                check_guided(sp.guided_regex, sp.guided_json)
                 _ensure_vocabulary()
         except ValueError as e:
             return JSONResponse({"error": str(e)}, status_code=400)
@@ -406,6 +413,8 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None,
             sp = sampling_from_body(body, default_max=int(body.get("max_completion_tokens", 256)),
                                     defaults=gen_defaults)
             if sp.guided_regex is not None or sp.guided_json is not None:
+                from ..engine.guided import check_guided
+                check_guided(sp.guided_regex, sp.guided_json)
                 _ensure_vocabulary()
         except ValueError as e:
             return JSONResponse({"error": str(e)}, status_code=400)
@@ -421,7 +430,7 @@ def build_app(engine: Any, tokenizer: Any, model_name: str, pooler: Any = None,
             else:
                 ids = render_chat([{**m, "content": "".join(p.get("text", "") for p in m["content"])}
                                    if isinstance(m.get("content"), list) else m for m in messages])
-            engine.validate_prompt(ids)
+            engine.validate_prompt(ids, multimodal=bool(images))
         except (ValueError, KeyError, OSError) as e:
             return JSONResponse({"error": str(e)}, status_code=400)
         rid = "chatcmpl-" + uuid.uuid4().hex[:16]
