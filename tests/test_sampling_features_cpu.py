@@ -190,3 +190,15 @@ def test_token_ids_outside_the_vocabulary_are_refused():
         llm.engine.add_request([1, 2], SamplingParams(max_tokens=0))
     out = llm.generate([[1, 2, 31999]], sp)[0]            # the engine is unharmed
     assert len(out.outputs[0].token_ids) == 2
+
+
+def test_mask_ids_and_adapters_are_checked_at_admission():
+    import pytest
+    llm = _llm()
+    for sp in (SamplingParams(max_tokens=2, allowed_token_ids=(5, 40000)),
+               SamplingParams(max_tokens=2, guided_choice=((1, 2), (3, -7)))):
+        with pytest.raises(ValueError, match="token ids"):
+            llm.engine.add_request([1, 2, 3], sp)
+    with pytest.raises(ValueError, match="LoRA"):
+        llm.engine.add_request([1, 2, 3], SamplingParams(max_tokens=2), lora_id=3)
+    assert not llm.engine.has_unfinished()

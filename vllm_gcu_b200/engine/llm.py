@@ -163,6 +163,18 @@ class LLMEngine:
                         allow_placeholders=bool(multi_modal_data))
         if sampling_params is not None and sampling_params.max_tokens < 1:
             raise ValueError("max_tokens must be at least 1")
+        if sampling_params is not None and sampling_params.constrained:
+            # these ids index the logits when the mask is built
+            V = self.cfg.model.vocab_size
+            ids_ = list(sampling_params.allowed_token_ids or ())
+            for c_ in sampling_params.guided_choice or ():
+                ids_ += list(c_)
+            if ids_ and (min(ids_) < 0 or max(ids_) >= V):
+                raise ValueError(f"allowed / choice token ids must lie in [0, {V})")
+        if lora_id is not None and lora_id >= 0:
+            mgr = self.runner.lora
+            if mgr is None or lora_id not in mgr.slots:
+                raise ValueError(f"LoRA adapter {lora_id} is not loaded")
         if sampling_params is not None and sampling_params.pooling \
                 and sampling_params.max_tokens != 1:
             import dataclasses
