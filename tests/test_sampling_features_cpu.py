@@ -202,3 +202,23 @@ def test_mask_ids_and_adapters_are_checked_at_admission():
     with pytest.raises(ValueError, match="LoRA"):
         llm.engine.add_request([1, 2, 3], SamplingParams(max_tokens=2), lora_id=3)
     assert not llm.engine.has_unfinished()
+
+
+def test_out_of_range_sampling_values_are_normalised():
+    llm = _llm()
+    p = _prompt(9, 1)
+    ref_ = llm.generate([p], SamplingParams(max_tokens=4, temperature=0.8, seed=1,
+                                            ignore_eos=True))[0].outputs[0].token_ids
+    wild = llm.generate([p], SamplingParams(max_tokens=4, temperature=0.8, seed=1, top_k=10 ** 9,
+                                            top_p=7.0, ignore_eos=True))[0].outputs[0].token_ids
+    off = llm.generate([p], SamplingParams(max_tokens=4, temperature=0.8, seed=1, top_k=-1,
+                                           top_p=1.0, ignore_eos=True))[0].outputs[0].token_ids
+    assert ref_ == wild == off
+    cold = llm.generate([p], SamplingParams(max_tokens=4, temperature=float("nan"),
+                                            ignore_eos=True))[0].outputs[0].token_ids
+    greedy = llm.generate([p], SamplingParams(max_tokens=4, temperature=0.0,
+                                              ignore_eos=True))[0].outputs[0].token_ids
+    assert cold == greedy
+    tiny = llm.generate([p], SamplingParams(max_tokens=4, temperature=0.8, seed=1, top_p=0.0,
+                                            ignore_eos=True))[0].outputs[0].token_ids
+    assert len(tiny) == 4

@@ -163,6 +163,19 @@ class LLMEngine:
                         allow_placeholders=bool(multi_modal_data))
         if sampling_params is not None and sampling_params.max_tokens < 1:
             raise ValueError("max_tokens must be at least 1")
+        if sampling_params is not None:
+            sp0 = sampling_params
+            V0 = self.cfg.model.vocab_size
+            # values the sampling kernels are not written for: top_k beyond the vocabulary or
+            # negative (the "disabled" spelling of other servers), top_p outside (0, 1]
+            tk = 0 if sp0.top_k is None or sp0.top_k < 0 or sp0.top_k >= V0 else int(sp0.top_k)
+            tp_ = float(sp0.top_p) if sp0.top_p is not None else 1.0
+            tp_ = 1.0 if not (tp_ == tp_) or tp_ > 1.0 else max(tp_, 1e-6)
+            tmp = float(sp0.temperature) if sp0.temperature == sp0.temperature else 0.0
+            tmp = min(max(tmp, 0.0), 1e4)
+            if (tk, tp_, tmp) != (sp0.top_k, sp0.top_p, sp0.temperature):
+                import dataclasses
+                sampling_params = dataclasses.replace(sp0, top_k=tk, top_p=tp_, temperature=tmp)
         if sampling_params is not None and sampling_params.constrained:
             # these ids index the logits when the mask is built
             V = self.cfg.model.vocab_size
