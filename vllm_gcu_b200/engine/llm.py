@@ -176,6 +176,10 @@ class LLMEngine:
             if (tk, tp_, tmp) != (sp0.top_k, sp0.top_p, sp0.temperature):
                 import dataclasses
                 sampling_params = dataclasses.replace(sp0, top_k=tk, top_p=tp_, temperature=tmp)
+            for name_ in ("logprobs", "prompt_logprobs"):
+                k_ = getattr(sampling_params, name_)
+                if k_ is not None and not 0 <= int(k_) <= self.MAX_LOGPROBS:
+                    raise ValueError(f"{name_} must be between 0 and {self.MAX_LOGPROBS}")
         if sampling_params is not None and sampling_params.constrained:
             # these ids index the logits when the mask is built
             V = self.cfg.model.vocab_size
@@ -366,6 +370,7 @@ class LLMEngine:
                     r.spec_token_ids = self.proposer.propose(r.all_token_ids)[:max(0, room)]
         return outs
 
+    MAX_LOGPROBS = 20      # alternatives reported per position, as upstream servers limit it
     detokenizer = None     # callable(token ids) -> text; set by LLM / the server for stop strings
 
     def _apply_stop_strings(self, so: SchedulerOutput, outs: list[RequestOutput]
