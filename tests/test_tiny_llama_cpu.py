@@ -93,3 +93,18 @@ def test_step_times_are_logged_by_batch_size(monkeypatch, caplog):
     times = llm.engine._step_times
     assert sum(len(v) for v in times.values()) == llm.engine.stats["steps"] and 2 in times
     assert any("median step time by batch size" in r.getMessage() for r in caplog.records)
+
+
+def test_additional_config_reaches_the_model_options():
+    """Engine-level options named in ``additional_config`` (redundant experts, EP workspace
+    size, sequence parallelism ...) are visible to the layers that read them."""
+    from vllm_gcu_b200.engine.llm import LLM
+    llm = LLM("tiny-qwen3-moe", device="cpu", max_num_seqs=4, max_num_batched_tokens=64,
+              max_model_len=128, num_gpu_blocks=64, dtype="float32",
+              additional_config={"num_redundant_experts": 2, "ep_max_tokens": 512,
+                                 "cascade_min_tokens": 64})
+    extra = llm.engine.cfg.model.extra
+    assert extra["num_redundant_experts"] == 2 and extra["ep_max_tokens"] == 512
+    blk = llm.engine.model.layers["0"].mlp
+    assert blk.eplb is not None and blk.eplb.num_physical == 8 + 2
+    assert llm.engine.runner.cascade_min_tokens == 64

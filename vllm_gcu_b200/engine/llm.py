@@ -44,6 +44,19 @@ class LLMEngine:
         if pc.data_parallel_size > 1:
             # every replica holds different tokens: MoE layers dispatch (EP) or gather (ETP)
             cfg.model.extra.setdefault("dp_attention", True)
+        # engine-level options that the model's layers read from its configuration
+        # (``additional_config`` of the reference, vllm_gcu/gcu.py:184-354, and the parallel
+        # configuration's expert-placement fields)
+        for key in ("num_redundant_experts", "enable_eplb", "expert_map_path", "ep_max_tokens",
+                    "ep_backend", "ep_fp8_dispatch", "etp", "sequence_parallel", "q8_experts"):
+            if key in cfg.additional_config:
+                cfg.model.extra.setdefault(key, cfg.additional_config[key])
+        if pc.num_redundant_experts and pc.enable_expert_parallel:
+            cfg.model.extra.setdefault("num_redundant_experts", pc.num_redundant_experts)
+        if pc.enable_eplb:
+            cfg.model.extra.setdefault("enable_eplb", True)
+        if pc.enable_sequence_parallel:
+            cfg.model.extra.setdefault("sequence_parallel", True)
         self.model = build_model(cfg.model, self.device)
         if cfg.load_format == "dummy":
             self.model.init_random(cfg.seed)
