@@ -284,6 +284,13 @@ def test_server_on_a_data_parallel_expert_parallel_engine():
             one = (await c.post("/v1/completions", json={**body, "prompt": [1, 2, 3, 4]})).json()
             assert one["choices"][0]["token_ids"] == js["choices"][0]["token_ids"]
             assert (await c.get("/health")).json()["status"] == "ok"
+            # the workers report their scheduler counters to the front end
+            for _ in range(40):
+                m = (await c.get("/metrics")).text
+                if "vllm_b200_kv_cache_usage" in m:
+                    break
+                await asyncio.sleep(0.1)
+            assert "vllm_b200_num_running" in m and "vllm_b200_kv_cache_usage" in m
     try:
         asyncio.run(run())
     finally:

@@ -127,6 +127,7 @@ def _worker_main(rank: int, world: int, port: int, cfg: EngineConfig, cmd_q, out
         out_q.put(("READY", rank, engine.runner.num_blocks))
         pending: list[_Cmd] = []
         stop = False
+        last_stats, stepped = 0.0, False
         while not stop:
             hb.value = time.monotonic()
             if parent_pid and os.getppid() != parent_pid:
@@ -185,6 +186,7 @@ def _worker_main(rank: int, world: int, port: int, cfg: EngineConfig, cmd_q, out
             # 2) one engine step
             if engine.has_unfinished() or dp > 1:
                 outs = engine.step()          # dp > 1: every replica joins the exchange
+                stepped = stepped or engine.has_unfinished() or bool(outs)
                 if rank == lead and outs:
                     if connector is not None:
                         for o in outs:          # answers name the instance by its base address
@@ -193,6 +195,15 @@ def _worker_main(rank: int, world: int, port: int, cfg: EngineConfig, cmd_q, out
                                     o.kv_transfer_params,
                                     remote=_rank_address(o.kv_transfer_params["remote"], -rank))
                     out_q.put(("OUT", outs))
+            if rank == lead and stepped and time.monotonic() - last_stats > 0.5:
+                stepped = False
+                # the front end's /metrics: scheduler and engine counters of this replica
+                last_stats = time.monotonic()
+                st_ = dict(engine.scheduler.stats())
+                st_.update(engine.stats)
+                if engine.spec_metrics is not None:
+                    st_["spec_acceptance_rate"] = engine.spec_metrics.acceptance_rate
+                out_q.put(("STATS", rank, st_))
         out_q.put(("STOPPED", rank, None))
     except SystemExit:
         raise
@@ -241,6 +252,7 @@ class MultiprocExecutor:
         self._lock = threading.Lock()
         self._ids = 0
         self._replica_of: dict[str, int] = {}
+        self._replica_stats: dict[int, dict] = {}      # lead rank -> latest counters
         self._in_flight = [0] * self.dp
         ready = 0
         deadline = time.monotonic() + start_timeout_s
@@ -343,6 +355,20 @@ class MultiprocExecutor:
             self._send(d, cmd)
         return request_id
 
+    def stats(self) -> dict:
+        """Latest counters of the replicas (sums; cache usage and acceptance rate as means),
+        refreshed about twice a second while the workers step."""
+        out: dict = {}
+        reps = list(self._replica_stats.values())
+        for st_ in reps:
+            for k, v in st_.items():
+                if isinstance(v, (int, float)):
+                    out[k] = out.get(k, 0.0) + v
+        for k in ("kv_cache_usage", "spec_acceptance_rate"):
+            if k in out and reps:
+                out[k] /= len(reps)
+        return out
+
     def abort_request(self, request_id: str) -> None:
         self._broadcast(_Cmd("abort", request_id))
 
@@ -372,6 +398,8 @@ class MultiprocExecutor:
                                 self._in_flight[d] -= 1
             elif msg[0] == "FAILURE":
                 self._fail(f"worker {msg[1]} failed:\n{msg[2]}")
+            elif msg[0] == "STATS":
+                self._replica_stats[msg[1]] = msg[2]
             try:
                 msg = self.out_q.get_nowait()
             except queue.Empty:
