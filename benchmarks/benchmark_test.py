@@ -84,6 +84,9 @@ def main():
     ap.add_argument("--perf", action="store_true")
     ap.add_argument("--acc", action="store_true")
     ap.add_argument("--reference-file", default=None)
+    ap.add_argument("--dump-reference", default=None,
+                    help="write this run's greedy outputs as a reference file for --acc (e.g. "
+                         "from the unquantised model, to score a quantised or sharded one)")
     ap.add_argument("--save-output", default=None, help="CSV file for the metrics")
     ap.add_argument("--dtype", default=None)
     a = ap.parse_args()
@@ -91,8 +94,19 @@ def main():
               max_num_seqs=a.max_num_seqs, dtype=a.dtype,
               max_model_len=a.input_len + a.output_len + 16)
     res = {}
-    if a.perf or not a.acc:
+    if a.perf or not (a.acc or a.dump_reference):
         res.update(run_perf(llm, a)[0])
+    if a.dump_reference:
+        import torch
+        g = torch.Generator().manual_seed(0)
+        vocab = llm.engine.cfg.model.vocab_size
+        prompts = torch.randint(10, vocab, (a.num_prompts, a.input_len), generator=g).tolist()
+        outs = llm.generate(prompts, SamplingParams(max_tokens=a.output_len, temperature=0.0))
+        with open(a.dump_reference, "w") as f:
+            for p_, o in zip(prompts, outs):
+                f.write(json.dumps({"prompt_token_ids": p_,
+                                    "reference": o.outputs[0].token_ids}) + "\n")
+        res["reference_rows"] = len(prompts)
     if a.acc:
         assert a.reference_file, "--acc needs --reference-file"
         res.update(run_acc(llm, a)[0])

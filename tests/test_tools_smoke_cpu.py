@@ -35,6 +35,24 @@ CASES = {
 
 
 @pytest.mark.timeout(300)
+def test_accuracy_mode_scores_against_a_dumped_reference(tmp_path):
+    """``benchmark_test.py``: outputs dumped by one configuration are the ROUGE-L reference of
+    another (here the same one: score 1)."""
+    ref = str(tmp_path / "ref.jsonl")
+    common = ["--model", "tiny-llama", "--device", "cpu", "--input-len", "16", "--output-len",
+              "6", "--num-prompts", "3", "--dtype", "float32"]
+    tool = os.path.join(ROOT, "benchmarks", "benchmark_test.py")
+    r = subprocess.run([sys.executable, tool, *common, "--dump-reference", ref],
+                       capture_output=True, text=True, timeout=280, cwd=ROOT)
+    assert r.returncode == 0, r.stderr[-2000:]
+    r = subprocess.run([sys.executable, tool, *common, "--acc", "--reference-file", ref],
+                       capture_output=True, text=True, timeout=280, cwd=ROOT)
+    assert r.returncode == 0, r.stderr[-2000:]
+    out = json.loads(r.stdout[r.stdout.index("{"):])
+    assert out["rouge_l"] == 1.0 and out["samples"] == 3
+
+
+@pytest.mark.timeout(300)
 @pytest.mark.parametrize("name", sorted(CASES))
 def test_tool_runs(name):
     argv = CASES[name]
