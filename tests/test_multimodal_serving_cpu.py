@@ -198,3 +198,66 @@ def test_offline_prompt_with_a_pil_image():
         LLM(_llava_config(), device="cpu", max_num_seqs=4, max_num_batched_tokens=32,
             max_model_len=128, num_gpu_blocks=64).generate(
             [{"prompt": "x <image>", "multi_modal_data": {"image": img}}], sp)
+
+
+def test_checkpoint_directory_with_a_huggingface_processor(tmp_path):
+    """A LLaVA checkpoint directory as users have it (weights, tokenizer with an ``<image>``
+    token and a chat template, image processor): ``LLM(directory)`` finds the processor, a text
+    prompt with the placeholder and a PIL image gives the tokens of transformers' ``generate``
+    on the processor's own encoding, and chat messages with an image part are expanded."""
+    import numpy as np
+    tr = pytest.importorskip("transformers")
+    tokenizers = pytest.importorskip("tokenizers")
+    from PIL import Image
+    from tokenizers import Tokenizer, decoders, models, pre_tokenizers, trainers
+    tok = Tokenizer(models.BPE(unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False)
+    tok.decoder = decoders.ByteLevel()
+    tok.train_from_iterator(
+        ["describe the picture please", "what is in this image?"] * 20,
+        trainers.BpeTrainer(vocab_size=300,
+                            special_tokens=["<unk>", "<s>", "</s>", "<image>", "<pad>"],
+                            initial_alphabet=pre_tokenizers.ByteLevel.alphabet()))
+    fast = tr.PreTrainedTokenizerFast(tokenizer_object=tok, bos_token="<s>", eos_token="</s>",
+                                      unk_token="<unk>", pad_token="<pad>")
+    fast.chat_template = ("{% for m in messages %}{{ m['role'] }}: {% for p in m['content'] %}"
+                          "{% if p['type'] == 'image' %}<image>{% else %}{{ p['text'] }}"
+                          "{% endif %}{% endfor %}\n{% endfor %}assistant: ")
+    img_tok = fast.convert_tokens_to_ids("<image>")
+    proc = tr.LlavaProcessor(
+        image_processor=tr.CLIPImageProcessor(size={"shortest_edge": 28},
+                                              crop_size={"height": 28, "width": 28}),
+        tokenizer=fast, patch_size=14, vision_feature_select_strategy="default",
+        image_token="<image>", num_additional_image_tokens=1)
+    cfg = tr.LlavaConfig(
+        text_config=dict(model_type="llama", vocab_size=len(fast), hidden_size=64,
+                         intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, max_position_embeddings=256,
+                         tie_word_embeddings=False, rms_norm_eps=1e-6),
+        vision_config=dict(model_type="clip_vision_model", hidden_size=32, intermediate_size=64,
+                           num_hidden_layers=3, num_attention_heads=2, image_size=28,
+                           patch_size=14, hidden_act="quick_gelu", projection_dim=16),
+        image_token_index=img_tok, vision_feature_layer=-2,
+        vision_feature_select_strategy="default", image_seq_length=4)
+    torch.manual_seed(0)
+    hf = tr.LlavaForConditionalGeneration(cfg).eval().float()
+    d = str(tmp_path)
+    hf.save_pretrained(d, safe_serialization=True)
+    proc.save_pretrained(d)
+    llm = LLM(d, device="cpu", max_num_seqs=4, max_num_batched_tokens=64, max_model_len=128,
+              num_gpu_blocks=64, dtype="float32")
+    assert isinstance(llm.mm_processor, HFProcessorAdapter)
+    img = Image.fromarray(np.random.default_rng(0).integers(0, 255, (40, 52, 3), dtype=np.uint8))
+    text = "<image>\ndescribe the picture"
+    out = llm.generate([{"prompt": text, "multi_modal_data": {"image": img}}],
+                       SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True))[0]
+    enc = proc(text=[text], images=[img], return_tensors="pt")
+    with torch.inference_mode():
+        want = hf.generate(**enc, max_new_tokens=5, do_sample=False,
+                           pad_token_id=0)[0, enc["input_ids"].shape[1]:].tolist()
+    assert out.prompt_token_ids == enc["input_ids"][0].tolist()
+    assert out.outputs[0].token_ids == want
+    msgs, images = split_messages([{"role": "user", "content": [
+        {"type": "image", "image": img}, {"type": "text", "text": "what is in this image?"}]}])
+    ids, mm = llm.mm_processor(msgs, images)
+    assert ids.count(img_tok) == 4 and tuple(mm["pixel_values"].shape) == (1, 3, 28, 28)
