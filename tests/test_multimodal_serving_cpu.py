@@ -261,3 +261,64 @@ def test_checkpoint_directory_with_a_huggingface_processor(tmp_path):
         {"type": "image", "image": img}, {"type": "text", "text": "what is in this image?"}]}])
     ids, mm = llm.mm_processor(msgs, images)
     assert ids.count(img_tok) == 4 and tuple(mm["pixel_values"].shape) == (1, 3, 28, 28)
+
+
+def test_qwen2_vl_checkpoint_directory_with_its_processor(tmp_path):
+    """Qwen2-VL with the HuggingFace processor of its checkpoint directory: the processor
+    resizes and patchifies the image and expands the placeholder; the engine's tokens equal
+    transformers' ``generate`` on the same encoding (multimodal rotary positions included)."""
+    import numpy as np
+    tr = pytest.importorskip("transformers")
+    pytest.importorskip("tokenizers")
+    from PIL import Image
+    from tokenizers import Tokenizer, decoders, models, pre_tokenizers, trainers
+    tok = Tokenizer(models.BPE(unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False)
+    tok.decoder = decoders.ByteLevel()
+    sp_toks = ["<unk>", "<|endoftext|>", "<|vision_start|>", "<|vision_end|>", "<|image_pad|>",
+               "<|video_pad|>", "<|im_start|>", "<|im_end|>"]
+    tok.train_from_iterator(
+        ["describe the picture please", "what is in this image?"] * 20,
+        trainers.BpeTrainer(vocab_size=300, special_tokens=sp_toks,
+                            initial_alphabet=pre_tokenizers.ByteLevel.alphabet()))
+    fast = tr.PreTrainedTokenizerFast(tokenizer_object=tok, eos_token="<|endoftext|>",
+                                      unk_token="<unk>", pad_token="<|endoftext|>")
+    fast.chat_template = (
+        "{% for m in messages %}<|im_start|>{{ m['role'] }}\n{% for p in m['content'] %}"
+        "{% if p['type'] == 'image' %}<|vision_start|><|image_pad|><|vision_end|>{% else %}"
+        "{{ p['text'] }}{% endif %}{% endfor %}<|im_end|>\n{% endfor %}<|im_start|>assistant\n")
+    ids = {t: fast.convert_tokens_to_ids(t) for t in sp_toks}
+    ip = tr.Qwen2VLImageProcessor(min_pixels=28 * 28 * 4, max_pixels=28 * 28 * 16, patch_size=14,
+                                  merge_size=2, temporal_patch_size=2)
+    proc = tr.Qwen2VLProcessor(image_processor=ip, tokenizer=fast,
+                               video_processor=tr.Qwen2VLVideoProcessor(),
+                               chat_template=fast.chat_template)
+    text = dict(vocab_size=len(fast), hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=512,
+                rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
+                rope_scaling={"type": "mrope", "mrope_section": [2, 3, 3]})
+    vision = dict(depth=2, embed_dim=32, hidden_size=64, mlp_ratio=2, num_heads=2, in_channels=3,
+                  patch_size=14, spatial_merge_size=2, temporal_patch_size=2)
+    cfg = tr.Qwen2VLConfig(text_config=text, vision_config=vision,
+                           image_token_id=ids["<|image_pad|>"],
+                           video_token_id=ids["<|video_pad|>"],
+                           vision_start_token_id=ids["<|vision_start|>"],
+                           vision_end_token_id=ids["<|vision_end|>"])
+    torch.manual_seed(0)
+    hf = tr.Qwen2VLForConditionalGeneration(cfg).eval().float()
+    d = str(tmp_path)
+    hf.save_pretrained(d, safe_serialization=True)
+    proc.save_pretrained(d)
+    llm = LLM(d, device="cpu", max_num_seqs=4, max_num_batched_tokens=64, max_model_len=256,
+              num_gpu_blocks=64, dtype="float32")
+    assert isinstance(llm.mm_processor, HFProcessorAdapter)
+    img = Image.fromarray(np.random.default_rng(0).integers(0, 255, (60, 90, 3), dtype=np.uint8))
+    prompt = "<|vision_start|><|image_pad|><|vision_end|>describe the picture"
+    out = llm.generate([{"prompt": prompt, "multi_modal_data": {"image": img}}],
+                       SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True))[0]
+    enc = proc(text=[prompt], images=[img], return_tensors="pt")
+    with torch.inference_mode():
+        want = hf.generate(**enc, max_new_tokens=5, do_sample=False,
+                           pad_token_id=1)[0, enc["input_ids"].shape[1]:].tolist()
+    assert out.prompt_token_ids == enc["input_ids"][0].tolist()
+    assert out.outputs[0].token_ids == want
