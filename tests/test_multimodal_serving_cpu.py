@@ -322,3 +322,60 @@ def test_qwen2_vl_checkpoint_directory_with_its_processor(tmp_path):
                            pad_token_id=1)[0, enc["input_ids"].shape[1]:].tolist()
     assert out.prompt_token_ids == enc["input_ids"][0].tolist()
     assert out.outputs[0].token_ids == want
+
+
+def test_glm4v_checkpoint_directory_with_its_processor(tmp_path):
+    """GLM-4.1V with the HuggingFace processor of its checkpoint directory against
+    transformers' ``generate`` (prefill and decode steps with multimodal rotary positions)."""
+    import numpy as np
+    tr = pytest.importorskip("transformers")
+    pytest.importorskip("tokenizers")
+    from PIL import Image
+    from tokenizers import Tokenizer, decoders, models, pre_tokenizers, trainers
+    tok = Tokenizer(models.BPE(unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False)
+    tok.decoder = decoders.ByteLevel()
+    sp_toks = ["<unk>", "<|endoftext|>", "<|begin_of_image|>", "<|end_of_image|>", "<|image|>",
+               "<|video|>", "<|begin_of_video|>", "<|end_of_video|>"]
+    tok.train_from_iterator(
+        ["describe the picture please"] * 20,
+        trainers.BpeTrainer(vocab_size=300, special_tokens=sp_toks,
+                            initial_alphabet=pre_tokenizers.ByteLevel.alphabet()))
+    fast = tr.PreTrainedTokenizerFast(tokenizer_object=tok, eos_token="<|endoftext|>",
+                                      unk_token="<unk>", pad_token="<|endoftext|>")
+    fast.chat_template = "{% for m in messages %}{{ m['content'] }}{% endfor %}"
+    ids = {t: fast.convert_tokens_to_ids(t) for t in sp_toks}
+    ip = tr.Glm4vImageProcessor(size={"shortest_edge": 28 * 28 * 4, "longest_edge": 28 * 28 * 16},
+                                patch_size=14, merge_size=2, temporal_patch_size=2)
+    proc = tr.Glm4vProcessor(image_processor=ip, tokenizer=fast,
+                             video_processor=tr.Glm4vVideoProcessor(),
+                             chat_template=fast.chat_template)
+    text = dict(vocab_size=len(fast), hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=512,
+                rms_norm_eps=1e-6, tie_word_embeddings=False, attention_bias=True, pad_token_id=1,
+                rope_parameters={"rope_type": "default", "rope_theta": 10000.0,
+                                 "mrope_section": [2, 1, 1], "partial_rotary_factor": 0.5})
+    vision = dict(depth=2, hidden_size=32, intermediate_size=48, num_heads=2, in_channels=3,
+                  image_size=56, patch_size=14, spatial_merge_size=2, temporal_patch_size=2,
+                  out_hidden_size=64, rms_norm_eps=1e-5, attention_bias=True, hidden_act="silu")
+    cfg = tr.Glm4vConfig(text_config=text, vision_config=vision, image_token_id=ids["<|image|>"],
+                         video_token_id=ids["<|video|>"],
+                         image_start_token_id=ids["<|begin_of_image|>"],
+                         image_end_token_id=ids["<|end_of_image|>"])
+    torch.manual_seed(0)
+    hf = tr.Glm4vForConditionalGeneration(cfg).eval().float()
+    d = str(tmp_path)
+    hf.save_pretrained(d, safe_serialization=True)
+    proc.save_pretrained(d)
+    llm = LLM(d, device="cpu", max_num_seqs=4, max_num_batched_tokens=64, max_model_len=256,
+              num_gpu_blocks=64, dtype="float32")
+    assert isinstance(llm.mm_processor, HFProcessorAdapter)
+    img = Image.fromarray(np.random.default_rng(0).integers(0, 255, (60, 90, 3), dtype=np.uint8))
+    prompt = "<|begin_of_image|><|image|><|end_of_image|>describe the picture"
+    out = llm.generate([{"prompt": prompt, "multi_modal_data": {"image": img}}],
+                       SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True))[0]
+    enc = proc(text=[prompt], images=[img], return_tensors="pt")
+    with torch.inference_mode():
+        want = hf.generate(**enc, max_new_tokens=5, do_sample=False,
+                           pad_token_id=1)[0, enc["input_ids"].shape[1]:].tolist()
+    assert out.outputs[0].token_ids == want
