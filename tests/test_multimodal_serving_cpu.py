@@ -379,3 +379,62 @@ def test_glm4v_checkpoint_directory_with_its_processor(tmp_path):
         want = hf.generate(**enc, max_new_tokens=5, do_sample=False,
                            pad_token_id=1)[0, enc["input_ids"].shape[1]:].tolist()
     assert out.outputs[0].token_ids == want
+
+
+@pytest.mark.parametrize("size", [(40, 90), (90, 40), (50, 50)])
+def test_llava_next_checkpoint_directory_with_its_processor(tmp_path, size):
+    """LLaVA-NeXT with its HuggingFace processor (any-resolution views as a 5-D pixel tensor plus
+    the original image size) for wide, tall and square images against transformers."""
+    import numpy as np
+    tr = pytest.importorskip("transformers")
+    pytest.importorskip("tokenizers")
+    from PIL import Image
+    from tokenizers import Tokenizer, decoders, models, pre_tokenizers, trainers
+    tok = Tokenizer(models.BPE(unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False)
+    tok.decoder = decoders.ByteLevel()
+    tok.train_from_iterator(
+        ["describe the picture please"] * 20,
+        trainers.BpeTrainer(vocab_size=300,
+                            special_tokens=["<unk>", "<s>", "</s>", "<image>", "<pad>"],
+                            initial_alphabet=pre_tokenizers.ByteLevel.alphabet()))
+    fast = tr.PreTrainedTokenizerFast(tokenizer_object=tok, bos_token="<s>", eos_token="</s>",
+                                      unk_token="<unk>", pad_token="<pad>")
+    fast.chat_template = "{% for m in messages %}{{ m['content'] }}{% endfor %}"
+    img_tok = fast.convert_tokens_to_ids("<image>")
+    pin = [[28, 56], [56, 28], [56, 56]]
+    ip = tr.LlavaNextImageProcessor(size={"shortest_edge": 28},
+                                    crop_size={"height": 28, "width": 28},
+                                    image_grid_pinpoints=pin)
+    proc = tr.LlavaNextProcessor(image_processor=ip, tokenizer=fast, patch_size=7,
+                                 vision_feature_select_strategy="default", image_token="<image>",
+                                 num_additional_image_tokens=1)
+    cfg = tr.LlavaNextConfig(
+        text_config=dict(model_type="llama", vocab_size=len(fast), hidden_size=64,
+                         intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, max_position_embeddings=512,
+                         tie_word_embeddings=False, rms_norm_eps=1e-6),
+        vision_config=dict(model_type="clip_vision_model", hidden_size=32, intermediate_size=64,
+                           num_hidden_layers=3, num_attention_heads=2, image_size=28,
+                           patch_size=7, hidden_act="quick_gelu", projection_dim=16),
+        image_token_index=img_tok, vision_feature_layer=-2,
+        vision_feature_select_strategy="default", image_grid_pinpoints=pin, image_seq_length=16)
+    torch.manual_seed(0)
+    hf = tr.LlavaNextForConditionalGeneration(cfg).eval().float()
+    with torch.no_grad():
+        hf.model.image_newline.copy_(torch.randn(64) * 0.5)
+    d = str(tmp_path)
+    hf.save_pretrained(d, safe_serialization=True)
+    proc.save_pretrained(d)
+    llm = LLM(d, device="cpu", max_num_seqs=4, max_num_batched_tokens=128, max_model_len=512,
+              num_gpu_blocks=64, dtype="float32")
+    img = Image.fromarray(np.random.default_rng(0).integers(0, 255, (*size, 3), dtype=np.uint8))
+    prompt = "<image>\ndescribe the picture"
+    enc = proc(text=[prompt], images=[img], return_tensors="pt")
+    out = llm.generate([{"prompt": prompt, "multi_modal_data": {"image": img}}],
+                       SamplingParams(max_tokens=4, temperature=0.0, ignore_eos=True))[0]
+    with torch.inference_mode():
+        want = hf.generate(**enc, max_new_tokens=4, do_sample=False,
+                           pad_token_id=4)[0, enc["input_ids"].shape[1]:].tolist()
+    assert out.prompt_token_ids == enc["input_ids"][0].tolist()
+    assert out.outputs[0].token_ids == want
